@@ -1,0 +1,279 @@
+/*
+ * tpw_b200.h -- C ABI of the B200 (sm_100a) pairwise-reduction kernels.
+ *
+ * Every entry point is torch-free: plain device pointers, sizes and a CUDA stream.
+ * Unless a comment says otherwise a call
+ *   - is asynchronous on `stream` (a cudaStream_t passed as void*; NULL = legacy default stream),
+ *   - runs on the calling thread's current CUDA device,
+ *   - allocates no device memory and never synchronises,
+ *   - returns TPW_OK (0) or a tpw_status error; tpw_last_error() then holds a message.
+ * All matrices are dense row-major:  x1 [B,N1,D], x2 [B,N2,D], out/grad [B,N1,N2]
+ * (an unbatched call passes B = 1).  Sizes are int64 so that outputs beyond 2^31
+ * elements are addressed correctly.
+ *
+ * Each declaration cites the interface of inspiros/torchpairwise v0.3.0 that it replaces
+ * (paths relative to that project; OPS = torchpairwise/csrc/ops).
+ */
+#ifndef TPW_B200_H
+#define TPW_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TPW_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define TPW_API __attribute__((visibility("default")))
+#else
+#define TPW_API
+#endif
+
+typedef void *tpw_stream_t;
+
+enum tpw_status {
+    TPW_OK = 0,
+    TPW_ERR_INVALID = 1,     /* bad argument (shape, pointer alignment, enum value) */
+    TPW_ERR_UNSUPPORTED = 2, /* valid request that this build has no kernel for */
+    TPW_ERR_CUDA = 3,        /* a CUDA runtime/driver call failed */
+    TPW_ERR_TIMEOUT = 4      /* a bounded device-side wait gave up (see tpw_device_status) */
+};
+
+enum tpw_dtype {
+    TPW_F32 = 0,
+    TPW_F64 = 1,
+    TPW_I32 = 2, /* accepted by tpw_cmp_reduce_forward only */
+    TPW_I64 = 3  /* accepted by tpw_cmp_reduce_forward only */
+};
+
+/* ---- library ------------------------------------------------------------------------------ */
+
+/* Replaces torchpairwise::_cuda_version / _cuda_arch_flags (csrc/torchpairwise.cpp:28-56). */
+TPW_API int tpw_abi_version(void);
+TPW_API int tpw_cuda_version(void);          /* CUDART_VERSION the library was built with */
+TPW_API const char *tpw_cuda_arch_flags(void); /* "sm_100a" */
+/* Thread-local text of the last failure on this thread ("" when none). */
+TPW_API const char *tpw_last_error(void);
+
+/*
+ * Device-side status word.  Kernels that wait on an mbarrier (TMA, tcgen05) bound the wait;
+ * when a wait gives up the kernel records a non-zero code here and returns early, leaving the
+ * context usable.  tpw_device_status() synchronises `stream`, copies the word to *code and
+ * clears it.  No counterpart in the reference (its kernels never wait).
+ */
+TPW_API int tpw_device_status(int *code, tpw_stream_t stream);
+
+/* ---- L_p family on the CUDA cores ---------------------------------------------------------- */
+
+/*
+ * out[b,i,j] = ( sum_k w[b,k] * |x1[b,i,k] - x2[b,j,k]|^p ) ^ out_exponent       (finite p > 0)
+ * out[b,i,j] =   max_k w[b,k] * |x1[b,i,k] - x2[b,j,k]|                            (p = +inf)
+ * out[b,i,j] =   min_k w[b,k] * |x1[b,i,k] - x2[b,j,k]|                            (p = -inf)
+ * w may be NULL (all ones).  out_exponent = 1/p gives Minkowski / weighted Minkowski,
+ * 1 gives the un-rooted power sum, 1/p - 1 gives the coefficient matrix that the weighted
+ * backward consumes.  p = 1, 2, 3 run multiply-only inner loops; other p use exp2/log2.
+ *
+ * Replaces: at::cdist as called by euclidean/manhattan/minkowski/chebyshev_distances
+ * (OPS/pairwise_metrics.cpp:30,48,167,305); _ppminkowski forward
+ * (OPS/cuda/ppminkowski_kernel.cu:16-59,62-130); _wminkowski forward incl. its `backward`
+ * template flag (OPS/cuda/wminkowski_kernel.cu:16-64,67-143).
+ */
+TPW_API int tpw_lp_forward(int dtype, const void *x1, const void *x2, const void *w, void *out,
+                   int64_t B, int64_t N1, int64_t N2, int64_t D,
+                   double p, double out_exponent, tpw_stream_t stream);
+
+enum tpw_lp_backward_mode {
+    /* ATen cdist backward: aux = forward output o.  p=1: g*sgn(d); p=2: g*d/o;
+       other finite p: g*d*|d|^(p-2)/o^(p-1); +inf: g*sgn(d)*[|d|==o]; all 0 where o==0.
+       (what autograd runs under OPS/pairwise_metrics.cpp:30,48,167,305) */
+    TPW_LP_BWD_CDIST = 0,
+    /* _ppminkowski backward: g*p*|d|^(p-1)*sgn(d); aux unused.
+       (OPS/cuda/ppminkowski_kernel.cu:133-179) */
+    TPW_LP_BWD_PPMINKOWSKI = 1,
+    /* _wminkowski backward w.r.t. x1/x2: g*|d|^(p-1)*w_k*aux*sgn(d) with
+       aux = S^(1/p-1) from tpw_lp_forward(out_exponent = 1/p-1).
+       (OPS/cuda/wminkowski_kernel.cu:146-196) */
+    TPW_LP_BWD_WMINKOWSKI = 2,
+    /* plain contraction grad_x1 = g @ x2, grad_x2 = g^T @ x1 (aux unused, p ignored); the
+       matrix-matrix part of the cosine / correlation / linear-kernel backward
+       (autograd of OPS/pairwise_metrics.cpp:64,121,203). */
+    TPW_LP_BWD_MATMUL = 3
+};
+
+/*
+ * grad_x1[b,i,k] = sum_j coef[b,i,j] * phi(x1[b,i,k] - x2[b,j,k])   and the mirrored
+ * grad_x2[b,j,k] = sum_i coef[b,i,j] * phi(x2[b,j,k] - x1[b,i,k]); every element is
+ * written exactly once (no atomics, fixed summation order, bit-reproducible).
+ * Either grad pointer may be NULL to skip that side.  Finite p only, except
+ * TPW_LP_BWD_CDIST which also takes p = +inf.
+ */
+TPW_API int tpw_lp_backward(int dtype, int mode, const void *grad, const void *aux,
+                    const void *x1, const void *x2, const void *w,
+                    void *grad_x1, void *grad_x2,
+                    int64_t B, int64_t N1, int64_t N2, int64_t D,
+                    double p, tpw_stream_t stream);
+
+/*
+ * grad_w[b,k] = sum_{i,j} grad*aux * |x1-x2|^p / p  (aux as in TPW_LP_BWD_WMINKOWSKI).
+ * `scratch` holds B*N1*D elements of `dtype` (per-row partial sums reduced in a second,
+ * ordered stage).  Replaces OPS/cuda/wminkowski_kernel.cu:198-221.
+ */
+TPW_API int tpw_wminkowski_backward_w(int dtype, const void *grad, const void *aux,
+                              const void *x1, const void *x2, void *grad_w, void *scratch,
+                              int64_t B, int64_t N1, int64_t N2, int64_t D,
+                              double p, tpw_stream_t stream);
+
+/*
+ * Single-coordinate backward of the +-inf variants: for each pair the FIRST k attaining the
+ * extreme of w_k*|d_k| receives the gradient (float atomics; grads must be zero-filled by
+ * the caller).  w/grad_w may be NULL (un-weighted _ppminkowski form).
+ * Replaces OPS/cuda/ppminkowski_kernel.cu:181-218 and OPS/cuda/wminkowski_kernel.cu:223-266.
+ */
+TPW_API int tpw_lp_inf_backward(int dtype, const void *grad, const void *x1, const void *x2, const void *w,
+                        void *grad_x1, void *grad_x2, void *grad_w,
+                        int64_t B, int64_t N1, int64_t N2, int64_t D,
+                        int negative, tpw_stream_t stream);
+
+/* ---- dense-contraction metrics -------------------------------------------------------------- */
+
+enum tpw_dot_epilogue {
+    TPW_DOT_LINEAR = 0,       /* x.y                                  (OPS/pairwise_metrics.cpp:58-65)   */
+    TPW_DOT_COSINE_SIM = 1,   /* x.y/(|x||y|), numerator kept when the denominator is 0 (:112-122)        */
+    TPW_DOT_COSINE_DIST = 2,  /* clip(1 - cosine_sim, 0, 2)           (:51-56)                           */
+    TPW_DOT_ONE_MINUS_SIM = 3,/* 1 - cosine_sim, no clip: correlation on pre-centred rows (:190-204)      */
+    TPW_DOT_SQEUCLIDEAN = 4,  /* max(|x|^2 + |y|^2 - 2 x.y, 0)        (:181-188, contraction form)       */
+    TPW_DOT_EUCLIDEAN = 5     /* sqrt of the above: ATen's matmul form of cdist(p=2) (:24-31)             */
+};
+
+enum tpw_dot_engine {
+    TPW_ENGINE_AUTO = 0,
+    TPW_ENGINE_SIMT_FP32 = 1,   /* CUDA-core tile, exact fp32/fp64 FMA chain */
+    TPW_ENGINE_TCGEN05_BF16X3 = 2 /* TMA-fed tcgen05.mma, bf16 hi/lo split (3 MMAs), fp32 TMEM accumulators */
+};
+
+/*
+ * Cross-term metrics.  Row norms are accumulated inside the kernel from the staged tiles.
+ * fp64 always uses the SIMT engine.
+ */
+TPW_API int tpw_dot_metric_forward(int dtype, int epilogue, int engine,
+                           const void *x1, const void *x2, void *out,
+                           int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream);
+
+/* Bytes of scratch the tcgen05 engine needs for the bf16 hi/lo operand copies (0 for SIMT). */
+TPW_API int64_t tpw_dot_metric_scratch_bytes(int dtype, int engine, int64_t B, int64_t N1, int64_t N2, int64_t D);
+TPW_API int tpw_dot_metric_forward_ws(int dtype, int epilogue, int engine,
+                              const void *x1, const void *x2, void *out, void *scratch, int64_t scratch_bytes,
+                              int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream);
+
+/* Row helpers used by cosine / correlation host code (x.norm(2,-1), x - x.mean(-1):
+   OPS/pairwise_metrics.cpp:118-119,197-201). rows = B*N. */
+TPW_API int tpw_row_center(int dtype, const void *x, void *out, int64_t rows, int64_t D, tpw_stream_t stream);
+TPW_API int tpw_row_norm(int dtype, const void *x, void *norm, int64_t rows, int64_t D, tpw_stream_t stream);
+
+/* ---- boolean family on packed bits ---------------------------------------------------------- */
+
+/*
+ * Packs rows of one-byte booleans (any non-zero byte = 1) into little-endian 32-bit words,
+ * `words_per_row` words per row (>= ceil(D/32), tail bits zero), and writes each row's
+ * population count.  The reference never packs (one byte per bool, one thread per pair:
+ * OPS/cuda/pairwise_binary_kernels.cu:32-53); this is the B200 layout of its inputs.
+ */
+TPW_API int tpw_bitpack(const uint8_t *src, uint32_t *words, int32_t *row_popcount,
+                int64_t rows, int64_t D, int64_t words_per_row, tpw_stream_t stream);
+
+enum tpw_bool_metric {
+    TPW_BOOL_AND_SUM = 0, TPW_BOOL_OR_SUM = 1, TPW_BOOL_XOR_SUM = 2,     /* pwand_sum, pwor_sum, pwxor_sum */
+    TPW_BOOL_EQ_SUM = 3, TPW_BOOL_NE_SUM = 4,                            /* pweq_sum, pwne_sum */
+    TPW_BOOL_EQ_MEAN = 5, TPW_BOOL_NE_MEAN = 6,                          /* pweq_mean, pwne_mean (= hamming) */
+    TPW_BOOL_JACCARD = 7, TPW_BOOL_KULSINSKI = 8, TPW_BOOL_KULCZYNSKI1 = 9,
+    TPW_BOOL_YULE = 10, TPW_BOOL_DICE = 11, TPW_BOOL_ROGERSTANIMOTO = 12,
+    TPW_BOOL_RUSSELLRAO = 13, TPW_BOOL_SOKALMICHENER = 14, TPW_BOOL_SOKALSNEATH = 15,
+    TPW_BOOL_METRIC_COUNT = 16
+};
+
+/*
+ * One AND-popcount tile pass gives n11; with the row popcounts every count of the 2x2
+ * contingency table follows exactly, and the epilogue evaluates the metric with the same
+ * float32 operation order as the reference's composition (no FMA contraction, IEEE divide),
+ * so results are bit-identical.  out is float32 [B,N1,N2].
+ * Replaces pw{and,or,xor,eq,ne}_sum / pw{eq,ne}_mean on bool inputs
+ * (OPS/cuda/pairwise_binary_kernels.cu:144-220) and the compositions at
+ * OPS/pairwise_metrics.cpp:206-243,339-399.
+ */
+TPW_API int tpw_bool_metric_forward(int metric, const uint32_t *x1_words, const uint32_t *x2_words,
+                            const int32_t *x1_popcount, const int32_t *x2_popcount, float *out,
+                            int64_t B, int64_t N1, int64_t N2, int64_t D, int64_t words_per_row,
+                            tpw_stream_t stream);
+
+enum tpw_cmp_op { TPW_CMP_EQ = 0, TPW_CMP_NE = 1 };
+enum tpw_cmp_reduction { TPW_RED_SUM = 0, TPW_RED_MEAN = 1 };
+
+/*
+ * out[b,i,j] = sum_k float(x1[b,i,k] op x2[b,j,k])  (MEAN: divided by float(D)); float32 out.
+ * Non-boolean inputs of hamming_distances / pw{eq,ne}_{sum,mean}
+ * (OPS/pairwise_metrics.cpp:206-213; OPS/cuda/pairwise_binary_kernels.cu:32-53).
+ * dtype: TPW_F32, TPW_F64 (IEEE compare), TPW_I32, TPW_I64.
+ */
+TPW_API int tpw_cmp_reduce_forward(int dtype, int op, int reduction, const void *x1, const void *x2, float *out,
+                           int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream);
+
+/* ---- directed Hausdorff ---------------------------------------------------------------------- */
+
+/*
+ * x1 [B,N1,M1,D], x2 [B,N2,M2,D]  ->  out [B,N1,N2] = sqrt(max_m min_n |x1[m]-x2[n]|^2),
+ * idx1/idx2 int64 [B,N1,N2] = the attaining m and n.  The [M1,M2] matrix is never written:
+ * each thread keeps one x1 point and streams the x2 cloud through shared memory, row minima
+ * are combined with warp shuffles and one 64-bit atomicMax per warp.
+ * Tie rule of the reference loop: n = first n reaching the row minimum, m = LAST m whose
+ * row minimum equals the maximum.  order1/order2 (int64 [B,M1] / [B,M2], may be NULL) give
+ * each point's visiting position when the caller shuffles; ties then follow visiting order.
+ * `scratch` holds tpw_hausdorff_scratch_bytes() bytes and needs no initialisation.
+ * Replaces OPS/cuda/hausdorff_kernel.cu:16-104,107-195.
+ */
+TPW_API int64_t tpw_hausdorff_scratch_bytes(int64_t B, int64_t N1, int64_t N2, int64_t M1);
+TPW_API int tpw_hausdorff_forward(int dtype, const void *x1, const void *x2,
+                          const int64_t *order1, const int64_t *order2,
+                          void *out, int64_t *idx1, int64_t *idx2, void *scratch,
+                          int64_t B, int64_t N1, int64_t N2, int64_t M1, int64_t M2, int64_t D,
+                          tpw_stream_t stream);
+
+/*
+ * grad_x1[b,i,m*,:] += g*(x1[m*]-x2[n*])/out, grad_x2[b,j,n*,:] -= same; the call zero-fills
+ * both gradients first.  Replaces OPS/cuda/hausdorff_kernel.cu:198-246 (the reference re-runs
+ * the forward inside its backward, :283-321; here the caller passes the saved forward results).
+ */
+TPW_API int tpw_hausdorff_backward(int dtype, const void *grad, const void *out,
+                           const int64_t *idx1, const int64_t *idx2,
+                           const void *x1, const void *x2, void *grad_x1, void *grad_x2,
+                           int64_t B, int64_t N1, int64_t N2, int64_t M1, int64_t M2, int64_t D,
+                           tpw_stream_t stream);
+
+/* ---- element-wise safe divide ---------------------------------------------------------------- */
+
+enum tpw_prf_div_mode { TPW_PRF_ZERO = 0, TPW_PRF_IDENTITY = 1 };
+
+/* out = y != 0 ? x/y : (mode == ZERO ? 0 : x).  Replaces OPS/cuda/prf_div_kernel.cu:24-74. */
+TPW_API int tpw_prf_div_forward(int dtype, int mode, const void *x, const void *y, void *out,
+                        int64_t n, tpw_stream_t stream);
+/* grad_x = y != 0 ? g/y : (IDENTITY ? g : 0); grad_y = y != 0 ? -grad_x*x/y : 0.
+   Replaces OPS/cuda/prf_div_kernel.cu:315-366. Either output may be NULL. */
+TPW_API int tpw_prf_div_backward(int dtype, int mode, const void *grad, const void *x, const void *y,
+                         void *grad_x, void *grad_y, int64_t n, tpw_stream_t stream);
+
+/* ---- measured issue peaks (roofline denominators for the CUDA-core kernels) -------------------- */
+
+/*
+ * Runs a register-only microbenchmark on the current device, synchronises, and reports the
+ * sustained rate in operations per second: kind 0 = fp32 FMA lane-operations (scalar FFMA),
+ * 1 = fp32 FMA lane-operations issued as packed fma.rn.f32x2, 2 = 32-bit POPC lane-operations.
+ * No counterpart in the reference.
+ */
+TPW_API int tpw_measure_issue_peak(int kind, double *ops_per_second);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TPW_B200_H */

@@ -1,0 +1,194 @@
+// Library plumbing of the C ABI: versioning, thread-local error text, the device status word,
+// tensor-map encoding through the driver entry point, and the issue-rate microbenchmarks that
+// give the CUDA-core kernels their roofline denominators.
+#include "common.cuh"
+
+#include <mutex>
+#include <string.h>
+
+namespace tpw {
+
+static thread_local char t_error[512] = {0};
+
+char *error_buffer() { return t_error; }
+
+void clear_error() { t_error[0] = 0; }
+
+int fail(int status, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_error, sizeof(t_error), fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+__device__ int g_device_status_word = 0;
+
+static const int kMaxDevices = 64;
+
+int *device_status_ptr() {
+    static int *cache[kMaxDevices] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    if (!cache[dev]) {
+        int *p = nullptr;
+        if (cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_device_status_word) != cudaSuccess) return nullptr;
+        cache[dev] = p;
+    }
+    return cache[dev];
+}
+
+int sm_count() {
+    static int cache[kMaxDevices] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+    if (!cache[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cache[dev] = n;
+    }
+    return cache[dev];
+}
+
+typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                    CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                    CUtensorMapFloatOOBfill);
+
+static encode_tiled_fn resolve_encode_tiled() {
+    static encode_tiled_fn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<encode_tiled_fn>(p);
+    });
+    return fn;
+}
+
+int make_tensor_map_3d(CUtensorMap *map, const void *base, int elem_bytes,
+                       uint64_t dim0, uint64_t dim1, uint64_t dim2,
+                       uint32_t box0, uint32_t box1, bool swizzle128) {
+    encode_tiled_fn encode = resolve_encode_tiled();
+    if (!encode) return fail(TPW_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    CUtensorMapDataType dt;
+    switch (elem_bytes) {
+        case 2: dt = CU_TENSOR_MAP_DATA_TYPE_UINT16; break;
+        case 4: dt = CU_TENSOR_MAP_DATA_TYPE_UINT32; break;
+        case 8: dt = CU_TENSOR_MAP_DATA_TYPE_UINT64; break;
+        default: return fail(TPW_ERR_INVALID, "tensor map: unsupported element size %d", elem_bytes);
+    }
+    if (!aligned16(base)) return fail(TPW_ERR_INVALID, "tensor map: base address is not 16-byte aligned");
+    if ((dim0 * elem_bytes) % 16 != 0) return fail(TPW_ERR_INVALID, "tensor map: row pitch is not a multiple of 16 bytes");
+    if (swizzle128 && box0 * (uint32_t)elem_bytes != 128)
+        return fail(TPW_ERR_INVALID, "tensor map: a 128-byte swizzled box must span 128 bytes");
+    cuuint64_t dims[3] = {dim0, dim1 ? dim1 : 1, dim2 ? dim2 : 1};
+    cuuint64_t strides[2] = {dim0 * (uint64_t)elem_bytes, dim0 * dims[1] * (uint64_t)elem_bytes};
+    cuuint32_t box[3] = {box0, box1, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = encode(map, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(TPW_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return TPW_OK;
+}
+
+// ---- issue-rate microbenchmarks ------------------------------------------------------------------
+template <int KIND>
+__global__ void __launch_bounds__(256) issue_peak_kernel(float *sink, int iters, float seed) {
+    float a[16];
+    uint32_t u[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        a[i] = seed + (float)(threadIdx.x + i);
+        u[i] = __float_as_uint(a[i]) * 2654435761u;
+    }
+    const float m = 1.0000001f, c = 1e-9f;
+    for (int it = 0; it < iters; ++it) {
+        if (KIND == 0) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) a[i] = fmaf(a[i], m, c);
+        } else if (KIND == 1) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int i = 0; i < 16; i += 2) {
+                    uint64_t v, mm, cc;
+                    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(a[i]), "f"(a[i + 1]));
+                    asm("mov.b64 %0, {%1, %1};" : "=l"(mm) : "f"(m));
+                    asm("mov.b64 %0, {%1, %1};" : "=l"(cc) : "f"(c));
+                    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(v) : "l"(v), "l"(mm), "l"(cc));
+                    asm("mov.b64 {%0, %1}, %2;" : "=f"(a[i]), "=f"(a[i + 1]) : "l"(v));
+                }
+        } else {
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) u[i] = __popc(u[i]) + u[(i + 1) & 15];
+        }
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) s += a[i] + (float)u[i];
+    if (s == 123.456f) sink[0] = s; // never true in practice; keeps the chains alive
+}
+
+} // namespace tpw
+
+extern "C" {
+
+int tpw_abi_version(void) { return TPW_ABI_VERSION; }
+int tpw_cuda_version(void) { return CUDART_VERSION; }
+const char *tpw_cuda_arch_flags(void) { return "sm_100a"; }
+const char *tpw_last_error(void) { return tpw::error_buffer(); }
+
+int tpw_device_status(int *code, tpw_stream_t stream) {
+    TPW_CHECK_ARG(code != nullptr, "tpw_device_status: code is NULL");
+    int *p = tpw::device_status_ptr();
+    if (!p) return tpw::fail(TPW_ERR_CUDA, "tpw_device_status: cannot resolve the device status word");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    TPW_CUDA_OK(cudaStreamSynchronize(s));
+    TPW_CUDA_OK(cudaMemcpy(code, p, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*code != 0) TPW_CUDA_OK(cudaMemset(p, 0, sizeof(int)));
+    return TPW_OK;
+}
+
+int tpw_measure_issue_peak(int kind, double *ops_per_second) {
+    TPW_CHECK_ARG(ops_per_second != nullptr, "tpw_measure_issue_peak: output pointer is NULL");
+    TPW_CHECK_ARG(kind >= 0 && kind <= 2, "tpw_measure_issue_peak: kind must be 0, 1 or 2");
+    int *sink_i = tpw::device_status_ptr();
+    if (!sink_i) return tpw::fail(TPW_ERR_CUDA, "tpw_measure_issue_peak: no device");
+    float *sink = reinterpret_cast<float *>(sink_i); // never written (see kernel)
+    const int blocks = tpw::sm_count() * 8, threads = 256, iters = 4096;
+    cudaEvent_t e0, e1;
+    TPW_CUDA_OK(cudaEventCreate(&e0));
+    TPW_CUDA_OK(cudaEventCreate(&e1));
+    float best_ms = 1e30f;
+    for (int rep = 0; rep < 4; ++rep) {
+        cudaEventRecord(e0, 0);
+        if (kind == 0) tpw::issue_peak_kernel<0><<<blocks, threads>>>(sink, iters, 1.0f);
+        else if (kind == 1) tpw::issue_peak_kernel<1><<<blocks, threads>>>(sink, iters, 1.0f);
+        else tpw::issue_peak_kernel<2><<<blocks, threads>>>(sink, iters, 1.0f);
+        cudaEventRecord(e1, 0);
+        cudaError_t e = cudaEventSynchronize(e1);
+        if (e != cudaSuccess) {
+            cudaEventDestroy(e0);
+            cudaEventDestroy(e1);
+            return tpw::fail(TPW_ERR_CUDA, "issue peak kernel failed: %s", cudaGetErrorString(e));
+        }
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        if (rep > 0 && ms < best_ms) best_ms = ms;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    const double ops = (double)blocks * threads * (double)iters * 64.0; // 4 x 16 operations per iteration
+    *ops_per_second = ops / (best_ms * 1e-3);
+    return TPW_OK;
+}
+
+} // extern "C"

@@ -1,0 +1,284 @@
+// Boolean pairwise metrics on bit-packed rows.
+//
+// tpw_bitpack turns one-byte booleans into 32-bit words (bit t of word q = feature 32q + t) and
+// records each row's population count.  The tile kernel then needs a single AND-popcount per word
+// pair: with n11 = |x & y| and the row counts |x|, |y| every cell of the 2x2 contingency table
+// is an exact integer, and the epilogue turns it into the requested metric with the float32
+// operation order of the reference's tensor compositions (each *, +, -, / rounded separately, no
+// FMA contraction), which makes the float32 output bit-identical.
+//
+// Tiling is the same as the CUDA-core L_p forward: 128 x 128 outputs per CTA, 8 x 8 per thread,
+// operand tiles of 128 rows x 32 words staged by TMA with the 128-byte swizzle (three-stage
+// mbarrier ring), conflict-free 128-bit shared loads.  Within a 16-byte chunk three of the four
+// AND words go through a carry-save adder first, so four words cost three POPCs.
+#include "common.cuh"
+
+namespace tpw {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kStages = 3;
+constexpr int R = 8;
+constexpr int TILE = 128;
+constexpr int KC = 32; // words per 128-byte chunk row
+constexpr int TILE_BYTES = TILE * 128;
+constexpr int OFF_BAR = kStages * 2 * TILE_BYTES;
+constexpr int SMEM_BYTES = OFF_BAR + kStages * 8;
+constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
+
+struct BoolParams {
+    const uint32_t *x1, *x2;
+    const int32_t *pop1, *pop2;
+    float *out;
+    long long B, N1, N2, D, W;
+    long long tiles_i, tiles_j;
+    int metric;
+    int *status;
+};
+
+// One row per warp: lane l tests byte 32q + l, the ballot is word q.
+__global__ void bitpack_kernel(const uint8_t *__restrict__ src, uint32_t *__restrict__ words,
+                               int32_t *__restrict__ row_pop, long long rows, long long D, long long W) {
+    const int lane = threadIdx.x & 31;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long row = warp; row < rows; row += nwarps) {
+        const uint8_t *s = src + row * D;
+        int pop = 0;
+        for (long long q = 0; q < W; ++q) {
+            const long long k = q * 32 + lane;
+            const bool bit = (k < D) && (s[k] != 0);
+            const uint32_t word = __ballot_sync(0xffffffffu, bit);
+            if (lane == 0) words[row * W + q] = word;
+            pop += __popc(word);
+        }
+        if (lane == 0) row_pop[row] = pop;
+    }
+}
+
+__device__ __forceinline__ float bool_epilogue(int metric, int n11, int a, int b, int D) {
+    const int nxor_i = a + b - 2 * n11;
+    const int nor_i = a + b - n11;
+    const float fand = (float)n11, fxor = (float)nxor_i, f_or = (float)nor_i;
+    const float feq = (float)(D - nxor_i), fD = (float)D;
+    switch (metric) {
+        case TPW_BOOL_AND_SUM: return fand;
+        case TPW_BOOL_OR_SUM: return f_or;
+        case TPW_BOOL_XOR_SUM:
+        case TPW_BOOL_NE_SUM: return fxor;
+        case TPW_BOOL_EQ_SUM: return feq;
+        case TPW_BOOL_EQ_MEAN: return __fdiv_rn(feq, fD);
+        case TPW_BOOL_NE_MEAN: return __fdiv_rn(fxor, fD);
+        case TPW_BOOL_JACCARD: return f_or != 0.f ? __fdiv_rn(fxor, f_or) : 0.f;
+        case TPW_BOOL_KULSINSKI: return __fdiv_rn(__fadd_rn(__fsub_rn(fxor, fand), fD), __fadd_rn(fxor, fD));
+        case TPW_BOOL_KULCZYNSKI1: return __fdiv_rn(fand, fxor);
+        case TPW_BOOL_YULE: {
+            const float half_r = __fmul_rn((float)(a - n11), (float)(b - n11));
+            const float den = __fadd_rn(__fmul_rn(fand, (float)(D - nor_i)), half_r);
+            return den != 0.f ? __fdiv_rn(__fmul_rn(2.f, half_r), den) : 0.f;
+        }
+        case TPW_BOOL_DICE: return __fdiv_rn(fxor, __fadd_rn(__fmul_rn(2.f, fand), fxor));
+        case TPW_BOOL_ROGERSTANIMOTO:
+        case TPW_BOOL_SOKALMICHENER: {
+            const float r2 = __fmul_rn(2.f, fxor);
+            return __fdiv_rn(r2, __fadd_rn(feq, r2));
+        }
+        case TPW_BOOL_RUSSELLRAO: return __fdiv_rn(__fsub_rn(fD, fand), fD);
+        case TPW_BOOL_SOKALSNEATH: {
+            const float r2 = __fmul_rn(2.f, fxor);
+            return __fdiv_rn(r2, __fadd_rn(fand, r2));
+        }
+        default: return 0.f;
+    }
+}
+
+template <bool USE_TMA>
+__global__ void __launch_bounds__(kThreads, 2)
+bool_popcount_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constant__ CUtensorMap map2,
+                     const BoolParams P) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + OFF_BAR);
+
+    const int tid = threadIdx.x;
+    const uint32_t ti = tid >> 4, tj = tid & 15;
+    long long tile = blockIdx.x;
+    const long long tjx = tile % P.tiles_j;
+    tile /= P.tiles_j;
+    const long long tix = tile % P.tiles_i;
+    const long long b = tile / P.tiles_i;
+    const long long i0 = tix * TILE, j0 = tjx * TILE;
+    const uint32_t *x1 = P.x1 + b * P.N1 * P.W;
+    const uint32_t *x2 = P.x2 + b * P.N2 * P.W;
+    const int nchunks = (int)((P.W + KC - 1) / KC);
+
+    int acc[R][R];
+#pragma unroll
+    for (int a = 0; a < R; ++a)
+#pragma unroll
+        for (int c = 0; c < R; ++c) acc[a][c] = 0;
+
+    if (USE_TMA) {
+        if (tid == 0) {
+#pragma unroll
+            for (int s = 0; s < kStages; ++s) mbar_init(&full[s], 1);
+            mbar_init_fence();
+            tma_prefetch_descriptor(&map1);
+            tma_prefetch_descriptor(&map2);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            for (int c = 0; c < kStages - 1 && c < nchunks; ++c) {
+                mbar_expect_tx(&full[c], 2 * TILE_BYTES);
+                tma_load_3d(smem + (2 * c) * TILE_BYTES, &map1, &full[c], c * KC, (int)i0, (int)b);
+                tma_load_3d(smem + (2 * c + 1) * TILE_BYTES, &map2, &full[c], c * KC, (int)j0, (int)b);
+            }
+        }
+    }
+
+    int failed = 0;
+    for (int t = 0; t < nchunks; ++t) {
+        int stage;
+        if (USE_TMA) {
+            if (__syncthreads_or(failed)) {
+                if (tid == 0 && P.status) atomicCAS(P.status, 0, (3 << 16) | 1);
+                return;
+            }
+            const int nxt = t + kStages - 1;
+            if (tid == 0 && nxt < nchunks) {
+                const int ns = nxt % kStages;
+                mbar_expect_tx(&full[ns], 2 * TILE_BYTES);
+                tma_load_3d(smem + (2 * ns) * TILE_BYTES, &map1, &full[ns], nxt * KC, (int)i0, (int)b);
+                tma_load_3d(smem + (2 * ns + 1) * TILE_BYTES, &map2, &full[ns], nxt * KC, (int)j0, (int)b);
+            }
+            stage = t % kStages;
+            if (!mbar_wait_bounded(&full[stage], (uint32_t)((t / kStages) & 1))) failed = 1;
+        } else {
+            stage = 0;
+            __syncthreads();
+            for (int e = tid; e < 2 * TILE * KC; e += kThreads) {
+                const int which = e / (TILE * KC), r = (e / KC) % TILE, kk = e % KC;
+                const long long row = (which ? j0 : i0) + r, q = (long long)t * KC + kk;
+                const long long nrows = which ? P.N2 : P.N1;
+                const uint32_t *src = which ? x2 : x1;
+                const uint32_t v = (row < nrows && q < P.W) ? src[row * P.W + q] : 0u;
+                *reinterpret_cast<uint32_t *>(smem + which * TILE_BYTES + swz128(r, kk / 4) + (kk % 4) * 4) = v;
+            }
+            __syncthreads();
+        }
+        const unsigned char *xs = smem + (2 * stage) * TILE_BYTES;
+        const unsigned char *ys = xs + TILE_BYTES;
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+            uint4 xa[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+                xa[r] = *reinterpret_cast<const uint4 *>(xs + (ti + 16 * r) * 128u + ((c ^ (ti & 7u)) << 4));
+#pragma unroll
+            for (int rj = 0; rj < R; ++rj) {
+                const uint4 yb = *reinterpret_cast<const uint4 *>(ys + (tj + 16 * rj) * 128u + ((c ^ (tj & 7u)) << 4));
+#pragma unroll
+                for (int ri = 0; ri < R; ++ri) {
+                    const uint32_t a0 = xa[ri].x & yb.x, a1 = xa[ri].y & yb.y, a2 = xa[ri].z & yb.z, a3 = xa[ri].w & yb.w;
+                    const uint32_t sum = a0 ^ a1 ^ a2;                      // carry-save adder: ones
+                    const uint32_t carry = (a0 & a1) | (a2 & (a0 ^ a1));    // twos
+                    acc[ri][rj] += __popc(sum) + 2 * __popc(carry) + __popc(a3);
+                }
+            }
+        }
+    }
+    if (USE_TMA) {
+        if (__syncthreads_or(failed)) {
+            if (tid == 0 && P.status) atomicCAS(P.status, 0, (3 << 16) | 2);
+            return;
+        }
+    }
+
+    float *out = P.out + b * P.N1 * P.N2;
+    const int32_t *pop1 = P.pop1 + b * P.N1, *pop2 = P.pop2 + b * P.N2;
+    int pb[R];
+#pragma unroll
+    for (int rj = 0; rj < R; ++rj) {
+        const long long j = j0 + tj + 16 * rj;
+        pb[rj] = j < P.N2 ? pop2[j] : 0;
+    }
+#pragma unroll
+    for (int ri = 0; ri < R; ++ri) {
+        const long long i = i0 + ti + 16 * ri;
+        if (i >= P.N1) continue;
+        const int pa = pop1[i];
+#pragma unroll
+        for (int rj = 0; rj < R; ++rj) {
+            const long long j = j0 + tj + 16 * rj;
+            if (j >= P.N2) continue;
+            out[i * P.N2 + j] = bool_epilogue(P.metric, acc[ri][rj], pa, pb[rj], (int)P.D);
+        }
+    }
+}
+
+} // namespace
+} // namespace tpw
+
+using namespace tpw;
+
+extern "C" int tpw_bitpack(const uint8_t *src, uint32_t *words, int32_t *row_popcount,
+                           int64_t rows, int64_t D, int64_t words_per_row, tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(rows >= 0 && D >= 0, "tpw_bitpack: negative size");
+    TPW_CHECK_ARG(words_per_row * 32 >= D, "tpw_bitpack: words_per_row (%lld) is too small for D = %lld",
+                  (long long)words_per_row, (long long)D);
+    if (rows == 0) return TPW_OK;
+    TPW_CHECK_ARG(words && row_popcount && (src || D == 0), "tpw_bitpack: NULL pointer");
+    TPW_CHECK_ARG(words_per_row > 0, "tpw_bitpack: words_per_row must be positive");
+    const int threads = 256;
+    long long blocks = (rows * 32 + threads - 1) / threads;
+    const long long cap = (long long)sm_count() * 32;
+    if (blocks > cap) blocks = cap;
+    bitpack_kernel<<<(unsigned)blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(src, words, row_popcount, rows, D,
+                                                                                         words_per_row);
+    TPW_LAUNCH_OK("bitpack_kernel");
+    return TPW_OK;
+}
+
+extern "C" int tpw_bool_metric_forward(int metric, const uint32_t *x1_words, const uint32_t *x2_words,
+                                       const int32_t *x1_popcount, const int32_t *x2_popcount, float *out,
+                                       int64_t B, int64_t N1, int64_t N2, int64_t D, int64_t words_per_row,
+                                       tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(metric >= 0 && metric < TPW_BOOL_METRIC_COUNT, "tpw_bool_metric_forward: unknown metric %d", metric);
+    TPW_CHECK_ARG(B >= 0 && N1 >= 0 && N2 >= 0 && D >= 0, "tpw_bool_metric_forward: negative size");
+    if (B == 0 || N1 == 0 || N2 == 0) return TPW_OK;
+    TPW_CHECK_ARG(D > 0 && D <= (1 << 24), "tpw_bool_metric_forward: D must be in [1, 2^24] (exact float32 counts)");
+    TPW_CHECK_ARG(words_per_row * 32 >= D, "tpw_bool_metric_forward: words_per_row too small");
+    TPW_CHECK_ARG(x1_words && x2_words && x1_popcount && x2_popcount && out, "tpw_bool_metric_forward: NULL pointer");
+    BoolParams P;
+    memset(&P, 0, sizeof(P));
+    P.x1 = x1_words; P.x2 = x2_words; P.pop1 = x1_popcount; P.pop2 = x2_popcount; P.out = out;
+    P.B = B; P.N1 = N1; P.N2 = N2; P.D = D; P.W = words_per_row;
+    P.metric = metric;
+    P.tiles_i = (N1 + TILE - 1) / TILE;
+    P.tiles_j = (N2 + TILE - 1) / TILE;
+    const long long tiles = B * P.tiles_i * P.tiles_j;
+    TPW_CHECK_ARG(tiles < (1ll << 31), "tpw_bool_metric_forward: too many tiles");
+    TPW_CHECK_ARG(N1 < (1ll << 31) && N2 < (1ll << 31) && B < (1ll << 31) && words_per_row < (1ll << 31),
+                  "tpw_bool_metric_forward: a dimension exceeds 2^31-1");
+    P.status = device_status_ptr();
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool tma_ok = aligned16(x1_words) && aligned16(x2_words) && words_per_row % 4 == 0;
+    CUtensorMap m1, m2;
+    memset(&m1, 0, sizeof(m1));
+    memset(&m2, 0, sizeof(m2));
+    if (tma_ok) {
+        int st = make_tensor_map_3d(&m1, x1_words, 4, words_per_row, N1, B, KC, TILE, true);
+        if (st != TPW_OK) return st;
+        st = make_tensor_map_3d(&m2, x2_words, 4, words_per_row, N2, B, KC, TILE, true);
+        if (st != TPW_OK) return st;
+        TPW_CUDA_OK(cudaFuncSetAttribute(bool_popcount_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
+        bool_popcount_kernel<true><<<(unsigned)tiles, kThreads, SMEM_ALLOC, s>>>(m1, m2, P);
+    } else {
+        TPW_CUDA_OK(cudaFuncSetAttribute(bool_popcount_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
+        bool_popcount_kernel<false><<<(unsigned)tiles, kThreads, SMEM_ALLOC, s>>>(m1, m2, P);
+    }
+    TPW_LAUNCH_OK("bool_popcount_kernel");
+    return TPW_OK;
+}

@@ -1,0 +1,120 @@
+// Shared host/device helpers of the sm_100a pairwise kernels: error plumbing, launch checks,
+// and thin wrappers over the PTX used for TMA (cp.async.bulk.tensor) and mbarriers.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+
+#include "../../include/tpw_b200.h"
+
+namespace tpw {
+
+// ---- host-side error text (thread local) ------------------------------------------------------
+char *error_buffer();                       // 512 bytes, thread local
+int fail(int status, const char *fmt, ...); // formats into error_buffer(), returns status
+void clear_error();
+
+#define TPW_CHECK_ARG(cond, ...)                                  \
+    do {                                                          \
+        if (!(cond)) return ::tpw::fail(TPW_ERR_INVALID, __VA_ARGS__); \
+    } while (0)
+
+#define TPW_CUDA_OK(expr)                                                                     \
+    do {                                                                                      \
+        cudaError_t _e = (expr);                                                              \
+        if (_e != cudaSuccess)                                                                \
+            return ::tpw::fail(TPW_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e)); \
+    } while (0)
+
+#define TPW_LAUNCH_OK(name)                                                                      \
+    do {                                                                                         \
+        cudaError_t _e = cudaGetLastError();                                                     \
+        if (_e != cudaSuccess)                                                                   \
+            return ::tpw::fail(TPW_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(_e)); \
+    } while (0)
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Device status word shared by all kernels of the library (one per device that loads it).
+// Codes: 0 = fine, otherwise (kernel id << 16) | site.  Kernels receive its device address
+// as an argument; NULL is returned when the address cannot be resolved.
+int *device_status_ptr();
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+// Builds a tiled tensor map over a dense row-major [dim2, dim1, dim0] tensor (dim0 innermost).
+// elem_bytes is 2, 4 or 8; swizzle128 selects CU_TENSOR_MAP_SWIZZLE_128B (inner box must span
+// exactly 128 bytes) or no swizzle.  Returns a tpw_status.
+int make_tensor_map_3d(CUtensorMap *map, const void *base, int elem_bytes,
+                       uint64_t dim0, uint64_t dim1, uint64_t dim2,
+                       uint32_t box0, uint32_t box1, bool swizzle128);
+
+#ifdef __CUDACC__
+// ---- device-side PTX wrappers -----------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+// Makes freshly initialised mbarriers visible to the async (TMA / tensor-core) proxy.
+__device__ __forceinline__ void mbar_init_fence() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: returns false after `limit` failed polls (each poll may itself block for a
+// hardware-defined short time), so a lost TMA completion can never hang the GPU.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, uint32_t limit = (1u << 22)) {
+    for (uint32_t it = 0; it < limit; ++it)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// 3-D tiled TMA load global -> shared, completion on an mbarrier.  c0 is the innermost
+// coordinate and must keep c0 * element size a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, uint64_t *bar,
+                                            int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(smem_u32(dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+// Byte offset of 16-byte chunk `chunk` (0..7) of row `row` inside a tile whose rows are 128
+// bytes and which was written with the 128-byte swizzle (tile base 1024-byte aligned).
+__device__ __forceinline__ uint32_t swz128(uint32_t row, uint32_t chunk) {
+    return row * 128u + ((chunk ^ (row & 7u)) << 4);
+}
+#endif // __CUDACC__
+
+} // namespace tpw

@@ -1,0 +1,158 @@
+// Small memory-bound helpers of the pairwise path: the "safe divide" and its gradient, and the
+// per-row mean-centering / L2 norm that cosine and correlation need before the contraction.
+#include "common.cuh"
+
+#include <math.h>
+
+namespace tpw {
+namespace {
+
+constexpr int kThreads = 256;
+
+template <typename T>
+__global__ void prf_div_forward_kernel(const T *x, const T *y, T *out, long long n, int identity) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const T a = x[i], b = y[i];
+        out[i] = b != T(0) ? a / b : (identity ? a : T(0));
+    }
+}
+
+template <typename T>
+__global__ void prf_div_backward_kernel(const T *g, const T *x, const T *y, T *gx, T *gy, long long n, int identity) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const T go = g[i], b = y[i];
+        const bool nz = b != T(0);
+        const T gs = nz ? go / b : (identity ? go : T(0));
+        if (gx) gx[i] = gs;
+        if (gy) gy[i] = nz ? -gs * x[i] / b : T(0);
+    }
+}
+
+// One warp per row: mean or sum of squares by shuffle reduction, rows of any length.
+template <typename T, bool CENTER>
+__global__ void row_stat_kernel(const T *x, T *out, long long rows, long long D) {
+    const int lane = threadIdx.x & 31;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long r = warp; r < rows; r += nwarps) {
+        const T *row = x + r * D;
+        T s = T(0);
+        for (long long k = lane; k < D; k += 32) {
+            const T v = row[k];
+            s += CENTER ? v : v * v;
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+        if (CENTER) {
+            const T mean = s / (T)D;
+            for (long long k = lane; k < D; k += 32) out[r * D + k] = row[k] - mean;
+        } else if (lane == 0) {
+            out[r] = (T)sqrt((double)s);
+        }
+    }
+}
+
+inline unsigned grid_for(long long n) {
+    long long blocks = (n + kThreads - 1) / kThreads;
+    const long long cap = (long long)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (unsigned)blocks;
+}
+
+} // namespace
+} // namespace tpw
+
+using namespace tpw;
+
+extern "C" int tpw_prf_div_forward(int dtype, int mode, const void *x, const void *y, void *out,
+                                   int64_t n, tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(dtype == TPW_F32 || dtype == TPW_F64, "tpw_prf_div_forward: dtype must be TPW_F32 or TPW_F64");
+    TPW_CHECK_ARG(mode == TPW_PRF_ZERO || mode == TPW_PRF_IDENTITY, "tpw_prf_div_forward: bad mode %d", mode);
+    TPW_CHECK_ARG(n >= 0, "tpw_prf_div_forward: negative size");
+    if (n == 0) return TPW_OK;
+    TPW_CHECK_ARG(x && y && out, "tpw_prf_div_forward: NULL pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == TPW_F32)
+        prf_div_forward_kernel<float><<<grid_for(n), kThreads, 0, s>>>((const float *)x, (const float *)y, (float *)out, n, mode == TPW_PRF_IDENTITY);
+    else
+        prf_div_forward_kernel<double><<<grid_for(n), kThreads, 0, s>>>((const double *)x, (const double *)y, (double *)out, n, mode == TPW_PRF_IDENTITY);
+    TPW_LAUNCH_OK("prf_div_forward_kernel");
+    return TPW_OK;
+}
+
+extern "C" int tpw_prf_div_backward(int dtype, int mode, const void *grad, const void *x, const void *y,
+                                    void *grad_x, void *grad_y, int64_t n, tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(dtype == TPW_F32 || dtype == TPW_F64, "tpw_prf_div_backward: dtype must be TPW_F32 or TPW_F64");
+    TPW_CHECK_ARG(mode == TPW_PRF_ZERO || mode == TPW_PRF_IDENTITY, "tpw_prf_div_backward: bad mode %d", mode);
+    TPW_CHECK_ARG(n >= 0, "tpw_prf_div_backward: negative size");
+    if (n == 0 || (!grad_x && !grad_y)) return TPW_OK;
+    TPW_CHECK_ARG(grad && x && y, "tpw_prf_div_backward: NULL pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == TPW_F32)
+        prf_div_backward_kernel<float><<<grid_for(n), kThreads, 0, s>>>((const float *)grad, (const float *)x, (const float *)y,
+                                                                        (float *)grad_x, (float *)grad_y, n, mode == TPW_PRF_IDENTITY);
+    else
+        prf_div_backward_kernel<double><<<grid_for(n), kThreads, 0, s>>>((const double *)grad, (const double *)x, (const double *)y,
+                                                                         (double *)grad_x, (double *)grad_y, n, mode == TPW_PRF_IDENTITY);
+    TPW_LAUNCH_OK("prf_div_backward_kernel");
+    return TPW_OK;
+}
+
+extern "C" int tpw_row_center(int dtype, const void *x, void *out, int64_t rows, int64_t D, tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(dtype == TPW_F32 || dtype == TPW_F64, "tpw_row_center: dtype must be TPW_F32 or TPW_F64");
+    TPW_CHECK_ARG(rows >= 0 && D >= 0, "tpw_row_center: negative size");
+    if (rows == 0 || D == 0) return TPW_OK;
+    TPW_CHECK_ARG(x && out, "tpw_row_center: NULL pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == TPW_F32) row_stat_kernel<float, true><<<grid_for(rows * 32), kThreads, 0, s>>>((const float *)x, (float *)out, rows, D);
+    else row_stat_kernel<double, true><<<grid_for(rows * 32), kThreads, 0, s>>>((const double *)x, (double *)out, rows, D);
+    TPW_LAUNCH_OK("row_stat_kernel");
+    return TPW_OK;
+}
+
+extern "C" int tpw_row_norm(int dtype, const void *x, void *norm, int64_t rows, int64_t D, tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(dtype == TPW_F32 || dtype == TPW_F64, "tpw_row_norm: dtype must be TPW_F32 or TPW_F64");
+    TPW_CHECK_ARG(rows >= 0 && D >= 0, "tpw_row_norm: negative size");
+    if (rows == 0) return TPW_OK;
+    TPW_CHECK_ARG(norm && (x || D == 0), "tpw_row_norm: NULL pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == TPW_F32) row_stat_kernel<float, false><<<grid_for(rows * 32), kThreads, 0, s>>>((const float *)x, (float *)norm, rows, D);
+    else row_stat_kernel<double, false><<<grid_for(rows * 32), kThreads, 0, s>>>((const double *)x, (double *)norm, rows, D);
+    TPW_LAUNCH_OK("row_stat_kernel");
+    return TPW_OK;
+}
+
+// Dispatcher of the cross-term metrics: SIMT engine here, tensor-core engine in gemm_tcgen05.cu.
+extern "C" int tpw_dot_metric_forward_simt(int dtype, int epilogue, const void *x1, const void *x2, void *out,
+                                           int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream);
+
+extern "C" int tpw_dot_metric_forward(int dtype, int epilogue, int engine,
+                                      const void *x1, const void *x2, void *out,
+                                      int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream) {
+    clear_error();
+    if (engine == TPW_ENGINE_AUTO || engine == TPW_ENGINE_SIMT_FP32)
+        return tpw_dot_metric_forward_simt(dtype, epilogue, x1, x2, out, B, N1, N2, D, stream);
+    return fail(TPW_ERR_UNSUPPORTED, "tpw_dot_metric_forward: engine %d needs scratch; call tpw_dot_metric_forward_ws", engine);
+}
+
+extern "C" int64_t tpw_dot_metric_scratch_bytes(int dtype, int engine, int64_t B, int64_t N1, int64_t N2, int64_t D) {
+    (void)dtype; (void)engine; (void)B; (void)N1; (void)N2; (void)D;
+    return 0;
+}
+
+extern "C" int tpw_dot_metric_forward_ws(int dtype, int epilogue, int engine,
+                                         const void *x1, const void *x2, void *out, void *scratch, int64_t scratch_bytes,
+                                         int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream) {
+    (void)scratch; (void)scratch_bytes;
+    clear_error();
+    if (engine == TPW_ENGINE_AUTO || engine == TPW_ENGINE_SIMT_FP32)
+        return tpw_dot_metric_forward_simt(dtype, epilogue, x1, x2, out, B, N1, N2, D, stream);
+    return fail(TPW_ERR_UNSUPPORTED, "tpw_dot_metric_forward_ws: engine %d is not built", engine);
+}

@@ -1,0 +1,362 @@
+// Directed Hausdorff distance between point sets, fused so that the [M1, M2] distance matrix is
+// never written.
+//
+// Fast path (float32, D <= 4): a CTA of 256 threads owns 1024 points of x1 for one set pair;
+// each thread keeps four of them in registers and streams the whole x2 cloud through shared
+// memory (one broadcast 128-bit load per x2 point feeds four point pairs).  Only the running row
+// minimum is kept in the hot loop.  Row minima are packed as (float bits << 32 | visiting
+// position of m), reduced with warp shuffles, and merged across CTAs with one 64-bit atomicMax
+// per warp: the float bits of a non-negative value order like the value, and the low word makes
+// the LAST visited m win ties, which is the rule of the reference loop.  A finishing kernel then
+// recomputes the single winning row to find the FIRST visited n reaching its minimum, and writes
+// sqrt(max), m*, n*.
+//
+// Squared distances are accumulated coordinate by coordinate with separately rounded multiply and
+// add (no FMA contraction), i.e. bit-for-bit what the reference's CPU loop computes, so the
+// selected indices agree with it whenever they are determined at all.
+//
+// Any other dtype / feature count runs a plain one-CTA-per-set-pair kernel with the same rules.
+#include "common.cuh"
+
+#include <math.h>
+
+namespace tpw {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int PM = 4;            // x1 points per thread
+constexpr int CHUNK = 2048;      // x2 points staged per pass (float4 each: 32 KB)
+
+__device__ __forceinline__ float sqdist_exact(const float *a, const float *b, int D) {
+    float d = 0.f;
+    for (int k = 0; k < D; ++k) {
+        const float diff = __fsub_rn(a[k], b[k]);
+        d = __fadd_rn(d, __fmul_rn(diff, diff));
+    }
+    return d;
+}
+__device__ __forceinline__ double sqdist_exact(const double *a, const double *b, int D) {
+    double d = 0.0;
+    for (int k = 0; k < D; ++k) {
+        const double diff = __dsub_rn(a[k], b[k]);
+        d = __dadd_rn(d, __dmul_rn(diff, diff));
+    }
+    return d;
+}
+
+struct HdParams {
+    const void *x1, *x2;
+    const long long *order1, *order2;
+    void *out;
+    long long *idx1, *idx2;
+    unsigned long long *keys;
+    long long B, N1, N2, M1, M2, D;
+    long long mtiles;
+};
+
+// keys[pair] = max over m of (bits(rowmin) << 32 | position(m))
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+hausdorff_rowmin_kernel(const HdParams P) {
+    __shared__ float4 pts[CHUNK];
+    const int tid = threadIdx.x;
+    long long blk = blockIdx.x;
+    const long long mt = blk % P.mtiles;
+    blk /= P.mtiles;
+    const long long pair = blk; // (b*N1 + i)*N2 + j
+    const long long j = pair % P.N2;
+    const long long bi = pair / P.N2;
+    const long long b = bi / P.N1;
+    const float *x1 = reinterpret_cast<const float *>(P.x1) + bi * P.M1 * D;
+    const float *x2 = reinterpret_cast<const float *>(P.x2) + (b * P.N2 + j) * P.M2 * D;
+
+    float px[PM][D];
+    float rowmin[PM];
+    long long mm[PM];
+#pragma unroll
+    for (int q = 0; q < PM; ++q) {
+        mm[q] = mt * (kThreads * PM) + q * kThreads + tid;
+        rowmin[q] = INFINITY;
+#pragma unroll
+        for (int k = 0; k < D; ++k) px[q][k] = mm[q] < P.M1 ? x1[mm[q] * D + k] : 0.f;
+    }
+
+    for (long long n0 = 0; n0 < P.M2; n0 += CHUNK) {
+        const int cnt = (int)((P.M2 - n0) < CHUNK ? (P.M2 - n0) : CHUNK);
+        __syncthreads();
+        for (int e = tid; e < cnt; e += kThreads) {
+            const float *s = x2 + (n0 + e) * D;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            v.x = s[0];
+            if (D > 1) v.y = s[1];
+            if (D > 2) v.z = s[2];
+            if (D > 3) v.w = s[3];
+            pts[e] = v;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int e = 0; e < cnt; ++e) {
+            const float4 v = pts[e];
+            const float c[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < PM; ++q) {
+                float d = 0.f;
+#pragma unroll
+                for (int k = 0; k < D; ++k) {
+                    const float diff = __fsub_rn(px[q][k], c[k]);
+                    d = __fadd_rn(d, __fmul_rn(diff, diff));
+                }
+                rowmin[q] = fminf(rowmin[q], d);
+            }
+        }
+    }
+
+    unsigned long long key = 0ull;
+#pragma unroll
+    for (int q = 0; q < PM; ++q) {
+        if (mm[q] < P.M1) {
+            const unsigned long long pos =
+                (unsigned long long)(P.order1 ? P.order1[b * P.M1 + mm[q]] : mm[q]);
+            const unsigned long long kq = ((unsigned long long)__float_as_uint(rowmin[q]) << 32) | (pos & 0xffffffffull);
+            key = kq > key ? kq : key;
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, off);
+        key = other > key ? other : key;
+    }
+    if ((tid & 31) == 0) atomicMax(P.keys + pair, key);
+}
+
+// One CTA per set pair: decode the winning m, recompute its row, pick the first visited n.
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+hausdorff_finish_kernel(const HdParams P) {
+    __shared__ unsigned long long best;
+    __shared__ long long mstar_s;
+    const int tid = threadIdx.x;
+    const long long pair = blockIdx.x;
+    const long long j = pair % P.N2;
+    const long long bi = pair / P.N2;
+    const long long b = bi / P.N1;
+    const float *x1 = reinterpret_cast<const float *>(P.x1) + bi * P.M1 * D;
+    const float *x2 = reinterpret_cast<const float *>(P.x2) + (b * P.N2 + j) * P.M2 * D;
+    const unsigned long long key = P.keys[pair];
+    const unsigned int pos = (unsigned int)(key & 0xffffffffull);
+    if (tid == 0) {
+        best = ~0ull;
+        mstar_s = P.order1 ? -1 : (long long)pos;
+    }
+    __syncthreads();
+    if (P.order1) {
+        for (long long m = tid; m < P.M1; m += kThreads)
+            if ((unsigned int)P.order1[b * P.M1 + m] == pos) mstar_s = m;
+        __syncthreads();
+    }
+    const long long mstar = mstar_s;
+    float a[D];
+#pragma unroll
+    for (int k = 0; k < D; ++k) a[k] = (mstar >= 0 && mstar < P.M1) ? x1[mstar * D + k] : 0.f;
+    unsigned long long mine = ~0ull;
+    for (long long n = tid; n < P.M2; n += kThreads) {
+        float c[D];
+#pragma unroll
+        for (int k = 0; k < D; ++k) c[k] = x2[n * D + k];
+        const float d = sqdist_exact(a, c, D);
+        const unsigned long long p2 = (unsigned long long)(P.order2 ? P.order2[b * P.M2 + n] : n);
+        const unsigned long long kq = ((unsigned long long)__float_as_uint(d) << 32) | (p2 & 0xffffffffull);
+        mine = kq < mine ? kq : mine;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, mine, off);
+        mine = other < mine ? other : mine;
+    }
+    if ((tid & 31) == 0) atomicMin(&best, mine);
+    __syncthreads();
+    const unsigned int npos = (unsigned int)(best & 0xffffffffull);
+    if (P.order2) {
+        for (long long n = tid; n < P.M2; n += kThreads)
+            if ((unsigned int)P.order2[b * P.M2 + n] == npos) P.idx2[pair] = n;
+    } else if (tid == 0) {
+        P.idx2[pair] = P.M2 > 0 ? (long long)npos : 0;
+    }
+    if (tid == 0) {
+        const float cmax = __uint_as_float((unsigned int)(key >> 32));
+        reinterpret_cast<float *>(P.out)[pair] = sqrtf(cmax);
+        P.idx1[pair] = mstar >= 0 ? mstar : 0;
+    }
+}
+
+// Plain path: any dtype, any D.  One CTA per set pair; thread t scans rows m = t, t+256, ...
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+hausdorff_plain_kernel(const HdParams P) {
+    __shared__ T s_val[kThreads];
+    __shared__ long long s_pos[kThreads], s_m[kThreads], s_n[kThreads];
+    const int tid = threadIdx.x;
+    const long long pair = blockIdx.x;
+    const long long j = pair % P.N2;
+    const long long bi = pair / P.N2;
+    const long long b = bi / P.N1;
+    const int D = (int)P.D;
+    const T *x1 = reinterpret_cast<const T *>(P.x1) + bi * P.M1 * D;
+    const T *x2 = reinterpret_cast<const T *>(P.x2) + (b * P.N2 + j) * P.M2 * D;
+
+    T best = T(-1);
+    long long best_pos = -1, best_m = 0, best_n = 0;
+    for (long long m = tid; m < P.M1; m += kThreads) {
+        T rowmin = T(INFINITY);
+        long long rn = 0, rpos = 0x7fffffffffffffffll;
+        for (long long n = 0; n < P.M2; ++n) {
+            const T d = sqdist_exact(x1 + m * D, x2 + n * D, D);
+            const long long p2 = P.order2 ? P.order2[b * P.M2 + n] : n;
+            if (d < rowmin || (d == rowmin && p2 < rpos)) { rowmin = d; rn = n; rpos = p2; }
+        }
+        const long long p1 = P.order1 ? P.order1[b * P.M1 + m] : m;
+        if (rowmin > best || (rowmin == best && p1 > best_pos)) { best = rowmin; best_pos = p1; best_m = m; best_n = rn; }
+    }
+    s_val[tid] = best; s_pos[tid] = best_pos; s_m[tid] = best_m; s_n[tid] = best_n;
+    __syncthreads();
+    for (int off = kThreads / 2; off > 0; off >>= 1) {
+        if (tid < off) {
+            const T v = s_val[tid + off];
+            const long long p = s_pos[tid + off];
+            if (v > s_val[tid] || (v == s_val[tid] && p > s_pos[tid])) {
+                s_val[tid] = v; s_pos[tid] = p; s_m[tid] = s_m[tid + off]; s_n[tid] = s_n[tid + off];
+            }
+        }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        const T cmax = s_pos[0] >= 0 ? s_val[0] : T(0);
+        reinterpret_cast<T *>(P.out)[pair] = (T)sqrt((double)cmax);
+        P.idx1[pair] = s_m[0];
+        P.idx2[pair] = s_n[0];
+    }
+}
+
+// grad_x1[b,i,m*,k] += g * (x1[m*] - x2[n*]) / out, one thread per (b,i,k), ascending j.
+template <typename T, bool SIDE2>
+__global__ void hausdorff_backward_kernel(const T *grad, const T *out, const long long *idx1, const long long *idx2,
+                                          const T *x1, const T *x2, T *gx,
+                                          long long B, long long N1, long long N2, long long M1, long long M2, long long D) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long NO = SIDE2 ? N2 : N1; // sets on the side that owns the gradient
+    if (idx >= B * NO * D) return;
+    const long long k = idx % D, s = (idx / D) % NO, b = idx / (D * NO);
+    const long long NI = SIDE2 ? N1 : N2;
+    for (long long t = 0; t < NI; ++t) {
+        const long long i = SIDE2 ? t : s, j = SIDE2 ? s : t;
+        const long long pair = (b * N1 + i) * N2 + j;
+        const long long m = idx1[pair], n = idx2[pair];
+        const T a = x1[((b * N1 + i) * M1 + m) * D + k];
+        const T c = x2[((b * N2 + j) * M2 + n) * D + k];
+        const T diff = SIDE2 ? c - a : a - c;
+        T *dst = SIDE2 ? gx + ((b * N2 + j) * M2 + n) * D + k : gx + ((b * N1 + i) * M1 + m) * D + k;
+        *dst += grad[pair] * diff / out[pair];
+    }
+}
+
+template <int D>
+int launch_fast(HdParams P, cudaStream_t s) {
+    const long long pairs = P.B * P.N1 * P.N2;
+    P.mtiles = (P.M1 + kThreads * PM - 1) / (kThreads * PM);
+    const long long blocks = pairs * P.mtiles;
+    TPW_CHECK_ARG(blocks < (1ll << 31), "hausdorff: too many blocks");
+    TPW_CUDA_OK(cudaMemsetAsync(P.keys, 0, (size_t)pairs * sizeof(unsigned long long), s));
+    hausdorff_rowmin_kernel<D><<<(unsigned)blocks, kThreads, 0, s>>>(P);
+    TPW_LAUNCH_OK("hausdorff_rowmin_kernel");
+    hausdorff_finish_kernel<D><<<(unsigned)pairs, kThreads, 0, s>>>(P);
+    TPW_LAUNCH_OK("hausdorff_finish_kernel");
+    return TPW_OK;
+}
+
+} // namespace
+} // namespace tpw
+
+using namespace tpw;
+
+extern "C" int64_t tpw_hausdorff_scratch_bytes(int64_t B, int64_t N1, int64_t N2, int64_t M1) {
+    (void)M1;
+    if (B <= 0 || N1 <= 0 || N2 <= 0) return 0;
+    return B * N1 * N2 * (int64_t)sizeof(unsigned long long);
+}
+
+extern "C" int tpw_hausdorff_forward(int dtype, const void *x1, const void *x2,
+                                     const int64_t *order1, const int64_t *order2,
+                                     void *out, int64_t *idx1, int64_t *idx2, void *scratch,
+                                     int64_t B, int64_t N1, int64_t N2, int64_t M1, int64_t M2, int64_t D,
+                                     tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(dtype == TPW_F32 || dtype == TPW_F64, "tpw_hausdorff_forward: dtype must be TPW_F32 or TPW_F64");
+    TPW_CHECK_ARG(B >= 0 && N1 >= 0 && N2 >= 0 && M1 >= 0 && M2 >= 0 && D >= 0, "tpw_hausdorff_forward: negative size");
+    const long long pairs = B * N1 * N2;
+    if (pairs == 0) return TPW_OK;
+    TPW_CHECK_ARG(M1 > 0 && M2 > 0 && D > 0, "tpw_hausdorff_forward: empty point sets (M1=%lld, M2=%lld, D=%lld)",
+                  (long long)M1, (long long)M2, (long long)D);
+    TPW_CHECK_ARG(M1 < (1ll << 32) && M2 < (1ll << 32), "tpw_hausdorff_forward: more than 2^32 points per set");
+    TPW_CHECK_ARG(x1 && x2 && out && idx1 && idx2, "tpw_hausdorff_forward: NULL pointer");
+    TPW_CHECK_ARG(pairs < (1ll << 31), "tpw_hausdorff_forward: too many set pairs");
+    HdParams P;
+    memset(&P, 0, sizeof(P));
+    P.x1 = x1; P.x2 = x2;
+    P.order1 = reinterpret_cast<const long long *>(order1);
+    P.order2 = reinterpret_cast<const long long *>(order2);
+    P.out = out;
+    P.idx1 = reinterpret_cast<long long *>(idx1);
+    P.idx2 = reinterpret_cast<long long *>(idx2);
+    P.keys = reinterpret_cast<unsigned long long *>(scratch);
+    P.B = B; P.N1 = N1; P.N2 = N2; P.M1 = M1; P.M2 = M2; P.D = D;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == TPW_F32 && D <= 4) {
+        TPW_CHECK_ARG(scratch != nullptr, "tpw_hausdorff_forward: scratch is NULL");
+        TPW_CHECK_ARG((reinterpret_cast<uintptr_t>(scratch) & 7u) == 0, "tpw_hausdorff_forward: scratch must be 8-byte aligned");
+        switch (D) {
+            case 1: return launch_fast<1>(P, s);
+            case 2: return launch_fast<2>(P, s);
+            case 3: return launch_fast<3>(P, s);
+            default: return launch_fast<4>(P, s);
+        }
+    }
+    if (dtype == TPW_F32) hausdorff_plain_kernel<float><<<(unsigned)pairs, kThreads, 0, s>>>(P);
+    else hausdorff_plain_kernel<double><<<(unsigned)pairs, kThreads, 0, s>>>(P);
+    TPW_LAUNCH_OK("hausdorff_plain_kernel");
+    return TPW_OK;
+}
+
+extern "C" int tpw_hausdorff_backward(int dtype, const void *grad, const void *out,
+                                      const int64_t *idx1, const int64_t *idx2,
+                                      const void *x1, const void *x2, void *grad_x1, void *grad_x2,
+                                      int64_t B, int64_t N1, int64_t N2, int64_t M1, int64_t M2, int64_t D,
+                                      tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(dtype == TPW_F32 || dtype == TPW_F64, "tpw_hausdorff_backward: dtype must be TPW_F32 or TPW_F64");
+    TPW_CHECK_ARG(B >= 0 && N1 >= 0 && N2 >= 0 && M1 >= 0 && M2 >= 0 && D >= 0, "tpw_hausdorff_backward: negative size");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t es = dtype == TPW_F32 ? 4 : 8;
+    if (grad_x1 && B * N1 * M1 * D > 0) TPW_CUDA_OK(cudaMemsetAsync(grad_x1, 0, (size_t)(B * N1 * M1 * D) * es, s));
+    if (grad_x2 && B * N2 * M2 * D > 0) TPW_CUDA_OK(cudaMemsetAsync(grad_x2, 0, (size_t)(B * N2 * M2 * D) * es, s));
+    if (B * N1 * N2 == 0 || M1 == 0 || M2 == 0 || D == 0) return TPW_OK;
+    TPW_CHECK_ARG(grad && out && idx1 && idx2 && x1 && x2, "tpw_hausdorff_backward: NULL pointer");
+    const int threads = 128;
+    const long long *i1 = reinterpret_cast<const long long *>(idx1), *i2 = reinterpret_cast<const long long *>(idx2);
+#define TPW_HD_BWD(T)                                                                                                   \
+    do {                                                                                                                \
+        if (grad_x1) {                                                                                                  \
+            const long long n = B * N1 * D;                                                                             \
+            hausdorff_backward_kernel<T, false><<<(unsigned)((n + threads - 1) / threads), threads, 0, s>>>(            \
+                (const T *)grad, (const T *)out, i1, i2, (const T *)x1, (const T *)x2, (T *)grad_x1, B, N1, N2, M1, M2, D); \
+        }                                                                                                               \
+        if (grad_x2) {                                                                                                  \
+            const long long n = B * N2 * D;                                                                             \
+            hausdorff_backward_kernel<T, true><<<(unsigned)((n + threads - 1) / threads), threads, 0, s>>>(             \
+                (const T *)grad, (const T *)out, i1, i2, (const T *)x1, (const T *)x2, (T *)grad_x2, B, N1, N2, M1, M2, D); \
+        }                                                                                                               \
+    } while (0)
+    if (dtype == TPW_F32) TPW_HD_BWD(float); else TPW_HD_BWD(double);
+#undef TPW_HD_BWD
+    TPW_LAUNCH_OK("hausdorff_backward_kernel");
+    return TPW_OK;
+}

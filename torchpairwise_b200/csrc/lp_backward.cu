@@ -1,0 +1,550 @@
+// Backward of the pairwise L_p reductions on the CUDA cores.
+//
+//   grad_x1[b,i,k] = post * w[b,k] * sum_j coef[b,i,j] * phi(x1[b,i,k] - x2[b,j,k])
+//   grad_x2[b,j,k] = post * w[b,k] * sum_i coef[b,i,j] * phi(x2[b,j,k] - x1[b,i,k])
+//
+// with coef derived on the fly from the upstream gradient g and an auxiliary [B,N1,N2] matrix
+// (the forward output, or the S^(1/p-1) matrix of the weighted form), and phi an odd function of
+// the coordinate difference chosen by p.  The two sums are two passes of ONE kernel: the "row"
+// operand (x1 for grad_x1, x2 for grad_x2) sits in registers, the other operand and the
+// coefficient tile are streamed through shared memory 32 rows at a time.  A CTA of 256 threads
+// owns a (16R rows) x (16R features) block of the gradient and sums over the whole streamed
+// dimension itself, so every gradient element is written once, without atomics, in a fixed order.
+//
+// Thread (tr, tk) = (tid/16, tid%16) owns rows {64g + 4tr + e} and features {64g + 4tk + e}
+// (g < R/4, e < 4): 16-byte shared loads of the streamed operand are contiguous across a quarter
+// warp and the coefficient loads are broadcasts.  Aligned problems are fed by TMA (three-stage
+// mbarrier ring, one issuing thread); others use guarded plain loads into the same layout.
+#include "common.cuh"
+
+#include <math.h>
+
+namespace tpw {
+namespace {
+
+enum Phi {
+    PHI_SGN = 0,    // sgn(d)
+    PHI_D = 1,      // d
+    PHI_DABS = 2,   // d*|d|
+    PHI_SGNPOW = 3, // sgn(d)*|d|^q
+    PHI_ABSPOW = 4, // |d|^q
+    PHI_Y = 5,      // the streamed operand itself (plain contraction)
+    PHI_SGN_EQ = 6  // sgn(d) where |d| equals the auxiliary value, else 0
+};
+
+enum CoefMode { COEF_G = 0, COEF_DIV_O = 1, COEF_DIV_O2 = 2, COEF_DIV_POW = 3, COEF_MUL = 4 };
+
+struct BwdParams {
+    const void *rowop;  // [B, NR, D] operand held in registers
+    const void *stream; // [B, NS, D] operand streamed through shared memory
+    const void *grad;   // [B, N1, N2]
+    const void *aux;    // [B, N1, N2] or NULL
+    const void *w;      // [B, D] or NULL
+    void *out;          // [B, NR, D]
+    long long B, N1, N2, D, NR, NS;
+    long long tiles_r, tiles_k;
+    double q;           // exponent of PHI_SGNPOW / PHI_ABSPOW, and of COEF_DIV_POW
+    double post;        // scalar applied to every result
+    int coef_mode;
+    int *status;
+};
+
+constexpr int kThreads = 256;
+constexpr int kStages = 3;
+constexpr int SC = 32; // streamed rows per stage
+
+template <typename T> __device__ __forceinline__ void load4(T *dst, const T *src);
+template <> __device__ __forceinline__ void load4<float>(float *dst, const float *src) {
+    float4 v = *reinterpret_cast<const float4 *>(src);
+    dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+}
+template <> __device__ __forceinline__ void load4<double>(double *dst, const double *src) {
+    double2 a = *reinterpret_cast<const double2 *>(src);
+    double2 b = *reinterpret_cast<const double2 *>(src + 2);
+    dst[0] = a.x; dst[1] = a.y; dst[2] = b.x; dst[3] = b.y;
+}
+
+__device__ __forceinline__ float b_abs(float v) { return fabsf(v); }
+__device__ __forceinline__ double b_abs(double v) { return fabs(v); }
+__device__ __forceinline__ float b_fma(float a, float b, float c) { return fmaf(a, b, c); }
+__device__ __forceinline__ double b_fma(double a, double b, double c) { return fma(a, b, c); }
+__device__ __forceinline__ float b_powabs(float a, float q) { return a == 0.f ? 0.f : exp2f(q * __log2f(a)); }
+__device__ __forceinline__ double b_powabs(double a, double q) { return a == 0.0 ? 0.0 : pow(a, q); }
+__device__ __forceinline__ float b_copysign(float a, float s) { return copysignf(a, s); }
+__device__ __forceinline__ double b_copysign(double a, double s) { return copysign(a, s); }
+__device__ __forceinline__ float b_pow(float a, double q) { return powf(a, (float)q); }
+__device__ __forceinline__ double b_pow(double a, double q) { return pow(a, q); }
+
+// acc += c * phi(x - y)
+template <int PHI, typename T>
+__device__ __forceinline__ void bwd_accumulate(T &acc, T x, T y, T c, T o, T q) {
+    if (PHI == PHI_Y) {
+        acc = b_fma(c, y, acc);
+        return;
+    }
+    T d = x - y;
+    if (PHI == PHI_D) {
+        acc = b_fma(c, d, acc);
+    } else if (PHI == PHI_DABS) {
+        acc = b_fma(c, d * b_abs(d), acc);
+    } else if (PHI == PHI_SGN) {
+        T s = d > T(0) ? c : -c;
+        acc += d != T(0) ? s : T(0);
+    } else if (PHI == PHI_SGNPOW) {
+        acc = b_fma(c, b_copysign(b_powabs(b_abs(d), q), d), acc);
+    } else if (PHI == PHI_ABSPOW) {
+        acc = b_fma(c, b_powabs(b_abs(d), q), acc);
+    } else if (PHI == PHI_SGN_EQ) {
+        T s = d > T(0) ? c : -c;
+        acc += (d != T(0) && b_abs(d) == o) ? s : T(0);
+    }
+}
+
+template <typename T, int R> struct BwdSmem {
+    static constexpr int TR = 16 * R;             // rows of the register operand per CTA
+    static constexpr int TK = 16 * R;             // features per CTA
+    static constexpr int YS_BYTES = SC * TK * (int)sizeof(T);
+    static constexpr int GS_BYTES = SC * TR * (int)sizeof(T);
+    static constexpr int STAGE_BYTES = YS_BYTES + 2 * GS_BYTES; // streamed rows | grad tile | aux tile
+    static constexpr int OFF_BAR = kStages * STAGE_BYTES;
+    static constexpr int BYTES = OFF_BAR + kStages * 8;
+    static constexpr int ALLOC = BYTES + 128;
+};
+
+// TRANS = false: the register operand is x1 (rows i), streamed rows are j; the coefficient tile is
+// stored [TR rows i][SC] exactly as it lies in memory.  TRANS = true: register operand x2 (rows j),
+// streamed rows are i; the coefficient tile is stored [SC][TR rows j], again as it lies in memory.
+template <typename T, int R, int PHI, bool NEED_AUX, bool TRANS, bool USE_TMA>
+__global__ void __launch_bounds__(kThreads, 1)
+lp_backward_kernel(const __grid_constant__ CUtensorMap map_stream, const __grid_constant__ CUtensorMap map_grad,
+                   const __grid_constant__ CUtensorMap map_aux, const BwdParams P) {
+    typedef BwdSmem<T, R> S;
+    constexpr int TR = S::TR, TK = S::TK, G = R / 4;
+    constexpr bool AUX_IN_LOOP = (PHI == PHI_SGN_EQ);
+
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + S::OFF_BAR);
+
+    const int tid = threadIdx.x;
+    const int tr = tid >> 4, tk = tid & 15;
+
+    long long tile = blockIdx.x;
+    const long long tkx = tile % P.tiles_k;
+    tile /= P.tiles_k;
+    const long long trx = tile % P.tiles_r;
+    const long long b = tile / P.tiles_r;
+    const long long r0 = trx * TR, k0 = tkx * TK;
+
+    const T *rowop = reinterpret_cast<const T *>(P.rowop) + b * P.NR * P.D;
+    const T *stream = reinterpret_cast<const T *>(P.stream) + b * P.NS * P.D;
+    const T *grad = reinterpret_cast<const T *>(P.grad) + b * P.N1 * P.N2;
+    const T *aux = NEED_AUX ? reinterpret_cast<const T *>(P.aux) + b * P.N1 * P.N2 : nullptr;
+
+    // register operand: rows {64g + 4tr + e}, features {64g + 4tk + e}
+    T xr[R][R];
+    if (PHI != PHI_Y) {
+#pragma unroll
+        for (int a = 0; a < R; ++a) {
+            const long long row = r0 + (a / 4) * 64 + tr * 4 + (a % 4);
+#pragma unroll
+            for (int c = 0; c < R; ++c) {
+                const long long k = k0 + (c / 4) * 64 + tk * 4 + (c % 4);
+                xr[a][c] = (row < P.NR && k < P.D) ? rowop[row * P.D + k] : T(0);
+            }
+        }
+    }
+    T acc[R][R];
+#pragma unroll
+    for (int a = 0; a < R; ++a)
+#pragma unroll
+        for (int c = 0; c < R; ++c) acc[a][c] = T(0);
+
+    const int nchunks = (int)((P.NS + SC - 1) / SC);
+    const uint32_t tx_bytes = S::YS_BYTES + S::GS_BYTES + (NEED_AUX ? S::GS_BYTES : 0);
+
+    auto issue = [&](int chunk) {
+        const int st = chunk % kStages;
+        unsigned char *base = smem + st * S::STAGE_BYTES;
+        const int s0 = chunk * SC;
+        mbar_expect_tx(&full[st], tx_bytes);
+        tma_load_3d(base, &map_stream, &full[st], (int)k0, s0, (int)b);
+        if (!TRANS) {
+            tma_load_3d(base + S::YS_BYTES, &map_grad, &full[st], s0, (int)r0, (int)b);
+            if (NEED_AUX) tma_load_3d(base + S::YS_BYTES + S::GS_BYTES, &map_aux, &full[st], s0, (int)r0, (int)b);
+        } else {
+            tma_load_3d(base + S::YS_BYTES, &map_grad, &full[st], (int)r0, s0, (int)b);
+            if (NEED_AUX) tma_load_3d(base + S::YS_BYTES + S::GS_BYTES, &map_aux, &full[st], (int)r0, s0, (int)b);
+        }
+    };
+
+    if (USE_TMA) {
+        if (tid == 0) {
+#pragma unroll
+            for (int s = 0; s < kStages; ++s) mbar_init(&full[s], 1);
+            mbar_init_fence();
+            tma_prefetch_descriptor(&map_stream);
+            tma_prefetch_descriptor(&map_grad);
+            if (NEED_AUX) tma_prefetch_descriptor(&map_aux);
+        }
+        __syncthreads();
+        if (tid == 0)
+            for (int c = 0; c < kStages - 1 && c < nchunks; ++c) issue(c);
+    }
+
+    const T q = (T)P.q;
+    int failed = 0;
+
+    for (int t = 0; t < nchunks; ++t) {
+        const int stage = USE_TMA ? t % kStages : 0;
+        unsigned char *base = smem + stage * S::STAGE_BYTES;
+        T *ys = reinterpret_cast<T *>(base);
+        T *gs = reinterpret_cast<T *>(base + S::YS_BYTES);
+        T *as = reinterpret_cast<T *>(base + S::YS_BYTES + S::GS_BYTES);
+        const long long s0 = (long long)t * SC;
+
+        if (USE_TMA) {
+            if (__syncthreads_or(failed)) {
+                if (tid == 0 && P.status) atomicCAS(P.status, 0, (2 << 16) | 1);
+                return;
+            }
+            if (tid == 0 && t + kStages - 1 < nchunks) issue(t + kStages - 1);
+            if (!mbar_wait_bounded(&full[stage], (uint32_t)((t / kStages) & 1))) failed = 1;
+        } else {
+            __syncthreads();
+            for (int e = tid; e < SC * TK; e += kThreads) {
+                const int s = e / TK, kk = e % TK;
+                const long long row = s0 + s, k = k0 + kk;
+                ys[e] = (row < P.NS && k < P.D) ? stream[row * P.D + k] : T(0);
+            }
+            for (int e = tid; e < SC * TR; e += kThreads) {
+                long long i, j;
+                if (!TRANS) { i = r0 + e / SC; j = s0 + e % SC; }
+                else        { i = s0 + e / TR; j = r0 + e % TR; }
+                const bool ok = i < P.N1 && j < P.N2;
+                gs[e] = ok ? grad[i * P.N2 + j] : T(0);
+                if (NEED_AUX) as[e] = ok ? aux[i * P.N2 + j] : T(0);
+            }
+            __syncthreads();
+        }
+
+        if (NEED_AUX && !AUX_IN_LOOP) {
+            // coefficient tile in place: c = f(g, aux)
+            for (int e = tid; e < SC * TR; e += kThreads) {
+                const T g = gs[e], o = as[e];
+                T c;
+                switch (P.coef_mode) {
+                    case COEF_DIV_O: c = o == T(0) ? T(0) : g / o; break;
+                    case COEF_DIV_O2: c = o == T(0) ? T(0) : g / (o * o); break;
+                    case COEF_DIV_POW: c = o == T(0) ? T(0) : g / b_pow(o, P.q); break;
+                    case COEF_MUL: c = g * o; break;
+                    default: c = g; break;
+                }
+                gs[e] = c;
+            }
+            __syncthreads();
+        }
+
+#pragma unroll 1
+        for (int s = 0; s < SC; s += 4) {
+            T cv[TRANS ? 1 : R][4];
+            T ov[(AUX_IN_LOOP && !TRANS) ? R : 1][4];
+            if (!TRANS) {
+#pragma unroll
+                for (int a = 0; a < R; ++a) {
+                    const int row = (a / 4) * 64 + tr * 4 + (a % 4);
+                    load4<T>(cv[a], gs + row * SC + s);
+                    if (AUX_IN_LOOP) load4<T>(ov[a], as + row * SC + s);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                T yv[R];
+#pragma unroll
+                for (int g = 0; g < G; ++g) load4<T>(&yv[g * 4], ys + (s + u) * TK + g * 64 + tk * 4);
+                T ct[R], ot[R];
+                if (TRANS) {
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        load4<T>(&ct[g * 4], gs + (s + u) * TR + g * 64 + tr * 4);
+                        if (AUX_IN_LOOP) load4<T>(&ot[g * 4], as + (s + u) * TR + g * 64 + tr * 4);
+                    }
+                }
+#pragma unroll
+                for (int a = 0; a < R; ++a) {
+                    const T c = TRANS ? ct[a] : cv[a][u];
+                    const T o = AUX_IN_LOOP ? (TRANS ? ot[a] : ov[a][u]) : T(0);
+#pragma unroll
+                    for (int kk = 0; kk < R; ++kk) bwd_accumulate<PHI, T>(acc[a][kk], xr[a][kk], yv[kk], c, o, q);
+                }
+            }
+        }
+    }
+    if (USE_TMA) {
+        if (__syncthreads_or(failed)) {
+            if (tid == 0 && P.status) atomicCAS(P.status, 0, (2 << 16) | 2);
+            return;
+        }
+    }
+
+    T *out = reinterpret_cast<T *>(P.out) + b * P.NR * P.D;
+    const T *w = P.w ? reinterpret_cast<const T *>(P.w) + b * P.D : nullptr;
+    const T post = (T)P.post;
+#pragma unroll
+    for (int a = 0; a < R; ++a) {
+        const long long row = r0 + (a / 4) * 64 + tr * 4 + (a % 4);
+        if (row >= P.NR) continue;
+#pragma unroll
+        for (int c = 0; c < R; ++c) {
+            const long long k = k0 + (c / 4) * 64 + tk * 4 + (c % 4);
+            if (k >= P.D) continue;
+            T v = acc[a][c] * post;
+            if (w) v *= w[k];
+            out[row * P.D + k] = v;
+        }
+    }
+}
+
+template <typename T, int PHI, bool NEED_AUX, bool TRANS>
+int launch_backward(BwdParams P, cudaStream_t stream) {
+    constexpr int R = sizeof(T) == 4 ? 8 : 4;
+    typedef BwdSmem<T, R> S;
+    P.tiles_r = (P.NR + S::TR - 1) / S::TR;
+    P.tiles_k = (P.D + S::TK - 1) / S::TK;
+    const long long tiles = P.B * P.tiles_r * P.tiles_k;
+    if (tiles <= 0) return TPW_OK;
+    TPW_CHECK_ARG(tiles < (1ll << 31), "lp backward: too many tiles (%lld)", tiles);
+    TPW_CHECK_ARG(P.N1 < (1ll << 31) && P.N2 < (1ll << 31) && P.B < (1ll << 31) && P.D < (1ll << 31),
+                  "lp backward: a dimension exceeds 2^31-1");
+    P.status = device_status_ptr();
+
+    bool tma_ok = aligned16(P.stream) && aligned16(P.grad) && (!NEED_AUX || aligned16(P.aux)) &&
+                  (P.D * (long long)sizeof(T)) % 16 == 0 && (P.N2 * (long long)sizeof(T)) % 16 == 0;
+    CUtensorMap ms, mg, ma;
+    memset(&ms, 0, sizeof(ms));
+    memset(&mg, 0, sizeof(mg));
+    memset(&ma, 0, sizeof(ma));
+    if (tma_ok) {
+        int st = make_tensor_map_3d(&ms, P.stream, sizeof(T), P.D, P.NS, P.B, S::TK, SC, false);
+        if (st != TPW_OK) return st;
+        const uint32_t gb0 = TRANS ? S::TR : SC, gb1 = TRANS ? SC : S::TR;
+        st = make_tensor_map_3d(&mg, P.grad, sizeof(T), P.N2, P.N1, P.B, gb0, gb1, false);
+        if (st != TPW_OK) return st;
+        if (NEED_AUX) {
+            st = make_tensor_map_3d(&ma, P.aux, sizeof(T), P.N2, P.N1, P.B, gb0, gb1, false);
+            if (st != TPW_OK) return st;
+        }
+        auto kern = lp_backward_kernel<T, R, PHI, NEED_AUX, TRANS, true>;
+        TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::ALLOC));
+        kern<<<(unsigned)tiles, kThreads, S::ALLOC, stream>>>(ms, mg, ma, P);
+    } else {
+        auto kern = lp_backward_kernel<T, R, PHI, NEED_AUX, TRANS, false>;
+        TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::ALLOC));
+        kern<<<(unsigned)tiles, kThreads, S::ALLOC, stream>>>(ms, mg, ma, P);
+    }
+    TPW_LAUNCH_OK("lp_backward_kernel");
+    return TPW_OK;
+}
+
+// One side (grad_x1 when trans == false, grad_x2 when true).
+template <typename T, int PHI, bool NEED_AUX>
+int launch_side(const BwdParams &base, bool trans, const void *x1, const void *x2, void *out, cudaStream_t stream) {
+    BwdParams P = base;
+    P.out = out;
+    if (!trans) {
+        P.rowop = x1; P.stream = x2; P.NR = base.N1; P.NS = base.N2;
+        return launch_backward<T, PHI, NEED_AUX, false>(P, stream);
+    }
+    P.rowop = x2; P.stream = x1; P.NR = base.N2; P.NS = base.N1;
+    return launch_backward<T, PHI, NEED_AUX, true>(P, stream);
+}
+
+template <typename T, int PHI, bool NEED_AUX>
+int launch_both(const BwdParams &base, const void *x1, const void *x2, void *g1, void *g2, cudaStream_t stream) {
+    if (g1) {
+        int st = launch_side<T, PHI, NEED_AUX>(base, false, x1, x2, g1, stream);
+        if (st != TPW_OK) return st;
+    }
+    if (g2) {
+        int st = launch_side<T, PHI, NEED_AUX>(base, true, x1, x2, g2, stream);
+        if (st != TPW_OK) return st;
+    }
+    return TPW_OK;
+}
+
+template <typename T>
+int lp_backward_typed(int mode, BwdParams P, const void *x1, const void *x2, void *g1, void *g2, double p,
+                      cudaStream_t stream) {
+    P.post = 1.0;
+    P.q = p - 1.0;
+    P.coef_mode = COEF_G;
+    switch (mode) {
+        case TPW_LP_BWD_MATMUL:
+            P.aux = nullptr; P.w = nullptr;
+            return launch_both<T, PHI_Y, false>(P, x1, x2, g1, g2, stream);
+        case TPW_LP_BWD_CDIST:
+            P.w = nullptr;
+            if (isinf(p)) return launch_both<T, PHI_SGN_EQ, true>(P, x1, x2, g1, g2, stream);
+            if (p == 1.0) { P.aux = nullptr; return launch_both<T, PHI_SGN, false>(P, x1, x2, g1, g2, stream); }
+            if (p == 2.0) { P.coef_mode = COEF_DIV_O; return launch_both<T, PHI_D, true>(P, x1, x2, g1, g2, stream); }
+            if (p == 3.0) { P.coef_mode = COEF_DIV_O2; return launch_both<T, PHI_DABS, true>(P, x1, x2, g1, g2, stream); }
+            P.coef_mode = COEF_DIV_POW;
+            return launch_both<T, PHI_SGNPOW, true>(P, x1, x2, g1, g2, stream);
+        case TPW_LP_BWD_PPMINKOWSKI:
+            P.aux = nullptr; P.w = nullptr; P.post = p;
+            if (p == 1.0) return launch_both<T, PHI_SGN, false>(P, x1, x2, g1, g2, stream);
+            if (p == 2.0) return launch_both<T, PHI_D, false>(P, x1, x2, g1, g2, stream);
+            if (p == 3.0) return launch_both<T, PHI_DABS, false>(P, x1, x2, g1, g2, stream);
+            return launch_both<T, PHI_SGNPOW, false>(P, x1, x2, g1, g2, stream);
+        case TPW_LP_BWD_WMINKOWSKI:
+            P.coef_mode = COEF_MUL;
+            if (p == 1.0) return launch_both<T, PHI_SGN, true>(P, x1, x2, g1, g2, stream);
+            if (p == 2.0) return launch_both<T, PHI_D, true>(P, x1, x2, g1, g2, stream);
+            if (p == 3.0) return launch_both<T, PHI_DABS, true>(P, x1, x2, g1, g2, stream);
+            return launch_both<T, PHI_SGNPOW, true>(P, x1, x2, g1, g2, stream);
+        default:
+            return fail(TPW_ERR_INVALID, "tpw_lp_backward: unknown mode %d", mode);
+    }
+}
+
+// grad_w[b,k] = (1/p) * sum_i scratch[b,i,k]; one thread per (b,k), ascending i.
+template <typename T>
+__global__ void column_sum_kernel(const T *scratch, T *grad_w, long long B, long long N1, long long D, double scale) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= B * D) return;
+    const long long b = idx / D, k = idx % D;
+    const T *col = scratch + b * N1 * D + k;
+    T s = T(0);
+    for (long long i = 0; i < N1; ++i) s += col[i * D];
+    grad_w[idx] = s * (T)scale;
+}
+
+// Single-coordinate +-inf backward: one thread per pair, first extreme coordinate wins.
+template <typename T, bool NEG>
+__global__ void lp_inf_backward_kernel(const T *grad, const T *x1, const T *x2, const T *w, T *g1, T *g2, T *gw,
+                                       long long B, long long N1, long long N2, long long D) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= B * N1 * N2) return;
+    const long long j = idx % N2, i = (idx / N2) % N1, b = idx / (N2 * N1);
+    const T *a = x1 + (b * N1 + i) * D, *c = x2 + (b * N2 + j) * D;
+    const T *wb = w ? w + b * D : nullptr;
+    T val = a[0] - c[0], fabs_val = b_abs(val), w_val = wb ? fabs_val * wb[0] : fabs_val;
+    long long best = 0;
+    for (long long k = 1; k < D; ++k) {
+        const T tmp = a[k] - c[k], ft = b_abs(tmp), wt = wb ? ft * wb[k] : ft;
+        if (NEG ? (wt < w_val) : (wt > w_val)) { val = tmp; fabs_val = ft; w_val = wt; best = k; }
+    }
+    const T sgn = (T)((T(0) < val) - (val < T(0)));
+    const T g = grad[idx];
+    const T scale = wb ? wb[best] : T(1);
+    if (g1) atomicAdd(g1 + (b * N1 + i) * D + best, g * scale * sgn);
+    if (g2) atomicAdd(g2 + (b * N2 + j) * D + best, g * scale * -sgn);
+    if (gw && wb) atomicAdd(gw + b * D + best, g * fabs_val);
+}
+
+} // namespace
+} // namespace tpw
+
+using namespace tpw;
+
+extern "C" int tpw_lp_backward(int dtype, int mode, const void *grad, const void *aux,
+                               const void *x1, const void *x2, const void *w,
+                               void *grad_x1, void *grad_x2,
+                               int64_t B, int64_t N1, int64_t N2, int64_t D,
+                               double p, tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(dtype == TPW_F32 || dtype == TPW_F64, "tpw_lp_backward: dtype must be TPW_F32 or TPW_F64");
+    TPW_CHECK_ARG(B >= 0 && N1 >= 0 && N2 >= 0 && D >= 0, "tpw_lp_backward: negative size");
+    if (B == 0 || D == 0 || (N1 == 0 && N2 == 0)) return TPW_OK;
+    TPW_CHECK_ARG(x1 && x2, "tpw_lp_backward: NULL input");
+    TPW_CHECK_ARG(grad != nullptr || N1 == 0 || N2 == 0, "tpw_lp_backward: grad is NULL");
+    TPW_CHECK_ARG(!isnan(p), "tpw_lp_backward: p is NaN");
+    if (mode != TPW_LP_BWD_MATMUL) {
+        TPW_CHECK_ARG(p > 0, "tpw_lp_backward: p must be positive (got %g)", p);
+        TPW_CHECK_ARG(!isinf(p) || mode == TPW_LP_BWD_CDIST,
+                      "tpw_lp_backward: p = inf is only defined for TPW_LP_BWD_CDIST; use tpw_lp_inf_backward");
+    }
+    const bool needs_aux = (mode == TPW_LP_BWD_WMINKOWSKI) || (mode == TPW_LP_BWD_CDIST && p != 1.0);
+    TPW_CHECK_ARG(!needs_aux || aux != nullptr, "tpw_lp_backward: this mode needs the auxiliary matrix");
+    TPW_CHECK_ARG(mode != TPW_LP_BWD_WMINKOWSKI || w != nullptr, "tpw_lp_backward: weighted mode needs w");
+    BwdParams P;
+    memset(&P, 0, sizeof(P));
+    P.grad = grad; P.aux = aux; P.w = w;
+    P.B = B; P.N1 = N1; P.N2 = N2; P.D = D;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (N1 == 0 || N2 == 0) {
+        // empty sums: gradients are all zero
+        const size_t es = dtype == TPW_F32 ? 4 : 8;
+        if (grad_x1 && N1 > 0) TPW_CUDA_OK(cudaMemsetAsync(grad_x1, 0, (size_t)(B * N1 * D) * es, s));
+        if (grad_x2 && N2 > 0) TPW_CUDA_OK(cudaMemsetAsync(grad_x2, 0, (size_t)(B * N2 * D) * es, s));
+        return TPW_OK;
+    }
+    return dtype == TPW_F32 ? lp_backward_typed<float>(mode, P, x1, x2, grad_x1, grad_x2, p, s)
+                            : lp_backward_typed<double>(mode, P, x1, x2, grad_x1, grad_x2, p, s);
+}
+
+extern "C" int tpw_wminkowski_backward_w(int dtype, const void *grad, const void *aux,
+                                         const void *x1, const void *x2, void *grad_w, void *scratch,
+                                         int64_t B, int64_t N1, int64_t N2, int64_t D,
+                                         double p, tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(dtype == TPW_F32 || dtype == TPW_F64, "tpw_wminkowski_backward_w: dtype must be TPW_F32 or TPW_F64");
+    TPW_CHECK_ARG(B >= 0 && N1 >= 0 && N2 >= 0 && D >= 0, "tpw_wminkowski_backward_w: negative size");
+    if (B == 0 || D == 0) return TPW_OK;
+    TPW_CHECK_ARG(grad_w != nullptr, "tpw_wminkowski_backward_w: grad_w is NULL");
+    TPW_CHECK_ARG(p > 0 && !isinf(p), "tpw_wminkowski_backward_w: p must be finite and positive");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t es = dtype == TPW_F32 ? 4 : 8;
+    if (N1 == 0 || N2 == 0) {
+        TPW_CUDA_OK(cudaMemsetAsync(grad_w, 0, (size_t)(B * D) * es, s));
+        return TPW_OK;
+    }
+    TPW_CHECK_ARG(grad && aux && x1 && x2 && scratch, "tpw_wminkowski_backward_w: NULL pointer");
+    BwdParams P;
+    memset(&P, 0, sizeof(P));
+    P.grad = grad; P.aux = aux; P.w = nullptr;
+    P.B = B; P.N1 = N1; P.N2 = N2; P.D = D;
+    P.post = 1.0; P.q = p; P.coef_mode = COEF_MUL;
+    int st = dtype == TPW_F32 ? launch_side<float, PHI_ABSPOW, true>(P, false, x1, x2, scratch, s)
+                              : launch_side<double, PHI_ABSPOW, true>(P, false, x1, x2, scratch, s);
+    if (st != TPW_OK) return st;
+    const long long n = B * D;
+    const int threads = 128;
+    const unsigned blocks = (unsigned)((n + threads - 1) / threads);
+    if (dtype == TPW_F32)
+        column_sum_kernel<float><<<blocks, threads, 0, s>>>((const float *)scratch, (float *)grad_w, B, N1, D, 1.0 / p);
+    else
+        column_sum_kernel<double><<<blocks, threads, 0, s>>>((const double *)scratch, (double *)grad_w, B, N1, D, 1.0 / p);
+    TPW_LAUNCH_OK("column_sum_kernel");
+    return TPW_OK;
+}
+
+extern "C" int tpw_lp_inf_backward(int dtype, const void *grad, const void *x1, const void *x2, const void *w,
+                                   void *grad_x1, void *grad_x2, void *grad_w,
+                                   int64_t B, int64_t N1, int64_t N2, int64_t D,
+                                   int negative, tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(dtype == TPW_F32 || dtype == TPW_F64, "tpw_lp_inf_backward: dtype must be TPW_F32 or TPW_F64");
+    TPW_CHECK_ARG(B >= 0 && N1 >= 0 && N2 >= 0 && D >= 0, "tpw_lp_inf_backward: negative size");
+    const long long n = B * N1 * N2;
+    if (n == 0) return TPW_OK;
+    TPW_CHECK_ARG(D > 0, "tpw_lp_inf_backward: D must be positive");
+    TPW_CHECK_ARG(grad && x1 && x2, "tpw_lp_inf_backward: NULL input");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int threads = 256;
+    const long long blocks_ll = (n + threads - 1) / threads;
+    TPW_CHECK_ARG(blocks_ll < (1ll << 31), "tpw_lp_inf_backward: too many pairs");
+    const unsigned blocks = (unsigned)blocks_ll;
+#define TPW_INF_LAUNCH(T, NEG)                                                                              \
+    lp_inf_backward_kernel<T, NEG><<<blocks, threads, 0, s>>>((const T *)grad, (const T *)x1, (const T *)x2, \
+                                                              (const T *)w, (T *)grad_x1, (T *)grad_x2,      \
+                                                              (T *)grad_w, B, N1, N2, D)
+    if (dtype == TPW_F32) {
+        if (negative) TPW_INF_LAUNCH(float, true); else TPW_INF_LAUNCH(float, false);
+    } else {
+        if (negative) TPW_INF_LAUNCH(double, true); else TPW_INF_LAUNCH(double, false);
+    }
+#undef TPW_INF_LAUNCH
+    TPW_LAUNCH_OK("lp_inf_backward_kernel");
+    return TPW_OK;
+}

@@ -1,0 +1,344 @@
+"""Throughput of the pairwise-reduction hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (``config.workload``): batched ``minkowski_distances(p=3)`` forward + backward in fp32 on
+X, Y [16, 4096, 256] i.i.d. N(0,1) with an upstream gradient [16, 4096, 4096] -- 268.4 M pairs per
+step, seeded synthetic data.  One step = one forward + backward over the batch.  With N > 1 ranks
+every rank runs its own 16 batches (the path shards by batch with no data-path collective), so the
+job is weakly scaled and ``value`` is the sum over ranks divided by the slowest rank's time.
+
+One JSON line is printed by rank 0.  ``value`` is timed with the inputs resident in HBM; ``e2e``
+times the same step through the public API from pinned host buffers (inputs copied in, both
+gradients copied out, every step).  ``roofline`` describes the dominant kernel (the backward tile
+kernel, two launches per step), timed alone with CUDA events on its stream; its bound is the fp32
+issue rate, measured live by the library's register-only microbenchmark, and ``roofline_hbm``
+restates the same launch against the measured copy bandwidth.  ``cpu_baseline`` times the
+reference's own CPU operators (built from its sources into oracle/_ref) on a bounded row block.
+
+``--impl reference`` times that CPU implementation alone, on the same workload definition, each
+step a bounded row block.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "Gpairs/s, minkowski_distances(p=3) forward+backward, fp32"
+B, N1, N2, D, P = 16, 4096, 4096, 256, 3.0
+PAIRS_PER_STEP = B * N1 * N2
+# lane-operations of the dominant kernel per pair and feature: subtract, d*|d|, fused multiply-add
+BWD_OPS_PER_ELEMENT = 3
+# algorithmic HBM bytes of one backward launch: upstream gradient + forward output read once,
+# both operands read once, one gradient written
+BWD_BYTES_PER_LAUNCH = 4 * (2 * B * N1 * N2 + 3 * B * N1 * D)
+# dram__bytes_read.sum + dram__bytes_write.sum of one backward launch, from the ncu capture
+# summarised in profiles/ (None until a capture exists)
+BWD_DRAM_TRAFFIC_BYTES = None
+
+REF_SO = ROOT / "oracle" / "_ref" / "torchpairwise_ref.so"
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def cpu_reference_step(rows: int, threads: int):
+    """One forward + backward of the reference's CPU operators on a row block of the workload:
+    X[1, rows, 256] against Y[1, 4096, 256].  Returns (seconds, pairs, kind)."""
+    import torch
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    X = torch.randn(1, rows, D, generator=g).requires_grad_(True)
+    Y = torch.randn(1, N2, D, generator=g).requires_grad_(True)
+    G = torch.randn(1, rows, N2, generator=g)
+    if REF_SO.exists():
+        if not getattr(cpu_reference_step, "_loaded", False):
+            torch.ops.load_library(str(REF_SO))
+            cpu_reference_step._loaded = True
+        fn = lambda: torch.ops.torchpairwise.minkowski_distances(X, Y, P).backward(G)  # noqa: E731
+        kind = "reference"
+    else:
+        from oracle import pairwise_oracle as O
+        xn, yn, gn = X.detach().numpy(), Y.detach().numpy(), G.numpy()
+        fn = lambda: O.cdist_backward(gn, xn, yn, P, out=O.cdist(xn, yn, P))  # noqa: E731
+        kind = "port"
+    t0 = time.perf_counter()
+    fn()
+    return time.perf_counter() - t0, rows * N2, kind
+
+
+def run_reference(args, rank: int):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    rows = 128
+    cpu_reference_step(rows, threads)  # library load + first-touch, not counted as a warm-up step
+    for _ in range(args.warmup):
+        cpu_reference_step(rows, threads)
+    t0 = time.perf_counter()
+    kind = "port"
+    for _ in range(args.steps):
+        _, pairs, kind = cpu_reference_step(rows, threads)
+    dt = time.perf_counter() - t0
+    value = args.steps * rows * N2 / dt / 1e9
+    sample = f"per step: batch 1 of 16, rows 0:{rows} of 4096 against all 4096 columns, D=256, forward+backward"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "Gpairs/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "C2 minkowski p=3 fwd+bwd: X,Y[16,4096,256], G[16,4096,4096] fp32 N(0,1) seed 0",
+                   "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "Gpairs/s", "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "Gpairs/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import torch
+    import torch.distributed as dist
+    import torchpairwise_b200 as tpw
+    from torchpairwise_b200 import _abi
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # per-rank seeded synthetic inputs, generated on the host so that the e2e leg can reuse them
+    g = torch.Generator().manual_seed(1000 + rank)
+    Xh = torch.randn(B, N1, D, generator=g).pin_memory()
+    Yh = torch.randn(B, N2, D, generator=g).pin_memory()
+    Gh = torch.randn(B, N1, N2, generator=g).pin_memory()
+    X = Xh.to(dev).requires_grad_(True)
+    Y = Yh.to(dev).requires_grad_(True)
+    G = Gh.to(dev)
+
+    def step():
+        X.grad = None
+        Y.grad = None
+        out = tpw.minkowski_distances(X, Y, P)
+        out.backward(G)
+
+    for _ in range(args.warmup):
+        step()
+    sampler = ClockSampler(local_rank)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = world * args.steps * PAIRS_PER_STEP / (ms * 1e-3) / 1e9
+
+    # ---- end to end: host buffers in, gradients out, every step ---------------------------------
+    g1h = torch.empty(B, N1, D).pin_memory()
+    g2h = torch.empty(B, N2, D).pin_memory()
+
+    def e2e_step():
+        x = Xh.to(dev, non_blocking=True).requires_grad_(True)
+        y = Yh.to(dev, non_blocking=True).requires_grad_(True)
+        gr = Gh.to(dev, non_blocking=True)
+        tpw.minkowski_distances(x, y, P).backward(gr)
+        g1h.copy_(x.grad, non_blocking=True)
+        g2h.copy_(y.grad, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_e2e], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_e2e = float(t.item())
+    e2e = world * args.steps * PAIRS_PER_STEP / (ms_e2e * 1e-3) / 1e9
+
+    line = None
+    if rank == 0:
+        # ---- dominant kernel alone: backward w.r.t. x1 (grad + forward output streamed) -----------
+        with torch.no_grad():
+            out = tpw.minkowski_distances(X, Y, P)
+        g1 = torch.empty_like(X)
+        stream = torch.cuda.current_stream().cuda_stream
+
+        def bwd_launch():
+            _abi.check(_abi.lib.tpw_lp_backward(_abi.F32, _abi.LP_BWD_CDIST, G.data_ptr(), out.data_ptr(),
+                                                X.data_ptr(), Y.data_ptr(), None, g1.data_ptr(), None,
+                                                B, N1, N2, D, P, stream))
+
+        for _ in range(3):
+            bwd_launch()
+        torch.cuda.synchronize()
+        reps = max(5, args.steps)
+        e0.record()
+        for _ in range(reps):
+            bwd_launch()
+        e1.record()
+        torch.cuda.synchronize()
+        k_ms = e0.elapsed_time(e1) / reps
+        ops = PAIRS_PER_STEP * D * BWD_OPS_PER_ELEMENT
+        fp32_peak = tpw.measure_issue_peak(0)
+        achieved = ops / (k_ms * 1e-3)
+        hbm_peak, hbm_src = load_peaks()
+        roofline = {"bound": "fp32_issue", "achieved": achieved / 1e12, "peak": fp32_peak / 1e12,
+                    "unit": "Tlane-op/s", "frac": achieved / fp32_peak, "traffic": BWD_DRAM_TRAFFIC_BYTES,
+                    "kernel": "lp_backward_kernel (grad_x1 pass, p=3)", "ms_per_launch": k_ms,
+                    "peak_source": "live register-only FFMA microbenchmark (tpw_measure_issue_peak)"}
+        roofline_hbm = {"bound": "hbm", "achieved": BWD_BYTES_PER_LAUNCH / (k_ms * 1e-3) / 1e9, "peak": hbm_peak,
+                        "unit": "GB/s", "frac": BWD_BYTES_PER_LAUNCH / (k_ms * 1e-3) / 1e9 / hbm_peak,
+                        "traffic": BWD_DRAM_TRAFFIC_BYTES, "peak_source": hbm_src}
+        # ---- other metrics of the path, a few launches each (not part of the timed K steps) --------
+        extra = {}
+
+        def timeit(fn, n=3):
+            fn()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / n
+
+        def cheb():
+            X.grad = None
+            Y.grad = None
+            tpw.chebyshev_distances(X, Y).backward(G)
+
+        extra["chebyshev_fwd_bwd_C2_Gpairs_s"] = PAIRS_PER_STEP / (timeit(cheb) * 1e-3) / 1e9
+        with torch.no_grad():
+            extra["minkowski_p3_fwd_C2_Gpairs_s"] = PAIRS_PER_STEP / (timeit(lambda: tpw.minkowski_distances(X, Y, P)) * 1e-3) / 1e9
+        del out, g1
+        # ---- CPU baseline: the reference's own operators on a bounded row block -------------------
+        threads = os.cpu_count() or 1
+        rows = 512
+        cpu_reference_step(64, threads)
+        secs, pairs, kind = cpu_reference_step(rows, threads)
+        cpu_baseline = {"value": pairs / secs / 1e9, "unit": "Gpairs/s", "cores": threads, "kind": kind,
+                        "sample": f"batch 1 of 16, rows 0:{rows} of 4096 against all 4096 columns, D=256, forward+backward, "
+                                  f"{secs:.1f} s"}
+        line = {
+            "metric": METRIC, "value": value, "unit": "Gpairs/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "C2 minkowski p=3 fwd+bwd: X,Y[16,4096,256], G[16,4096,4096] fp32 N(0,1) per GPU",
+                       "pairs_per_step_per_gpu": PAIRS_PER_STEP, "parallelism": f"batch-sharded x{world}, no collective",
+                       "l2": "inputs larger than L2 (2.1 GB of gradient + output streamed per step)"},
+            "clocks": clocks,
+            "e2e": {"value": e2e, "unit": "Gpairs/s", "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": 4 * (B * N1 * D + B * N2 * D + B * N1 * N2),
+                    "d2h_bytes_per_step": 4 * (B * N1 * D + B * N2 * D)},
+            "gpu_launches": 3 * args.steps,
+            "roofline": roofline, "roofline_hbm": roofline_hbm, "cpu_baseline": cpu_baseline, "extra": extra,
+            "device_status": tpw.device_status(),
+        }
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

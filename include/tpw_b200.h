@@ -173,6 +173,23 @@ TPW_API int tpw_dot_metric_forward_ws(int dtype, int epilogue, int engine,
 TPW_API int tpw_row_center(int dtype, const void *x, void *out, int64_t rows, int64_t D, tpw_stream_t stream);
 TPW_API int tpw_row_norm(int dtype, const void *x, void *norm, int64_t rows, int64_t D, tpw_stream_t stream);
 
+/*
+ * Element-wise part of the cosine-similarity backward (the autograd chain of
+ * OPS/pairwise_metrics.cpp:118-121: norm, outer product, matmul, prf_div "identity",
+ * OPS/cuda/prf_div_kernel.cu:315-366).  `out` is the saved forward result of `epilogue`
+ * (COSINE_SIM, COSINE_DIST or ONE_MINUS_SIM), norm1/norm2 the row norms [B,N1]/[B,N2].
+ * Writes dM [B,N1,N2] (gradient w.r.t. the raw dot products; may alias nothing),
+ * rowterm [B,N1] and colterm [B,N2] (gradients w.r.t. the two norm vectors).  Fixed summation
+ * order, no atomics.  The matrix products dM @ x2 and dM^T @ x1 are then TPW_LP_BWD_MATMUL,
+ * and tpw_cosine_backward_finish adds term[r] * x[r,:] / norm[r] (rows with a zero norm skipped).
+ */
+TPW_API int tpw_cosine_backward_prepare(int dtype, int epilogue, const void *grad, const void *out,
+                                        const void *norm1, const void *norm2,
+                                        void *dM, void *rowterm, void *colterm,
+                                        int64_t B, int64_t N1, int64_t N2, tpw_stream_t stream);
+TPW_API int tpw_cosine_backward_finish(int dtype, void *grad_x, const void *x, const void *norm, const void *term,
+                                       int64_t rows, int64_t D, tpw_stream_t stream);
+
 /* ---- boolean family on packed bits ---------------------------------------------------------- */
 
 /*

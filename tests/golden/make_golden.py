@@ -1,0 +1,146 @@
+"""Generates the golden vectors under tests/golden/ from the reference itself.
+
+Needs ``oracle/_ref/torchpairwise_ref.so`` (``make -C oracle``: the unmodified CPU operators of
+inspiros/torchpairwise v0.3.0 compiled from its own sources).  Every vector is the output of
+``torch.ops.torchpairwise.*`` on CPU for small seeded inputs; inputs are stored next to outputs,
+except for the config-shaped cases whose inputs are regenerated from the seed (their float64
+checksum is stored so that a generator drift is detected rather than mis-reported as a parity
+failure).
+
+    python tests/golden/make_golden.py
+"""
+from __future__ import annotations
+
+import math
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parent.parent
+sys.path.insert(0, str(HERE.parent))
+from cases import (BOOL_METRICS, FLOAT_CASES, FLOAT_METRICS, HAUSDORFF_CASES, config_inputs, float_inputs,  # noqa: E402
+                   bool_inputs, hausdorff_inputs, BOOL_CASES, call_metric)
+
+torch.ops.load_library(str(ROOT / "oracle" / "_ref" / "torchpairwise_ref.so"))
+T = torch.ops.torchpairwise
+
+
+def npy(t):
+    return t.detach().cpu().numpy()
+
+
+def float_golden():
+    out = {}
+    for case in FLOAT_CASES:
+        x1, x2, w, g = float_inputs(case)
+        out[f"{case['name']}/x1"], out[f"{case['name']}/x2"] = npy(x1), npy(x2)
+        out[f"{case['name']}/w"], out[f"{case['name']}/g"] = npy(w), npy(g)
+        for metric in FLOAT_METRICS:
+            if metric.get("needs_square") and not case.get("square", False) and x1.dim() == 3:
+                continue  # the reference's batched weighted check only passes when N1 == D
+            a = x1.clone().requires_grad_(True)
+            b = x2.clone().requires_grad_(True)
+            ww = w.clone().requires_grad_(True)
+            res = call_metric(T, metric, a, b, ww)
+            key = f"{case['name']}/{metric['name']}"
+            st = case.get("stride", 1)  # large outputs are stored sub-sampled
+            out[key + "/out"] = npy(res[..., ::st, ::st])
+            if metric.get("grad", True):
+                res.backward(g)
+                out[key + "/gx1"], out[key + "/gx2"] = npy(a.grad), npy(b.grad)
+                if metric.get("weighted"):
+                    out[key + "/gw"] = npy(ww.grad)
+    np.savez_compressed(HERE / "float_metrics.npz", **out)
+    print("float_metrics.npz", len(out), "arrays")
+
+
+def bool_golden():
+    out = {}
+    for case in BOOL_CASES:
+        x1, x2 = bool_inputs(case)
+        out[f"{case['name']}/x1"], out[f"{case['name']}/x2"] = npy(x1), npy(x2)
+        for name in BOOL_METRICS:
+            fn = getattr(T, name)
+            if name.startswith("pw") and name[2:5] in ("and", "or_", "xor") and x1.dtype != torch.bool:
+                continue
+            with torch.no_grad():
+                import warnings
+                with warnings.catch_warnings():
+                    warnings.simplefilter("ignore")
+                    res = fn(x1, x2)
+            out[f"{case['name']}/{name}"] = npy(res)
+    np.savez_compressed(HERE / "bool_metrics.npz", **out)
+    print("bool_metrics.npz", len(out), "arrays")
+
+
+def hausdorff_golden():
+    out = {}
+    for case in HAUSDORFF_CASES:
+        x1, x2, g = hausdorff_inputs(case)
+        a = x1.clone().requires_grad_(True)
+        b = x2.clone().requires_grad_(True)
+        res, i1, i2 = T.directed_hausdorff_distances(a, b, shuffle=False)
+        res.backward(g)
+        n = case["name"]
+        out[f"{n}/x1"], out[f"{n}/x2"], out[f"{n}/g"] = npy(x1), npy(x2), npy(g)
+        out[f"{n}/out"], out[f"{n}/idx1"], out[f"{n}/idx2"] = npy(res), npy(i1), npy(i2)
+        out[f"{n}/gx1"], out[f"{n}/gx2"] = npy(a.grad), npy(b.grad)
+    np.savez_compressed(HERE / "hausdorff.npz", **out)
+    print("hausdorff.npz", len(out), "arrays")
+
+
+def config_golden():
+    out = {}
+    # C1: X[1024,128], Y[2048,128] fp32, rows ::128 of the output
+    X, Y = config_inputs("C1")
+    out["C1/checksum"] = np.array([X.double().sum().item(), Y.double().sum().item()])
+    for name in ("euclidean_distances", "manhattan_distances", "cosine_distances", "chebyshev_distances",
+                 "sqeuclidean_distances", "correlation_distances"):
+        out[f"C1/{name}"] = npy(getattr(T, name)(X, Y)[::128])
+    # C2 shape, one batch and a 256-row block: minkowski p=3 and chebyshev, forward + backward
+    X, Y, G = config_inputs("C2")
+    out["C2/checksum"] = np.array([X.double().sum().item(), Y.double().sum().item(), G.double().sum().item()])
+    for name, fn in (("minkowski3", lambda a, b: T.minkowski_distances(a, b, 3.0)),
+                     ("chebyshev", lambda a, b: T.chebyshev_distances(a, b))):
+        a = X.clone().requires_grad_(True)
+        b = Y.clone().requires_grad_(True)
+        res = fn(a, b)
+        res.backward(G)
+        out[f"C2/{name}/out"] = npy(res[:, ::16, ::4])
+        out[f"C2/{name}/gx1"] = npy(a.grad[:, ::8])
+        out[f"C2/{name}/gx2"] = npy(b.grad[:, ::8])
+    # C3 shape: bool X[256,1024], Y[512,1024]
+    X, Y = config_inputs("C3")
+    out["C3/checksum"] = np.array([X.double().sum().item(), Y.double().sum().item()])
+    out["C3/hamming_distances"] = npy(T.hamming_distances(X, Y)[::4, ::4])
+    out["C3/jaccard_distances"] = npy(T.jaccard_distances(X, Y)[::4, ::4])
+    # C4 shape: X[256,512], Y[1024,512]
+    X, Y = config_inputs("C4")
+    out["C4/checksum"] = np.array([X.double().sum().item(), Y.double().sum().item()])
+    out["C4/sqeuclidean_distances"] = npy(T.sqeuclidean_distances(X, Y)[::8, ::8])
+    out["C4/cosine_distances"] = npy(T.cosine_distances(X, Y)[::8, ::8])
+    # C5 shape: x1, x2 [4,1,2048,3]
+    X, Y = config_inputs("C5")
+    out["C5/checksum"] = np.array([X.double().sum().item(), Y.double().sum().item()])
+    a = X.clone().requires_grad_(True)
+    b = Y.clone().requires_grad_(True)
+    res, i1, i2 = T.directed_hausdorff_distances(a, b, shuffle=False)
+    res.backward(torch.ones_like(res))
+    out["C5/out"], out["C5/idx1"], out["C5/idx2"] = npy(res), npy(i1), npy(i2)
+    rows1 = a.grad.abs().sum(-1).nonzero()
+    rows2 = b.grad.abs().sum(-1).nonzero()
+    out["C5/gx1_rows"], out["C5/gx1_vals"] = npy(rows1), npy(a.grad[tuple(rows1.t())])
+    out["C5/gx2_rows"], out["C5/gx2_vals"] = npy(rows2), npy(b.grad[tuple(rows2.t())])
+    np.savez_compressed(HERE / "configs.npz", **out)
+    print("configs.npz", len(out), "arrays")
+
+
+if __name__ == "__main__":
+    torch.set_num_threads(8)
+    float_golden()
+    bool_golden()
+    hausdorff_golden()
+    config_golden()

@@ -1,0 +1,359 @@
+"""Parity of the CUDA path with the reference, through the package API (which calls the C ABI).
+
+Three sources of truth, all derived from the reference: the golden vectors it produced
+(tests/golden), the numpy oracle that is pinned against those vectors, and -- at the full
+benchmark sizes, where neither can run -- size-independent identities of the metrics.
+"""
+import math
+import warnings
+
+import numpy as np
+import pytest
+import torch
+
+from cases import (BOOL_CASES, BOOL_METRICS, FLOAT_CASES, FLOAT_METRICS, HAUSDORFF_CASES, call_metric,
+                   config_inputs)
+from oracle import pairwise_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+# the parity contract: fp32 rtol 1e-4 / atol 1e-5, fp64 1e-10, boolean and index outputs bit-exact
+TOL = {torch.float32: dict(rtol=1e-4, atol=1e-5), torch.float64: dict(rtol=1e-10, atol=1e-10)}
+
+
+@pytest.fixture(scope="module")
+def tpw():
+    import torchpairwise_b200
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    yield torchpairwise_b200
+    assert torchpairwise_b200.device_status() == 0, "a kernel gave up a bounded wait"
+
+
+def cuda(a, requires_grad=False):
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t.requires_grad_(True) if requires_grad else t
+
+
+def close(got, ref, tol, scale=1.0, msg=""):
+    ref_t = torch.from_numpy(np.asarray(ref))
+    torch.testing.assert_close(got.detach().cpu(), ref_t, rtol=tol["rtol"], atol=tol["atol"] * scale,
+                               equal_nan=True, msg=lambda m: f"{msg}: {m}")
+
+
+@pytest.mark.parametrize("case", FLOAT_CASES, ids=lambda c: c["name"])
+@pytest.mark.parametrize("metric", FLOAT_METRICS, ids=lambda m: m["name"])
+def test_float_metric_golden(tpw, golden, case, metric):
+    G = golden("float_metrics")
+    key = f"{case['name']}/{metric['name']}"
+    n = case["name"]
+    weighted_batched = metric.get("weighted") and len(case["x1"]) == 3
+    x1, x2 = cuda(G[f"{n}/x1"], True), cuda(G[f"{n}/x2"], True)
+    w, g = cuda(G[f"{n}/w"], True), cuda(G[f"{n}/g"])
+    tol = TOL[x1.dtype]
+    st = case.get("stride", 1)
+    out = call_metric(tpw, metric, x1, x2, w)
+    if key + "/out" in G.files:
+        ref_out, ref_g1, ref_g2 = G[key + "/out"], G[key + "/gx1"], G[key + "/gx2"]
+        ref_gw = G[key + "/gw"] if metric.get("weighted") else None
+    else:
+        # batched weights with N1 != D: the reference rejects them (shape-check slip); the oracle
+        # restates the same arithmetic
+        assert weighted_batched
+        p = metric["kw"]["p"]
+        ref_out = O.wminkowski(G[f"{n}/x1"], G[f"{n}/x2"], G[f"{n}/w"], p)[..., ::st, ::st]
+        ref_g1, ref_g2, ref_gw = O.wminkowski_backward(G[f"{n}/g"], G[f"{n}/x1"], G[f"{n}/x2"], G[f"{n}/w"], p)
+    close(out[..., ::st, ::st], ref_out, tol, msg=key + " forward")
+    out.backward(g)
+    scale = 10 * max(1.0, float(np.abs(ref_g1).max()))
+    close(x1.grad, ref_g1, tol, scale, key + " grad_x1")
+    close(x2.grad, ref_g2, tol, scale, key + " grad_x2")
+    if ref_gw is not None:
+        close(w.grad, ref_gw, tol, 10 * max(1.0, float(np.abs(ref_gw).max())), key + " grad_w")
+
+
+@pytest.mark.parametrize("case", BOOL_CASES, ids=lambda c: c["name"])
+def test_boolean_metrics_bit_exact(tpw, golden, case):
+    G = golden("bool_metrics")
+    n = case["name"]
+    x1, x2 = cuda(G[f"{n}/x1"]), cuda(G[f"{n}/x2"])
+    for name in BOOL_METRICS:
+        if f"{n}/{name}" not in G.files:
+            with pytest.raises(RuntimeError):
+                getattr(tpw, name)(x1, x2)  # pw{and,or,xor}_sum are boolean-only, as in the reference
+            continue
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            got = getattr(tpw, name)(x1, x2)
+        ref = torch.from_numpy(G[f"{n}/{name}"])
+        assert got.dtype == torch.float32
+        got_c = got.cpu()
+        same = (got_c == ref) | (got_c.isnan() & ref.isnan())
+        assert bool(same.all()), f"{n}/{name}: {int((~same).sum())} of {ref.numel()} values differ"
+
+
+def test_boolean_cast_warns(tpw):
+    x = torch.randint(0, 3, (6, 9), device="cuda")
+    with pytest.warns(UserWarning, match="converted to torch.bool"):
+        tpw.jaccard_distances(x)
+    with pytest.warns(DeprecationWarning):
+        tpw.kulsinski_distances(x > 0)
+
+
+@pytest.mark.parametrize("case", HAUSDORFF_CASES, ids=lambda c: c["name"])
+def test_hausdorff_golden(tpw, golden, case):
+    G = golden("hausdorff")
+    n = case["name"]
+    x1, x2, g = cuda(G[f"{n}/x1"], True), cuda(G[f"{n}/x2"], True), cuda(G[f"{n}/g"])
+    out, i1, i2 = tpw.directed_hausdorff_distances(x1, x2)
+    # the squared distances are accumulated with the reference's rounding, so even fp32 agrees exactly
+    assert torch.equal(out.detach().cpu(), torch.from_numpy(G[f"{n}/out"]))
+    assert torch.equal(i1.cpu(), torch.from_numpy(G[f"{n}/idx1"]))
+    assert torch.equal(i2.cpu(), torch.from_numpy(G[f"{n}/idx2"]))
+    assert i1.dtype == torch.int64 and not i1.requires_grad
+    out.backward(g)
+    tol = TOL[x1.dtype]
+    close(x1.grad, G[f"{n}/gx1"], tol, msg=n + " grad_x1")
+    close(x2.grad, G[f"{n}/gx2"], tol, msg=n + " grad_x2")
+
+
+def test_hausdorff_shuffle_and_cdist(tpw):
+    g = torch.Generator().manual_seed(3)
+    x1 = torch.rand(2, 3, 40, 3, generator=g).cuda()
+    x2 = torch.rand(2, 2, 31, 3, generator=g).cuda()
+    ref, r1, r2 = tpw.directed_hausdorff_distances(x1, x2)
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    out, i1, i2 = tpw.directed_hausdorff_distances(x1, x2, shuffle=True, generator=gen)
+    assert torch.equal(out, ref)  # visiting order never changes the value
+    # random data has no ties, so the indices agree as well
+    assert torch.equal(i1, r1) and torch.equal(i2, r2)
+    assert torch.equal(tpw.cdist(x1, x2, "directed_hausdorff"), ref)
+    # with exact ties the shuffled indices follow visiting order; the attained distance is still the output
+    xi = torch.randint(0, 3, (1, 2, 30, 3), generator=g).float().cuda()
+    yi = torch.randint(0, 3, (1, 2, 33, 3), generator=g).float().cuda() + 0.5
+    out, i1, i2 = tpw.directed_hausdorff_distances(xi, yi, shuffle=True, generator=gen)
+    for i in range(2):
+        for j in range(2):
+            d = (xi[0, i, i1[0, i, j]] - yi[0, j, i2[0, i, j]]).pow(2).sum().sqrt()
+            assert torch.equal(d, out[0, i, j])
+    o_ref, _, _ = O.directed_hausdorff(xi.cpu().numpy(), yi.cpu().numpy())
+    assert np.array_equal(out.cpu().numpy(), o_ref)
+
+
+def test_config_shaped_golden(tpw, golden):
+    G = golden("configs")
+
+    def inputs(name):
+        ts = config_inputs(name)
+        chk = np.array([t.double().sum().item() for t in ts])
+        if not np.array_equal(chk, G[f"{name}/checksum"]):
+            pytest.skip("this torch build generates different seeded inputs than the one that made the vectors")
+        return ts
+
+    tol = TOL[torch.float32]
+    X, Y = inputs("C1")
+    for name in ("euclidean_distances", "manhattan_distances", "cosine_distances", "chebyshev_distances",
+                 "sqeuclidean_distances", "correlation_distances"):
+        close(getattr(tpw, name)(X.cuda(), Y.cuda())[::128], G[f"C1/{name}"], tol, msg="C1 " + name)
+    X, Y, Gr = inputs("C2")
+    for name, fn in (("minkowski3", lambda a, b: tpw.minkowski_distances(a, b, 3.0)),
+                     ("chebyshev", lambda a, b: tpw.chebyshev_distances(a, b))):
+        a, b = X.cuda().requires_grad_(True), Y.cuda().requires_grad_(True)
+        res = fn(a, b)
+        res.backward(Gr.cuda())
+        close(res[:, ::16, ::4], G[f"C2/{name}/out"], tol, msg="C2 " + name)
+        scale = 10 * float(np.abs(G[f"C2/{name}/gx1"]).max())
+        close(a.grad[:, ::8], G[f"C2/{name}/gx1"], tol, scale, "C2 grad_x1 " + name)
+        close(b.grad[:, ::8], G[f"C2/{name}/gx2"], tol, scale, "C2 grad_x2 " + name)
+    X, Y = inputs("C3")
+    for name in ("hamming_distances", "jaccard_distances"):
+        got = getattr(tpw, name)(X.cuda(), Y.cuda())[::4, ::4].cpu()
+        assert torch.equal(got, torch.from_numpy(G[f"C3/{name}"])), name
+    X, Y = inputs("C4")
+    for name in ("sqeuclidean_distances", "cosine_distances"):
+        close(getattr(tpw, name)(X.cuda(), Y.cuda())[::8, ::8], G[f"C4/{name}"], tol, msg="C4 " + name)
+    X, Y = inputs("C5")
+    a, b = X.cuda().requires_grad_(True), Y.cuda().requires_grad_(True)
+    res, i1, i2 = tpw.directed_hausdorff_distances(a, b)
+    assert torch.equal(res.detach().cpu(), torch.from_numpy(G["C5/out"]))
+    assert torch.equal(i1.cpu(), torch.from_numpy(G["C5/idx1"])) and torch.equal(i2.cpu(), torch.from_numpy(G["C5/idx2"]))
+    res.backward(torch.ones_like(res))
+    r1 = torch.from_numpy(G["C5/gx1_rows"])
+    close(a.grad.cpu()[tuple(r1.t())], G["C5/gx1_vals"], tol, msg="C5 grad_x1")
+    assert int((a.grad.abs().sum(-1) != 0).sum()) == r1.shape[0]
+    r2 = torch.from_numpy(G["C5/gx2_rows"])
+    close(b.grad.cpu()[tuple(r2.t())], G["C5/gx2_vals"], tol, msg="C5 grad_x2")
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 1), (3, 1, 2), (129, 127, 33), (2, 257, 130), (50, 300, 7), (64, 64, 260)])
+@pytest.mark.parametrize("p", [1.0, 2.0, 3.0, 2.5, math.inf])
+def test_ragged_shapes_vs_oracle(tpw, shape, p):
+    n1, n2, d = shape
+    g = torch.Generator().manual_seed(n1 * 1000 + n2 * 10 + d)
+    x1 = torch.randn(2, n1, d, generator=g)
+    x2 = torch.randn(2, n2, d, generator=g)
+    gr = torch.randn(2, n1, n2, generator=g)
+    a, b = x1.cuda().requires_grad_(True), x2.cuda().requires_grad_(True)
+    out = tpw.minkowski_distances(a, b, p)
+    ref = O.cdist(x1.numpy(), x2.numpy(), p)
+    tol = TOL[torch.float32]
+    close(out, ref, tol, msg=f"forward {shape} p={p}")
+    out.backward(gr.cuda())
+    # the oracle's backward in float64 from the same inputs: the tolerance then only sees our rounding
+    g1, g2 = O.cdist_backward(gr.double().numpy(), x1.double().numpy(), x2.double().numpy(), p)
+    if math.isinf(p):
+        g1, g2 = O.cdist_backward(gr.numpy(), x1.numpy(), x2.numpy(), p, out=out.detach().cpu().numpy())
+    scale = 10 * max(1.0, float(np.abs(g1).max()))
+    close(a.grad, g1.astype(np.float32), tol, scale, f"grad_x1 {shape} p={p}")
+    close(b.grad, g2.astype(np.float32), tol, scale, f"grad_x2 {shape} p={p}")
+
+
+def test_tma_and_plain_load_paths_agree(tpw):
+    """An input whose base address is not 16-byte aligned takes the guarded plain-load path; it
+    stages the same layout, so results are bit-identical to the TMA path."""
+    g = torch.Generator().manual_seed(9)
+    x1 = torch.randn(200, 64, generator=g).cuda()
+    x2 = torch.randn(150, 64, generator=g).cuda()
+    gr = torch.randn(200, 150, generator=g).cuda()
+
+    def shifted(t):
+        buf = torch.empty(t.numel() + 1, device="cuda", dtype=t.dtype)
+        view = buf[1:].view(t.shape)
+        view.copy_(t)
+        assert view.data_ptr() % 16 != 0
+        return view
+
+    for p in (1.0, 3.0, math.inf, 2.5):
+        a, b = x1.clone().requires_grad_(True), x2.clone().requires_grad_(True)
+        o1 = tpw.minkowski_distances(a, b, p)
+        o1.backward(gr)
+        a2, b2 = shifted(x1).requires_grad_(True), shifted(x2).requires_grad_(True)
+        o2 = tpw.minkowski_distances(a2, b2, p)
+        o2.backward(shifted(gr))
+        assert torch.equal(o1, o2), p
+        assert torch.equal(a.grad, a2.grad) and torch.equal(b.grad, b2.grad), p
+    xb = torch.rand(70, 300, generator=g).cuda() < 0.2
+    assert torch.equal(tpw.jaccard_distances(xb), tpw.jaccard_distances(shifted(xb)))
+
+
+def test_self_distances_and_empty_inputs(tpw):
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(40, 16, generator=g).cuda()
+    # x2 = None means (x1, x1); the direct-difference form gives an exactly zero diagonal
+    assert torch.equal(tpw.sqeuclidean_distances(x).diagonal(), torch.zeros(40, device="cuda"))
+    assert torch.equal(tpw.euclidean_distances(x).diagonal(), torch.zeros(40, device="cuda"))
+    assert torch.equal(tpw.manhattan_distances(x), tpw.manhattan_distances(x, x))
+    e = torch.empty(0, 16, device="cuda")
+    assert tpw.euclidean_distances(e, x).shape == (0, 40)
+    assert tpw.euclidean_distances(x, e).shape == (40, 0)
+    assert tpw.jaccard_distances(e > 0, x > 0).shape == (0, 40)
+    xr = x.clone().requires_grad_(True)
+    tpw.minkowski_distances(xr, e, 3.0).sum().backward()
+    assert torch.equal(xr.grad, torch.zeros_like(xr))
+
+
+def test_half_precision_inputs(tpw):
+    g = torch.Generator().manual_seed(8)
+    x1 = torch.randn(33, 24, generator=g).cuda()
+    x2 = torch.randn(20, 24, generator=g).cuda()
+    for dt in (torch.float16, torch.bfloat16):
+        out = tpw.manhattan_distances(x1.to(dt), x2.to(dt))
+        assert out.dtype == dt
+        ref = tpw.manhattan_distances(x1.to(dt).float(), x2.to(dt).float())
+        assert torch.equal(out, ref.to(dt))
+
+
+def test_cdist_dispatcher(tpw):
+    g = torch.Generator().manual_seed(2)
+    x1 = torch.randn(12, 6, generator=g).cuda()
+    x2 = torch.randn(9, 6, generator=g).cuda()
+    assert torch.equal(tpw.cdist(x1, x2), tpw.minkowski_distances(x1, x2, 2.0))
+    assert torch.equal(tpw.cdist(x1, x2, "minkowski", p=3.0), tpw.minkowski_distances(x1, x2, 3.0))
+    assert torch.equal(tpw.cdist(x1, x2, "manhattan"), tpw.manhattan_distances(x1, x2))
+    assert torch.equal(tpw.cdist(x1, x2, "l1"), tpw.cdist(x1, x2, "cityblock"))
+    assert torch.equal(tpw.cdist(x1, x2, "linf"), tpw.chebyshev_distances(x1, x2))
+    w = torch.rand(6, generator=g).cuda()
+    assert torch.equal(tpw.cdist(x1, x2, "wminkowski", w=w, p=3.0), tpw.wminkowski_distances(x1, x2, 3.0, w))
+    xb, yb = x1 > 0, x2 > 0
+    # the reference's cdist maps "kulsinski" onto kulczynski1
+    assert torch.equal(tpw.cdist(xb, yb, "kulsinski"), tpw.kulczynski1_distances(xb, yb), )
+    with pytest.raises(TypeError, match="incompatible arguments p"):
+        tpw.cdist(x1, x2, "euclidean", p=3.0)
+    with pytest.raises(RuntimeError, match="unkown distance metric"):
+        tpw.cdist(x1, x2, "nope")
+    with pytest.raises(NotImplementedError):
+        tpw.pdist(x1)
+
+
+def test_gradcheck_float64(tpw):
+    g = torch.Generator().manual_seed(6)
+    x1 = torch.randn(5, 4, generator=g, dtype=torch.float64).cuda().requires_grad_(True)
+    x2 = torch.randn(6, 4, generator=g, dtype=torch.float64).cuda().requires_grad_(True)
+    w = (torch.rand(4, generator=g, dtype=torch.float64) + 0.5).cuda().requires_grad_(True)
+    gc = torch.autograd.gradcheck
+    assert gc(lambda a, b: tpw.minkowski_distances(a, b, 3.0), (x1, x2))
+    assert gc(lambda a, b: tpw.minkowski_distances(a, b, 2.5), (x1, x2))
+    assert gc(lambda a, b: tpw.euclidean_distances(a, b), (x1, x2))
+    assert gc(lambda a, b: tpw.sqeuclidean_distances(a, b), (x1, x2))
+    assert gc(lambda a, b: tpw.cosine_similarity(a, b), (x1, x2))
+    assert gc(lambda a, b: tpw.correlation_distances(a, b), (x1, x2))
+    assert gc(lambda a, b, c: tpw.wminkowski_distances(a, b, 3.0, c), (x1, x2, w))
+    s1 = torch.rand(2, 7, 3, generator=g, dtype=torch.float64).cuda().requires_grad_(True)
+    s2 = torch.rand(3, 5, 3, generator=g, dtype=torch.float64).cuda().requires_grad_(True)
+    assert gc(lambda a, b: tpw.directed_hausdorff_distances(a, b)[0], (s1, s2))  # the reference's one real test
+
+
+def test_full_size_identities(tpw):
+    """Benchmark-size runs checked through identities that need no reference run."""
+    g = torch.Generator().manual_seed(0)
+    # C2: translation invariance of the L_p distances => sum_i grad_x1[i] + sum_j grad_x2[j] = 0
+    X = torch.randn(4, 4096, 256, generator=g).cuda().requires_grad_(True)
+    Y = torch.randn(4, 4096, 256, generator=g).cuda().requires_grad_(True)
+    Gr = torch.randn(4, 4096, 4096, generator=g).cuda()
+    for p in (3.0, math.inf):
+        X.grad = Y.grad = None
+        out = tpw.minkowski_distances(X, Y, p)
+        out.backward(Gr)
+        resid = X.grad.double().sum(1) + Y.grad.double().sum(1)
+        ref_mag = X.grad.double().abs().sum(1) + Y.grad.double().abs().sum(1)
+        assert float((resid.abs() / ref_mag).max()) < 1e-5, p
+        with torch.no_grad():
+            assert torch.equal(tpw.minkowski_distances(Y, X, p), out.transpose(1, 2)), p  # exact symmetry
+    del X, Y, Gr, out
+    # C3: sum_ij |x_i & y_j| = sum_k colcount_x[k] * colcount_y[k], an integer identity
+    Xb = torch.rand(65536, 1024, generator=g).cuda() < 0.1
+    Yb = torch.rand(16384, 1024, generator=g).cuda() < 0.1
+    n11 = tpw.pwand_sum(Xb, Yb)
+    expect = int((Xb.sum(0, dtype=torch.int64) * Yb.sum(0, dtype=torch.int64)).sum())
+    assert int(n11.sum(dtype=torch.float64)) == expect
+    ham = tpw.hamming_distances(Xb, Yb)
+    nx, ny = Xb.sum(1, dtype=torch.float32)[:, None], Yb.sum(1, dtype=torch.float32)[None, :]
+    assert torch.equal(ham, (nx + ny - 2 * n11) / 1024.0)  # all operands are exact float32 integers
+    jac = tpw.jaccard_distances(Xb, Yb)
+    assert float(jac.min()) >= 0.0 and float(jac.max()) <= 1.0
+    del Xb, Yb, n11, ham, jac
+    # C4: sum_j |x_i - y_j|^2 = N2 |x_i|^2 + sum_j |y_j|^2 - 2 x_i . sum_j y_j
+    X = torch.randn(131072, 512, generator=g).cuda()
+    Y = torch.randn(16384, 512, generator=g).cuda()
+    sq = tpw.sqeuclidean_distances(X, Y)
+    lhs = sq.sum(1, dtype=torch.float64)
+    Xd, Yd = X.double(), Y.double()
+    rhs = 16384 * Xd.pow(2).sum(1) + Yd.pow(2).sum() - 2 * Xd @ Yd.sum(0)
+    assert float(((lhs - rhs).abs() / rhs).max()) < 1e-6
+    del sq, lhs, rhs, Xd, Yd
+    cd = tpw.cosine_distances(X[:32768], Y)
+    assert float(cd.min()) >= 0.0 and float(cd.max()) <= 2.0
+    close(cd[:64, :64], O.cosine_distances(X[:64].cpu().numpy(), Y[:64].cpu().numpy()), TOL[torch.float32])
+    del cd, X, Y
+    # C5: the attained pair reproduces the output, and the value does not depend on point order
+    P = torch.rand(64, 8192, 3, generator=g) * 2 - 1
+    Q = P + 0.05 * torch.randn(64, 8192, 3, generator=g)
+    x1, x2 = P[:, None].cuda(), Q[:, None].cuda()
+    out, i1, i2 = tpw.directed_hausdorff_distances(x1, x2)
+    pick1 = x1[:, 0].gather(1, i1.view(64, 1, 1).expand(64, 1, 3))[:, 0]
+    pick2 = x2[:, 0].gather(1, i2.view(64, 1, 1).expand(64, 1, 3))[:, 0]
+    d = pick1 - pick2
+    dd = ((d[:, 0] * d[:, 0] + d[:, 1] * d[:, 1]) + d[:, 2] * d[:, 2]).sqrt()
+    assert torch.equal(dd, out.view(64))
+    perm = torch.randperm(8192, generator=g).cuda()
+    out2, _, _ = tpw.directed_hausdorff_distances(x1[:, :, perm], x2[:, :, perm.flip(0)])
+    assert torch.equal(out, out2)

@@ -1,0 +1,114 @@
+"""The numpy oracle against the golden vectors produced by the reference itself (CPU only)."""
+import math
+
+import numpy as np
+import pytest
+
+from cases import BOOL_CASES, FLOAT_CASES, FLOAT_METRICS, HAUSDORFF_CASES
+from oracle import pairwise_oracle as O
+
+# fp32 tolerance of the parity contract; fp64 is held to 1e-10
+TOL = {np.dtype("float32"): dict(rtol=1e-4, atol=1e-5), np.dtype("float64"): dict(rtol=1e-10, atol=1e-10)}
+
+
+def _oracle_forward(metric, x1, x2, w):
+    fn, kw = metric["fn"], metric.get("kw", {})
+    p = kw.get("p")
+    if fn == "euclidean_distances": return O.cdist(x1, x2, 2.0)
+    if fn == "manhattan_distances": return O.cdist(x1, x2, 1.0)
+    if fn == "chebyshev_distances": return O.cdist(x1, x2, math.inf)
+    if fn == "minkowski_distances": return O.cdist(x1, x2, p)
+    if fn == "sqeuclidean_distances": return O.sqeuclidean(x1, x2)
+    if fn == "cosine_similarity": return O.cosine_similarity(x1, x2)
+    if fn == "cosine_distances": return O.cosine_distances(x1, x2)
+    if fn == "correlation_distances": return O.correlation_distances(x1, x2)
+    if fn == "linear_kernel": return x1 @ np.swapaxes(x2, -1, -2)
+    if fn == "wminkowski_distances": return O.wminkowski(x1, x2, w, p)
+    if fn == "_ppminkowski": return O.ppminkowski(x1, x2, p)
+    raise KeyError(fn)
+
+
+def _oracle_backward(metric, g, x1, x2, w):
+    fn, kw = metric["fn"], metric.get("kw", {})
+    p = kw.get("p")
+    if fn == "euclidean_distances": return O.cdist_backward(g, x1, x2, 2.0)
+    if fn == "manhattan_distances": return O.cdist_backward(g, x1, x2, 1.0)
+    if fn == "chebyshev_distances": return O.cdist_backward(g, x1, x2, math.inf)
+    if fn == "minkowski_distances": return O.cdist_backward(g, x1, x2, p)
+    if fn == "sqeuclidean_distances": return O.ppminkowski_backward(g, x1, x2, 2.0)
+    if fn == "_ppminkowski": return O.ppminkowski_backward(g, x1, x2, p)
+    if fn == "wminkowski_distances": return O.wminkowski_backward(g, x1, x2, w, p)
+    if fn == "cosine_similarity": return O.cosine_similarity_backward(g, x1, x2)
+    if fn == "linear_kernel": return g @ x2, np.swapaxes(g, -1, -2) @ x1
+    return None
+
+
+@pytest.mark.parametrize("case", FLOAT_CASES, ids=lambda c: c["name"])
+@pytest.mark.parametrize("metric", FLOAT_METRICS, ids=lambda m: m["name"])
+def test_float_metric_matches_reference(golden, case, metric):
+    G = golden("float_metrics")
+    key = f"{case['name']}/{metric['name']}"
+    if key + "/out" not in G.files:
+        pytest.skip("the reference rejects this input (batched weights need N1 == D)")
+    x1, x2, w, g = (G[f"{case['name']}/{k}"] for k in ("x1", "x2", "w", "g"))
+    tol = TOL[x1.dtype]
+    st = case.get("stride", 1)
+    out = _oracle_forward(metric, x1, x2, w)
+    np.testing.assert_allclose(out[..., ::st, ::st], G[key + "/out"], **tol)
+    grads = _oracle_backward(metric, g, x1, x2, w)
+    if grads is not None:
+        # gradients sum up to N terms of size |g|*|d|^(p-1): scale the absolute floor accordingly
+        scale = max(1.0, float(np.abs(G[key + "/gx1"]).max()))
+        gtol = dict(rtol=tol["rtol"], atol=tol["atol"] * scale * 10)
+        np.testing.assert_allclose(grads[0], G[key + "/gx1"], **gtol)
+        np.testing.assert_allclose(grads[1], G[key + "/gx2"], **gtol)
+        if metric.get("weighted"):
+            np.testing.assert_allclose(grads[2], G[key + "/gw"], **gtol)
+
+
+_BOOL_FAMILY = ["jaccard", "kulsinski", "kulczynski1", "yule", "dice", "rogerstanimoto", "russellrao",
+                "sokalmichener", "sokalsneath"]
+
+
+@pytest.mark.parametrize("case", BOOL_CASES, ids=lambda c: c["name"])
+def test_boolean_family_is_bit_exact(golden, case):
+    G = golden("bool_metrics")
+    n = case["name"]
+    x1, x2 = G[f"{n}/x1"], G[f"{n}/x2"]
+    for name in _BOOL_FAMILY:
+        ref = G[f"{n}/{name}_distances"]
+        got = O.boolean_metric(name, x1 != 0, x2 != 0)
+        np.testing.assert_array_equal(got, ref, err_msg=name)  # NaN == NaN in assert_array_equal
+        assert got.dtype == np.float32
+    np.testing.assert_array_equal(O.hamming(x1, x2), G[f"{n}/hamming_distances"])
+    for op in ("eq", "ne"):
+        for red in ("sum", "mean"):
+            np.testing.assert_array_equal(O.compare_reduce(x1, x2, op, red), G[f"{n}/pw{op}_{red}"])
+    if case["kind"] == "bool":
+        for op in ("and", "or", "xor"):
+            np.testing.assert_array_equal(O.pw_sum(x1, x2, op), G[f"{n}/pw{op}_sum"])
+
+
+@pytest.mark.parametrize("case", HAUSDORFF_CASES, ids=lambda c: c["name"])
+def test_hausdorff_matches_reference(golden, case):
+    G = golden("hausdorff")
+    n = case["name"]
+    x1, x2, g = G[f"{n}/x1"], G[f"{n}/x2"], G[f"{n}/g"]
+    out, i1, i2 = O.directed_hausdorff(x1, x2)
+    np.testing.assert_array_equal(out, G[f"{n}/out"])  # same arithmetic, same rounding
+    np.testing.assert_array_equal(i1, G[f"{n}/idx1"])
+    np.testing.assert_array_equal(i2, G[f"{n}/idx2"])
+    g1, g2 = O.directed_hausdorff_backward(g, out, i1, i2, x1, x2)
+    tol = TOL[x1.dtype]
+    np.testing.assert_allclose(g1, G[f"{n}/gx1"], **tol)
+    np.testing.assert_allclose(g2, G[f"{n}/gx2"], **tol)
+
+
+def test_prf_div_modes():
+    x = np.array([1.0, 2.0, 0.0, -3.0], dtype=np.float32)
+    y = np.array([2.0, 0.0, 0.0, 1.5], dtype=np.float32)
+    np.testing.assert_array_equal(O.prf_div(x, y, "zero"), np.array([0.5, 0.0, 0.0, -2.0], dtype=np.float32))
+    np.testing.assert_array_equal(O.prf_div(x, y, "identity"), np.array([0.5, 2.0, 0.0, -2.0], dtype=np.float32))
+    gs, go = O.prf_div_backward(np.ones_like(x), x, y, "identity")
+    np.testing.assert_allclose(gs, [0.5, 1.0, 1.0, 1 / 1.5], rtol=1e-6)
+    np.testing.assert_allclose(go, [-0.25, 0.0, 0.0, 3 / 2.25], rtol=1e-6)

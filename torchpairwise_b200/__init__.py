@@ -1,0 +1,69 @@
+"""B200 (sm_100a) implementation of torchpairwise's pairwise-reduction hot path.
+
+The module mirrors the reference's Python surface (``torchpairwise/__init__.py`` and
+``torchpairwise/ops``): the same function names with the same arguments, backed by hand-written
+CUDA kernels behind the C ABI of ``include/tpw_b200.h``.  CUDA tensors only.
+"""
+from ._abi import TpwError, device_status, lib, measure_issue_peak
+from .cpdist import cdist, pdist
+from .ops import (
+    _directed_hausdorff,
+    _ppminkowski,
+    _wminkowski,
+    chebyshev_distances,
+    cityblock_distances,
+    correlation_distances,
+    cosine_distances,
+    cosine_similarity,
+    dice_distances,
+    directed_hausdorff_distances,
+    euclidean_distances,
+    hamming_distances,
+    jaccard_distances,
+    kulczynski1_distances,
+    kulsinski_distances,
+    l1_distances,
+    l2_distances,
+    linear_kernel,
+    linf_distances,
+    lp_distances,
+    manhattan_distances,
+    minkowski_distances,
+    prf_div,
+    pwand_sum,
+    pweq_mean,
+    pweq_sum,
+    pwne_mean,
+    pwne_sum,
+    pwor_sum,
+    pwxor_sum,
+    rogerstanimoto_distances,
+    russellrao_distances,
+    sokalmichener_distances,
+    sokalsneath_distances,
+    sqeuclidean_distances,
+    wminkowski_distances,
+    yule_distances,
+)
+
+__version__ = "0.1.0"
+
+
+def has_ops() -> bool:
+    """torchpairwise.extension.has_ops (extension.py:163-165)."""
+    return True
+
+
+def with_cuda() -> bool:
+    """torchpairwise.extension.with_cuda (extension.py:168-175)."""
+    return True
+
+
+def cuda_version() -> int:
+    """CUDA runtime version the kernels were compiled with (csrc/torchpairwise.cpp:28-34)."""
+    return int(lib.tpw_cuda_version())
+
+
+def cuda_arch_list():
+    """Architectures in the binary (csrc/torchpairwise.cpp:36-52): sm_100a only."""
+    return [lib.tpw_cuda_arch_flags().decode()]

@@ -3,8 +3,10 @@
 Plain ``nvcc`` on the ``csrc/*.cu`` files (no torch headers), one object per source compiled in
 parallel, linked into one shared object that sits in-tree next to the package.
 
-    python -m torchpairwise_b200.build            # build if sources are newer than the library
-    python -m torchpairwise_b200.build --force -v # rebuild everything, print ptxas resource usage
+    python torchpairwise_b200/build.py            # rebuild the objects whose sources changed
+    python torchpairwise_b200/build.py --force -v # rebuild everything, print ptxas resource usage
+
+Run it as a file (not with ``-m``): importing the package needs the library this script makes.
 """
 from __future__ import annotations
 
@@ -48,8 +50,18 @@ def is_stale() -> bool:
     return any(p.stat().st_mtime > t for p in _deps())
 
 
-def _compile_one(nvcc: str, src: Path, verbose: bool) -> tuple[Path, str]:
+def _obj_stale(src: Path, obj: Path) -> bool:
+    if not obj.exists():
+        return True
+    t = obj.stat().st_mtime
+    shared = sorted(CSRC.glob("*.cuh")) + sorted(INCLUDE.glob("*.h")) + [Path(__file__)]
+    return any(p.stat().st_mtime > t for p in [src, *shared])
+
+
+def _compile_one(nvcc: str, src: Path, verbose: bool, force: bool) -> tuple[Path, str]:
     obj = OBJ_DIR / (src.stem + ".o")
+    if not force and not _obj_stale(src, obj):
+        return obj, ""
     cmd = [nvcc, *ARCH_FLAGS, "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC,-fvisibility=hidden",
            "-I", str(INCLUDE), "-c", str(src), "-o", str(obj)]
     if verbose:
@@ -69,7 +81,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     srcs = _sources()
     objs = []
     with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
-        for obj, log in ex.map(lambda s: _compile_one(nvcc, s, verbose), srcs):
+        for obj, log in ex.map(lambda s: _compile_one(nvcc, s, verbose, force), srcs):
             objs.append(obj)
             if verbose and log:
                 print(log, file=sys.stderr)

@@ -1,0 +1,82 @@
+"""``cdist(x1, x2, metric=..., **kwargs)``: the string dispatcher of OPS/cpdist.cpp:149-231.
+
+Same metric names, the same per-metric keyword validation (a keyword the metric does not take
+raises ``TypeError`` naming it, OPS/cpdist.cpp:35-79), the same defaults (``p`` defaults to 2) and
+the same quirk that ``metric="kulsinski"`` evaluates kulczynski1 (the inline helper at
+OPS/pairwise_metrics.h:557-561 calls that functor).  Metrics outside the accelerated path raise
+``NotImplementedError``; ``pdist`` raises it for everything, as the reference does
+(OPS/cpdist.cpp:233-246).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+from torch import Tensor
+
+from . import ops
+
+SUPPORTED_METRICS = [
+    "braycurtis", "canberra", "chebyshev", "cityblock", "correlation", "cosine",
+    "dice", "directed_hausdorff", "euclidean", "hamming", "haversine", "jaccard",
+    "jensenshannon", "kulczynski1", "kulsinski", "l1", "l2", "lp", "linf", "mahalanobis",
+    "manhattan", "minkowski", "rogerstanimoto", "russellrao", "seuclidean", "snr",
+    "sokalmichener", "sokalsneath", "sqeuclidean", "wminkowski", "yule",
+]
+
+# metric -> keyword arguments it accepts (DEFINE_CPDIST_METRIC_SPEC table, OPS/cpdist.cpp:82-147)
+_ACCEPTS = {m: () for m in SUPPORTED_METRICS}
+_ACCEPTS.update({
+    "directed_hausdorff": ("shuffle", "generator"),
+    "minkowski": ("p",), "lp": ("p",), "wminkowski": ("w", "p"),
+    "seuclidean": ("V",), "mahalanobis": ("VI",), "jensenshannon": ("base",),
+})
+
+_SCHEMAS = {
+    "minkowski": "(Tensor x1, Tensor? x2=None, float p=2) -> Tensor",
+    "lp": "(Tensor x1, Tensor? x2=None, float p=2) -> Tensor",
+    "wminkowski": "(Tensor x1, Tensor? x2=None, float p=2, Tensor? w=None) -> Tensor",
+    "seuclidean": "(Tensor x1, Tensor? x2=None, Tensor? V=None) -> Tensor",
+    "mahalanobis": "(Tensor x1, Tensor? x2=None, Tensor? VI=None) -> Tensor",
+    "jensenshannon": "(Tensor x1, Tensor? x2=None, float? base=None) -> Tensor",
+    "directed_hausdorff": "(Tensor x1, Tensor? x2=None, *, bool shuffle=False, Generator? generator=None) "
+                          "-> (Tensor output, Tensor x1_indices, Tensor x2_indices)",
+}
+
+_OUT_OF_SCOPE = {"braycurtis", "canberra", "haversine", "jensenshannon", "mahalanobis", "seuclidean", "snr"}
+
+
+def _check_extra_args(metric: str, **given) -> None:
+    bad = [k for k in ("w", "V", "VI", "p", "base", "shuffle", "generator")
+           if given.get(k) is not None and k not in _ACCEPTS[metric]]
+    if bad:
+        schema = _SCHEMAS.get(metric, "(Tensor x1, Tensor? x2=None) -> Tensor")
+        raise TypeError(
+            f"{metric}_distances was called with incompatible arguments {', '.join(bad)}.\n"
+            f"The following signature is supported:\n    torchpairwise::{metric}_distances{schema}\n"
+        )
+
+
+def cdist(x1: Tensor, x2: Tensor, metric: str = "minkowski", *, w: Optional[Tensor] = None,
+          V: Optional[Tensor] = None, VI: Optional[Tensor] = None, p: Optional[float] = None,
+          base: Optional[float] = None, shuffle: Optional[bool] = None, generator=None) -> Tensor:
+    if metric not in SUPPORTED_METRICS:
+        raise RuntimeError(f"Got unkown distance metric: {metric}. Supported metrics are [{', '.join(SUPPORTED_METRICS)}]")
+    _check_extra_args(metric, w=w, V=V, VI=VI, p=p, base=base, shuffle=shuffle, generator=generator)
+    if metric in _OUT_OF_SCOPE:
+        raise NotImplementedError(f"metric '{metric}' is outside the B200 pairwise-reduction path of this library")
+    if metric == "directed_hausdorff":
+        return ops.directed_hausdorff_distances(x1, x2, shuffle=bool(shuffle) if shuffle is not None else False,
+                                                generator=generator)[0]
+    if metric in ("minkowski", "lp"):
+        return ops.minkowski_distances(x1, x2, 2.0 if p is None else p)
+    if metric == "wminkowski":
+        return ops.wminkowski_distances(x1, x2, 2.0 if p is None else p, w)
+    if metric == "kulsinski":
+        return ops.kulczynski1_distances(x1, x2)
+    if metric == "cosine":
+        return ops.cosine_distances(x1, x2)
+    return getattr(ops, f"{metric}_distances")(x1, x2)
+
+
+def pdist(input: Tensor, metric: str = "minkowski", **kwargs) -> Tensor:
+    raise NotImplementedError("pdist is yet to be implemented.")

@@ -4,6 +4,7 @@
 #include "common.cuh"
 
 #include <mutex>
+#include <stdlib.h>
 #include <string.h>
 
 namespace tpw {
@@ -36,6 +37,14 @@ int *device_status_ptr() {
         cache[dev] = p;
     }
     return cache[dev];
+}
+
+bool tma_disabled() {
+    static const bool off = [] {
+        const char *v = getenv("TPW_DISABLE_TMA");
+        return v && v[0] && v[0] != '0';
+    }();
+    return off;
 }
 
 int sm_count() {

@@ -264,7 +264,7 @@ extern "C" int tpw_bool_metric_forward(int metric, const uint32_t *x1_words, con
                   "tpw_bool_metric_forward: a dimension exceeds 2^31-1");
     P.status = device_status_ptr();
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const bool tma_ok = aligned16(x1_words) && aligned16(x2_words) && words_per_row % 4 == 0;
+    const bool tma_ok = !tma_disabled() && aligned16(x1_words) && aligned16(x2_words) && words_per_row % 4 == 0;
     CUtensorMap m1, m2;
     memset(&m1, 0, sizeof(m1));
     memset(&m2, 0, sizeof(m2));

@@ -43,6 +43,10 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 // as an argument; NULL is returned when the address cannot be resolved.
 int *device_status_ptr();
 
+// True when the environment variable TPW_DISABLE_TMA is set to a non-zero value: every kernel then
+// stages its tiles with guarded plain loads (a debugging aid; results are bit-identical).
+bool tma_disabled();
+
 // Number of SMs of the current device (cached per device).
 int sm_count();
 

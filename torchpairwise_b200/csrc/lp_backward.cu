@@ -318,7 +318,7 @@ int launch_backward(BwdParams P, cudaStream_t stream) {
                   "lp backward: a dimension exceeds 2^31-1");
     P.status = device_status_ptr();
 
-    bool tma_ok = aligned16(P.stream) && aligned16(P.grad) && (!NEED_AUX || aligned16(P.aux)) &&
+    bool tma_ok = !tma_disabled() && aligned16(P.stream) && aligned16(P.grad) && (!NEED_AUX || aligned16(P.aux)) &&
                   (P.D * (long long)sizeof(T)) % 16 == 0 && (P.N2 * (long long)sizeof(T)) % 16 == 0;
     CUtensorMap ms, mg, ma;
     memset(&ms, 0, sizeof(ms));

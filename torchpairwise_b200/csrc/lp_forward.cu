@@ -351,7 +351,7 @@ int launch_forward(FwdParams P, cudaStream_t stream) {
                   "lp forward: a dimension exceeds 2^31-1");
     P.status = device_status_ptr();
 
-    const bool tma_ok = aligned16(P.x1) && aligned16(P.x2) && (P.D * (long long)sizeof(T)) % 16 == 0 && P.D > 0;
+    const bool tma_ok = !tma_disabled() && aligned16(P.x1) && aligned16(P.x2) && (P.D * (long long)sizeof(T)) % 16 == 0 && P.D > 0;
     CUtensorMap m1, m2;
     memset(&m1, 0, sizeof(m1));
     memset(&m2, 0, sizeof(m2));

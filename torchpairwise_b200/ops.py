@@ -1,0 +1,814 @@
+"""Host side of the pairwise path: the reference's operator surface on top of the C ABI.
+
+Names, argument meaning, defaults and error behaviour follow inspiros/torchpairwise v0.3.0
+(OPS = torchpairwise/csrc/ops): the public metric functions of OPS/pairwise_metrics.cpp, the
+internal ops they are built from (``_ppminkowski``, ``_wminkowski``, ``_directed_hausdorff``,
+``pw*_sum`` / ``pw*_mean``, ``prf_div``) and their hand-derived backward passes.  Every function
+here takes CUDA tensors and launches the sm_100a kernels of ``libtpw_b200.so`` on the current
+stream; nothing falls back to the CPU or to eager PyTorch arithmetic on the [N1, N2] matrix.
+"""
+from __future__ import annotations
+
+import math
+import warnings
+from typing import Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from . import _abi
+from ._abi import check, lib
+
+_FLOAT_CODES = {torch.float32: _abi.F32, torch.float64: _abi.F64}
+
+
+# --------------------------------------------------------------------------------------------
+# helpers
+# --------------------------------------------------------------------------------------------
+def _ptr(t: Optional[Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(t: Tensor):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _require_cuda(*tensors: Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(
+                "torchpairwise_b200 runs on CUDA tensors only (no CPU path); got a tensor on "
+                f"{t.device}"
+            )
+    devs = {t.device for t in tensors if t is not None}
+    if len(devs) > 1:
+        raise RuntimeError(f"Expected all tensors to be on the same device, got {sorted(map(str, devs))}")
+
+
+def _compute_dtype(dtype: torch.dtype) -> torch.dtype:
+    """Half and bfloat16 inputs are computed in float32 and rounded once on the way out."""
+    if dtype in (torch.float16, torch.bfloat16):
+        return torch.float32
+    if dtype in _FLOAT_CODES:
+        return dtype
+    raise RuntimeError(f"expected a floating point tensor, got {dtype}")
+
+
+def check_pairwise_inputs(name: str, x1: Tensor, x2: Optional[Tensor] = None, *, boolean: bool = False,
+                          sets: bool = False) -> Tuple[Tensor, Tensor]:
+    """Rank / feature checks of OPS/pairwise_metrics.h:10-67 (same messages)."""
+    lo = 3 if sets else 2
+    unbatched = x1.dim() == lo
+    if not (unbatched or x1.dim() == lo + 1):
+        raise RuntimeError(f"x1 must be {lo}D tensor (unbatched) or {lo + 1}D tensor (batched)")
+    if x2 is not None:
+        if not (unbatched or x2.dim() == lo + 1):
+            raise RuntimeError(f"x2 must be {lo}D tensor (unbatched) or {lo + 1}D tensor (batched)")
+        fdim = (lo - 1) if unbatched else lo
+        if x2.dim() <= fdim or x1.size(fdim) != x2.size(fdim):
+            got2 = x2.size(fdim) if x2.dim() > fdim else "?"
+            raise RuntimeError(
+                "x1 and x2 must have same number of features. Got: "
+                f"x1.size({fdim})={x1.size(fdim)}, x2.size({fdim})={got2}"
+            )
+    if boolean:
+        if x1.dtype != torch.bool or (x2 is not None and x2.dtype != torch.bool):
+            warnings.warn(f"Data was converted to {torch.bool} for metric {name}")
+        x1b = x1.to(torch.bool)
+        return x1b, (x1b if x2 is None else x2.to(torch.bool))
+    return x1, (x1 if x2 is None else x2)
+
+
+def _batched(x1: Tensor, x2: Tensor, what: str):
+    """contiguous() + leading batch dimension, as every reference kernel wrapper does
+    (e.g. OPS/cuda/ppminkowski_kernel.cu:75-90)."""
+    unbatched = x1.dim() == 2
+    if not (unbatched or x1.dim() == 3):
+        raise RuntimeError("x1 must be 2-D (unbatched) or 3-D (batched) tensor.")
+    if not (x2.dim() == x1.dim()):
+        raise RuntimeError("x2 must be 2-D (unbatched) or 3-D (batched) tensor.")
+    if not unbatched and x1.size(0) != x2.size(0):
+        raise RuntimeError("batch_size of x1 and x2 do not match.")
+    if x1.size(-1) != x2.size(-1):
+        raise RuntimeError("feature dimension of x1 and x2 do not match.")
+    if x1.dtype != x2.dtype:
+        raise RuntimeError(f"Expected tensor for argument #1 'x1' to have the same type as tensor for argument #2 'x2'; "
+                           f"but type {x1.dtype} does not equal {x2.dtype} (while checking arguments for {what})")
+    x1c, x2c = x1.contiguous(), x2.contiguous()
+    if unbatched:
+        x1c, x2c = x1c.unsqueeze(0), x2c.unsqueeze(0)
+    return x1c, x2c, unbatched
+
+
+def _sizes(x1c: Tensor, x2c: Tensor):
+    return x1c.size(0), x1c.size(1), x2c.size(1), x1c.size(2)
+
+
+# --------------------------------------------------------------------------------------------
+# raw launches (no autograd)
+# --------------------------------------------------------------------------------------------
+def _lp_forward_raw(x1c: Tensor, x2c: Tensor, w: Optional[Tensor], p: float, out_exponent: float) -> Tensor:
+    B, N1, N2, D = _sizes(x1c, x2c)
+    out = torch.empty((B, N1, N2), dtype=x1c.dtype, device=x1c.device)
+    if D == 0:
+        return out.zero_()
+    with torch.cuda.device(x1c.device):
+        check(lib.tpw_lp_forward(_FLOAT_CODES[x1c.dtype], _ptr(x1c), _ptr(x2c), _ptr(w), _ptr(out),
+                                 B, N1, N2, D, float(p), float(out_exponent), _stream(x1c)), "tpw_lp_forward")
+    return out
+
+
+def _lp_backward_raw(mode: int, grad: Tensor, aux: Optional[Tensor], x1c: Tensor, x2c: Tensor,
+                     w: Optional[Tensor], p: float, need1: bool = True, need2: bool = True):
+    B, N1, N2, D = _sizes(x1c, x2c)
+    g1 = torch.empty_like(x1c) if need1 else None
+    g2 = torch.empty_like(x2c) if need2 else None
+    with torch.cuda.device(x1c.device):
+        check(lib.tpw_lp_backward(_FLOAT_CODES[x1c.dtype], mode, _ptr(grad), _ptr(aux), _ptr(x1c), _ptr(x2c),
+                                  _ptr(w), _ptr(g1), _ptr(g2), B, N1, N2, D, float(p), _stream(x1c)),
+              "tpw_lp_backward")
+    return g1, g2
+
+
+def _dot_forward_raw(x1c: Tensor, x2c: Tensor, epilogue: int, engine: int = _abi.ENGINE_AUTO) -> Tensor:
+    B, N1, N2, D = _sizes(x1c, x2c)
+    out = torch.empty((B, N1, N2), dtype=x1c.dtype, device=x1c.device)
+    if D == 0:
+        # empty contraction: M = 0, norms = 0
+        return out.fill_(1.0 if epilogue in (_abi.DOT_COSINE_DIST, _abi.DOT_ONE_MINUS_SIM) else 0.0)
+    code = _FLOAT_CODES[x1c.dtype]
+    with torch.cuda.device(x1c.device):
+        nbytes = lib.tpw_dot_metric_scratch_bytes(code, engine, B, N1, N2, D)
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=x1c.device) if nbytes > 0 else None
+        check(lib.tpw_dot_metric_forward_ws(code, epilogue, engine, _ptr(x1c), _ptr(x2c), _ptr(out),
+                                            _ptr(scratch), nbytes, B, N1, N2, D, _stream(x1c)),
+              "tpw_dot_metric_forward_ws")
+    return out
+
+
+def _row_norm(xc: Tensor) -> Tensor:
+    B, N, D = xc.shape
+    out = torch.empty((B, N), dtype=xc.dtype, device=xc.device)
+    with torch.cuda.device(xc.device):
+        check(lib.tpw_row_norm(_FLOAT_CODES[xc.dtype], _ptr(xc), _ptr(out), B * N, D, _stream(xc)), "tpw_row_norm")
+    return out
+
+
+def _row_center(xc: Tensor) -> Tensor:
+    B, N, D = xc.shape
+    out = torch.empty_like(xc)
+    with torch.cuda.device(xc.device):
+        check(lib.tpw_row_center(_FLOAT_CODES[xc.dtype], _ptr(xc), _ptr(out), B * N, D, _stream(xc)), "tpw_row_center")
+    return out
+
+
+# --------------------------------------------------------------------------------------------
+# autograd functions
+# --------------------------------------------------------------------------------------------
+class _CdistFunction(torch.autograd.Function):
+    """at::cdist(x1, x2, p) as called by euclidean / manhattan / minkowski / chebyshev
+    (OPS/pairwise_metrics.cpp:30,48,167,305) with ATen's cdist backward formulas."""
+
+    @staticmethod
+    def forward(ctx, x1: Tensor, x2: Tensor, p: float):
+        in_dtype = x1.dtype
+        cdt = _compute_dtype(in_dtype)
+        x1c, x2c, unbatched = _batched(x1.to(cdt), x2.to(cdt), "cdist")
+        if p == 0:
+            out = _cmp_reduce_raw(x1c, x2c, _abi.CMP_NE, _abi.RED_SUM).to(cdt)
+        elif math.isinf(p):
+            out = _lp_forward_raw(x1c, x2c, None, math.inf, 1.0)
+        else:
+            out = _lp_forward_raw(x1c, x2c, None, p, 1.0 / p)
+        ctx.save_for_backward(x1c, x2c, out)
+        ctx.p, ctx.unbatched, ctx.in_dtype = p, unbatched, in_dtype
+        res = out.squeeze(0) if unbatched else out
+        return res.to(in_dtype)
+
+    @staticmethod
+    def backward(ctx, grad):
+        x1c, x2c, out = ctx.saved_tensors
+        need1, need2 = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        if ctx.p == 0:
+            g1 = torch.zeros_like(x1c) if need1 else None
+            g2 = torch.zeros_like(x2c) if need2 else None
+        else:
+            g = grad.to(x1c.dtype).contiguous()
+            if ctx.unbatched:
+                g = g.unsqueeze(0)
+            g1, g2 = _lp_backward_raw(_abi.LP_BWD_CDIST, g, out, x1c, x2c, None, ctx.p, need1, need2)
+        if ctx.unbatched:
+            g1 = None if g1 is None else g1.squeeze(0)
+            g2 = None if g2 is None else g2.squeeze(0)
+        g1 = None if g1 is None else g1.to(ctx.in_dtype)
+        g2 = None if g2 is None else g2.to(ctx.in_dtype)
+        return g1, g2, None
+
+
+class _PPMinkowskiFunction(torch.autograd.Function):
+    """PPowerMinkowskiFunction of OPS/autograd/ppminkowski_kernel.cpp:9-46."""
+
+    @staticmethod
+    def forward(ctx, x1: Tensor, x2: Tensor, p: float):
+        in_dtype = x1.dtype
+        cdt = _compute_dtype(in_dtype)
+        x1c, x2c, unbatched = _batched(x1.to(cdt), x2.to(cdt), "_ppminkowski_forward")
+        if p == 0:
+            B, N1, N2, D = _sizes(x1c, x2c)
+            out = torch.full((B, N1, N2), float(D), dtype=cdt, device=x1c.device)
+        else:
+            out = _lp_forward_raw(x1c, x2c, None, p, 1.0)
+        ctx.save_for_backward(x1c, x2c)
+        ctx.p, ctx.unbatched, ctx.in_dtype = p, unbatched, in_dtype
+        res = out.squeeze(0) if unbatched else out
+        return res.to(in_dtype)
+
+    @staticmethod
+    def backward(ctx, grad):
+        x1c, x2c = ctx.saved_tensors
+        g1, g2 = _ppminkowski_backward_raw(grad, x1c, x2c, ctx.p, ctx.unbatched,
+                                           ctx.needs_input_grad[0], ctx.needs_input_grad[1])
+        g1 = None if g1 is None else g1.to(ctx.in_dtype)
+        g2 = None if g2 is None else g2.to(ctx.in_dtype)
+        return g1, g2, None
+
+
+def _ppminkowski_backward_raw(grad, x1c, x2c, p, unbatched, need1=True, need2=True):
+    g = grad.to(x1c.dtype).contiguous()
+    if unbatched:
+        g = g.unsqueeze(0)
+    B, N1, N2, D = _sizes(x1c, x2c)
+    if p == 0:
+        g1 = torch.zeros_like(x1c) if need1 else None
+        g2 = torch.zeros_like(x2c) if need2 else None
+    elif math.isinf(p):
+        g1 = torch.zeros_like(x1c)
+        g2 = torch.zeros_like(x2c)
+        with torch.cuda.device(x1c.device):
+            check(lib.tpw_lp_inf_backward(_FLOAT_CODES[x1c.dtype], _ptr(g), _ptr(x1c), _ptr(x2c), None,
+                                          _ptr(g1), _ptr(g2), None, B, N1, N2, D, int(p < 0), _stream(x1c)),
+                  "tpw_lp_inf_backward")
+    else:
+        g1, g2 = _lp_backward_raw(_abi.LP_BWD_PPMINKOWSKI, g, None, x1c, x2c, None, p, need1, need2)
+    if unbatched:
+        g1 = None if g1 is None else g1.squeeze(0)
+        g2 = None if g2 is None else g2.squeeze(0)
+    return g1, g2
+
+
+class _WMinkowskiFunction(torch.autograd.Function):
+    """WeightedMinkowskiFunction of OPS/autograd/wminkowski_kernel.cpp:9-50."""
+
+    @staticmethod
+    def forward(ctx, x1: Tensor, x2: Tensor, w: Tensor, p: float):
+        in_dtype = x1.dtype
+        cdt = _compute_dtype(in_dtype)
+        if not (x1.dtype == x2.dtype == w.dtype):
+            raise RuntimeError("Expected x1, x2 and w to have the same type (while checking arguments for _wminkowski_forward)")
+        x1c, x2c, unbatched = _batched(x1.to(cdt), x2.to(cdt), "_wminkowski_forward")
+        if not (unbatched or w.dim() == 2):
+            raise RuntimeError("w must be 1-D (unbatched) or 2-D (batched) tensor.")
+        if unbatched and w.dim() != 1:
+            raise RuntimeError("w must be 1-D (unbatched) or 2-D (batched) tensor.")
+        wc = w.to(cdt).contiguous()
+        if unbatched:
+            wc = wc.unsqueeze(0)
+        B, N1, N2, D = _sizes(x1c, x2c)
+        if wc.size(0) != B:
+            raise RuntimeError("batch_size of x1, x2, and w do not match.")
+        # The reference compares w.size(1) with N1 in the batched case (OPS/cuda/wminkowski_kernel.cu:91),
+        # which rejects every valid weight vector unless N1 == D; the feature count is what is meant.
+        if wc.size(1) != D:
+            raise RuntimeError("feature dimension of x1, x2, and w do not match.")
+        if p == 0:
+            out = torch.full((B, N1, N2), float(D), dtype=cdt, device=x1c.device)
+        elif math.isinf(p):
+            out = _lp_forward_raw(x1c, x2c, wc, p, 1.0)
+        else:
+            out = _lp_forward_raw(x1c, x2c, wc, p, 1.0 / p)
+        ctx.save_for_backward(x1c, x2c, wc)
+        ctx.p, ctx.unbatched, ctx.in_dtype = p, unbatched, in_dtype
+        res = out.squeeze(0) if unbatched else out
+        return res.to(in_dtype)
+
+    @staticmethod
+    def backward(ctx, grad):
+        x1c, x2c, wc = ctx.saved_tensors
+        g1, g2, gw = _wminkowski_backward_raw(grad, x1c, x2c, wc, ctx.p, ctx.unbatched)
+        return g1.to(ctx.in_dtype), g2.to(ctx.in_dtype), gw.to(ctx.in_dtype), None
+
+
+def _wminkowski_backward_raw(grad, x1c, x2c, wc, p, unbatched):
+    g = grad.to(x1c.dtype).contiguous()
+    if unbatched:
+        g = g.unsqueeze(0)
+    B, N1, N2, D = _sizes(x1c, x2c)
+    code = _FLOAT_CODES[x1c.dtype]
+    g1, g2, gw = torch.zeros_like(x1c), torch.zeros_like(x2c), torch.zeros_like(wc)
+    if p != 0 and B * N1 * N2 * D > 0:
+        with torch.cuda.device(x1c.device):
+            if math.isinf(p):
+                check(lib.tpw_lp_inf_backward(code, _ptr(g), _ptr(x1c), _ptr(x2c), _ptr(wc), _ptr(g1), _ptr(g2),
+                                              _ptr(gw), B, N1, N2, D, int(p < 0), _stream(x1c)),
+                      "tpw_lp_inf_backward")
+            else:
+                # coefficient S^(1/p-1): the reference's forward kernel with its `backward` flag
+                # (OPS/cuda/wminkowski_kernel.cu:16-37 called at :300-320)
+                coef = _lp_forward_raw(x1c, x2c, wc, p, 1.0 / p - 1.0)
+                check(lib.tpw_lp_backward(code, _abi.LP_BWD_WMINKOWSKI, _ptr(g), _ptr(coef), _ptr(x1c), _ptr(x2c),
+                                          _ptr(wc), _ptr(g1), _ptr(g2), B, N1, N2, D, float(p), _stream(x1c)),
+                      "tpw_lp_backward")
+                scratch = torch.empty((B, N1, D), dtype=x1c.dtype, device=x1c.device)
+                check(lib.tpw_wminkowski_backward_w(code, _ptr(g), _ptr(coef), _ptr(x1c), _ptr(x2c), _ptr(gw),
+                                                    _ptr(scratch), B, N1, N2, D, float(p), _stream(x1c)),
+                      "tpw_wminkowski_backward_w")
+    if unbatched:
+        g1, g2, gw = g1.squeeze(0), g2.squeeze(0), gw.squeeze(0)
+    return g1, g2, gw
+
+
+class _CosineSimilarityFunction(torch.autograd.Function):
+    """x1.x2^T / (|x1||x2|^T) with prf_div mode "identity" (OPS/pairwise_metrics.cpp:112-122) and
+    the gradient that autograd derives for that composition (norm, outer product, matmul, prf_div:
+    OPS/cuda/prf_div_kernel.cu:315-366).  `epilogue` also folds the 1 - S (+clip) of cosine /
+    correlation distances (:51-56, :203)."""
+
+    @staticmethod
+    def forward(ctx, x1: Tensor, x2: Tensor, epilogue: int):
+        in_dtype = x1.dtype
+        cdt = _compute_dtype(in_dtype)
+        x1c, x2c, unbatched = _batched(x1.to(cdt), x2.to(cdt), "cosine_similarity")
+        out = _dot_forward_raw(x1c, x2c, epilogue)
+        ctx.save_for_backward(x1c, x2c, out)
+        ctx.epilogue, ctx.unbatched, ctx.in_dtype = epilogue, unbatched, in_dtype
+        res = out.squeeze(0) if unbatched else out
+        return res.to(in_dtype)
+
+    @staticmethod
+    def backward(ctx, grad):
+        x1c, x2c, out = ctx.saved_tensors
+        g = grad.to(x1c.dtype).contiguous()
+        if ctx.unbatched:
+            g = g.unsqueeze(0)
+        B, N1, N2, D = _sizes(x1c, x2c)
+        code = _FLOAT_CODES[x1c.dtype]
+        n1, n2 = _row_norm(x1c), _row_norm(x2c)
+        dM = torch.empty_like(g)
+        rowterm = torch.empty((B, N1), dtype=g.dtype, device=g.device)
+        colterm = torch.empty((B, N2), dtype=g.dtype, device=g.device)
+        g1 = torch.empty_like(x1c)
+        g2 = torch.empty_like(x2c)
+        with torch.cuda.device(x1c.device):
+            check(lib.tpw_cosine_backward_prepare(code, ctx.epilogue, _ptr(g), _ptr(out), _ptr(n1), _ptr(n2),
+                                                  _ptr(dM), _ptr(rowterm), _ptr(colterm), B, N1, N2, _stream(x1c)),
+                  "tpw_cosine_backward_prepare")
+            check(lib.tpw_lp_backward(code, _abi.LP_BWD_MATMUL, _ptr(dM), None, _ptr(x1c), _ptr(x2c), None,
+                                      _ptr(g1), _ptr(g2), B, N1, N2, D, 2.0, _stream(x1c)), "tpw_lp_backward")
+            check(lib.tpw_cosine_backward_finish(code, _ptr(g1), _ptr(x1c), _ptr(n1), _ptr(rowterm), B * N1, D, _stream(x1c)),
+                  "tpw_cosine_backward_finish")
+            check(lib.tpw_cosine_backward_finish(code, _ptr(g2), _ptr(x2c), _ptr(n2), _ptr(colterm), B * N2, D, _stream(x1c)),
+                  "tpw_cosine_backward_finish")
+        if ctx.unbatched:
+            g1, g2 = g1.squeeze(0), g2.squeeze(0)
+        return g1.to(ctx.in_dtype), g2.to(ctx.in_dtype), None
+
+
+class _RowCenterFunction(torch.autograd.Function):
+    """x - x.mean(-1, keepdim=True) (OPS/pairwise_metrics.cpp:197-198)."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor):
+        cdt = _compute_dtype(x.dtype)
+        xc = x.to(cdt).contiguous()
+        shape = xc.shape
+        out = _row_center(xc.reshape(1, -1, shape[-1])).reshape(shape)
+        ctx.in_dtype = x.dtype
+        return out.to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, grad):
+        cdt = _compute_dtype(grad.dtype)
+        gc = grad.to(cdt).contiguous()
+        shape = gc.shape
+        return _row_center(gc.reshape(1, -1, shape[-1])).reshape(shape).to(ctx.in_dtype)
+
+
+class _HausdorffFunction(torch.autograd.Function):
+    """DirectedHausdorffDistancesFunction of OPS/autograd/hausdorff_kernel.cpp:9-61.  The
+    reference re-runs the forward inside backward with a cloned generator; here the forward
+    results are saved instead, which is the same thing without the second pass."""
+
+    @staticmethod
+    def forward(ctx, x1: Tensor, x2: Tensor, shuffle: bool, generator):
+        if x1.dtype != x2.dtype:
+            raise RuntimeError("Expected x1 and x2 to have the same type (while checking arguments for _directed_hausdorff_forward)")
+        in_dtype = x1.dtype
+        cdt = _compute_dtype(in_dtype)
+        unbatched = x1.dim() == 3
+        if not (unbatched or x1.dim() == 4):
+            raise RuntimeError("x1 must be 3-D (unbatched) or 4-D (batched) tensor.")
+        if x2.dim() != x1.dim():
+            raise RuntimeError("x2 must be 3-D (unbatched) or 4-D (batched) tensor.")
+        if not unbatched and x1.size(0) != x2.size(0):
+            raise RuntimeError("batch_size of x1 and x2 do not match.")
+        if x1.size(-1) != x2.size(-1):
+            raise RuntimeError("feature dimension of x1 and x2 do not match.")
+        x1c, x2c = x1.to(cdt).contiguous(), x2.to(cdt).contiguous()
+        if unbatched:
+            x1c, x2c = x1c.unsqueeze(0), x2c.unsqueeze(0)
+        B, N1, M1, D = x1c.shape
+        N2, M2 = x2c.size(1), x2c.size(2)
+        dev = x1c.device
+        out = torch.empty((B, N1, N2), dtype=cdt, device=dev)
+        idx1 = torch.empty((B, N1, N2), dtype=torch.int64, device=dev)
+        idx2 = torch.empty((B, N1, N2), dtype=torch.int64, device=dev)
+        order1 = order2 = None
+        if shuffle and B > 0:
+            # per batch, x1's permutation then x2's, as OPS/cuda/hausdorff_kernel.cu:158-167 draws them
+            order1 = torch.empty((B, M1), dtype=torch.int64, device=dev)
+            order2 = torch.empty((B, M2), dtype=torch.int64, device=dev)
+            for b in range(B):
+                p1 = torch.randperm(M1, generator=generator, device=dev)
+                p2 = torch.randperm(M2, generator=generator, device=dev)
+                order1[b, p1] = torch.arange(M1, device=dev)
+                order2[b, p2] = torch.arange(M2, device=dev)
+        with torch.cuda.device(dev):
+            nbytes = lib.tpw_hausdorff_scratch_bytes(B, N1, N2, M1)
+            scratch = torch.empty(max(nbytes, 8), dtype=torch.uint8, device=dev)
+            check(lib.tpw_hausdorff_forward(_FLOAT_CODES[cdt], _ptr(x1c), _ptr(x2c), _ptr(order1), _ptr(order2),
+                                            _ptr(out), _ptr(idx1), _ptr(idx2), _ptr(scratch),
+                                            B, N1, N2, M1, M2, D, _stream(x1c)), "tpw_hausdorff_forward")
+        ctx.save_for_backward(x1c, x2c, out, idx1, idx2)
+        ctx.unbatched, ctx.in_dtype = unbatched, in_dtype
+        if unbatched:
+            out, idx1, idx2 = out.squeeze(0), idx1.squeeze(0), idx2.squeeze(0)
+        out = out.to(in_dtype)
+        ctx.mark_non_differentiable(idx1, idx2)
+        return out, idx1, idx2
+
+    @staticmethod
+    def backward(ctx, grad, _g1, _g2):
+        x1c, x2c, out, idx1, idx2 = ctx.saved_tensors
+        g = grad.to(x1c.dtype).contiguous()
+        if ctx.unbatched:
+            g = g.unsqueeze(0)
+        B, N1, M1, D = x1c.shape
+        N2, M2 = x2c.size(1), x2c.size(2)
+        g1, g2 = torch.empty_like(x1c), torch.empty_like(x2c)
+        with torch.cuda.device(x1c.device):
+            check(lib.tpw_hausdorff_backward(_FLOAT_CODES[x1c.dtype], _ptr(g), _ptr(out), _ptr(idx1), _ptr(idx2),
+                                             _ptr(x1c), _ptr(x2c), _ptr(g1), _ptr(g2),
+                                             B, N1, N2, M1, M2, D, _stream(x1c)), "tpw_hausdorff_backward")
+        if ctx.unbatched:
+            g1, g2 = g1.squeeze(0), g2.squeeze(0)
+        return g1.to(ctx.in_dtype), g2.to(ctx.in_dtype), None, None
+
+
+class _PRFDivFunction(torch.autograd.Function):
+    """PRFDivideFunction of OPS/autograd/prf_div_kernel.cpp:9-52 (same-shape operands)."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, y: Tensor, mode: int):
+        if x.shape != y.shape:
+            raise RuntimeError("self and other must have the same shape.")
+        dt = torch.result_type(x, y)
+        if not dt.is_floating_point:
+            dt = torch.float32
+        cdt = _compute_dtype(dt)
+        xc, yc = x.to(cdt).contiguous(), y.to(cdt).contiguous()
+        out = torch.empty_like(xc)
+        with torch.cuda.device(xc.device):
+            check(lib.tpw_prf_div_forward(_FLOAT_CODES[cdt], mode, _ptr(xc), _ptr(yc), _ptr(out), xc.numel(), _stream(xc)),
+                  "tpw_prf_div_forward")
+        ctx.save_for_backward(xc, yc)
+        ctx.mode, ctx.dtypes = mode, (x.dtype, y.dtype)
+        return out.to(dt)
+
+    @staticmethod
+    def backward(ctx, grad):
+        xc, yc = ctx.saved_tensors
+        g = grad.to(xc.dtype).contiguous()
+        gx = torch.empty_like(xc) if ctx.needs_input_grad[0] else None
+        gy = torch.empty_like(yc) if ctx.needs_input_grad[1] else None
+        with torch.cuda.device(xc.device):
+            check(lib.tpw_prf_div_backward(_FLOAT_CODES[xc.dtype], ctx.mode, _ptr(g), _ptr(xc), _ptr(yc),
+                                           _ptr(gx), _ptr(gy), xc.numel(), _stream(xc)), "tpw_prf_div_backward")
+        gx = None if gx is None else gx.to(ctx.dtypes[0])
+        gy = None if gy is None else gy.to(ctx.dtypes[1])
+        return gx, gy, None
+
+
+# --------------------------------------------------------------------------------------------
+# boolean / compare-reduce
+# --------------------------------------------------------------------------------------------
+def _pack_bool(xb: Tensor):
+    """[B, N, D] bool -> (words [B, N, W] int32 view of uint32, popcounts [B, N] int32, W)."""
+    B, N, D = xb.shape
+    W = max(4, (D + 31) // 32)
+    W = (W + 3) // 4 * 4  # 16-byte rows for the TMA path
+    words = torch.empty((B, N, W), dtype=torch.int32, device=xb.device)
+    pops = torch.empty((B, N), dtype=torch.int32, device=xb.device)
+    src = xb.contiguous().view(torch.uint8)
+    with torch.cuda.device(xb.device):
+        check(lib.tpw_bitpack(_ptr(src), _ptr(words), _ptr(pops), B * N, D, W, _stream(xb)), "tpw_bitpack")
+    return words, pops, W
+
+
+def _bool_metric_raw(x1: Tensor, x2: Tensor, metric: str) -> Tensor:
+    """x1, x2 boolean, 2-D or 3-D; float32 result."""
+    _require_cuda(x1, x2)
+    unbatched = x1.dim() == 2
+    if not (unbatched or x1.dim() == 3):
+        raise RuntimeError("x1 must be 2-D (unbatched) or 3-D (batched) tensor.")
+    if x2.dim() != x1.dim():
+        raise RuntimeError("x2 must be 2-D (unbatched) or 3-D (batched) tensor.")
+    if not unbatched and x1.size(0) != x2.size(0):
+        raise RuntimeError("batch_size of x1 and x2 do not match.")
+    if x1.size(-1) != x2.size(-1):
+        raise RuntimeError("feature dimension of x1 and x2 do not match.")
+    x1c, x2c = (x1.unsqueeze(0), x2.unsqueeze(0)) if unbatched else (x1, x2)
+    B, N1, D = x1c.shape
+    N2 = x2c.size(1)
+    out = torch.empty((B, N1, N2), dtype=torch.float32, device=x1.device)
+    if D == 0:
+        out.zero_()
+        if metric in ("eq_mean", "ne_mean", "kulczynski1", "russellrao", "kulsinski", "dice",
+                      "rogerstanimoto", "sokalmichener", "sokalsneath"):
+            out.fill_(float("nan"))
+    elif out.numel() > 0:
+        w1, p1, W = _pack_bool(x1c)
+        if x2c is x1c or (x2c.data_ptr() == x1c.data_ptr() and x2c.shape == x1c.shape):
+            w2, p2 = w1, p1
+        else:
+            w2, p2, _ = _pack_bool(x2c)
+        with torch.cuda.device(x1.device):
+            check(lib.tpw_bool_metric_forward(_abi.BOOL_METRICS[metric], _ptr(w1), _ptr(w2), _ptr(p1), _ptr(p2),
+                                              _ptr(out), B, N1, N2, D, W, _stream(x1)), "tpw_bool_metric_forward")
+    return out.squeeze(0) if unbatched else out
+
+
+_CMP_CODES = {torch.float32: _abi.F32, torch.float64: _abi.F64, torch.int32: _abi.I32, torch.int64: _abi.I64}
+
+
+def _cmp_reduce_raw(x1c: Tensor, x2c: Tensor, op: int, reduction: int) -> Tensor:
+    """x1c, x2c batched, same dtype among float32/float64/int32/int64; float32 result."""
+    B, N1, N2, D = _sizes(x1c, x2c)
+    out = torch.empty((B, N1, N2), dtype=torch.float32, device=x1c.device)
+    if D == 0:
+        return out.fill_(float("nan") if reduction == _abi.RED_MEAN else 0.0)
+    with torch.cuda.device(x1c.device):
+        check(lib.tpw_cmp_reduce_forward(_CMP_CODES[x1c.dtype], op, reduction, _ptr(x1c), _ptr(x2c), _ptr(out),
+                                         B, N1, N2, D, _stream(x1c)), "tpw_cmp_reduce_forward")
+    return out
+
+
+def _pairwise_compare(x1: Tensor, x2: Tensor, op: int, reduction: int) -> Tensor:
+    """pw{eq,ne}_{sum,mean}: any dtype, promoted with result_type, float32 output
+    (OPS/cuda/pairwise_binary_kernels.cu:144-220)."""
+    _require_cuda(x1, x2)
+    common = torch.result_type(x1, x2)
+    if common == torch.bool:
+        name = ("eq" if op == _abi.CMP_EQ else "ne") + ("_mean" if reduction == _abi.RED_MEAN else "_sum")
+        return _bool_metric_raw(x1.to(torch.bool), x2.to(torch.bool), name)
+    if common in (torch.float16, torch.bfloat16):
+        common = torch.float32  # exact widening keeps every comparison
+    elif common in (torch.uint8, torch.int8, torch.int16):
+        common = torch.int32
+    if common not in _CMP_CODES:
+        raise RuntimeError(f"pairwise comparison is not implemented for {common}")
+    x1c, x2c, unbatched = _batched(x1.to(common), x2.to(common), "pairwise_binary_reduction_forward")
+    out = _cmp_reduce_raw(x1c, x2c, op, reduction)
+    return out.squeeze(0) if unbatched else out
+
+
+def _require_bool(x1: Tensor, x2: Tensor, name: str):
+    if torch.result_type(x1, x2) != torch.bool:
+        raise RuntimeError(f'"{name}" not implemented for \'{torch.result_type(x1, x2)}\'')
+
+
+def pwand_sum(x1: Tensor, x2: Tensor) -> Tensor:
+    _require_bool(x1, x2, "pairwise_binary_reduction_forward")
+    return _bool_metric_raw(x1, x2, "and_sum")
+
+
+def pwor_sum(x1: Tensor, x2: Tensor) -> Tensor:
+    _require_bool(x1, x2, "pairwise_binary_reduction_forward")
+    return _bool_metric_raw(x1, x2, "or_sum")
+
+
+def pwxor_sum(x1: Tensor, x2: Tensor) -> Tensor:
+    _require_bool(x1, x2, "pairwise_binary_reduction_forward")
+    return _bool_metric_raw(x1, x2, "xor_sum")
+
+
+def pweq_sum(x1: Tensor, x2: Tensor) -> Tensor:
+    return _pairwise_compare(x1, x2, _abi.CMP_EQ, _abi.RED_SUM)
+
+
+def pwne_sum(x1: Tensor, x2: Tensor) -> Tensor:
+    return _pairwise_compare(x1, x2, _abi.CMP_NE, _abi.RED_SUM)
+
+
+def pweq_mean(x1: Tensor, x2: Tensor) -> Tensor:
+    return _pairwise_compare(x1, x2, _abi.CMP_EQ, _abi.RED_MEAN)
+
+
+def pwne_mean(x1: Tensor, x2: Tensor) -> Tensor:
+    return _pairwise_compare(x1, x2, _abi.CMP_NE, _abi.RED_MEAN)
+
+
+# --------------------------------------------------------------------------------------------
+# internal ops of the reference (same names)
+# --------------------------------------------------------------------------------------------
+def _ppminkowski(x1: Tensor, x2: Tensor, p: float = 2.0) -> Tensor:
+    """sum_k |x1 - x2|^p without the root (OPS/ppminkowski.cpp:31-38)."""
+    _require_cuda(x1, x2)
+    return _PPMinkowskiFunction.apply(x1, x2, float(p))
+
+
+def _wminkowski(x1: Tensor, x2: Tensor, w: Tensor, p: float = 2.0) -> Tensor:
+    """(sum_k w_k |x1 - x2|^p)^(1/p) (OPS/wminkowski.cpp:33-40)."""
+    _require_cuda(x1, x2, w)
+    return _WMinkowskiFunction.apply(x1, x2, w, float(p))
+
+
+def _directed_hausdorff(x1: Tensor, x2: Tensor, *, shuffle: bool = False, generator=None):
+    _require_cuda(x1, x2)
+    return _HausdorffFunction.apply(x1, x2, bool(shuffle), generator)
+
+
+def prf_div(x: Tensor, y: Tensor, mode: str = "zero") -> Tensor:
+    """y != 0 ? x / y : (0 | x) (OPS/prf_div.cpp:359-400, tensor/tensor overload)."""
+    if mode not in ("zero", "identity"):
+        raise RuntimeError(f"mode must be either zero or identity. Got {mode}")
+    _require_cuda(x, y)
+    return _PRFDivFunction.apply(x, y, _abi.PRF_IDENTITY if mode == "identity" else _abi.PRF_ZERO)
+
+
+def _cdist_p(x1: Tensor, x2: Tensor, p: float) -> Tensor:
+    _require_cuda(x1, x2)
+    if p < 0:
+        raise RuntimeError("cdist only supports non-negative p values")
+    if x1.dim() == 3 and x2.dim() == 3 and x1.size(0) != x2.size(0):
+        raise RuntimeError("batch_size of x1 and x2 do not match.")
+    return _CdistFunction.apply(x1, x2, float(p))
+
+
+# --------------------------------------------------------------------------------------------
+# public metrics (OPS/pairwise_metrics.cpp)
+# --------------------------------------------------------------------------------------------
+def euclidean_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    x1_, x2_ = check_pairwise_inputs("euclidean_distances", x1, x2)
+    return _cdist_p(x1_, x2_, 2.0)
+
+
+def manhattan_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    x1_, x2_ = check_pairwise_inputs("manhattan_distances", x1, x2)
+    return _cdist_p(x1_, x2_, 1.0)
+
+
+def chebyshev_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    x1_, x2_ = check_pairwise_inputs("chebyshev_distances", x1, x2)
+    return _cdist_p(x1_, x2_, math.inf)
+
+
+def minkowski_distances(x1: Tensor, x2: Optional[Tensor] = None, p: float = 2.0) -> Tensor:
+    x1_, x2_ = check_pairwise_inputs("minkowski_distances", x1, x2)
+    return _cdist_p(x1_, x2_, float(p))
+
+
+def wminkowski_distances(x1: Tensor, x2: Optional[Tensor] = None, p: float = 2.0, w: Optional[Tensor] = None) -> Tensor:
+    x1_, x2_ = check_pairwise_inputs("wminkowski_distances", x1, x2)
+    if w is None:
+        return _cdist_p(x1_, x2_, float(p))
+    return _wminkowski(x1_, x2_, w, p)
+
+
+def sqeuclidean_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    x1_, x2_ = check_pairwise_inputs("sqeuclidean_distances", x1, x2)
+    return _ppminkowski(x1_, x2_, 2.0)
+
+
+def cosine_similarity(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    x1_, x2_ = check_pairwise_inputs("cosine_similarity", x1, x2)
+    _require_cuda(x1_, x2_)
+    return _CosineSimilarityFunction.apply(x1_, x2_, _abi.DOT_COSINE_SIM)
+
+
+def cosine_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    x1_, x2_ = check_pairwise_inputs("cosine_similarity", x1, x2)
+    _require_cuda(x1_, x2_)
+    return _CosineSimilarityFunction.apply(x1_, x2_, _abi.DOT_COSINE_DIST)
+
+
+def correlation_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    x1_, x2_ = check_pairwise_inputs("correlation_distances", x1, x2)
+    _require_cuda(x1_, x2_)
+    c1 = _RowCenterFunction.apply(x1_)
+    c2 = c1 if x2 is None else _RowCenterFunction.apply(x2_)
+    return _CosineSimilarityFunction.apply(c1, c2, _abi.DOT_ONE_MINUS_SIM)
+
+
+def linear_kernel(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    x1_, x2_ = check_pairwise_inputs("linear_kernel", x1, x2)
+    _require_cuda(x1_, x2_)
+    return _LinearKernelFunction.apply(x1_, x2_)
+
+
+class _LinearKernelFunction(torch.autograd.Function):
+    """x1 @ x2^T (OPS/pairwise_metrics.cpp:58-65)."""
+
+    @staticmethod
+    def forward(ctx, x1, x2):
+        in_dtype = x1.dtype
+        cdt = _compute_dtype(in_dtype)
+        x1c, x2c, unbatched = _batched(x1.to(cdt), x2.to(cdt), "linear_kernel")
+        out = _dot_forward_raw(x1c, x2c, _abi.DOT_LINEAR)
+        ctx.save_for_backward(x1c, x2c)
+        ctx.unbatched, ctx.in_dtype = unbatched, in_dtype
+        return (out.squeeze(0) if unbatched else out).to(in_dtype)
+
+    @staticmethod
+    def backward(ctx, grad):
+        x1c, x2c = ctx.saved_tensors
+        g = grad.to(x1c.dtype).contiguous()
+        if ctx.unbatched:
+            g = g.unsqueeze(0)
+        g1, g2 = _lp_backward_raw(_abi.LP_BWD_MATMUL, g, None, x1c, x2c, None, 2.0)
+        if ctx.unbatched:
+            g1, g2 = g1.squeeze(0), g2.squeeze(0)
+        return g1.to(ctx.in_dtype), g2.to(ctx.in_dtype)
+
+
+def hamming_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    x1_, x2_ = check_pairwise_inputs("hamming_distances", x1, x2)
+    return pwne_mean(x1_, x2_)
+
+
+def _boolean_metric(name: str, metric: str, x1: Tensor, x2: Optional[Tensor]) -> Tensor:
+    x1_, x2_ = check_pairwise_inputs(name, x1, x2, boolean=True)
+    return _bool_metric_raw(x1_, x2_, metric)
+
+
+def jaccard_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    return _boolean_metric("jaccard_distances", "jaccard", x1, x2)
+
+
+def kulsinski_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    warnings.warn("kulsinski_distances is deprecated in SciPy 1.9.0 and might be removed in the future. "
+                  "Please use kulczynski1_distances.", DeprecationWarning)
+    return _boolean_metric("kulsinski_distances", "kulsinski", x1, x2)
+
+
+def kulczynski1_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    return _boolean_metric("kulczynski1_distances", "kulczynski1", x1, x2)
+
+
+def yule_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    return _boolean_metric("yule_distances", "yule", x1, x2)
+
+
+def dice_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    return _boolean_metric("dice_distances", "dice", x1, x2)
+
+
+def rogerstanimoto_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    return _boolean_metric("rogerstanimoto_distances", "rogerstanimoto", x1, x2)
+
+
+def russellrao_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    return _boolean_metric("russellrao_distances", "russellrao", x1, x2)
+
+
+def sokalmichener_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    return _boolean_metric("sokalmichener_distances", "sokalmichener", x1, x2)
+
+
+def sokalsneath_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    return _boolean_metric("sokalsneath_distances", "sokalsneath", x1, x2)
+
+
+def directed_hausdorff_distances(x1: Tensor, x2: Optional[Tensor] = None, *, shuffle: bool = False, generator=None):
+    x1_, x2_ = check_pairwise_inputs("directed_hausdorff_distances", x1, x2, sets=True)
+    return _directed_hausdorff(x1_, x2_, shuffle=shuffle, generator=generator)
+
+
+# aliases (OPS/pairwise_metrics.cpp:265-270, 411-438)
+def cityblock_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    return manhattan_distances(x1, x2)
+
+
+def l1_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    return manhattan_distances(x1, x2)
+
+
+def l2_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    return euclidean_distances(x1, x2)
+
+
+def lp_distances(x1: Tensor, x2: Optional[Tensor] = None, p: float = 2.0) -> Tensor:
+    return minkowski_distances(x1, x2, p)
+
+
+def linf_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    return chebyshev_distances(x1, x2)

@@ -211,6 +211,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     value = world * args.steps * PAIRS_PER_STEP / (ms * 1e-3) / 1e9
+    if args.profile:
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "not_a_bench_value": value, "batches": B, "ms_per_step": ms / args.steps}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- end to end: host buffers in, gradients out, every step ---------------------------------
     g1h = torch.empty(B, N1, D).pin_memory()
@@ -330,7 +336,16 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batches", type=int, default=B,
+                    help="batches per GPU (default 16 = the benchmark workload; smaller only for profiler captures)")
+    ap.add_argument("--profile", action="store_true",
+                    help="run only the warm-up and timed steps (for ncu captures); prints a reduced line that is not a bench value")
     args = ap.parse_args()
+    global B, PAIRS_PER_STEP, BWD_BYTES_PER_LAUNCH
+    if args.batches != B:
+        B = args.batches
+        PAIRS_PER_STEP = B * N1 * N2
+        BWD_BYTES_PER_LAUNCH = 4 * (2 * B * N1 * N2 + 3 * B * N1 * D)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

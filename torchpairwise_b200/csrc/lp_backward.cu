@@ -456,8 +456,16 @@ extern "C" int tpw_lp_backward(int dtype, int mode, const void *grad, const void
     TPW_CHECK_ARG(dtype == TPW_F32 || dtype == TPW_F64, "tpw_lp_backward: dtype must be TPW_F32 or TPW_F64");
     TPW_CHECK_ARG(B >= 0 && N1 >= 0 && N2 >= 0 && D >= 0, "tpw_lp_backward: negative size");
     if (B == 0 || D == 0 || (N1 == 0 && N2 == 0)) return TPW_OK;
+    if (N1 == 0 || N2 == 0) {
+        // empty sums: the gradient of the non-empty side is all zero (its inputs may be NULL)
+        cudaStream_t s0 = static_cast<cudaStream_t>(stream);
+        const size_t es0 = dtype == TPW_F32 ? 4 : 8;
+        if (grad_x1 && N1 > 0) TPW_CUDA_OK(cudaMemsetAsync(grad_x1, 0, (size_t)(B * N1 * D) * es0, s0));
+        if (grad_x2 && N2 > 0) TPW_CUDA_OK(cudaMemsetAsync(grad_x2, 0, (size_t)(B * N2 * D) * es0, s0));
+        return TPW_OK;
+    }
     TPW_CHECK_ARG(x1 && x2, "tpw_lp_backward: NULL input");
-    TPW_CHECK_ARG(grad != nullptr || N1 == 0 || N2 == 0, "tpw_lp_backward: grad is NULL");
+    TPW_CHECK_ARG(grad != nullptr, "tpw_lp_backward: grad is NULL");
     TPW_CHECK_ARG(!isnan(p), "tpw_lp_backward: p is NaN");
     if (mode != TPW_LP_BWD_MATMUL) {
         TPW_CHECK_ARG(p > 0, "tpw_lp_backward: p must be positive (got %g)", p);
@@ -472,13 +480,6 @@ extern "C" int tpw_lp_backward(int dtype, int mode, const void *grad, const void
     P.grad = grad; P.aux = aux; P.w = w;
     P.B = B; P.N1 = N1; P.N2 = N2; P.D = D;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (N1 == 0 || N2 == 0) {
-        // empty sums: gradients are all zero
-        const size_t es = dtype == TPW_F32 ? 4 : 8;
-        if (grad_x1 && N1 > 0) TPW_CUDA_OK(cudaMemsetAsync(grad_x1, 0, (size_t)(B * N1 * D) * es, s));
-        if (grad_x2 && N2 > 0) TPW_CUDA_OK(cudaMemsetAsync(grad_x2, 0, (size_t)(B * N2 * D) * es, s));
-        return TPW_OK;
-    }
     return dtype == TPW_F32 ? lp_backward_typed<float>(mode, P, x1, x2, grad_x1, grad_x2, p, s)
                             : lp_backward_typed<double>(mode, P, x1, x2, grad_x1, grad_x2, p, s);
 }

@@ -268,6 +268,31 @@ TPW_API int tpw_hausdorff_backward(int dtype, const void *grad, const void *out,
                            int64_t B, int64_t N1, int64_t N2, int64_t M1, int64_t M2, int64_t D,
                            tpw_stream_t stream);
 
+/*
+ * tpw_hausdorff_forward for callers that cannot hand over scratch memory because they are not
+ * allowed to allocate when the call is made -- a process that gave the whole GPU to its own pool
+ * at start-up, a plug-in host that forbids allocation in its compute callback, a loop that cannot
+ * take the device-wide stall an allocation may cause.  Same inputs, outputs and results as
+ * tpw_hausdorff_forward, no scratch argument: the 8-byte key per set pair lives in a fixed
+ * array inside the library's device image (tpw_hausdorff_static_max_pairs() * 8 bytes = 512 KiB,
+ * held by every GPU that loads the library until the process exits).  The call itself performs
+ * no allocation of any kind.
+ *   - Limit: B*N1*N2 <= tpw_hausdorff_static_max_pairs() (65536); larger problems are refused
+ *     with TPW_ERR_INVALID and a message, nothing is launched.
+ *   - The first call on each device looks up the array's device address (a host-side query, not
+ *     a stream operation); make that first call outside any stream capture.
+ *   - All calls on a device share the one array; the part a call uses is cleared on `stream`
+ *     before its kernels run, but two calls whose kernels may overlap on the GPU (different
+ *     streams, or different host threads) would race on it: keep them on one stream or serialise.
+ * This entry point has no counterpart in the reference (whose wrappers always allocate).
+ */
+TPW_API int64_t tpw_hausdorff_static_max_pairs(void);
+TPW_API int tpw_hausdorff_forward_static(int dtype, const void *x1, const void *x2,
+                                         const int64_t *order1, const int64_t *order2,
+                                         void *out, int64_t *idx1, int64_t *idx2,
+                                         int64_t B, int64_t N1, int64_t N2, int64_t M1, int64_t M2, int64_t D,
+                                         tpw_stream_t stream);
+
 /* ---- element-wise safe divide ---------------------------------------------------------------- */
 
 enum tpw_prf_div_mode { TPW_PRF_ZERO = 0, TPW_PRF_IDENTITY = 1 };

@@ -54,6 +54,8 @@ SIGNATURES = {
     "tpw_hausdorff_scratch_bytes": (_L, [_L, _L, _L, _L]),
     "tpw_hausdorff_forward": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P]),
     "tpw_hausdorff_backward": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P]),
+    "tpw_hausdorff_static_max_pairs": (_L, []),
+    "tpw_hausdorff_forward_static": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P]),
     "tpw_prf_div_forward": (_I, [_I, _I, _P, _P, _P, _L, _P]),
     "tpw_prf_div_backward": (_I, [_I, _I, _P, _P, _P, _P, _P, _L, _P]),
     "tpw_measure_issue_peak": (_I, [_I, POINTER(c_double)]),

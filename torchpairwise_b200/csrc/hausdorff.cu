@@ -360,3 +360,85 @@ extern "C" int tpw_hausdorff_backward(int dtype, const void *grad, const void *o
     TPW_LAUNCH_OK("hausdorff_backward_kernel");
     return TPW_OK;
 }
+
+
+// ---- allocation-free variant ----------------------------------------------------------------------
+// Some hosts of this library are not allowed to obtain device memory at call time: a serving
+// process that hands the whole GPU to its own pool when it starts, a plug-in host that forbids
+// allocation inside its compute callback, or a latency-critical loop that cannot afford the
+// device-wide synchronisation cudaMalloc may imply.  tpw_hausdorff_forward needs 8 bytes of scratch
+// per set pair from such a caller; this variant brings its own instead, in a fixed array that
+// lives in the library's device image (every GPU that loads the library holds it until exit).
+namespace tpw {
+namespace {
+
+constexpr long long kStaticMaxPairs = 65536; // 512 KiB of keys
+
+static __device__ __align__(256) unsigned long long g_hausdorff_static_keys[kStaticMaxPairs];
+
+// `g_hausdorff_static_keys` names a host-side shadow here, not device memory; the device address
+// has to be asked for, once per device, while that device is current.
+int resolve_static_keys(unsigned long long **ptr) {
+    static unsigned long long *cache[64] = {nullptr};
+    int dev = 0;
+    TPW_CUDA_OK(cudaGetDevice(&dev));
+    TPW_CHECK_ARG(dev >= 0 && dev < 64, "tpw_hausdorff_forward_static: device ordinal %d is out of range", dev);
+    if (!cache[dev]) {
+        void *p = nullptr;
+        TPW_CUDA_OK(cudaGetSymbolAddress(&p, g_hausdorff_static_keys));
+        TPW_CHECK_ARG(p != nullptr, "tpw_hausdorff_forward_static: the scratch symbol resolved to NULL");
+        cache[dev] = static_cast<unsigned long long *>(p);
+    }
+    *ptr = cache[dev];
+    return TPW_OK;
+}
+
+} // namespace
+} // namespace tpw
+
+extern "C" int64_t tpw_hausdorff_static_max_pairs(void) { return tpw::kStaticMaxPairs; }
+
+extern "C" int tpw_hausdorff_forward_static(int dtype, const void *x1, const void *x2,
+                                            const int64_t *order1, const int64_t *order2,
+                                            void *out, int64_t *idx1, int64_t *idx2,
+                                            int64_t B, int64_t N1, int64_t N2, int64_t M1, int64_t M2, int64_t D,
+                                            tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(dtype == TPW_F32 || dtype == TPW_F64, "tpw_hausdorff_forward_static: dtype must be TPW_F32 or TPW_F64");
+    TPW_CHECK_ARG(B >= 0 && N1 >= 0 && N2 >= 0 && M1 >= 0 && M2 >= 0 && D >= 0, "tpw_hausdorff_forward_static: negative size");
+    const long long pairs = B * N1 * N2;
+    if (pairs == 0) return TPW_OK;
+    TPW_CHECK_ARG(pairs <= kStaticMaxPairs,
+                  "tpw_hausdorff_forward_static: %lld set pairs exceed the built-in scratch of %lld; "
+                  "use tpw_hausdorff_forward with caller-provided scratch", pairs, kStaticMaxPairs);
+    TPW_CHECK_ARG(M1 > 0 && M2 > 0 && D > 0, "tpw_hausdorff_forward_static: empty point sets (M1=%lld, M2=%lld, D=%lld)",
+                  (long long)M1, (long long)M2, (long long)D);
+    TPW_CHECK_ARG(M1 < (1ll << 32) && M2 < (1ll << 32), "tpw_hausdorff_forward_static: more than 2^32 points per set");
+    TPW_CHECK_ARG(x1 && x2 && out && idx1 && idx2, "tpw_hausdorff_forward_static: NULL pointer");
+    HdParams P;
+    memset(&P, 0, sizeof(P));
+    P.x1 = x1; P.x2 = x2;
+    P.order1 = reinterpret_cast<const long long *>(order1);
+    P.order2 = reinterpret_cast<const long long *>(order2);
+    P.out = out;
+    P.idx1 = reinterpret_cast<long long *>(idx1);
+    P.idx2 = reinterpret_cast<long long *>(idx2);
+    P.B = B; P.N1 = N1; P.N2 = N2; P.M1 = M1; P.M2 = M2; P.D = D;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == TPW_F32 && D <= 4) {
+        int st = resolve_static_keys(&P.keys);
+        if (st != TPW_OK) return st;
+        // launch_fast clears the first `pairs` keys on the stream before the kernels use them
+        switch (D) {
+            case 1: return launch_fast<1>(P, s);
+            case 2: return launch_fast<2>(P, s);
+            case 3: return launch_fast<3>(P, s);
+            default: return launch_fast<4>(P, s);
+        }
+    }
+    // the one-CTA-per-pair kernel keeps its state in shared memory and needs no scratch at all
+    if (dtype == TPW_F32) hausdorff_plain_kernel<float><<<(unsigned)pairs, kThreads, 0, s>>>(P);
+    else hausdorff_plain_kernel<double><<<(unsigned)pairs, kThreads, 0, s>>>(P);
+    TPW_LAUNCH_OK("hausdorff_plain_kernel");
+    return TPW_OK;
+}

@@ -331,6 +331,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
 
 def main():
+    global B, PAIRS_PER_STEP, BWD_BYTES_PER_LAUNCH
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
@@ -341,7 +342,6 @@ def main():
     ap.add_argument("--profile", action="store_true",
                     help="run only the warm-up and timed steps (for ncu captures); prints a reduced line that is not a bench value")
     args = ap.parse_args()
-    global B, PAIRS_PER_STEP, BWD_BYTES_PER_LAUNCH
     if args.batches != B:
         B = args.batches
         PAIRS_PER_STEP = B * N1 * N2

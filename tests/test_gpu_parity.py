@@ -357,3 +357,74 @@ def test_full_size_identities(tpw):
     perm = torch.randperm(8192, generator=g).cuda()
     out2, _, _ = tpw.directed_hausdorff_distances(x1[:, :, perm], x2[:, :, perm.flip(0)])
     assert torch.equal(out, out2)
+
+
+@pytest.fixture
+def tensor_engine(tpw):
+    tpw.set_dot_engine("tcgen05")
+    yield tpw
+    tpw.set_dot_engine("auto")
+
+
+@pytest.mark.parametrize("shape", [(1, 128, 256, 64), (2, 300, 520, 200), (1, 1, 1, 8), (1, 130, 257, 70), (3, 77, 40, 513)])
+def test_tensor_core_engine_vs_oracle(tensor_engine, shape):
+    """The bf16x3 tcgen05 kernel against the float64 oracle, at the float32 parity tolerance."""
+    tpw = tensor_engine
+    B, n1, n2, d = shape
+    g = torch.Generator().manual_seed(sum(shape))
+    x1 = torch.randn(B, n1, d, generator=g)
+    x2 = torch.randn(B, n2, d, generator=g)
+    a, b = x1.cuda(), x2.cuda()
+    x1d, x2d = x1.double().numpy(), x2.double().numpy()
+    tol = TOL[torch.float32]
+    close(tpw.sqeuclidean_distances(a, b), O.sqeuclidean(x1d, x2d).astype(np.float32), tol, msg="sqeuclidean")
+    close(tpw.euclidean_distances(a, b), O.cdist(x1d, x2d, 2.0).astype(np.float32), tol, msg="euclidean")
+    close(tpw.cosine_similarity(a, b), O.cosine_similarity(x1d, x2d).astype(np.float32), tol, msg="cosine_similarity")
+    close(tpw.cosine_distances(a, b), O.cosine_distances(x1d, x2d).astype(np.float32), tol, msg="cosine_distances")
+    close(tpw.correlation_distances(a, b), O.correlation_distances(x1d, x2d).astype(np.float32), tol, msg="correlation")
+    close(tpw.linear_kernel(a, b), (x1d @ np.swapaxes(x2d, -1, -2)).astype(np.float32), tol, d ** 0.5, msg="linear")
+
+
+def test_tensor_core_engine_details(tensor_engine, golden):
+    tpw = tensor_engine
+    g = torch.Generator().manual_seed(77)
+    x = torch.randn(700, 96, generator=g).cuda()
+    # x2 = None: the diagonal of the distance epilogues is exactly zero
+    assert torch.equal(tpw.sqeuclidean_distances(x).diagonal(), torch.zeros(700, device="cuda"))
+    assert torch.equal(tpw.euclidean_distances(x).diagonal(), torch.zeros(700, device="cuda"))
+    # gradients do not depend on which engine produced the forward values beyond its rounding
+    a = x.clone().requires_grad_(True)
+    y = torch.randn(520, 96, generator=g).cuda().requires_grad_(True)
+    gr = torch.randn(700, 520, generator=g).cuda()
+    tpw.euclidean_distances(a, y).backward(gr)
+    g1, g2 = O.cdist_backward(gr.double().cpu().numpy(), x.double().cpu().numpy(), y.detach().double().cpu().numpy(), 2.0)
+    close(a.grad, g1.astype(np.float32), TOL[torch.float32], 10 * float(np.abs(g1).max()), "euclidean grad_x1")
+    close(y.grad, g2.astype(np.float32), TOL[torch.float32], 10 * float(np.abs(g2).max()), "euclidean grad_x2")
+    # zero rows: cosine similarity keeps the (zero) numerator, distance is 1
+    z = x.clone()
+    z[5] = 0
+    s = tpw.cosine_similarity(z, x)
+    assert torch.equal(s[5], torch.zeros(700, device="cuda"))
+    # the C4-shaped golden block through the tensor cores
+    G = golden("configs")
+    X, Y = config_inputs("C4")
+    if np.array_equal(np.array([X.double().sum().item(), Y.double().sum().item()]), G["C4/checksum"]):
+        for name in ("sqeuclidean_distances", "cosine_distances"):
+            close(getattr(tpw, name)(X.cuda(), Y.cuda())[::8, ::8], G[f"C4/{name}"], TOL[torch.float32], msg="C4 " + name)
+    # float64 never leaves the CUDA cores
+    xd = x.double()
+    close(tpw.sqeuclidean_distances(xd[:50], xd[50:90]), O.sqeuclidean(xd[:50].cpu().numpy(), xd[50:90].cpu().numpy()),
+          TOL[torch.float64])
+
+
+def test_engine_auto_selection(tpw):
+    from torchpairwise_b200 import _abi
+    lib = _abi.lib
+    assert tpw.get_dot_engine() == "auto"
+    # small problems and float64 stay on the CUDA cores, large float32 problems go to the tensor cores
+    assert lib.tpw_dot_metric_scratch_bytes(_abi.F32, _abi.ENGINE_AUTO, 1, 1024, 2048, 128) > 0
+    assert lib.tpw_dot_metric_scratch_bytes(_abi.F32, _abi.ENGINE_AUTO, 1, 100, 100, 16) == 0
+    assert lib.tpw_dot_metric_scratch_bytes(_abi.F64, _abi.ENGINE_AUTO, 1, 4096, 4096, 512) == 0
+    assert lib.tpw_dot_metric_scratch_bytes(_abi.F32, _abi.ENGINE_SIMT_FP32, 1, 4096, 4096, 512) == 0
+    with pytest.raises(ValueError):
+        tpw.set_dot_engine("nope")

@@ -18,6 +18,7 @@ from .ops import (
     dice_distances,
     directed_hausdorff_distances,
     euclidean_distances,
+    get_dot_engine,
     hamming_distances,
     jaccard_distances,
     kulczynski1_distances,
@@ -39,6 +40,7 @@ from .ops import (
     pwxor_sum,
     rogerstanimoto_distances,
     russellrao_distances,
+    set_dot_engine,
     sokalmichener_distances,
     sokalsneath_distances,
     sqeuclidean_distances,

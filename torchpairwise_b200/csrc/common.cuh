@@ -88,11 +88,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: returns false after `limit` failed polls (each poll may itself block for a
-// hardware-defined short time), so a lost TMA completion can never hang the GPU.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, uint32_t limit = (1u << 22)) {
-    for (uint32_t it = 0; it < limit; ++it)
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: gives up (returns false) once about two seconds of wall time have passed without
+// the phase completing, or after `limit` polls, whichever comes first, so a lost completion can
+// never hang the GPU.
+constexpr uint64_t kWaitBudgetNs = 2000000000ull;
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, uint32_t limit = (1u << 26)) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t it = 0; it < limit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 255u) == 255u && globaltimer_ns() - t0 > kWaitBudgetNs) return false;
+    }
     return false;
 }
 

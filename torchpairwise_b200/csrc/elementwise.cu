@@ -213,21 +213,6 @@ extern "C" int tpw_dot_metric_forward(int dtype, int epilogue, int engine,
     return fail(TPW_ERR_UNSUPPORTED, "tpw_dot_metric_forward: engine %d needs scratch; call tpw_dot_metric_forward_ws", engine);
 }
 
-extern "C" int64_t tpw_dot_metric_scratch_bytes(int dtype, int engine, int64_t B, int64_t N1, int64_t N2, int64_t D) {
-    (void)dtype; (void)engine; (void)B; (void)N1; (void)N2; (void)D;
-    return 0;
-}
-
-extern "C" int tpw_dot_metric_forward_ws(int dtype, int epilogue, int engine,
-                                         const void *x1, const void *x2, void *out, void *scratch, int64_t scratch_bytes,
-                                         int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream) {
-    (void)scratch; (void)scratch_bytes;
-    clear_error();
-    if (engine == TPW_ENGINE_AUTO || engine == TPW_ENGINE_SIMT_FP32)
-        return tpw_dot_metric_forward_simt(dtype, epilogue, x1, x2, out, B, N1, N2, D, stream);
-    return fail(TPW_ERR_UNSUPPORTED, "tpw_dot_metric_forward_ws: engine %d is not built", engine);
-}
-
 extern "C" int tpw_cosine_backward_prepare(int dtype, int epilogue, const void *grad, const void *out,
                                            const void *norm1, const void *norm2,
                                            void *dM, void *rowterm, void *colterm,

@@ -1,0 +1,443 @@
+// Dense-contraction metrics (sqeuclidean, euclidean, cosine similarity / distance, correlation,
+// linear kernel) on the 5th-generation tensor cores: TMA -> shared memory -> tcgen05.mma with fp32
+// accumulators in tensor memory -> tcgen05.ld -> fused epilogue -> global.
+//
+// Precision.  The inputs are fp32 and the parity contract is rtol 1e-4 / atol 1e-5, which a single
+// bf16 or tf32 pass does not meet.  Each operand is therefore split once into a bf16 "high" part
+// and a bf16 "low" part (x = xh + xl up to 2^-17 relative) and the cross term is accumulated as
+// xh.yh + xh.yl + xl.yh (three MMAs per k-step into the same fp32 accumulator; xl.yl is below the
+// fp32 rounding of the sum).  Row norms are summed in fp32 from the unsplit values by the same
+// pre-pass.
+//
+// Kernel.  Persistent, one CTA per SM, 192 threads: warp 0 = TMA producer (one lane), warp 1 =
+// tensor-memory owner and MMA issuer (one lane), warps 2..5 = epilogue (each owns the 32 TMEM lanes
+// its warp id selects).  Output tile 128 x 256; k-step 64 bf16 = one 128-byte swizzled row; a stage
+// holds xh, xl (2 x 16 KB) and yh, yl (2 x 32 KB); two stages.  The 512 TMEM columns hold two
+// 128 x 256 fp32 accumulators so the epilogue of tile t overlaps the MMAs of tile t + 1.
+// No cluster launch and no multicast: every CTA fetches its own tiles from this GPU's memory.
+//
+// Every wait (mbarrier) is bounded; a warp that gives up raises a CTA-wide abort flag that the other
+// roles poll, everybody falls through to the final barrier, tensor memory is released, and the
+// device status word reports the site.
+#include "common.cuh"
+
+#include <cuda_bf16.h>
+#include <math.h>
+
+namespace tpw {
+namespace {
+
+constexpr int BM = 128;           // rows of x1 per tile (TMEM lanes)
+constexpr int BN = 256;           // rows of x2 per tile (TMEM columns per accumulator)
+constexpr int BK = 64;            // bf16 per k-step: 128 bytes
+constexpr int kStages = 2;
+constexpr int A_BYTES = BM * BK * 2;          // 16 KB
+constexpr int B_BYTES = BN * BK * 2;          // 32 KB
+constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES; // xh | xl | yh | yl = 96 KB
+constexpr int OFF_BAR = kStages * STAGE_BYTES;
+// barriers: full[2], empty[2], tmem_full[2], tmem_empty[2]; then the TMEM base address and the abort flag
+constexpr int OFF_TMEM_PTR = OFF_BAR + 8 * 8;
+constexpr int OFF_ABORT = OFF_TMEM_PTR + 4;
+constexpr int SMEM_BYTES = OFF_ABORT + 4;
+constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
+constexpr int kThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kSpinLimit = 1u << 26;
+
+struct GemmParams {
+    const float *n1sq, *n2sq; // squared row norms [B*N1], [B*N2]
+    float *out;
+    long long B, N1, N2, D;
+    long long tiles_m, tiles_n, tiles;
+    int epilogue;
+    int self;                 // x2 is x1: the diagonal of the distance epilogues is exactly zero
+    int vec_store;            // N2 % 4 == 0 and out 16-byte aligned
+    int *status;
+};
+
+// ---- PTX wrappers (tcgen05) ---------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t *smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, bf16 operands, fp32 accumulate
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread t of the warp receives lane (base + t)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzle:
+// start address >> 4 in bits [0,14), stride between 8-row groups (1024 B) >> 4 in bits [32,46),
+// descriptor version 1 in bits [46,48), swizzle mode 2 (128 B) in bits [61,64).  The leading
+// byte offset is not used by swizzled K-major layouts (set to 1).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor, kind::f16: D = fp32 (bits [4,6) = 1), A = B = bf16 (bits [7,10) = [10,13) = 1),
+// both K-major (bits 15, 16 = 0), N >> 3 in bits [17,23), M >> 4 in bits [24,29).
+__device__ __forceinline__ uint32_t make_idesc(int M, int N) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// Bounded mbarrier wait that also gives up when another role raised the abort flag.
+__device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 63u && (*abort_flag || globaltimer_ns() - t0 > kWaitBudgetNs)) return false;
+    }
+    return false;
+}
+
+__device__ __forceinline__ float dot_epilogue(int epilogue, float dot, float n1, float n2, bool diag) {
+    switch (epilogue) {
+        case TPW_DOT_LINEAR: return dot;
+        case TPW_DOT_SQEUCLIDEAN: return diag ? 0.f : fmaxf(n1 + n2 - 2.f * dot, 0.f);
+        case TPW_DOT_EUCLIDEAN: return diag ? 0.f : sqrtf(fmaxf(n1 + n2 - 2.f * dot, 0.f));
+        default: {
+            const float denom = sqrtf(n1) * sqrtf(n2);
+            const float s = denom != 0.f ? __fdiv_rn(dot, denom) : dot;
+            if (epilogue == TPW_DOT_COSINE_SIM) return s;
+            float dist = 1.f - s;
+            if (epilogue == TPW_DOT_COSINE_DIST) dist = fminf(fmaxf(dist, 0.f), 2.f);
+            return dist;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_constant__ CUtensorMap map_xl,
+                   const __grid_constant__ CUtensorMap map_yh, const __grid_constant__ CUtensorMap map_yl,
+                   const GemmParams P) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + OFF_BAR);
+    uint64_t *empty = full + kStages;
+    uint64_t *tmem_full = empty + kStages;
+    uint64_t *tmem_empty = tmem_full + 2;
+    uint32_t *tmem_ptr = reinterpret_cast<uint32_t *>(smem + OFF_TMEM_PTR);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + OFF_ABORT);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nkb = (int)((P.D + BK - 1) / BK);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 4); }
+        *abort_flag = 0;
+        mbar_init_fence();
+        tma_prefetch_descriptor(&map_xh);
+        tma_prefetch_descriptor(&map_xl);
+        tma_prefetch_descriptor(&map_yh);
+        tma_prefetch_descriptor(&map_yl);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_ptr, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (long long tile = blockIdx.x; tile < P.tiles && ok; tile += gridDim.x) {
+                long long t = tile;
+                const long long tn = t % P.tiles_n; t /= P.tiles_n;
+                const long long tm = t % P.tiles_m;
+                const long long b = t / P.tiles_m;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t use = it / kStages;
+                    if (use > 0 && !wait_or_abort(&empty[s], (use - 1) & 1, abort_flag)) {
+                        *abort_flag = 1;
+                        if (P.status) atomicCAS(P.status, 0, (4 << 16) | 1);
+                        ok = false;
+                        break;
+                    }
+                    unsigned char *st = smem + s * STAGE_BYTES;
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    tma_load_3d(st, &map_xh, &full[s], kb * BK, (int)(tm * BM), (int)b);
+                    tma_load_3d(st + A_BYTES, &map_xl, &full[s], kb * BK, (int)(tm * BM), (int)b);
+                    tma_load_3d(st + 2 * A_BYTES, &map_yh, &full[s], kb * BK, (int)(tn * BN), (int)b);
+                    tma_load_3d(st + 2 * A_BYTES + B_BYTES, &map_yl, &full[s], kb * BK, (int)(tn * BN), (int)b);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(BM, BN);
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (long long tile = blockIdx.x; tile < P.tiles && ok; tile += gridDim.x, ++tcount) {
+                const uint32_t a = tcount & 1, ause = tcount >> 1;
+                if (ause > 0 && !wait_or_abort(&tmem_empty[a], (ause - 1) & 1, abort_flag)) {
+                    *abort_flag = 1;
+                    if (P.status) atomicCAS(P.status, 0, (4 << 16) | 2);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + a * BN;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % kStages;
+                    if (!wait_or_abort(&full[s], (it / kStages) & 1, abort_flag)) {
+                        *abort_flag = 1;
+                        if (P.status) atomicCAS(P.status, 0, (4 << 16) | 3);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sb = smem_u32(smem + s * STAGE_BYTES);
+                    const uint64_t dxh = make_smem_desc(sb), dxl = make_smem_desc(sb + A_BYTES);
+                    const uint64_t dyh = make_smem_desc(sb + 2 * A_BYTES), dyl = make_smem_desc(sb + 2 * A_BYTES + B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t adv = (uint64_t)((k * 32) >> 4); // 16 bf16 = 32 bytes along the swizzled row
+                        tc_mma_bf16(d_tmem, dxh + adv, dyh + adv, idesc, (kb | k) != 0);
+                        tc_mma_bf16(d_tmem, dxh + adv, dyl + adv, idesc, 1);
+                        tc_mma_bf16(d_tmem, dxl + adv, dyh + adv, idesc, 1);
+                    }
+                    tc_commit(&empty[s]); // the stage may be refilled once these MMAs have read it
+                }
+                if (ok) tc_commit(&tmem_full[a]);
+            }
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5, TMEM lanes 32*(warp % 4) .. +31 ----------------
+        const int q = warp & 3;
+        uint32_t tcount = 0;
+        bool ok = true;
+        for (long long tile = blockIdx.x; tile < P.tiles && ok; tile += gridDim.x, ++tcount) {
+            long long t = tile;
+            const long long tn = t % P.tiles_n; t /= P.tiles_n;
+            const long long tm = t % P.tiles_m;
+            const long long b = t / P.tiles_m;
+            const uint32_t a = tcount & 1;
+            if (!wait_or_abort(&tmem_full[a], (tcount >> 1) & 1, abort_flag)) {
+                *abort_flag = 1;
+                if (lane == 0 && P.status) atomicCAS(P.status, 0, (4 << 16) | 4);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const long long i = tm * BM + q * 32 + lane;
+            const bool row_ok = i < P.N1;
+            const float n1 = row_ok ? P.n1sq[b * P.N1 + i] : 0.f;
+            float *orow = P.out + (b * P.N1 + (row_ok ? i : 0)) * P.N2;
+            const float *n2p = P.n2sq + b * P.N2;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + a * BN + c * 32;
+                tmem_ld32(taddr, r);
+                tmem_ld_wait();
+                const long long j0 = tn * BN + c * 32;
+                if (!row_ok || j0 >= P.N2) continue;
+                if (P.vec_store && j0 + 32 <= P.N2) {
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) {
+                        const float4 nn = __ldg(reinterpret_cast<const float4 *>(n2p + j0) + v);
+                        float4 o;
+                        o.x = dot_epilogue(P.epilogue, __uint_as_float(r[4 * v + 0]), n1, nn.x, P.self && i == j0 + 4 * v + 0);
+                        o.y = dot_epilogue(P.epilogue, __uint_as_float(r[4 * v + 1]), n1, nn.y, P.self && i == j0 + 4 * v + 1);
+                        o.z = dot_epilogue(P.epilogue, __uint_as_float(r[4 * v + 2]), n1, nn.z, P.self && i == j0 + 4 * v + 2);
+                        o.w = dot_epilogue(P.epilogue, __uint_as_float(r[4 * v + 3]), n1, nn.w, P.self && i == j0 + 4 * v + 3);
+                        reinterpret_cast<float4 *>(orow + j0)[v] = o;
+                    }
+                } else {
+#pragma unroll
+                    for (int v = 0; v < 32; ++v) {
+                        const long long j = j0 + v;
+                        if (j < P.N2)
+                            orow[j] = dot_epilogue(P.epilogue, __uint_as_float(r[v]), n1, __ldg(n2p + j), P.self && i == j);
+                    }
+                }
+            }
+            // this warp has drained its quarter of accumulator `a`
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[a]);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// fp32 rows -> bf16 high/low parts (row pitch Dp, zero padded) and the fp32 squared norm; one warp per row
+__global__ void split_rows_kernel(const float *__restrict__ x, __nv_bfloat16 *__restrict__ hi, __nv_bfloat16 *__restrict__ lo,
+                                  float *__restrict__ nsq, long long rows, long long D, long long Dp) {
+    const int lane = threadIdx.x & 31;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long r = warp; r < rows; r += nwarps) {
+        const float *row = x + r * D;
+        float s = 0.f;
+        for (long long k = lane; k < Dp; k += 32) {
+            const float v = k < D ? row[k] : 0.f;
+            const __nv_bfloat16 h = __float2bfloat16_rn(v);
+            const __nv_bfloat16 l = __float2bfloat16_rn(v - __bfloat162float(h));
+            hi[r * Dp + k] = h;
+            lo[r * Dp + k] = l;
+            s = fmaf(v, v, s);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+        if (lane == 0) nsq[r] = s;
+    }
+}
+
+inline long long align_up(long long v, long long a) { return (v + a - 1) / a * a; }
+
+// TPW_ENGINE_AUTO: the tensor-core engine pays for its split pre-pass and 128 x 256 tiles only on
+// large fp32 problems; everything else stays on the exact fp32/fp64 CUDA-core tile.
+inline bool auto_picks_tensor_cores(int dtype, long long B, long long N1, long long N2, long long D) {
+    return dtype == TPW_F32 && D >= 64 && N1 >= 128 && N2 >= 256 && (double)B * N1 * N2 * D >= (double)(1ll << 28);
+}
+
+struct ScratchLayout {
+    long long Dp, off_xh, off_xl, off_yh, off_yl, off_n1, off_n2, total;
+};
+
+inline ScratchLayout scratch_layout(long long B, long long N1, long long N2, long long D, bool self) {
+    ScratchLayout L;
+    L.Dp = align_up(D, 8); // 16-byte row pitch for the tensor maps
+    const long long xa = align_up(B * N1 * L.Dp * 2, 1024), ya = self ? 0 : align_up(B * N2 * L.Dp * 2, 1024);
+    L.off_xh = 0;
+    L.off_xl = xa;
+    L.off_yh = self ? L.off_xh : 2 * xa;
+    L.off_yl = self ? L.off_xl : 2 * xa + ya;
+    L.off_n1 = 2 * xa + 2 * ya;
+    L.off_n2 = self ? L.off_n1 : L.off_n1 + align_up(B * N1 * 4, 1024);
+    L.total = L.off_n2 + align_up(B * N2 * 4, 1024);
+    return L;
+}
+
+} // namespace
+} // namespace tpw
+
+using namespace tpw;
+
+extern "C" int tpw_dot_metric_forward_simt(int dtype, int epilogue, const void *x1, const void *x2, void *out,
+                                           int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream);
+
+extern "C" int64_t tpw_dot_metric_scratch_bytes(int dtype, int engine, int64_t B, int64_t N1, int64_t N2, int64_t D) {
+    if (B <= 0 || N1 <= 0 || N2 <= 0 || D <= 0 || dtype != TPW_F32) return 0;
+    if (engine == TPW_ENGINE_TCGEN05_BF16X3 || (engine == TPW_ENGINE_AUTO && auto_picks_tensor_cores(dtype, B, N1, N2, D)))
+        return scratch_layout(B, N1, N2, D, false).total;
+    return 0;
+}
+
+extern "C" int tpw_dot_metric_forward_ws(int dtype, int epilogue, int engine,
+                                         const void *x1, const void *x2, void *out, void *scratch, int64_t scratch_bytes,
+                                         int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(engine >= TPW_ENGINE_AUTO && engine <= TPW_ENGINE_TCGEN05_BF16X3, "tpw_dot_metric_forward_ws: bad engine %d", engine);
+    if (engine == TPW_ENGINE_AUTO && auto_picks_tensor_cores(dtype, B, N1, N2, D) && scratch != nullptr &&
+        scratch_bytes >= scratch_layout(B, N1, N2, D, false).total)
+        engine = TPW_ENGINE_TCGEN05_BF16X3;
+    if (engine != TPW_ENGINE_TCGEN05_BF16X3 || dtype != TPW_F32) {
+        TPW_CHECK_ARG(engine != TPW_ENGINE_TCGEN05_BF16X3 || dtype == TPW_F64,
+                      "tpw_dot_metric_forward_ws: bad dtype %d", dtype);
+        return tpw_dot_metric_forward_simt(dtype, epilogue, x1, x2, out, B, N1, N2, D, stream);
+    }
+    TPW_CHECK_ARG(epilogue >= TPW_DOT_LINEAR && epilogue <= TPW_DOT_EUCLIDEAN, "tpw_dot_metric_forward_ws: bad epilogue %d", epilogue);
+    TPW_CHECK_ARG(B >= 0 && N1 >= 0 && N2 >= 0 && D >= 0, "tpw_dot_metric_forward_ws: negative size");
+    if (B == 0 || N1 == 0 || N2 == 0) return TPW_OK;
+    TPW_CHECK_ARG(x1 && x2 && out, "tpw_dot_metric_forward_ws: NULL pointer");
+    TPW_CHECK_ARG(D > 0, "tpw_dot_metric_forward_ws: D must be positive");
+    TPW_CHECK_ARG(N1 < (1ll << 31) && N2 < (1ll << 31) && B < (1ll << 31) && D < (1ll << 31),
+                  "tpw_dot_metric_forward_ws: a dimension exceeds 2^31-1");
+    const bool self = (x1 == x2) && (N1 == N2);
+    const ScratchLayout L = scratch_layout(B, N1, N2, D, false);
+    TPW_CHECK_ARG(scratch != nullptr && scratch_bytes >= L.total,
+                  "tpw_dot_metric_forward_ws: the tensor-core engine needs %lld bytes of scratch (got %lld)",
+                  L.total, (long long)scratch_bytes);
+    TPW_CHECK_ARG(aligned16(scratch), "tpw_dot_metric_forward_ws: scratch must be 16-byte aligned");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned char *base = static_cast<unsigned char *>(scratch);
+    __nv_bfloat16 *xh = reinterpret_cast<__nv_bfloat16 *>(base + L.off_xh), *xl = reinterpret_cast<__nv_bfloat16 *>(base + L.off_xl);
+    __nv_bfloat16 *yh = reinterpret_cast<__nv_bfloat16 *>(base + L.off_yh), *yl = reinterpret_cast<__nv_bfloat16 *>(base + L.off_yl);
+    float *n1 = reinterpret_cast<float *>(base + L.off_n1), *n2 = reinterpret_cast<float *>(base + L.off_n2);
+
+    const int threads = 256;
+    const long long cap = (long long)sm_count() * 16;
+    long long blocks = (B * N1 * 32 + threads - 1) / threads;
+    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x1, xh, xl, n1, B * N1, D, L.Dp);
+    blocks = (B * N2 * 32 + threads - 1) / threads;
+    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x2, yh, yl, n2, B * N2, D, L.Dp);
+    TPW_LAUNCH_OK("split_rows_kernel");
+
+    CUtensorMap mxh, mxl, myh, myl;
+    int st;
+    if ((st = make_tensor_map_3d(&mxh, xh, 2, L.Dp, N1, B, BK, BM, true)) != TPW_OK) return st;
+    if ((st = make_tensor_map_3d(&mxl, xl, 2, L.Dp, N1, B, BK, BM, true)) != TPW_OK) return st;
+    if ((st = make_tensor_map_3d(&myh, yh, 2, L.Dp, N2, B, BK, BN, true)) != TPW_OK) return st;
+    if ((st = make_tensor_map_3d(&myl, yl, 2, L.Dp, N2, B, BK, BN, true)) != TPW_OK) return st;
+
+    GemmParams P;
+    memset(&P, 0, sizeof(P));
+    P.n1sq = n1; P.n2sq = n2; P.out = static_cast<float *>(out);
+    P.B = B; P.N1 = N1; P.N2 = N2; P.D = L.Dp;
+    P.tiles_m = (N1 + BM - 1) / BM;
+    P.tiles_n = (N2 + BN - 1) / BN;
+    P.tiles = B * P.tiles_m * P.tiles_n;
+    P.epilogue = epilogue;
+    P.self = self ? 1 : 0;
+    P.vec_store = (N2 % 4 == 0 && aligned16(out)) ? 1 : 0;
+    P.status = device_status_ptr();
+    TPW_CHECK_ARG(P.tiles < (1ll << 40), "tpw_dot_metric_forward_ws: too many tiles");
+    TPW_CUDA_OK(cudaFuncSetAttribute(gemm_metric_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
+    const long long nsm = sm_count();
+    const unsigned grid = (unsigned)(P.tiles < nsm ? P.tiles : nsm);
+    gemm_metric_kernel<<<grid, kThreads, SMEM_ALLOC, s>>>(mxh, mxl, myh, myl, P);
+    TPW_LAUNCH_OK("gemm_metric_kernel");
+    return TPW_OK;
+}

@@ -7,13 +7,14 @@
 // (the forward output, or the S^(1/p-1) matrix of the weighted form), and phi an odd function of
 // the coordinate difference chosen by p.  The two sums are two passes of ONE kernel: the "row"
 // operand (x1 for grad_x1, x2 for grad_x2) sits in registers, the other operand and the
-// coefficient tile are streamed through shared memory 32 rows at a time.  A CTA of 256 threads
-// owns a (16R rows) x (16R features) block of the gradient and sums over the whole streamed
-// dimension itself, so every gradient element is written once, without atomics, in a fixed order.
+// coefficient tile are streamed through shared memory 32 rows at a time.  A CTA (512 threads for
+// float, 4 rows x 8 features each) owns a 128-row x 128-feature block of the gradient and sums
+// over the whole streamed dimension itself, so every gradient element is written once, without
+// atomics, in a fixed order.
 //
-// Thread (tr, tk) = (tid/16, tid%16) owns rows {64g + 4tr + e} and features {64g + 4tk + e}
-// (g < R/4, e < 4): 16-byte shared loads of the streamed operand are contiguous across a quarter
-// warp and the coefficient loads are broadcasts.  Aligned problems are fed by TMA (three-stage
+// Thread (tr, tk) = (tid/16, tid%16) owns rows {4tr + e} and features {64g + 4tk + e} (e < 4):
+// 16-byte shared loads of the streamed operand are contiguous across a quarter warp and the
+// coefficient loads are broadcasts.  Aligned problems are fed by TMA (three-stage
 // mbarrier ring, one issuing thread); others use guarded plain loads into the same layout.
 #include "common.cuh"
 
@@ -32,7 +33,7 @@ enum Phi {
     PHI_SGN_EQ = 6  // sgn(d) where |d| equals the auxiliary value, else 0
 };
 
-enum CoefMode { COEF_G = 0, COEF_DIV_O = 1, COEF_DIV_O2 = 2, COEF_DIV_POW = 3, COEF_MUL = 4 };
+enum CoefMode { COEF_G = 0, COEF_DIV_O = 1, COEF_DIV_O2 = 2, COEF_DIV_POW = 3, COEF_MUL = 4, COEF_ZERO_WHERE_O0 = 5 };
 
 struct BwdParams {
     const void *rowop;  // [B, NR, D] operand held in registers
@@ -49,7 +50,6 @@ struct BwdParams {
     int *status;
 };
 
-constexpr int kThreads = 256;
 constexpr int kStages = 3;
 constexpr int SC = 32; // streamed rows per stage
 
@@ -72,6 +72,11 @@ __device__ __forceinline__ float b_powabs(float a, float q) { return a == 0.f ? 
 __device__ __forceinline__ double b_powabs(double a, double q) { return a == 0.0 ? 0.0 : pow(a, q); }
 __device__ __forceinline__ float b_copysign(float a, float s) { return copysignf(a, s); }
 __device__ __forceinline__ double b_copysign(double a, double s) { return copysign(a, s); }
+// c * sgn(d) for d != 0: flip c's sign bit with d's (one logic operation)
+__device__ __forceinline__ float b_copysign_of(float c, float d) {
+    return __int_as_float(__float_as_int(c) ^ (__float_as_int(d) & 0x80000000));
+}
+__device__ __forceinline__ double b_copysign_of(double c, double d) { return d < 0.0 ? -c : c; }
 __device__ __forceinline__ float b_pow(float a, double q) { return powf(a, (float)q); }
 __device__ __forceinline__ double b_pow(double a, double q) { return pow(a, q); }
 
@@ -88,21 +93,23 @@ __device__ __forceinline__ void bwd_accumulate(T &acc, T x, T y, T c, T o, T q) 
     } else if (PHI == PHI_DABS) {
         acc = b_fma(c, d * b_abs(d), acc);
     } else if (PHI == PHI_SGN) {
-        T s = d > T(0) ? c : -c;
-        acc += d != T(0) ? s : T(0);
+        if (d != T(0)) acc += b_copysign_of(c, d);
     } else if (PHI == PHI_SGNPOW) {
         acc = b_fma(c, b_copysign(b_powabs(b_abs(d), q), d), acc);
     } else if (PHI == PHI_ABSPOW) {
         acc = b_fma(c, b_powabs(b_abs(d), q), acc);
     } else if (PHI == PHI_SGN_EQ) {
-        T s = d > T(0) ? c : -c;
-        acc += (d != T(0) && b_abs(d) == o) ? s : T(0);
+        // c is already zero where o == 0, and |d| == o > 0 implies d != 0
+        if (b_abs(d) == o) acc += b_copysign_of(c, d);
     }
 }
 
-template <typename T, int R> struct BwdSmem {
-    static constexpr int TR = 16 * R;             // rows of the register operand per CTA
-    static constexpr int TK = 16 * R;             // features per CTA
+// RR rows x RK features per thread, NTHR threads: (NTHR/16)*RR rows by 16*RK features per CTA.
+// float: 4 x 8 on 512 threads (128 x 128, 16 warps per SM for latency hiding at <= 128 registers);
+// double: 4 x 4 on 256 threads (64 x 64).
+template <typename T, int RR, int RK, int NTHR> struct BwdSmem {
+    static constexpr int TR = (NTHR / 16) * RR;   // rows of the register operand per CTA
+    static constexpr int TK = 16 * RK;            // features per CTA
     static constexpr int YS_BYTES = SC * TK * (int)sizeof(T);
     static constexpr int GS_BYTES = SC * TR * (int)sizeof(T);
     static constexpr int STAGE_BYTES = YS_BYTES + 2 * GS_BYTES; // streamed rows | grad tile | aux tile
@@ -114,12 +121,14 @@ template <typename T, int R> struct BwdSmem {
 // TRANS = false: the register operand is x1 (rows i), streamed rows are j; the coefficient tile is
 // stored [TR rows i][SC] exactly as it lies in memory.  TRANS = true: register operand x2 (rows j),
 // streamed rows are i; the coefficient tile is stored [SC][TR rows j], again as it lies in memory.
-template <typename T, int R, int PHI, bool NEED_AUX, bool TRANS, bool USE_TMA>
-__global__ void __launch_bounds__(kThreads, 1)
+template <typename T, int RR, int RK, int NTHR, int PHI, bool NEED_AUX, bool TRANS, bool USE_TMA>
+__global__ void __launch_bounds__(NTHR, 1)
 lp_backward_kernel(const __grid_constant__ CUtensorMap map_stream, const __grid_constant__ CUtensorMap map_grad,
                    const __grid_constant__ CUtensorMap map_aux, const BwdParams P) {
-    typedef BwdSmem<T, R> S;
-    constexpr int TR = S::TR, TK = S::TK, G = R / 4;
+    typedef BwdSmem<T, RR, RK, NTHR> S;
+    constexpr int TR = S::TR, TK = S::TK, GK = RK / 4;
+    constexpr int RSTRIDE = (NTHR / 16) * 4;      // distance between a thread's groups of four rows
+    constexpr int kThreads = NTHR;
     constexpr bool AUX_IN_LOOP = (PHI == PHI_SGN_EQ);
 
     extern __shared__ unsigned char smem_raw[];
@@ -141,24 +150,24 @@ lp_backward_kernel(const __grid_constant__ CUtensorMap map_stream, const __grid_
     const T *grad = reinterpret_cast<const T *>(P.grad) + b * P.N1 * P.N2;
     const T *aux = NEED_AUX ? reinterpret_cast<const T *>(P.aux) + b * P.N1 * P.N2 : nullptr;
 
-    // register operand: rows {64g + 4tr + e}, features {64g + 4tk + e}
-    T xr[R][R];
+    // register operand: rows {RSTRIDE*g + 4tr + e}, features {64g + 4tk + e}
+    T xr[RR][RK];
     if (PHI != PHI_Y) {
 #pragma unroll
-        for (int a = 0; a < R; ++a) {
-            const long long row = r0 + (a / 4) * 64 + tr * 4 + (a % 4);
+        for (int a = 0; a < RR; ++a) {
+            const long long row = r0 + (a / 4) * RSTRIDE + tr * 4 + (a % 4);
 #pragma unroll
-            for (int c = 0; c < R; ++c) {
+            for (int c = 0; c < RK; ++c) {
                 const long long k = k0 + (c / 4) * 64 + tk * 4 + (c % 4);
                 xr[a][c] = (row < P.NR && k < P.D) ? rowop[row * P.D + k] : T(0);
             }
         }
     }
-    T acc[R][R];
+    T acc[RR][RK];
 #pragma unroll
-    for (int a = 0; a < R; ++a)
+    for (int a = 0; a < RR; ++a)
 #pragma unroll
-        for (int c = 0; c < R; ++c) acc[a][c] = T(0);
+        for (int c = 0; c < RK; ++c) acc[a][c] = T(0);
 
     const int nchunks = (int)((P.NS + SC - 1) / SC);
     const uint32_t tx_bytes = S::YS_BYTES + S::GS_BYTES + (NEED_AUX ? S::GS_BYTES : 0);
@@ -228,7 +237,7 @@ lp_backward_kernel(const __grid_constant__ CUtensorMap map_stream, const __grid_
             __syncthreads();
         }
 
-        if (NEED_AUX && !AUX_IN_LOOP) {
+        if (NEED_AUX) {
             // coefficient tile in place: c = f(g, aux)
             for (int e = tid; e < SC * TR; e += kThreads) {
                 const T g = gs[e], o = as[e];
@@ -238,6 +247,7 @@ lp_backward_kernel(const __grid_constant__ CUtensorMap map_stream, const __grid_
                     case COEF_DIV_O2: c = o == T(0) ? T(0) : g / (o * o); break;
                     case COEF_DIV_POW: c = o == T(0) ? T(0) : g / b_pow(o, P.q); break;
                     case COEF_MUL: c = g * o; break;
+                    case COEF_ZERO_WHERE_O0: c = o == T(0) ? T(0) : g; break;
                     default: c = g; break;
                 }
                 gs[e] = c;
@@ -247,35 +257,35 @@ lp_backward_kernel(const __grid_constant__ CUtensorMap map_stream, const __grid_
 
 #pragma unroll 1
         for (int s = 0; s < SC; s += 4) {
-            T cv[TRANS ? 1 : R][4];
-            T ov[(AUX_IN_LOOP && !TRANS) ? R : 1][4];
+            T cv[TRANS ? 1 : RR][4];
+            T ov[(AUX_IN_LOOP && !TRANS) ? RR : 1][4];
             if (!TRANS) {
 #pragma unroll
-                for (int a = 0; a < R; ++a) {
-                    const int row = (a / 4) * 64 + tr * 4 + (a % 4);
+                for (int a = 0; a < RR; ++a) {
+                    const int row = (a / 4) * RSTRIDE + tr * 4 + (a % 4);
                     load4<T>(cv[a], gs + row * SC + s);
                     if (AUX_IN_LOOP) load4<T>(ov[a], as + row * SC + s);
                 }
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                T yv[R];
+                T yv[RK];
 #pragma unroll
-                for (int g = 0; g < G; ++g) load4<T>(&yv[g * 4], ys + (s + u) * TK + g * 64 + tk * 4);
-                T ct[R], ot[R];
+                for (int g = 0; g < GK; ++g) load4<T>(&yv[g * 4], ys + (s + u) * TK + g * 64 + tk * 4);
+                T ct[RR], ot[RR];
                 if (TRANS) {
 #pragma unroll
-                    for (int g = 0; g < G; ++g) {
-                        load4<T>(&ct[g * 4], gs + (s + u) * TR + g * 64 + tr * 4);
-                        if (AUX_IN_LOOP) load4<T>(&ot[g * 4], as + (s + u) * TR + g * 64 + tr * 4);
+                    for (int g = 0; g < RR / 4; ++g) {
+                        load4<T>(&ct[g * 4], gs + (s + u) * TR + g * RSTRIDE + tr * 4);
+                        if (AUX_IN_LOOP) load4<T>(&ot[g * 4], as + (s + u) * TR + g * RSTRIDE + tr * 4);
                     }
                 }
 #pragma unroll
-                for (int a = 0; a < R; ++a) {
+                for (int a = 0; a < RR; ++a) {
                     const T c = TRANS ? ct[a] : cv[a][u];
                     const T o = AUX_IN_LOOP ? (TRANS ? ot[a] : ov[a][u]) : T(0);
 #pragma unroll
-                    for (int kk = 0; kk < R; ++kk) bwd_accumulate<PHI, T>(acc[a][kk], xr[a][kk], yv[kk], c, o, q);
+                    for (int kk = 0; kk < RK; ++kk) bwd_accumulate<PHI, T>(acc[a][kk], xr[a][kk], yv[kk], c, o, q);
                 }
             }
         }
@@ -291,11 +301,11 @@ lp_backward_kernel(const __grid_constant__ CUtensorMap map_stream, const __grid_
     const T *w = P.w ? reinterpret_cast<const T *>(P.w) + b * P.D : nullptr;
     const T post = (T)P.post;
 #pragma unroll
-    for (int a = 0; a < R; ++a) {
-        const long long row = r0 + (a / 4) * 64 + tr * 4 + (a % 4);
+    for (int a = 0; a < RR; ++a) {
+        const long long row = r0 + (a / 4) * RSTRIDE + tr * 4 + (a % 4);
         if (row >= P.NR) continue;
 #pragma unroll
-        for (int c = 0; c < R; ++c) {
+        for (int c = 0; c < RK; ++c) {
             const long long k = k0 + (c / 4) * 64 + tk * 4 + (c % 4);
             if (k >= P.D) continue;
             T v = acc[a][c] * post;
@@ -307,8 +317,10 @@ lp_backward_kernel(const __grid_constant__ CUtensorMap map_stream, const __grid_
 
 template <typename T, int PHI, bool NEED_AUX, bool TRANS>
 int launch_backward(BwdParams P, cudaStream_t stream) {
-    constexpr int R = sizeof(T) == 4 ? 8 : 4;
-    typedef BwdSmem<T, R> S;
+    constexpr int RR = 4;
+    constexpr int RK = sizeof(T) == 4 ? 8 : 4;
+    constexpr int NTHR = sizeof(T) == 4 ? 512 : 256;
+    typedef BwdSmem<T, RR, RK, NTHR> S;
     P.tiles_r = (P.NR + S::TR - 1) / S::TR;
     P.tiles_k = (P.D + S::TK - 1) / S::TK;
     const long long tiles = P.B * P.tiles_r * P.tiles_k;
@@ -334,13 +346,13 @@ int launch_backward(BwdParams P, cudaStream_t stream) {
             st = make_tensor_map_3d(&ma, P.aux, sizeof(T), P.N2, P.N1, P.B, gb0, gb1, false);
             if (st != TPW_OK) return st;
         }
-        auto kern = lp_backward_kernel<T, R, PHI, NEED_AUX, TRANS, true>;
+        auto kern = lp_backward_kernel<T, RR, RK, NTHR, PHI, NEED_AUX, TRANS, true>;
         TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::ALLOC));
-        kern<<<(unsigned)tiles, kThreads, S::ALLOC, stream>>>(ms, mg, ma, P);
+        kern<<<(unsigned)tiles, NTHR, S::ALLOC, stream>>>(ms, mg, ma, P);
     } else {
-        auto kern = lp_backward_kernel<T, R, PHI, NEED_AUX, TRANS, false>;
+        auto kern = lp_backward_kernel<T, RR, RK, NTHR, PHI, NEED_AUX, TRANS, false>;
         TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::ALLOC));
-        kern<<<(unsigned)tiles, kThreads, S::ALLOC, stream>>>(ms, mg, ma, P);
+        kern<<<(unsigned)tiles, NTHR, S::ALLOC, stream>>>(ms, mg, ma, P);
     }
     TPW_LAUNCH_OK("lp_backward_kernel");
     return TPW_OK;
@@ -384,7 +396,7 @@ int lp_backward_typed(int mode, BwdParams P, const void *x1, const void *x2, voi
             return launch_both<T, PHI_Y, false>(P, x1, x2, g1, g2, stream);
         case TPW_LP_BWD_CDIST:
             P.w = nullptr;
-            if (isinf(p)) return launch_both<T, PHI_SGN_EQ, true>(P, x1, x2, g1, g2, stream);
+            if (isinf(p)) { P.coef_mode = COEF_ZERO_WHERE_O0; return launch_both<T, PHI_SGN_EQ, true>(P, x1, x2, g1, g2, stream); }
             if (p == 1.0) { P.aux = nullptr; return launch_both<T, PHI_SGN, false>(P, x1, x2, g1, g2, stream); }
             if (p == 2.0) { P.coef_mode = COEF_DIV_O; return launch_both<T, PHI_D, true>(P, x1, x2, g1, g2, stream); }
             if (p == 3.0) { P.coef_mode = COEF_DIV_O2; return launch_both<T, PHI_DABS, true>(P, x1, x2, g1, g2, stream); }

@@ -10,6 +10,7 @@ stream; nothing falls back to the CPU or to eager PyTorch arithmetic on the [N1,
 from __future__ import annotations
 
 import math
+import os
 import warnings
 from typing import Optional, Tuple
 
@@ -20,6 +21,33 @@ from . import _abi
 from ._abi import check, lib
 
 _FLOAT_CODES = {torch.float32: _abi.F32, torch.float64: _abi.F64}
+
+_ENGINE_NAMES = {"auto": _abi.ENGINE_AUTO, "simt": _abi.ENGINE_SIMT_FP32, "tcgen05": _abi.ENGINE_TCGEN05_BF16X3}
+_dot_engine = _ENGINE_NAMES.get(os.environ.get("TPW_DOT_ENGINE", "auto").lower(), _abi.ENGINE_AUTO)
+
+
+def set_dot_engine(name: str) -> None:
+    """Engine of the dense-contraction metrics (sqeuclidean, euclidean, cosine, correlation,
+    linear kernel) for float32 inputs: "auto" (tensor cores for large problems, CUDA cores
+    otherwise), "simt" (always the exact fp32 CUDA-core tile) or "tcgen05" (always the bf16x3
+    tensor-core kernel).  float64 always runs on the CUDA cores.  Also settable through the
+    environment variable TPW_DOT_ENGINE."""
+    global _dot_engine
+    if name not in _ENGINE_NAMES:
+        raise ValueError(f"engine must be one of {sorted(_ENGINE_NAMES)}")
+    _dot_engine = _ENGINE_NAMES[name]
+
+
+def get_dot_engine() -> str:
+    return {v: k for k, v in _ENGINE_NAMES.items()}[_dot_engine]
+
+
+def _tensor_engine_selected(x1c: Tensor, x2c: Tensor) -> bool:
+    """True when the current engine setting sends this float32 problem to the tensor cores."""
+    if x1c.dtype != torch.float32 or x1c.size(2) == 0:
+        return False
+    B, N1, N2, D = x1c.size(0), x1c.size(1), x2c.size(1), x1c.size(2)
+    return lib.tpw_dot_metric_scratch_bytes(_abi.F32, _dot_engine, B, N1, N2, D) > 0
 
 
 # --------------------------------------------------------------------------------------------
@@ -130,7 +158,8 @@ def _lp_backward_raw(mode: int, grad: Tensor, aux: Optional[Tensor], x1c: Tensor
     return g1, g2
 
 
-def _dot_forward_raw(x1c: Tensor, x2c: Tensor, epilogue: int, engine: int = _abi.ENGINE_AUTO) -> Tensor:
+def _dot_forward_raw(x1c: Tensor, x2c: Tensor, epilogue: int, engine: Optional[int] = None) -> Tensor:
+    engine = _dot_engine if engine is None else engine
     B, N1, N2, D = _sizes(x1c, x2c)
     out = torch.empty((B, N1, N2), dtype=x1c.dtype, device=x1c.device)
     if D == 0:
@@ -178,6 +207,9 @@ class _CdistFunction(torch.autograd.Function):
             out = _cmp_reduce_raw(x1c, x2c, _abi.CMP_NE, _abi.RED_SUM).to(cdt)
         elif math.isinf(p):
             out = _lp_forward_raw(x1c, x2c, None, math.inf, 1.0)
+        elif p == 2 and _tensor_engine_selected(x1c, x2c):
+            # sqrt(clamp(|x|^2 + |y|^2 - 2 x.y, 0)): the contraction form ATen itself uses for p = 2
+            out = _dot_forward_raw(x1c, x2c, _abi.DOT_EUCLIDEAN)
         else:
             out = _lp_forward_raw(x1c, x2c, None, p, 1.0 / p)
         ctx.save_for_backward(x1c, x2c, out)
@@ -216,6 +248,8 @@ class _PPMinkowskiFunction(torch.autograd.Function):
         if p == 0:
             B, N1, N2, D = _sizes(x1c, x2c)
             out = torch.full((B, N1, N2), float(D), dtype=cdt, device=x1c.device)
+        elif p == 2 and _tensor_engine_selected(x1c, x2c):
+            out = _dot_forward_raw(x1c, x2c, _abi.DOT_SQEUCLIDEAN)
         else:
             out = _lp_forward_raw(x1c, x2c, None, p, 1.0)
         ctx.save_for_backward(x1c, x2c)

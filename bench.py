@@ -330,6 +330,110 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         print(json.dumps(line), flush=True)
 
 
+def run_suite(args):
+    """Kernel-level throughput of every metric on the five benchmark configurations (1 GPU).
+
+    Times are CUDA-event averages over ``--steps`` launches after ``--warmup`` launches, inputs
+    resident in HBM, outputs larger than L2 except where noted.  Roofline fractions use the issue
+    rates measured live by the library (fp32 FMA, POPC), the copy bandwidth and the sustained
+    bf16 matmul rate of MEASURED_PEAKS.json."""
+    import torch
+    import torchpairwise_b200 as tpw
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    fp32_peak = tpw.measure_issue_peak(0)
+    popc_peak = tpw.measure_issue_peak(2)
+    hbm_peak, _ = load_peaks()
+    pk = ROOT / "MEASURED_PEAKS.json"
+    bf16_peak = float(json.loads(pk.read_text())["bf16_tflops_sustained"]) * 1e12 if pk.exists() else 1.4e15
+    only = set(filter(None, args.suite_only.split(",")))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    res = {"peaks": {"fp32_lane_ops_per_s": fp32_peak, "popc_per_s": popc_peak, "hbm_GBps": hbm_peak,
+                     "bf16_flops_per_s_sustained": bf16_peak}, "entries": {}}
+
+    def timeit(fn):
+        for _ in range(max(1, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.steps * 1e-3
+
+    def entry(name, pairs, secs, bound, work, peak, out_bytes):
+        res["entries"][name] = {"ms": secs * 1e3, "Gpairs_s": pairs / secs / 1e9, "bound": bound,
+                                "frac_of_bound": work / secs / peak, "hbm_frac_output_only": out_bytes / secs / 1e9 / hbm_peak}
+
+    g = torch.Generator().manual_seed(0)
+    want = lambda n: not only or n in only  # noqa: E731
+    # ---- C1: X[1024,128], Y[2048,128] (tiny: launch-latency bound, L2 resident) ---------------------
+    X, Y = torch.randn(1024, 128, generator=g).to(dev), torch.randn(2048, 128, generator=g).to(dev)
+    n = 1024 * 2048
+    for name, fn, ops in (("C1_euclidean", tpw.euclidean_distances, 2), ("C1_manhattan", tpw.manhattan_distances, 2),
+                          ("C1_cosine", tpw.cosine_distances, 1)):
+        if want(name):
+            entry(name, n, timeit(lambda: fn(X, Y)), "fp32_issue (L2 resident, launch bound)", n * 128 * ops, fp32_peak, 4 * n)
+    # ---- C2: X,Y[16,4096,256] forward and backward kernels ------------------------------------------
+    X = torch.randn(args.batches, 4096, 256, generator=g).to(dev).requires_grad_(True)
+    Y = torch.randn(args.batches, 4096, 256, generator=g).to(dev).requires_grad_(True)
+    G = torch.randn(args.batches, 4096, 4096, generator=g).to(dev)
+    n = args.batches * 4096 * 4096
+    for name, p, fo, bo in (("C2_minkowski_p3", 3.0, 3, 6), ("C2_chebyshev", math.inf, 2, 8), ("C2_manhattan", 1.0, 2, 8),
+                            ("C2_minkowski_p2.5", 2.5, 5, 12)):
+        if want(name + "_fwd"):
+            with torch.no_grad():
+                entry(name + "_fwd", n, timeit(lambda: tpw.minkowski_distances(X, Y, p)), "fp32_issue", n * 256 * fo, fp32_peak, 4 * n)
+        if want(name + "_bwd"):
+            out = tpw.minkowski_distances(X, Y, p)
+
+            def bwd():
+                X.grad = None
+                Y.grad = None
+                out.backward(G, retain_graph=True)
+            entry(name + "_bwd", n, timeit(bwd), "fp32_issue", n * 256 * bo, fp32_peak, 0)
+            del out
+    del X, Y, G
+    # ---- C3: bool X[65536,1024], Y[16384,1024] -------------------------------------------------------
+    r3 = args.rows or 65536
+    Xb, Yb = (torch.rand(r3, 1024, generator=g) < 0.1).to(dev), (torch.rand(16384, 1024, generator=g) < 0.1).to(dev)
+    n = r3 * 16384
+    for name, fn in (("C3_hamming", tpw.hamming_distances), ("C3_jaccard", tpw.jaccard_distances)):
+        if want(name):
+            entry(name, n, timeit(lambda: fn(Xb, Yb)), "popc_issue", n * 32 * 0.75, popc_peak, 4 * n)
+    del Xb, Yb
+    # ---- C4: X[131072,512], Y[16384,512] --------------------------------------------------------------
+    r4 = args.rows or 131072
+    X, Y = torch.randn(r4, 512, generator=g).to(dev), torch.randn(16384, 512, generator=g).to(dev)
+    n = r4 * 16384
+    for name, fn in (("C4_sqeuclidean", tpw.sqeuclidean_distances), ("C4_cosine", tpw.cosine_distances)):
+        if want(name):
+            entry(name, n, timeit(lambda: fn(X, Y)), "bf16 tensor (executed flops = 3 x algorithmic)", 3 * 2 * n * 512, bf16_peak, 4 * n)
+    if want("C4_sqeuclidean_simt"):
+        tpw.set_dot_engine("simt")
+        entry("C4_sqeuclidean_simt", n, timeit(lambda: tpw.sqeuclidean_distances(X, Y)), "fp32_issue", n * 512 * 2, fp32_peak, 4 * n)
+        tpw.set_dot_engine("auto")
+    del X, Y
+    # ---- C5: point clouds [64,1,8192,3] ------------------------------------------------------------------
+    P_ = torch.rand(64, 8192, 3, generator=g) * 2 - 1
+    Q_ = P_ + 0.05 * torch.randn(64, 8192, 3, generator=g)
+    x1, x2 = P_[:, None].to(dev).requires_grad_(True), Q_[:, None].to(dev).requires_grad_(True)
+    n = 64 * 8192 * 8192
+    if want("C5_hausdorff_fwd"):
+        with torch.no_grad():
+            entry("C5_hausdorff_fwd", n, timeit(lambda: tpw.directed_hausdorff_distances(x1, x2)), "fp32_issue (point pairs)", n * 9, fp32_peak, 0)
+    if want("C5_hausdorff_fwd_bwd"):
+        def hd():
+            x1.grad = None
+            x2.grad = None
+            tpw.directed_hausdorff_distances(x1, x2)[0].sum().backward()
+        entry("C5_hausdorff_fwd_bwd", n, timeit(hd), "fp32_issue (point pairs)", n * 9, fp32_peak, 0)
+    res["device_status"] = tpw.device_status()
+    print(json.dumps(res), flush=True)
+
+
 def main():
     global B, PAIRS_PER_STEP, BWD_BYTES_PER_LAUNCH
     ap = argparse.ArgumentParser()
@@ -339,6 +443,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batches", type=int, default=B,
                     help="batches per GPU (default 16 = the benchmark workload; smaller only for profiler captures)")
+    ap.add_argument("--suite", action="store_true",
+                    help="time every metric of the five benchmark configurations on one GPU (kernel time, inputs resident) "
+                         "and print one JSON object with throughputs and roofline fractions; not the driver's bench line")
+    ap.add_argument("--suite-only", default="", help="comma-separated subset of suite entries (for profiler captures)")
+    ap.add_argument("--rows", type=int, default=0, help="suite: cap N1 of the unbatched configurations (profiler captures)")
     ap.add_argument("--profile", action="store_true",
                     help="run only the warm-up and timed steps (for ncu captures); prints a reduced line that is not a bench value")
     args = ap.parse_args()
@@ -349,7 +458,9 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
+    if args.suite:
+        run_suite(args)
+    elif args.impl == "reference":
         run_reference(args, rank)
     else:
         run_ours(args, rank, world, local_rank)

@@ -126,22 +126,21 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, vo
     return false;
 }
 
-__device__ __forceinline__ float dot_epilogue(int epilogue, float dot, float n1, float n2, bool diag) {
-    switch (epilogue) {
-        case TPW_DOT_LINEAR: return dot;
-        case TPW_DOT_SQEUCLIDEAN: return diag ? 0.f : fmaxf(n1 + n2 - 2.f * dot, 0.f);
-        case TPW_DOT_EUCLIDEAN: return diag ? 0.f : sqrtf(fmaxf(n1 + n2 - 2.f * dot, 0.f));
-        default: {
-            const float denom = sqrtf(n1) * sqrtf(n2);
-            const float s = denom != 0.f ? __fdiv_rn(dot, denom) : dot;
-            if (epilogue == TPW_DOT_COSINE_SIM) return s;
-            float dist = 1.f - s;
-            if (epilogue == TPW_DOT_COSINE_DIST) dist = fminf(fmaxf(dist, 0.f), 2.f);
-            return dist;
-        }
-    }
+// n1, n2: squared row norms for the two distance epilogues, reciprocal row norms (0 for an all-zero
+// row, whose dot products are exactly 0 anyway) for the cosine family.
+template <int EPI>
+__device__ __forceinline__ float dot_epilogue(float dot, float n1, float n2, bool diag) {
+    if (EPI == TPW_DOT_LINEAR) return dot;
+    if (EPI == TPW_DOT_SQEUCLIDEAN) return diag ? 0.f : fmaxf(fmaf(-2.f, dot, n1 + n2), 0.f);
+    if (EPI == TPW_DOT_EUCLIDEAN) return diag ? 0.f : sqrtf(fmaxf(fmaf(-2.f, dot, n1 + n2), 0.f));
+    const float s = dot * (n1 * n2);
+    if (EPI == TPW_DOT_COSINE_SIM) return s;
+    const float dist = 1.f - s;
+    if (EPI == TPW_DOT_COSINE_DIST) return fminf(fmaxf(dist, 0.f), 2.f);
+    return dist;
 }
 
+template <int EPI, bool SELF>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_constant__ CUtensorMap map_xl,
                    const __grid_constant__ CUtensorMap map_yh, const __grid_constant__ CUtensorMap map_yl,
@@ -279,12 +278,13 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
                 if (P.vec_store && j0 + 32 <= P.N2) {
 #pragma unroll
                     for (int v = 0; v < 8; ++v) {
-                        const float4 nn = __ldg(reinterpret_cast<const float4 *>(n2p + j0) + v);
+                        const float4 nn = EPI == TPW_DOT_LINEAR ? make_float4(0.f, 0.f, 0.f, 0.f)
+                                                                : __ldg(reinterpret_cast<const float4 *>(n2p + j0) + v);
                         float4 o;
-                        o.x = dot_epilogue(P.epilogue, __uint_as_float(r[4 * v + 0]), n1, nn.x, P.self && i == j0 + 4 * v + 0);
-                        o.y = dot_epilogue(P.epilogue, __uint_as_float(r[4 * v + 1]), n1, nn.y, P.self && i == j0 + 4 * v + 1);
-                        o.z = dot_epilogue(P.epilogue, __uint_as_float(r[4 * v + 2]), n1, nn.z, P.self && i == j0 + 4 * v + 2);
-                        o.w = dot_epilogue(P.epilogue, __uint_as_float(r[4 * v + 3]), n1, nn.w, P.self && i == j0 + 4 * v + 3);
+                        o.x = dot_epilogue<EPI>(__uint_as_float(r[4 * v + 0]), n1, nn.x, SELF && i == j0 + 4 * v + 0);
+                        o.y = dot_epilogue<EPI>(__uint_as_float(r[4 * v + 1]), n1, nn.y, SELF && i == j0 + 4 * v + 1);
+                        o.z = dot_epilogue<EPI>(__uint_as_float(r[4 * v + 2]), n1, nn.z, SELF && i == j0 + 4 * v + 2);
+                        o.w = dot_epilogue<EPI>(__uint_as_float(r[4 * v + 3]), n1, nn.w, SELF && i == j0 + 4 * v + 3);
                         reinterpret_cast<float4 *>(orow + j0)[v] = o;
                     }
                 } else {
@@ -292,7 +292,7 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
                     for (int v = 0; v < 32; ++v) {
                         const long long j = j0 + v;
                         if (j < P.N2)
-                            orow[j] = dot_epilogue(P.epilogue, __uint_as_float(r[v]), n1, __ldg(n2p + j), P.self && i == j);
+                            orow[j] = dot_epilogue<EPI>(__uint_as_float(r[v]), n1, __ldg(n2p + j), SELF && i == j);
                     }
                 }
             }
@@ -311,9 +311,10 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
     }
 }
 
-// fp32 rows -> bf16 high/low parts (row pitch Dp, zero padded) and the fp32 squared norm; one warp per row
+// fp32 rows -> bf16 high/low parts (row pitch Dp, zero padded) and a per-row fp32 scalar: the
+// squared norm, or (recip != 0) the reciprocal norm with 0 for an all-zero row; one warp per row
 __global__ void split_rows_kernel(const float *__restrict__ x, __nv_bfloat16 *__restrict__ hi, __nv_bfloat16 *__restrict__ lo,
-                                  float *__restrict__ nsq, long long rows, long long D, long long Dp) {
+                                  float *__restrict__ nsq, long long rows, long long D, long long Dp, int recip) {
     const int lane = threadIdx.x & 31;
     const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
@@ -330,7 +331,14 @@ __global__ void split_rows_kernel(const float *__restrict__ x, __nv_bfloat16 *__
         }
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-        if (lane == 0) nsq[r] = s;
+        if (lane == 0) {
+            if (recip) {
+                const float nrm = sqrtf(s);
+                nsq[r] = nrm != 0.f ? __fdiv_rn(1.f, nrm) : 0.f;
+            } else {
+                nsq[r] = s;
+            }
+        }
     }
 }
 
@@ -410,9 +418,10 @@ extern "C" int tpw_dot_metric_forward_ws(int dtype, int epilogue, int engine,
     const int threads = 256;
     const long long cap = (long long)sm_count() * 16;
     long long blocks = (B * N1 * 32 + threads - 1) / threads;
-    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x1, xh, xl, n1, B * N1, D, L.Dp);
+    const int recip = (epilogue == TPW_DOT_COSINE_SIM || epilogue == TPW_DOT_COSINE_DIST || epilogue == TPW_DOT_ONE_MINUS_SIM) ? 1 : 0;
+    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x1, xh, xl, n1, B * N1, D, L.Dp, recip);
     blocks = (B * N2 * 32 + threads - 1) / threads;
-    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x2, yh, yl, n2, B * N2, D, L.Dp);
+    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x2, yh, yl, n2, B * N2, D, L.Dp, recip);
     TPW_LAUNCH_OK("split_rows_kernel");
 
     CUtensorMap mxh, mxl, myh, myl;
@@ -434,10 +443,27 @@ extern "C" int tpw_dot_metric_forward_ws(int dtype, int epilogue, int engine,
     P.vec_store = (N2 % 4 == 0 && aligned16(out)) ? 1 : 0;
     P.status = device_status_ptr();
     TPW_CHECK_ARG(P.tiles < (1ll << 40), "tpw_dot_metric_forward_ws: too many tiles");
-    TPW_CUDA_OK(cudaFuncSetAttribute(gemm_metric_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
     const long long nsm = sm_count();
     const unsigned grid = (unsigned)(P.tiles < nsm ? P.tiles : nsm);
-    gemm_metric_kernel<<<grid, kThreads, SMEM_ALLOC, s>>>(mxh, mxl, myh, myl, P);
+#define TPW_GEMM_LAUNCH(EPI, SELF)                                                                                        \
+    do {                                                                                                                  \
+        auto kern = gemm_metric_kernel<EPI, SELF>;                                                                        \
+        TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));                 \
+        kern<<<grid, kThreads, SMEM_ALLOC, s>>>(mxh, mxl, myh, myl, P);                                                   \
+    } while (0)
+    switch (epilogue) {
+        case TPW_DOT_LINEAR: TPW_GEMM_LAUNCH(TPW_DOT_LINEAR, false); break;
+        case TPW_DOT_COSINE_SIM: TPW_GEMM_LAUNCH(TPW_DOT_COSINE_SIM, false); break;
+        case TPW_DOT_COSINE_DIST: TPW_GEMM_LAUNCH(TPW_DOT_COSINE_DIST, false); break;
+        case TPW_DOT_ONE_MINUS_SIM: TPW_GEMM_LAUNCH(TPW_DOT_ONE_MINUS_SIM, false); break;
+        case TPW_DOT_SQEUCLIDEAN:
+            if (self) TPW_GEMM_LAUNCH(TPW_DOT_SQEUCLIDEAN, true); else TPW_GEMM_LAUNCH(TPW_DOT_SQEUCLIDEAN, false);
+            break;
+        default:
+            if (self) TPW_GEMM_LAUNCH(TPW_DOT_EUCLIDEAN, true); else TPW_GEMM_LAUNCH(TPW_DOT_EUCLIDEAN, false);
+            break;
+    }
+#undef TPW_GEMM_LAUNCH
     TPW_LAUNCH_OK("gemm_metric_kernel");
     return TPW_OK;
 }

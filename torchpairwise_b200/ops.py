@@ -757,7 +757,8 @@ class _LinearKernelFunction(torch.autograd.Function):
         in_dtype = x1.dtype
         cdt = _compute_dtype(in_dtype)
         x1c, x2c, unbatched = _batched(x1.to(cdt), x2.to(cdt), "linear_kernel")
-        out = _dot_forward_raw(x1c, x2c, _abi.DOT_LINEAR)
+        # the raw dot product has no norm to hide cancellation behind: always the exact fp32 tile
+        out = _dot_forward_raw(x1c, x2c, _abi.DOT_LINEAR, _abi.ENGINE_SIMT_FP32)
         ctx.save_for_backward(x1c, x2c)
         ctx.unbatched, ctx.in_dtype = unbatched, in_dtype
         return (out.squeeze(0) if unbatched else out).to(in_dtype)

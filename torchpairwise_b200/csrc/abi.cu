@@ -82,6 +82,19 @@ int make_tensor_map_3d(CUtensorMap *map, const void *base, int elem_bytes,
                        uint32_t box0, uint32_t box1, bool swizzle128) {
     encode_tiled_fn encode = resolve_encode_tiled();
     if (!encode) return fail(TPW_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    // The encoder is a driver call and needs a context bound to the calling thread.  A thread that
+    // has only ever been handed tensors (an autograd worker, say) may not have one yet: binding the
+    // runtime's current device does it.  Once per thread and device.
+    {
+        static thread_local int bound_device = -1;
+        int dev = 0;
+        TPW_CUDA_OK(cudaGetDevice(&dev));
+        if (bound_device != dev) {
+            TPW_CUDA_OK(cudaSetDevice(dev));
+            TPW_CUDA_OK(cudaFree(nullptr));
+            bound_device = dev;
+        }
+    }
     CUtensorMapDataType dt;
     switch (elem_bytes) {
         case 2: dt = CU_TENSOR_MAP_DATA_TYPE_UINT16; break;

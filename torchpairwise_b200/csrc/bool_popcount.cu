@@ -7,10 +7,11 @@
 // operation order of the reference's tensor compositions (each *, +, -, / rounded separately, no
 // FMA contraction), which makes the float32 output bit-identical.
 //
-// Tiling is the same as the CUDA-core L_p forward: 128 x 128 outputs per CTA, 8 x 8 per thread,
-// operand tiles of 128 rows x 32 words staged by TMA with the 128-byte swizzle (three-stage
-// mbarrier ring), conflict-free 128-bit shared loads.  Within a 16-byte chunk three of the four
-// AND words go through a carry-save adder first, so four words cost three POPCs.
+// Tiling follows the CUDA-core L_p forward: 64 x 128 outputs per CTA of 256 threads, 4 x 8 per
+// thread (two CTAs per SM), operand tiles of 64 / 128 rows x 32 words staged by TMA with the
+// 128-byte swizzle (three-stage mbarrier ring), conflict-free 128-bit shared loads.  POPC issues at
+// 16 lanes per clock per SM, a quarter of the logic rate, so eight AND words at a time go through
+// a 7:3 carry-save adder tree (four 3-input logic pairs) and cost four POPCs instead of eight.
 #include "common.cuh"
 
 namespace tpw {
@@ -18,11 +19,13 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kStages = 3;
-constexpr int R = 8;
-constexpr int TILE = 128;
+constexpr int RI = 4, RJ = 8;
+constexpr int TILE_I = 16 * RI;  // 64 rows of x1
+constexpr int TILE_J = 16 * RJ;  // 128 rows of x2
 constexpr int KC = 32; // words per 128-byte chunk row
-constexpr int TILE_BYTES = TILE * 128;
-constexpr int OFF_BAR = kStages * 2 * TILE_BYTES;
+constexpr int XT_BYTES = TILE_I * 128, YT_BYTES = TILE_J * 128;
+constexpr int STAGE_BYTES = XT_BYTES + YT_BYTES;
+constexpr int OFF_BAR = kStages * STAGE_BYTES;
 constexpr int SMEM_BYTES = OFF_BAR + kStages * 8;
 constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
 
@@ -33,6 +36,7 @@ struct BoolParams {
     long long B, N1, N2, D, W;
     long long tiles_i, tiles_j;
     int metric;
+    float inv_d; // 1/D when D is a power of two (then x * inv_d == x / D exactly), else 0
     int *status;
 };
 
@@ -56,7 +60,7 @@ __global__ void bitpack_kernel(const uint8_t *__restrict__ src, uint32_t *__rest
     }
 }
 
-__device__ __forceinline__ float bool_epilogue(int metric, int n11, int a, int b, int D) {
+__device__ __forceinline__ float bool_epilogue(int metric, int n11, int a, int b, int D, float inv_d) {
     const int nxor_i = a + b - 2 * n11;
     const int nor_i = a + b - n11;
     const float fand = (float)n11, fxor = (float)nxor_i, f_or = (float)nor_i;
@@ -67,8 +71,9 @@ __device__ __forceinline__ float bool_epilogue(int metric, int n11, int a, int b
         case TPW_BOOL_XOR_SUM:
         case TPW_BOOL_NE_SUM: return fxor;
         case TPW_BOOL_EQ_SUM: return feq;
-        case TPW_BOOL_EQ_MEAN: return __fdiv_rn(feq, fD);
-        case TPW_BOOL_NE_MEAN: return __fdiv_rn(fxor, fD);
+        // dividing by a power of two is exact, and so is multiplying by its reciprocal
+        case TPW_BOOL_EQ_MEAN: return inv_d != 0.f ? __fmul_rn(feq, inv_d) : __fdiv_rn(feq, fD);
+        case TPW_BOOL_NE_MEAN: return inv_d != 0.f ? __fmul_rn(fxor, inv_d) : __fdiv_rn(fxor, fD);
         case TPW_BOOL_JACCARD: return f_or != 0.f ? __fdiv_rn(fxor, f_or) : 0.f;
         case TPW_BOOL_KULSINSKI: return __fdiv_rn(__fadd_rn(__fsub_rn(fxor, fand), fD), __fadd_rn(fxor, fD));
         case TPW_BOOL_KULCZYNSKI1: return __fdiv_rn(fand, fxor);
@@ -92,6 +97,12 @@ __device__ __forceinline__ float bool_epilogue(int metric, int n11, int a, int b
     }
 }
 
+// sum (weight 1) and carry (weight 2) of three bit-vectors
+__device__ __forceinline__ void csa(uint32_t a, uint32_t b, uint32_t c, uint32_t &sum, uint32_t &carry) {
+    sum = a ^ b ^ c;
+    carry = (a & b) | (c & (a ^ b));
+}
+
 template <bool USE_TMA>
 __global__ void __launch_bounds__(kThreads, 2)
 bool_popcount_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constant__ CUtensorMap map2,
@@ -107,16 +118,23 @@ bool_popcount_kernel(const __grid_constant__ CUtensorMap map1, const __grid_cons
     tile /= P.tiles_j;
     const long long tix = tile % P.tiles_i;
     const long long b = tile / P.tiles_i;
-    const long long i0 = tix * TILE, j0 = tjx * TILE;
+    const long long i0 = tix * TILE_I, j0 = tjx * TILE_J;
     const uint32_t *x1 = P.x1 + b * P.N1 * P.W;
     const uint32_t *x2 = P.x2 + b * P.N2 * P.W;
     const int nchunks = (int)((P.W + KC - 1) / KC);
 
-    int acc[R][R];
+    int acc[RI][RJ];
 #pragma unroll
-    for (int a = 0; a < R; ++a)
+    for (int a = 0; a < RI; ++a)
 #pragma unroll
-        for (int c = 0; c < R; ++c) acc[a][c] = 0;
+        for (int c = 0; c < RJ; ++c) acc[a][c] = 0;
+
+    auto issue = [&](int chunk) {
+        const int st = chunk % kStages;
+        mbar_expect_tx(&full[st], STAGE_BYTES);
+        tma_load_3d(smem + st * STAGE_BYTES, &map1, &full[st], chunk * KC, (int)i0, (int)b);
+        tma_load_3d(smem + st * STAGE_BYTES + XT_BYTES, &map2, &full[st], chunk * KC, (int)j0, (int)b);
+    };
 
     if (USE_TMA) {
         if (tid == 0) {
@@ -127,13 +145,8 @@ bool_popcount_kernel(const __grid_constant__ CUtensorMap map1, const __grid_cons
             tma_prefetch_descriptor(&map2);
         }
         __syncthreads();
-        if (tid == 0) {
-            for (int c = 0; c < kStages - 1 && c < nchunks; ++c) {
-                mbar_expect_tx(&full[c], 2 * TILE_BYTES);
-                tma_load_3d(smem + (2 * c) * TILE_BYTES, &map1, &full[c], c * KC, (int)i0, (int)b);
-                tma_load_3d(smem + (2 * c + 1) * TILE_BYTES, &map2, &full[c], c * KC, (int)j0, (int)b);
-            }
-        }
+        if (tid == 0)
+            for (int c = 0; c < kStages - 1 && c < nchunks; ++c) issue(c);
     }
 
     int failed = 0;
@@ -144,45 +157,45 @@ bool_popcount_kernel(const __grid_constant__ CUtensorMap map1, const __grid_cons
                 if (tid == 0 && P.status) atomicCAS(P.status, 0, (3 << 16) | 1);
                 return;
             }
-            const int nxt = t + kStages - 1;
-            if (tid == 0 && nxt < nchunks) {
-                const int ns = nxt % kStages;
-                mbar_expect_tx(&full[ns], 2 * TILE_BYTES);
-                tma_load_3d(smem + (2 * ns) * TILE_BYTES, &map1, &full[ns], nxt * KC, (int)i0, (int)b);
-                tma_load_3d(smem + (2 * ns + 1) * TILE_BYTES, &map2, &full[ns], nxt * KC, (int)j0, (int)b);
-            }
+            if (tid == 0 && t + kStages - 1 < nchunks) issue(t + kStages - 1);
             stage = t % kStages;
             if (!mbar_wait_bounded(&full[stage], (uint32_t)((t / kStages) & 1))) failed = 1;
         } else {
             stage = 0;
             __syncthreads();
-            for (int e = tid; e < 2 * TILE * KC; e += kThreads) {
-                const int which = e / (TILE * KC), r = (e / KC) % TILE, kk = e % KC;
+            for (int e = tid; e < (TILE_I + TILE_J) * KC; e += kThreads) {
+                const int which = e >= TILE_I * KC, el = which ? e - TILE_I * KC : e;
+                const int r = el / KC, kk = el % KC;
                 const long long row = (which ? j0 : i0) + r, q = (long long)t * KC + kk;
                 const long long nrows = which ? P.N2 : P.N1;
                 const uint32_t *src = which ? x2 : x1;
                 const uint32_t v = (row < nrows && q < P.W) ? src[row * P.W + q] : 0u;
-                *reinterpret_cast<uint32_t *>(smem + which * TILE_BYTES + swz128(r, kk / 4) + (kk % 4) * 4) = v;
+                *reinterpret_cast<uint32_t *>(smem + (which ? XT_BYTES : 0) + swz128(r, kk / 4) + (kk % 4) * 4) = v;
             }
             __syncthreads();
         }
-        const unsigned char *xs = smem + (2 * stage) * TILE_BYTES;
-        const unsigned char *ys = xs + TILE_BYTES;
+        const unsigned char *xs = smem + stage * STAGE_BYTES;
+        const unsigned char *ys = xs + XT_BYTES;
 #pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
-            uint4 xa[R];
+        for (int c = 0; c < 8; c += 2) {
+            uint4 xa[RI], xb[RI];
 #pragma unroll
-            for (int r = 0; r < R; ++r)
+            for (int r = 0; r < RI; ++r) {
                 xa[r] = *reinterpret_cast<const uint4 *>(xs + (ti + 16 * r) * 128u + ((c ^ (ti & 7u)) << 4));
+                xb[r] = *reinterpret_cast<const uint4 *>(xs + (ti + 16 * r) * 128u + (((c + 1) ^ (ti & 7u)) << 4));
+            }
 #pragma unroll
-            for (int rj = 0; rj < R; ++rj) {
-                const uint4 yb = *reinterpret_cast<const uint4 *>(ys + (tj + 16 * rj) * 128u + ((c ^ (tj & 7u)) << 4));
+            for (int rj = 0; rj < RJ; ++rj) {
+                const uint4 ya = *reinterpret_cast<const uint4 *>(ys + (tj + 16 * rj) * 128u + ((c ^ (tj & 7u)) << 4));
+                const uint4 yb = *reinterpret_cast<const uint4 *>(ys + (tj + 16 * rj) * 128u + (((c + 1) ^ (tj & 7u)) << 4));
 #pragma unroll
-                for (int ri = 0; ri < R; ++ri) {
-                    const uint32_t a0 = xa[ri].x & yb.x, a1 = xa[ri].y & yb.y, a2 = xa[ri].z & yb.z, a3 = xa[ri].w & yb.w;
-                    const uint32_t sum = a0 ^ a1 ^ a2;                      // carry-save adder: ones
-                    const uint32_t carry = (a0 & a1) | (a2 & (a0 ^ a1));    // twos
-                    acc[ri][rj] += __popc(sum) + 2 * __popc(carry) + __popc(a3);
+                for (int ri = 0; ri < RI; ++ri) {
+                    uint32_t s1, c1, s2, c2, s3, c3, s4, c4;
+                    csa(xa[ri].x & ya.x, xa[ri].y & ya.y, xa[ri].z & ya.z, s1, c1);
+                    csa(xa[ri].w & ya.w, xb[ri].x & yb.x, xb[ri].y & yb.y, s2, c2);
+                    csa(s1, s2, xb[ri].z & yb.z, s3, c3);
+                    csa(c1, c2, c3, s4, c4);
+                    acc[ri][rj] += __popc(s3) + __popc(xb[ri].w & yb.w) + 2 * __popc(s4) + 4 * __popc(c4);
                 }
             }
         }
@@ -196,22 +209,22 @@ bool_popcount_kernel(const __grid_constant__ CUtensorMap map1, const __grid_cons
 
     float *out = P.out + b * P.N1 * P.N2;
     const int32_t *pop1 = P.pop1 + b * P.N1, *pop2 = P.pop2 + b * P.N2;
-    int pb[R];
+    int pb[RJ];
 #pragma unroll
-    for (int rj = 0; rj < R; ++rj) {
+    for (int rj = 0; rj < RJ; ++rj) {
         const long long j = j0 + tj + 16 * rj;
         pb[rj] = j < P.N2 ? pop2[j] : 0;
     }
 #pragma unroll
-    for (int ri = 0; ri < R; ++ri) {
+    for (int ri = 0; ri < RI; ++ri) {
         const long long i = i0 + ti + 16 * ri;
         if (i >= P.N1) continue;
         const int pa = pop1[i];
 #pragma unroll
-        for (int rj = 0; rj < R; ++rj) {
+        for (int rj = 0; rj < RJ; ++rj) {
             const long long j = j0 + tj + 16 * rj;
             if (j >= P.N2) continue;
-            out[i * P.N2 + j] = bool_epilogue(P.metric, acc[ri][rj], pa, pb[rj], (int)P.D);
+            out[i * P.N2 + j] = bool_epilogue(P.metric, acc[ri][rj], pa, pb[rj], (int)P.D, P.inv_d);
         }
     }
 }
@@ -256,8 +269,9 @@ extern "C" int tpw_bool_metric_forward(int metric, const uint32_t *x1_words, con
     P.x1 = x1_words; P.x2 = x2_words; P.pop1 = x1_popcount; P.pop2 = x2_popcount; P.out = out;
     P.B = B; P.N1 = N1; P.N2 = N2; P.D = D; P.W = words_per_row;
     P.metric = metric;
-    P.tiles_i = (N1 + TILE - 1) / TILE;
-    P.tiles_j = (N2 + TILE - 1) / TILE;
+    P.inv_d = (D & (D - 1)) == 0 ? 1.0f / (float)D : 0.f;
+    P.tiles_i = (N1 + TILE_I - 1) / TILE_I;
+    P.tiles_j = (N2 + TILE_J - 1) / TILE_J;
     const long long tiles = B * P.tiles_i * P.tiles_j;
     TPW_CHECK_ARG(tiles < (1ll << 31), "tpw_bool_metric_forward: too many tiles");
     TPW_CHECK_ARG(N1 < (1ll << 31) && N2 < (1ll << 31) && B < (1ll << 31) && words_per_row < (1ll << 31),
@@ -269,9 +283,9 @@ extern "C" int tpw_bool_metric_forward(int metric, const uint32_t *x1_words, con
     memset(&m1, 0, sizeof(m1));
     memset(&m2, 0, sizeof(m2));
     if (tma_ok) {
-        int st = make_tensor_map_3d(&m1, x1_words, 4, words_per_row, N1, B, KC, TILE, true);
+        int st = make_tensor_map_3d(&m1, x1_words, 4, words_per_row, N1, B, KC, TILE_I, true);
         if (st != TPW_OK) return st;
-        st = make_tensor_map_3d(&m2, x2_words, 4, words_per_row, N2, B, KC, TILE, true);
+        st = make_tensor_map_3d(&m2, x2_words, 4, words_per_row, N2, B, KC, TILE_J, true);
         if (st != TPW_OK) return st;
         TPW_CUDA_OK(cudaFuncSetAttribute(bool_popcount_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
         bool_popcount_kernel<true><<<(unsigned)tiles, kThreads, SMEM_ALLOC, s>>>(m1, m2, P);

@@ -55,3 +55,24 @@ def test_argument_errors_are_reported_before_any_launch():
     assert lib.tpw_last_error() == b""
     with pytest.raises(_abi.TpwError, match="status 1"):
         _abi.check(lib.tpw_prf_div_forward(0, 9, None, None, None, 4, None), "tpw_prf_div_forward")
+
+
+def test_cpp_host_layer_registers_the_reference_schemas():
+    """Stand-alone load on a machine without a GPU: the schemas exist with the reference's
+    signatures and CUDA/AutogradCUDA kernels are attached (nothing is executed)."""
+    import subprocess, sys
+    code = (
+        "import torch, torchpairwise_b200 as t\n"
+        "t.load_torch_ops()\n"
+        "s = {str(x.name): str(x) for x in torch._C._jit_get_all_schemas() if x.name.startswith('torchpairwise::')}\n"
+        "assert s['torchpairwise::minkowski_distances'] in ('torchpairwise::minkowski_distances(Tensor x1, Tensor? x2=None, float p=2) -> Tensor', 'torchpairwise::minkowski_distances(Tensor x1, Tensor? x2=None, float p=2.) -> Tensor'), s['torchpairwise::minkowski_distances']\n"
+        "assert 'Generator? generator=None' in s['torchpairwise::cdist'] and 'str metric=\\\"minkowski\\\"' in s['torchpairwise::cdist']\n"
+        "assert len(s) >= 38, len(s)\n"
+        "tab = torch._C._dispatch_dump_table('torchpairwise::euclidean_distances')\n"
+        "assert 'AutogradCUDA' in tab and 'tpw_torch.cpp' in tab\n"
+        "tab = torch._C._dispatch_dump_table('torchpairwise::pwxor_sum')\n"
+        "assert 'CUDA' in tab\n"
+        "print('ok')\n"
+    )
+    r = subprocess.run([sys.executable, "-c", code], cwd=str(ROOT), capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr

@@ -1,0 +1,141 @@
+"""The C++ host layer: `torch.ops.torchpairwise.*` with the reference's own schemas.
+
+With the reference's CPU build loaded in the same process the very same call goes to the reference
+for CPU tensors and to the sm_100a kernels for CUDA tensors, so parity is checked operator by
+operator with nothing in between.  Stand-alone registration is checked in a child process.
+"""
+import math
+import subprocess
+import sys
+import warnings
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+REF = ROOT / "oracle" / "_ref" / "torchpairwise_ref.so"
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def T():
+    if not REF.exists():
+        pytest.skip("oracle/_ref is not built on this machine")
+    torch.ops.load_library(str(REF))  # reference first: its schemas are reused
+    import torchpairwise_b200
+    torchpairwise_b200.load_torch_ops()
+    yield torch.ops.torchpairwise
+    assert torchpairwise_b200.device_status() == 0
+
+
+FLOAT_OPS = [
+    ("euclidean_distances", {}), ("manhattan_distances", {}), ("chebyshev_distances", {}), ("sqeuclidean_distances", {}),
+    ("minkowski_distances", {"p": 3.0}), ("minkowski_distances", {"p": 1.5}), ("cosine_similarity", {}),
+    ("cosine_distances", {}), ("correlation_distances", {}), ("l1_distances", {}), ("l2_distances", {}),
+    ("lp_distances", {"p": 2.5}), ("linf_distances", {}), ("cityblock_distances", {}),
+]
+
+
+@pytest.mark.parametrize("name,kw", FLOAT_OPS, ids=lambda v: str(v))
+@pytest.mark.parametrize("shape", [((37, 19), (23, 19)), ((2, 140, 70), (2, 131, 70))])
+def test_same_call_reference_on_cpu_kernels_on_cuda(T, name, kw, shape):
+    g = torch.Generator().manual_seed(11)
+    x1 = torch.randn(*shape[0], generator=g)
+    x2 = torch.randn(*shape[1], generator=g)
+    up = torch.randn(*shape[0][:-1], shape[1][-2], generator=g)
+    a, b = x1.clone().requires_grad_(True), x2.clone().requires_grad_(True)
+    ref = getattr(T, name)(a, b, **kw)
+    ref.backward(up)
+    c, d = x1.cuda().requires_grad_(True), x2.cuda().requires_grad_(True)
+    out = getattr(T, name)(c, d, **kw)
+    out.backward(up.cuda())
+    torch.testing.assert_close(out.cpu(), ref, rtol=1e-4, atol=1e-5)
+    scale = 10 * max(1.0, float(a.grad.abs().max()))
+    torch.testing.assert_close(c.grad.cpu(), a.grad, rtol=1e-4, atol=1e-5 * scale)
+    torch.testing.assert_close(d.grad.cpu(), b.grad, rtol=1e-4, atol=1e-5 * scale)
+
+
+def test_weighted_internal_and_boolean_ops(T):
+    g = torch.Generator().manual_seed(12)
+    x1, x2 = torch.randn(9, 9, generator=g), torch.randn(7, 9, generator=g)
+    w = torch.rand(9, generator=g) + 0.3
+    up = torch.randn(9, 7, generator=g)
+    for p in (3.0, 1.0, math.inf):
+        a, b, ww = x1.clone().requires_grad_(True), x2.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        ref = T.wminkowski_distances(a, b, p, ww)
+        ref.backward(up)
+        c, d, wc = x1.cuda().requires_grad_(True), x2.cuda().requires_grad_(True), w.cuda().requires_grad_(True)
+        out = T.wminkowski_distances(c, d, p, wc)
+        out.backward(up.cuda())
+        torch.testing.assert_close(out.cpu(), ref, rtol=1e-4, atol=1e-5)
+        for got, want in ((c.grad, a.grad), (d.grad, b.grad), (wc.grad, ww.grad)):
+            torch.testing.assert_close(got.cpu(), want, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(T._ppminkowski(x1.cuda(), x2.cuda(), 3.0).cpu(), T._ppminkowski(x1, x2, 3.0), rtol=1e-4, atol=1e-5)
+    xb, yb = torch.rand(50, 77, generator=g) < 0.3, torch.rand(41, 77, generator=g) < 0.3
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        for name in ("hamming", "jaccard", "kulsinski", "kulczynski1", "yule", "dice", "rogerstanimoto", "russellrao",
+                     "sokalmichener", "sokalsneath"):
+            ref = getattr(T, name + "_distances")(xb, yb)
+            out = getattr(T, name + "_distances")(xb.cuda(), yb.cuda()).cpu()
+            assert bool(((out == ref) | (out.isnan() & ref.isnan())).all()), name
+        for name in ("pwand_sum", "pwor_sum", "pwxor_sum", "pweq_sum", "pwne_sum", "pweq_mean", "pwne_mean"):
+            assert torch.equal(getattr(T, name)(xb.cuda(), yb.cuda()).cpu(), getattr(T, name)(xb, yb)), name
+        xi, yi = torch.randint(0, 3, (12, 20), generator=g), torch.randint(0, 3, (9, 20), generator=g)
+        assert torch.equal(T.hamming_distances(xi.cuda(), yi.cuda()).cpu(), T.hamming_distances(xi, yi))
+        assert torch.equal(T.jaccard_distances(xi.cuda(), yi.cuda()).cpu(), T.jaccard_distances(xi, yi))
+
+
+def test_hausdorff_and_cdist_dispatcher(T):
+    g = torch.Generator().manual_seed(13)
+    s1, s2 = torch.rand(2, 3, 60, 3, generator=g), torch.rand(2, 2, 45, 3, generator=g)
+    up = torch.randn(2, 3, 2, generator=g)
+    a, b = s1.clone().requires_grad_(True), s2.clone().requires_grad_(True)
+    ref, r1, r2 = T.directed_hausdorff_distances(a, b)
+    ref.backward(up)
+    c, d = s1.cuda().requires_grad_(True), s2.cuda().requires_grad_(True)
+    out, i1, i2 = T.directed_hausdorff_distances(c, d)
+    out.backward(up.cuda())
+    assert torch.equal(out.cpu(), ref) and torch.equal(i1.cpu(), r1) and torch.equal(i2.cpu(), r2)
+    torch.testing.assert_close(c.grad.cpu(), a.grad, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(d.grad.cpu(), b.grad, rtol=1e-4, atol=1e-5)
+    x1, x2 = torch.randn(20, 8, generator=g), torch.randn(17, 8, generator=g)
+    for metric, kw in (("euclidean", {}), ("minkowski", {"p": 3.0}), ("cosine", {}), ("manhattan", {}), ("sqeuclidean", {}),
+                       ("chebyshev", {}), ("correlation", {})):
+        torch.testing.assert_close(T.cdist(x1.cuda(), x2.cuda(), metric, **kw).cpu(), T.cdist(x1, x2, metric, **kw),
+                                   rtol=1e-4, atol=1e-5)
+    assert torch.equal(T.cdist(s1.cuda(), s2.cuda(), "directed_hausdorff").cpu(), ref.detach())
+    with pytest.raises(TypeError, match="incompatible arguments p"):
+        T.cdist(x1.cuda(), x2.cuda(), "euclidean", p=2.0)
+    with pytest.raises(RuntimeError, match="unkown distance metric"):
+        T.cdist(x1.cuda(), x2.cuda(), "nope")
+    with pytest.raises(NotImplementedError):
+        T.cdist(x1.cuda(), x2.cuda(), "canberra")
+
+
+def test_cpp_layer_agrees_with_python_layer(T):
+    import torchpairwise_b200 as tpw
+    g = torch.Generator().manual_seed(14)
+    x1, x2 = torch.randn(300, 64, generator=g).cuda(), torch.randn(200, 64, generator=g).cuda()
+    for name in ("euclidean_distances", "manhattan_distances", "cosine_distances", "correlation_distances", "sqeuclidean_distances"):
+        assert torch.equal(getattr(T, name)(x1, x2), getattr(tpw, name)(x1, x2)), name
+    assert torch.equal(T.minkowski_distances(x1, x2, 3.0), tpw.minkowski_distances(x1, x2, 3.0))
+
+
+def test_stand_alone_registration():
+    code = (
+        "import torch, torchpairwise_b200 as t\n"
+        "t.load_torch_ops()\n"
+        "T = torch.ops.torchpairwise\n"
+        "x = torch.randn(40, 16, device='cuda', requires_grad=True); y = torch.randn(30, 16, device='cuda')\n"
+        "o = T.minkowski_distances(x, y, 3.0); o.sum().backward()\n"
+        "assert torch.allclose(o, torch.cdist(x, y, p=3.0), rtol=1e-4, atol=1e-5)\n"
+        "assert x.grad.shape == x.shape and torch.isfinite(x.grad).all()\n"
+        "assert torch.equal(T.jaccard_distances(x > 0, y > 0), t.jaccard_distances(x > 0, y > 0))\n"
+        "assert torch.equal(T.cdist(x, y, 'manhattan'), t.manhattan_distances(x, y))\n"
+        "print('standalone ok')\n"
+    )
+    r = subprocess.run([sys.executable, "-c", code], cwd=str(ROOT), capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "standalone ok" in r.stdout, r.stdout + r.stderr

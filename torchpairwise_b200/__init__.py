@@ -4,7 +4,7 @@ The module mirrors the reference's Python surface (``torchpairwise/__init__.py``
 ``torchpairwise/ops``): the same function names with the same arguments, backed by hand-written
 CUDA kernels behind the C ABI of ``include/tpw_b200.h``.  CUDA tensors only.
 """
-from ._abi import TpwError, device_status, lib, measure_issue_peak
+from ._abi import LIB_PATH, TpwError, device_status, lib, measure_issue_peak
 from .cpdist import cdist, pdist
 from .ops import (
     _directed_hausdorff,
@@ -49,6 +49,21 @@ from .ops import (
 )
 
 __version__ = "0.1.0"
+
+TORCH_OPS_LIBRARY = LIB_PATH.parent / "libtpw_b200_torch.so"
+
+
+def load_torch_ops() -> str:
+    """Register the C++ host layer with the torch dispatcher: afterwards
+    ``torch.ops.torchpairwise.<op>`` (the reference's own operator names and schemas) runs the
+    sm_100a kernels for CUDA tensors.  If the reference extension is installed, load it first: its
+    schemas are reused and it keeps serving CPU tensors.  Returns the library path."""
+    import torch
+
+    if not TORCH_OPS_LIBRARY.exists():
+        raise ImportError(f"{TORCH_OPS_LIBRARY} is missing; run `python torchpairwise_b200/build.py`")
+    torch.ops.load_library(str(TORCH_OPS_LIBRARY))
+    return str(TORCH_OPS_LIBRARY)
 
 
 def has_ops() -> bool:

@@ -94,9 +94,40 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+TORCH_SRC = CSRC / "torch" / "tpw_torch.cpp"
+TORCH_LIB_PATH = LIB_DIR / "libtpw_b200_torch.so"
+
+
+def build_torch_ops(force: bool = False) -> Path:
+    """Compile the C++ host layer (``csrc/torch/tpw_torch.cpp``: the ``torchpairwise::`` operator
+    registrations on top of the C ABI) with g++ against the installed torch, linked to
+    ``libtpw_b200.so``; returns the path of ``libtpw_b200_torch.so``."""
+    build_library()
+    deps = [TORCH_SRC, *sorted(INCLUDE.glob("*.h")), Path(__file__)]
+    if not force and TORCH_LIB_PATH.exists() and all(p.stat().st_mtime <= TORCH_LIB_PATH.stat().st_mtime for p in deps):
+        return TORCH_LIB_PATH
+    import torch
+    from torch.utils import cpp_extension as ce
+    tdir = Path(torch.__file__).resolve().parent
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    cxx = os.environ.get("CXX", "g++")
+    tmp = TORCH_LIB_PATH.with_suffix(".so.tmp")
+    cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-w", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           *[f"-I{p}" for p in ce.include_paths()], f"-I{cuda_home}/include", f"-I{INCLUDE}",
+           str(TORCH_SRC), "-o", str(tmp),
+           f"-L{tdir / 'lib'}", "-ltorch", "-ltorch_cpu", "-lc10", "-ltorch_cuda", "-lc10_cuda",
+           f"-L{LIB_DIR}", "-ltpw_b200", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{tdir / 'lib'}"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"building the torch host layer failed:\n{r.stdout[-3000:]}\n{r.stderr[-3000:]}")
+    os.replace(tmp, TORCH_LIB_PATH)
+    return TORCH_LIB_PATH
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--force", action="store_true")
     ap.add_argument("-v", "--verbose", action="store_true", help="print ptxas resource usage")
     a = ap.parse_args()
     print(build_library(force=a.force, verbose=a.verbose))
+    print(build_torch_ops(force=a.force))

@@ -1,0 +1,677 @@
+// C++ host layer: the reference's operator schemas (namespace `torchpairwise`) bound to the C ABI.
+//
+// Loading this library makes `torch.ops.torchpairwise.<op>` run the sm_100a kernels for CUDA tensors.
+// It works in two modes:
+//   * next to the reference extension (loaded first): the schemas already exist, the reference keeps
+//     serving CPU tensors, and the AutogradCUDA kernels registered here take over CUDA tensors --
+//     including the public ops that the reference implements with at::cdist / matmul
+//     (OPS/pairwise_metrics.cpp:30,48,121,167,203,305) and the string dispatcher `cdist`
+//     (OPS/cpdist.cpp:149-231), whose body calls the reference functors directly;
+//   * stand-alone: the schemas are defined here with the reference's exact strings
+//     (OPS/pairwise_metrics.h:73-425, OPS/ppminkowski.cpp:31-38, OPS/wminkowski.cpp:33-40,
+//     OPS/hausdorff.cpp:34-39, OPS/pairwise_binary.cpp:151-159, OPS/cpdist.cpp:248-251).
+// Each body does what the reference's kernel wrappers do -- checks, contiguous(), leading batch
+// dimension, allocation, current stream -- and then calls the C ABI.  Nothing here computes on the
+// CPU; a CPU tensor reaching one of these kernels is an error.
+#include <ATen/ATen.h>
+#include <ATen/core/dispatch/Dispatcher.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/autograd.h>
+#include <torch/library.h>
+
+#include <cmath>
+#include <limits>
+
+#include "../../../include/tpw_b200.h"
+
+namespace {
+
+using at::Tensor;
+using torch::autograd::AutogradContext;
+using torch::autograd::variable_list;
+using OptTensor = c10::optional<Tensor>;
+
+#define TPW_CALL(expr)                                                        \
+    do {                                                                      \
+        int status_ = (expr);                                                 \
+        TORCH_CHECK(status_ == TPW_OK, #expr " failed: ", tpw_last_error());  \
+    } while (0)
+
+int code_of(const Tensor &t) { return t.scalar_type() == at::kDouble ? TPW_F64 : TPW_F32; }
+tpw_stream_t stream_of(const Tensor &t) { return c10::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
+
+at::ScalarType compute_type(at::ScalarType t) {
+    if (t == at::kHalf || t == at::kBFloat16) return at::kFloat;
+    TORCH_CHECK(t == at::kFloat || t == at::kDouble, "expected a floating point tensor, got ", t);
+    return t;
+}
+
+void require_cuda(const Tensor &t) {
+    TORCH_CHECK(t.is_cuda(), "torchpairwise (B200 build) runs on CUDA tensors only (no CPU path); got a tensor on ", t.device());
+}
+
+// OPS/pairwise_metrics.h:10-67
+std::pair<Tensor, Tensor> check_pairwise_inputs(const char *name, const Tensor &x1, const OptTensor &x2,
+                                                bool boolean = false, bool sets = false) {
+    const int64_t lo = sets ? 3 : 2;
+    const bool unbatched = x1.dim() == lo;
+    TORCH_CHECK(unbatched || x1.dim() == lo + 1, "x1 must be ", lo, "D tensor (unbatched) or ", lo + 1, "D tensor (batched)");
+    if (x2.has_value()) {
+        const Tensor &b = x2.value();
+        TORCH_CHECK(unbatched || b.dim() == lo + 1, "x2 must be ", lo, "D tensor (unbatched) or ", lo + 1, "D tensor (batched)");
+        const int64_t f = unbatched ? lo - 1 : lo;
+        TORCH_CHECK(b.dim() > f && x1.size(f) == b.size(f), "x1 and x2 must have same number of features. Got: x1.size(", f,
+                    ")=", x1.size(f), ", x2.size(", f, ")=", b.dim() > f ? b.size(f) : -1);
+    }
+    if (boolean) {
+        if (x1.scalar_type() != at::kBool || (x2.has_value() && x2->scalar_type() != at::kBool))
+            TORCH_WARN("Data was converted to ", at::kBool, " for metric ", name);
+        Tensor a = x1.to(at::kBool);
+        return {a, x2.has_value() ? x2->to(at::kBool) : a};
+    }
+    return {x1, x2.has_value() ? x2.value() : x1};
+}
+
+struct Prepared {
+    Tensor a, b;
+    bool unbatched;
+    int64_t B, N1, N2, D;
+};
+
+// contiguous() + leading batch dimension (e.g. OPS/cuda/ppminkowski_kernel.cu:70-90)
+Prepared prepare(const Tensor &x1, const Tensor &x2, at::ScalarType dt) {
+    require_cuda(x1);
+    require_cuda(x2);
+    TORCH_CHECK(x1.get_device() == x2.get_device(), "Expected all tensors to be on the same device");
+    const bool unbatched = x1.dim() == 2;
+    TORCH_CHECK(unbatched || x1.dim() == 3, "x1 must be 2-D (unbatched) or 3-D (batched) tensor.");
+    TORCH_CHECK(x2.dim() == x1.dim(), "x2 must be 2-D (unbatched) or 3-D (batched) tensor.");
+    TORCH_CHECK(unbatched || x1.size(0) == x2.size(0), "batch_size of x1 and x2 do not match.");
+    TORCH_CHECK(x1.size(-1) == x2.size(-1), "feature dimension of x1 and x2 do not match.");
+    Prepared p;
+    p.a = x1.to(dt).contiguous();
+    p.b = x2.is_same(x1) ? p.a : x2.to(dt).contiguous();
+    p.unbatched = unbatched;
+    if (unbatched) {
+        p.a = p.a.unsqueeze(0);
+        p.b = p.b.unsqueeze(0);
+    }
+    p.B = p.a.size(0); p.N1 = p.a.size(1); p.N2 = p.b.size(1); p.D = p.a.size(2);
+    return p;
+}
+
+Tensor finish(Tensor out, bool unbatched, at::ScalarType dt) {
+    if (unbatched) out = out.squeeze(0);
+    return out.scalar_type() == dt ? out : out.to(dt);
+}
+
+Tensor lp_forward(const Prepared &p, const Tensor *w, double pw, double exponent) {
+    Tensor out = at::empty({p.B, p.N1, p.N2}, p.a.options());
+    if (p.D == 0) return out.zero_();
+    TPW_CALL(tpw_lp_forward(code_of(p.a), p.a.data_ptr(), p.b.data_ptr(), w ? w->data_ptr() : nullptr, out.data_ptr(),
+                            p.B, p.N1, p.N2, p.D, pw, exponent, stream_of(p.a)));
+    return out;
+}
+
+Tensor dot_forward(const Prepared &p, int epilogue, int engine) {
+    Tensor out = at::empty({p.B, p.N1, p.N2}, p.a.options());
+    if (p.D == 0) return out.fill_(epilogue == TPW_DOT_COSINE_DIST || epilogue == TPW_DOT_ONE_MINUS_SIM ? 1.0 : 0.0);
+    const int64_t bytes = tpw_dot_metric_scratch_bytes(code_of(p.a), engine, p.B, p.N1, p.N2, p.D);
+    Tensor scratch;
+    if (bytes > 0) scratch = at::empty({bytes}, p.a.options().dtype(at::kByte));
+    TPW_CALL(tpw_dot_metric_forward_ws(code_of(p.a), epilogue, engine, p.a.data_ptr(), p.b.data_ptr(), out.data_ptr(),
+                                       bytes > 0 ? scratch.data_ptr() : nullptr, bytes, p.B, p.N1, p.N2, p.D, stream_of(p.a)));
+    return out;
+}
+
+bool tensor_engine_selected(const Prepared &p) {
+    return p.a.scalar_type() == at::kFloat && p.D > 0 &&
+           tpw_dot_metric_scratch_bytes(TPW_F32, TPW_ENGINE_AUTO, p.B, p.N1, p.N2, p.D) > 0;
+}
+
+Tensor cmp_reduce(const Tensor &a, const Tensor &b, int op, int red);
+
+// ---- at::cdist as the reference's public ops call it -------------------------------------------------
+struct CdistFn : torch::autograd::Function<CdistFn> {
+    static Tensor forward(AutogradContext *ctx, const Tensor &x1, const Tensor &x2, double p) {
+        at::AutoDispatchBelowADInplaceOrView guard;
+        TORCH_CHECK(p >= 0, "cdist only supports non-negative p values");
+        const auto in_dt = x1.scalar_type();
+        TORCH_CHECK(in_dt == x2.scalar_type(), "x1 and x2 must have the same dtype");
+        Prepared q = prepare(x1, x2, compute_type(in_dt));
+        c10::cuda::CUDAGuard dg(q.a.device());
+        Tensor out;
+        if (p == 0) out = cmp_reduce(q.a, q.b, TPW_CMP_NE, TPW_RED_SUM).to(q.a.scalar_type());
+        else if (std::isinf(p)) out = lp_forward(q, nullptr, p, 1.0);
+        else if (p == 2 && tensor_engine_selected(q)) out = dot_forward(q, TPW_DOT_EUCLIDEAN, TPW_ENGINE_AUTO);
+        else out = lp_forward(q, nullptr, p, 1.0 / p);
+        ctx->save_for_backward({q.a, q.b, out});
+        ctx->saved_data["p"] = p;
+        ctx->saved_data["unbatched"] = q.unbatched;
+        ctx->saved_data["dt"] = static_cast<int64_t>(in_dt);
+        return finish(out, q.unbatched, in_dt);
+    }
+    static variable_list backward(AutogradContext *ctx, variable_list go) {
+        auto s = ctx->get_saved_variables();
+        const Tensor &a = s[0], &b = s[1], &out = s[2];
+        const double p = ctx->saved_data["p"].toDouble();
+        const bool ub = ctx->saved_data["unbatched"].toBool();
+        const auto dt = static_cast<at::ScalarType>(ctx->saved_data["dt"].toInt());
+        c10::cuda::CUDAGuard dg(a.device());
+        Tensor g = go[0].to(a.scalar_type()).contiguous();
+        if (ub) g = g.unsqueeze(0);
+        Tensor g1 = at::empty_like(a), g2 = at::empty_like(b);
+        if (p == 0) { g1.zero_(); g2.zero_(); }
+        else TPW_CALL(tpw_lp_backward(code_of(a), TPW_LP_BWD_CDIST, g.data_ptr(), out.data_ptr(), a.data_ptr(), b.data_ptr(), nullptr,
+                                      g1.data_ptr(), g2.data_ptr(), a.size(0), a.size(1), b.size(1), a.size(2), p, stream_of(a)));
+        return {finish(g1, ub, dt), finish(g2, ub, dt), Tensor()};
+    }
+};
+
+// ---- _ppminkowski (OPS/autograd/ppminkowski_kernel.cpp:9-46) ------------------------------------------
+struct PPMinkowskiFn : torch::autograd::Function<PPMinkowskiFn> {
+    static Tensor forward(AutogradContext *ctx, const Tensor &x1, const Tensor &x2, double p) {
+        at::AutoDispatchBelowADInplaceOrView guard;
+        const auto in_dt = x1.scalar_type();
+        TORCH_CHECK(in_dt == x2.scalar_type(), "x1 and x2 must have the same dtype (while checking arguments for _ppminkowski_forward)");
+        Prepared q = prepare(x1, x2, compute_type(in_dt));
+        c10::cuda::CUDAGuard dg(q.a.device());
+        Tensor out;
+        if (p == 0) out = at::full({q.B, q.N1, q.N2}, static_cast<double>(q.D), q.a.options());
+        else if (p == 2 && tensor_engine_selected(q)) out = dot_forward(q, TPW_DOT_SQEUCLIDEAN, TPW_ENGINE_AUTO);
+        else out = lp_forward(q, nullptr, p, 1.0);
+        ctx->save_for_backward({q.a, q.b});
+        ctx->saved_data["p"] = p;
+        ctx->saved_data["unbatched"] = q.unbatched;
+        ctx->saved_data["dt"] = static_cast<int64_t>(in_dt);
+        return finish(out, q.unbatched, in_dt);
+    }
+    static std::pair<Tensor, Tensor> raw_backward(const Tensor &grad, const Tensor &a, const Tensor &b, double p, bool ub) {
+        c10::cuda::CUDAGuard dg(a.device());
+        Tensor g = grad.to(a.scalar_type()).contiguous();
+        if (ub) g = g.unsqueeze(0);
+        Tensor g1 = at::zeros_like(a), g2 = at::zeros_like(b);
+        const int64_t B = a.size(0), N1 = a.size(1), N2 = b.size(1), D = a.size(2);
+        if (p != 0 && B * N1 * N2 * D > 0) {
+            if (std::isinf(p))
+                TPW_CALL(tpw_lp_inf_backward(code_of(a), g.data_ptr(), a.data_ptr(), b.data_ptr(), nullptr, g1.data_ptr(), g2.data_ptr(),
+                                             nullptr, B, N1, N2, D, p < 0, stream_of(a)));
+            else
+                TPW_CALL(tpw_lp_backward(code_of(a), TPW_LP_BWD_PPMINKOWSKI, g.data_ptr(), nullptr, a.data_ptr(), b.data_ptr(), nullptr,
+                                         g1.data_ptr(), g2.data_ptr(), B, N1, N2, D, p, stream_of(a)));
+        }
+        return {g1, g2};
+    }
+    static variable_list backward(AutogradContext *ctx, variable_list go) {
+        auto s = ctx->get_saved_variables();
+        const bool ub = ctx->saved_data["unbatched"].toBool();
+        const auto dt = static_cast<at::ScalarType>(ctx->saved_data["dt"].toInt());
+        auto g = raw_backward(go[0], s[0], s[1], ctx->saved_data["p"].toDouble(), ub);
+        return {finish(g.first, ub, dt), finish(g.second, ub, dt), Tensor()};
+    }
+};
+
+// ---- _wminkowski (OPS/autograd/wminkowski_kernel.cpp:9-50) ---------------------------------------------
+struct WMinkowskiFn : torch::autograd::Function<WMinkowskiFn> {
+    static Tensor forward(AutogradContext *ctx, const Tensor &x1, const Tensor &x2, const Tensor &w, double p) {
+        at::AutoDispatchBelowADInplaceOrView guard;
+        const auto in_dt = x1.scalar_type();
+        TORCH_CHECK(in_dt == x2.scalar_type() && in_dt == w.scalar_type(),
+                    "x1, x2 and w must have the same dtype (while checking arguments for _wminkowski_forward)");
+        require_cuda(w);
+        Prepared q = prepare(x1, x2, compute_type(in_dt));
+        TORCH_CHECK(q.unbatched ? w.dim() == 1 : w.dim() == 2, "w must be 1-D (unbatched) or 2-D (batched) tensor.");
+        Tensor wc = w.to(q.a.scalar_type()).contiguous();
+        if (q.unbatched) wc = wc.unsqueeze(0);
+        TORCH_CHECK(wc.size(0) == q.B, "batch_size of x1, x2, and w do not match.");
+        // the reference compares w.size(1) with N1 here (OPS/cuda/wminkowski_kernel.cu:91); the feature count is meant
+        TORCH_CHECK(wc.size(1) == q.D, "feature dimension of x1, x2, and w do not match.");
+        c10::cuda::CUDAGuard dg(q.a.device());
+        Tensor out;
+        if (p == 0) out = at::full({q.B, q.N1, q.N2}, static_cast<double>(q.D), q.a.options());
+        else out = lp_forward(q, &wc, p, std::isinf(p) ? 1.0 : 1.0 / p);
+        ctx->save_for_backward({q.a, q.b, wc});
+        ctx->saved_data["p"] = p;
+        ctx->saved_data["unbatched"] = q.unbatched;
+        ctx->saved_data["dt"] = static_cast<int64_t>(in_dt);
+        return finish(out, q.unbatched, in_dt);
+    }
+    static std::tuple<Tensor, Tensor, Tensor> raw_backward(const Tensor &grad, const Tensor &a, const Tensor &b, const Tensor &w,
+                                                           double p, bool ub) {
+        c10::cuda::CUDAGuard dg(a.device());
+        Tensor g = grad.to(a.scalar_type()).contiguous();
+        if (ub) g = g.unsqueeze(0);
+        Tensor g1 = at::zeros_like(a), g2 = at::zeros_like(b), gw = at::zeros_like(w);
+        const int64_t B = a.size(0), N1 = a.size(1), N2 = b.size(1), D = a.size(2);
+        if (p != 0 && B * N1 * N2 * D > 0) {
+            if (std::isinf(p)) {
+                TPW_CALL(tpw_lp_inf_backward(code_of(a), g.data_ptr(), a.data_ptr(), b.data_ptr(), w.data_ptr(), g1.data_ptr(),
+                                             g2.data_ptr(), gw.data_ptr(), B, N1, N2, D, p < 0, stream_of(a)));
+            } else {
+                Prepared q{a, b, false, B, N1, N2, D};
+                Tensor coef = lp_forward(q, &w, p, 1.0 / p - 1.0); // S^(1/p-1), OPS/cuda/wminkowski_kernel.cu:16-37
+                TPW_CALL(tpw_lp_backward(code_of(a), TPW_LP_BWD_WMINKOWSKI, g.data_ptr(), coef.data_ptr(), a.data_ptr(), b.data_ptr(),
+                                         w.data_ptr(), g1.data_ptr(), g2.data_ptr(), B, N1, N2, D, p, stream_of(a)));
+                Tensor scratch = at::empty({B, N1, D}, a.options());
+                TPW_CALL(tpw_wminkowski_backward_w(code_of(a), g.data_ptr(), coef.data_ptr(), a.data_ptr(), b.data_ptr(), gw.data_ptr(),
+                                                   scratch.data_ptr(), B, N1, N2, D, p, stream_of(a)));
+            }
+        }
+        return {g1, g2, gw};
+    }
+    static variable_list backward(AutogradContext *ctx, variable_list go) {
+        auto s = ctx->get_saved_variables();
+        const bool ub = ctx->saved_data["unbatched"].toBool();
+        const auto dt = static_cast<at::ScalarType>(ctx->saved_data["dt"].toInt());
+        auto g = raw_backward(go[0], s[0], s[1], s[2], ctx->saved_data["p"].toDouble(), ub);
+        return {finish(std::get<0>(g), ub, dt), finish(std::get<1>(g), ub, dt), finish(std::get<2>(g), ub, dt), Tensor()};
+    }
+};
+
+// ---- cosine similarity and its 1 - S variants (OPS/pairwise_metrics.cpp:51-56,112-122,203) ---------------
+struct CosineFn : torch::autograd::Function<CosineFn> {
+    static Tensor forward(AutogradContext *ctx, const Tensor &x1, const Tensor &x2, int64_t epilogue) {
+        at::AutoDispatchBelowADInplaceOrView guard;
+        const auto in_dt = x1.scalar_type();
+        TORCH_CHECK(in_dt == x2.scalar_type(), "x1 and x2 must have the same dtype");
+        Prepared q = prepare(x1, x2, compute_type(in_dt));
+        c10::cuda::CUDAGuard dg(q.a.device());
+        Tensor out = dot_forward(q, static_cast<int>(epilogue), TPW_ENGINE_AUTO);
+        ctx->save_for_backward({q.a, q.b, out});
+        ctx->saved_data["epilogue"] = epilogue;
+        ctx->saved_data["unbatched"] = q.unbatched;
+        ctx->saved_data["dt"] = static_cast<int64_t>(in_dt);
+        return finish(out, q.unbatched, in_dt);
+    }
+    static variable_list backward(AutogradContext *ctx, variable_list go) {
+        auto s = ctx->get_saved_variables();
+        const Tensor &a = s[0], &b = s[1], &out = s[2];
+        const bool ub = ctx->saved_data["unbatched"].toBool();
+        const auto dt = static_cast<at::ScalarType>(ctx->saved_data["dt"].toInt());
+        const int epilogue = static_cast<int>(ctx->saved_data["epilogue"].toInt());
+        c10::cuda::CUDAGuard dg(a.device());
+        Tensor g = go[0].to(a.scalar_type()).contiguous();
+        if (ub) g = g.unsqueeze(0);
+        const int64_t B = a.size(0), N1 = a.size(1), N2 = b.size(1), D = a.size(2);
+        const int code = code_of(a);
+        auto st = stream_of(a);
+        Tensor n1 = at::empty({B, N1}, a.options()), n2 = at::empty({B, N2}, a.options());
+        TPW_CALL(tpw_row_norm(code, a.data_ptr(), n1.data_ptr(), B * N1, D, st));
+        TPW_CALL(tpw_row_norm(code, b.data_ptr(), n2.data_ptr(), B * N2, D, st));
+        Tensor dM = at::empty_like(g), rowterm = at::empty({B, N1}, a.options()), colterm = at::empty({B, N2}, a.options());
+        Tensor g1 = at::empty_like(a), g2 = at::empty_like(b);
+        TPW_CALL(tpw_cosine_backward_prepare(code, epilogue, g.data_ptr(), out.data_ptr(), n1.data_ptr(), n2.data_ptr(), dM.data_ptr(),
+                                             rowterm.data_ptr(), colterm.data_ptr(), B, N1, N2, st));
+        TPW_CALL(tpw_lp_backward(code, TPW_LP_BWD_MATMUL, dM.data_ptr(), nullptr, a.data_ptr(), b.data_ptr(), nullptr, g1.data_ptr(),
+                                 g2.data_ptr(), B, N1, N2, D, 2.0, st));
+        TPW_CALL(tpw_cosine_backward_finish(code, g1.data_ptr(), a.data_ptr(), n1.data_ptr(), rowterm.data_ptr(), B * N1, D, st));
+        TPW_CALL(tpw_cosine_backward_finish(code, g2.data_ptr(), b.data_ptr(), n2.data_ptr(), colterm.data_ptr(), B * N2, D, st));
+        return {finish(g1, ub, dt), finish(g2, ub, dt), Tensor()};
+    }
+};
+
+// x - x.mean(-1, keepdim) (OPS/pairwise_metrics.cpp:197-198); its own gradient is the same map
+struct RowCenterFn : torch::autograd::Function<RowCenterFn> {
+    static Tensor center(const Tensor &x) {
+        require_cuda(x);
+        const auto in_dt = x.scalar_type();
+        Tensor xc = x.to(compute_type(in_dt)).contiguous();
+        Tensor out = at::empty_like(xc);
+        c10::cuda::CUDAGuard dg(xc.device());
+        const int64_t D = xc.size(-1);
+        if (xc.numel() > 0)
+            TPW_CALL(tpw_row_center(code_of(xc), xc.data_ptr(), out.data_ptr(), xc.numel() / D, D, stream_of(xc)));
+        return out.to(in_dt);
+    }
+    static Tensor forward(AutogradContext *, const Tensor &x) {
+        at::AutoDispatchBelowADInplaceOrView guard;
+        return center(x);
+    }
+    static variable_list backward(AutogradContext *, variable_list go) { return {center(go[0])}; }
+};
+
+// ---- directed Hausdorff (OPS/autograd/hausdorff_kernel.cpp:9-61) -------------------------------------------
+struct HausdorffFn : torch::autograd::Function<HausdorffFn> {
+    static variable_list forward(AutogradContext *ctx, const Tensor &x1, const Tensor &x2, bool shuffle,
+                                 c10::optional<at::Generator> generator) {
+        at::AutoDispatchBelowADInplaceOrView guard;
+        require_cuda(x1);
+        require_cuda(x2);
+        const auto in_dt = x1.scalar_type();
+        TORCH_CHECK(in_dt == x2.scalar_type(), "x1 and x2 must have the same dtype (while checking arguments for _directed_hausdorff_forward)");
+        const bool ub = x1.dim() == 3;
+        TORCH_CHECK(ub || x1.dim() == 4, "x1 must be 3-D (unbatched) or 4-D (batched) tensor.");
+        TORCH_CHECK(x2.dim() == x1.dim(), "x2 must be 3-D (unbatched) or 4-D (batched) tensor.");
+        TORCH_CHECK(ub || x1.size(0) == x2.size(0), "batch_size of x1 and x2 do not match.");
+        TORCH_CHECK(x1.size(-1) == x2.size(-1), "feature dimension of x1 and x2 do not match.");
+        const auto dt = compute_type(in_dt);
+        Tensor a = x1.to(dt).contiguous(), b = x2.is_same(x1) ? a : x2.to(dt).contiguous();
+        if (ub) { a = a.unsqueeze(0); b = b.unsqueeze(0); }
+        const int64_t B = a.size(0), N1 = a.size(1), M1 = a.size(2), D = a.size(3), N2 = b.size(1), M2 = b.size(2);
+        c10::cuda::CUDAGuard dg(a.device());
+        Tensor out = at::empty({B, N1, N2}, a.options());
+        Tensor i1 = at::empty({B, N1, N2}, a.options().dtype(at::kLong)), i2 = at::empty_like(i1);
+        Tensor o1, o2;
+        if (shuffle && B > 0) {
+            // per batch, x1's permutation then x2's (OPS/cuda/hausdorff_kernel.cu:158-167); order[perm[t]] = t
+            o1 = at::empty({B, M1}, i1.options());
+            o2 = at::empty({B, M2}, i1.options());
+            for (int64_t bb = 0; bb < B; ++bb) {
+                Tensor p1 = at::randperm(M1, generator, i1.options()), p2 = at::randperm(M2, generator, i1.options());
+                o1[bb].index_put_({p1}, at::arange(M1, i1.options()));
+                o2[bb].index_put_({p2}, at::arange(M2, i1.options()));
+            }
+        }
+        const int64_t bytes = std::max<int64_t>(tpw_hausdorff_scratch_bytes(B, N1, N2, M1), 8);
+        Tensor scratch = at::empty({bytes}, a.options().dtype(at::kByte));
+        TPW_CALL(tpw_hausdorff_forward(code_of(a), a.data_ptr(), b.data_ptr(), o1.defined() ? o1.data_ptr<int64_t>() : nullptr,
+                                       o2.defined() ? o2.data_ptr<int64_t>() : nullptr, out.data_ptr(), i1.data_ptr<int64_t>(),
+                                       i2.data_ptr<int64_t>(), scratch.data_ptr(), B, N1, N2, M1, M2, D, stream_of(a)));
+        ctx->save_for_backward({a, b, out, i1, i2});
+        ctx->saved_data["unbatched"] = ub;
+        ctx->saved_data["dt"] = static_cast<int64_t>(in_dt);
+        Tensor r = finish(out, ub, in_dt), r1 = ub ? i1.squeeze(0) : i1, r2 = ub ? i2.squeeze(0) : i2;
+        ctx->mark_non_differentiable({r1, r2});
+        return {r, r1, r2};
+    }
+    static variable_list backward(AutogradContext *ctx, variable_list go) {
+        auto s = ctx->get_saved_variables();
+        const Tensor &a = s[0], &b = s[1], &out = s[2], &i1 = s[3], &i2 = s[4];
+        const bool ub = ctx->saved_data["unbatched"].toBool();
+        const auto dt = static_cast<at::ScalarType>(ctx->saved_data["dt"].toInt());
+        c10::cuda::CUDAGuard dg(a.device());
+        Tensor g = go[0].to(a.scalar_type()).contiguous();
+        if (ub) g = g.unsqueeze(0);
+        Tensor g1 = at::empty_like(a), g2 = at::empty_like(b);
+        TPW_CALL(tpw_hausdorff_backward(code_of(a), g.data_ptr(), out.data_ptr(), i1.data_ptr<int64_t>(), i2.data_ptr<int64_t>(),
+                                        a.data_ptr(), b.data_ptr(), g1.data_ptr(), g2.data_ptr(), a.size(0), a.size(1), b.size(1),
+                                        a.size(2), b.size(2), a.size(3), stream_of(a)));
+        return {finish(g1, ub, dt), finish(g2, ub, dt), Tensor(), Tensor()};
+    }
+};
+
+// ---- boolean / compare-reduce (no autograd: the reference registers none either) ---------------------------
+std::tuple<Tensor, Tensor, int64_t> pack_bool(const Tensor &xb) {
+    const int64_t B = xb.size(0), N = xb.size(1), D = xb.size(2);
+    int64_t W = std::max<int64_t>(4, (D + 31) / 32);
+    W = (W + 3) / 4 * 4;
+    Tensor words = at::empty({B, N, W}, xb.options().dtype(at::kInt)), pops = at::empty({B, N}, xb.options().dtype(at::kInt));
+    Tensor src = xb.contiguous();
+    TPW_CALL(tpw_bitpack(static_cast<const uint8_t *>(src.data_ptr()), static_cast<uint32_t *>(words.data_ptr()),
+                         static_cast<int32_t *>(pops.data_ptr()), B * N, D, W, stream_of(xb)));
+    return {words, pops, W};
+}
+
+Tensor bool_metric(const Tensor &x1, const Tensor &x2, int metric) {
+    require_cuda(x1);
+    require_cuda(x2);
+    const bool ub = x1.dim() == 2;
+    TORCH_CHECK(ub || x1.dim() == 3, "x1 must be 2-D (unbatched) or 3-D (batched) tensor.");
+    TORCH_CHECK(x2.dim() == x1.dim(), "x2 must be 2-D (unbatched) or 3-D (batched) tensor.");
+    TORCH_CHECK(ub || x1.size(0) == x2.size(0), "batch_size of x1 and x2 do not match.");
+    TORCH_CHECK(x1.size(-1) == x2.size(-1), "feature dimension of x1 and x2 do not match.");
+    Tensor a = ub ? x1.unsqueeze(0) : x1, b = ub ? x2.unsqueeze(0) : x2;
+    const int64_t B = a.size(0), N1 = a.size(1), N2 = b.size(1), D = a.size(2);
+    c10::cuda::CUDAGuard dg(a.device());
+    Tensor out = at::empty({B, N1, N2}, a.options().dtype(at::kFloat));
+    if (D == 0) {
+        out.fill_(metric <= TPW_BOOL_NE_SUM || metric == TPW_BOOL_JACCARD || metric == TPW_BOOL_YULE
+                      ? 0.0 : std::numeric_limits<double>::quiet_NaN());
+    } else if (out.numel() > 0) {
+        auto pa = pack_bool(a);
+        auto pb = x2.is_same(x1) ? pa : pack_bool(b);
+        TPW_CALL(tpw_bool_metric_forward(metric, static_cast<const uint32_t *>(std::get<0>(pa).data_ptr()),
+                                         static_cast<const uint32_t *>(std::get<0>(pb).data_ptr()),
+                                         static_cast<const int32_t *>(std::get<1>(pa).data_ptr()),
+                                         static_cast<const int32_t *>(std::get<1>(pb).data_ptr()), out.data_ptr<float>(),
+                                         B, N1, N2, D, std::get<2>(pa), stream_of(a)));
+    }
+    return ub ? out.squeeze(0) : out;
+}
+
+// a, b batched, same dtype in {float, double, int, long}
+Tensor cmp_reduce(const Tensor &a, const Tensor &b, int op, int red) {
+    const int64_t B = a.size(0), N1 = a.size(1), N2 = b.size(1), D = a.size(2);
+    Tensor out = at::empty({B, N1, N2}, a.options().dtype(at::kFloat));
+    if (D == 0) return out.fill_(red == TPW_RED_MEAN ? std::numeric_limits<double>::quiet_NaN() : 0.0);
+    int code;
+    switch (a.scalar_type()) {
+        case at::kFloat: code = TPW_F32; break;
+        case at::kDouble: code = TPW_F64; break;
+        case at::kInt: code = TPW_I32; break;
+        case at::kLong: code = TPW_I64; break;
+        default: TORCH_CHECK(false, "pairwise comparison is not implemented for ", a.scalar_type());
+    }
+    TPW_CALL(tpw_cmp_reduce_forward(code, op, red, a.data_ptr(), b.data_ptr(), out.data_ptr<float>(), B, N1, N2, D, stream_of(a)));
+    return out;
+}
+
+// pw{eq,ne}_{sum,mean}: any dtype, result_type promotion, float32 out (OPS/cuda/pairwise_binary_kernels.cu:144-220)
+Tensor pairwise_compare(const Tensor &x1, const Tensor &x2, int op, int red) {
+    require_cuda(x1);
+    require_cuda(x2);
+    auto common = at::result_type(x1, x2);
+    if (common == at::kBool) {
+        const int metric = op == TPW_CMP_EQ ? (red == TPW_RED_MEAN ? TPW_BOOL_EQ_MEAN : TPW_BOOL_EQ_SUM)
+                                            : (red == TPW_RED_MEAN ? TPW_BOOL_NE_MEAN : TPW_BOOL_NE_SUM);
+        return bool_metric(x1.to(at::kBool), x2.to(at::kBool), metric);
+    }
+    if (common == at::kHalf || common == at::kBFloat16) common = at::kFloat; // exact widening keeps every comparison
+    else if (common == at::kByte || common == at::kChar || common == at::kShort) common = at::kInt;
+    Prepared q = prepare(x1.to(common), x2.to(common), common);
+    c10::cuda::CUDAGuard dg(q.a.device());
+    Tensor out = cmp_reduce(q.a, q.b, op, red);
+    return q.unbatched ? out.squeeze(0) : out;
+}
+
+Tensor pw_logic(const Tensor &x1, const Tensor &x2, int metric) {
+    TORCH_CHECK(at::result_type(x1, x2) == at::kBool, "\"pairwise_binary_reduction_forward\" not implemented for '",
+                at::result_type(x1, x2), "'");
+    return bool_metric(x1, x2, metric);
+}
+
+// ---- public ops ------------------------------------------------------------------------------------------------
+Tensor cdist_p(const char *name, const Tensor &x1, const OptTensor &x2, double p) {
+    auto ab = check_pairwise_inputs(name, x1, x2);
+    return CdistFn::apply(ab.first, ab.second, p);
+}
+Tensor euclidean_distances(const Tensor &x1, const OptTensor &x2) { return cdist_p("euclidean_distances", x1, x2, 2.0); }
+Tensor manhattan_distances(const Tensor &x1, const OptTensor &x2) { return cdist_p("manhattan_distances", x1, x2, 1.0); }
+Tensor chebyshev_distances(const Tensor &x1, const OptTensor &x2) {
+    return cdist_p("chebyshev_distances", x1, x2, std::numeric_limits<double>::infinity());
+}
+Tensor minkowski_distances(const Tensor &x1, const OptTensor &x2, double p) { return cdist_p("minkowski_distances", x1, x2, p); }
+Tensor ppminkowski(const Tensor &x1, const Tensor &x2, double p) { return PPMinkowskiFn::apply(x1, x2, p); }
+Tensor wminkowski(const Tensor &x1, const Tensor &x2, const Tensor &w, double p) { return WMinkowskiFn::apply(x1, x2, w, p); }
+Tensor wminkowski_distances(const Tensor &x1, const OptTensor &x2, double p, const OptTensor &w) {
+    auto ab = check_pairwise_inputs("wminkowski_distances", x1, x2);
+    return w.has_value() ? WMinkowskiFn::apply(ab.first, ab.second, w.value(), p) : CdistFn::apply(ab.first, ab.second, p);
+}
+Tensor sqeuclidean_distances(const Tensor &x1, const OptTensor &x2) {
+    auto ab = check_pairwise_inputs("sqeuclidean_distances", x1, x2);
+    return PPMinkowskiFn::apply(ab.first, ab.second, 2.0);
+}
+Tensor cosine_similarity(const Tensor &x1, const OptTensor &x2) {
+    auto ab = check_pairwise_inputs("cosine_similarity", x1, x2);
+    return CosineFn::apply(ab.first, ab.second, static_cast<int64_t>(TPW_DOT_COSINE_SIM));
+}
+Tensor cosine_distances(const Tensor &x1, const OptTensor &x2) {
+    auto ab = check_pairwise_inputs("cosine_similarity", x1, x2);
+    return CosineFn::apply(ab.first, ab.second, static_cast<int64_t>(TPW_DOT_COSINE_DIST));
+}
+Tensor correlation_distances(const Tensor &x1, const OptTensor &x2) {
+    auto ab = check_pairwise_inputs("correlation_distances", x1, x2);
+    Tensor c1 = RowCenterFn::apply(ab.first);
+    Tensor c2 = x2.has_value() ? RowCenterFn::apply(ab.second) : c1;
+    return CosineFn::apply(c1, c2, static_cast<int64_t>(TPW_DOT_ONE_MINUS_SIM));
+}
+Tensor hamming_distances(const Tensor &x1, const OptTensor &x2) {
+    auto ab = check_pairwise_inputs("hamming_distances", x1, x2);
+    return pairwise_compare(ab.first, ab.second, TPW_CMP_NE, TPW_RED_MEAN);
+}
+template <int METRIC>
+Tensor boolean_metric_op(const Tensor &x1, const OptTensor &x2) {
+    static const char *names[] = {"", "", "", "", "", "", "", "jaccard_distances", "kulsinski_distances", "kulczynski1_distances",
+                                  "yule_distances", "dice_distances", "rogerstanimoto_distances", "russellrao_distances",
+                                  "sokalmichener_distances", "sokalsneath_distances"};
+    if (METRIC == TPW_BOOL_KULSINSKI)
+        TORCH_WARN_DEPRECATION("kulsinski_distances is deprecated in SciPy 1.9.0 and might be removed in the future. "
+                               "Please use kulczynski1_distances.");
+    auto ab = check_pairwise_inputs(names[METRIC], x1, x2, /*boolean=*/true);
+    return bool_metric(ab.first, ab.second, METRIC);
+}
+std::tuple<Tensor, Tensor, Tensor> directed_hausdorff_raw(const Tensor &x1, const Tensor &x2, bool shuffle,
+                                                          c10::optional<at::Generator> generator) {
+    auto r = HausdorffFn::apply(x1, x2, shuffle, generator);
+    return {r[0], r[1], r[2]};
+}
+std::tuple<Tensor, Tensor, Tensor> directed_hausdorff_distances(const Tensor &x1, const OptTensor &x2, bool shuffle,
+                                                                c10::optional<at::Generator> generator) {
+    auto ab = check_pairwise_inputs("directed_hausdorff_distances", x1, x2, false, /*sets=*/true);
+    return directed_hausdorff_raw(ab.first, ab.second, shuffle, generator);
+}
+
+// ---- cdist: string dispatcher with the reference's keyword validation (OPS/cpdist.cpp:35-79,149-231) -----------
+Tensor cdist(const Tensor &x1, const Tensor &x2, c10::string_view metric, const OptTensor &w, const OptTensor &V,
+             const OptTensor &VI, c10::optional<double> p, c10::optional<double> base, c10::optional<bool> shuffle,
+             c10::optional<at::Generator> generator) {
+    static const char *supported =
+        "braycurtis, canberra, chebyshev, cityblock, correlation, cosine, dice, directed_hausdorff, euclidean, hamming, "
+        "haversine, jaccard, jensenshannon, kulczynski1, kulsinski, l1, l2, lp, linf, mahalanobis, manhattan, minkowski, "
+        "rogerstanimoto, russellrao, seuclidean, snr, sokalmichener, sokalsneath, sqeuclidean, wminkowski, yule";
+    const std::string m(metric.data(), metric.size());
+    auto accepts = [&](const char *arg) {
+        if (m == "directed_hausdorff") return !strcmp(arg, "shuffle") || !strcmp(arg, "generator");
+        if (m == "minkowski" || m == "lp") return !strcmp(arg, "p");
+        if (m == "wminkowski") return !strcmp(arg, "w") || !strcmp(arg, "p");
+        if (m == "seuclidean") return !strcmp(arg, "V");
+        if (m == "mahalanobis") return !strcmp(arg, "VI");
+        if (m == "jensenshannon") return !strcmp(arg, "base");
+        return false;
+    };
+    std::string bad;
+    auto note = [&](bool given, const char *arg) {
+        if (given && !accepts(arg)) bad += (bad.empty() ? "" : ", ") + std::string(arg);
+    };
+    const bool known = std::string(", ").append(supported).append(", ").find(", " + m + ", ") != std::string::npos;
+    TORCH_CHECK(known, "Got unkown distance metric: ", m, ". Supported metrics are [", supported, "]");
+    note(w.has_value(), "w"); note(V.has_value(), "V"); note(VI.has_value(), "VI"); note(p.has_value(), "p");
+    note(base.has_value(), "base"); note(shuffle.has_value(), "shuffle"); note(generator.has_value(), "generator");
+    TORCH_CHECK_TYPE(bad.empty(), "torchpairwise::", m, "_distances was called with incompatible arguments ", bad, ".");
+    if (m == "euclidean" || m == "l2") return euclidean_distances(x1, x2);
+    if (m == "manhattan" || m == "cityblock" || m == "l1") return manhattan_distances(x1, x2);
+    if (m == "chebyshev" || m == "linf") return chebyshev_distances(x1, x2);
+    if (m == "minkowski" || m == "lp") return minkowski_distances(x1, x2, p.value_or(2));
+    if (m == "wminkowski") return wminkowski_distances(x1, x2, p.value_or(2), w);
+    if (m == "sqeuclidean") return sqeuclidean_distances(x1, x2);
+    if (m == "cosine") return cosine_distances(x1, x2);
+    if (m == "correlation") return correlation_distances(x1, x2);
+    if (m == "hamming") return hamming_distances(x1, x2);
+    if (m == "jaccard") return boolean_metric_op<TPW_BOOL_JACCARD>(x1, x2);
+    // the reference's cdist routes "kulsinski" through the kulczynski1 functor (OPS/pairwise_metrics.h:557-561)
+    if (m == "kulsinski" || m == "kulczynski1") return boolean_metric_op<TPW_BOOL_KULCZYNSKI1>(x1, x2);
+    if (m == "yule") return boolean_metric_op<TPW_BOOL_YULE>(x1, x2);
+    if (m == "dice") return boolean_metric_op<TPW_BOOL_DICE>(x1, x2);
+    if (m == "rogerstanimoto") return boolean_metric_op<TPW_BOOL_ROGERSTANIMOTO>(x1, x2);
+    if (m == "russellrao") return boolean_metric_op<TPW_BOOL_RUSSELLRAO>(x1, x2);
+    if (m == "sokalmichener") return boolean_metric_op<TPW_BOOL_SOKALMICHENER>(x1, x2);
+    if (m == "sokalsneath") return boolean_metric_op<TPW_BOOL_SOKALSNEATH>(x1, x2);
+    if (m == "directed_hausdorff") return std::get<0>(directed_hausdorff_distances(x1, x2, shuffle.value_or(false), generator));
+    TORCH_CHECK_NOT_IMPLEMENTED(false, "metric '", m, "' is outside the B200 pairwise-reduction path of this library");
+}
+
+bool defined(const char *name) {
+    return c10::Dispatcher::singleton().findSchema({std::string("torchpairwise::") + name, ""}).has_value();
+}
+
+#define OPT2 "(Tensor x1, Tensor? x2=None) -> Tensor"
+
+// Schemas, only where the reference extension has not already defined them.
+TORCH_LIBRARY_FRAGMENT(torchpairwise, m) {
+    auto def = [&](const char *name, const char *sig) {
+        if (!defined(name)) m.def((std::string("torchpairwise::") + name + sig).c_str());
+    };
+    for (const char *n : {"euclidean_distances", "manhattan_distances", "cosine_distances", "cosine_similarity",
+                          "sqeuclidean_distances", "correlation_distances", "hamming_distances", "jaccard_distances",
+                          "kulsinski_distances", "kulczynski1_distances", "cityblock_distances", "chebyshev_distances",
+                          "yule_distances", "dice_distances", "rogerstanimoto_distances", "russellrao_distances",
+                          "sokalmichener_distances", "sokalsneath_distances", "l1_distances", "l2_distances", "linf_distances"})
+        def(n, OPT2);
+    def("minkowski_distances", "(Tensor x1, Tensor? x2=None, float p=2) -> Tensor");
+    def("lp_distances", "(Tensor x1, Tensor? x2=None, float p=2) -> Tensor");
+    def("wminkowski_distances", "(Tensor x1, Tensor? x2=None, float p=2, Tensor? w=None) -> Tensor");
+    def("directed_hausdorff_distances",
+        "(Tensor x1, Tensor? x2=None, *, bool shuffle=False, Generator? generator=None) -> (Tensor output, Tensor x1_indices, Tensor x2_indices)");
+    def("_ppminkowski", "(Tensor x1, Tensor x2, float p=2) -> Tensor");
+    def("__ppminkowski_backward", "(Tensor grad, Tensor x1, Tensor x2, float p) -> (Tensor grad_x1, Tensor grad_x2)");
+    def("_wminkowski", "(Tensor x1, Tensor x2, Tensor w, float p=2) -> Tensor");
+    def("__wminkowski_backward", "(Tensor grad, Tensor x1, Tensor x2, Tensor w, float p) -> (Tensor grad_x1, Tensor grad_x2, Tensor grad_w)");
+    def("_directed_hausdorff",
+        "(Tensor x1, Tensor x2, *, bool shuffle=False, Generator? generator=None) -> (Tensor output, Tensor x1_indices, Tensor x2_indices)");
+    for (const char *n : {"pwand_sum", "pwor_sum", "pwxor_sum", "pweq_sum", "pwne_sum", "pweq_mean", "pwne_mean"})
+        def(n, "(Tensor x1, Tensor x2) -> Tensor");
+    def("cdist", "(Tensor x1, Tensor x2, str metric=\"minkowski\", *, Tensor? w=None, Tensor? V=None, Tensor? VI=None, "
+                 "float? p=None, float? base=None, bool? shuffle=None, Generator? generator=None) -> Tensor");
+}
+
+// CUDA tensors of every op above.  AutogradCUDA sits in front of both the reference's
+// CompositeImplicitAutograd bodies and its `Autograd` alias kernels, for CUDA tensors only.
+TORCH_LIBRARY_IMPL(torchpairwise, AutogradCUDA, m) {
+    m.impl("euclidean_distances", euclidean_distances);
+    m.impl("l2_distances", euclidean_distances);
+    m.impl("manhattan_distances", manhattan_distances);
+    m.impl("cityblock_distances", manhattan_distances);
+    m.impl("l1_distances", manhattan_distances);
+    m.impl("chebyshev_distances", chebyshev_distances);
+    m.impl("linf_distances", chebyshev_distances);
+    m.impl("minkowski_distances", minkowski_distances);
+    m.impl("lp_distances", minkowski_distances);
+    m.impl("wminkowski_distances", wminkowski_distances);
+    m.impl("sqeuclidean_distances", sqeuclidean_distances);
+    m.impl("cosine_similarity", cosine_similarity);
+    m.impl("cosine_distances", cosine_distances);
+    m.impl("correlation_distances", correlation_distances);
+    m.impl("hamming_distances", hamming_distances);
+    m.impl("jaccard_distances", boolean_metric_op<TPW_BOOL_JACCARD>);
+    m.impl("kulsinski_distances", boolean_metric_op<TPW_BOOL_KULSINSKI>);
+    m.impl("kulczynski1_distances", boolean_metric_op<TPW_BOOL_KULCZYNSKI1>);
+    m.impl("yule_distances", boolean_metric_op<TPW_BOOL_YULE>);
+    m.impl("dice_distances", boolean_metric_op<TPW_BOOL_DICE>);
+    m.impl("rogerstanimoto_distances", boolean_metric_op<TPW_BOOL_ROGERSTANIMOTO>);
+    m.impl("russellrao_distances", boolean_metric_op<TPW_BOOL_RUSSELLRAO>);
+    m.impl("sokalmichener_distances", boolean_metric_op<TPW_BOOL_SOKALMICHENER>);
+    m.impl("sokalsneath_distances", boolean_metric_op<TPW_BOOL_SOKALSNEATH>);
+    m.impl("directed_hausdorff_distances", directed_hausdorff_distances);
+    m.impl("_ppminkowski", ppminkowski);
+    m.impl("_wminkowski", wminkowski);
+    m.impl("_directed_hausdorff", directed_hausdorff_raw);
+    m.impl("cdist", cdist);
+}
+
+// Ops without a gradient, and the stand-alone backward ops the reference's own Autograd kernels call.
+TORCH_LIBRARY_IMPL(torchpairwise, CUDA, m) {
+    m.impl("pwand_sum", [](const Tensor &a, const Tensor &b) { return pw_logic(a, b, TPW_BOOL_AND_SUM); });
+    m.impl("pwor_sum", [](const Tensor &a, const Tensor &b) { return pw_logic(a, b, TPW_BOOL_OR_SUM); });
+    m.impl("pwxor_sum", [](const Tensor &a, const Tensor &b) { return pw_logic(a, b, TPW_BOOL_XOR_SUM); });
+    m.impl("pweq_sum", [](const Tensor &a, const Tensor &b) { return pairwise_compare(a, b, TPW_CMP_EQ, TPW_RED_SUM); });
+    m.impl("pwne_sum", [](const Tensor &a, const Tensor &b) { return pairwise_compare(a, b, TPW_CMP_NE, TPW_RED_SUM); });
+    m.impl("pweq_mean", [](const Tensor &a, const Tensor &b) { return pairwise_compare(a, b, TPW_CMP_EQ, TPW_RED_MEAN); });
+    m.impl("pwne_mean", [](const Tensor &a, const Tensor &b) { return pairwise_compare(a, b, TPW_CMP_NE, TPW_RED_MEAN); });
+    m.impl("__ppminkowski_backward", [](const Tensor &grad, const Tensor &x1, const Tensor &x2, double p) {
+        Prepared q = prepare(x1, x2, compute_type(x1.scalar_type()));
+        auto g = PPMinkowskiFn::raw_backward(grad, q.a, q.b, p, q.unbatched);
+        return std::make_tuple(finish(g.first, q.unbatched, x1.scalar_type()), finish(g.second, q.unbatched, x1.scalar_type()));
+    });
+    m.impl("__wminkowski_backward", [](const Tensor &grad, const Tensor &x1, const Tensor &x2, const Tensor &w, double p) {
+        Prepared q = prepare(x1, x2, compute_type(x1.scalar_type()));
+        Tensor wc = w.to(q.a.scalar_type()).contiguous();
+        if (q.unbatched) wc = wc.unsqueeze(0);
+        auto g = WMinkowskiFn::raw_backward(grad, q.a, q.b, wc, p, q.unbatched);
+        const auto dt = x1.scalar_type();
+        return std::make_tuple(finish(std::get<0>(g), q.unbatched, dt), finish(std::get<1>(g), q.unbatched, dt),
+                               finish(std::get<2>(g), q.unbatched, dt));
+    });
+}
+
+} // namespace

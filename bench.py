@@ -43,9 +43,10 @@ BWD_OPS_PER_ELEMENT = 3
 # algorithmic HBM bytes of one backward launch: upstream gradient + forward output read once,
 # both operands read once, one gradient written
 BWD_BYTES_PER_LAUNCH = 4 * (2 * B * N1 * N2 + 3 * B * N1 * D)
-# dram__bytes_read.sum + dram__bytes_write.sum of one backward launch, from the ncu capture
-# summarised in profiles/ (None until a capture exists)
-BWD_DRAM_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one backward launch: 589.6 MB measured by ncu at
+# batch 4 (profiles/lp_kernels_c2_minkowski_p3.md); the traffic is the streamed gradient and forward
+# output, so it grows in proportion to the batch
+BWD_DRAM_TRAFFIC_BYTES_PER_BATCH = 589.6e6 / 4
 
 REF_SO = ROOT / "oracle" / "_ref" / "torchpairwise_ref.so"
 
@@ -272,12 +273,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         achieved = ops / (k_ms * 1e-3)
         hbm_peak, hbm_src = load_peaks()
         roofline = {"bound": "fp32_issue", "achieved": achieved / 1e12, "peak": fp32_peak / 1e12,
-                    "unit": "Tlane-op/s", "frac": achieved / fp32_peak, "traffic": BWD_DRAM_TRAFFIC_BYTES,
+                    "unit": "Tlane-op/s", "frac": achieved / fp32_peak, "traffic": BWD_DRAM_TRAFFIC_BYTES_PER_BATCH * B,
                     "kernel": "lp_backward_kernel (grad_x1 pass, p=3)", "ms_per_launch": k_ms,
                     "peak_source": "live register-only FFMA microbenchmark (tpw_measure_issue_peak)"}
         roofline_hbm = {"bound": "hbm", "achieved": BWD_BYTES_PER_LAUNCH / (k_ms * 1e-3) / 1e9, "peak": hbm_peak,
                         "unit": "GB/s", "frac": BWD_BYTES_PER_LAUNCH / (k_ms * 1e-3) / 1e9 / hbm_peak,
-                        "traffic": BWD_DRAM_TRAFFIC_BYTES, "peak_source": hbm_src}
+                        "traffic": BWD_DRAM_TRAFFIC_BYTES_PER_BATCH * B, "peak_source": hbm_src}
         # ---- other metrics of the path, a few launches each (not part of the timed K steps) --------
         extra = {}
 

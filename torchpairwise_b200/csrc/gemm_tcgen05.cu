@@ -14,7 +14,7 @@
 // its warp id selects).  Output tile 128 x 256; k-step 64 bf16 = one 128-byte swizzled row; a stage
 // holds xh, xl (2 x 16 KB) and yh, yl (2 x 32 KB); two stages.  The 512 TMEM columns hold two
 // 128 x 256 fp32 accumulators so the epilogue of tile t overlaps the MMAs of tile t + 1.
-// No cluster launch and no multicast: every CTA fetches its own tiles from this GPU's memory.
+// No cluster launch: every CTA fetches its own tiles, with plain per-CTA TMA loads, from this GPU's memory.
 //
 // Every wait (mbarrier) is bounded; a warp that gives up raises a CTA-wide abort flag that the other
 // roles poll, everybody falls through to the final barrier, tensor memory is released, and the

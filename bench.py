@@ -234,13 +234,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     g1h = torch.empty(B, N1, D).pin_memory()
     g2h = torch.empty(B, N2, D).pin_memory()
 
+    from torchpairwise_b200.host_pipeline import forward_backward_from_host
+
     def e2e_step():
-        x = Xh.to(dev, non_blocking=True).requires_grad_(True)
-        y = Yh.to(dev, non_blocking=True).requires_grad_(True)
-        gr = Gh.to(dev, non_blocking=True)
-        tpw.minkowski_distances(x, y, P).backward(gr)
-        g1h.copy_(x.grad, non_blocking=True)
-        g2h.copy_(y.grad, non_blocking=True)
+        # public API for host-resident operands: copies of chunk c+1 overlap the kernels of chunk c
+        forward_backward_from_host(tpw.minkowski_distances, Xh, Yh, Gh, g1h, g2h, dev, chunk=2, p=P)
 
     e2e_step()
     barrier()

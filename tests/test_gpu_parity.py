@@ -428,3 +428,20 @@ def test_engine_auto_selection(tpw):
     assert lib.tpw_dot_metric_scratch_bytes(_abi.F32, _abi.ENGINE_SIMT_FP32, 1, 4096, 4096, 512) == 0
     with pytest.raises(ValueError):
         tpw.set_dot_engine("nope")
+
+
+def test_host_pipeline_matches_single_call(tpw):
+    from torchpairwise_b200.host_pipeline import forward_backward_from_host
+    g = torch.Generator().manual_seed(21)
+    X = torch.randn(5, 200, 64, generator=g).pin_memory()
+    Y = torch.randn(5, 150, 64, generator=g).pin_memory()
+    G = torch.randn(5, 200, 150, generator=g).pin_memory()
+    g1 = torch.empty_like(X).pin_memory()
+    g2 = torch.empty_like(Y).pin_memory()
+    out = torch.empty_like(G).pin_memory()
+    forward_backward_from_host(tpw.minkowski_distances, X, Y, G, g1, g2, "cuda:0", chunk=2, out_host=out, p=3.0)
+    a, b = X.cuda().requires_grad_(True), Y.cuda().requires_grad_(True)
+    ref = tpw.minkowski_distances(a, b, 3.0)
+    ref.backward(G.cuda())
+    assert torch.equal(out, ref.detach().cpu())
+    assert torch.equal(g1, a.grad.cpu()) and torch.equal(g2, b.grad.cpu())

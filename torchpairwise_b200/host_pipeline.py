@@ -1,0 +1,56 @@
+"""Forward + backward of a batched pairwise metric whose operands live in pinned host memory.
+
+A [B, N1, N2] upstream gradient is usually far larger than the operands (C2: 1.07 GB against
+2 x 16.8 MB), so a step that starts from host buffers is bound by the host-to-device copy unless
+the copy of batch chunk c+1 runs while chunk c computes.  ``forward_backward_from_host`` does
+exactly that with three streams (copy-in, compute, copy-out); batches are independent, so the
+results are identical to one call on the whole batch.  The reference has no such helper (it is
+single-stream throughout); this is an addition for callers that feed the GPU from the host.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+from torch import Tensor
+
+
+def forward_backward_from_host(metric: Callable[..., Tensor], x1_host: Tensor, x2_host: Tensor, grad_host: Tensor,
+                               grad_x1_host: Tensor, grad_x2_host: Tensor, device, *, chunk: int = 2,
+                               out_host: Optional[Tensor] = None, **kwargs) -> None:
+    """``metric(x1, x2, **kwargs).backward(grad)`` batch chunk by batch chunk.
+
+    All tensors are batched ([B, N, D] / [B, N1, N2]) and should be pinned.  Gradients are
+    written into ``grad_x1_host`` / ``grad_x2_host`` (and the distances into ``out_host`` when
+    given).  Returns after every device-to-host copy has completed."""
+    dev = torch.device(device)
+    B = x1_host.size(0)
+    compute = torch.cuda.current_stream(dev)
+    copy_in, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    copy_in.wait_stream(compute)
+    keep = []
+    for lo in range(0, B, chunk):
+        hi = min(B, lo + chunk)
+        with torch.cuda.stream(copy_in):
+            x = x1_host[lo:hi].to(dev, non_blocking=True)
+            y = x2_host[lo:hi].to(dev, non_blocking=True)
+            g = grad_host[lo:hi].to(dev, non_blocking=True)
+            ready = torch.cuda.Event()
+            ready.record(copy_in)
+        compute.wait_event(ready)
+        x.requires_grad_(True)
+        y.requires_grad_(True)
+        out = metric(x, y, **kwargs)
+        out.backward(g)
+        done = torch.cuda.Event()
+        done.record(compute)
+        copy_out.wait_event(done)
+        with torch.cuda.stream(copy_out):
+            grad_x1_host[lo:hi].copy_(x.grad, non_blocking=True)
+            grad_x2_host[lo:hi].copy_(y.grad, non_blocking=True)
+            if out_host is not None:
+                out_host[lo:hi].copy_(out.detach(), non_blocking=True)
+        keep.append((x, y, g, out))  # blocks stay owned until every stream that touched them is done
+    copy_out.synchronize()
+    compute.synchronize()
+    del keep

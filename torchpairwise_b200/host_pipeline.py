@@ -15,6 +15,18 @@ import torch
 from torch import Tensor
 
 
+_streams = {}
+
+
+def _side_streams(dev: torch.device):
+    """One copy-in and one copy-out stream per device, created once: the caching allocator keeps
+    a pool per stream, so fresh streams on every call would mean fresh cudaMallocs on every call."""
+    key = (dev.type, dev.index if dev.index is not None else torch.cuda.current_device())
+    if key not in _streams:
+        _streams[key] = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
+    return _streams[key]
+
+
 def forward_backward_from_host(metric: Callable[..., Tensor], x1_host: Tensor, x2_host: Tensor, grad_host: Tensor,
                                grad_x1_host: Tensor, grad_x2_host: Tensor, device, *, chunk: int = 2,
                                out_host: Optional[Tensor] = None, **kwargs) -> None:
@@ -26,7 +38,7 @@ def forward_backward_from_host(metric: Callable[..., Tensor], x1_host: Tensor, x
     dev = torch.device(device)
     B = x1_host.size(0)
     compute = torch.cuda.current_stream(dev)
-    copy_in, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    copy_in, copy_out = _side_streams(dev)
     copy_in.wait_stream(compute)
     keep = []
     for lo in range(0, B, chunk):

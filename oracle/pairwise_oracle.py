@@ -259,6 +259,50 @@ def cosine_similarity_backward(grad, x1, x2):
     return _un(g1.astype(a.dtype), ub), _un(g2.astype(a.dtype), ub)
 
 
+# ---- kernel functions and standardised Euclidean (compositions; OPS/pairwise_metrics.cpp:67-110,245-263)
+def _gamma(x1, gamma):
+    """Default gamma is 1 / x1.size(1) whatever the rank (OPS/pairwise_metrics.cpp:76,88,97,108)."""
+    return 1.0 / np.asarray(x1).shape[1] if gamma is None else gamma
+
+
+def polynomial_kernel(x1, x2, degree=3, gamma=None, coef0=1.0):
+    a, b = np.asarray(x1), np.asarray(x2)
+    dt = a.dtype
+    return ((a @ np.swapaxes(b, -1, -2) * dt.type(_gamma(a, gamma)) + dt.type(coef0)) ** int(degree)).astype(dt)
+
+
+def sigmoid_kernel(x1, x2, gamma=None, coef0=1.0):
+    a, b = np.asarray(x1), np.asarray(x2)
+    dt = a.dtype
+    return np.tanh(a @ np.swapaxes(b, -1, -2) * dt.type(_gamma(a, gamma)) + dt.type(coef0)).astype(dt)
+
+
+def rbf_kernel(x1, x2, gamma=None):
+    d = sqeuclidean(x1, x2)
+    return np.exp(d * d.dtype.type(-_gamma(x1, gamma))).astype(d.dtype)
+
+
+def laplacian_kernel(x1, x2, gamma=None):
+    d = cdist(x1, x2, 1.0)
+    return np.exp(d * d.dtype.type(-_gamma(x1, gamma))).astype(d.dtype)
+
+
+def seuclidean(x1, x2, V):
+    """_wminkowski(x1, x2, 1/V (1 where V == 0), 2) (OPS/pairwise_metrics.cpp:262)."""
+    V = np.asarray(V)
+    w = prf_div(np.ones_like(V), V, "identity")
+    return wminkowski(x1, x2, w, 2.0)
+
+
+def k_neighbors_mask(dists, k):
+    """True at the k + 1 smallest entries of every row (OPS/neighbors.cpp:29-33)."""
+    d = np.asarray(dists)
+    idx = np.argsort(d, axis=1, kind="stable")[:, : k + 1]
+    out = np.zeros(d.shape, dtype=bool)
+    np.put_along_axis(out, idx, True, axis=1)
+    return out
+
+
 # ---- boolean family (OPS/cpu/pairwise_binary_kernels.cpp:28-49 + compositions) -------------------
 def _counts(x1, x2):
     a, ub = _b3(np.asarray(x1).astype(bool))

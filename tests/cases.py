@@ -44,6 +44,11 @@ FLOAT_METRICS = [
     {"name": "ppminkowski_pinf", "fn": "_ppminkowski", "kw": {"p": math.inf}},
     {"name": "ppminkowski_pneginf", "fn": "_ppminkowski", "kw": {"p": -math.inf}},
     {"name": "ppminkowski_p0", "fn": "_ppminkowski", "kw": {"p": 0.0}},
+    {"name": "rbf_kernel", "fn": "rbf_kernel"},
+    {"name": "rbf_kernel_g0.3", "fn": "rbf_kernel", "kw": {"gamma": 0.3}},
+    {"name": "laplacian_kernel", "fn": "laplacian_kernel", "grad": False},  # the reference's own backward fails (in-place on cdist output)
+    {"name": "polynomial_kernel", "fn": "polynomial_kernel", "kw": {"degree": 2, "gamma": 0.05, "coef0": 0.5}},
+    {"name": "sigmoid_kernel", "fn": "sigmoid_kernel", "kw": {"gamma": 0.02, "coef0": 0.1}},
 ]
 
 

@@ -138,9 +138,35 @@ def config_golden():
     print("configs.npz", len(out), "arrays")
 
 
+def extras_golden():
+    """seuclidean and the neighbour masks (callers of the path), small unbatched inputs."""
+    out = {}
+    g = torch.Generator().manual_seed(41)
+    x1, x2 = torch.randn(14, 6, generator=g), torch.randn(9, 6, generator=g)
+    V = torch.rand(6, generator=g) + 0.2
+    up1, up2 = torch.randn(14, 14, generator=g), torch.randn(14, 9, generator=g)
+    out["x1"], out["x2"], out["V"], out["up1"], out["up2"] = npy(x1), npy(x2), npy(V), npy(up1), npy(up2)
+    a = x1.clone().requires_grad_(True)
+    r = T.seuclidean_distances(a, None, V)  # V=None trips a dangling IntArrayRef in the reference (OPS/pairwise_metrics.cpp:259)
+    r.backward(up1)
+    out["seuclidean_self/out"], out["seuclidean_self/gx1"] = npy(r), npy(a.grad)
+    a, b = x1.clone().requires_grad_(True), x2.clone().requires_grad_(True)
+    r = T.seuclidean_distances(a, b, V)
+    r.backward(up2)
+    out["seuclidean/out"], out["seuclidean/gx1"], out["seuclidean/gx2"] = npy(r), npy(a.grad), npy(b.grad)
+    out["cdist_seuclidean"] = npy(T.cdist(x1, x2, "seuclidean", V=V))
+    out["k_neighbors_k3"] = npy(T.k_neighbors_mask(x1, x2, 3))
+    out["k_neighbors_self_k2_manhattan"] = npy(T.k_neighbors_mask(x1, None, 2, "manhattan"))
+    out["radius_2.5"] = npy(T.radius_neighbors_mask(x1, x2, 2.5))
+    out["radius_self_3_minkowski3"] = npy(T.radius_neighbors_mask(x1, None, 3.0, "minkowski", p=3.0))
+    np.savez_compressed(HERE / "extras.npz", **out)
+    print("extras.npz", len(out), "arrays")
+
+
 if __name__ == "__main__":
     torch.set_num_threads(8)
     float_golden()
     bool_golden()
     hausdorff_golden()
     config_golden()
+    extras_golden()

@@ -63,6 +63,8 @@ def test_float_metric_golden(tpw, golden, case, metric):
         ref_out = O.wminkowski(G[f"{n}/x1"], G[f"{n}/x2"], G[f"{n}/w"], p)[..., ::st, ::st]
         ref_g1, ref_g2, ref_gw = O.wminkowski_backward(G[f"{n}/g"], G[f"{n}/x1"], G[f"{n}/x2"], G[f"{n}/w"], p)
     close(out[..., ::st, ::st], ref_out, tol, msg=key + " forward")
+    if not metric.get("grad", True):
+        return
     out.backward(g)
     scale = 10 * max(1.0, float(np.abs(ref_g1).max()))
     close(x1.grad, ref_g1, tol, scale, key + " grad_x1")
@@ -445,3 +447,32 @@ def test_host_pipeline_matches_single_call(tpw):
     ref.backward(G.cuda())
     assert torch.equal(out, ref.detach().cpu())
     assert torch.equal(g1, a.grad.cpu()) and torch.equal(g2, b.grad.cpu())
+
+
+def test_extras_golden(tpw, golden):
+    """seuclidean and the neighbour masks: the callers on either side of the path."""
+    G = golden("extras")
+    tol = TOL[torch.float32]
+    x1, x2, V = cuda(G["x1"], True), cuda(G["x2"], True), cuda(G["V"])
+    out = tpw.seuclidean_distances(x1, x2, V)
+    close(out, G["seuclidean/out"], tol, msg="seuclidean")
+    out.backward(cuda(G["up2"]))
+    close(x1.grad, G["seuclidean/gx1"], tol, 10, "seuclidean grad_x1")
+    close(x2.grad, G["seuclidean/gx2"], tol, 10, "seuclidean grad_x2")
+    x1.grad = None
+    out = tpw.seuclidean_distances(x1, None, V)
+    close(out, G["seuclidean_self/out"], tol, msg="seuclidean self")
+    out.backward(cuda(G["up1"]))
+    close(x1.grad, G["seuclidean_self/gx1"], tol, 10, "seuclidean self grad")
+    close(tpw.cdist(x1.detach(), x2.detach(), "seuclidean", V=V), G["cdist_seuclidean"], tol, msg="cdist seuclidean")
+    # V = None: the feature variances of x1 (the reference intends this; its own call trips on a dangling array ref)
+    xd = x1.detach()
+    close(tpw.seuclidean_distances(xd), O.seuclidean(G["x1"], G["x1"], G["x1"].var(0, ddof=1)), tol, msg="seuclidean V=None")
+    with pytest.raises(RuntimeError, match="V is required"):
+        tpw.seuclidean_distances(xd, x2.detach())
+    xd2 = x2.detach()
+    assert torch.equal(tpw.k_neighbors_mask(xd, xd2, 3).cpu(), torch.from_numpy(G["k_neighbors_k3"]))
+    assert torch.equal(tpw.k_neighbors_mask(xd, None, 2, "manhattan").cpu(), torch.from_numpy(G["k_neighbors_self_k2_manhattan"]))
+    assert torch.equal(tpw.radius_neighbors_mask(xd, xd2, 2.5).cpu(), torch.from_numpy(G["radius_2.5"]))
+    assert torch.equal(tpw.radius_neighbors_mask(xd, None, 3.0, "minkowski", p=3.0).cpu(),
+                       torch.from_numpy(G["radius_self_3_minkowski3"]))

@@ -25,6 +25,7 @@ def _oracle_forward(metric, x1, x2, w):
     if fn == "linear_kernel": return x1 @ np.swapaxes(x2, -1, -2)
     if fn == "wminkowski_distances": return O.wminkowski(x1, x2, w, p)
     if fn == "_ppminkowski": return O.ppminkowski(x1, x2, p)
+    if fn in ("rbf_kernel", "laplacian_kernel", "polynomial_kernel", "sigmoid_kernel"): return getattr(O, fn)(x1, x2, **kw)
     raise KeyError(fn)
 
 
@@ -55,7 +56,7 @@ def test_float_metric_matches_reference(golden, case, metric):
     st = case.get("stride", 1)
     out = _oracle_forward(metric, x1, x2, w)
     np.testing.assert_allclose(out[..., ::st, ::st], G[key + "/out"], **tol)
-    grads = _oracle_backward(metric, g, x1, x2, w)
+    grads = _oracle_backward(metric, g, x1, x2, w) if metric.get("grad", True) else None
     if grads is not None:
         # gradients sum up to N terms of size |g|*|d|^(p-1): scale the absolute floor accordingly
         scale = max(1.0, float(np.abs(G[key + "/gx1"]).max()))
@@ -112,3 +113,16 @@ def test_prf_div_modes():
     gs, go = O.prf_div_backward(np.ones_like(x), x, y, "identity")
     np.testing.assert_allclose(gs, [0.5, 1.0, 1.0, 1 / 1.5], rtol=1e-6)
     np.testing.assert_allclose(go, [-0.25, 0.0, 0.0, 3 / 2.25], rtol=1e-6)
+
+
+def test_extras_match_reference(golden):
+    G = golden("extras")
+    x1, x2, V = G["x1"], G["x2"], G["V"]
+    tol = TOL[x1.dtype]
+    np.testing.assert_allclose(O.seuclidean(x1, x2, V), G["seuclidean/out"], **tol)
+    np.testing.assert_allclose(O.seuclidean(x1, x1, V), G["seuclidean_self/out"], **tol)
+    np.testing.assert_allclose(O.seuclidean(x1, x2, V), G["cdist_seuclidean"], **tol)
+    np.testing.assert_array_equal(O.k_neighbors_mask(O.cdist(x1, x2, 2.0), 3), G["k_neighbors_k3"])
+    np.testing.assert_array_equal(O.k_neighbors_mask(O.cdist(x1, x1, 1.0), 2), G["k_neighbors_self_k2_manhattan"])
+    np.testing.assert_array_equal(O.cdist(x1, x2, 2.0) <= 2.5, G["radius_2.5"])
+    np.testing.assert_array_equal(O.cdist(x1, x1, 3.0) <= 3.0, G["radius_self_3_minkowski3"])

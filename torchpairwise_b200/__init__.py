@@ -21,8 +21,10 @@ from .ops import (
     get_dot_engine,
     hamming_distances,
     jaccard_distances,
+    k_neighbors_mask,
     kulczynski1_distances,
     kulsinski_distances,
+    laplacian_kernel,
     l1_distances,
     l2_distances,
     linear_kernel,
@@ -30,6 +32,7 @@ from .ops import (
     lp_distances,
     manhattan_distances,
     minkowski_distances,
+    polynomial_kernel,
     prf_div,
     pwand_sum,
     pweq_mean,
@@ -38,9 +41,13 @@ from .ops import (
     pwne_sum,
     pwor_sum,
     pwxor_sum,
+    radius_neighbors_mask,
+    rbf_kernel,
     rogerstanimoto_distances,
     russellrao_distances,
     set_dot_engine,
+    seuclidean_distances,
+    sigmoid_kernel,
     sokalmichener_distances,
     sokalsneath_distances,
     sqeuclidean_distances,

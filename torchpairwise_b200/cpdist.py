@@ -42,7 +42,7 @@ _SCHEMAS = {
                           "-> (Tensor output, Tensor x1_indices, Tensor x2_indices)",
 }
 
-_OUT_OF_SCOPE = {"braycurtis", "canberra", "haversine", "jensenshannon", "mahalanobis", "seuclidean", "snr"}
+_OUT_OF_SCOPE = {"braycurtis", "canberra", "haversine", "jensenshannon", "mahalanobis", "snr"}
 
 
 def _check_extra_args(metric: str, **given) -> None:
@@ -71,6 +71,8 @@ def cdist(x1: Tensor, x2: Tensor, metric: str = "minkowski", *, w: Optional[Tens
         return ops.minkowski_distances(x1, x2, 2.0 if p is None else p)
     if metric == "wminkowski":
         return ops.wminkowski_distances(x1, x2, 2.0 if p is None else p, w)
+    if metric == "seuclidean":
+        return ops.seuclidean_distances(x1, x2, V)
     if metric == "kulsinski":
         return ops.kulczynski1_distances(x1, x2)
     if metric == "cosine":

@@ -847,3 +847,72 @@ def lp_distances(x1: Tensor, x2: Optional[Tensor] = None, p: float = 2.0) -> Ten
 
 def linf_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
     return chebyshev_distances(x1, x2)
+
+
+# --------------------------------------------------------------------------------------------
+# callers on either side of the path: kernel functions, standardised Euclidean, neighbour masks
+# (compositions of the operators above, as in the reference; gradients flow through them)
+# --------------------------------------------------------------------------------------------
+def _default_gamma(x1: Tensor, gamma: Optional[float]) -> float:
+    # the reference divides by x1.size(1) whatever the rank (OPS/pairwise_metrics.cpp:76,88,97,108)
+    return 1.0 / x1.size(1) if gamma is None else float(gamma)
+
+
+def polynomial_kernel(x1: Tensor, x2: Optional[Tensor] = None, degree: int = 3, gamma: Optional[float] = None,
+                      coef0: float = 1.0) -> Tensor:
+    """(gamma <x, y> + coef0)^degree (OPS/pairwise_metrics.cpp:67-78)."""
+    return (linear_kernel(x1, x2) * _default_gamma(x1, gamma) + coef0) ** int(degree)
+
+
+def sigmoid_kernel(x1: Tensor, x2: Optional[Tensor] = None, gamma: Optional[float] = None, coef0: float = 1.0) -> Tensor:
+    """tanh(gamma <x, y> + coef0) (OPS/pairwise_metrics.cpp:80-90)."""
+    return torch.tanh(linear_kernel(x1, x2) * _default_gamma(x1, gamma) + coef0)
+
+
+def rbf_kernel(x1: Tensor, x2: Optional[Tensor] = None, gamma: Optional[float] = None) -> Tensor:
+    """exp(-gamma |x - y|^2) (OPS/pairwise_metrics.cpp:92-99)."""
+    return torch.exp(sqeuclidean_distances(x1, x2) * -_default_gamma(x1, gamma))
+
+
+def laplacian_kernel(x1: Tensor, x2: Optional[Tensor] = None, gamma: Optional[float] = None) -> Tensor:
+    """exp(-gamma |x - y|_1) (OPS/pairwise_metrics.cpp:101-110)."""
+    return torch.exp(manhattan_distances(x1, x2) * -_default_gamma(x1, gamma))
+
+
+def seuclidean_distances(x1: Tensor, x2: Optional[Tensor] = None, V: Optional[Tensor] = None) -> Tensor:
+    """sqrt(sum_k (x_k - y_k)^2 / V_k): weighted Minkowski with w = 1/V, p = 2; V defaults to the
+    feature variances of x1 (OPS/pairwise_metrics.cpp:245-263)."""
+    if x2 is not None and V is None:
+        raise RuntimeError("V is required for seuclidean when x2 is passed.")
+    x1_, x2_ = check_pairwise_inputs("euclidean_distances", x1, x2)
+    if V is None:
+        with torch.no_grad():
+            V = x1_.var(dim=0 if x1_.dim() == 2 else (0, 1))
+    w = prf_div(torch.ones_like(V), V, "identity")  # prf_ldiv(V, 1, "identity"): 1/V, and 1 where V == 0
+    return _wminkowski(x1_, x2_, w, 2.0)
+
+
+def radius_neighbors_mask(x1: Tensor, x2: Optional[Tensor] = None, epsilon: float = 0.0, metric: str = "euclidean",
+                          **kwargs) -> Tensor:
+    """cdist(x1, x2, metric) <= epsilon (OPS/neighbors.cpp:37-58)."""
+    from .cpdist import cdist
+    x1_, x2_ = check_pairwise_inputs("radius_neighbors_mask", x1, x2)
+    if epsilon < 0:
+        raise RuntimeError(f"epsilon must be non-negative. Got epsilon={epsilon}")
+    with torch.no_grad():
+        return cdist(x1_, x2_, metric, **kwargs) <= epsilon
+
+
+def k_neighbors_mask(x1: Tensor, x2: Optional[Tensor] = None, k: int = 1, metric: str = "euclidean", **kwargs) -> Tensor:
+    """True at the k + 1 smallest distances of every row (OPS/neighbors.cpp:10-35; the reference keeps
+    k + 1 columns, i.e. the point itself plus k neighbours when x2 is x1; unbatched inputs)."""
+    from .cpdist import cdist
+    x1_, x2_ = check_pairwise_inputs("k_neighbors_mask", x1, x2)
+    if k < 0:
+        raise RuntimeError(f"k must be non-negative. Got k={k}")
+    with torch.no_grad():
+        dists = cdist(x1_, x2_, metric, **kwargs)
+        inds = dists.argsort(dim=1, descending=False)[:, : k + 1]
+        out = torch.zeros((x1_.size(0), x2_.size(0)), dtype=torch.bool, device=x1_.device)
+        out.scatter_(1, inds, True)
+        return out

@@ -53,7 +53,9 @@ def test_float_metric_golden(tpw, golden, case, metric):
     st = case.get("stride", 1)
     out = call_metric(tpw, metric, x1, x2, w)
     if key + "/out" in G.files:
-        ref_out, ref_g1, ref_g2 = G[key + "/out"], G[key + "/gx1"], G[key + "/gx2"]
+        ref_out = G[key + "/out"]
+        has_grad = metric.get("grad", True)
+        ref_g1, ref_g2 = (G[key + "/gx1"], G[key + "/gx2"]) if has_grad else (None, None)
         ref_gw = G[key + "/gw"] if metric.get("weighted") else None
     else:
         # batched weights with N1 != D: the reference rejects them (shape-check slip); the oracle

@@ -50,8 +50,8 @@ struct BwdParams {
     int *status;
 };
 
-constexpr int kStages = 3;
-constexpr int SC = 32; // streamed rows per stage
+constexpr int kStages = 2;
+constexpr int SC = 64; // streamed rows per stage
 
 template <typename T> __device__ __forceinline__ void load4(T *dst, const T *src);
 template <> __device__ __forceinline__ void load4<float>(float *dst, const float *src) {
@@ -77,6 +77,10 @@ __device__ __forceinline__ float b_copysign_of(float c, float d) {
     return __int_as_float(__float_as_int(c) ^ (__float_as_int(d) & 0x80000000));
 }
 __device__ __forceinline__ double b_copysign_of(double c, double d) { return d < 0.0 ? -c : c; }
+// g / v for the coefficient tile: an approximate reciprocal (2 ulp) is far inside the fp32 parity
+// tolerance and an order of magnitude cheaper than the IEEE sequence; fp64 keeps the exact divide
+__device__ __forceinline__ float b_div(float g, float v) { return __fdividef(g, v); }
+__device__ __forceinline__ double b_div(double g, double v) { return g / v; }
 __device__ __forceinline__ float b_pow(float a, double q) { return powf(a, (float)q); }
 __device__ __forceinline__ double b_pow(double a, double q) { return pow(a, q); }
 
@@ -243,9 +247,9 @@ lp_backward_kernel(const __grid_constant__ CUtensorMap map_stream, const __grid_
                 const T g = gs[e], o = as[e];
                 T c;
                 switch (P.coef_mode) {
-                    case COEF_DIV_O: c = o == T(0) ? T(0) : g / o; break;
-                    case COEF_DIV_O2: c = o == T(0) ? T(0) : g / (o * o); break;
-                    case COEF_DIV_POW: c = o == T(0) ? T(0) : g / b_pow(o, P.q); break;
+                    case COEF_DIV_O: c = o == T(0) ? T(0) : b_div(g, o); break;
+                    case COEF_DIV_O2: c = o == T(0) ? T(0) : b_div(g, o * o); break;
+                    case COEF_DIV_POW: c = o == T(0) ? T(0) : b_div(g, b_pow(o, P.q)); break;
                     case COEF_MUL: c = g * o; break;
                     case COEF_ZERO_WHERE_O0: c = o == T(0) ? T(0) : g; break;
                     default: c = g; break;

@@ -9,9 +9,9 @@
 // fp32 rounding of the sum).  Row norms are summed in fp32 from the unsplit values by the same
 // pre-pass.
 //
-// Kernel.  Persistent, one CTA per SM, 192 threads: warp 0 = TMA producer (one lane), warp 1 =
-// tensor-memory owner and MMA issuer (one lane), warps 2..5 = epilogue (each owns the 32 TMEM lanes
-// its warp id selects).  Output tile 128 x 256; k-step 64 bf16 = one 128-byte swizzled row; a stage
+// Kernel.  Persistent, one CTA per SM, 320 threads: warp 0 = TMA producer (one lane), warp 1 =
+// tensor-memory owner and MMA issuer (one lane), warps 2..9 = epilogue (each owns the 32 TMEM lanes
+// its warp id selects and one half of the columns).  Output tile 128 x 256; k-step 64 bf16 = one 128-byte swizzled row; a stage
 // holds xh, xl (2 x 16 KB) and yh, yl (2 x 32 KB); two stages.  The 512 TMEM columns hold two
 // 128 x 256 fp32 accumulators so the epilogue of tile t overlaps the MMAs of tile t + 1.
 // No cluster launch: every CTA fetches its own tiles, with plain per-CTA TMA loads, from this GPU's memory.
@@ -35,12 +35,16 @@ constexpr int A_BYTES = BM * BK * 2;          // 16 KB
 constexpr int B_BYTES = BN * BK * 2;          // 32 KB
 constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES; // xh | xl | yh | yl = 96 KB
 constexpr int OFF_BAR = kStages * STAGE_BYTES;
-// barriers: full[2], empty[2], tmem_full[2], tmem_empty[2]; then the TMEM base address and the abort flag
-constexpr int OFF_TMEM_PTR = OFF_BAR + 8 * 8;
+// barriers: full_hi[2], full_lo[2], empty[2], tmem_full[2], tmem_empty[2]; then the TMEM base address and the abort flag
+constexpr int OFF_TMEM_PTR = OFF_BAR + 10 * 8;
 constexpr int OFF_ABORT = OFF_TMEM_PTR + 4;
-constexpr int SMEM_BYTES = OFF_ABORT + 4;
+// per epilogue warp a 32 x 32 fp32 staging block (4 KB) used to turn "one row per thread" into
+// "eight lanes per 128-byte row segment" before the global stores
+constexpr int OFF_STAGE = (OFF_ABORT + 4 + 127) / 128 * 128;
+constexpr int SMEM_BYTES = OFF_STAGE + 8 * 4096;
 constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
-constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 8;             // two per TMEM lane quarter, each draining half of the columns
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kSpinLimit = 1u << 26;
 
@@ -147,8 +151,10 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
                    const GemmParams P) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t *full = reinterpret_cast<uint64_t *>(smem + OFF_BAR);
-    uint64_t *empty = full + kStages;
+    // a stage lands in two halves so that the xh.yh products can start while xl, yl are still in flight
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + OFF_BAR);   // xh + yh of a stage
+    uint64_t *full_lo = full + kStages;                               // xl + yl of a stage
+    uint64_t *empty = full_lo + kStages;
     uint64_t *tmem_full = empty + kStages;
     uint64_t *tmem_empty = tmem_full + 2;
     uint32_t *tmem_ptr = reinterpret_cast<uint32_t *>(smem + OFF_TMEM_PTR);
@@ -158,8 +164,8 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
     const int nkb = (int)((P.D + BK - 1) / BK);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 4); }
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&full_lo[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], kEpilogueWarps); }
         *abort_flag = 0;
         mbar_init_fence();
         tma_prefetch_descriptor(&map_xh);
@@ -196,11 +202,12 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
                         break;
                     }
                     unsigned char *st = smem + s * STAGE_BYTES;
-                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
                     tma_load_3d(st, &map_xh, &full[s], kb * BK, (int)(tm * BM), (int)b);
-                    tma_load_3d(st + A_BYTES, &map_xl, &full[s], kb * BK, (int)(tm * BM), (int)b);
                     tma_load_3d(st + 2 * A_BYTES, &map_yh, &full[s], kb * BK, (int)(tn * BN), (int)b);
-                    tma_load_3d(st + 2 * A_BYTES + B_BYTES, &map_yl, &full[s], kb * BK, (int)(tn * BN), (int)b);
+                    mbar_expect_tx(&full_lo[s], A_BYTES + B_BYTES);
+                    tma_load_3d(st + A_BYTES, &map_xl, &full_lo[s], kb * BK, (int)(tm * BM), (int)b);
+                    tma_load_3d(st + 2 * A_BYTES + B_BYTES, &map_yl, &full_lo[s], kb * BK, (int)(tn * BN), (int)b);
                 }
             }
         }
@@ -232,12 +239,21 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
                     const uint32_t sb = smem_u32(smem + s * STAGE_BYTES);
                     const uint64_t dxh = make_smem_desc(sb), dxl = make_smem_desc(sb + A_BYTES);
                     const uint64_t dyh = make_smem_desc(sb + 2 * A_BYTES), dyl = make_smem_desc(sb + 2 * A_BYTES + B_BYTES);
+                    // 16 bf16 = 32 bytes along the swizzled row per MMA: advance the start address by 2 units
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        tc_mma_bf16(d_tmem, dxh + 2 * k, dyh + 2 * k, idesc, (kb | k) != 0);
+                    if (!wait_or_abort(&full_lo[s], (it / kStages) & 1, abort_flag)) {
+                        *abort_flag = 1;
+                        if (P.status) atomicCAS(P.status, 0, (4 << 16) | 5);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k) {
-                        const uint64_t adv = (uint64_t)((k * 32) >> 4); // 16 bf16 = 32 bytes along the swizzled row
-                        tc_mma_bf16(d_tmem, dxh + adv, dyh + adv, idesc, (kb | k) != 0);
-                        tc_mma_bf16(d_tmem, dxh + adv, dyl + adv, idesc, 1);
-                        tc_mma_bf16(d_tmem, dxl + adv, dyh + adv, idesc, 1);
+                        tc_mma_bf16(d_tmem, dxh + 2 * k, dyl + 2 * k, idesc, 1);
+                        tc_mma_bf16(d_tmem, dxl + 2 * k, dyh + 2 * k, idesc, 1);
                     }
                     tc_commit(&empty[s]); // the stage may be refilled once these MMAs have read it
                 }
@@ -245,8 +261,9 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
             }
         }
     } else {
-        // ---------------- epilogue: warps 2..5, TMEM lanes 32*(warp % 4) .. +31 ----------------
+        // ---------------- epilogue: warps 2..9, TMEM lanes 32*(warp % 4) .. +31, column half (warp-2)/4 ----------------
         const int q = warp & 3;
+        const int chalf = (warp - 2) >> 2;
         uint32_t tcount = 0;
         bool ok = true;
         for (long long tile = blockIdx.x; tile < P.tiles && ok; tile += gridDim.x, ++tcount) {
@@ -268,14 +285,17 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
             float *orow = P.out + (b * P.N1 + (row_ok ? i : 0)) * P.N2;
             const float *n2p = P.n2sq + b * P.N2;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
                 uint32_t r[32];
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + a * BN + c * 32;
                 tmem_ld32(taddr, r);
                 tmem_ld_wait();
                 const long long j0 = tn * BN + c * 32;
-                if (!row_ok || j0 >= P.N2) continue;
+                if (j0 >= P.N2) continue;
+                if (!row_ok && !(P.vec_store && j0 + 32 <= P.N2)) continue;
                 if (P.vec_store && j0 + 32 <= P.N2) {
+                    // epilogue math on this thread's row, staged with a 16-byte-chunk XOR swizzle ...
+                    unsigned char *stg = smem + OFF_STAGE + (warp - 2) * 4096;
 #pragma unroll
                     for (int v = 0; v < 8; ++v) {
                         const float4 nn = EPI == TPW_DOT_LINEAR ? make_float4(0.f, 0.f, 0.f, 0.f)
@@ -285,8 +305,19 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
                         o.y = dot_epilogue<EPI>(__uint_as_float(r[4 * v + 1]), n1, nn.y, SELF && i == j0 + 4 * v + 1);
                         o.z = dot_epilogue<EPI>(__uint_as_float(r[4 * v + 2]), n1, nn.z, SELF && i == j0 + 4 * v + 2);
                         o.w = dot_epilogue<EPI>(__uint_as_float(r[4 * v + 3]), n1, nn.w, SELF && i == j0 + 4 * v + 3);
-                        reinterpret_cast<float4 *>(orow + j0)[v] = o;
+                        *reinterpret_cast<float4 *>(stg + lane * 128 + ((v ^ (lane & 7)) << 4)) = o;
                     }
+                    __syncwarp();
+                    // ... and written out four full 128-byte row segments per instruction
+                    const long long row_base = tm * BM + q * 32;
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int rr = it * 4 + (lane >> 3), cc = lane & 7;
+                        const float4 o = *reinterpret_cast<const float4 *>(stg + rr * 128 + ((cc ^ (rr & 7)) << 4));
+                        if (row_base + rr < P.N1)
+                            reinterpret_cast<float4 *>(P.out + (b * P.N1 + row_base + rr) * P.N2 + j0)[cc] = o;
+                    }
+                    __syncwarp();
                 } else {
 #pragma unroll
                     for (int v = 0; v < 32; ++v) {

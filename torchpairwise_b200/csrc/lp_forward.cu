@@ -283,10 +283,10 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
                 V yb = *reinterpret_cast<const V *>(ys + (yrow + 16 * rj) * 128u + ((c ^ (yrow & 7u)) << 4));
                 const T *ye = reinterpret_cast<const T *>(&yb);
 #pragma unroll
-                for (int ri = 0; ri < R; ++ri) {
-                    const T *xe = reinterpret_cast<const T *>(&xa[ri]);
+                for (int e = 0; e < VN; ++e) {
 #pragma unroll
-                    for (int e = 0; e < VN; ++e) {
+                    for (int ri = 0; ri < R; ++ri) {
+                        const T *xe = reinterpret_cast<const T *>(&xa[ri]);
                         if (KIND == K_MIN) {
                             // zero padding beyond D must not win the minimum
                             if (kbase + c * VN + e < P.D) accumulate<KIND, WEIGHTED, T>(acc[ri][rj], xe[e], ye[e], wv[e], pexp);

@@ -457,6 +457,21 @@ def run_suite(args):
         entry("C4_sqeuclidean_simt", n, timeit(lambda: tpw.sqeuclidean_distances(X, Y)), "fp32_issue", n * 512 * 2, fp32_peak, 4 * n)
         tpw.set_dot_engine("auto")
     del X, Y
+    # ---- output-bound shapes (small D): achieved HBM write bandwidth -------------------------------------------
+    ro = args.rows or 65536
+    X, Y = torch.randn(ro, 16, generator=g).to(dev), torch.randn(16384, 16, generator=g).to(dev)
+    n = ro * 16384
+    for name, fn in (("OB_manhattan_D16", tpw.manhattan_distances), ("OB_chebyshev_D16", tpw.chebyshev_distances),
+                     ("OB_sqeuclidean_D16", tpw.sqeuclidean_distances)):
+        if want(name):
+            entry(name, n, timeit(lambda: fn(X, Y)), "hbm (output write)", 4 * n / 1e9, hbm_peak, 4 * n)
+    Xb, Yb = (torch.rand(ro, 64, generator=g) < 0.3).to(dev), (torch.rand(16384, 64, generator=g) < 0.3).to(dev)
+    if want("OB_jaccard_D64"):
+        entry("OB_jaccard_D64", n, timeit(lambda: tpw.jaccard_distances(Xb, Yb)), "hbm (output write)", 4 * n / 1e9, hbm_peak, 4 * n)
+    X, Y = torch.randn(ro, 64, generator=g).to(dev), torch.randn(16384, 64, generator=g).to(dev)
+    if want("OB_cosine_D64_tensor"):
+        entry("OB_cosine_D64_tensor", n, timeit(lambda: tpw.cosine_distances(X, Y)), "hbm (output write)", 4 * n / 1e9, hbm_peak, 4 * n)
+    del X, Y, Xb, Yb
     # ---- C5: point clouds [64,1,8192,3] ------------------------------------------------------------------
     P_ = torch.rand(64, 8192, 3, generator=g) * 2 - 1
     Q_ = P_ + 0.05 * torch.randn(64, 8192, 3, generator=g)

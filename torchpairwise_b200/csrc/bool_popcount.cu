@@ -36,6 +36,7 @@ struct BoolParams {
     long long B, N1, N2, D, W;
     long long tiles_i, tiles_j;
     int metric;
+    int vec_store; // N2 % 4 == 0 and out 16-byte aligned: staged 128-bit stores
     float inv_d; // 1/D when D is a power of two (then x * inv_d == x / D exactly), else 0
     int *status;
 };
@@ -176,8 +177,11 @@ bool_popcount_kernel(const __grid_constant__ CUtensorMap map1, const __grid_cons
         }
         const unsigned char *xs = smem + stage * STAGE_BYTES;
         const unsigned char *ys = xs + XT_BYTES;
+        // pairs of 16-byte groups that hold real words in this chunk (the rest is zero fill)
+        const long long wleft = P.W - (long long)t * KC;
+        const int cend = wleft >= KC ? 8 : (int)((wleft + 7) / 8) * 2;
 #pragma unroll 1
-        for (int c = 0; c < 8; c += 2) {
+        for (int c = 0; c < cend; c += 2) {
             uint4 xa[RI], xb[RI];
 #pragma unroll
             for (int r = 0; r < RI; ++r) {
@@ -209,6 +213,41 @@ bool_popcount_kernel(const __grid_constant__ CUtensorMap map1, const __grid_cons
 
     float *out = P.out + b * P.N1 * P.N2;
     const int32_t *pop1 = P.pop1 + b * P.N1, *pop2 = P.pop2 + b * P.N2;
+    if (P.vec_store) {
+        // Stage the raw AND counts of the 64 x 128 tile in the (now idle) operand stages, then let
+        // every warp turn whole 512-byte row segments into the metric and write them with 128-bit
+        // stores.  The metric code exists four times per thread here instead of thirty-two times in
+        // the register-tile order, which keeps the kernel inside the instruction cache.
+        constexpr int ROWB = (TILE_J + 16) * 4;
+        static_assert(TILE_I * ROWB <= kStages * STAGE_BYTES, "staging tile must fit in the operand stages");
+        __syncthreads();
+#pragma unroll
+        for (int ri = 0; ri < RI; ++ri)
+#pragma unroll
+            for (int rj = 0; rj < RJ; ++rj)
+                *reinterpret_cast<int *>(smem + (ti + 16 * ri) * ROWB + (tj + 16 * rj) * 4) = acc[ri][rj];
+        __syncthreads();
+        const int warp = tid >> 5, lane = tid & 31;
+        const long long jcol = j0 + lane * 4;
+        if (jcol < P.N2) { // N2 % 4 == 0: a group of four columns is entirely inside or entirely outside
+            const int4 pbv = *reinterpret_cast<const int4 *>(pop2 + jcol);
+            const int D = (int)P.D;
+#pragma unroll 1
+            for (int rr = warp; rr < TILE_I; rr += kThreads / 32) {
+                const long long i = i0 + rr;
+                if (i >= P.N1) break;
+                const int pa = pop1[i];
+                const int4 n = *reinterpret_cast<const int4 *>(smem + rr * ROWB + lane * 16);
+                float4 o;
+                o.x = bool_epilogue(P.metric, n.x, pa, pbv.x, D, P.inv_d);
+                o.y = bool_epilogue(P.metric, n.y, pa, pbv.y, D, P.inv_d);
+                o.z = bool_epilogue(P.metric, n.z, pa, pbv.z, D, P.inv_d);
+                o.w = bool_epilogue(P.metric, n.w, pa, pbv.w, D, P.inv_d);
+                *reinterpret_cast<float4 *>(out + i * P.N2 + jcol) = o;
+            }
+        }
+        return;
+    }
     int pb[RJ];
 #pragma unroll
     for (int rj = 0; rj < RJ; ++rj) {
@@ -269,6 +308,7 @@ extern "C" int tpw_bool_metric_forward(int metric, const uint32_t *x1_words, con
     P.x1 = x1_words; P.x2 = x2_words; P.pop1 = x1_popcount; P.pop2 = x2_popcount; P.out = out;
     P.B = B; P.N1 = N1; P.N2 = N2; P.D = D; P.W = words_per_row;
     P.metric = metric;
+    P.vec_store = (N2 % 4 == 0 && aligned16(out) && aligned16(x2_popcount)) ? 1 : 0;
     P.inv_d = (D & (D - 1)) == 0 ? 1.0f / (float)D : 0.f;
     P.tiles_i = (N1 + TILE_I - 1) / TILE_I;
     P.tiles_j = (N2 + TILE_J - 1) / TILE_J;

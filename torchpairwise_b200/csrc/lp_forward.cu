@@ -40,6 +40,7 @@ struct FwdParams {
     double out_exponent; // finite kinds: out = sum ^ out_exponent
     int root_mode;       // 0 none, 1 sqrt, 2 cbrt, 3 pow(out_exponent)
     int epilogue;        // K_DOT: tpw_dot_epilogue; K_NE*: bit0 = report equal count, bit1 = mean
+    int vec_store;       // 4-byte outputs, N2 % 4 == 0, 16-byte aligned base: staged 128-bit stores
     int *status;
 };
 
@@ -163,7 +164,7 @@ __device__ __forceinline__ void stage_rows_generic(unsigned char *tile, const T 
     }
 }
 
-template <typename T, typename OutT, int R, int KIND, bool WEIGHTED, bool USE_TMA>
+template <typename T, typename OutT, int R, int KIND, bool WEIGHTED, bool USE_TMA, bool PARTIAL>
 __global__ void __launch_bounds__(kThreads, (sizeof(T) == 4 ? 2 : 1))
 lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constant__ CUtensorMap map2,
                   const FwdParams P) {
@@ -269,8 +270,14 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
         const uint32_t xrow = ti, yrow = tj; // (row + 16 r) & 7 == row & 7
         const long long kbase = (long long)t * KC;
 
+        // Each trip handles one 16-byte group of features (4 floats / 2 doubles) against the whole
+        // register tile.  PARTIAL instantiations (D not a multiple of the chunk) stop the last chunk at
+        // the last group that holds real features -- the rest is zero fill -- which keeps small-D
+        // shapes output-bound; the others keep a constant trip count.
+        const long long kleft = P.D - kbase;
+        const int cmax = (PARTIAL && kleft < KC) ? (int)((kleft + VN - 1) / VN) : 8;
 #pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < cmax; ++c) {
             V xa[R];
 #pragma unroll
             for (int r = 0; r < R; ++r)
@@ -283,10 +290,10 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
                 V yb = *reinterpret_cast<const V *>(ys + (yrow + 16 * rj) * 128u + ((c ^ (yrow & 7u)) << 4));
                 const T *ye = reinterpret_cast<const T *>(&yb);
 #pragma unroll
-                for (int e = 0; e < VN; ++e) {
+                for (int ri = 0; ri < R; ++ri) {
+                    const T *xe = reinterpret_cast<const T *>(&xa[ri]);
 #pragma unroll
-                    for (int ri = 0; ri < R; ++ri) {
-                        const T *xe = reinterpret_cast<const T *>(&xa[ri]);
+                    for (int e = 0; e < VN; ++e) {
                         if (KIND == K_MIN) {
                             // zero padding beyond D must not win the minimum
                             if (kbase + c * VN + e < P.D) accumulate<KIND, WEIGHTED, T>(acc[ri][rj], xe[e], ye[e], wv[e], pexp);
@@ -323,6 +330,33 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
     }
 
     OutT *out = reinterpret_cast<OutT *>(P.out) + b * P.N1 * P.N2;
+    if (sizeof(OutT) == 4 && P.vec_store) {
+        // Full tiles of 4-byte outputs go through shared memory (the operand stages are free now):
+        // every warp then writes whole 512-byte row segments with 128-bit stores.
+        constexpr int ROWB = (TILE + 16) * 4; // 16 floats of padding: the two x1 rows a warp writes hit disjoint banks
+        static_assert(TILE * ROWB <= kStages * 2 * S::TILE_BYTES, "staging tile must fit in the operand stages");
+        __syncthreads();
+#pragma unroll
+        for (int ri = 0; ri < R; ++ri) {
+            const T n1 = KIND == K_DOT ? norms[ti + 16 * ri] : T(0);
+#pragma unroll
+            for (int rj = 0; rj < R; ++rj) {
+                const T n2 = KIND == K_DOT ? norms[TILE + tj + 16 * rj] : T(0);
+                *reinterpret_cast<OutT *>(smem + (ti + 16 * ri) * ROWB + (tj + 16 * rj) * 4) =
+                    finish<T, OutT, KIND>(acc[ri][rj], n1, n2, P);
+            }
+        }
+        __syncthreads();
+        const int warp = tid >> 5, lane = tid & 31;
+        const long long jcol = j0 + lane * 4;
+#pragma unroll 4
+        for (int rr = warp; rr < TILE; rr += kThreads / 32) {
+            const long long i = i0 + rr;
+            if (i < P.N1 && jcol < P.N2) // N2 % 4 == 0: a float4 is entirely inside or entirely outside
+                *reinterpret_cast<float4 *>(out + i * P.N2 + jcol) = *reinterpret_cast<const float4 *>(smem + rr * ROWB + lane * 16);
+        }
+        return;
+    }
 #pragma unroll
     for (int ri = 0; ri < R; ++ri) {
         const long long i = i0 + ti + 16 * ri;
@@ -350,6 +384,7 @@ int launch_forward(FwdParams P, cudaStream_t stream) {
     TPW_CHECK_ARG(P.N1 < (1ll << 31) && P.N2 < (1ll << 31) && P.B < (1ll << 31) && P.D < (1ll << 31),
                   "lp forward: a dimension exceeds 2^31-1");
     P.status = device_status_ptr();
+    P.vec_store = (sizeof(OutT) == 4 && S::TILE == 128 && P.N2 % 4 == 0 && aligned16(P.out)) ? 1 : 0;
 
     const bool tma_ok = !tma_disabled() && aligned16(P.x1) && aligned16(P.x2) && (P.D * (long long)sizeof(T)) % 16 == 0 && P.D > 0;
     CUtensorMap m1, m2;
@@ -360,11 +395,17 @@ int launch_forward(FwdParams P, cudaStream_t stream) {
         if (st != TPW_OK) return st;
         st = make_tensor_map_3d(&m2, P.x2, sizeof(T), P.D, P.N2, P.B, S::KC, S::TILE, true);
         if (st != TPW_OK) return st;
-        auto kern = lp_forward_kernel<T, OutT, R, KIND, WEIGHTED, true>;
-        TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::ALLOC));
-        kern<<<(unsigned)tiles, kThreads, S::ALLOC, stream>>>(m1, m2, P);
+        if (P.D % S::KC == 0) {
+            auto kern = lp_forward_kernel<T, OutT, R, KIND, WEIGHTED, true, false>;
+            TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::ALLOC));
+            kern<<<(unsigned)tiles, kThreads, S::ALLOC, stream>>>(m1, m2, P);
+        } else {
+            auto kern = lp_forward_kernel<T, OutT, R, KIND, WEIGHTED, true, true>;
+            TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::ALLOC));
+            kern<<<(unsigned)tiles, kThreads, S::ALLOC, stream>>>(m1, m2, P);
+        }
     } else {
-        auto kern = lp_forward_kernel<T, OutT, R, KIND, WEIGHTED, false>;
+        auto kern = lp_forward_kernel<T, OutT, R, KIND, WEIGHTED, false, true>;
         TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::ALLOC));
         kern<<<(unsigned)tiles, kThreads, S::ALLOC, stream>>>(m1, m2, P);
     }

@@ -66,6 +66,15 @@ TPW_API const char *tpw_last_error(void);
  */
 TPW_API int tpw_device_status(int *code, tpw_stream_t stream);
 
+/*
+ * Failure-path self-test: launches one small CTA that waits, with the same bounded-wait code as
+ * the TMA / tcgen05 kernels, on an mbarrier that nothing will ever complete.  After `budget_ms`
+ * (1..1000) the CTA gives up, records code (15 << 16) | 1 in the device status word and returns;
+ * the context stays usable.  Lets a test exercise "a wait ran out" without faulting or hanging
+ * the GPU.  No counterpart in the reference.
+ */
+TPW_API int tpw_selftest_bounded_wait(int budget_ms, tpw_stream_t stream);
+
 /* ---- L_p family on the CUDA cores ---------------------------------------------------------- */
 
 /*

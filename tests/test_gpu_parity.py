@@ -478,3 +478,59 @@ def test_extras_golden(tpw, golden):
     assert torch.equal(tpw.radius_neighbors_mask(xd, xd2, 2.5).cpu(), torch.from_numpy(G["radius_2.5"]))
     assert torch.equal(tpw.radius_neighbors_mask(xd, None, 3.0, "minkowski", p=3.0).cpu(),
                        torch.from_numpy(G["radius_self_3_minkowski3"]))
+
+
+def test_bounded_wait_reports_instead_of_hanging(tpw):
+    """A wait that can never complete gives up after its budget, leaves a code in the device status
+    word and leaves the context usable (no trap, no fault, no endless loop)."""
+    import time
+    from torchpairwise_b200 import _abi
+    assert tpw.device_status() == 0
+    t0 = time.perf_counter()
+    _abi.check(_abi.lib.tpw_selftest_bounded_wait(50, torch.cuda.current_stream().cuda_stream))
+    code = tpw.device_status()  # synchronises, reads and clears
+    dt = time.perf_counter() - t0
+    assert code == (15 << 16) | 1
+    assert 0.04 < dt < 1.0, dt
+    assert tpw.device_status() == 0  # cleared
+    x = torch.randn(64, 32, device="cuda")
+    assert torch.isfinite(tpw.euclidean_distances(x)).all()  # the context still works
+    assert _abi.lib.tpw_selftest_bounded_wait(0, None) == 1  # argument check
+
+
+def test_layout_and_size_edges(tpw):
+    g = torch.Generator().manual_seed(33)
+    base1 = torch.randn(24, 50, generator=g).cuda()
+    base2 = torch.randn(24, 41, generator=g).cuda()
+    # non-contiguous views are made contiguous, as the reference's wrappers do
+    x1, x2 = base1.t(), base2.t()          # [50, 24], [41, 24] with strides (1, 50)
+    assert not x1.is_contiguous()
+    ref = O.cdist(x1.cpu().numpy(), x2.cpu().numpy(), 3.0)
+    close(tpw.minkowski_distances(x1, x2, 3.0), ref, TOL[torch.float32], msg="non-contiguous")
+    close(tpw.cosine_distances(x1[::2], x2[::3]), O.cosine_distances(x1[::2].cpu().numpy(), x2[::3].cpu().numpy()),
+          TOL[torch.float32], msg="strided rows")
+    # more than 65535 row tiles in one launch, ragged last tile, D not a multiple of four
+    xa = torch.randn(70001, 3, generator=g).cuda()
+    xb = torch.randn(130, 3, generator=g).cuda()
+    out = tpw.manhattan_distances(xa, xb)
+    pick = torch.tensor([0, 1, 127, 128, 65535, 65536, 70000])
+    close(out[pick.cuda()], O.cdist(xa[pick.cuda()].cpu().numpy(), xb.cpu().numpy(), 1.0), TOL[torch.float32], msg="many tiles")
+    xbool = torch.rand(70001, 40, generator=g).cuda() < 0.4
+    ybool = torch.rand(130, 40, generator=g).cuda() < 0.4
+    jac = tpw.jaccard_distances(xbool, ybool)
+    assert np.array_equal(jac[pick.cuda()].cpu().numpy(), O.boolean_metric("jaccard", xbool[pick.cuda()].cpu().numpy(), ybool.cpu().numpy()))
+    # zero features: empty sums
+    z1, z2 = torch.empty(5, 0, device="cuda"), torch.empty(4, 0, device="cuda")
+    assert torch.equal(tpw.manhattan_distances(z1, z2), torch.zeros(5, 4, device="cuda"))
+    assert torch.equal(tpw.cosine_distances(z1, z2), torch.ones(5, 4, device="cuda"))
+    # mixed dtypes promote as torch.result_type does before comparing (hamming on non-boolean data)
+    a8 = torch.randint(0, 3, (9, 13), generator=g).to(torch.int8).cuda()
+    f32 = torch.randint(0, 3, (7, 13), generator=g).float().cuda()
+    assert np.array_equal(tpw.hamming_distances(a8, f32).cpu().numpy(), O.hamming(a8.cpu().numpy(), f32.cpu().numpy()))
+    # dtype and device mismatches are errors, as in the reference
+    with pytest.raises(RuntimeError):
+        tpw.sqeuclidean_distances(base1, base2.double()[:, :50])
+    with pytest.raises(RuntimeError, match="same number of features"):
+        tpw.euclidean_distances(base1, base2)
+    with pytest.raises(RuntimeError, match="batch_size"):
+        tpw.euclidean_distances(torch.randn(2, 4, 3, device="cuda"), torch.randn(3, 4, 3, device="cuda"))

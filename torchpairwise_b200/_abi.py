@@ -37,6 +37,7 @@ SIGNATURES = {
     "tpw_cuda_arch_flags": (c_char_p, []),
     "tpw_last_error": (c_char_p, []),
     "tpw_device_status": (_I, [POINTER(c_int), _P]),
+    "tpw_selftest_bounded_wait": (_I, [_I, _P]),
     "tpw_lp_forward": (_I, [_I, _P, _P, _P, _P, _L, _L, _L, _L, _D, _D, _P]),
     "tpw_lp_backward": (_I, [_I, _I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _D, _P]),
     "tpw_wminkowski_backward_w": (_I, [_I, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _D, _P]),

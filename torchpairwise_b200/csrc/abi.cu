@@ -159,6 +159,29 @@ __global__ void __launch_bounds__(256) issue_peak_kernel(float *sink, int iters,
     if (s == 123.456f) sink[0] = s; // never true in practice; keeps the chains alive
 }
 
+// Waits on an mbarrier that nothing ever completes, with a caller-chosen budget, then records
+// the give-up in the status word exactly as the production kernels do.
+__global__ void wait_selftest_kernel(int *status, unsigned long long budget_ns) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+    int failed = 0;
+    const uint64_t t0 = globaltimer_ns();
+    bool done = false;
+    for (uint32_t it = 0; it < (1u << 26) && !done; ++it) {
+        if (mbar_try_wait(&bar, 0)) done = true;
+        else if ((it & 15u) == 15u && globaltimer_ns() - t0 > budget_ns) break;
+    }
+    if (!done) failed = 1;
+    if (__syncthreads_or(failed)) {
+        if (threadIdx.x == 0 && status) atomicCAS(status, 0, (15 << 16) | 1);
+        return;
+    }
+}
+
 } // namespace tpw
 
 extern "C" {
@@ -176,6 +199,15 @@ int tpw_device_status(int *code, tpw_stream_t stream) {
     TPW_CUDA_OK(cudaStreamSynchronize(s));
     TPW_CUDA_OK(cudaMemcpy(code, p, sizeof(int), cudaMemcpyDeviceToHost));
     if (*code != 0) TPW_CUDA_OK(cudaMemset(p, 0, sizeof(int)));
+    return TPW_OK;
+}
+
+int tpw_selftest_bounded_wait(int budget_ms, tpw_stream_t stream) {
+    TPW_CHECK_ARG(budget_ms >= 1 && budget_ms <= 1000, "tpw_selftest_bounded_wait: budget must be 1..1000 ms");
+    int *p = tpw::device_status_ptr();
+    if (!p) return tpw::fail(TPW_ERR_CUDA, "tpw_selftest_bounded_wait: cannot resolve the device status word");
+    tpw::wait_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(p, (unsigned long long)budget_ms * 1000000ull);
+    TPW_LAUNCH_OK("wait_selftest_kernel");
     return TPW_OK;
 }
 

@@ -40,29 +40,41 @@ def forward_backward_from_host(metric: Callable[..., Tensor], x1_host: Tensor, x
     compute = torch.cuda.current_stream(dev)
     copy_in, copy_out = _side_streams(dev)
     copy_in.wait_stream(compute)
-    keep = []
-    for lo in range(0, B, chunk):
-        hi = min(B, lo + chunk)
-        with torch.cuda.stream(copy_in):
-            x = x1_host[lo:hi].to(dev, non_blocking=True)
-            y = x2_host[lo:hi].to(dev, non_blocking=True)
-            g = grad_host[lo:hi].to(dev, non_blocking=True)
-            ready = torch.cuda.Event()
-            ready.record(copy_in)
-        compute.wait_event(ready)
-        x.requires_grad_(True)
-        y.requires_grad_(True)
-        out = metric(x, y, **kwargs)
-        out.backward(g)
+    bounds = [(lo, min(B, lo + chunk)) for lo in range(0, B, chunk)]
+    # Copy-in stream: all operand chunks first (small), then the gradient chunks (large), in order.
+    xs, ys, gs, x_ready, g_ready = [], [], [], [], []
+    with torch.cuda.stream(copy_in):
+        for lo, hi in bounds:
+            xs.append(x1_host[lo:hi].to(dev, non_blocking=True))
+            ys.append(x2_host[lo:hi].to(dev, non_blocking=True))
+            ev = torch.cuda.Event()
+            ev.record(copy_in)
+            x_ready.append(ev)
+        for lo, hi in bounds:
+            gs.append(grad_host[lo:hi].to(dev, non_blocking=True))
+            ev = torch.cuda.Event()
+            ev.record(copy_in)
+            g_ready.append(ev)
+    # Compute stream: every forward needs only its operands, so all forwards run while the gradient is
+    # still crossing the bus; each backward starts as soon as its gradient chunk has landed.
+    outs = []
+    for c in range(len(bounds)):
+        compute.wait_event(x_ready[c])
+        xs[c].requires_grad_(True)
+        ys[c].requires_grad_(True)
+        outs.append(metric(xs[c], ys[c], **kwargs))
+    for c, (lo, hi) in enumerate(bounds):
+        compute.wait_event(g_ready[c])
+        outs[c].backward(gs[c])
         done = torch.cuda.Event()
         done.record(compute)
         copy_out.wait_event(done)
         with torch.cuda.stream(copy_out):
-            grad_x1_host[lo:hi].copy_(x.grad, non_blocking=True)
-            grad_x2_host[lo:hi].copy_(y.grad, non_blocking=True)
+            grad_x1_host[lo:hi].copy_(xs[c].grad, non_blocking=True)
+            grad_x2_host[lo:hi].copy_(ys[c].grad, non_blocking=True)
             if out_host is not None:
-                out_host[lo:hi].copy_(out.detach(), non_blocking=True)
-        keep.append((x, y, g, out))  # blocks stay owned until every stream that touched them is done
+                out_host[lo:hi].copy_(outs[c].detach(), non_blocking=True)
+    # the device tensors stay referenced until every stream that touched them has drained
     copy_out.synchronize()
     compute.synchronize()
-    del keep
+    del xs, ys, gs, outs

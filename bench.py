@@ -436,6 +436,10 @@ def run_suite(args):
                 out.backward(G, retain_graph=True)
             entry(name + "_bwd", n, timeit(bwd), "fp32_issue", n * 256 * bo, fp32_peak, 0)
             del out
+    if want("C2_manhattan_rowmin"):
+        with torch.no_grad():
+            entry("C2_manhattan_rowmin", n, timeit(lambda: tpw.pairwise_argmin_min(X, Y, "manhattan")), "fp32_issue (matrix never written)",
+                  n * 256 * 2, fp32_peak, 0)
     del X, Y, G
     # ---- C3: bool X[65536,1024], Y[16384,1024] -------------------------------------------------------
     r3 = args.rows or 65536
@@ -465,6 +469,9 @@ def run_suite(args):
                      ("OB_sqeuclidean_D16", tpw.sqeuclidean_distances)):
         if want(name):
             entry(name, n, timeit(lambda: fn(X, Y)), "hbm (output write)", 4 * n / 1e9, hbm_peak, 4 * n)
+    if want("OB_manhattan_D16_rowmin"):
+        entry("OB_manhattan_D16_rowmin", n, timeit(lambda: tpw.pairwise_argmin_min(X, Y, "manhattan")),
+              "fp32_issue (matrix never written)", n * 16 * 2, fp32_peak, 0)
     Xb, Yb = (torch.rand(ro, 64, generator=g) < 0.3).to(dev), (torch.rand(16384, 64, generator=g) < 0.3).to(dev)
     if want("OB_jaccard_D64"):
         entry("OB_jaccard_D64", n, timeit(lambda: tpw.jaccard_distances(Xb, Yb)), "hbm (output write)", 4 * n / 1e9, hbm_peak, 4 * n)

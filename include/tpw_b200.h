@@ -94,6 +94,24 @@ TPW_API int tpw_lp_forward(int dtype, const void *x1, const void *x2, const void
                    int64_t B, int64_t N1, int64_t N2, int64_t D,
                    double p, double out_exponent, tpw_stream_t stream);
 
+/*
+ * Streaming row minimum of the same reduction: min_out[b,i] = min_j out[b,i,j] and
+ * arg_out[b,i] = the smallest j that attains it, for out as tpw_lp_forward defines it with
+ * finite p > 0 or p = +inf.  The [B,N1,N2] matrix is never written: each 128x128 tile is
+ * reduced in registers and warp shuffles and folded into one 64-bit key per x1 row.
+ * float32 only (TPW_F32).  A NaN distance ranks above +inf; N2 = 0 gives +inf and -1.
+ * scratch: tpw_lp_rowmin_scratch_bytes(B, N1) bytes on the device, 8-byte aligned; the call
+ * initialises it.  Either of min_out / arg_out may be NULL.
+ *
+ * No counterpart in the reference, which materialises the matrix and then sorts every row
+ * of it (k_neighbors_mask, OPS/neighbors.cpp:10-35: dists.argsort(1).slice(1, 0, k + 1)).
+ */
+TPW_API int64_t tpw_lp_rowmin_scratch_bytes(int64_t B, int64_t N1);
+TPW_API int tpw_lp_rowmin_forward(int dtype, const void *x1, const void *x2, const void *w,
+                          float *min_out, int64_t *arg_out, void *scratch,
+                          int64_t B, int64_t N1, int64_t N2, int64_t D,
+                          double p, double out_exponent, tpw_stream_t stream);
+
 enum tpw_lp_backward_mode {
     /* ATen cdist backward: aux = forward output o.  p=1: g*sgn(d); p=2: g*d/o;
        other finite p: g*d*|d|^(p-2)/o^(p-1); +inf: g*sgn(d)*[|d|==o]; all 0 where o==0.

@@ -6,6 +6,7 @@ benchmark sizes, where neither can run -- size-independent identities of the met
 """
 import math
 import warnings
+import zlib
 
 import numpy as np
 import pytest
@@ -478,6 +479,80 @@ def test_extras_golden(tpw, golden):
     assert torch.equal(tpw.radius_neighbors_mask(xd, xd2, 2.5).cpu(), torch.from_numpy(G["radius_2.5"]))
     assert torch.equal(tpw.radius_neighbors_mask(xd, None, 3.0, "minkowski", p=3.0).cpu(),
                        torch.from_numpy(G["radius_self_3_minkowski3"]))
+
+
+ROWMIN_SHAPES = [((130, 7), (257, 7)), ((3, 200, 32), (3, 129, 32)), ((1, 5), (1, 5)), ((2, 300, 96), (2, 40, 96)),
+                 ((513, 36), (1000, 36))]
+ROWMIN_METRICS = [("euclidean", None, 2.0, 0.5), ("sqeuclidean", None, 2.0, 1.0), ("manhattan", None, 1.0, 1.0),
+                  ("chebyshev", None, math.inf, 1.0), ("minkowski", 3.0, 3.0, 1 / 3), ("minkowski", 1.5, 1.5, 1 / 1.5)]
+
+
+@pytest.mark.parametrize("shapes", ROWMIN_SHAPES, ids=lambda s: "x".join(map(str, s[0])) + "_" + "x".join(map(str, s[1])))
+@pytest.mark.parametrize("metric,p,pp,ex", ROWMIN_METRICS, ids=lambda v: str(v))
+def test_pairwise_argmin_min_matches_oracle(tpw, shapes, metric, p, pp, ex):
+    """The streaming row minimum against min / argmin of the oracle's full matrix (float64 inputs of
+    the same float32 values): the value within the float32 contract, and the chosen column's true
+    distance equal to the true minimum within the same bound (robust to near ties)."""
+    rng = np.random.default_rng(zlib.crc32(repr((shapes, metric, p)).encode()))
+    a = rng.standard_normal(shapes[0]).astype(np.float32)
+    b = rng.standard_normal(shapes[1]).astype(np.float32)
+    ref = O.cdist(a.astype(np.float64), b.astype(np.float64), pp)
+    if ex == 1.0 and pp == 2.0:
+        ref = ref * ref
+    arg, mn = tpw.pairwise_argmin_min(cuda(a), cuda(b), metric, p)
+    assert arg.dtype == torch.int64 and mn.dtype == torch.float32
+    assert tuple(arg.shape) == shapes[0][:-1] and tuple(mn.shape) == shapes[0][:-1]
+    tol = TOL[torch.float32]
+    close(mn.double(), ref.min(-1), tol, msg="row minimum")
+    picked = np.take_along_axis(ref, arg.cpu().numpy()[..., None], -1)[..., 0]
+    np.testing.assert_allclose(picked, ref.min(-1), rtol=tol["rtol"], atol=tol["atol"])
+    # the same kernel's full matrix reduces to exactly the same value
+    full = tpw.cdist(cuda(a), cuda(b), "minkowski", p=pp) if metric != "sqeuclidean" else None
+    if full is not None and not (metric == "euclidean" and tpw.get_dot_engine() != "simt"):
+        assert torch.equal(full.min(-1).values, mn)
+
+
+def test_pairwise_argmin_min_ties_and_edges(tpw):
+    """Exact ties go to the smaller x2 row (integer-valued inputs make the distances exact), in a
+    tile interior, across the 128-column tile boundary and across batches; other dtypes and the
+    k = 0 neighbour mask agree with the matrix path; bad arguments raise."""
+    rng = np.random.default_rng(11)
+    b = rng.integers(-8, 9, size=(2, 400, 12)).astype(np.float32)
+    b[:, 300] = b[:, 17]    # duplicates of row 17 in another column tile
+    b[:, 130] = b[:, 17]
+    b[:, 129] = b[:, 128]   # duplicates inside one tile
+    a = b[:, [17, 128, 5, 399]] + 0.0
+    for metric in ("manhattan", "sqeuclidean", "chebyshev"):
+        arg, mn = tpw.pairwise_argmin_min(cuda(a), cuda(b), metric)
+        ref = O.cdist(a.astype(np.float64), b.astype(np.float64), {"manhattan": 1.0, "sqeuclidean": 2.0, "chebyshev": math.inf}[metric])
+        if metric == "sqeuclidean":
+            ref = ref * ref
+        assert np.array_equal(arg.cpu().numpy(), ref.argmin(-1)), metric   # numpy: first minimum
+        assert np.array_equal(mn.cpu().numpy().astype(np.float64), ref.min(-1)), metric
+    x = cuda(rng.standard_normal((70, 9)).astype(np.float32))
+    y = cuda(rng.standard_normal((90, 9)).astype(np.float32))
+    arg64, mn64 = tpw.pairwise_argmin_min(x.double(), y.double(), "euclidean")
+    arg32, mn32 = tpw.pairwise_argmin_min(x, y, "euclidean")
+    assert mn64.dtype == torch.float64 and torch.equal(arg64, arg32)
+    torch.testing.assert_close(mn64.float(), mn32, rtol=1e-5, atol=1e-6)
+    argh, mnh = tpw.pairwise_argmin_min(x.half(), y.half(), "manhattan")
+    assert mnh.dtype == torch.float16 and argh.shape == arg32.shape
+    # self distances: every row finds itself at distance 0
+    args, mns = tpw.pairwise_argmin_min(x, None, "manhattan")
+    assert torch.equal(args.cpu(), torch.arange(70)) and float(mns.abs().max()) == 0.0
+    # k = 0: one True per row, at the nearest x2 row
+    mask = tpw.k_neighbors_mask(x, y, 0)
+    assert mask.dtype == torch.bool and torch.equal(mask.sum(1).cpu(), torch.ones(70, dtype=torch.int64))
+    assert torch.equal(mask.float().argmax(1), arg32)
+    assert torch.equal(mask, tpw.k_neighbors_mask(x.double(), y.double(), 0))
+    with pytest.raises(ValueError, match="supports"):
+        tpw.pairwise_argmin_min(x, y, "cosine")
+    with pytest.raises(RuntimeError, match="no rows"):
+        tpw.pairwise_argmin_min(x, y[:0])
+    with pytest.raises(RuntimeError, match="positive"):
+        tpw.pairwise_argmin_min(x, y, "minkowski", -1.0)
+    e_arg, e_mn = tpw.pairwise_argmin_min(x[:0], y)
+    assert e_arg.shape == (0,) and e_mn.shape == (0,)
 
 
 def test_bounded_wait_reports_instead_of_hanging(tpw):

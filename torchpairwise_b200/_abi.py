@@ -39,6 +39,8 @@ SIGNATURES = {
     "tpw_device_status": (_I, [POINTER(c_int), _P]),
     "tpw_selftest_bounded_wait": (_I, [_I, _P]),
     "tpw_lp_forward": (_I, [_I, _P, _P, _P, _P, _L, _L, _L, _L, _D, _D, _P]),
+    "tpw_lp_rowmin_scratch_bytes": (_L, [_L, _L]),
+    "tpw_lp_rowmin_forward": (_I, [_I, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _D, _D, _P]),
     "tpw_lp_backward": (_I, [_I, _I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _D, _P]),
     "tpw_wminkowski_backward_w": (_I, [_I, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _D, _P]),
     "tpw_lp_inf_backward": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _P]),

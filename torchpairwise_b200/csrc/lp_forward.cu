@@ -42,6 +42,9 @@ struct FwdParams {
     int epilogue;        // K_DOT: tpw_dot_epilogue; K_NE*: bit0 = report equal count, bit1 = mean
     int vec_store;       // 4-byte outputs, N2 % 4 == 0, 16-byte aligned base: staged 128-bit stores
     int *status;
+    // Non-NULL (fp32 L_p kinds only): the tile is not stored; every x1 row folds its smallest
+    // finished value, packed as (float bits << 32 | x2 row), into keys[b * N1 + i] with atomicMin.
+    unsigned long long *rowmin_keys;
 };
 
 template <typename T> struct Vec16;
@@ -329,6 +332,35 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
         __syncthreads();
     }
 
+    if constexpr (sizeof(T) == 4 && sizeof(OutT) == 4 && (KIND == K_L1 || KIND == K_P2 || KIND == K_P3 || KIND == K_PGEN || KIND == K_MAX)) {
+        if (P.rowmin_keys) {
+            // Streaming row minimum: distances are non-negative, so their float bit patterns order
+            // like unsigned integers and the x2 row in the low word breaks ties towards the smaller
+            // index. The 16 threads that share an x1 row sit in one half warp: four xor shuffles,
+            // then one atomicMin per row and column tile. A NaN distance sorts above +inf.
+            unsigned long long *keys = P.rowmin_keys + b * P.N1;
+#pragma unroll
+            for (int ri = 0; ri < R; ++ri) {
+                unsigned long long best = ~0ull;
+#pragma unroll
+                for (int rj = 0; rj < R; ++rj) {
+                    const long long j = j0 + tj + 16 * rj;
+                    const float v = (float)finish<T, OutT, KIND>(acc[ri][rj], T(0), T(0), P);
+                    const unsigned long long key = ((unsigned long long)__float_as_uint(v) << 32) | (unsigned long long)(uint32_t)j;
+                    if (j < P.N2 && key < best) best = key;
+                }
+#pragma unroll
+                for (int off = 1; off < 16; off <<= 1) {
+                    const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, off);
+                    best = other < best ? other : best;
+                }
+                const long long i = i0 + ti + 16 * ri;
+                if (tj == 0 && i < P.N1) atomicMin(keys + i, best);
+            }
+            return;
+        }
+    }
+
     OutT *out = reinterpret_cast<OutT *>(P.out) + b * P.N1 * P.N2;
     if (sizeof(OutT) == 4 && P.vec_store) {
         // Full tiles of 4-byte outputs go through shared memory (the operand stages are free now):
@@ -413,6 +445,17 @@ int launch_forward(FwdParams P, cudaStream_t stream) {
     return TPW_OK;
 }
 
+// keys -> (smallest distance, its x2 row); a row that saw no x2 row keeps +inf and index -1.
+__global__ void rowmin_finish_kernel(const unsigned long long *__restrict__ keys, float *__restrict__ min_out,
+                                     long long *__restrict__ arg_out, long long n) {
+    const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (t >= n) return;
+    const unsigned long long key = keys[t];
+    const bool none = key == ~0ull;
+    if (min_out) min_out[t] = none ? __int_as_float(0x7f800000) : __uint_as_float((uint32_t)(key >> 32));
+    if (arg_out) arg_out[t] = none ? -1ll : (long long)(uint32_t)key;
+}
+
 template <typename T, int KIND>
 int launch_forward_w(const FwdParams &P, cudaStream_t stream) {
     if (P.w) return launch_forward<T, T, KIND, true>(P, stream);
@@ -457,6 +500,42 @@ extern "C" int tpw_lp_forward(int dtype, const void *x1, const void *x2, const v
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return dtype == TPW_F32 ? lp_forward_typed<float>(P, p, out_exponent, s)
                             : lp_forward_typed<double>(P, p, out_exponent, s);
+}
+
+extern "C" int64_t tpw_lp_rowmin_scratch_bytes(int64_t B, int64_t N1) {
+    if (B <= 0 || N1 <= 0) return 0;
+    return B * N1 * (int64_t)sizeof(unsigned long long);
+}
+
+extern "C" int tpw_lp_rowmin_forward(int dtype, const void *x1, const void *x2, const void *w,
+                                     float *min_out, int64_t *arg_out, void *scratch,
+                                     int64_t B, int64_t N1, int64_t N2, int64_t D,
+                                     double p, double out_exponent, tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(dtype == TPW_F32, "tpw_lp_rowmin_forward: dtype must be TPW_F32 (the key packs a 32-bit distance)");
+    TPW_CHECK_ARG(B >= 0 && N1 >= 0 && N2 >= 0 && D >= 0, "tpw_lp_rowmin_forward: negative size");
+    if (B == 0 || N1 == 0) return TPW_OK;
+    TPW_CHECK_ARG(scratch != nullptr && (min_out || arg_out), "tpw_lp_rowmin_forward: NULL pointer");
+    TPW_CHECK_ARG(p > 0 && !isnan(p) && !isnan(out_exponent), "tpw_lp_rowmin_forward: p must be positive (got %g)", p);
+    TPW_CHECK_ARG(N2 < (1ll << 32), "tpw_lp_rowmin_forward: N2 must fit 32 bits");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const long long n = B * N1;
+    TPW_CUDA_OK(cudaMemsetAsync(scratch, 0xFF, (size_t)n * sizeof(unsigned long long), s));
+    if (N2 > 0) {
+        TPW_CHECK_ARG(x1 && x2, "tpw_lp_rowmin_forward: NULL pointer");
+        TPW_CHECK_ARG(D > 0, "tpw_lp_rowmin_forward: D must be positive");
+        FwdParams P;
+        memset(&P, 0, sizeof(P));
+        P.x1 = x1; P.x2 = x2; P.w = w; P.out = nullptr;
+        P.B = B; P.N1 = N1; P.N2 = N2; P.D = D;
+        P.rowmin_keys = static_cast<unsigned long long *>(scratch);
+        int st = lp_forward_typed<float>(P, p, out_exponent, s);
+        if (st != TPW_OK) return st;
+    }
+    rowmin_finish_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(static_cast<const unsigned long long *>(scratch), min_out,
+                                                                     reinterpret_cast<long long *>(arg_out), n);
+    TPW_LAUNCH_OK("rowmin_finish_kernel");
+    return TPW_OK;
 }
 
 extern "C" int tpw_dot_metric_forward_simt(int dtype, int epilogue, const void *x1, const void *x2, void *out,

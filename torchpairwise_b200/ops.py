@@ -911,8 +911,68 @@ def k_neighbors_mask(x1: Tensor, x2: Optional[Tensor] = None, k: int = 1, metric
     if k < 0:
         raise RuntimeError(f"k must be non-negative. Got k={k}")
     with torch.no_grad():
+        if (k == 0 and metric in _ROWMIN_METRICS and x1_.dtype == torch.float32 and x2_.dtype == torch.float32
+                and x1_.is_cuda and x2_.size(0) > 0 and set(kwargs) <= {"p"}):
+            # one column per row: the streaming row minimum, no distance matrix and no sort
+            inds = pairwise_argmin_min(x1_, x2_, metric, kwargs.get("p"))[0].unsqueeze(1)
+            out = torch.zeros((x1_.size(0), x2_.size(0)), dtype=torch.bool, device=x1_.device)
+            return out.scatter_(1, inds, True)
         dists = cdist(x1_, x2_, metric, **kwargs)
         inds = dists.argsort(dim=1, descending=False)[:, : k + 1]
         out = torch.zeros((x1_.size(0), x2_.size(0)), dtype=torch.bool, device=x1_.device)
         out.scatter_(1, inds, True)
         return out
+
+
+_ROWMIN_METRICS = {
+    # metric -> (p, out_exponent); None = taken from the `p` argument
+    "euclidean": (2.0, 0.5), "l2": (2.0, 0.5),
+    "sqeuclidean": (2.0, 1.0),
+    "manhattan": (1.0, 1.0), "cityblock": (1.0, 1.0), "l1": (1.0, 1.0),
+    "chebyshev": (math.inf, 1.0), "linf": (math.inf, 1.0),
+    "minkowski": (None, None), "lp": (None, None),
+}
+
+
+def pairwise_argmin_min(x1: Tensor, x2: Optional[Tensor] = None, metric: str = "euclidean",
+                        p: Optional[float] = None) -> Tuple[Tensor, Tensor]:
+    """For every x1 row, the x2 row at the smallest distance and that distance:
+    ``(argmin [.., N1] int64, min [.., N1])``, ties to the smaller index, no gradient.
+
+    float32 inputs stream through the L_p tile kernel, whose epilogue folds each tile into one
+    64-bit key per row (warp shuffles, then atomicMin) so the [N1, N2] matrix is never written;
+    the values equal ``minkowski_distances(...).min(-1)``. The reference has no such operator: it
+    sorts whole rows of the materialised matrix (k_neighbors_mask, OPS/neighbors.cpp:10-35).
+    Other floating dtypes take this package's distance kernel followed by ``Tensor.min``.
+    """
+    if metric not in _ROWMIN_METRICS:
+        raise ValueError(f"pairwise_argmin_min supports {sorted(_ROWMIN_METRICS)}; got {metric!r}")
+    pp, ex = _ROWMIN_METRICS[metric]
+    if pp is None:
+        pp = 2.0 if p is None else float(p)
+        if not pp > 0:
+            raise RuntimeError(f"p must be positive. Got p={pp}")
+        ex = 1.0 if math.isinf(pp) else 1.0 / pp
+    x1_, x2_ = check_pairwise_inputs("pairwise_argmin_min", x1, x2)
+    _require_cuda(x1_, x2_)
+    with torch.no_grad():
+        x1c, x2c, unbatched = _batched(x1_, x2_, "pairwise_argmin_min")
+        B, N1, N2, D = _sizes(x1c, x2c)
+        if N2 == 0:
+            raise RuntimeError("pairwise_argmin_min: x2 has no rows")
+        if x1c.dtype != torch.float32 or D == 0:
+            dist = _lp_forward_raw(x1c.to(_compute_dtype(x1c.dtype)), x2c.to(_compute_dtype(x2c.dtype)), None, pp, ex)
+            mins, args = dist.min(dim=-1)
+            mins = mins.to(x1c.dtype)
+        else:
+            mins = torch.empty((B, N1), dtype=torch.float32, device=x1c.device)
+            args = torch.empty((B, N1), dtype=torch.int64, device=x1c.device)
+            nbytes = lib.tpw_lp_rowmin_scratch_bytes(B, N1)
+            scratch = torch.empty((max(nbytes, 8) // 8,), dtype=torch.int64, device=x1c.device)
+            with torch.cuda.device(x1c.device):
+                check(lib.tpw_lp_rowmin_forward(_abi.F32, _ptr(x1c), _ptr(x2c), None, _ptr(mins), _ptr(args),
+                                                _ptr(scratch), B, N1, N2, D, pp, ex, _stream(x1c)),
+                      "tpw_lp_rowmin_forward")
+        if unbatched:
+            mins, args = mins.squeeze(0), args.squeeze(0)
+        return args, mins

@@ -178,7 +178,9 @@ enum tpw_dot_epilogue {
 enum tpw_dot_engine {
     TPW_ENGINE_AUTO = 0,
     TPW_ENGINE_SIMT_FP32 = 1,   /* CUDA-core tile, exact fp32/fp64 FMA chain */
-    TPW_ENGINE_TCGEN05_BF16X3 = 2 /* TMA-fed tcgen05.mma, bf16 hi/lo split (3 MMAs), fp32 TMEM accumulators */
+    TPW_ENGINE_TCGEN05_BF16X3 = 2, /* TMA-fed tcgen05.mma, bf16 hi/lo split (3 MMAs), fp32 TMEM accumulators */
+    TPW_ENGINE_TCGEN05_TF32X3 = 3  /* same pipeline with tf32 hi/lo parts (22 bits per factor): the gradient
+                                      products of tpw_dot_backward_ws; not a forward engine */
 };
 
 /*
@@ -194,6 +196,27 @@ TPW_API int64_t tpw_dot_metric_scratch_bytes(int dtype, int engine, int64_t B, i
 TPW_API int tpw_dot_metric_forward_ws(int dtype, int epilogue, int engine,
                               const void *x1, const void *x2, void *out, void *scratch, int64_t scratch_bytes,
                               int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream);
+
+/*
+ * Backward of the p = 2 metrics and the plain gradient products as two tensor-core contractions:
+ *   TPW_LP_BWD_PPMINKOWSKI (sqeuclidean): C = g,      grad_x1 = 2 (x1 * rowsum(C) - C x2),  grad_x2 = 2 (x2 * colsum(C) - C^T x1)
+ *   TPW_LP_BWD_CDIST       (euclidean):   C = g / o (0 where o == 0), same without the factor 2; aux = o
+ *   TPW_LP_BWD_MATMUL:                    grad_x1 = g x2, grad_x2 = g^T x1
+ * (OPS/cpu/ppminkowski_kernel.cpp:131-169 for p = 2; ATen's cdist backward under
+ * OPS/pairwise_metrics.cpp:30; the matmul nodes under :64,121,203.)  A pre-pass writes C and C^T
+ * as tf32 high/low parts, tcgen05.mma accumulates hi.hi + hi.lo + lo.hi in fp32, row and column
+ * sums are reduced in a fixed order: deterministic, about 2^-21 relative error per product.
+ * engine AUTO picks this for float32 with D >= 64, N1, N2 >= 256 and B*N1*N2*D >= 2^28 when the
+ * scratch is large enough, otherwise the call is tpw_lp_backward(p = 2) on the CUDA cores;
+ * engine SIMT_FP32 always is; either TCGEN05 value forces the tensor cores (float32 only).
+ * scratch: tpw_dot_backward_scratch_bytes(...) bytes (0 = CUDA-core path), 16-byte aligned;
+ * about 16 bytes per element of grad.  grad_x1 or grad_x2 may be NULL.
+ */
+TPW_API int64_t tpw_dot_backward_scratch_bytes(int dtype, int mode, int engine, int64_t B, int64_t N1, int64_t N2, int64_t D);
+TPW_API int tpw_dot_backward_ws(int dtype, int mode, int engine, const void *grad, const void *aux,
+                        const void *x1, const void *x2, void *grad_x1, void *grad_x2,
+                        void *scratch, int64_t scratch_bytes,
+                        int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream);
 
 /* Row helpers used by cosine / correlation host code (x.norm(2,-1), x - x.mean(-1):
    OPS/pairwise_metrics.cpp:118-119,197-201). rows = B*N. */

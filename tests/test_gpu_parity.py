@@ -422,6 +422,122 @@ def test_tensor_core_engine_details(tensor_engine, golden):
           TOL[torch.float64])
 
 
+def _sum_close(got, ref, msg):
+    """Gradients are sums of K signed terms: float32 evaluation orders differ by about 1e-7 * sqrt(K) of
+    the typical magnitude, so the absolute slack is tied to the RMS of the reference (plus the
+    contract's relative 1e-4 per element)."""
+    ref = ref.double()
+    bound = 1e-4 * ref.abs() + 2e-5 * ref.pow(2).mean().sqrt() + 1e-5
+    err = (got.double() - ref).abs()
+    worst = float((err / bound).max())
+    assert worst <= 1.0, f"{msg}: max error / bound = {worst:.3f} (max abs error {float(err.max()):.3e})"
+
+
+DENSE_BWD_OPS = {
+    "sqeuclidean": lambda t, a, b: t.sqeuclidean_distances(a, b),
+    "euclidean": lambda t, a, b: t.euclidean_distances(a, b),
+    "cosine_similarity": lambda t, a, b: t.cosine_similarity(a, b),
+    "correlation": lambda t, a, b: t.correlation_distances(a, b),
+    "linear_kernel": lambda t, a, b: t.linear_kernel(a, b),
+}
+
+
+@pytest.mark.parametrize("shape", [(1, 300, 520, 96), (2, 257, 1030, 130), (3, 129, 67, 33), (1, 64, 4100, 8), (1, 1, 1, 4)],
+                         ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("op", sorted(DENSE_BWD_OPS))
+def test_tensor_core_backward_vs_float64(tensor_engine, shape, op):
+    """The tf32x3 tcgen05 gradient products (forced) against the float64 CUDA-core kernels of the same
+    operator, next to the float32 CUDA-core result held to the same bound."""
+    tpw = tensor_engine
+    B, n1, n2, d = shape
+    g = torch.Generator().manual_seed(sum(shape) + len(op))
+    x1 = torch.randn(B, n1, d, generator=g).cuda()
+    x2 = torch.randn(B, n2, d, generator=g).cuda()
+    up = torch.randn(B, n1, n2, generator=g).cuda()
+
+    def grads(a, b, u):
+        a, b = a.clone().requires_grad_(True), b.clone().requires_grad_(True)
+        DENSE_BWD_OPS[op](tpw, a, b).backward(u)
+        return a.grad, b.grad
+
+    r1, r2 = grads(x1.double(), x2.double(), up.double())
+    t1, t2 = grads(x1, x2, up)
+    _sum_close(t1, r1, f"{op} grad_x1 (tensor cores)")
+    _sum_close(t2, r2, f"{op} grad_x2 (tensor cores)")
+    tpw.set_dot_engine("simt")
+    s1, s2 = grads(x1, x2, up)
+    tpw.set_dot_engine("tcgen05")
+    _sum_close(s1, r1, f"{op} grad_x1 (CUDA cores)")
+    _sum_close(s2, r2, f"{op} grad_x2 (CUDA cores)")
+
+
+def test_tensor_core_backward_blocking_and_abi(tensor_engine, monkeypatch):
+    """Scratch-capped blocking (groups of batches, row blocks of one batch) reproduces the single
+    call; one-sided gradients; argument checks of the C entry point."""
+    tpw = tensor_engine
+    from torchpairwise_b200 import _abi
+    lib = _abi.lib
+    g = torch.Generator().manual_seed(5)
+    x1 = torch.randn(3, 600, 64, generator=g).cuda()
+    x2 = torch.randn(3, 520, 64, generator=g).cuda()
+    up = torch.randn(3, 600, 520, generator=g).cuda()
+
+    def grads(need2=True):
+        a, b = x1.clone().requires_grad_(True), x2.clone().requires_grad_(need2)
+        tpw.sqeuclidean_distances(a, b).backward(up)
+        return a.grad, b.grad
+
+    full1, full2 = grads()
+    per_batch = lib.tpw_dot_backward_scratch_bytes(_abi.F32, _abi.LP_BWD_PPMINKOWSKI, _abi.ENGINE_TCGEN05_TF32X3, 1, 600, 520, 64)
+    assert per_batch > 16 * 600 * 520
+    monkeypatch.setenv("TPW_BWD_SCRATCH_GB", str(2.5 * per_batch / 2 ** 30))   # groups of two batches
+    b1, b2 = grads()
+    assert torch.equal(b1, full1) and torch.equal(b2, full2)
+    monkeypatch.setenv("TPW_BWD_SCRATCH_GB", str(0.5 * per_batch / 2 ** 30))   # row blocks of 256 within a batch
+    r1, r2 = grads()
+    assert torch.equal(r1, full1)
+    _sum_close(r2, full2, "row-blocked grad_x2")
+    monkeypatch.delenv("TPW_BWD_SCRATCH_GB")
+    o1, o2 = grads(need2=False)
+    assert o2 is None and torch.equal(o1, full1)
+    # C entry point: too little scratch is an error when the engine is forced, a CUDA-core call under AUTO
+    nb = lib.tpw_dot_backward_scratch_bytes(_abi.F32, _abi.LP_BWD_MATMUL, _abi.ENGINE_TCGEN05_TF32X3, 3, 600, 520, 64)
+    small = torch.empty(1024, dtype=torch.uint8, device="cuda")
+    g1, g2 = torch.empty_like(x1), torch.empty_like(x2)
+    st = torch.cuda.current_stream().cuda_stream
+    args = (up.data_ptr(), None, x1.data_ptr(), x2.data_ptr(), g1.data_ptr(), g2.data_ptr(), small.data_ptr(), 1024, 3, 600, 520, 64, st)
+    assert lib.tpw_dot_backward_ws(_abi.F32, _abi.LP_BWD_MATMUL, _abi.ENGINE_TCGEN05_TF32X3, *args) == 1
+    assert "scratch" in lib.tpw_last_error().decode()
+    assert lib.tpw_dot_backward_ws(_abi.F32, _abi.LP_BWD_WMINKOWSKI, _abi.ENGINE_AUTO, *args) == 1
+    assert lib.tpw_dot_backward_ws(_abi.F32, _abi.LP_BWD_MATMUL, _abi.ENGINE_AUTO, *args) == 0
+    _sum_close(g1, up.double() @ x2.double(), "AUTO without scratch runs the CUDA-core products")
+    assert nb > 0 and lib.tpw_dot_backward_scratch_bytes(_abi.F64, _abi.LP_BWD_MATMUL, _abi.ENGINE_AUTO, 1, 4096, 4096, 512) == 0
+    assert lib.tpw_dot_backward_scratch_bytes(_abi.F32, _abi.LP_BWD_MATMUL, _abi.ENGINE_AUTO, 1, 4096, 4096, 512) > 0
+    assert lib.tpw_dot_backward_scratch_bytes(_abi.F32, _abi.LP_BWD_MATMUL, _abi.ENGINE_AUTO, 1, 200, 200, 64) == 0
+    assert lib.tpw_dot_backward_scratch_bytes(_abi.F32, _abi.LP_BWD_WMINKOWSKI, _abi.ENGINE_TCGEN05_TF32X3, 1, 4096, 4096, 512) == 0
+
+
+def test_full_size_dense_backward(tpw):
+    """A quarter of C4 (X[32768,512], Y[16384,512], 2.1 GB of upstream gradient) through the engine
+    rule: the sqeuclidean backward runs as row-blocked tensor-core contractions; checked by
+    translation invariance and by float64 evaluation of sampled rows of both gradients."""
+    g = torch.Generator().manual_seed(3)
+    X = torch.randn(32768, 512, generator=g).cuda().requires_grad_(True)
+    Y = torch.randn(16384, 512, generator=g).cuda().requires_grad_(True)
+    up = torch.randn(32768, 16384, generator=g).cuda()
+    tpw.sqeuclidean_distances(X, Y).backward(up)
+    resid = X.grad.double().sum(0) + Y.grad.double().sum(0)
+    mag = X.grad.double().abs().sum(0) + Y.grad.double().abs().sum(0)
+    assert float((resid.abs() / mag).max()) < 1e-5
+    Xd, Yd = X.detach().double(), Y.detach().double()
+    rows = torch.arange(0, 32768, 512, device="cuda")
+    ud = up[rows].double()
+    _sum_close(X.grad[rows], 2 * (Xd[rows] * ud.sum(1, keepdim=True) - ud @ Yd), "C4 quarter grad_x1 rows")
+    cols = torch.arange(0, 16384, 256, device="cuda")
+    uc = up[:, cols].double()
+    _sum_close(Y.grad[cols], 2 * (Yd[cols] * uc.sum(0).unsqueeze(1) - uc.t() @ Xd), "C4 quarter grad_x2 rows")
+
+
 def test_engine_auto_selection(tpw):
     from torchpairwise_b200 import _abi
     lib = _abi.lib

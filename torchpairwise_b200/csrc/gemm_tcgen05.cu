@@ -31,6 +31,7 @@ constexpr int BM = 128;           // rows of x1 per tile (TMEM lanes)
 constexpr int BN = 256;           // rows of x2 per tile (TMEM columns per accumulator)
 constexpr int BK = 64;            // bf16 per k-step: 128 bytes
 constexpr int kStages = 2;
+constexpr int kMmasPerStep = 4;    // a 128-byte operand row feeds four MMAs of 32 bytes (16 bf16 or 8 tf32) each
 constexpr int A_BYTES = BM * BK * 2;          // 16 KB
 constexpr int B_BYTES = BN * BK * 2;          // 32 KB
 constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES; // xh | xl | yh | yl = 96 KB
@@ -56,6 +57,7 @@ struct GemmParams {
     int epilogue;
     int self;                 // x2 is x1: the diagonal of the distance epilogues is exactly zero
     int vec_store;            // N2 % 4 == 0 and out 16-byte aligned
+    int kchunk;               // k-steps accumulated in tensor memory before the sum moves to registers (0: all)
     int *status;
 };
 
@@ -76,14 +78,24 @@ __device__ __forceinline__ void tc_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
 }
-// D[tmem] (+)= A[smem] * B[smem]^T, bf16 operands, fp32 accumulate
-__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
+// D[tmem] (+)= A[smem] * B[smem]^T, fp32 accumulate; TF32 = false: bf16 operands (K = 16 per
+// instruction), true: tf32 operands in 32-bit containers (K = 8 per instruction)
+template <bool TF32>
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    if (TF32)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
 }
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp receives lane (base + t)
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -113,10 +125,12 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
     d |= (uint64_t)2 << 61;
     return d;
 }
-// Instruction descriptor, kind::f16: D = fp32 (bits [4,6) = 1), A = B = bf16 (bits [7,10) = [10,13) = 1),
-// both K-major (bits 15, 16 = 0), N >> 3 in bits [17,23), M >> 4 in bits [24,29).
-__device__ __forceinline__ uint32_t make_idesc(int M, int N) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+// Instruction descriptor: D = fp32 (bits [4,6) = 1); A and B formats in bits [7,10) and [10,13):
+// 1 = bf16 under kind::f16, 2 = tf32 under kind::tf32; both K-major (bits 15, 16 = 0);
+// N >> 3 in bits [17,23), M >> 4 in bits [24,29).
+__device__ __forceinline__ uint32_t make_idesc(int M, int N, bool tf32) {
+    const uint32_t fmt = tf32 ? 2u : 1u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
 // Bounded mbarrier wait that also gives up when another role raised the abort flag.
@@ -144,7 +158,10 @@ __device__ __forceinline__ float dot_epilogue(float dot, float n1, float n2, boo
     return dist;
 }
 
-template <int EPI, bool SELF>
+// TF32 = false: operands are bf16 high/low parts, 64 per k-step; true: tf32 high/low parts in fp32
+// containers, 32 per k-step.  Either way a k-step is one 128-byte swizzled row per operand row and
+// four MMAs per operand pair, so the pipeline below is the same.
+template <int EPI, bool SELF, bool TF32>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_constant__ CUtensorMap map_xl,
                    const __grid_constant__ CUtensorMap map_yh, const __grid_constant__ CUtensorMap map_yl,
@@ -161,7 +178,8 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + OFF_ABORT);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nkb = (int)((P.D + BK - 1) / BK);
+    constexpr int BKE = TF32 ? BK / 2 : BK; // operand elements per k-step
+    const int nkb = (int)((P.D + BKE - 1) / BKE);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&full_lo[s], 1); mbar_init(&empty[s], 1); }
@@ -203,61 +221,67 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
                     }
                     unsigned char *st = smem + s * STAGE_BYTES;
                     mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-                    tma_load_3d(st, &map_xh, &full[s], kb * BK, (int)(tm * BM), (int)b);
-                    tma_load_3d(st + 2 * A_BYTES, &map_yh, &full[s], kb * BK, (int)(tn * BN), (int)b);
+                    tma_load_3d(st, &map_xh, &full[s], kb * BKE, (int)(tm * BM), (int)b);
+                    tma_load_3d(st + 2 * A_BYTES, &map_yh, &full[s], kb * BKE, (int)(tn * BN), (int)b);
                     mbar_expect_tx(&full_lo[s], A_BYTES + B_BYTES);
-                    tma_load_3d(st + A_BYTES, &map_xl, &full_lo[s], kb * BK, (int)(tm * BM), (int)b);
-                    tma_load_3d(st + 2 * A_BYTES + B_BYTES, &map_yl, &full_lo[s], kb * BK, (int)(tn * BN), (int)b);
+                    tma_load_3d(st + A_BYTES, &map_xl, &full_lo[s], kb * BKE, (int)(tm * BM), (int)b);
+                    tma_load_3d(st + 2 * A_BYTES + B_BYTES, &map_yl, &full_lo[s], kb * BKE, (int)(tn * BN), (int)b);
                 }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            const uint32_t idesc = make_idesc(BM, BN);
-            uint32_t it = 0, tcount = 0;
+            const uint32_t idesc = make_idesc(BM, BN, TF32);
+            uint32_t it = 0, acount = 0;
             bool ok = true;
-            for (long long tile = blockIdx.x; tile < P.tiles && ok; tile += gridDim.x, ++tcount) {
-                const uint32_t a = tcount & 1, ause = tcount >> 1;
-                if (ause > 0 && !wait_or_abort(&tmem_empty[a], (ause - 1) & 1, abort_flag)) {
-                    *abort_flag = 1;
-                    if (P.status) atomicCAS(P.status, 0, (4 << 16) | 2);
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + a * BN;
-                for (int kb = 0; kb < nkb; ++kb, ++it) {
-                    const int s = it % kStages;
-                    if (!wait_or_abort(&full[s], (it / kStages) & 1, abort_flag)) {
+            const int kchunk = (P.kchunk > 0 && P.kchunk < nkb) ? P.kchunk : nkb;
+            for (long long tile = blockIdx.x; tile < P.tiles && ok; tile += gridDim.x) {
+                // one accumulator per chunk of k-steps: the tensor cores add into tensor memory with
+                // truncation, so long reductions are cut into chunks that the epilogue sums in registers
+                for (int kb0 = 0; kb0 < nkb && ok; kb0 += kchunk, ++acount) {
+                    const uint32_t a = acount & 1, ause = acount >> 1;
+                    if (ause > 0 && !wait_or_abort(&tmem_empty[a], (ause - 1) & 1, abort_flag)) {
                         *abort_flag = 1;
-                        if (P.status) atomicCAS(P.status, 0, (4 << 16) | 3);
+                        if (P.status) atomicCAS(P.status, 0, (4 << 16) | 2);
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t sb = smem_u32(smem + s * STAGE_BYTES);
-                    const uint64_t dxh = make_smem_desc(sb), dxl = make_smem_desc(sb + A_BYTES);
-                    const uint64_t dyh = make_smem_desc(sb + 2 * A_BYTES), dyl = make_smem_desc(sb + 2 * A_BYTES + B_BYTES);
-                    // 16 bf16 = 32 bytes along the swizzled row per MMA: advance the start address by 2 units
+                    const uint32_t d_tmem = tmem_base + a * BN;
+                    const int kb1 = kb0 + kchunk < nkb ? kb0 + kchunk : nkb;
+                    for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                        const int s = it % kStages;
+                        if (!wait_or_abort(&full[s], (it / kStages) & 1, abort_flag)) {
+                            *abort_flag = 1;
+                            if (P.status) atomicCAS(P.status, 0, (4 << 16) | 3);
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint32_t sb = smem_u32(smem + s * STAGE_BYTES);
+                        const uint64_t dxh = make_smem_desc(sb), dxl = make_smem_desc(sb + A_BYTES);
+                        const uint64_t dyh = make_smem_desc(sb + 2 * A_BYTES), dyl = make_smem_desc(sb + 2 * A_BYTES + B_BYTES);
+                        // one MMA consumes 32 bytes of the swizzled row (16 bf16 or 8 tf32): advance the start address by 2 units
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)
-                        tc_mma_bf16(d_tmem, dxh + 2 * k, dyh + 2 * k, idesc, (kb | k) != 0);
-                    if (!wait_or_abort(&full_lo[s], (it / kStages) & 1, abort_flag)) {
-                        *abort_flag = 1;
-                        if (P.status) atomicCAS(P.status, 0, (4 << 16) | 5);
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after();
+                        for (int k = 0; k < kMmasPerStep; ++k)
+                            tc_mma<TF32>(d_tmem, dxh + 2 * k, dyh + 2 * k, idesc, ((kb - kb0) | k) != 0);
+                        if (!wait_or_abort(&full_lo[s], (it / kStages) & 1, abort_flag)) {
+                            *abort_flag = 1;
+                            if (P.status) atomicCAS(P.status, 0, (4 << 16) | 5);
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k) {
-                        tc_mma_bf16(d_tmem, dxh + 2 * k, dyl + 2 * k, idesc, 1);
-                        tc_mma_bf16(d_tmem, dxl + 2 * k, dyh + 2 * k, idesc, 1);
+                        for (int k = 0; k < kMmasPerStep; ++k) {
+                            tc_mma<TF32>(d_tmem, dxh + 2 * k, dyl + 2 * k, idesc, 1);
+                            tc_mma<TF32>(d_tmem, dxl + 2 * k, dyh + 2 * k, idesc, 1);
+                        }
+                        tc_commit(&empty[s]); // the stage may be refilled once these MMAs have read it
                     }
-                    tc_commit(&empty[s]); // the stage may be refilled once these MMAs have read it
+                    if (ok) tc_commit(&tmem_full[a]);
                 }
-                if (ok) tc_commit(&tmem_full[a]);
             }
         }
     } else {
@@ -266,6 +290,74 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
         const int chalf = (warp - 2) >> 2;
         uint32_t tcount = 0;
         bool ok = true;
+        if constexpr (TF32) {
+            // Chunked reduction (plain products only): every chunk's accumulator is added, rounded to
+            // nearest, into 128 register-resident sums per thread; the tile is stored after its last chunk.
+            static_assert(!TF32 || EPI == TPW_DOT_LINEAR, "the tf32 pipeline serves the plain products");
+            const int kchunk = (P.kchunk > 0 && P.kchunk < nkb) ? P.kchunk : nkb;
+            const int nchunks = (nkb + kchunk - 1) / kchunk;
+            uint32_t acount = 0;
+            for (long long tile = blockIdx.x; tile < P.tiles && ok; tile += gridDim.x) {
+                long long t = tile;
+                const long long tn = t % P.tiles_n; t /= P.tiles_n;
+                const long long tm = t % P.tiles_m;
+                const long long b = t / P.tiles_m;
+                float sums[BN / 2];
+#pragma unroll
+                for (int v = 0; v < BN / 2; ++v) sums[v] = 0.f;
+                for (int ch = 0; ch < nchunks && ok; ++ch, ++acount) {
+                    const uint32_t a = acount & 1;
+                    if (!wait_or_abort(&tmem_full[a], (acount >> 1) & 1, abort_flag)) {
+                        *abort_flag = 1;
+                        if (lane == 0 && P.status) atomicCAS(P.status, 0, (4 << 16) | 6);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < BN / 64; ++c) {
+                        uint32_t r[32];
+                        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + a * BN + (chalf * (BN / 64) + c) * 32, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int v = 0; v < 32; ++v) sums[c * 32 + v] += __uint_as_float(r[v]);
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&tmem_empty[a]);
+                }
+                if (!ok) break;
+                const long long i = tm * BM + q * 32 + lane;
+                const bool row_ok = i < P.N1;
+                float *orow = P.out + (b * P.N1 + (row_ok ? i : 0)) * P.N2;
+                unsigned char *stg = smem + OFF_STAGE + (warp - 2) * 4096;
+                const long long row_base = tm * BM + q * 32;
+#pragma unroll
+                for (int c = 0; c < BN / 64; ++c) {
+                    const long long j0 = tn * BN + (chalf * (BN / 64) + c) * 32;
+                    if (j0 >= P.N2) continue;
+                    if (P.vec_store && j0 + 32 <= P.N2) {
+#pragma unroll
+                        for (int v = 0; v < 8; ++v)
+                            *reinterpret_cast<float4 *>(stg + lane * 128 + ((v ^ (lane & 7)) << 4)) =
+                                make_float4(sums[c * 32 + 4 * v], sums[c * 32 + 4 * v + 1], sums[c * 32 + 4 * v + 2], sums[c * 32 + 4 * v + 3]);
+                        __syncwarp();
+#pragma unroll
+                        for (int it = 0; it < 8; ++it) {
+                            const int rr = it * 4 + (lane >> 3), cc = lane & 7;
+                            const float4 o = *reinterpret_cast<const float4 *>(stg + rr * 128 + ((cc ^ (rr & 7)) << 4));
+                            if (row_base + rr < P.N1)
+                                reinterpret_cast<float4 *>(P.out + (b * P.N1 + row_base + rr) * P.N2 + j0)[cc] = o;
+                        }
+                        __syncwarp();
+                    } else if (row_ok) {
+#pragma unroll
+                        for (int v = 0; v < 32; ++v)
+                            if (j0 + v < P.N2) orow[j0 + v] = sums[c * 32 + v];
+                    }
+                }
+            }
+        } else
         for (long long tile = blockIdx.x; tile < P.tiles && ok; tile += gridDim.x, ++tcount) {
             long long t = tile;
             const long long tn = t % P.tiles_n; t /= P.tiles_n;
@@ -281,7 +373,7 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
             tc_fence_after();
             const long long i = tm * BM + q * 32 + lane;
             const bool row_ok = i < P.N1;
-            const float n1 = row_ok ? P.n1sq[b * P.N1 + i] : 0.f;
+            const float n1 = (EPI != TPW_DOT_LINEAR && row_ok) ? P.n1sq[b * P.N1 + i] : 0.f;
             float *orow = P.out + (b * P.N1 + (row_ok ? i : 0)) * P.N2;
             const float *n2p = P.n2sq + b * P.N2;
 #pragma unroll 1
@@ -323,7 +415,7 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
                     for (int v = 0; v < 32; ++v) {
                         const long long j = j0 + v;
                         if (j < P.N2)
-                            orow[j] = dot_epilogue<EPI>(__uint_as_float(r[v]), n1, __ldg(n2p + j), SELF && i == j);
+                            orow[j] = dot_epilogue<EPI>(__uint_as_float(r[v]), n1, EPI == TPW_DOT_LINEAR ? 0.f : __ldg(n2p + j), SELF && i == j);
                     }
                 }
             }
@@ -397,6 +489,215 @@ inline ScratchLayout scratch_layout(long long B, long long N1, long long N2, lon
     L.off_n2 = self ? L.off_n1 : L.off_n1 + align_up(B * N1 * 4, 1024);
     L.total = L.off_n2 + align_up(B * N2 * 4, 1024);
     return L;
+}
+
+
+// ---- gradient products on the tensor cores (tf32 x 3) ---------------------------------------------
+//
+// grad_x1 = s_mm * (C . X2) + s_row * x1 * rowsum(C),  grad_x2 = s_mm * (C^T . X1) + s_row * x2 * colsum(C)
+// with C = g (squared Euclidean, plain products) or g / o (Euclidean).  Each operand is split into
+// two tf32 numbers, hi = rn_tf32(v) and lo = rn_tf32(v - hi), and hi.hi + hi.lo + lo.hi is
+// accumulated in fp32: 22 bits of every factor take part, so the products carry about 2^-21 of
+// relative error, two orders below the float32 parity tolerance even for sums that cancel.
+
+__device__ __forceinline__ float rn_tf32(float v) {
+    uint32_t u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
+    return __uint_as_float(u);
+}
+
+enum { COEF_ID = 0, COEF_DIV_AUX = 1 };
+constexpr int PT = 64;        // pre-pass tile edge
+constexpr int PT_PITCH = 65;  // shared-memory pitch (floats) of the transposing tile
+
+struct SplitParams {
+    const float *a, *aux;       // [B,R,C]
+    float *hi, *lo;             // [B,R,Cp]   (STRAIGHT)
+    float *thi, *tlo;           // [B,C,Rp]   (TRANSPOSED)
+    float *rowpart, *colpart;   // [B,TC,R], [B,TR,C]   (SUMS)
+    long long R, C, Rp, Cp, TR, TC;
+    int vec_in;                 // C % 4 == 0 and 16-byte aligned inputs
+};
+
+// One 64 x 64 tile per CTA of 256 threads: coefficient, tf32 split, straight and transposed copies
+// (row pitches padded to a multiple of 4 and zero filled), per-tile row and column sums.
+template <int MODE, bool STRAIGHT, bool TRANSPOSED, bool SUMS>
+__global__ void __launch_bounds__(256)
+split_tile_kernel(const SplitParams P) {
+    __shared__ float tile[PT * PT_PITCH];
+    const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    const long long b = blockIdx.z;
+    const long long r0 = (long long)blockIdx.y * PT, c0 = (long long)blockIdx.x * PT;
+    const float *a = P.a + b * P.R * P.C;
+    const float *aux = MODE == COEF_DIV_AUX ? P.aux + b * P.R * P.C : nullptr;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int lr = ty + 16 * r;
+        const long long row = r0 + lr, col = c0 + 4 * tx;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (row < P.R) {
+            if (P.vec_in && col + 3 < P.C) {
+                const float4 t = *reinterpret_cast<const float4 *>(a + row * P.C + col);
+                v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+                if (MODE == COEF_DIV_AUX) {
+                    const float4 o = *reinterpret_cast<const float4 *>(aux + row * P.C + col);
+                    v[0] = o.x != 0.f ? __fdiv_rn(v[0], o.x) : 0.f;
+                    v[1] = o.y != 0.f ? __fdiv_rn(v[1], o.y) : 0.f;
+                    v[2] = o.z != 0.f ? __fdiv_rn(v[2], o.z) : 0.f;
+                    v[3] = o.w != 0.f ? __fdiv_rn(v[3], o.w) : 0.f;
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (col + e < P.C) {
+                        v[e] = a[row * P.C + col + e];
+                        if (MODE == COEF_DIV_AUX) {
+                            const float o = aux[row * P.C + col + e];
+                            v[e] = o != 0.f ? __fdiv_rn(v[e], o) : 0.f;
+                        }
+                    }
+            }
+        }
+        if (STRAIGHT && row < P.R && col < P.Cp) {
+            float4 h, l;
+            h.x = rn_tf32(v[0]); l.x = rn_tf32(v[0] - h.x);
+            h.y = rn_tf32(v[1]); l.y = rn_tf32(v[1] - h.y);
+            h.z = rn_tf32(v[2]); l.z = rn_tf32(v[2] - h.z);
+            h.w = rn_tf32(v[3]); l.w = rn_tf32(v[3] - h.w);
+            *reinterpret_cast<float4 *>(P.hi + (b * P.R + row) * P.Cp + col) = h;
+            *reinterpret_cast<float4 *>(P.lo + (b * P.R + row) * P.Cp + col) = l;
+        }
+        if (SUMS) {
+            float s = (v[0] + v[1]) + (v[2] + v[3]);
+#pragma unroll
+            for (int off = 1; off < 16; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+            if (tx == 0 && row < P.R) P.rowpart[(b * P.TC + blockIdx.x) * P.R + row] = s;
+        }
+        if (TRANSPOSED || SUMS) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) tile[lr * PT_PITCH + 4 * tx + e] = v[e];
+        }
+    }
+    if (!(TRANSPOSED || SUMS)) return;
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int lc = ty + 16 * r;                       // tile column = row of the transposed copy
+        const long long col = c0 + lc, row = r0 + 4 * tx; // four consecutive source rows
+        float v[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = tile[(4 * tx + e) * PT_PITCH + lc]; // rows past R hold zeros
+        if (TRANSPOSED && col < P.C && row < P.Rp) {
+            float4 h, l;
+            h.x = rn_tf32(v[0]); l.x = rn_tf32(v[0] - h.x);
+            h.y = rn_tf32(v[1]); l.y = rn_tf32(v[1] - h.y);
+            h.z = rn_tf32(v[2]); l.z = rn_tf32(v[2] - h.z);
+            h.w = rn_tf32(v[3]); l.w = rn_tf32(v[3] - h.w);
+            *reinterpret_cast<float4 *>(P.thi + (b * P.C + col) * P.Rp + row) = h;
+            *reinterpret_cast<float4 *>(P.tlo + (b * P.C + col) * P.Rp + row) = l;
+        }
+        if (SUMS) {
+            float s = (v[0] + v[1]) + (v[2] + v[3]);
+#pragma unroll
+            for (int off = 1; off < 16; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+            if (tx == 0 && col < P.C) P.colpart[(b * P.TR + blockIdx.y) * P.C + col] = s;
+        }
+    }
+}
+
+// sums[b,n] = part[b,0,n] + part[b,1,n] + ... in that order (deterministic)
+__global__ void reduce_partials_kernel(const float *__restrict__ part, float *__restrict__ sums, long long B, long long T, long long N) {
+    const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (t >= B * N) return;
+    const long long b = t / N, n = t % N;
+    float s = 0.f;
+    for (long long k = 0; k < T; ++k) s += part[(b * T + k) * N + n];
+    sums[t] = s;
+}
+
+// g[r,k] = s_mm * g[r,k] + s_row * x[r,k] * sums[r]
+__global__ void grad_finish_kernel(float *__restrict__ g, const float *__restrict__ x, const float *__restrict__ sums,
+                                   long long rows, long long D, float s_mm, float s_row) {
+    const long long n = rows * D;
+    for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < n; t += (long long)gridDim.x * blockDim.x) {
+        const float base = s_mm * g[t];
+        g[t] = sums ? fmaf(s_row * x[t], sums[t / D], base) : base;
+    }
+}
+
+struct BwdScratch {
+    long long N1p, N2p, TR, TC;
+    long long off_chi, off_clo, off_cthi, off_ctlo, off_x2thi, off_x2tlo, off_x1thi, off_x1tlo;
+    long long off_rowpart, off_colpart, off_rowsum, off_colsum, total;
+};
+
+inline BwdScratch bwd_scratch_layout(long long B, long long N1, long long N2, long long D) {
+    BwdScratch L;
+    L.N1p = align_up(N1, 4);
+    L.N2p = align_up(N2, 4);
+    L.TR = (N1 + PT - 1) / PT;
+    L.TC = (N2 + PT - 1) / PT;
+    long long off = 0;
+    auto take = [&](long long bytes) { const long long o = off; off += align_up(bytes, 1024); return o; };
+    L.off_chi = take(B * N1 * L.N2p * 4);
+    L.off_clo = take(B * N1 * L.N2p * 4);
+    L.off_cthi = take(B * N2 * L.N1p * 4);
+    L.off_ctlo = take(B * N2 * L.N1p * 4);
+    L.off_x2thi = take(B * D * L.N2p * 4);
+    L.off_x2tlo = take(B * D * L.N2p * 4);
+    L.off_x1thi = take(B * D * L.N1p * 4);
+    L.off_x1tlo = take(B * D * L.N1p * 4);
+    L.off_rowpart = take(B * L.TC * N1 * 4);
+    L.off_colpart = take(B * L.TR * N2 * 4);
+    L.off_rowsum = take(B * N1 * 4);
+    L.off_colsum = take(B * N2 * 4);
+    L.total = off;
+    return L;
+}
+
+// The tensor-core gradient products pay for their split pre-pass only on large fp32 problems.
+inline bool auto_picks_tensor_backward(int dtype, long long B, long long N1, long long N2, long long D) {
+    return dtype == TPW_F32 && D >= 64 && N1 >= 256 && N2 >= 256 && (double)B * N1 * N2 * D >= (double)(1ll << 28);
+}
+
+template <int MODE, bool STRAIGHT, bool TRANSPOSED, bool SUMS>
+int launch_split(const SplitParams &P, long long B, cudaStream_t s) {
+    const long long gx = (P.C + PT - 1) / PT, gy = (P.R + PT - 1) / PT;
+    TPW_CHECK_ARG(gy <= 65535 && B <= 65535, "dense backward: more than 65535 row tiles or batches");
+    split_tile_kernel<MODE, STRAIGHT, TRANSPOSED, SUMS><<<dim3((unsigned)gx, (unsigned)gy, (unsigned)B), 256, 0, s>>>(P);
+    TPW_LAUNCH_OK("split_tile_kernel");
+    return TPW_OK;
+}
+
+// out[b,m,n] = sum_k a[b,m,k] * bt[b,n,k] from tf32 high/low parts with row pitch Kp
+int launch_tf32_product(const float *ahi, const float *alo, const float *bhi, const float *blo, float *out,
+                        long long B, long long M, long long N, long long Kp, cudaStream_t s) {
+    CUtensorMap mah, mal, mbh, mbl;
+    int st;
+    if ((st = make_tensor_map_3d(&mah, ahi, 4, Kp, M, B, BK / 2, BM, true)) != TPW_OK) return st;
+    if ((st = make_tensor_map_3d(&mal, alo, 4, Kp, M, B, BK / 2, BM, true)) != TPW_OK) return st;
+    if ((st = make_tensor_map_3d(&mbh, bhi, 4, Kp, N, B, BK / 2, BN, true)) != TPW_OK) return st;
+    if ((st = make_tensor_map_3d(&mbl, blo, 4, Kp, N, B, BK / 2, BN, true)) != TPW_OK) return st;
+    GemmParams P;
+    memset(&P, 0, sizeof(P));
+    P.out = out;
+    P.B = B; P.N1 = M; P.N2 = N; P.D = Kp;
+    P.tiles_m = (M + BM - 1) / BM;
+    P.tiles_n = (N + BN - 1) / BN;
+    P.tiles = B * P.tiles_m * P.tiles_n;
+    P.epilogue = TPW_DOT_LINEAR;
+    // 64 elements per chunk: measured against float64, the products are then as accurate as the fp32
+    // FMA chain of the CUDA-core kernel (the error grows in proportion to the chunk length) at no cost in time
+    P.kchunk = 2;
+    P.vec_store = (N % 4 == 0 && aligned16(out)) ? 1 : 0;
+    P.status = device_status_ptr();
+    const long long nsm = sm_count();
+    const unsigned grid = (unsigned)(P.tiles < nsm ? P.tiles : nsm);
+    auto kern = gemm_metric_kernel<TPW_DOT_LINEAR, false, true>;
+    TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
+    kern<<<grid, kThreads, SMEM_ALLOC, s>>>(mah, mal, mbh, mbl, P);
+    TPW_LAUNCH_OK("gemm_metric_kernel (tf32)");
+    return TPW_OK;
 }
 
 } // namespace
@@ -478,7 +779,7 @@ extern "C" int tpw_dot_metric_forward_ws(int dtype, int epilogue, int engine,
     const unsigned grid = (unsigned)(P.tiles < nsm ? P.tiles : nsm);
 #define TPW_GEMM_LAUNCH(EPI, SELF)                                                                                        \
     do {                                                                                                                  \
-        auto kern = gemm_metric_kernel<EPI, SELF>;                                                                        \
+        auto kern = gemm_metric_kernel<EPI, SELF, false>;                                                                        \
         TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));                 \
         kern<<<grid, kThreads, SMEM_ALLOC, s>>>(mxh, mxl, myh, myl, P);                                                   \
     } while (0)
@@ -496,5 +797,107 @@ extern "C" int tpw_dot_metric_forward_ws(int dtype, int epilogue, int engine,
     }
 #undef TPW_GEMM_LAUNCH
     TPW_LAUNCH_OK("gemm_metric_kernel");
+    return TPW_OK;
+}
+
+static bool backward_uses_tensor_cores(int dtype, int mode, int engine, int64_t B, int64_t N1, int64_t N2, int64_t D) {
+    if (dtype != TPW_F32 || B <= 0 || N1 <= 0 || N2 <= 0 || D <= 0) return false;
+    if (mode != TPW_LP_BWD_CDIST && mode != TPW_LP_BWD_PPMINKOWSKI && mode != TPW_LP_BWD_MATMUL) return false;
+    if (engine == TPW_ENGINE_TCGEN05_BF16X3 || engine == TPW_ENGINE_TCGEN05_TF32X3) return true;
+    return engine == TPW_ENGINE_AUTO && auto_picks_tensor_backward(dtype, B, N1, N2, D);
+}
+
+extern "C" int64_t tpw_dot_backward_scratch_bytes(int dtype, int mode, int engine, int64_t B, int64_t N1, int64_t N2, int64_t D) {
+    if (!backward_uses_tensor_cores(dtype, mode, engine, B, N1, N2, D)) return 0;
+    return bwd_scratch_layout(B, N1, N2, D).total;
+}
+
+extern "C" int tpw_dot_backward_ws(int dtype, int mode, int engine, const void *grad, const void *aux,
+                                   const void *x1, const void *x2, void *grad_x1, void *grad_x2,
+                                   void *scratch, int64_t scratch_bytes,
+                                   int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(engine >= TPW_ENGINE_AUTO && engine <= TPW_ENGINE_TCGEN05_TF32X3, "tpw_dot_backward_ws: bad engine %d", engine);
+    TPW_CHECK_ARG(mode == TPW_LP_BWD_CDIST || mode == TPW_LP_BWD_PPMINKOWSKI || mode == TPW_LP_BWD_MATMUL,
+                  "tpw_dot_backward_ws: mode %d has no contraction form (p = 2 modes and the plain products only)", mode);
+    TPW_CHECK_ARG(B >= 0 && N1 >= 0 && N2 >= 0 && D >= 0, "tpw_dot_backward_ws: negative size");
+    bool tensor = backward_uses_tensor_cores(dtype, mode, engine, B, N1, N2, D);
+    if (tensor && engine == TPW_ENGINE_AUTO && (scratch == nullptr || scratch_bytes < bwd_scratch_layout(B, N1, N2, D).total))
+        tensor = false;
+    if (!tensor) {
+        TPW_CHECK_ARG(engine == TPW_ENGINE_AUTO || engine == TPW_ENGINE_SIMT_FP32 || dtype == TPW_F64,
+                      "tpw_dot_backward_ws: the tensor-core engine takes float32 only");
+        return tpw_lp_backward(dtype, mode, grad, aux, x1, x2, nullptr, grad_x1, grad_x2, B, N1, N2, D, 2.0, stream);
+    }
+    TPW_CHECK_ARG(grad && x1 && x2 && (grad_x1 || grad_x2), "tpw_dot_backward_ws: NULL pointer");
+    TPW_CHECK_ARG(mode != TPW_LP_BWD_CDIST || aux != nullptr, "tpw_dot_backward_ws: the Euclidean mode needs the forward output");
+    TPW_CHECK_ARG(N1 < (1ll << 31) && N2 < (1ll << 31) && D < (1ll << 31), "tpw_dot_backward_ws: a dimension exceeds 2^31-1");
+    const BwdScratch L = bwd_scratch_layout(B, N1, N2, D);
+    TPW_CHECK_ARG(scratch != nullptr && scratch_bytes >= L.total,
+                  "tpw_dot_backward_ws: the tensor-core engine needs %lld bytes of scratch (got %lld)", L.total, (long long)scratch_bytes);
+    TPW_CHECK_ARG(aligned16(scratch), "tpw_dot_backward_ws: scratch must be 16-byte aligned");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned char *base = static_cast<unsigned char *>(scratch);
+    auto F = [&](long long off) { return reinterpret_cast<float *>(base + off); };
+    const bool sums = mode != TPW_LP_BWD_MATMUL;
+    int st;
+
+    // coefficient matrix: straight copy for grad_x1 (K = N2), transposed copy for grad_x2 (K = N1)
+    SplitParams C;
+    memset(&C, 0, sizeof(C));
+    C.a = static_cast<const float *>(grad);
+    C.aux = static_cast<const float *>(aux);
+    C.hi = F(L.off_chi); C.lo = F(L.off_clo); C.thi = F(L.off_cthi); C.tlo = F(L.off_ctlo);
+    C.rowpart = F(L.off_rowpart); C.colpart = F(L.off_colpart);
+    C.R = N1; C.C = N2; C.Rp = L.N1p; C.Cp = L.N2p; C.TR = L.TR; C.TC = L.TC;
+    C.vec_in = (N2 % 4 == 0 && aligned16(grad) && (mode != TPW_LP_BWD_CDIST || aligned16(aux))) ? 1 : 0;
+    if (mode == TPW_LP_BWD_CDIST) st = launch_split<COEF_DIV_AUX, true, true, true>(C, B, s);
+    else if (mode == TPW_LP_BWD_PPMINKOWSKI) st = launch_split<COEF_ID, true, true, true>(C, B, s);
+    else st = launch_split<COEF_ID, true, true, false>(C, B, s);
+    if (st != TPW_OK) return st;
+    if (sums) {
+        reduce_partials_kernel<<<(unsigned)((B * N1 + 255) / 256), 256, 0, s>>>(F(L.off_rowpart), F(L.off_rowsum), B, L.TC, N1);
+        reduce_partials_kernel<<<(unsigned)((B * N2 + 255) / 256), 256, 0, s>>>(F(L.off_colpart), F(L.off_colsum), B, L.TR, N2);
+        TPW_LAUNCH_OK("reduce_partials_kernel");
+    }
+    const float s_mm = mode == TPW_LP_BWD_MATMUL ? 1.f : (mode == TPW_LP_BWD_PPMINKOWSKI ? -2.f : -1.f);
+    const float s_row = mode == TPW_LP_BWD_PPMINKOWSKI ? 2.f : 1.f;
+    const long long cap = (long long)sm_count() * 8;
+
+    if (grad_x1) {
+        // X2^T [B,D,N2p]
+        SplitParams X;
+        memset(&X, 0, sizeof(X));
+        X.a = static_cast<const float *>(x2);
+        X.thi = F(L.off_x2thi); X.tlo = F(L.off_x2tlo);
+        X.R = N2; X.C = D; X.Rp = L.N2p; X.Cp = align_up(D, 4);
+        X.vec_in = (D % 4 == 0 && aligned16(x2)) ? 1 : 0;
+        if ((st = launch_split<COEF_ID, false, true, false>(X, B, s)) != TPW_OK) return st;
+        if ((st = launch_tf32_product(F(L.off_chi), F(L.off_clo), F(L.off_x2thi), F(L.off_x2tlo),
+                                      static_cast<float *>(grad_x1), B, N1, D, L.N2p, s)) != TPW_OK) return st;
+        if (mode != TPW_LP_BWD_MATMUL) {
+            const long long n = B * N1 * D, blocks = (n + 255) / 256;
+            grad_finish_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, s>>>(
+                static_cast<float *>(grad_x1), static_cast<const float *>(x1), F(L.off_rowsum), B * N1, D, s_mm, s_row);
+            TPW_LAUNCH_OK("grad_finish_kernel");
+        }
+    }
+    if (grad_x2) {
+        SplitParams X;
+        memset(&X, 0, sizeof(X));
+        X.a = static_cast<const float *>(x1);
+        X.thi = F(L.off_x1thi); X.tlo = F(L.off_x1tlo);
+        X.R = N1; X.C = D; X.Rp = L.N1p; X.Cp = align_up(D, 4);
+        X.vec_in = (D % 4 == 0 && aligned16(x1)) ? 1 : 0;
+        if ((st = launch_split<COEF_ID, false, true, false>(X, B, s)) != TPW_OK) return st;
+        if ((st = launch_tf32_product(F(L.off_cthi), F(L.off_ctlo), F(L.off_x1thi), F(L.off_x1tlo),
+                                      static_cast<float *>(grad_x2), B, N2, D, L.N1p, s)) != TPW_OK) return st;
+        if (mode != TPW_LP_BWD_MATMUL) {
+            const long long n = B * N2 * D, blocks = (n + 255) / 256;
+            grad_finish_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, s>>>(
+                static_cast<float *>(grad_x2), static_cast<const float *>(x2), F(L.off_colsum), B * N2, D, s_mm, s_row);
+            TPW_LAUNCH_OK("grad_finish_kernel");
+        }
+    }
     return TPW_OK;
 }

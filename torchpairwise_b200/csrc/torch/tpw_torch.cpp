@@ -20,7 +20,9 @@
 #include <torch/autograd.h>
 #include <torch/library.h>
 
+#include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <limits>
 
 #include "../../../include/tpw_b200.h"
@@ -130,6 +132,52 @@ bool tensor_engine_selected(const Prepared &p) {
            tpw_dot_metric_scratch_bytes(TPW_F32, TPW_ENGINE_AUTO, p.B, p.N1, p.N2, p.D) > 0;
 }
 
+// Backward of the p = 2 metrics and the plain gradient products: tensor-core contractions when the
+// engine rule of tpw_dot_backward_ws picks them (large float32 problems), the CUDA-core kernel
+// otherwise.  The split copies take about 16 bytes per element of grad; above TPW_BWD_SCRATCH_GB
+// (default 8) the work is cut into groups of batches, or row blocks of one batch whose grad_x2
+// contributions are added in block order.
+void dense_backward(int mode, const Tensor &g, const Tensor *aux, const Tensor &a, const Tensor &b, Tensor &g1, Tensor &g2) {
+    const int64_t B = a.size(0), N1 = a.size(1), N2 = b.size(1), D = a.size(2);
+    const int code = code_of(a);
+    auto st = stream_of(a);
+    if (tpw_dot_backward_scratch_bytes(code, mode, TPW_ENGINE_AUTO, B, N1, N2, D) <= 0) {
+        TPW_CALL(tpw_lp_backward(code, mode, g.data_ptr(), aux ? aux->data_ptr() : nullptr, a.data_ptr(), b.data_ptr(), nullptr,
+                                 g1.data_ptr(), g2.data_ptr(), B, N1, N2, D, 2.0, st));
+        return;
+    }
+    const int eng = TPW_ENGINE_TCGEN05_TF32X3;
+    const char *env = std::getenv("TPW_BWD_SCRATCH_GB");
+    const int64_t cap = static_cast<int64_t>((env ? std::atof(env) : 8.0) * 1073741824.0);
+    const int64_t per_batch = tpw_dot_backward_scratch_bytes(code, mode, eng, 1, N1, N2, D);
+    int64_t nb = 1, rows = N1;
+    if (per_batch <= cap) {
+        nb = std::max<int64_t>(1, std::min<int64_t>(B, cap / per_batch));
+    } else {
+        while (rows > 256 && tpw_dot_backward_scratch_bytes(code, mode, eng, 1, rows, N2, D) > cap)
+            rows = std::max<int64_t>(256, (rows / 2 + 255) / 256 * 256);
+    }
+    const int64_t bytes = tpw_dot_backward_scratch_bytes(code, mode, eng, nb, std::min(rows, N1), N2, D);
+    Tensor scratch = at::empty({bytes}, a.options().dtype(at::kByte));
+    Tensor part;
+    for (int64_t b0 = 0; b0 < B; b0 += nb) {
+        const int64_t bn = std::min(nb, B - b0);
+        for (int64_t r0 = 0; r0 < N1; r0 += rows) {
+            const int64_t rn = std::min(rows, N1 - r0);
+            Tensor gv = g.narrow(0, b0, bn).narrow(1, r0, rn), av = a.narrow(0, b0, bn).narrow(1, r0, rn);
+            Tensor g1v = g1.narrow(0, b0, bn).narrow(1, r0, rn), g2v = g2.narrow(0, b0, bn);
+            if (r0 > 0) {
+                if (!part.defined()) part = at::empty_like(g2v);
+                g2v = part;
+            }
+            const void *auxp = aux ? aux->narrow(0, b0, bn).narrow(1, r0, rn).data_ptr() : nullptr;
+            TPW_CALL(tpw_dot_backward_ws(code, mode, eng, gv.data_ptr(), auxp, av.data_ptr(), b.narrow(0, b0, bn).data_ptr(),
+                                         g1v.data_ptr(), g2v.data_ptr(), scratch.data_ptr(), bytes, bn, rn, N2, D, st));
+            if (r0 > 0) g2.narrow(0, b0, bn).add_(part);
+        }
+    }
+}
+
 Tensor cmp_reduce(const Tensor &a, const Tensor &b, int op, int red);
 
 // ---- at::cdist as the reference's public ops call it -------------------------------------------------
@@ -163,6 +211,7 @@ struct CdistFn : torch::autograd::Function<CdistFn> {
         if (ub) g = g.unsqueeze(0);
         Tensor g1 = at::empty_like(a), g2 = at::empty_like(b);
         if (p == 0) { g1.zero_(); g2.zero_(); }
+        else if (p == 2 && a.numel() > 0 && b.numel() > 0) dense_backward(TPW_LP_BWD_CDIST, g, &out, a, b, g1, g2);
         else TPW_CALL(tpw_lp_backward(code_of(a), TPW_LP_BWD_CDIST, g.data_ptr(), out.data_ptr(), a.data_ptr(), b.data_ptr(), nullptr,
                                       g1.data_ptr(), g2.data_ptr(), a.size(0), a.size(1), b.size(1), a.size(2), p, stream_of(a)));
         return {finish(g1, ub, dt), finish(g2, ub, dt), Tensor()};
@@ -197,6 +246,8 @@ struct PPMinkowskiFn : torch::autograd::Function<PPMinkowskiFn> {
             if (std::isinf(p))
                 TPW_CALL(tpw_lp_inf_backward(code_of(a), g.data_ptr(), a.data_ptr(), b.data_ptr(), nullptr, g1.data_ptr(), g2.data_ptr(),
                                              nullptr, B, N1, N2, D, p < 0, stream_of(a)));
+            else if (p == 2)
+                dense_backward(TPW_LP_BWD_PPMINKOWSKI, g, nullptr, a, b, g1, g2);
             else
                 TPW_CALL(tpw_lp_backward(code_of(a), TPW_LP_BWD_PPMINKOWSKI, g.data_ptr(), nullptr, a.data_ptr(), b.data_ptr(), nullptr,
                                          g1.data_ptr(), g2.data_ptr(), B, N1, N2, D, p, stream_of(a)));
@@ -303,8 +354,7 @@ struct CosineFn : torch::autograd::Function<CosineFn> {
         Tensor g1 = at::empty_like(a), g2 = at::empty_like(b);
         TPW_CALL(tpw_cosine_backward_prepare(code, epilogue, g.data_ptr(), out.data_ptr(), n1.data_ptr(), n2.data_ptr(), dM.data_ptr(),
                                              rowterm.data_ptr(), colterm.data_ptr(), B, N1, N2, st));
-        TPW_CALL(tpw_lp_backward(code, TPW_LP_BWD_MATMUL, dM.data_ptr(), nullptr, a.data_ptr(), b.data_ptr(), nullptr, g1.data_ptr(),
-                                 g2.data_ptr(), B, N1, N2, D, 2.0, st));
+        dense_backward(TPW_LP_BWD_MATMUL, dM, nullptr, a, b, g1, g2);
         TPW_CALL(tpw_cosine_backward_finish(code, g1.data_ptr(), a.data_ptr(), n1.data_ptr(), rowterm.data_ptr(), B * N1, D, st));
         TPW_CALL(tpw_cosine_backward_finish(code, g2.data_ptr(), b.data_ptr(), n2.data_ptr(), colterm.data_ptr(), B * N2, D, st));
         return {finish(g1, ub, dt), finish(g2, ub, dt), Tensor()};

@@ -149,12 +149,70 @@ def _lp_forward_raw(x1c: Tensor, x2c: Tensor, w: Optional[Tensor], p: float, out
 def _lp_backward_raw(mode: int, grad: Tensor, aux: Optional[Tensor], x1c: Tensor, x2c: Tensor,
                      w: Optional[Tensor], p: float, need1: bool = True, need2: bool = True):
     B, N1, N2, D = _sizes(x1c, x2c)
+    if w is None and (mode == _abi.LP_BWD_MATMUL or (p == 2.0 and mode in (_abi.LP_BWD_CDIST, _abi.LP_BWD_PPMINKOWSKI))):
+        res = _dense_backward_tensor(mode, grad, aux, x1c, x2c, need1, need2)
+        if res is not None:
+            return res
     g1 = torch.empty_like(x1c) if need1 else None
     g2 = torch.empty_like(x2c) if need2 else None
     with torch.cuda.device(x1c.device):
         check(lib.tpw_lp_backward(_FLOAT_CODES[x1c.dtype], mode, _ptr(grad), _ptr(aux), _ptr(x1c), _ptr(x2c),
                                   _ptr(w), _ptr(g1), _ptr(g2), B, N1, N2, D, float(p), _stream(x1c)),
               "tpw_lp_backward")
+    return g1, g2
+
+
+def _bwd_scratch_cap() -> int:
+    return int(float(os.environ.get("TPW_BWD_SCRATCH_GB", "8")) * (1 << 30))
+
+
+def _dense_backward_tensor(mode: int, grad: Tensor, aux: Optional[Tensor], x1c: Tensor, x2c: Tensor,
+                           need1: bool, need2: bool):
+    """Backward of the p = 2 metrics / the plain gradient products as tensor-core contractions
+    (``tpw_dot_backward_ws``), or None when the engine rule keeps the problem on the CUDA cores.
+
+    The split copies of the coefficient matrix take about 16 bytes per element of ``grad``; above
+    ``TPW_BWD_SCRATCH_GB`` (default 8) the work is cut into groups of batches, or row blocks of a
+    single batch whose grad_x2 contributions are summed in block order (deterministic)."""
+    if x1c.dtype != torch.float32 or not (need1 or need2):
+        return None
+    B, N1, N2, D = _sizes(x1c, x2c)
+    code = _abi.F32
+    if lib.tpw_dot_backward_scratch_bytes(code, mode, _dot_engine, B, N1, N2, D) <= 0:
+        return None
+    eng = _abi.ENGINE_TCGEN05_TF32X3
+    cap = _bwd_scratch_cap()
+    g1 = torch.empty_like(x1c) if need1 else None
+    g2 = torch.empty_like(x2c) if need2 else None
+    per_batch = lib.tpw_dot_backward_scratch_bytes(code, mode, eng, 1, N1, N2, D)
+    if per_batch <= cap:
+        nb = max(1, min(B, cap // per_batch))
+        blocks = [(b0, min(B, b0 + nb), 0, N1) for b0 in range(0, B, nb)]
+    else:
+        rows = N1
+        while rows > 256 and lib.tpw_dot_backward_scratch_bytes(code, mode, eng, 1, rows, N2, D) > cap:
+            rows = max(256, (rows // 2 + 255) // 256 * 256)
+        blocks = [(b, b + 1, r0, min(N1, r0 + rows)) for b in range(B) for r0 in range(0, N1, rows)]
+    nbytes = max(lib.tpw_dot_backward_scratch_bytes(code, mode, eng, b1 - b0, r1 - r0, N2, D) for b0, b1, r0, r1 in blocks)
+    scratch = torch.empty((nbytes,), dtype=torch.uint8, device=x1c.device)
+    part = None
+    with torch.cuda.device(x1c.device):
+        for b0, b1, r0, r1 in blocks:
+            whole = r0 == 0 and r1 == N1
+            g1v = None if g1 is None else g1[b0:b1, r0:r1]
+            if g2 is None:
+                g2v = None
+            elif whole or r0 == 0:
+                g2v = g2[b0:b1]
+            else:
+                part = torch.empty_like(g2[b0:b1]) if part is None else part
+                g2v = part
+            auxv = None if aux is None else aux[b0:b1, r0:r1]
+            check(lib.tpw_dot_backward_ws(code, mode, eng, _ptr(grad[b0:b1, r0:r1]), _ptr(auxv), _ptr(x1c[b0:b1, r0:r1]),
+                                          _ptr(x2c[b0:b1]), _ptr(g1v), _ptr(g2v), _ptr(scratch), nbytes,
+                                          b1 - b0, r1 - r0, N2, D, _stream(x1c)), "tpw_dot_backward_ws")
+            if g2 is not None and not (whole or r0 == 0):
+                g2[b0:b1] += part
     return g1, g2
 
 
@@ -390,14 +448,11 @@ class _CosineSimilarityFunction(torch.autograd.Function):
         dM = torch.empty_like(g)
         rowterm = torch.empty((B, N1), dtype=g.dtype, device=g.device)
         colterm = torch.empty((B, N2), dtype=g.dtype, device=g.device)
-        g1 = torch.empty_like(x1c)
-        g2 = torch.empty_like(x2c)
         with torch.cuda.device(x1c.device):
             check(lib.tpw_cosine_backward_prepare(code, ctx.epilogue, _ptr(g), _ptr(out), _ptr(n1), _ptr(n2),
                                                   _ptr(dM), _ptr(rowterm), _ptr(colterm), B, N1, N2, _stream(x1c)),
                   "tpw_cosine_backward_prepare")
-            check(lib.tpw_lp_backward(code, _abi.LP_BWD_MATMUL, _ptr(dM), None, _ptr(x1c), _ptr(x2c), None,
-                                      _ptr(g1), _ptr(g2), B, N1, N2, D, 2.0, _stream(x1c)), "tpw_lp_backward")
+            g1, g2 = _lp_backward_raw(_abi.LP_BWD_MATMUL, dM, None, x1c, x2c, None, 2.0)
             check(lib.tpw_cosine_backward_finish(code, _ptr(g1), _ptr(x1c), _ptr(n1), _ptr(rowterm), B * N1, D, _stream(x1c)),
                   "tpw_cosine_backward_finish")
             check(lib.tpw_cosine_backward_finish(code, _ptr(g2), _ptr(x2c), _ptr(n2), _ptr(colterm), B * N2, D, _stream(x1c)),

@@ -436,6 +436,30 @@ def run_suite(args):
                 out.backward(G, retain_graph=True)
             entry(name + "_bwd", n, timeit(bwd), "fp32_issue", n * 256 * bo, fp32_peak, 0)
             del out
+    # dense-contraction backward at C2: two tf32x3 tensor-core products per call (executed flops = 3 x 4 n D);
+    # the tf32 rate is taken as half of the measured sustained bf16 rate
+    for name, fn in (("C2_sqeuclidean_bwd", tpw.sqeuclidean_distances), ("C2_euclidean_bwd", tpw.euclidean_distances),
+                     ("C2_cosine_bwd", tpw.cosine_distances)):
+        if want(name):
+            out = fn(X, Y)
+
+            def bwd():
+                X.grad = None
+                Y.grad = None
+                out.backward(G, retain_graph=True)
+            entry(name, n, timeit(bwd), "tf32 tensor (executed flops = 3 x algorithmic; split pre-pass included)", 3 * 4 * n * 256, bf16_peak / 2, 0)
+            del out
+    if want("C2_sqeuclidean_bwd_simt"):
+        tpw.set_dot_engine("simt")
+        out = tpw.sqeuclidean_distances(X, Y)
+
+        def bwd():
+            X.grad = None
+            Y.grad = None
+            out.backward(G, retain_graph=True)
+        entry("C2_sqeuclidean_bwd_simt", n, timeit(bwd), "fp32_issue", n * 256 * 4, fp32_peak, 0)
+        del out
+        tpw.set_dot_engine("auto")
     if want("C2_manhattan_rowmin"):
         with torch.no_grad():
             entry("C2_manhattan_rowmin", n, timeit(lambda: tpw.pairwise_argmin_min(X, Y, "manhattan")), "fp32_issue (matrix never written)",
@@ -456,6 +480,18 @@ def run_suite(args):
     for name, fn in (("C4_sqeuclidean", tpw.sqeuclidean_distances), ("C4_cosine", tpw.cosine_distances)):
         if want(name):
             entry(name, n, timeit(lambda: fn(X, Y)), "bf16 tensor (executed flops = 3 x algorithmic)", 3 * 2 * n * 512, bf16_peak, 4 * n)
+    if want("C4_sqeuclidean_bwd"):
+        Xg, Yg = X.clone().requires_grad_(True), Y.clone().requires_grad_(True)
+        out = tpw.sqeuclidean_distances(Xg, Yg)
+        G4 = torch.empty_like(out).normal_(generator=torch.Generator(device=dev).manual_seed(1))
+
+        def bwd4():
+            Xg.grad = None
+            Yg.grad = None
+            out.backward(G4, retain_graph=True)
+        entry("C4_sqeuclidean_bwd", n, timeit(bwd4), "tf32 tensor (executed flops = 3 x algorithmic; split pre-pass included; row-blocked under the 8 GB scratch cap)",
+              3 * 4 * n * 512, bf16_peak / 2, 0)
+        del Xg, Yg, out, G4
     if want("C4_sqeuclidean_simt"):
         tpw.set_dot_engine("simt")
         entry("C4_sqeuclidean_simt", n, timeit(lambda: tpw.sqeuclidean_distances(X, Y)), "fp32_issue", n * 512 * 2, fp32_peak, 4 * n)

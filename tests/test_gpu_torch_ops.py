@@ -124,6 +124,34 @@ def test_cpp_layer_agrees_with_python_layer(T):
     assert torch.equal(T.minkowski_distances(x1, x2, 3.0), tpw.minkowski_distances(x1, x2, 3.0))
 
 
+def test_cpp_layer_dense_backward_on_tensor_cores(T, monkeypatch):
+    """Above the engine threshold the C++ autograd nodes of the p = 2 metrics and the cosine family
+    run the tcgen05 gradient products, blocked by the same scratch cap, and agree bit for bit with
+    the Python layer, which takes the same path."""
+    import torchpairwise_b200 as tpw
+    from torchpairwise_b200 import _abi
+    g = torch.Generator().manual_seed(15)
+    x1, x2 = torch.randn(2, 2048, 64, generator=g).cuda(), torch.randn(2, 1100, 64, generator=g).cuda()
+    up = torch.randn(2, 2048, 1100, generator=g).cuda()
+    assert _abi.lib.tpw_dot_backward_scratch_bytes(_abi.F32, _abi.LP_BWD_MATMUL, _abi.ENGINE_AUTO, 2, 2048, 1100, 64) > 0
+    per_batch = _abi.lib.tpw_dot_backward_scratch_bytes(_abi.F32, _abi.LP_BWD_MATMUL, _abi.ENGINE_TCGEN05_TF32X3, 1, 2048, 1100, 64)
+    for cap in (None, 0.4 * per_batch / 2 ** 30):
+        if cap is not None:
+            monkeypatch.setenv("TPW_BWD_SCRATCH_GB", str(cap))   # row blocks inside each batch
+        for name in ("sqeuclidean_distances", "euclidean_distances", "cosine_distances", "correlation_distances"):
+            grads = []
+            for fn in (getattr(T, name), getattr(tpw, name)):
+                a, b = x1.clone().requires_grad_(True), x2.clone().requires_grad_(True)
+                fn(a, b).backward(up)
+                grads.append((a.grad, b.grad))
+            assert torch.equal(grads[0][0], grads[1][0]) and torch.equal(grads[0][1], grads[1][1]), name
+            a, b = x1.double().requires_grad_(True), x2.double().requires_grad_(True)
+            getattr(tpw, name)(a, b).backward(up.double())
+            for got, ref in ((grads[0][0], a.grad), (grads[0][1], b.grad)):
+                bound = 1e-4 * ref.abs() + 2e-5 * ref.pow(2).mean().sqrt() + 1e-5
+                assert float(((got.double() - ref).abs() / bound).max()) <= 1.0, name
+
+
 def test_stand_alone_registration():
     code = (
         "import torch, torchpairwise_b200 as t\n"

@@ -218,6 +218,19 @@ TPW_API int tpw_dot_backward_ws(int dtype, int mode, int engine, const void *gra
                         void *scratch, int64_t scratch_bytes,
                         int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream);
 
+/*
+ * Whole backward of cosine_similarity / cosine_distances / correlation's 1 - S on the tensor cores
+ * (float32): the element-wise chain of tpw_cosine_backward_prepare is folded into the pre-pass of
+ * the two products, so dM is never written as a float32 matrix, and tpw_cosine_backward_finish is
+ * applied to both gradients.  Same scratch as tpw_dot_backward_ws with TPW_LP_BWD_MATMUL; callers
+ * use it when that size query is positive and the prepare / tpw_lp_backward / finish sequence otherwise.
+ * (the autograd chain under OPS/pairwise_metrics.cpp:118-121; OPS/cuda/prf_div_kernel.cu:315-366)
+ */
+TPW_API int tpw_cosine_backward_ws(int epilogue, const void *grad, const void *out, const void *norm1, const void *norm2,
+                           const void *x1, const void *x2, void *grad_x1, void *grad_x2,
+                           void *scratch, int64_t scratch_bytes,
+                           int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream);
+
 /* Row helpers used by cosine / correlation host code (x.norm(2,-1), x - x.mean(-1):
    OPS/pairwise_metrics.cpp:118-119,197-201). rows = B*N. */
 TPW_API int tpw_row_center(int dtype, const void *x, void *out, int64_t rows, int64_t D, tpw_stream_t stream);

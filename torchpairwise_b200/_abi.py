@@ -48,6 +48,7 @@ SIGNATURES = {
     "tpw_dot_metric_scratch_bytes": (_L, [_I, _I, _L, _L, _L, _L]),
     "tpw_dot_backward_scratch_bytes": (_L, [_I, _I, _I, _L, _L, _L, _L]),
     "tpw_dot_backward_ws": (_I, [_I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P]),
+    "tpw_cosine_backward_ws": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P]),
     "tpw_dot_metric_forward_ws": (_I, [_I, _I, _I, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P]),
     "tpw_row_center": (_I, [_I, _P, _P, _L, _L, _P]),
     "tpw_row_norm": (_I, [_I, _P, _P, _L, _L, _P]),

@@ -506,57 +506,102 @@ __device__ __forceinline__ float rn_tf32(float v) {
     return __uint_as_float(u);
 }
 
-enum { COEF_ID = 0, COEF_DIV_AUX = 1 };
+enum { COEF_ID = 0, COEF_DIV_AUX = 1, COEF_COSINE = 2 };
 constexpr int PT = 64;        // pre-pass tile edge
 constexpr int PT_PITCH = 65;  // shared-memory pitch (floats) of the transposing tile
 
 struct SplitParams {
     const float *a, *aux;       // [B,R,C]
+    const float *n1, *n2;       // COEF_COSINE: row norms [B,R], [B,C]
     float *hi, *lo;             // [B,R,Cp]   (STRAIGHT)
     float *thi, *tlo;           // [B,C,Rp]   (TRANSPOSED)
     float *rowpart, *colpart;   // [B,TC,R], [B,TR,C]   (SUMS)
     long long R, C, Rp, Cp, TR, TC;
     int vec_in;                 // C % 4 == 0 and 16-byte aligned inputs
+    int epilogue;               // COEF_COSINE: what aux holds (tpw_dot_epilogue)
 };
+
+// Coefficient of one element and the summands of its row and column sums.
+//   COEF_ID:      c = a
+//   COEF_DIV_AUX: c = a / aux, 0 where aux == 0                     (Euclidean: g / o)
+//   COEF_COSINE:  S = M / (n1 n2) with the "identity" safe divide, aux = S or 1 - S, a = upstream
+//                 gradient: c = dM = gs / (n1 n2) (gs where that is 0), and with dd = -c S (0 where
+//                 the denominator is 0) the row summand is dd n2[j], the column summand dd n1[i]
+//                 (the gradients of the two norm vectors)
+template <int MODE>
+__device__ __forceinline__ void coefficient(float a, float aux, float na, float nb, int epilogue, float &c, float &rs, float &cs) {
+    if (MODE == COEF_ID) {
+        c = rs = cs = a;
+    } else if (MODE == COEF_DIV_AUX) {
+        c = aux != 0.f ? __fdiv_rn(a, aux) : 0.f;
+        rs = cs = c;
+    } else {
+        const float S = epilogue == TPW_DOT_COSINE_SIM ? aux : 1.f - aux;
+        const float gs = epilogue == TPW_DOT_COSINE_SIM ? a : -a;
+        const float denom = na * nb;
+        float dd = 0.f;
+        if (denom != 0.f) {
+            c = __fdiv_rn(gs, denom);
+            dd = -c * S;
+        } else {
+            c = gs;
+        }
+        rs = dd * nb;
+        cs = dd * na;
+    }
+}
 
 // One 64 x 64 tile per CTA of 256 threads: coefficient, tf32 split, straight and transposed copies
 // (row pitches padded to a multiple of 4 and zero filled), per-tile row and column sums.
 template <int MODE, bool STRAIGHT, bool TRANSPOSED, bool SUMS>
 __global__ void __launch_bounds__(256)
 split_tile_kernel(const SplitParams P) {
-    __shared__ float tile[PT * PT_PITCH];
+    __shared__ float tile[TRANSPOSED ? PT * PT_PITCH : 1];
+    __shared__ float colacc[SUMS ? 16 * PT : 1];
     const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
     const long long b = blockIdx.z;
     const long long r0 = (long long)blockIdx.y * PT, c0 = (long long)blockIdx.x * PT;
     const float *a = P.a + b * P.R * P.C;
-    const float *aux = MODE == COEF_DIV_AUX ? P.aux + b * P.R * P.C : nullptr;
+    const float *aux = MODE != COEF_ID ? P.aux + b * P.R * P.C : nullptr;
+    const long long col = c0 + 4 * tx;
+    float nb[4] = {0.f, 0.f, 0.f, 0.f};
+    if (MODE == COEF_COSINE) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            if (col + e < P.C) nb[e] = P.n2[b * P.C + col + e];
+    }
+    float colp[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
         const int lr = ty + 16 * r;
-        const long long row = r0 + lr, col = c0 + 4 * tx;
-        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        const long long row = r0 + lr;
+        float v[4] = {0.f, 0.f, 0.f, 0.f}, rs[4] = {0.f, 0.f, 0.f, 0.f};
         if (row < P.R) {
-            if (P.vec_in && col + 3 < P.C) {
+            float av[4] = {0.f, 0.f, 0.f, 0.f}, ov[4] = {0.f, 0.f, 0.f, 0.f};
+            const bool vec = P.vec_in && col + 3 < P.C;
+            if (vec) {
                 const float4 t = *reinterpret_cast<const float4 *>(a + row * P.C + col);
-                v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
-                if (MODE == COEF_DIV_AUX) {
+                av[0] = t.x; av[1] = t.y; av[2] = t.z; av[3] = t.w;
+                if (MODE != COEF_ID) {
                     const float4 o = *reinterpret_cast<const float4 *>(aux + row * P.C + col);
-                    v[0] = o.x != 0.f ? __fdiv_rn(v[0], o.x) : 0.f;
-                    v[1] = o.y != 0.f ? __fdiv_rn(v[1], o.y) : 0.f;
-                    v[2] = o.z != 0.f ? __fdiv_rn(v[2], o.z) : 0.f;
-                    v[3] = o.w != 0.f ? __fdiv_rn(v[3], o.w) : 0.f;
+                    ov[0] = o.x; ov[1] = o.y; ov[2] = o.z; ov[3] = o.w;
                 }
             } else {
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
                     if (col + e < P.C) {
-                        v[e] = a[row * P.C + col + e];
-                        if (MODE == COEF_DIV_AUX) {
-                            const float o = aux[row * P.C + col + e];
-                            v[e] = o != 0.f ? __fdiv_rn(v[e], o) : 0.f;
-                        }
+                        av[e] = a[row * P.C + col + e];
+                        if (MODE != COEF_ID) ov[e] = aux[row * P.C + col + e];
                     }
             }
+            const float na = MODE == COEF_COSINE ? P.n1[b * P.R + row] : 0.f;
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (col + e < P.C) {
+                    float cs;
+                    coefficient<MODE>(av[e], ov[e], na, nb[e], P.epilogue, v[e], rs[e], cs);
+                    colp[e] += cs;
+                }
         }
         if (STRAIGHT && row < P.R && col < P.Cp) {
             float4 h, l;
@@ -568,39 +613,44 @@ split_tile_kernel(const SplitParams P) {
             *reinterpret_cast<float4 *>(P.lo + (b * P.R + row) * P.Cp + col) = l;
         }
         if (SUMS) {
-            float s = (v[0] + v[1]) + (v[2] + v[3]);
+            float s = (rs[0] + rs[1]) + (rs[2] + rs[3]);
 #pragma unroll
             for (int off = 1; off < 16; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
             if (tx == 0 && row < P.R) P.rowpart[(b * P.TC + blockIdx.x) * P.R + row] = s;
         }
-        if (TRANSPOSED || SUMS) {
+        if (TRANSPOSED) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) tile[lr * PT_PITCH + 4 * tx + e] = v[e];
         }
     }
+    if (SUMS) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) colacc[ty * PT + 4 * tx + e] = colp[e];
+    }
     if (!(TRANSPOSED || SUMS)) return;
     __syncthreads();
+    if (SUMS && tid < PT && c0 + tid < P.C) {
+        float s = 0.f;
+#pragma unroll
+        for (int y = 0; y < 16; ++y) s += colacc[y * PT + tid];
+        P.colpart[(b * P.TR + blockIdx.y) * P.C + c0 + tid] = s;
+    }
+    if (!TRANSPOSED) return;
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-        const int lc = ty + 16 * r;                       // tile column = row of the transposed copy
-        const long long col = c0 + lc, row = r0 + 4 * tx; // four consecutive source rows
-        float v[4];
+        const int lc = ty + 16 * r;                        // tile column = row of the transposed copy
+        const long long tcol = c0 + lc, row = r0 + 4 * tx; // four consecutive source rows
+        if (tcol < P.C && row < P.Rp) {
+            float v[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) v[e] = tile[(4 * tx + e) * PT_PITCH + lc]; // rows past R hold zeros
-        if (TRANSPOSED && col < P.C && row < P.Rp) {
+            for (int e = 0; e < 4; ++e) v[e] = tile[(4 * tx + e) * PT_PITCH + lc]; // rows past R hold zeros
             float4 h, l;
             h.x = rn_tf32(v[0]); l.x = rn_tf32(v[0] - h.x);
             h.y = rn_tf32(v[1]); l.y = rn_tf32(v[1] - h.y);
             h.z = rn_tf32(v[2]); l.z = rn_tf32(v[2] - h.z);
             h.w = rn_tf32(v[3]); l.w = rn_tf32(v[3] - h.w);
-            *reinterpret_cast<float4 *>(P.thi + (b * P.C + col) * P.Rp + row) = h;
-            *reinterpret_cast<float4 *>(P.tlo + (b * P.C + col) * P.Rp + row) = l;
-        }
-        if (SUMS) {
-            float s = (v[0] + v[1]) + (v[2] + v[3]);
-#pragma unroll
-            for (int off = 1; off < 16; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-            if (tx == 0 && col < P.C) P.colpart[(b * P.TR + blockIdx.y) * P.C + col] = s;
+            *reinterpret_cast<float4 *>(P.thi + (b * P.C + tcol) * P.Rp + row) = h;
+            *reinterpret_cast<float4 *>(P.tlo + (b * P.C + tcol) * P.Rp + row) = l;
         }
     }
 }
@@ -812,6 +862,73 @@ extern "C" int64_t tpw_dot_backward_scratch_bytes(int dtype, int mode, int engin
     return bwd_scratch_layout(B, N1, N2, D).total;
 }
 
+extern "C" int tpw_cosine_backward_finish(int dtype, void *grad_x, const void *x, const void *norm, const void *term,
+                                          int64_t rows, int64_t D, tpw_stream_t stream);
+
+// Shared body of the two entry points below.  coef: COEF_ID / COEF_DIV_AUX / COEF_COSINE.
+static int dense_backward_tensor(int coef, int epilogue, bool sums, float s_mm, float s_row,
+                                 const void *grad, const void *aux, const void *norm1, const void *norm2,
+                                 const void *x1, const void *x2, void *grad_x1, void *grad_x2, void *scratch,
+                                 int64_t B, int64_t N1, int64_t N2, int64_t D, cudaStream_t s) {
+    const BwdScratch L = bwd_scratch_layout(B, N1, N2, D);
+    unsigned char *base = static_cast<unsigned char *>(scratch);
+    auto F = [&](long long off) { return reinterpret_cast<float *>(base + off); };
+    int st;
+
+    // coefficient matrix: straight copy for grad_x1 (K = N2), transposed copy for grad_x2 (K = N1)
+    SplitParams C;
+    memset(&C, 0, sizeof(C));
+    C.a = static_cast<const float *>(grad);
+    C.aux = static_cast<const float *>(aux);
+    C.n1 = static_cast<const float *>(norm1);
+    C.n2 = static_cast<const float *>(norm2);
+    C.epilogue = epilogue;
+    C.hi = F(L.off_chi); C.lo = F(L.off_clo); C.thi = F(L.off_cthi); C.tlo = F(L.off_ctlo);
+    C.rowpart = F(L.off_rowpart); C.colpart = F(L.off_colpart);
+    C.R = N1; C.C = N2; C.Rp = L.N1p; C.Cp = L.N2p; C.TR = L.TR; C.TC = L.TC;
+    C.vec_in = (N2 % 4 == 0 && aligned16(grad) && (coef == COEF_ID || aligned16(aux))) ? 1 : 0;
+    if (coef == COEF_COSINE) st = launch_split<COEF_COSINE, true, true, true>(C, B, s);
+    else if (coef == COEF_DIV_AUX) st = launch_split<COEF_DIV_AUX, true, true, true>(C, B, s);
+    else if (sums) st = launch_split<COEF_ID, true, true, true>(C, B, s);
+    else st = launch_split<COEF_ID, true, true, false>(C, B, s);
+    if (st != TPW_OK) return st;
+    if (sums) {
+        reduce_partials_kernel<<<(unsigned)((B * N1 + 255) / 256), 256, 0, s>>>(F(L.off_rowpart), F(L.off_rowsum), B, L.TC, N1);
+        reduce_partials_kernel<<<(unsigned)((B * N2 + 255) / 256), 256, 0, s>>>(F(L.off_colpart), F(L.off_colsum), B, L.TR, N2);
+        TPW_LAUNCH_OK("reduce_partials_kernel");
+    }
+    const long long cap = (long long)sm_count() * 8;
+    for (int side = 0; side < 2; ++side) {
+        void *gout = side == 0 ? grad_x1 : grad_x2;
+        if (!gout) continue;
+        // side 0: grad_x1 = C . X2 needs X2^T [B,D,N2p]; side 1: grad_x2 = C^T . X1 needs X1^T [B,D,N1p]
+        const void *xk = side == 0 ? x2 : x1;   // operand contracted against
+        const void *xo = side == 0 ? x1 : x2;   // rows that receive the gradient
+        const long long Nk = side == 0 ? N2 : N1, Nkp = side == 0 ? L.N2p : L.N1p, No = side == 0 ? N1 : N2;
+        float *xthi = F(side == 0 ? L.off_x2thi : L.off_x1thi), *xtlo = F(side == 0 ? L.off_x2tlo : L.off_x1tlo);
+        SplitParams X;
+        memset(&X, 0, sizeof(X));
+        X.a = static_cast<const float *>(xk);
+        X.thi = xthi; X.tlo = xtlo;
+        X.R = Nk; X.C = D; X.Rp = Nkp; X.Cp = align_up(D, 4);
+        X.vec_in = (D % 4 == 0 && aligned16(xk)) ? 1 : 0;
+        if ((st = launch_split<COEF_ID, false, true, false>(X, B, s)) != TPW_OK) return st;
+        if ((st = launch_tf32_product(F(side == 0 ? L.off_chi : L.off_cthi), F(side == 0 ? L.off_clo : L.off_ctlo), xthi, xtlo,
+                                      static_cast<float *>(gout), B, No, D, Nkp, s)) != TPW_OK) return st;
+        const float *sumv = F(side == 0 ? L.off_rowsum : L.off_colsum);
+        if (coef == COEF_COSINE) {
+            // the norm part of the chain: g[r,:] += term[r] * x[r,:] / norm[r]
+            if ((st = tpw_cosine_backward_finish(TPW_F32, gout, xo, side == 0 ? norm1 : norm2, sumv, B * No, D, s)) != TPW_OK) return st;
+        } else if (sums) {
+            const long long n = B * No * D, blocks = (n + 255) / 256;
+            grad_finish_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, s>>>(
+                static_cast<float *>(gout), static_cast<const float *>(xo), sumv, B * No, D, s_mm, s_row);
+            TPW_LAUNCH_OK("grad_finish_kernel");
+        }
+    }
+    return TPW_OK;
+}
+
 extern "C" int tpw_dot_backward_ws(int dtype, int mode, int engine, const void *grad, const void *aux,
                                    const void *x1, const void *x2, void *grad_x1, void *grad_x2,
                                    void *scratch, int64_t scratch_bytes,
@@ -832,72 +949,31 @@ extern "C" int tpw_dot_backward_ws(int dtype, int mode, int engine, const void *
     TPW_CHECK_ARG(grad && x1 && x2 && (grad_x1 || grad_x2), "tpw_dot_backward_ws: NULL pointer");
     TPW_CHECK_ARG(mode != TPW_LP_BWD_CDIST || aux != nullptr, "tpw_dot_backward_ws: the Euclidean mode needs the forward output");
     TPW_CHECK_ARG(N1 < (1ll << 31) && N2 < (1ll << 31) && D < (1ll << 31), "tpw_dot_backward_ws: a dimension exceeds 2^31-1");
-    const BwdScratch L = bwd_scratch_layout(B, N1, N2, D);
-    TPW_CHECK_ARG(scratch != nullptr && scratch_bytes >= L.total,
-                  "tpw_dot_backward_ws: the tensor-core engine needs %lld bytes of scratch (got %lld)", L.total, (long long)scratch_bytes);
+    const long long need = bwd_scratch_layout(B, N1, N2, D).total;
+    TPW_CHECK_ARG(scratch != nullptr && scratch_bytes >= need,
+                  "tpw_dot_backward_ws: the tensor-core engine needs %lld bytes of scratch (got %lld)", need, (long long)scratch_bytes);
     TPW_CHECK_ARG(aligned16(scratch), "tpw_dot_backward_ws: scratch must be 16-byte aligned");
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    unsigned char *base = static_cast<unsigned char *>(scratch);
-    auto F = [&](long long off) { return reinterpret_cast<float *>(base + off); };
-    const bool sums = mode != TPW_LP_BWD_MATMUL;
-    int st;
-
-    // coefficient matrix: straight copy for grad_x1 (K = N2), transposed copy for grad_x2 (K = N1)
-    SplitParams C;
-    memset(&C, 0, sizeof(C));
-    C.a = static_cast<const float *>(grad);
-    C.aux = static_cast<const float *>(aux);
-    C.hi = F(L.off_chi); C.lo = F(L.off_clo); C.thi = F(L.off_cthi); C.tlo = F(L.off_ctlo);
-    C.rowpart = F(L.off_rowpart); C.colpart = F(L.off_colpart);
-    C.R = N1; C.C = N2; C.Rp = L.N1p; C.Cp = L.N2p; C.TR = L.TR; C.TC = L.TC;
-    C.vec_in = (N2 % 4 == 0 && aligned16(grad) && (mode != TPW_LP_BWD_CDIST || aligned16(aux))) ? 1 : 0;
-    if (mode == TPW_LP_BWD_CDIST) st = launch_split<COEF_DIV_AUX, true, true, true>(C, B, s);
-    else if (mode == TPW_LP_BWD_PPMINKOWSKI) st = launch_split<COEF_ID, true, true, true>(C, B, s);
-    else st = launch_split<COEF_ID, true, true, false>(C, B, s);
-    if (st != TPW_OK) return st;
-    if (sums) {
-        reduce_partials_kernel<<<(unsigned)((B * N1 + 255) / 256), 256, 0, s>>>(F(L.off_rowpart), F(L.off_rowsum), B, L.TC, N1);
-        reduce_partials_kernel<<<(unsigned)((B * N2 + 255) / 256), 256, 0, s>>>(F(L.off_colpart), F(L.off_colsum), B, L.TR, N2);
-        TPW_LAUNCH_OK("reduce_partials_kernel");
-    }
     const float s_mm = mode == TPW_LP_BWD_MATMUL ? 1.f : (mode == TPW_LP_BWD_PPMINKOWSKI ? -2.f : -1.f);
     const float s_row = mode == TPW_LP_BWD_PPMINKOWSKI ? 2.f : 1.f;
-    const long long cap = (long long)sm_count() * 8;
+    return dense_backward_tensor(mode == TPW_LP_BWD_CDIST ? COEF_DIV_AUX : COEF_ID, 0, mode != TPW_LP_BWD_MATMUL, s_mm, s_row,
+                                 grad, aux, nullptr, nullptr, x1, x2, grad_x1, grad_x2, scratch, B, N1, N2, D,
+                                 static_cast<cudaStream_t>(stream));
+}
 
-    if (grad_x1) {
-        // X2^T [B,D,N2p]
-        SplitParams X;
-        memset(&X, 0, sizeof(X));
-        X.a = static_cast<const float *>(x2);
-        X.thi = F(L.off_x2thi); X.tlo = F(L.off_x2tlo);
-        X.R = N2; X.C = D; X.Rp = L.N2p; X.Cp = align_up(D, 4);
-        X.vec_in = (D % 4 == 0 && aligned16(x2)) ? 1 : 0;
-        if ((st = launch_split<COEF_ID, false, true, false>(X, B, s)) != TPW_OK) return st;
-        if ((st = launch_tf32_product(F(L.off_chi), F(L.off_clo), F(L.off_x2thi), F(L.off_x2tlo),
-                                      static_cast<float *>(grad_x1), B, N1, D, L.N2p, s)) != TPW_OK) return st;
-        if (mode != TPW_LP_BWD_MATMUL) {
-            const long long n = B * N1 * D, blocks = (n + 255) / 256;
-            grad_finish_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, s>>>(
-                static_cast<float *>(grad_x1), static_cast<const float *>(x1), F(L.off_rowsum), B * N1, D, s_mm, s_row);
-            TPW_LAUNCH_OK("grad_finish_kernel");
-        }
-    }
-    if (grad_x2) {
-        SplitParams X;
-        memset(&X, 0, sizeof(X));
-        X.a = static_cast<const float *>(x1);
-        X.thi = F(L.off_x1thi); X.tlo = F(L.off_x1tlo);
-        X.R = N1; X.C = D; X.Rp = L.N1p; X.Cp = align_up(D, 4);
-        X.vec_in = (D % 4 == 0 && aligned16(x1)) ? 1 : 0;
-        if ((st = launch_split<COEF_ID, false, true, false>(X, B, s)) != TPW_OK) return st;
-        if ((st = launch_tf32_product(F(L.off_cthi), F(L.off_ctlo), F(L.off_x1thi), F(L.off_x1tlo),
-                                      static_cast<float *>(grad_x2), B, N2, D, L.N1p, s)) != TPW_OK) return st;
-        if (mode != TPW_LP_BWD_MATMUL) {
-            const long long n = B * N2 * D, blocks = (n + 255) / 256;
-            grad_finish_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, s>>>(
-                static_cast<float *>(grad_x2), static_cast<const float *>(x2), F(L.off_colsum), B * N2, D, s_mm, s_row);
-            TPW_LAUNCH_OK("grad_finish_kernel");
-        }
-    }
-    return TPW_OK;
+extern "C" int tpw_cosine_backward_ws(int epilogue, const void *grad, const void *out, const void *norm1, const void *norm2,
+                                      const void *x1, const void *x2, void *grad_x1, void *grad_x2,
+                                      void *scratch, int64_t scratch_bytes,
+                                      int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(epilogue == TPW_DOT_COSINE_SIM || epilogue == TPW_DOT_COSINE_DIST || epilogue == TPW_DOT_ONE_MINUS_SIM,
+                  "tpw_cosine_backward_ws: bad epilogue %d", epilogue);
+    TPW_CHECK_ARG(B > 0 && N1 > 0 && N2 > 0 && D > 0, "tpw_cosine_backward_ws: sizes must be positive");
+    TPW_CHECK_ARG(grad && out && norm1 && norm2 && x1 && x2 && (grad_x1 || grad_x2), "tpw_cosine_backward_ws: NULL pointer");
+    TPW_CHECK_ARG(N1 < (1ll << 31) && N2 < (1ll << 31) && D < (1ll << 31), "tpw_cosine_backward_ws: a dimension exceeds 2^31-1");
+    const long long need = bwd_scratch_layout(B, N1, N2, D).total;
+    TPW_CHECK_ARG(scratch != nullptr && scratch_bytes >= need,
+                  "tpw_cosine_backward_ws: needs %lld bytes of scratch (got %lld)", need, (long long)scratch_bytes);
+    TPW_CHECK_ARG(aligned16(scratch), "tpw_cosine_backward_ws: scratch must be 16-byte aligned");
+    return dense_backward_tensor(COEF_COSINE, epilogue, true, 1.f, 0.f, grad, out, norm1, norm2, x1, x2, grad_x1, grad_x2, scratch,
+                                 B, N1, N2, D, static_cast<cudaStream_t>(stream));
 }

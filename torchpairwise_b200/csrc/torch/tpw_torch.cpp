@@ -137,14 +137,24 @@ bool tensor_engine_selected(const Prepared &p) {
 // otherwise.  The split copies take about 16 bytes per element of grad; above TPW_BWD_SCRATCH_GB
 // (default 8) the work is cut into groups of batches, or row blocks of one batch whose grad_x2
 // contributions are added in block order.
-void dense_backward(int mode, const Tensor &g, const Tensor *aux, const Tensor &a, const Tensor &b, Tensor &g1, Tensor &g2) {
+// With `cosine` set (epilogue >= 0, the two norm vectors) the call is the whole cosine-family backward,
+// tpw_cosine_backward_ws, with g the upstream gradient and aux the saved forward result; it returns
+// false without doing anything when the engine rule keeps the problem on the CUDA cores.
+struct CosineArgs {
+    int epilogue = -1;
+    const Tensor *n1 = nullptr, *n2 = nullptr;
+};
+
+bool dense_backward(int mode, const Tensor &g, const Tensor *aux, const Tensor &a, const Tensor &b, Tensor &g1, Tensor &g2,
+                    const CosineArgs &cosine = CosineArgs()) {
     const int64_t B = a.size(0), N1 = a.size(1), N2 = b.size(1), D = a.size(2);
     const int code = code_of(a);
     auto st = stream_of(a);
     if (tpw_dot_backward_scratch_bytes(code, mode, TPW_ENGINE_AUTO, B, N1, N2, D) <= 0) {
+        if (cosine.epilogue >= 0) return false;
         TPW_CALL(tpw_lp_backward(code, mode, g.data_ptr(), aux ? aux->data_ptr() : nullptr, a.data_ptr(), b.data_ptr(), nullptr,
                                  g1.data_ptr(), g2.data_ptr(), B, N1, N2, D, 2.0, st));
-        return;
+        return true;
     }
     const int eng = TPW_ENGINE_TCGEN05_TF32X3;
     const char *env = std::getenv("TPW_BWD_SCRATCH_GB");
@@ -171,11 +181,17 @@ void dense_backward(int mode, const Tensor &g, const Tensor *aux, const Tensor &
                 g2v = part;
             }
             const void *auxp = aux ? aux->narrow(0, b0, bn).narrow(1, r0, rn).data_ptr() : nullptr;
-            TPW_CALL(tpw_dot_backward_ws(code, mode, eng, gv.data_ptr(), auxp, av.data_ptr(), b.narrow(0, b0, bn).data_ptr(),
-                                         g1v.data_ptr(), g2v.data_ptr(), scratch.data_ptr(), bytes, bn, rn, N2, D, st));
+            if (cosine.epilogue >= 0)
+                TPW_CALL(tpw_cosine_backward_ws(cosine.epilogue, gv.data_ptr(), auxp, cosine.n1->narrow(0, b0, bn).narrow(1, r0, rn).data_ptr(),
+                                                cosine.n2->narrow(0, b0, bn).data_ptr(), av.data_ptr(), b.narrow(0, b0, bn).data_ptr(),
+                                                g1v.data_ptr(), g2v.data_ptr(), scratch.data_ptr(), bytes, bn, rn, N2, D, st));
+            else
+                TPW_CALL(tpw_dot_backward_ws(code, mode, eng, gv.data_ptr(), auxp, av.data_ptr(), b.narrow(0, b0, bn).data_ptr(),
+                                             g1v.data_ptr(), g2v.data_ptr(), scratch.data_ptr(), bytes, bn, rn, N2, D, st));
             if (r0 > 0) g2.narrow(0, b0, bn).add_(part);
         }
     }
+    return true;
 }
 
 Tensor cmp_reduce(const Tensor &a, const Tensor &b, int op, int red);
@@ -350,8 +366,12 @@ struct CosineFn : torch::autograd::Function<CosineFn> {
         Tensor n1 = at::empty({B, N1}, a.options()), n2 = at::empty({B, N2}, a.options());
         TPW_CALL(tpw_row_norm(code, a.data_ptr(), n1.data_ptr(), B * N1, D, st));
         TPW_CALL(tpw_row_norm(code, b.data_ptr(), n2.data_ptr(), B * N2, D, st));
-        Tensor dM = at::empty_like(g), rowterm = at::empty({B, N1}, a.options()), colterm = at::empty({B, N2}, a.options());
         Tensor g1 = at::empty_like(a), g2 = at::empty_like(b);
+        CosineArgs cos;
+        cos.epilogue = epilogue; cos.n1 = &n1; cos.n2 = &n2;
+        if (a.numel() > 0 && b.numel() > 0 && dense_backward(TPW_LP_BWD_MATMUL, g, &out, a, b, g1, g2, cos))
+            return {finish(g1, ub, dt), finish(g2, ub, dt), Tensor()};
+        Tensor dM = at::empty_like(g), rowterm = at::empty({B, N1}, a.options()), colterm = at::empty({B, N2}, a.options());
         TPW_CALL(tpw_cosine_backward_prepare(code, epilogue, g.data_ptr(), out.data_ptr(), n1.data_ptr(), n2.data_ptr(), dM.data_ptr(),
                                              rowterm.data_ptr(), colterm.data_ptr(), B, N1, N2, st));
         dense_backward(TPW_LP_BWD_MATMUL, dM, nullptr, a, b, g1, g2);

@@ -167,13 +167,16 @@ def _bwd_scratch_cap() -> int:
 
 
 def _dense_backward_tensor(mode: int, grad: Tensor, aux: Optional[Tensor], x1c: Tensor, x2c: Tensor,
-                           need1: bool, need2: bool):
+                           need1: bool, need2: bool, cosine=None):
     """Backward of the p = 2 metrics / the plain gradient products as tensor-core contractions
     (``tpw_dot_backward_ws``), or None when the engine rule keeps the problem on the CUDA cores.
 
     The split copies of the coefficient matrix take about 16 bytes per element of ``grad``; above
     ``TPW_BWD_SCRATCH_GB`` (default 8) the work is cut into groups of batches, or row blocks of a
-    single batch whose grad_x2 contributions are summed in block order (deterministic)."""
+    single batch whose grad_x2 contributions are summed in block order (deterministic).
+
+    ``cosine=(epilogue, norm1, norm2)`` runs the whole cosine-family backward instead
+    (``tpw_cosine_backward_ws``: ``grad`` is the upstream gradient, ``aux`` the saved forward result)."""
     if x1c.dtype != torch.float32 or not (need1 or need2):
         return None
     B, N1, N2, D = _sizes(x1c, x2c)
@@ -208,9 +211,16 @@ def _dense_backward_tensor(mode: int, grad: Tensor, aux: Optional[Tensor], x1c: 
                 part = torch.empty_like(g2[b0:b1]) if part is None else part
                 g2v = part
             auxv = None if aux is None else aux[b0:b1, r0:r1]
-            check(lib.tpw_dot_backward_ws(code, mode, eng, _ptr(grad[b0:b1, r0:r1]), _ptr(auxv), _ptr(x1c[b0:b1, r0:r1]),
-                                          _ptr(x2c[b0:b1]), _ptr(g1v), _ptr(g2v), _ptr(scratch), nbytes,
-                                          b1 - b0, r1 - r0, N2, D, _stream(x1c)), "tpw_dot_backward_ws")
+            if cosine is not None:
+                epilogue, n1, n2 = cosine
+                check(lib.tpw_cosine_backward_ws(epilogue, _ptr(grad[b0:b1, r0:r1]), _ptr(auxv), _ptr(n1[b0:b1, r0:r1]),
+                                                 _ptr(n2[b0:b1]), _ptr(x1c[b0:b1, r0:r1]), _ptr(x2c[b0:b1]), _ptr(g1v), _ptr(g2v),
+                                                 _ptr(scratch), nbytes, b1 - b0, r1 - r0, N2, D, _stream(x1c)),
+                      "tpw_cosine_backward_ws")
+            else:
+                check(lib.tpw_dot_backward_ws(code, mode, eng, _ptr(grad[b0:b1, r0:r1]), _ptr(auxv), _ptr(x1c[b0:b1, r0:r1]),
+                                              _ptr(x2c[b0:b1]), _ptr(g1v), _ptr(g2v), _ptr(scratch), nbytes,
+                                              b1 - b0, r1 - r0, N2, D, _stream(x1c)), "tpw_dot_backward_ws")
             if g2 is not None and not (whole or r0 == 0):
                 g2[b0:b1] += part
     return g1, g2
@@ -445,18 +455,22 @@ class _CosineSimilarityFunction(torch.autograd.Function):
         B, N1, N2, D = _sizes(x1c, x2c)
         code = _FLOAT_CODES[x1c.dtype]
         n1, n2 = _row_norm(x1c), _row_norm(x2c)
-        dM = torch.empty_like(g)
-        rowterm = torch.empty((B, N1), dtype=g.dtype, device=g.device)
-        colterm = torch.empty((B, N2), dtype=g.dtype, device=g.device)
-        with torch.cuda.device(x1c.device):
-            check(lib.tpw_cosine_backward_prepare(code, ctx.epilogue, _ptr(g), _ptr(out), _ptr(n1), _ptr(n2),
-                                                  _ptr(dM), _ptr(rowterm), _ptr(colterm), B, N1, N2, _stream(x1c)),
-                  "tpw_cosine_backward_prepare")
-            g1, g2 = _lp_backward_raw(_abi.LP_BWD_MATMUL, dM, None, x1c, x2c, None, 2.0)
-            check(lib.tpw_cosine_backward_finish(code, _ptr(g1), _ptr(x1c), _ptr(n1), _ptr(rowterm), B * N1, D, _stream(x1c)),
-                  "tpw_cosine_backward_finish")
-            check(lib.tpw_cosine_backward_finish(code, _ptr(g2), _ptr(x2c), _ptr(n2), _ptr(colterm), B * N2, D, _stream(x1c)),
-                  "tpw_cosine_backward_finish")
+        fused = _dense_backward_tensor(_abi.LP_BWD_MATMUL, g, out, x1c, x2c, True, True, cosine=(ctx.epilogue, n1, n2))
+        if fused is not None:
+            g1, g2 = fused
+        else:
+            dM = torch.empty_like(g)
+            rowterm = torch.empty((B, N1), dtype=g.dtype, device=g.device)
+            colterm = torch.empty((B, N2), dtype=g.dtype, device=g.device)
+            with torch.cuda.device(x1c.device):
+                check(lib.tpw_cosine_backward_prepare(code, ctx.epilogue, _ptr(g), _ptr(out), _ptr(n1), _ptr(n2),
+                                                      _ptr(dM), _ptr(rowterm), _ptr(colterm), B, N1, N2, _stream(x1c)),
+                      "tpw_cosine_backward_prepare")
+                g1, g2 = _lp_backward_raw(_abi.LP_BWD_MATMUL, dM, None, x1c, x2c, None, 2.0)
+                check(lib.tpw_cosine_backward_finish(code, _ptr(g1), _ptr(x1c), _ptr(n1), _ptr(rowterm), B * N1, D, _stream(x1c)),
+                      "tpw_cosine_backward_finish")
+                check(lib.tpw_cosine_backward_finish(code, _ptr(g2), _ptr(x2c), _ptr(n2), _ptr(colterm), B * N2, D, _stream(x1c)),
+                      "tpw_cosine_backward_finish")
         if ctx.unbatched:
             g1, g2 = g1.squeeze(0), g2.squeeze(0)
         return g1.to(ctx.in_dtype), g2.to(ctx.in_dtype), None

@@ -112,6 +112,16 @@ TPW_API int tpw_lp_rowmin_forward(int dtype, const void *x1, const void *x2, con
                           int64_t B, int64_t N1, int64_t N2, int64_t D,
                           double p, double out_exponent, tpw_stream_t stream);
 
+/*
+ * mask[b,i,j] = (out[b,i,j] <= radius) as one byte (0 / 1) per pair, for out as tpw_lp_forward
+ * defines it with finite p > 0 or p = +inf: the comparison of radius_neighbors_mask
+ * (OPS/neighbors.cpp:37-58: cdist(x1, x2, metric) <= epsilon) fused into the tile epilogue, so the
+ * float matrix is neither written nor read back.  A NaN distance gives 0.
+ */
+TPW_API int tpw_lp_radius_mask_forward(int dtype, const void *x1, const void *x2, const void *w, uint8_t *mask,
+                               int64_t B, int64_t N1, int64_t N2, int64_t D,
+                               double p, double out_exponent, double radius, tpw_stream_t stream);
+
 enum tpw_lp_backward_mode {
     /* ATen cdist backward: aux = forward output o.  p=1: g*sgn(d); p=2: g*d/o;
        other finite p: g*d*|d|^(p-2)/o^(p-1); +inf: g*sgn(d)*[|d|==o]; all 0 where o==0.
@@ -179,8 +189,9 @@ enum tpw_dot_engine {
     TPW_ENGINE_AUTO = 0,
     TPW_ENGINE_SIMT_FP32 = 1,   /* CUDA-core tile, exact fp32/fp64 FMA chain */
     TPW_ENGINE_TCGEN05_BF16X3 = 2, /* TMA-fed tcgen05.mma, bf16 hi/lo split (3 MMAs), fp32 TMEM accumulators */
-    TPW_ENGINE_TCGEN05_TF32X3 = 3  /* same pipeline with tf32 hi/lo parts (22 bits per factor): the gradient
-                                      products of tpw_dot_backward_ws; not a forward engine */
+    TPW_ENGINE_TCGEN05_TF32X3 = 3  /* same pipeline with tf32 hi/lo parts (22 bits per factor) and chunked
+                                      accumulation: the gradient products of tpw_dot_backward_ws and, forward,
+                                      TPW_DOT_LINEAR only (a plain dot product has no norm to hide bf16 rounding behind) */
 };
 
 /*

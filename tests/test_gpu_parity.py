@@ -471,6 +471,24 @@ def test_tensor_core_backward_vs_float64(tensor_engine, shape, op):
     _sum_close(s2, r2, f"{op} grad_x2 (CUDA cores)")
 
 
+@pytest.mark.parametrize("shape", [(2, 300, 520, 200), (1, 130, 257, 70), (1, 64, 64, 4100), (1, 1, 1, 3)], ids=lambda s: "x".join(map(str, s)))
+def test_linear_kernel_tf32_forward(tensor_engine, shape):
+    """linear_kernel on the tensor cores (tf32x3, chunked accumulation) against float64, held to the
+    same bound as the fp32 FMA chain of the CUDA-core tile."""
+    tpw = tensor_engine
+    B, n1, n2, d = shape
+    g = torch.Generator().manual_seed(sum(shape))
+    x1, x2 = torch.randn(B, n1, d, generator=g).cuda(), torch.randn(B, n2, d, generator=g).cuda()
+    ref = x1.double() @ x2.double().transpose(1, 2)
+    _sum_close(tpw.linear_kernel(x1, x2), ref, "linear_kernel (tensor cores)")
+    tpw.set_dot_engine("simt")
+    _sum_close(tpw.linear_kernel(x1, x2), ref, "linear_kernel (CUDA cores)")
+    tpw.set_dot_engine("tcgen05")
+    # the kernels built on it
+    _sum_close(tpw.polynomial_kernel(x1[0], x2[0], degree=2, gamma=0.01, coef0=1.0),
+               (0.01 * ref[0] + 1.0) ** 2, "polynomial_kernel")
+
+
 def test_tensor_core_backward_blocking_and_abi(tensor_engine, monkeypatch):
     """Scratch-capped blocking (groups of batches, row blocks of one batch) reproduces the single
     call; one-sided gradients; argument checks of the C entry point."""
@@ -669,6 +687,30 @@ def test_pairwise_argmin_min_ties_and_edges(tpw):
         tpw.pairwise_argmin_min(x, y, "minkowski", -1.0)
     e_arg, e_mn = tpw.pairwise_argmin_min(x[:0], y)
     assert e_arg.shape == (0,) and e_mn.shape == (0,)
+
+
+@pytest.mark.parametrize("shapes", [((130, 7), (257, 7)), ((3, 200, 32), (3, 144, 32)), ((513, 36), (1008, 36)), ((1, 5), (1, 5))],
+                         ids=lambda s: "x".join(map(str, s[0])) + "_" + "x".join(map(str, s[1])))
+def test_radius_mask_fused_equals_compare_pass(tpw, shapes):
+    """radius_neighbors_mask through the fused epilogue (one byte per pair, no float matrix) equals
+    `distance <= epsilon` on the matrix the same kernel writes, metric by metric and dtype by dtype."""
+    rng = np.random.default_rng(zlib.crc32(repr(shapes).encode()))
+    a = cuda(rng.standard_normal(shapes[0]).astype(np.float32))
+    b = cuda(rng.standard_normal(shapes[1]).astype(np.float32))
+    for metric, kw, fn in (("euclidean", {}, tpw.euclidean_distances), ("manhattan", {}, tpw.manhattan_distances),
+                           ("chebyshev", {}, tpw.chebyshev_distances), ("sqeuclidean", {}, tpw.sqeuclidean_distances),
+                           ("minkowski", {"p": 3.0}, lambda x, y: tpw.minkowski_distances(x, y, 3.0)),
+                           ("minkowski", {"p": 1.5}, lambda x, y: tpw.minkowski_distances(x, y, 1.5))):
+        for x, y in ((a, b), (a.double(), b.double())):
+            dist = fn(x, y)
+            eps = float(dist.median())
+            mask = tpw.radius_neighbors_mask(x, y, eps, metric, **kw)
+            assert mask.dtype == torch.bool and mask.shape == dist.shape
+            assert torch.equal(mask, dist <= eps), (metric, kw, x.dtype)
+            assert 0 < int(mask.sum()) < mask.numel() or mask.numel() == 1
+    assert torch.equal(tpw.radius_neighbors_mask(a, None, 0.0, "manhattan").diagonal(dim1=-2, dim2=-1).all(), torch.tensor(True, device="cuda"))
+    with pytest.raises(RuntimeError, match="non-negative"):
+        tpw.radius_neighbors_mask(a, b, -1.0)
 
 
 def test_bounded_wait_reports_instead_of_hanging(tpw):

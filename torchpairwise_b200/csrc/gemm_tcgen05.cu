@@ -758,8 +758,15 @@ using namespace tpw;
 extern "C" int tpw_dot_metric_forward_simt(int dtype, int epilogue, const void *x1, const void *x2, void *out,
                                            int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream);
 
+// tf32 x 3 forward (plain dot products only): straight hi/lo copies of both operands
+static long long tf32_forward_scratch(long long B, long long N1, long long N2, long long D) {
+    const long long Dp = align_up(D, 4);
+    return 2 * align_up(B * N1 * Dp * 4, 1024) + 2 * align_up(B * N2 * Dp * 4, 1024);
+}
+
 extern "C" int64_t tpw_dot_metric_scratch_bytes(int dtype, int engine, int64_t B, int64_t N1, int64_t N2, int64_t D) {
     if (B <= 0 || N1 <= 0 || N2 <= 0 || D <= 0 || dtype != TPW_F32) return 0;
+    if (engine == TPW_ENGINE_TCGEN05_TF32X3) return tf32_forward_scratch(B, N1, N2, D);
     if (engine == TPW_ENGINE_TCGEN05_BF16X3 || (engine == TPW_ENGINE_AUTO && auto_picks_tensor_cores(dtype, B, N1, N2, D)))
         return scratch_layout(B, N1, N2, D, false).total;
     return 0;
@@ -769,7 +776,36 @@ extern "C" int tpw_dot_metric_forward_ws(int dtype, int epilogue, int engine,
                                          const void *x1, const void *x2, void *out, void *scratch, int64_t scratch_bytes,
                                          int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream) {
     clear_error();
-    TPW_CHECK_ARG(engine >= TPW_ENGINE_AUTO && engine <= TPW_ENGINE_TCGEN05_BF16X3, "tpw_dot_metric_forward_ws: bad engine %d", engine);
+    TPW_CHECK_ARG(engine >= TPW_ENGINE_AUTO && engine <= TPW_ENGINE_TCGEN05_TF32X3, "tpw_dot_metric_forward_ws: bad engine %d", engine);
+    if (engine == TPW_ENGINE_TCGEN05_TF32X3) {
+        // x1 . x2^T with fp32-chain accuracy: tf32 high/low parts, chunked accumulation (see the gradient products)
+        TPW_CHECK_ARG(dtype == TPW_F32 && epilogue == TPW_DOT_LINEAR,
+                      "tpw_dot_metric_forward_ws: the tf32 engine computes float32 plain dot products (TPW_DOT_LINEAR) only");
+        TPW_CHECK_ARG(B >= 0 && N1 >= 0 && N2 >= 0 && D >= 0, "tpw_dot_metric_forward_ws: negative size");
+        if (B == 0 || N1 == 0 || N2 == 0) return TPW_OK;
+        TPW_CHECK_ARG(x1 && x2 && out && D > 0, "tpw_dot_metric_forward_ws: NULL pointer or empty feature dimension");
+        TPW_CHECK_ARG(N1 < (1ll << 31) && N2 < (1ll << 31) && D < (1ll << 31), "tpw_dot_metric_forward_ws: a dimension exceeds 2^31-1");
+        const long long need = tf32_forward_scratch(B, N1, N2, D);
+        TPW_CHECK_ARG(scratch != nullptr && scratch_bytes >= need && aligned16(scratch),
+                      "tpw_dot_metric_forward_ws: the tf32 engine needs %lld bytes of 16-byte aligned scratch (got %lld)", need, (long long)scratch_bytes);
+        cudaStream_t s = static_cast<cudaStream_t>(stream);
+        const long long Dp = align_up(D, 4), xa = align_up(B * N1 * Dp * 4, 1024), ya = align_up(B * N2 * Dp * 4, 1024);
+        unsigned char *base = static_cast<unsigned char *>(scratch);
+        float *xhi = reinterpret_cast<float *>(base), *xlo = reinterpret_cast<float *>(base + xa);
+        float *yhi = reinterpret_cast<float *>(base + 2 * xa), *ylo = reinterpret_cast<float *>(base + 2 * xa + ya);
+        int st;
+        for (int side = 0; side < 2; ++side) {
+            SplitParams X;
+            memset(&X, 0, sizeof(X));
+            X.a = static_cast<const float *>(side == 0 ? x1 : x2);
+            X.hi = side == 0 ? xhi : yhi;
+            X.lo = side == 0 ? xlo : ylo;
+            X.R = side == 0 ? N1 : N2; X.C = D; X.Cp = Dp; X.Rp = align_up(X.R, 4);
+            X.vec_in = (D % 4 == 0 && aligned16(X.a)) ? 1 : 0;
+            if ((st = launch_split<COEF_ID, true, false, false>(X, B, s)) != TPW_OK) return st;
+        }
+        return launch_tf32_product(xhi, xlo, yhi, ylo, static_cast<float *>(out), B, N1, N2, Dp, s);
+    }
     if (engine == TPW_ENGINE_AUTO && auto_picks_tensor_cores(dtype, B, N1, N2, D) && scratch != nullptr &&
         scratch_bytes >= scratch_layout(B, N1, N2, D, false).total)
         engine = TPW_ENGINE_TCGEN05_BF16X3;

@@ -45,6 +45,10 @@ struct FwdParams {
     // Non-NULL (fp32 L_p kinds only): the tile is not stored; every x1 row folds its smallest
     // finished value, packed as (float bits << 32 | x2 row), into keys[b * N1 + i] with atomicMin.
     unsigned long long *rowmin_keys;
+    // Non-NULL (L_p kinds): the tile is not stored; one byte per pair, finished value <= threshold.
+    unsigned char *mask_out;
+    double threshold;
+    int mask_vec;        // N2 % 16 == 0 and 16-byte aligned mask: staged 128-bit stores
 };
 
 template <typename T> struct Vec16;
@@ -361,6 +365,44 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
         }
     }
 
+    if constexpr (KIND == K_L1 || KIND == K_P2 || KIND == K_P3 || KIND == K_PGEN || KIND == K_MAX) {
+        if (P.mask_out) {
+            // Radius test fused into the epilogue: a quarter of the bytes of the float matrix and no second pass.
+            unsigned char *mout = P.mask_out + b * P.N1 * P.N2;
+            const T thr = static_cast<T>(P.threshold);
+            if (P.mask_vec) {
+                constexpr int ROWB = TILE + 16;
+                static_assert(TILE * ROWB <= kStages * 2 * S::TILE_BYTES, "mask staging tile must fit in the operand stages");
+                __syncthreads();
+#pragma unroll
+                for (int ri = 0; ri < R; ++ri)
+#pragma unroll
+                    for (int rj = 0; rj < R; ++rj)
+                        smem[(ti + 16 * ri) * ROWB + tj + 16 * rj] =
+                            static_cast<T>(finish<T, OutT, KIND>(acc[ri][rj], T(0), T(0), P)) <= thr ? 1 : 0;
+                __syncthreads();
+                for (int idx = tid; idx < TILE * (TILE / 16); idx += kThreads) {
+                    const int rr = idx / (TILE / 16), cc = idx % (TILE / 16);
+                    const long long i = i0 + rr, j = j0 + cc * 16;
+                    if (i < P.N1 && j < P.N2) // N2 % 16 == 0: a 16-byte group is entirely inside or outside
+                        *reinterpret_cast<uint4 *>(mout + i * P.N2 + j) = *reinterpret_cast<const uint4 *>(smem + rr * ROWB + cc * 16);
+                }
+            } else {
+#pragma unroll
+                for (int ri = 0; ri < R; ++ri) {
+                    const long long i = i0 + ti + 16 * ri;
+                    if (i >= P.N1) continue;
+#pragma unroll
+                    for (int rj = 0; rj < R; ++rj) {
+                        const long long j = j0 + tj + 16 * rj;
+                        if (j < P.N2) mout[i * P.N2 + j] = static_cast<T>(finish<T, OutT, KIND>(acc[ri][rj], T(0), T(0), P)) <= thr ? 1 : 0;
+                    }
+                }
+            }
+            return;
+        }
+    }
+
     OutT *out = reinterpret_cast<OutT *>(P.out) + b * P.N1 * P.N2;
     if (sizeof(OutT) == 4 && P.vec_store) {
         // Full tiles of 4-byte outputs go through shared memory (the operand stages are free now):
@@ -536,6 +578,27 @@ extern "C" int tpw_lp_rowmin_forward(int dtype, const void *x1, const void *x2, 
                                                                      reinterpret_cast<long long *>(arg_out), n);
     TPW_LAUNCH_OK("rowmin_finish_kernel");
     return TPW_OK;
+}
+
+extern "C" int tpw_lp_radius_mask_forward(int dtype, const void *x1, const void *x2, const void *w, uint8_t *mask,
+                                          int64_t B, int64_t N1, int64_t N2, int64_t D,
+                                          double p, double out_exponent, double radius, tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(dtype == TPW_F32 || dtype == TPW_F64, "tpw_lp_radius_mask_forward: dtype must be TPW_F32 or TPW_F64");
+    TPW_CHECK_ARG(B >= 0 && N1 >= 0 && N2 >= 0 && D >= 0, "tpw_lp_radius_mask_forward: negative size");
+    if (B == 0 || N1 == 0 || N2 == 0) return TPW_OK;
+    TPW_CHECK_ARG(x1 && x2 && mask, "tpw_lp_radius_mask_forward: NULL pointer");
+    TPW_CHECK_ARG(D > 0, "tpw_lp_radius_mask_forward: D must be positive");
+    TPW_CHECK_ARG(p > 0 && !isnan(p) && !isnan(out_exponent) && !isnan(radius), "tpw_lp_radius_mask_forward: p must be positive (got %g)", p);
+    FwdParams P;
+    memset(&P, 0, sizeof(P));
+    P.x1 = x1; P.x2 = x2; P.w = w; P.out = nullptr;
+    P.B = B; P.N1 = N1; P.N2 = N2; P.D = D;
+    P.mask_out = mask;
+    P.threshold = radius;
+    P.mask_vec = (N2 % 16 == 0 && aligned16(mask)) ? 1 : 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return dtype == TPW_F32 ? lp_forward_typed<float>(P, p, out_exponent, s) : lp_forward_typed<double>(P, p, out_exponent, s);
 }
 
 extern "C" int tpw_dot_metric_forward_simt(int dtype, int epilogue, const void *x1, const void *x2, void *out,

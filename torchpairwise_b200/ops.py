@@ -826,8 +826,10 @@ class _LinearKernelFunction(torch.autograd.Function):
         in_dtype = x1.dtype
         cdt = _compute_dtype(in_dtype)
         x1c, x2c, unbatched = _batched(x1.to(cdt), x2.to(cdt), "linear_kernel")
-        # the raw dot product has no norm to hide cancellation behind: always the exact fp32 tile
-        out = _dot_forward_raw(x1c, x2c, _abi.DOT_LINEAR, _abi.ENGINE_SIMT_FP32)
+        # the raw dot product has no norm to hide bf16 rounding behind: tf32 x 3 with chunked accumulation
+        # (as accurate as the fp32 FMA chain) on large problems, the exact fp32 / fp64 tile otherwise
+        tensor = _dot_engine != _abi.ENGINE_SIMT_FP32 and _tensor_engine_selected(x1c, x2c)
+        out = _dot_forward_raw(x1c, x2c, _abi.DOT_LINEAR, _abi.ENGINE_TCGEN05_TF32X3 if tensor else _abi.ENGINE_SIMT_FP32)
         ctx.save_for_backward(x1c, x2c)
         ctx.unbatched, ctx.in_dtype = unbatched, in_dtype
         return (out.squeeze(0) if unbatched else out).to(in_dtype)
@@ -969,6 +971,22 @@ def radius_neighbors_mask(x1: Tensor, x2: Optional[Tensor] = None, epsilon: floa
     if epsilon < 0:
         raise RuntimeError(f"epsilon must be non-negative. Got epsilon={epsilon}")
     with torch.no_grad():
+        if metric in _ROWMIN_METRICS and x1_.is_cuda and set(kwargs) <= {"p"} and x1_.dtype == x2_.dtype \
+                and x1_.dtype in _FLOAT_CODES and x1_.size(-1) > 0:
+            pp, ex = _ROWMIN_METRICS[metric]
+            if pp is None:
+                pp = 2.0 if kwargs.get("p") is None else float(kwargs["p"])
+                ex = 1.0 if math.isinf(pp) else (1.0 / pp if pp > 0 else None)
+            x1c, x2c, unbatched = _batched(x1_, x2_, "radius_neighbors_mask")
+            # p = 2 on a large float32 problem is faster as a tensor-core contraction plus a compare pass
+            if ex is not None and pp > 0 and not (pp == 2.0 and _tensor_engine_selected(x1c, x2c)):
+                B, N1, N2, D = _sizes(x1c, x2c)
+                mask = torch.empty((B, N1, N2), dtype=torch.bool, device=x1c.device)
+                with torch.cuda.device(x1c.device):
+                    check(lib.tpw_lp_radius_mask_forward(_FLOAT_CODES[x1c.dtype], _ptr(x1c), _ptr(x2c), None, _ptr(mask),
+                                                         B, N1, N2, D, pp, ex, float(epsilon), _stream(x1c)),
+                          "tpw_lp_radius_mask_forward")
+                return mask.squeeze(0) if unbatched else mask
         return cdist(x1_, x2_, metric, **kwargs) <= epsilon
 
 

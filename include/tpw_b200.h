@@ -99,7 +99,7 @@ TPW_API int tpw_lp_forward(int dtype, const void *x1, const void *x2, const void
  * arg_out[b,i] = the smallest j that attains it, for out as tpw_lp_forward defines it with
  * finite p > 0 or p = +inf.  The [B,N1,N2] matrix is never written: each 128x128 tile is
  * reduced in registers and warp shuffles and folded into one 64-bit key per x1 row.
- * float32 only (TPW_F32).  A NaN distance ranks above +inf; N2 = 0 gives +inf and -1.
+ * float32 only (TPW_F32), w must be NULL.  A NaN distance ranks above +inf; N2 = 0 gives +inf and -1.
  * scratch: tpw_lp_rowmin_scratch_bytes(B, N1) bytes on the device, 8-byte aligned; the call
  * initialises it.  Either of min_out / arg_out may be NULL.
  *
@@ -116,7 +116,7 @@ TPW_API int tpw_lp_rowmin_forward(int dtype, const void *x1, const void *x2, con
  * mask[b,i,j] = (out[b,i,j] <= radius) as one byte (0 / 1) per pair, for out as tpw_lp_forward
  * defines it with finite p > 0 or p = +inf: the comparison of radius_neighbors_mask
  * (OPS/neighbors.cpp:37-58: cdist(x1, x2, metric) <= epsilon) fused into the tile epilogue, so the
- * float matrix is neither written nor read back.  A NaN distance gives 0.
+ * float matrix is neither written nor read back.  A NaN distance gives 0.  w must be NULL.
  */
 TPW_API int tpw_lp_radius_mask_forward(int dtype, const void *x1, const void *x2, const void *w, uint8_t *mask,
                                int64_t B, int64_t N1, int64_t N2, int64_t D,

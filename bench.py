@@ -147,7 +147,7 @@ def run_reference(args, rank: int):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    rows = 128
+    rows = 512  # the same row block as the cpu_baseline leg of the GPU arm
     cpu_reference_step(rows, threads)  # library load + first-touch, not counted as a warm-up step
     for _ in range(args.warmup):
         cpu_reference_step(rows, threads)

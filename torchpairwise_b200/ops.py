@@ -1005,7 +1005,8 @@ def k_neighbors_mask(x1: Tensor, x2: Optional[Tensor] = None, k: int = 1, metric
             out = torch.zeros((x1_.size(0), x2_.size(0)), dtype=torch.bool, device=x1_.device)
             return out.scatter_(1, inds, True)
         dists = cdist(x1_, x2_, metric, **kwargs)
-        inds = dists.argsort(dim=1, descending=False)[:, : k + 1]
+        # the k + 1 smallest of every row: a partial selection, not the reference's full argsort of each row
+        inds = dists.topk(min(k + 1, dists.size(1)), dim=1, largest=False, sorted=False).indices
         out = torch.zeros((x1_.size(0), x2_.size(0)), dtype=torch.bool, device=x1_.device)
         out.scatter_(1, inds, True)
         return out

@@ -480,6 +480,9 @@ def run_suite(args):
     for name, fn in (("C4_sqeuclidean", tpw.sqeuclidean_distances), ("C4_cosine", tpw.cosine_distances)):
         if want(name):
             entry(name, n, timeit(lambda: fn(X, Y)), "bf16 tensor (executed flops = 3 x algorithmic)", 3 * 2 * n * 512, bf16_peak, 4 * n)
+    if want("C4_sqeuclidean_rowmin"):
+        entry("C4_sqeuclidean_rowmin", n, timeit(lambda: tpw.pairwise_argmin_min(X, Y, "sqeuclidean")),
+              "bf16 tensor (executed flops = 3 x algorithmic; matrix never written)", 3 * 2 * n * 512, bf16_peak, 0)
     if want("C4_sqeuclidean_bwd"):
         Xg, Yg = X.clone().requires_grad_(True), Y.clone().requires_grad_(True)
         out = tpw.sqeuclidean_distances(Xg, Yg)

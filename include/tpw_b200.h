@@ -209,6 +209,21 @@ TPW_API int tpw_dot_metric_forward_ws(int dtype, int epilogue, int engine,
                               int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream);
 
 /*
+ * Streaming row minimum of the squared Euclidean / Euclidean distance on the tensor cores (float32):
+ * min_out[b,i] = min_j d(x1[b,i], x2[b,j]), arg_out[b,i] = the smallest j that attains it.  The bf16 x 3
+ * pipeline of tpw_dot_metric_forward_ws with an epilogue in which every thread folds the columns
+ * of its row into one 64-bit key; no [B,N1,N2] matrix is written, so the kernel stays bound by the
+ * tensor pipe.  Distances carry the rounding of that pipeline (within the float32 parity tolerance);
+ * between candidates closer than that the choice may differ from an exact evaluation.
+ * scratch: tpw_dot_rowmin_scratch_bytes(...) bytes, 16-byte aligned.  No counterpart in the
+ * reference (OPS/neighbors.cpp:10-35 sorts rows of the materialised matrix).
+ */
+TPW_API int64_t tpw_dot_rowmin_scratch_bytes(int64_t B, int64_t N1, int64_t N2, int64_t D);
+TPW_API int tpw_dot_rowmin_forward_ws(int epilogue, const void *x1, const void *x2, float *min_out, int64_t *arg_out,
+                              void *scratch, int64_t scratch_bytes,
+                              int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream);
+
+/*
  * Backward of the p = 2 metrics and the plain gradient products as two tensor-core contractions:
  *   TPW_LP_BWD_PPMINKOWSKI (sqeuclidean): C = g,      grad_x1 = 2 (x1 * rowsum(C) - C x2),  grad_x2 = 2 (x2 * colsum(C) - C^T x1)
  *   TPW_LP_BWD_CDIST       (euclidean):   C = g / o (0 where o == 0), same without the factor 2; aux = o

@@ -646,6 +646,27 @@ def test_pairwise_argmin_min_matches_oracle(tpw, shapes, metric, p, pp, ex):
         assert torch.equal(full.min(-1).values, mn)
 
 
+@pytest.mark.parametrize("shape", [(1, 300, 520, 96), (2, 257, 1030, 130), (1, 128, 256, 64), (1, 5, 3, 8)], ids=lambda s: "x".join(map(str, s)))
+def test_pairwise_argmin_min_tensor_cores(tensor_engine, shape):
+    """Euclidean / squared Euclidean row minimum in the tcgen05 epilogue (forced) against the float64
+    matrix: value within the float32 contract, chosen column attains the minimum within the same bound."""
+    tpw = tensor_engine
+    B, n1, n2, d = shape
+    g = torch.Generator().manual_seed(sum(shape))
+    x1, x2 = torch.randn(B, n1, d, generator=g), torch.randn(B, n2, d, generator=g)
+    ref = O.cdist(x1.double().numpy(), x2.double().numpy(), 2.0)
+    tol = TOL[torch.float32]
+    for metric, r in (("euclidean", ref), ("sqeuclidean", ref * ref)):
+        arg, mn = tpw.pairwise_argmin_min(x1.cuda(), x2.cuda(), metric)
+        assert arg.shape == (B, n1) and arg.dtype == torch.int64
+        close(mn.double(), r.min(-1), tol, msg=metric + " row minimum")
+        picked = np.take_along_axis(r, arg.cpu().numpy()[..., None], -1)[..., 0]
+        np.testing.assert_allclose(picked, r.min(-1), rtol=tol["rtol"], atol=tol["atol"])
+        # the matrix the same engine writes has the same row minimum
+        full = tpw.euclidean_distances(x1.cuda(), x2.cuda()) if metric == "euclidean" else tpw.sqeuclidean_distances(x1.cuda(), x2.cuda())
+        assert torch.equal(full.min(-1).values, mn)
+
+
 def test_pairwise_argmin_min_ties_and_edges(tpw):
     """Exact ties go to the smaller x2 row (integer-valued inputs make the distances exact), in a
     tile interior, across the 128-column tile boundary and across batches; other dtypes and the

@@ -47,6 +47,8 @@ SIGNATURES = {
     "tpw_lp_inf_backward": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _P]),
     "tpw_dot_metric_forward": (_I, [_I, _I, _I, _P, _P, _P, _L, _L, _L, _L, _P]),
     "tpw_dot_metric_scratch_bytes": (_L, [_I, _I, _L, _L, _L, _L]),
+    "tpw_dot_rowmin_scratch_bytes": (_L, [_L, _L, _L, _L]),
+    "tpw_dot_rowmin_forward_ws": (_I, [_I, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P]),
     "tpw_dot_backward_scratch_bytes": (_L, [_I, _I, _I, _L, _L, _L, _L]),
     "tpw_dot_backward_ws": (_I, [_I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P]),
     "tpw_cosine_backward_ws": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P]),

@@ -16,6 +16,13 @@
 // 128 x 256 fp32 accumulators so the epilogue of tile t overlaps the MMAs of tile t + 1.
 // No cluster launch: every CTA fetches its own tiles, with plain per-CTA TMA loads, from this GPU's memory.
 //
+// Three more instantiations share the pipeline: (1) kind::tf32 operands (high/low tf32 parts in fp32
+// containers, 32 elements per k-step) for the gradient products of the backward and for plain dot
+// products, with the reduction cut into chunks of 64 elements whose accumulators the epilogue warps
+// add, rounded to nearest, into register-resident sums (the tensor cores add into tensor memory with
+// truncation; see dense_backward_tensor below); (2) a row-minimum epilogue that folds each thread's
+// accumulator row into one 64-bit key and stores no tile; (3) SELF, which zeroes the diagonal.
+//
 // Every wait (mbarrier) is bounded; a warp that gives up raises a CTA-wide abort flag that the other
 // roles poll, everybody falls through to the final barrier, tensor memory is released, and the
 // device status word reports the site.
@@ -58,6 +65,7 @@ struct GemmParams {
     int self;                 // x2 is x1: the diagonal of the distance epilogues is exactly zero
     int vec_store;            // N2 % 4 == 0 and out 16-byte aligned
     int kchunk;               // k-steps accumulated in tensor memory before the sum moves to registers (0: all)
+    unsigned long long *rowmin_keys; // ROWMIN instantiation: [B*N1] keys (float bits << 32 | x2 row), nothing is stored to out
     int *status;
 };
 
@@ -161,7 +169,7 @@ __device__ __forceinline__ float dot_epilogue(float dot, float n1, float n2, boo
 // TF32 = false: operands are bf16 high/low parts, 64 per k-step; true: tf32 high/low parts in fp32
 // containers, 32 per k-step.  Either way a k-step is one 128-byte swizzled row per operand row and
 // four MMAs per operand pair, so the pipeline below is the same.
-template <int EPI, bool SELF, bool TF32>
+template <int EPI, bool SELF, bool TF32, bool ROWMIN = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_constant__ CUtensorMap map_xl,
                    const __grid_constant__ CUtensorMap map_yh, const __grid_constant__ CUtensorMap map_yl,
@@ -376,6 +384,7 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
             const float n1 = (EPI != TPW_DOT_LINEAR && row_ok) ? P.n1sq[b * P.N1 + i] : 0.f;
             float *orow = P.out + (b * P.N1 + (row_ok ? i : 0)) * P.N2;
             const float *n2p = P.n2sq + b * P.N2;
+            unsigned long long best = ~0ull;
 #pragma unroll 1
             for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
                 uint32_t r[32];
@@ -384,6 +393,19 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
                 tmem_ld_wait();
                 const long long j0 = tn * BN + c * 32;
                 if (j0 >= P.N2) continue;
+                if constexpr (ROWMIN) {
+                    // streaming row minimum: this thread owns row i and folds its 32 columns into one key
+                    // (the epilogue value is non-negative, so its bit pattern orders like an unsigned integer)
+#pragma unroll
+                    for (int v = 0; v < 32; ++v) {
+                        const long long j = j0 + v;
+                        const float nn = j < P.N2 ? __ldg(n2p + j) : 0.f;
+                        const float o = dot_epilogue<EPI>(__uint_as_float(r[v]), n1, nn, false);
+                        const unsigned long long key = ((unsigned long long)__float_as_uint(o) << 32) | (unsigned long long)(uint32_t)j;
+                        if (j < P.N2 && key < best) best = key;
+                    }
+                    continue;
+                }
                 if (!row_ok && !(P.vec_store && j0 + 32 <= P.N2)) continue;
                 if (P.vec_store && j0 + 32 <= P.N2) {
                     // epilogue math on this thread's row, staged with a 16-byte-chunk XOR swizzle ...
@@ -418,6 +440,9 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
                             orow[j] = dot_epilogue<EPI>(__uint_as_float(r[v]), n1, EPI == TPW_DOT_LINEAR ? 0.f : __ldg(n2p + j), SELF && i == j);
                     }
                 }
+            }
+            if constexpr (ROWMIN) {
+                if (row_ok && best != ~0ull) atomicMin(P.rowmin_keys + b * P.N1 + i, best);
             }
             // this warp has drained its quarter of accumulator `a`
             tc_fence_before();
@@ -762,6 +787,84 @@ extern "C" int tpw_dot_metric_forward_simt(int dtype, int epilogue, const void *
 static long long tf32_forward_scratch(long long B, long long N1, long long N2, long long D) {
     const long long Dp = align_up(D, 4);
     return 2 * align_up(B * N1 * Dp * 4, 1024) + 2 * align_up(B * N2 * Dp * 4, 1024);
+}
+
+namespace tpw {
+namespace {
+// keys -> (smallest value, optionally its square root; its x2 row)
+__global__ void dot_rowmin_finish_kernel(const unsigned long long *__restrict__ keys, float *__restrict__ min_out,
+                                         long long *__restrict__ arg_out, long long n, int take_sqrt) {
+    const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (t >= n) return;
+    const unsigned long long key = keys[t];
+    const bool none = key == ~0ull;
+    float v = none ? __int_as_float(0x7f800000) : __uint_as_float((uint32_t)(key >> 32));
+    if (take_sqrt) v = sqrtf(v);
+    if (min_out) min_out[t] = v;
+    if (arg_out) arg_out[t] = none ? -1ll : (long long)(uint32_t)key;
+}
+} // namespace
+} // namespace tpw
+
+extern "C" int64_t tpw_dot_rowmin_scratch_bytes(int64_t B, int64_t N1, int64_t N2, int64_t D) {
+    if (B <= 0 || N1 <= 0 || N2 <= 0 || D <= 0) return 0;
+    return scratch_layout(B, N1, N2, D, false).total + align_up(B * N1 * 8, 1024);
+}
+
+extern "C" int tpw_dot_rowmin_forward_ws(int epilogue, const void *x1, const void *x2, float *min_out, int64_t *arg_out,
+                                         void *scratch, int64_t scratch_bytes,
+                                         int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(epilogue == TPW_DOT_SQEUCLIDEAN || epilogue == TPW_DOT_EUCLIDEAN,
+                  "tpw_dot_rowmin_forward_ws: epilogue must be TPW_DOT_SQEUCLIDEAN or TPW_DOT_EUCLIDEAN");
+    TPW_CHECK_ARG(B > 0 && N1 > 0 && N2 > 0 && D > 0, "tpw_dot_rowmin_forward_ws: sizes must be positive");
+    TPW_CHECK_ARG(x1 && x2 && (min_out || arg_out), "tpw_dot_rowmin_forward_ws: NULL pointer");
+    TPW_CHECK_ARG(N1 < (1ll << 31) && N2 < (1ll << 31) && B < (1ll << 31) && D < (1ll << 31),
+                  "tpw_dot_rowmin_forward_ws: a dimension exceeds 2^31-1");
+    const ScratchLayout L = scratch_layout(B, N1, N2, D, false);
+    const long long need = L.total + align_up(B * N1 * 8, 1024);
+    TPW_CHECK_ARG(scratch != nullptr && scratch_bytes >= need && aligned16(scratch),
+                  "tpw_dot_rowmin_forward_ws: needs %lld bytes of 16-byte aligned scratch (got %lld)", need, (long long)scratch_bytes);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned char *base = static_cast<unsigned char *>(scratch);
+    __nv_bfloat16 *xh = reinterpret_cast<__nv_bfloat16 *>(base + L.off_xh), *xl = reinterpret_cast<__nv_bfloat16 *>(base + L.off_xl);
+    __nv_bfloat16 *yh = reinterpret_cast<__nv_bfloat16 *>(base + L.off_yh), *yl = reinterpret_cast<__nv_bfloat16 *>(base + L.off_yl);
+    float *n1 = reinterpret_cast<float *>(base + L.off_n1), *n2 = reinterpret_cast<float *>(base + L.off_n2);
+    unsigned long long *keys = reinterpret_cast<unsigned long long *>(base + L.total);
+    TPW_CUDA_OK(cudaMemsetAsync(keys, 0xFF, (size_t)(B * N1) * 8, s));
+    const int threads = 256;
+    const long long cap = (long long)sm_count() * 16;
+    long long blocks = (B * N1 * 32 + threads - 1) / threads;
+    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x1, xh, xl, n1, B * N1, D, L.Dp, 0);
+    blocks = (B * N2 * 32 + threads - 1) / threads;
+    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x2, yh, yl, n2, B * N2, D, L.Dp, 0);
+    TPW_LAUNCH_OK("split_rows_kernel");
+    CUtensorMap mxh, mxl, myh, myl;
+    int st;
+    if ((st = make_tensor_map_3d(&mxh, xh, 2, L.Dp, N1, B, BK, BM, true)) != TPW_OK) return st;
+    if ((st = make_tensor_map_3d(&mxl, xl, 2, L.Dp, N1, B, BK, BM, true)) != TPW_OK) return st;
+    if ((st = make_tensor_map_3d(&myh, yh, 2, L.Dp, N2, B, BK, BN, true)) != TPW_OK) return st;
+    if ((st = make_tensor_map_3d(&myl, yl, 2, L.Dp, N2, B, BK, BN, true)) != TPW_OK) return st;
+    GemmParams P;
+    memset(&P, 0, sizeof(P));
+    P.n1sq = n1; P.n2sq = n2; P.out = nullptr;
+    P.B = B; P.N1 = N1; P.N2 = N2; P.D = L.Dp;
+    P.tiles_m = (N1 + BM - 1) / BM;
+    P.tiles_n = (N2 + BN - 1) / BN;
+    P.tiles = B * P.tiles_m * P.tiles_n;
+    P.epilogue = TPW_DOT_SQEUCLIDEAN;
+    P.rowmin_keys = keys;
+    P.status = device_status_ptr();
+    const long long nsm = sm_count();
+    const unsigned grid = (unsigned)(P.tiles < nsm ? P.tiles : nsm);
+    auto kern = gemm_metric_kernel<TPW_DOT_SQEUCLIDEAN, false, false, true>;
+    TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
+    kern<<<grid, kThreads, SMEM_ALLOC, s>>>(mxh, mxl, myh, myl, P);
+    TPW_LAUNCH_OK("gemm_metric_kernel (row minimum)");
+    dot_rowmin_finish_kernel<<<(unsigned)((B * N1 + 255) / 256), 256, 0, s>>>(keys, min_out, reinterpret_cast<long long *>(arg_out), B * N1,
+                                                                             epilogue == TPW_DOT_EUCLIDEAN ? 1 : 0);
+    TPW_LAUNCH_OK("dot_rowmin_finish_kernel");
+    return TPW_OK;
 }
 
 extern "C" int64_t tpw_dot_metric_scratch_bytes(int dtype, int engine, int64_t B, int64_t N1, int64_t N2, int64_t D) {

@@ -1052,6 +1052,17 @@ def pairwise_argmin_min(x1: Tensor, x2: Optional[Tensor] = None, metric: str = "
             dist = _lp_forward_raw(x1c.to(_compute_dtype(x1c.dtype)), x2c.to(_compute_dtype(x2c.dtype)), None, pp, ex)
             mins, args = dist.min(dim=-1)
             mins = mins.to(x1c.dtype)
+        elif pp == 2.0 and _tensor_engine_selected(x1c, x2c):
+            # large float32 problem: the contraction form on the tensor cores with the row minimum taken in
+            # the epilogue (bf16 x 3 rounding: candidates closer than ~1e-5 of the norms may swap)
+            mins = torch.empty((B, N1), dtype=torch.float32, device=x1c.device)
+            args = torch.empty((B, N1), dtype=torch.int64, device=x1c.device)
+            nbytes = lib.tpw_dot_rowmin_scratch_bytes(B, N1, N2, D)
+            scratch = torch.empty((nbytes,), dtype=torch.uint8, device=x1c.device)
+            with torch.cuda.device(x1c.device):
+                check(lib.tpw_dot_rowmin_forward_ws(_abi.DOT_EUCLIDEAN if ex == 0.5 else _abi.DOT_SQEUCLIDEAN, _ptr(x1c), _ptr(x2c),
+                                                    _ptr(mins), _ptr(args), _ptr(scratch), nbytes, B, N1, N2, D, _stream(x1c)),
+                      "tpw_dot_rowmin_forward_ws")
         else:
             mins = torch.empty((B, N1), dtype=torch.float32, device=x1c.device)
             args = torch.empty((B, N1), dtype=torch.int64, device=x1c.device)

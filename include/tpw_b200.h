@@ -229,14 +229,16 @@ TPW_API int tpw_dot_rowmin_forward_ws(int epilogue, const void *x1, const void *
  *   TPW_LP_BWD_CDIST       (euclidean):   C = g / o (0 where o == 0), same without the factor 2; aux = o
  *   TPW_LP_BWD_MATMUL:                    grad_x1 = g x2, grad_x2 = g^T x1
  * (OPS/cpu/ppminkowski_kernel.cpp:131-169 for p = 2; ATen's cdist backward under
- * OPS/pairwise_metrics.cpp:30; the matmul nodes under :64,121,203.)  A pre-pass writes C and C^T
- * as tf32 high/low parts, tcgen05.mma accumulates hi.hi + hi.lo + lo.hi in fp32, row and column
- * sums are reduced in a fixed order: deterministic, about 2^-21 relative error per product.
+ * OPS/pairwise_metrics.cpp:30; the matmul nodes under :64,121,203.)  A pre-pass writes C once as
+ * tf32 high/low parts (C x2 reads it K-major, C^T x1 reads the same copy MN-major, no transposed
+ * copy), tcgen05.mma accumulates hi.hi + hi.lo + lo.hi in fp32 in chunks of 64 elements that are
+ * summed in registers, row and column sums are reduced in a fixed order: deterministic, as
+ * accurate as the fp32 FMA chain.
  * engine AUTO picks this for float32 with D >= 64, N1, N2 >= 256 and B*N1*N2*D >= 2^28 when the
  * scratch is large enough, otherwise the call is tpw_lp_backward(p = 2) on the CUDA cores;
  * engine SIMT_FP32 always is; either TCGEN05 value forces the tensor cores (float32 only).
  * scratch: tpw_dot_backward_scratch_bytes(...) bytes (0 = CUDA-core path), 16-byte aligned;
- * about 16 bytes per element of grad.  grad_x1 or grad_x2 may be NULL.
+ * about 8 bytes per element of grad.  grad_x1 or grad_x2 may be NULL.
  */
 TPW_API int64_t tpw_dot_backward_scratch_bytes(int dtype, int mode, int engine, int64_t B, int64_t N1, int64_t N2, int64_t D);
 TPW_API int tpw_dot_backward_ws(int dtype, int mode, int engine, const void *grad, const void *aux,

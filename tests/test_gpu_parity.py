@@ -507,7 +507,7 @@ def test_tensor_core_backward_blocking_and_abi(tensor_engine, monkeypatch):
 
     full1, full2 = grads()
     per_batch = lib.tpw_dot_backward_scratch_bytes(_abi.F32, _abi.LP_BWD_PPMINKOWSKI, _abi.ENGINE_TCGEN05_TF32X3, 1, 600, 520, 64)
-    assert per_batch > 16 * 600 * 520
+    assert per_batch > 8 * 600 * 520   # tf32 high and low copies of the coefficient matrix
     monkeypatch.setenv("TPW_BWD_SCRATCH_GB", str(2.5 * per_batch / 2 ** 30))   # groups of two batches
     b1, b2 = grads()
     assert torch.equal(b1, full1) and torch.equal(b2, full2)

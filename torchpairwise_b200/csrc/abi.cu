@@ -77,9 +77,25 @@ static encode_tiled_fn resolve_encode_tiled() {
     return fn;
 }
 
+static int encode_map_3d(CUtensorMap *map, const void *base, int elem_bytes,
+                         uint64_t dim0, uint64_t dim1, uint64_t dim2,
+                         uint32_t box0, uint32_t box1, bool swizzle128, CUtensorMapSwizzle swizzle);
+
 int make_tensor_map_3d(CUtensorMap *map, const void *base, int elem_bytes,
                        uint64_t dim0, uint64_t dim1, uint64_t dim2,
                        uint32_t box0, uint32_t box1, bool swizzle128) {
+    return encode_map_3d(map, base, elem_bytes, dim0, dim1, dim2, box0, box1, swizzle128,
+                         swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
+int make_tensor_map_3d_atom32(CUtensorMap *map, const void *base, int elem_bytes,
+                              uint64_t dim0, uint64_t dim1, uint64_t dim2, uint32_t box0, uint32_t box1) {
+    return encode_map_3d(map, base, elem_bytes, dim0, dim1, dim2, box0, box1, true, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+}
+
+static int encode_map_3d(CUtensorMap *map, const void *base, int elem_bytes,
+                         uint64_t dim0, uint64_t dim1, uint64_t dim2,
+                         uint32_t box0, uint32_t box1, bool swizzle128, CUtensorMapSwizzle swizzle) {
     encode_tiled_fn encode = resolve_encode_tiled();
     if (!encode) return fail(TPW_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     // The encoder is a driver call and needs a context bound to the calling thread.  A thread that
@@ -111,7 +127,7 @@ int make_tensor_map_3d(CUtensorMap *map, const void *base, int elem_bytes,
     cuuint32_t box[3] = {box0, box1, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = encode(map, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        swizzle,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(TPW_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return TPW_OK;

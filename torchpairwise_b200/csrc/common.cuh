@@ -56,6 +56,10 @@ int sm_count();
 int make_tensor_map_3d(CUtensorMap *map, const void *base, int elem_bytes,
                        uint64_t dim0, uint64_t dim1, uint64_t dim2,
                        uint32_t box0, uint32_t box1, bool swizzle128);
+// Same with CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B: 128-byte rows whose 32-byte groups are permuted by
+// the row index modulo 4, the shared-memory layout tcgen05 expects for MN-major 32-bit operands.
+int make_tensor_map_3d_atom32(CUtensorMap *map, const void *base, int elem_bytes,
+                              uint64_t dim0, uint64_t dim1, uint64_t dim2, uint32_t box0, uint32_t box1);
 
 #ifdef __CUDACC__
 // ---- device-side PTX wrappers -----------------------------------------------------------------

@@ -133,12 +133,26 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
     d |= (uint64_t)2 << 61;
     return d;
 }
+// MN-major 32-bit tile: the only layout tcgen05 takes for it is the 128-byte swizzle with 32-byte
+// atoms (layout type 1): rows of 128 bytes are k, four rows form one 512-byte atom (stride between
+// 4-row groups in bits [32,46)), and the 32-value blocks along M/N follow each other at the leading
+// byte offset in bits [16,30) (here 4096: 32 k-rows of 128 bytes).
+__device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)(4096 >> 4) << 16;
+    d |= (uint64_t)(512 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)1 << 61;
+    return d;
+}
 // Instruction descriptor: D = fp32 (bits [4,6) = 1); A and B formats in bits [7,10) and [10,13):
-// 1 = bf16 under kind::f16, 2 = tf32 under kind::tf32; both K-major (bits 15, 16 = 0);
-// N >> 3 in bits [17,23), M >> 4 in bits [24,29).
-__device__ __forceinline__ uint32_t make_idesc(int M, int N, bool tf32) {
+// 1 = bf16 under kind::f16, 2 = tf32 under kind::tf32; bit 15 / bit 16 = 1 when A / B is MN-major
+// (0: K-major); N >> 3 in bits [17,23), M >> 4 in bits [24,29).
+__device__ __forceinline__ uint32_t make_idesc(int M, int N, bool tf32, bool a_mn = false, bool b_mn = false) {
     const uint32_t fmt = tf32 ? 2u : 1u;
-    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
 // Bounded mbarrier wait that also gives up when another role raised the abort flag.
@@ -169,7 +183,11 @@ __device__ __forceinline__ float dot_epilogue(float dot, float n1, float n2, boo
 // TF32 = false: operands are bf16 high/low parts, 64 per k-step; true: tf32 high/low parts in fp32
 // containers, 32 per k-step.  Either way a k-step is one 128-byte swizzled row per operand row and
 // four MMAs per operand pair, so the pipeline below is the same.
-template <int EPI, bool SELF, bool TF32, bool ROWMIN = false>
+// AMN / BMN (tf32 only): the operand is MN-major, i.e. its global rows run along k and each row holds
+// the tile's M (or N) values contiguously, so a matrix can be contracted over its row index without a
+// transposed copy.  Such a tile is staged as blocks of {32 values, 32 k-rows} (one TMA box each, 4 KB,
+// 128-byte swizzle with 32-byte atoms): block m holds values 32m..32m+31, an MMA consumes 8 k-rows = 1024 bytes.
+template <int EPI, bool SELF, bool TF32, bool ROWMIN = false, bool AMN = false, bool BMN = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_constant__ CUtensorMap map_xl,
                    const __grid_constant__ CUtensorMap map_yh, const __grid_constant__ CUtensorMap map_yl,
@@ -228,19 +246,44 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
                         break;
                     }
                     unsigned char *st = smem + s * STAGE_BYTES;
+                    static_assert(TF32 || !(AMN || BMN), "MN-major staging is laid out for 32-bit operands");
                     mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-                    tma_load_3d(st, &map_xh, &full[s], kb * BKE, (int)(tm * BM), (int)b);
-                    tma_load_3d(st + 2 * A_BYTES, &map_yh, &full[s], kb * BKE, (int)(tn * BN), (int)b);
+                    if constexpr (AMN) {
+#pragma unroll
+                        for (int m = 0; m < BM / 32; ++m)
+                            tma_load_3d(st + m * 4096, &map_xh, &full[s], (int)(tm * BM) + 32 * m, kb * BKE, (int)b);
+                    } else {
+                        tma_load_3d(st, &map_xh, &full[s], kb * BKE, (int)(tm * BM), (int)b);
+                    }
+                    if constexpr (BMN) {
+#pragma unroll
+                        for (int m = 0; m < BN / 32; ++m)
+                            tma_load_3d(st + 2 * A_BYTES + m * 4096, &map_yh, &full[s], (int)(tn * BN) + 32 * m, kb * BKE, (int)b);
+                    } else {
+                        tma_load_3d(st + 2 * A_BYTES, &map_yh, &full[s], kb * BKE, (int)(tn * BN), (int)b);
+                    }
                     mbar_expect_tx(&full_lo[s], A_BYTES + B_BYTES);
-                    tma_load_3d(st + A_BYTES, &map_xl, &full_lo[s], kb * BKE, (int)(tm * BM), (int)b);
-                    tma_load_3d(st + 2 * A_BYTES + B_BYTES, &map_yl, &full_lo[s], kb * BKE, (int)(tn * BN), (int)b);
+                    if constexpr (AMN) {
+#pragma unroll
+                        for (int m = 0; m < BM / 32; ++m)
+                            tma_load_3d(st + A_BYTES + m * 4096, &map_xl, &full_lo[s], (int)(tm * BM) + 32 * m, kb * BKE, (int)b);
+                    } else {
+                        tma_load_3d(st + A_BYTES, &map_xl, &full_lo[s], kb * BKE, (int)(tm * BM), (int)b);
+                    }
+                    if constexpr (BMN) {
+#pragma unroll
+                        for (int m = 0; m < BN / 32; ++m)
+                            tma_load_3d(st + 2 * A_BYTES + B_BYTES + m * 4096, &map_yl, &full_lo[s], (int)(tn * BN) + 32 * m, kb * BKE, (int)b);
+                    } else {
+                        tma_load_3d(st + 2 * A_BYTES + B_BYTES, &map_yl, &full_lo[s], kb * BKE, (int)(tn * BN), (int)b);
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            const uint32_t idesc = make_idesc(BM, BN, TF32);
+            const uint32_t idesc = make_idesc(BM, BN, TF32, AMN, BMN);
             uint32_t it = 0, acount = 0;
             bool ok = true;
             const int kchunk = (P.kchunk > 0 && P.kchunk < nkb) ? P.kchunk : nkb;
@@ -268,12 +311,16 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
                         }
                         tc_fence_after();
                         const uint32_t sb = smem_u32(smem + s * STAGE_BYTES);
-                        const uint64_t dxh = make_smem_desc(sb), dxl = make_smem_desc(sb + A_BYTES);
-                        const uint64_t dyh = make_smem_desc(sb + 2 * A_BYTES), dyl = make_smem_desc(sb + 2 * A_BYTES + B_BYTES);
-                        // one MMA consumes 32 bytes of the swizzled row (16 bf16 or 8 tf32): advance the start address by 2 units
+                        const uint64_t dxh = AMN ? make_smem_desc_mn(sb) : make_smem_desc(sb);
+                        const uint64_t dxl = AMN ? make_smem_desc_mn(sb + A_BYTES) : make_smem_desc(sb + A_BYTES);
+                        const uint64_t dyh = BMN ? make_smem_desc_mn(sb + 2 * A_BYTES) : make_smem_desc(sb + 2 * A_BYTES);
+                        const uint64_t dyl = BMN ? make_smem_desc_mn(sb + 2 * A_BYTES + B_BYTES) : make_smem_desc(sb + 2 * A_BYTES + B_BYTES);
+                        // K-major: one MMA consumes 32 bytes of the swizzled row (16 bf16 or 8 tf32), so the start
+                        // address advances by 2 units of 16 bytes; MN-major: 8 k-rows = 1024 bytes = 64 units
+                        constexpr uint64_t ka = AMN ? 64 : 2, kbn = BMN ? 64 : 2;
 #pragma unroll
                         for (int k = 0; k < kMmasPerStep; ++k)
-                            tc_mma<TF32>(d_tmem, dxh + 2 * k, dyh + 2 * k, idesc, ((kb - kb0) | k) != 0);
+                            tc_mma<TF32>(d_tmem, dxh + ka * k, dyh + kbn * k, idesc, ((kb - kb0) | k) != 0);
                         if (!wait_or_abort(&full_lo[s], (it / kStages) & 1, abort_flag)) {
                             *abort_flag = 1;
                             if (P.status) atomicCAS(P.status, 0, (4 << 16) | 5);
@@ -283,8 +330,8 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
                         tc_fence_after();
 #pragma unroll
                         for (int k = 0; k < kMmasPerStep; ++k) {
-                            tc_mma<TF32>(d_tmem, dxh + 2 * k, dyl + 2 * k, idesc, 1);
-                            tc_mma<TF32>(d_tmem, dxl + 2 * k, dyh + 2 * k, idesc, 1);
+                            tc_mma<TF32>(d_tmem, dxh + ka * k, dyl + kbn * k, idesc, 1);
+                            tc_mma<TF32>(d_tmem, dxl + ka * k, dyh + kbn * k, idesc, 1);
                         }
                         tc_commit(&empty[s]); // the stage may be refilled once these MMAs have read it
                     }
@@ -533,15 +580,13 @@ __device__ __forceinline__ float rn_tf32(float v) {
 
 enum { COEF_ID = 0, COEF_DIV_AUX = 1, COEF_COSINE = 2 };
 constexpr int PT = 64;        // pre-pass tile edge
-constexpr int PT_PITCH = 65;  // shared-memory pitch (floats) of the transposing tile
 
 struct SplitParams {
     const float *a, *aux;       // [B,R,C]
     const float *n1, *n2;       // COEF_COSINE: row norms [B,R], [B,C]
     float *hi, *lo;             // [B,R,Cp]   (STRAIGHT)
-    float *thi, *tlo;           // [B,C,Rp]   (TRANSPOSED)
     float *rowpart, *colpart;   // [B,TC,R], [B,TR,C]   (SUMS)
-    long long R, C, Rp, Cp, TR, TC;
+    long long R, C, Cp, TR, TC;
     int vec_in;                 // C % 4 == 0 and 16-byte aligned inputs
     int epilogue;               // COEF_COSINE: what aux holds (tpw_dot_epilogue)
 };
@@ -576,12 +621,11 @@ __device__ __forceinline__ void coefficient(float a, float aux, float na, float 
     }
 }
 
-// One 64 x 64 tile per CTA of 256 threads: coefficient, tf32 split, straight and transposed copies
-// (row pitches padded to a multiple of 4 and zero filled), per-tile row and column sums.
-template <int MODE, bool STRAIGHT, bool TRANSPOSED, bool SUMS>
+// One 64 x 64 tile per CTA of 256 threads: coefficient, tf32 high/low copies (row pitch padded to a
+// multiple of 4 and zero filled), per-tile row and column sums.
+template <int MODE, bool SUMS>
 __global__ void __launch_bounds__(256)
 split_tile_kernel(const SplitParams P) {
-    __shared__ float tile[TRANSPOSED ? PT * PT_PITCH : 1];
     __shared__ float colacc[SUMS ? 16 * PT : 1];
     const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
     const long long b = blockIdx.z;
@@ -598,8 +642,7 @@ split_tile_kernel(const SplitParams P) {
     float colp[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-        const int lr = ty + 16 * r;
-        const long long row = r0 + lr;
+        const long long row = r0 + ty + 16 * r;
         float v[4] = {0.f, 0.f, 0.f, 0.f}, rs[4] = {0.f, 0.f, 0.f, 0.f};
         if (row < P.R) {
             float av[4] = {0.f, 0.f, 0.f, 0.f}, ov[4] = {0.f, 0.f, 0.f, 0.f};
@@ -628,7 +671,7 @@ split_tile_kernel(const SplitParams P) {
                     colp[e] += cs;
                 }
         }
-        if (STRAIGHT && row < P.R && col < P.Cp) {
+        if (row < P.R && col < P.Cp) {
             float4 h, l;
             h.x = rn_tf32(v[0]); l.x = rn_tf32(v[0] - h.x);
             h.y = rn_tf32(v[1]); l.y = rn_tf32(v[1] - h.y);
@@ -643,40 +686,16 @@ split_tile_kernel(const SplitParams P) {
             for (int off = 1; off < 16; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
             if (tx == 0 && row < P.R) P.rowpart[(b * P.TC + blockIdx.x) * P.R + row] = s;
         }
-        if (TRANSPOSED) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) tile[lr * PT_PITCH + 4 * tx + e] = v[e];
-        }
     }
-    if (SUMS) {
+    if (!SUMS) return;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) colacc[ty * PT + 4 * tx + e] = colp[e];
-    }
-    if (!(TRANSPOSED || SUMS)) return;
+    for (int e = 0; e < 4; ++e) colacc[ty * PT + 4 * tx + e] = colp[e];
     __syncthreads();
-    if (SUMS && tid < PT && c0 + tid < P.C) {
+    if (tid < PT && c0 + tid < P.C) {
         float s = 0.f;
 #pragma unroll
         for (int y = 0; y < 16; ++y) s += colacc[y * PT + tid];
         P.colpart[(b * P.TR + blockIdx.y) * P.C + c0 + tid] = s;
-    }
-    if (!TRANSPOSED) return;
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-        const int lc = ty + 16 * r;                        // tile column = row of the transposed copy
-        const long long tcol = c0 + lc, row = r0 + 4 * tx; // four consecutive source rows
-        if (tcol < P.C && row < P.Rp) {
-            float v[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) v[e] = tile[(4 * tx + e) * PT_PITCH + lc]; // rows past R hold zeros
-            float4 h, l;
-            h.x = rn_tf32(v[0]); l.x = rn_tf32(v[0] - h.x);
-            h.y = rn_tf32(v[1]); l.y = rn_tf32(v[1] - h.y);
-            h.z = rn_tf32(v[2]); l.z = rn_tf32(v[2] - h.z);
-            h.w = rn_tf32(v[3]); l.w = rn_tf32(v[3] - h.w);
-            *reinterpret_cast<float4 *>(P.thi + (b * P.C + tcol) * P.Rp + row) = h;
-            *reinterpret_cast<float4 *>(P.tlo + (b * P.C + tcol) * P.Rp + row) = l;
-        }
     }
 }
 
@@ -701,27 +720,25 @@ __global__ void grad_finish_kernel(float *__restrict__ g, const float *__restric
 }
 
 struct BwdScratch {
-    long long N1p, N2p, TR, TC;
-    long long off_chi, off_clo, off_cthi, off_ctlo, off_x2thi, off_x2tlo, off_x1thi, off_x1tlo;
+    long long N2p, Dp, TR, TC;
+    long long off_chi, off_clo, off_x1hi, off_x1lo, off_x2hi, off_x2lo;
     long long off_rowpart, off_colpart, off_rowsum, off_colsum, total;
 };
 
 inline BwdScratch bwd_scratch_layout(long long B, long long N1, long long N2, long long D) {
     BwdScratch L;
-    L.N1p = align_up(N1, 4);
     L.N2p = align_up(N2, 4);
+    L.Dp = align_up(D, 4);
     L.TR = (N1 + PT - 1) / PT;
     L.TC = (N2 + PT - 1) / PT;
     long long off = 0;
     auto take = [&](long long bytes) { const long long o = off; off += align_up(bytes, 1024); return o; };
     L.off_chi = take(B * N1 * L.N2p * 4);
     L.off_clo = take(B * N1 * L.N2p * 4);
-    L.off_cthi = take(B * N2 * L.N1p * 4);
-    L.off_ctlo = take(B * N2 * L.N1p * 4);
-    L.off_x2thi = take(B * D * L.N2p * 4);
-    L.off_x2tlo = take(B * D * L.N2p * 4);
-    L.off_x1thi = take(B * D * L.N1p * 4);
-    L.off_x1tlo = take(B * D * L.N1p * 4);
+    L.off_x1hi = take(B * N1 * L.Dp * 4);
+    L.off_x1lo = take(B * N1 * L.Dp * 4);
+    L.off_x2hi = take(B * N2 * L.Dp * 4);
+    L.off_x2lo = take(B * N2 * L.Dp * 4);
     L.off_rowpart = take(B * L.TC * N1 * 4);
     L.off_colpart = take(B * L.TR * N2 * 4);
     L.off_rowsum = take(B * N1 * 4);
@@ -735,28 +752,42 @@ inline bool auto_picks_tensor_backward(int dtype, long long B, long long N1, lon
     return dtype == TPW_F32 && D >= 64 && N1 >= 256 && N2 >= 256 && (double)B * N1 * N2 * D >= (double)(1ll << 28);
 }
 
-template <int MODE, bool STRAIGHT, bool TRANSPOSED, bool SUMS>
+template <int MODE, bool SUMS>
 int launch_split(const SplitParams &P, long long B, cudaStream_t s) {
     const long long gx = (P.C + PT - 1) / PT, gy = (P.R + PT - 1) / PT;
     TPW_CHECK_ARG(gy <= 65535 && B <= 65535, "dense backward: more than 65535 row tiles or batches");
-    split_tile_kernel<MODE, STRAIGHT, TRANSPOSED, SUMS><<<dim3((unsigned)gx, (unsigned)gy, (unsigned)B), 256, 0, s>>>(P);
+    split_tile_kernel<MODE, SUMS><<<dim3((unsigned)gx, (unsigned)gy, (unsigned)B), 256, 0, s>>>(P);
     TPW_LAUNCH_OK("split_tile_kernel");
     return TPW_OK;
 }
 
-// out[b,m,n] = sum_k a[b,m,k] * bt[b,n,k] from tf32 high/low parts with row pitch Kp
-int launch_tf32_product(const float *ahi, const float *alo, const float *bhi, const float *blo, float *out,
-                        long long B, long long M, long long N, long long Kp, cudaStream_t s) {
+// One operand of a tf32 product as high/low parts.  K-major (mn = false): rows are the M (or N) index,
+// `pitch` elements per row hold k (zero padded).  MN-major (mn = true): rows are k, `pitch` elements
+// per row hold the M (or N) index.
+struct Tf32Operand {
+    const float *hi, *lo;
+    long long pitch;
+    bool mn;
+};
+
+// out[b,m,n] = sum_k A[b](m,k) * Bm[b](n,k); K = length of the reduction.  A K-major operand holds
+// `pitch` >= K elements per row (zero beyond K), an MN-major operand has exactly K rows per batch.
+int launch_tf32_product(const Tf32Operand &A, const Tf32Operand &Bm, float *out,
+                        long long B, long long M, long long N, long long K, cudaStream_t s) {
     CUtensorMap mah, mal, mbh, mbl;
     int st;
-    if ((st = make_tensor_map_3d(&mah, ahi, 4, Kp, M, B, BK / 2, BM, true)) != TPW_OK) return st;
-    if ((st = make_tensor_map_3d(&mal, alo, 4, Kp, M, B, BK / 2, BM, true)) != TPW_OK) return st;
-    if ((st = make_tensor_map_3d(&mbh, bhi, 4, Kp, N, B, BK / 2, BN, true)) != TPW_OK) return st;
-    if ((st = make_tensor_map_3d(&mbl, blo, 4, Kp, N, B, BK / 2, BN, true)) != TPW_OK) return st;
+    auto encode = [&](CUtensorMap *m, const float *p, const Tf32Operand &o, long long rows, int box_rows) {
+        return o.mn ? make_tensor_map_3d_atom32(m, p, 4, o.pitch, K, B, 32, 32)
+                    : make_tensor_map_3d(m, p, 4, o.pitch, rows, B, BK / 2, box_rows, true);
+    };
+    if ((st = encode(&mah, A.hi, A, M, BM)) != TPW_OK) return st;
+    if ((st = encode(&mal, A.lo, A, M, BM)) != TPW_OK) return st;
+    if ((st = encode(&mbh, Bm.hi, Bm, N, BN)) != TPW_OK) return st;
+    if ((st = encode(&mbl, Bm.lo, Bm, N, BN)) != TPW_OK) return st;
     GemmParams P;
     memset(&P, 0, sizeof(P));
     P.out = out;
-    P.B = B; P.N1 = M; P.N2 = N; P.D = Kp;
+    P.B = B; P.N1 = M; P.N2 = N; P.D = K; // K-major tails beyond K are zero padding or zero fill
     P.tiles_m = (M + BM - 1) / BM;
     P.tiles_n = (N + BN - 1) / BN;
     P.tiles = B * P.tiles_m * P.tiles_n;
@@ -768,9 +799,17 @@ int launch_tf32_product(const float *ahi, const float *alo, const float *bhi, co
     P.status = device_status_ptr();
     const long long nsm = sm_count();
     const unsigned grid = (unsigned)(P.tiles < nsm ? P.tiles : nsm);
-    auto kern = gemm_metric_kernel<TPW_DOT_LINEAR, false, true>;
-    TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
-    kern<<<grid, kThreads, SMEM_ALLOC, s>>>(mah, mal, mbh, mbl, P);
+#define TPW_TF32_LAUNCH(AMN, BMN)                                                                                         \
+    do {                                                                                                                  \
+        auto kern = gemm_metric_kernel<TPW_DOT_LINEAR, false, true, false, AMN, BMN>;                                     \
+        TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));                 \
+        kern<<<grid, kThreads, SMEM_ALLOC, s>>>(mah, mal, mbh, mbl, P);                                                   \
+    } while (0)
+    if (!A.mn && !Bm.mn) TPW_TF32_LAUNCH(false, false);
+    else if (!A.mn && Bm.mn) TPW_TF32_LAUNCH(false, true);
+    else if (A.mn && Bm.mn) TPW_TF32_LAUNCH(true, true);
+    else return fail(TPW_ERR_UNSUPPORTED, "tf32 product: MN-major A with K-major B is not instantiated");
+#undef TPW_TF32_LAUNCH
     TPW_LAUNCH_OK("gemm_metric_kernel (tf32)");
     return TPW_OK;
 }
@@ -903,11 +942,11 @@ extern "C" int tpw_dot_metric_forward_ws(int dtype, int epilogue, int engine,
             X.a = static_cast<const float *>(side == 0 ? x1 : x2);
             X.hi = side == 0 ? xhi : yhi;
             X.lo = side == 0 ? xlo : ylo;
-            X.R = side == 0 ? N1 : N2; X.C = D; X.Cp = Dp; X.Rp = align_up(X.R, 4);
+            X.R = side == 0 ? N1 : N2; X.C = D; X.Cp = Dp;
             X.vec_in = (D % 4 == 0 && aligned16(X.a)) ? 1 : 0;
-            if ((st = launch_split<COEF_ID, true, false, false>(X, B, s)) != TPW_OK) return st;
+            if ((st = launch_split<COEF_ID, false>(X, B, s)) != TPW_OK) return st;
         }
-        return launch_tf32_product(xhi, xlo, yhi, ylo, static_cast<float *>(out), B, N1, N2, Dp, s);
+        return launch_tf32_product(Tf32Operand{xhi, xlo, Dp, false}, Tf32Operand{yhi, ylo, Dp, false}, static_cast<float *>(out), B, N1, N2, Dp, s);
     }
     if (engine == TPW_ENGINE_AUTO && auto_picks_tensor_cores(dtype, B, N1, N2, D) && scratch != nullptr &&
         scratch_bytes >= scratch_layout(B, N1, N2, D, false).total)
@@ -1014,7 +1053,8 @@ static int dense_backward_tensor(int coef, int epilogue, bool sums, float s_mm, 
     auto F = [&](long long off) { return reinterpret_cast<float *>(base + off); };
     int st;
 
-    // coefficient matrix: straight copy for grad_x1 (K = N2), transposed copy for grad_x2 (K = N1)
+    // coefficient matrix C [N1,N2] as tf32 high/low parts, written once: grad_x1 = C . X2 reads it K-major
+    // (reduction along its rows), grad_x2 = C^T . X1 reads the same copy MN-major (reduction over its row index)
     SplitParams C;
     memset(&C, 0, sizeof(C));
     C.a = static_cast<const float *>(grad);
@@ -1022,14 +1062,14 @@ static int dense_backward_tensor(int coef, int epilogue, bool sums, float s_mm, 
     C.n1 = static_cast<const float *>(norm1);
     C.n2 = static_cast<const float *>(norm2);
     C.epilogue = epilogue;
-    C.hi = F(L.off_chi); C.lo = F(L.off_clo); C.thi = F(L.off_cthi); C.tlo = F(L.off_ctlo);
+    C.hi = F(L.off_chi); C.lo = F(L.off_clo);
     C.rowpart = F(L.off_rowpart); C.colpart = F(L.off_colpart);
-    C.R = N1; C.C = N2; C.Rp = L.N1p; C.Cp = L.N2p; C.TR = L.TR; C.TC = L.TC;
+    C.R = N1; C.C = N2; C.Cp = L.N2p; C.TR = L.TR; C.TC = L.TC;
     C.vec_in = (N2 % 4 == 0 && aligned16(grad) && (coef == COEF_ID || aligned16(aux))) ? 1 : 0;
-    if (coef == COEF_COSINE) st = launch_split<COEF_COSINE, true, true, true>(C, B, s);
-    else if (coef == COEF_DIV_AUX) st = launch_split<COEF_DIV_AUX, true, true, true>(C, B, s);
-    else if (sums) st = launch_split<COEF_ID, true, true, true>(C, B, s);
-    else st = launch_split<COEF_ID, true, true, false>(C, B, s);
+    if (coef == COEF_COSINE) st = launch_split<COEF_COSINE, true>(C, B, s);
+    else if (coef == COEF_DIV_AUX) st = launch_split<COEF_DIV_AUX, true>(C, B, s);
+    else if (sums) st = launch_split<COEF_ID, true>(C, B, s);
+    else st = launch_split<COEF_ID, false>(C, B, s);
     if (st != TPW_OK) return st;
     if (sums) {
         reduce_partials_kernel<<<(unsigned)((B * N1 + 255) / 256), 256, 0, s>>>(F(L.off_rowpart), F(L.off_rowsum), B, L.TC, N1);
@@ -1037,23 +1077,26 @@ static int dense_backward_tensor(int coef, int epilogue, bool sums, float s_mm, 
         TPW_LAUNCH_OK("reduce_partials_kernel");
     }
     const long long cap = (long long)sm_count() * 8;
+    const Tf32Operand Ck{F(L.off_chi), F(L.off_clo), L.N2p, false}, Cmn{F(L.off_chi), F(L.off_clo), L.N2p, true};
     for (int side = 0; side < 2; ++side) {
         void *gout = side == 0 ? grad_x1 : grad_x2;
         if (!gout) continue;
-        // side 0: grad_x1 = C . X2 needs X2^T [B,D,N2p]; side 1: grad_x2 = C^T . X1 needs X1^T [B,D,N1p]
-        const void *xk = side == 0 ? x2 : x1;   // operand contracted against
+        // side 0: grad_x1[N1,D] = C . X2, X2 [N2,D] contracted over its rows; side 1: grad_x2[N2,D] = C^T . X1
+        const void *xk = side == 0 ? x2 : x1;   // operand contracted against (MN-major: its rows are k)
         const void *xo = side == 0 ? x1 : x2;   // rows that receive the gradient
-        const long long Nk = side == 0 ? N2 : N1, Nkp = side == 0 ? L.N2p : L.N1p, No = side == 0 ? N1 : N2;
-        float *xthi = F(side == 0 ? L.off_x2thi : L.off_x1thi), *xtlo = F(side == 0 ? L.off_x2tlo : L.off_x1tlo);
+        const long long Nk = side == 0 ? N2 : N1, No = side == 0 ? N1 : N2;
+        float *xhi = F(side == 0 ? L.off_x2hi : L.off_x1hi), *xlo = F(side == 0 ? L.off_x2lo : L.off_x1lo);
         SplitParams X;
         memset(&X, 0, sizeof(X));
         X.a = static_cast<const float *>(xk);
-        X.thi = xthi; X.tlo = xtlo;
-        X.R = Nk; X.C = D; X.Rp = Nkp; X.Cp = align_up(D, 4);
+        X.hi = xhi; X.lo = xlo;
+        X.R = Nk; X.C = D; X.Cp = L.Dp;
         X.vec_in = (D % 4 == 0 && aligned16(xk)) ? 1 : 0;
-        if ((st = launch_split<COEF_ID, false, true, false>(X, B, s)) != TPW_OK) return st;
-        if ((st = launch_tf32_product(F(side == 0 ? L.off_chi : L.off_cthi), F(side == 0 ? L.off_clo : L.off_ctlo), xthi, xtlo,
-                                      static_cast<float *>(gout), B, No, D, Nkp, s)) != TPW_OK) return st;
+        if ((st = launch_split<COEF_ID, false>(X, B, s)) != TPW_OK) return st;
+        const Tf32Operand Xmn{xhi, xlo, L.Dp, true};
+        if (side == 0) st = launch_tf32_product(Ck, Xmn, static_cast<float *>(gout), B, N1, D, N2, s);
+        else st = launch_tf32_product(Cmn, Xmn, static_cast<float *>(gout), B, N2, D, N1, s);
+        if (st != TPW_OK) return st;
         const float *sumv = F(side == 0 ? L.off_rowsum : L.off_colsum);
         if (coef == COEF_COSINE) {
             // the norm part of the chain: g[r,:] += term[r] * x[r,:] / norm[r]

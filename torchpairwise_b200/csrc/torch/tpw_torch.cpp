@@ -134,7 +134,7 @@ bool tensor_engine_selected(const Prepared &p) {
 
 // Backward of the p = 2 metrics and the plain gradient products: tensor-core contractions when the
 // engine rule of tpw_dot_backward_ws picks them (large float32 problems), the CUDA-core kernel
-// otherwise.  The split copies take about 16 bytes per element of grad; above TPW_BWD_SCRATCH_GB
+// otherwise.  The split copies take about 8 bytes per element of grad; above TPW_BWD_SCRATCH_GB
 // (default 8) the work is cut into groups of batches, or row blocks of one batch whose grad_x2
 // contributions are added in block order.
 // With `cosine` set (epilogue >= 0, the two norm vectors) the call is the whole cosine-family backward,

@@ -171,7 +171,7 @@ def _dense_backward_tensor(mode: int, grad: Tensor, aux: Optional[Tensor], x1c: 
     """Backward of the p = 2 metrics / the plain gradient products as tensor-core contractions
     (``tpw_dot_backward_ws``), or None when the engine rule keeps the problem on the CUDA cores.
 
-    The split copies of the coefficient matrix take about 16 bytes per element of ``grad``; above
+    The split copies of the coefficient matrix take about 8 bytes per element of ``grad``; above
     ``TPW_BWD_SCRATCH_GB`` (default 8) the work is cut into groups of batches, or row blocks of a
     single batch whose grad_x2 contributions are summed in block order (deterministic).
 

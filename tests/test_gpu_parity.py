@@ -556,6 +556,28 @@ def test_full_size_dense_backward(tpw):
     _sum_close(Y.grad[cols], 2 * (Yd[cols] * uc.sum(0).unsqueeze(1) - uc.t() @ Xd), "C4 quarter grad_x2 rows")
 
 
+def test_full_size_neighbour_reductions(tpw):
+    """C4-sized nearest-row query (engine rule: tcgen05 row-minimum epilogue, nothing but keys written)
+    checked on sampled rows against float64, and a C2-sized fused radius mask against the matrix path."""
+    g = torch.Generator().manual_seed(9)
+    X = torch.randn(131072, 512, generator=g).cuda()
+    Y = torch.randn(16384, 512, generator=g).cuda()
+    arg, mn = tpw.pairwise_argmin_min(X, Y, "euclidean")
+    rows = torch.arange(0, 131072, 2048, device="cuda")
+    ref = torch.cdist(X[rows].double(), Y.double())
+    tol = TOL[torch.float32]
+    torch.testing.assert_close(mn[rows].double(), ref.min(1).values, rtol=tol["rtol"], atol=tol["atol"])
+    picked = ref.gather(1, arg[rows].unsqueeze(1))[:, 0]
+    torch.testing.assert_close(picked, ref.min(1).values, rtol=tol["rtol"], atol=tol["atol"])
+    assert int(arg.min()) >= 0 and int(arg.max()) < 16384
+    del X, Y, ref
+    A = torch.randn(4, 4096, 256, generator=g).cuda()
+    Bm = torch.randn(4, 4096, 256, generator=g).cuda()
+    dist = tpw.chebyshev_distances(A, Bm)
+    eps = float(dist[0, :64].median())
+    assert torch.equal(tpw.radius_neighbors_mask(A, Bm, eps, "chebyshev"), dist <= eps)
+
+
 def test_engine_auto_selection(tpw):
     from torchpairwise_b200 import _abi
     lib = _abi.lib

@@ -209,7 +209,8 @@ TPW_API int tpw_dot_metric_forward_ws(int dtype, int epilogue, int engine,
                               int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream);
 
 /*
- * Streaming row minimum of the squared Euclidean / Euclidean distance on the tensor cores (float32):
+ * Streaming row minimum of the squared Euclidean / Euclidean / cosine distance (TPW_DOT_SQEUCLIDEAN,
+ * TPW_DOT_EUCLIDEAN, TPW_DOT_COSINE_DIST: clip(1 - S, 0, 2), non-negative) on the tensor cores (float32):
  * min_out[b,i] = min_j d(x1[b,i], x2[b,j]), arg_out[b,i] = the smallest j that attains it.  The bf16 x 3
  * pipeline of tpw_dot_metric_forward_ws with an epilogue in which every thread folds the columns
  * of its row into one 64-bit key; no [B,N1,N2] matrix is written, so the kernel stays bound by the

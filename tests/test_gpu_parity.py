@@ -687,6 +687,11 @@ def test_pairwise_argmin_min_tensor_cores(tensor_engine, shape):
         # the matrix the same engine writes has the same row minimum
         full = tpw.euclidean_distances(x1.cuda(), x2.cuda()) if metric == "euclidean" else tpw.sqeuclidean_distances(x1.cuda(), x2.cuda())
         assert torch.equal(full.min(-1).values, mn)
+    argc, mnc = tpw.pairwise_argmin_min(x1.cuda(), x2.cuda(), "cosine")
+    cd = tpw.cosine_distances(x1.cuda(), x2.cuda())
+    assert torch.equal(mnc, cd.min(-1).values)
+    assert torch.equal(cd.gather(-1, argc.unsqueeze(-1))[..., 0], mnc)
+    close(mnc.double(), O.cosine_distances(x1.double().numpy(), x2.double().numpy()).min(-1), tol, msg="cosine row minimum")
 
 
 def test_pairwise_argmin_min_ties_and_edges(tpw):
@@ -723,7 +728,10 @@ def test_pairwise_argmin_min_ties_and_edges(tpw):
     assert torch.equal(mask.float().argmax(1), arg32)
     assert torch.equal(mask, tpw.k_neighbors_mask(x.double(), y.double(), 0))
     with pytest.raises(ValueError, match="supports"):
-        tpw.pairwise_argmin_min(x, y, "cosine")
+        tpw.pairwise_argmin_min(x, y, "jaccard")
+    argc, mnc = tpw.pairwise_argmin_min(x, y, "cosine")     # small problem: matrix kernel + min
+    cd = tpw.cosine_distances(x, y)
+    assert torch.equal(mnc, cd.min(1).values) and torch.equal(cd.gather(1, argc[:, None])[:, 0], mnc)
     with pytest.raises(RuntimeError, match="no rows"):
         tpw.pairwise_argmin_min(x, y[:0])
     with pytest.raises(RuntimeError, match="positive"):

@@ -854,8 +854,9 @@ extern "C" int tpw_dot_rowmin_forward_ws(int epilogue, const void *x1, const voi
                                          void *scratch, int64_t scratch_bytes,
                                          int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream) {
     clear_error();
-    TPW_CHECK_ARG(epilogue == TPW_DOT_SQEUCLIDEAN || epilogue == TPW_DOT_EUCLIDEAN,
-                  "tpw_dot_rowmin_forward_ws: epilogue must be TPW_DOT_SQEUCLIDEAN or TPW_DOT_EUCLIDEAN");
+    TPW_CHECK_ARG(epilogue == TPW_DOT_SQEUCLIDEAN || epilogue == TPW_DOT_EUCLIDEAN || epilogue == TPW_DOT_COSINE_DIST,
+                  "tpw_dot_rowmin_forward_ws: epilogue must be TPW_DOT_SQEUCLIDEAN, TPW_DOT_EUCLIDEAN or TPW_DOT_COSINE_DIST");
+    const bool cosine = epilogue == TPW_DOT_COSINE_DIST;
     TPW_CHECK_ARG(B > 0 && N1 > 0 && N2 > 0 && D > 0, "tpw_dot_rowmin_forward_ws: sizes must be positive");
     TPW_CHECK_ARG(x1 && x2 && (min_out || arg_out), "tpw_dot_rowmin_forward_ws: NULL pointer");
     TPW_CHECK_ARG(N1 < (1ll << 31) && N2 < (1ll << 31) && B < (1ll << 31) && D < (1ll << 31),
@@ -874,9 +875,9 @@ extern "C" int tpw_dot_rowmin_forward_ws(int epilogue, const void *x1, const voi
     const int threads = 256;
     const long long cap = (long long)sm_count() * 16;
     long long blocks = (B * N1 * 32 + threads - 1) / threads;
-    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x1, xh, xl, n1, B * N1, D, L.Dp, 0);
+    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x1, xh, xl, n1, B * N1, D, L.Dp, cosine ? 1 : 0);
     blocks = (B * N2 * 32 + threads - 1) / threads;
-    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x2, yh, yl, n2, B * N2, D, L.Dp, 0);
+    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x2, yh, yl, n2, B * N2, D, L.Dp, cosine ? 1 : 0);
     TPW_LAUNCH_OK("split_rows_kernel");
     CUtensorMap mxh, mxl, myh, myl;
     int st;
@@ -891,14 +892,20 @@ extern "C" int tpw_dot_rowmin_forward_ws(int epilogue, const void *x1, const voi
     P.tiles_m = (N1 + BM - 1) / BM;
     P.tiles_n = (N2 + BN - 1) / BN;
     P.tiles = B * P.tiles_m * P.tiles_n;
-    P.epilogue = TPW_DOT_SQEUCLIDEAN;
+    P.epilogue = cosine ? TPW_DOT_COSINE_DIST : TPW_DOT_SQEUCLIDEAN;
     P.rowmin_keys = keys;
     P.status = device_status_ptr();
     const long long nsm = sm_count();
     const unsigned grid = (unsigned)(P.tiles < nsm ? P.tiles : nsm);
-    auto kern = gemm_metric_kernel<TPW_DOT_SQEUCLIDEAN, false, false, true>;
-    TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
-    kern<<<grid, kThreads, SMEM_ALLOC, s>>>(mxh, mxl, myh, myl, P);
+    if (cosine) {
+        auto kern = gemm_metric_kernel<TPW_DOT_COSINE_DIST, false, false, true>;
+        TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
+        kern<<<grid, kThreads, SMEM_ALLOC, s>>>(mxh, mxl, myh, myl, P);
+    } else {
+        auto kern = gemm_metric_kernel<TPW_DOT_SQEUCLIDEAN, false, false, true>;
+        TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
+        kern<<<grid, kThreads, SMEM_ALLOC, s>>>(mxh, mxl, myh, myl, P);
+    }
     TPW_LAUNCH_OK("gemm_metric_kernel (row minimum)");
     dot_rowmin_finish_kernel<<<(unsigned)((B * N1 + 255) / 256), 256, 0, s>>>(keys, min_out, reinterpret_cast<long long *>(arg_out), B * N1,
                                                                              epilogue == TPW_DOT_EUCLIDEAN ? 1 : 0);

@@ -1020,6 +1020,8 @@ _ROWMIN_METRICS = {
     "chebyshev": (math.inf, 1.0), "linf": (math.inf, 1.0),
     "minkowski": (None, None), "lp": (None, None),
 }
+# served by the matrix kernel + Tensor.min, or by the tensor-core row-minimum epilogue on large problems
+_ROWMIN_DOT_METRICS = {"cosine": _abi.DOT_COSINE_DIST}
 
 
 def pairwise_argmin_min(x1: Tensor, x2: Optional[Tensor] = None, metric: str = "euclidean",
@@ -1033,8 +1035,29 @@ def pairwise_argmin_min(x1: Tensor, x2: Optional[Tensor] = None, metric: str = "
     sorts whole rows of the materialised matrix (k_neighbors_mask, OPS/neighbors.cpp:10-35).
     Other floating dtypes take this package's distance kernel followed by ``Tensor.min``.
     """
+    if metric in _ROWMIN_DOT_METRICS:
+        x1_, x2_ = check_pairwise_inputs("pairwise_argmin_min", x1, x2)
+        _require_cuda(x1_, x2_)
+        with torch.no_grad():
+            x1c, x2c, unbatched = _batched(x1_, x2_, "pairwise_argmin_min")
+            B, N1, N2, D = _sizes(x1c, x2c)
+            if N2 == 0:
+                raise RuntimeError("pairwise_argmin_min: x2 has no rows")
+            if x1c.dtype == torch.float32 and D > 0 and _tensor_engine_selected(x1c, x2c):
+                mins = torch.empty((B, N1), dtype=torch.float32, device=x1c.device)
+                args = torch.empty((B, N1), dtype=torch.int64, device=x1c.device)
+                nbytes = lib.tpw_dot_rowmin_scratch_bytes(B, N1, N2, D)
+                scratch = torch.empty((nbytes,), dtype=torch.uint8, device=x1c.device)
+                with torch.cuda.device(x1c.device):
+                    check(lib.tpw_dot_rowmin_forward_ws(_ROWMIN_DOT_METRICS[metric], _ptr(x1c), _ptr(x2c), _ptr(mins), _ptr(args),
+                                                        _ptr(scratch), nbytes, B, N1, N2, D, _stream(x1c)), "tpw_dot_rowmin_forward_ws")
+            else:
+                mins, args = cosine_distances(x1c, x2c).min(dim=-1)
+            if unbatched:
+                mins, args = mins.squeeze(0), args.squeeze(0)
+            return args, mins
     if metric not in _ROWMIN_METRICS:
-        raise ValueError(f"pairwise_argmin_min supports {sorted(_ROWMIN_METRICS)}; got {metric!r}")
+        raise ValueError(f"pairwise_argmin_min supports {sorted(set(_ROWMIN_METRICS) | set(_ROWMIN_DOT_METRICS))}; got {metric!r}")
     pp, ex = _ROWMIN_METRICS[metric]
     if pp is None:
         pp = 2.0 if p is None else float(p)

@@ -483,6 +483,10 @@ def run_suite(args):
     if want("C4_sqeuclidean_rowmin"):
         entry("C4_sqeuclidean_rowmin", n, timeit(lambda: tpw.pairwise_argmin_min(X, Y, "sqeuclidean")),
               "bf16 tensor (executed flops = 3 x algorithmic; matrix never written)", 3 * 2 * n * 512, bf16_peak, 0)
+    for kk in (8, 16):
+        if want(f"C4_sqeuclidean_top{kk}"):
+            entry(f"C4_sqeuclidean_top{kk}", n, timeit(lambda: tpw.pairwise_argkmin(X, Y, kk, "sqeuclidean")),
+                  "bf16 tensor (executed flops = 3 x algorithmic; matrix never written)", 3 * 2 * n * 512, bf16_peak, 0)
     if want("C4_sqeuclidean_bwd"):
         Xg, Yg = X.clone().requires_grad_(True), Y.clone().requires_grad_(True)
         out = tpw.sqeuclidean_distances(Xg, Yg)

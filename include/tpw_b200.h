@@ -225,6 +225,21 @@ TPW_API int tpw_dot_rowmin_forward_ws(int epilogue, const void *x1, const void *
                               int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream);
 
 /*
+ * The k nearest x2 rows of every x1 row (k <= tpw_dot_topk_max_k()), same distances and pipeline as
+ * tpw_dot_rowmin_forward_ws: val_out [B,N1,k] ascending, idx_out [B,N1,k] (ties towards the smaller
+ * row; -1 / +inf when N2 < k).  Each epilogue thread keeps a sorted register list of the k smallest
+ * keys of its accumulator row, candidates at or above an already published bound of the row's k-th
+ * smallest are dropped first, the per-tile lists are merged by one warp per row.  Deterministic.
+ * No [B,N1,N2] matrix is written (the reference sorts every row of it: OPS/neighbors.cpp:10-35;
+ * its README lists argkmin as future work).
+ */
+TPW_API int tpw_dot_topk_max_k(void);
+TPW_API int64_t tpw_dot_topk_scratch_bytes(int64_t k, int64_t B, int64_t N1, int64_t N2, int64_t D);
+TPW_API int tpw_dot_topk_forward_ws(int epilogue, int k, const void *x1, const void *x2, float *val_out, int64_t *idx_out,
+                            void *scratch, int64_t scratch_bytes,
+                            int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream);
+
+/*
  * Backward of the p = 2 metrics and the plain gradient products as two tensor-core contractions:
  *   TPW_LP_BWD_PPMINKOWSKI (sqeuclidean): C = g,      grad_x1 = 2 (x1 * rowsum(C) - C x2),  grad_x2 = 2 (x2 * colsum(C) - C^T x1)
  *   TPW_LP_BWD_CDIST       (euclidean):   C = g / o (0 where o == 0), same without the factor 2; aux = o

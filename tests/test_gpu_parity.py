@@ -694,6 +694,59 @@ def test_pairwise_argmin_min_tensor_cores(tensor_engine, shape):
     close(mnc.double(), O.cosine_distances(x1.double().numpy(), x2.double().numpy()).min(-1), tol, msg="cosine row minimum")
 
 
+@pytest.mark.parametrize("shape,k", [((1, 300, 520, 96), 1), ((1, 300, 520, 96), 3), ((1, 300, 520, 96), 8), ((1, 300, 520, 96), 16),
+                                     ((2, 257, 1030, 130), 5), ((1, 128, 256, 64), 8), ((1, 40, 9, 16), 9), ((1, 700, 2100, 64), 12)],
+                         ids=lambda v: "x".join(map(str, v)) if isinstance(v, tuple) else str(v))
+def test_pairwise_argkmin_tensor_cores(tensor_engine, shape, k):
+    """The k nearest rows from the tcgen05 top-k epilogue (forced) against the float64 matrix: ascending
+    values within the float32 contract, distinct valid columns whose true distances are the k smallest
+    within the same bound, and agreement with a partial selection on the matrix the same engine writes."""
+    tpw = tensor_engine
+    B, n1, n2, d = shape
+    g = torch.Generator().manual_seed(sum(shape) + k)
+    x1, x2 = torch.randn(B, n1, d, generator=g), torch.randn(B, n2, d, generator=g)
+    a, b = x1.cuda(), x2.cuda()
+    ref = O.cdist(x1.double().numpy(), x2.double().numpy(), 2.0)
+    tol = TOL[torch.float32]
+    for metric, r, fn in (("euclidean", ref, tpw.euclidean_distances), ("sqeuclidean", ref * ref, tpw.sqeuclidean_distances),
+                          ("cosine", O.cosine_distances(x1.double().numpy(), x2.double().numpy()), tpw.cosine_distances)):
+        inds, vals = tpw.pairwise_argkmin(a, b, k, metric)
+        assert inds.shape == (B, n1, k) and inds.dtype == torch.int64 and vals.dtype == torch.float32
+        iv = inds.cpu().numpy()
+        assert iv.min() >= 0 and iv.max() < n2
+        assert all(len(set(row)) == k for row in iv.reshape(-1, k)), "columns of a row must be distinct"
+        assert bool((vals[..., 1:] >= vals[..., :-1]).all())
+        want = np.sort(r, axis=-1)[..., :k]
+        close(vals.double(), want, tol, msg=f"{metric} k smallest values")
+        np.testing.assert_allclose(np.sort(np.take_along_axis(r, iv, -1), -1), want, rtol=tol["rtol"], atol=tol["atol"])
+        full = fn(a, b)
+        fv = full.topk(k, dim=-1, largest=False, sorted=True).values
+        assert torch.equal(fv, vals), metric
+        assert torch.equal(full.gather(-1, inds), vals), metric
+
+
+def test_pairwise_argkmin_other_paths(tpw):
+    """Small problems and other metrics take the matrix kernel plus a partial selection; k_neighbors_mask
+    on a large problem takes the tensor-core top-k and marks exactly k + 1 columns per row."""
+    g = torch.Generator().manual_seed(4)
+    x, y = torch.randn(70, 9, generator=g).cuda(), torch.randn(90, 9, generator=g).cuda()
+    inds, vals = tpw.pairwise_argkmin(x, y, 4, "manhattan")
+    dist = tpw.manhattan_distances(x, y)
+    assert torch.equal(vals, dist.topk(4, largest=False).values) and torch.equal(dist.gather(1, inds), vals)
+    i64, v64 = tpw.pairwise_argkmin(x.double(), y.double(), 2, "euclidean")
+    assert v64.dtype == torch.float64 and i64.shape == (70, 2)
+    with pytest.raises(RuntimeError, match="exceeds"):
+        tpw.pairwise_argkmin(x, y, 91)
+    with pytest.raises(RuntimeError, match="positive"):
+        tpw.pairwise_argkmin(x, y, 0)
+    X, Y = torch.randn(2048, 128, generator=g).cuda(), torch.randn(3000, 128, generator=g).cuda()   # engine rule: tensor cores
+    mask = tpw.k_neighbors_mask(X, Y, 4)
+    assert mask.dtype == torch.bool and torch.equal(mask.sum(1), torch.full((2048,), 5, device="cuda"))
+    d = tpw.euclidean_distances(X, Y)
+    kth = d.topk(5, dim=1, largest=False).values[:, -1:]
+    assert bool((d[mask].view(2048, 5) <= kth * (1 + 1e-4) + 1e-5).all())
+
+
 def test_pairwise_argmin_min_ties_and_edges(tpw):
     """Exact ties go to the smaller x2 row (integer-valued inputs make the distances exact), in a
     tile interior, across the 128-column tile boundary and across batches; other dtypes and the

@@ -32,6 +32,7 @@ from .ops import (
     lp_distances,
     manhattan_distances,
     minkowski_distances,
+    pairwise_argkmin,
     pairwise_argmin_min,
     polynomial_kernel,
     prf_div,

@@ -49,6 +49,9 @@ SIGNATURES = {
     "tpw_dot_metric_scratch_bytes": (_L, [_I, _I, _L, _L, _L, _L]),
     "tpw_dot_rowmin_scratch_bytes": (_L, [_L, _L, _L, _L]),
     "tpw_dot_rowmin_forward_ws": (_I, [_I, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P]),
+    "tpw_dot_topk_max_k": (_I, []),
+    "tpw_dot_topk_scratch_bytes": (_L, [_L, _L, _L, _L, _L]),
+    "tpw_dot_topk_forward_ws": (_I, [_I, _I, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P]),
     "tpw_dot_backward_scratch_bytes": (_L, [_I, _I, _I, _L, _L, _L, _L]),
     "tpw_dot_backward_ws": (_I, [_I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P]),
     "tpw_cosine_backward_ws": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P]),

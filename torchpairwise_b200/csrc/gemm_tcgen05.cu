@@ -66,6 +66,10 @@ struct GemmParams {
     int vec_store;            // N2 % 4 == 0 and out 16-byte aligned
     int kchunk;               // k-steps accumulated in tensor memory before the sum moves to registers (0: all)
     unsigned long long *rowmin_keys; // ROWMIN instantiation: [B*N1] keys (float bits << 32 | x2 row), nothing is stored to out
+    // TOPK instantiations: per row and per (column tile, half) a sorted list of the k smallest keys,
+    // [B*N1][topk_L][topk_k], and [B*N1] published upper bounds of the row's k-th smallest key
+    unsigned long long *topk_lists, *topk_thr;
+    int topk_k, topk_L;
     int *status;
 };
 
@@ -183,11 +187,23 @@ __device__ __forceinline__ float dot_epilogue(float dot, float n1, float n2, boo
 // TF32 = false: operands are bf16 high/low parts, 64 per k-step; true: tf32 high/low parts in fp32
 // containers, 32 per k-step.  Either way a k-step is one 128-byte swizzled row per operand row and
 // four MMAs per operand pair, so the pipeline below is the same.
+// Sorted insertion into an ascending register-resident list (branch-free: slot t becomes
+// min(max(previous slot, key), slot t)); the largest entry falls off the end.
+template <int N>
+__device__ __forceinline__ void sorted_insert(unsigned long long (&lst)[N], unsigned long long key) {
+#pragma unroll
+    for (int t = N - 1; t > 0; --t) {
+        const unsigned long long hi = lst[t - 1] > key ? lst[t - 1] : key;
+        lst[t] = hi < lst[t] ? hi : lst[t];
+    }
+    lst[0] = key < lst[0] ? key : lst[0];
+}
+
 // AMN / BMN (tf32 only): the operand is MN-major, i.e. its global rows run along k and each row holds
 // the tile's M (or N) values contiguously, so a matrix can be contracted over its row index without a
 // transposed copy.  Such a tile is staged as blocks of {32 values, 32 k-rows} (one TMA box each, 4 KB,
 // 128-byte swizzle with 32-byte atoms): block m holds values 32m..32m+31, an MMA consumes 8 k-rows = 1024 bytes.
-template <int EPI, bool SELF, bool TF32, bool ROWMIN = false, bool AMN = false, bool BMN = false>
+template <int EPI, bool SELF, bool TF32, bool ROWMIN = false, bool AMN = false, bool BMN = false, int TOPK = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_constant__ CUtensorMap map_xl,
                    const __grid_constant__ CUtensorMap map_yh, const __grid_constant__ CUtensorMap map_yl,
@@ -432,6 +448,15 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
             float *orow = P.out + (b * P.N1 + (row_ok ? i : 0)) * P.N2;
             const float *n2p = P.n2sq + b * P.N2;
             unsigned long long best = ~0ull;
+            // TOPK: a fresh list per tile half; candidates at or above an already published bound of the
+            // row's k-th smallest key cannot be among its k smallest and are dropped before the insertion
+            unsigned long long lst[TOPK > 0 ? TOPK : 1];
+            unsigned long long bound = 0;
+            if constexpr (TOPK > 0) {
+#pragma unroll
+                for (int t = 0; t < TOPK; ++t) lst[t] = ~0ull;
+                if (row_ok) bound = *reinterpret_cast<volatile unsigned long long *>(P.topk_thr + b * P.N1 + i);
+            }
 #pragma unroll 1
             for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
                 uint32_t r[32];
@@ -440,6 +465,17 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
                 tmem_ld_wait();
                 const long long j0 = tn * BN + c * 32;
                 if (j0 >= P.N2) continue;
+                if constexpr (TOPK > 0) {
+#pragma unroll
+                    for (int v = 0; v < 32; ++v) { // fully unrolled: r[] must stay in registers
+                        const long long j = j0 + v;
+                        const float nn = j < P.N2 ? __ldg(n2p + j) : 0.f;
+                        const float o = dot_epilogue<EPI>(__uint_as_float(r[v]), n1, nn, false);
+                        const unsigned long long key = ((unsigned long long)__float_as_uint(o) << 32) | (unsigned long long)(uint32_t)j;
+                        if (j < P.N2 && key < bound && key < lst[TOPK - 1]) sorted_insert<TOPK>(lst, key);
+                    }
+                    continue;
+                }
                 if constexpr (ROWMIN) {
                     // streaming row minimum: this thread owns row i and folds its 32 columns into one key
                     // (the epilogue value is non-negative, so its bit pattern orders like an unsigned integer)
@@ -490,6 +526,18 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
             }
             if constexpr (ROWMIN) {
                 if (row_ok && best != ~0ull) atomicMin(P.rowmin_keys + b * P.N1 + i, best);
+            }
+            if constexpr (TOPK > 0) {
+                if (row_ok) {
+                    unsigned long long *dst = P.topk_lists + ((b * P.N1 + i) * P.topk_L + tn * 2 + chalf) * P.topk_k;
+                    unsigned long long kth = ~0ull;
+#pragma unroll
+                    for (int t = 0; t < TOPK; ++t) {
+                        if (t < P.topk_k && lst[t] != ~0ull) dst[t] = lst[t];
+                        if (t == P.topk_k - 1) kth = lst[t];
+                    }
+                    if (kth != ~0ull) atomicMin(P.topk_thr + b * P.N1 + i, kth); // k entries in this list: a valid bound
+                }
             }
             // this warp has drained its quarter of accumulator `a`
             tc_fence_before();
@@ -844,6 +892,138 @@ __global__ void dot_rowmin_finish_kernel(const unsigned long long *__restrict__ 
 }
 } // namespace
 } // namespace tpw
+
+namespace tpw {
+namespace {
+// One warp per row: the k smallest of the row's n candidate keys (lists written by the top-k epilogue;
+// unused slots hold ~0), ascending.  Every lane keeps the TOPK smallest of its share, then the warp
+// extracts the global minimum k times (keys are unique: the x2 row is part of the key).
+template <int TOPK>
+__global__ void topk_merge_kernel(const unsigned long long *__restrict__ lists, float *__restrict__ val_out,
+                                  long long *__restrict__ idx_out, long long rows, long long n, int k, int take_sqrt) {
+    const int lane = threadIdx.x & 31;
+    const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (row >= rows) return;
+    unsigned long long mine[TOPK];
+#pragma unroll
+    for (int t = 0; t < TOPK; ++t) mine[t] = ~0ull;
+    const unsigned long long *src = lists + row * n;
+    for (long long e = lane; e < n; e += 32) {
+        const unsigned long long key = src[e];
+        if (key < mine[TOPK - 1]) sorted_insert<TOPK>(mine, key);
+    }
+    for (int r = 0; r < k; ++r) {
+        unsigned long long m = mine[0];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xffffffffu, m, off);
+            m = other < m ? other : m;
+        }
+        if (m != ~0ull && mine[0] == m) { // the owner pops its head
+#pragma unroll
+            for (int t = 0; t < TOPK - 1; ++t) mine[t] = mine[t + 1];
+            mine[TOPK - 1] = ~0ull;
+        }
+        if (lane == 0) {
+            const bool none = m == ~0ull;
+            float v = none ? __int_as_float(0x7f800000) : __uint_as_float((uint32_t)(m >> 32));
+            if (take_sqrt) v = sqrtf(v);
+            if (val_out) val_out[row * k + r] = v;
+            if (idx_out) idx_out[row * k + r] = none ? -1ll : (long long)(uint32_t)m;
+        }
+    }
+}
+
+constexpr int kTopkMax = 16;
+
+struct TopkScratch {
+    long long L, off_lists, off_thr, total;
+};
+inline TopkScratch topk_scratch_layout(long long B, long long N1, long long N2, long long D, long long k) {
+    TopkScratch T;
+    T.L = 2 * ((N2 + BN - 1) / BN);
+    const long long gemm = scratch_layout(B, N1, N2, D, false).total;
+    T.off_lists = gemm;
+    T.off_thr = gemm + align_up(B * N1 * T.L * k * 8, 1024);
+    T.total = T.off_thr + align_up(B * N1 * 8, 1024);
+    return T;
+}
+} // namespace
+} // namespace tpw
+
+extern "C" int tpw_dot_topk_max_k(void) { return kTopkMax; }
+
+extern "C" int64_t tpw_dot_topk_scratch_bytes(int64_t k, int64_t B, int64_t N1, int64_t N2, int64_t D) {
+    if (k <= 0 || k > kTopkMax || B <= 0 || N1 <= 0 || N2 <= 0 || D <= 0) return 0;
+    return topk_scratch_layout(B, N1, N2, D, k).total;
+}
+
+extern "C" int tpw_dot_topk_forward_ws(int epilogue, int k, const void *x1, const void *x2, float *val_out, int64_t *idx_out,
+                                       void *scratch, int64_t scratch_bytes,
+                                       int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(epilogue == TPW_DOT_SQEUCLIDEAN || epilogue == TPW_DOT_EUCLIDEAN || epilogue == TPW_DOT_COSINE_DIST,
+                  "tpw_dot_topk_forward_ws: epilogue must be TPW_DOT_SQEUCLIDEAN, TPW_DOT_EUCLIDEAN or TPW_DOT_COSINE_DIST");
+    TPW_CHECK_ARG(k >= 1 && k <= kTopkMax, "tpw_dot_topk_forward_ws: k must be in [1, %d] (got %d)", kTopkMax, k);
+    TPW_CHECK_ARG(B > 0 && N1 > 0 && N2 > 0 && D > 0, "tpw_dot_topk_forward_ws: sizes must be positive");
+    TPW_CHECK_ARG(x1 && x2 && (val_out || idx_out), "tpw_dot_topk_forward_ws: NULL pointer");
+    TPW_CHECK_ARG(N1 < (1ll << 31) && N2 < (1ll << 31) && B < (1ll << 31) && D < (1ll << 31),
+                  "tpw_dot_topk_forward_ws: a dimension exceeds 2^31-1");
+    const bool cosine = epilogue == TPW_DOT_COSINE_DIST;
+    const ScratchLayout L = scratch_layout(B, N1, N2, D, false);
+    const TopkScratch T = topk_scratch_layout(B, N1, N2, D, k);
+    TPW_CHECK_ARG(scratch != nullptr && scratch_bytes >= T.total && aligned16(scratch),
+                  "tpw_dot_topk_forward_ws: needs %lld bytes of 16-byte aligned scratch (got %lld)", T.total, (long long)scratch_bytes);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned char *base = static_cast<unsigned char *>(scratch);
+    __nv_bfloat16 *xh = reinterpret_cast<__nv_bfloat16 *>(base + L.off_xh), *xl = reinterpret_cast<__nv_bfloat16 *>(base + L.off_xl);
+    __nv_bfloat16 *yh = reinterpret_cast<__nv_bfloat16 *>(base + L.off_yh), *yl = reinterpret_cast<__nv_bfloat16 *>(base + L.off_yl);
+    float *n1 = reinterpret_cast<float *>(base + L.off_n1), *n2 = reinterpret_cast<float *>(base + L.off_n2);
+    unsigned long long *lists = reinterpret_cast<unsigned long long *>(base + T.off_lists);
+    unsigned long long *thr = reinterpret_cast<unsigned long long *>(base + T.off_thr);
+    TPW_CUDA_OK(cudaMemsetAsync(lists, 0xFF, (size_t)(T.total - T.off_lists), s)); // lists and bounds: "nothing yet"
+    const int threads = 256;
+    const long long cap = (long long)sm_count() * 16;
+    long long blocks = (B * N1 * 32 + threads - 1) / threads;
+    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x1, xh, xl, n1, B * N1, D, L.Dp, cosine ? 1 : 0);
+    blocks = (B * N2 * 32 + threads - 1) / threads;
+    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x2, yh, yl, n2, B * N2, D, L.Dp, cosine ? 1 : 0);
+    TPW_LAUNCH_OK("split_rows_kernel");
+    CUtensorMap mxh, mxl, myh, myl;
+    int st;
+    if ((st = make_tensor_map_3d(&mxh, xh, 2, L.Dp, N1, B, BK, BM, true)) != TPW_OK) return st;
+    if ((st = make_tensor_map_3d(&mxl, xl, 2, L.Dp, N1, B, BK, BM, true)) != TPW_OK) return st;
+    if ((st = make_tensor_map_3d(&myh, yh, 2, L.Dp, N2, B, BK, BN, true)) != TPW_OK) return st;
+    if ((st = make_tensor_map_3d(&myl, yl, 2, L.Dp, N2, B, BK, BN, true)) != TPW_OK) return st;
+    GemmParams P;
+    memset(&P, 0, sizeof(P));
+    P.n1sq = n1; P.n2sq = n2; P.out = nullptr;
+    P.B = B; P.N1 = N1; P.N2 = N2; P.D = L.Dp;
+    P.tiles_m = (N1 + BM - 1) / BM;
+    P.tiles_n = (N2 + BN - 1) / BN;
+    P.tiles = B * P.tiles_m * P.tiles_n;
+    P.epilogue = cosine ? TPW_DOT_COSINE_DIST : TPW_DOT_SQEUCLIDEAN;
+    P.topk_lists = lists; P.topk_thr = thr; P.topk_k = k; P.topk_L = (int)T.L;
+    P.status = device_status_ptr();
+    const long long nsm = sm_count();
+    const unsigned grid = (unsigned)(P.tiles < nsm ? P.tiles : nsm);
+#define TPW_TOPK_LAUNCH(EPI, CAP)                                                                                         \
+    do {                                                                                                                  \
+        auto kern = gemm_metric_kernel<EPI, false, false, false, false, false, CAP>;                                      \
+        TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));                 \
+        kern<<<grid, kThreads, SMEM_ALLOC, s>>>(mxh, mxl, myh, myl, P);                                                   \
+    } while (0)
+    if (cosine) { if (k <= 8) TPW_TOPK_LAUNCH(TPW_DOT_COSINE_DIST, 8); else TPW_TOPK_LAUNCH(TPW_DOT_COSINE_DIST, 16); }
+    else { if (k <= 8) TPW_TOPK_LAUNCH(TPW_DOT_SQEUCLIDEAN, 8); else TPW_TOPK_LAUNCH(TPW_DOT_SQEUCLIDEAN, 16); }
+#undef TPW_TOPK_LAUNCH
+    TPW_LAUNCH_OK("gemm_metric_kernel (top-k)");
+    const long long rows = B * N1, n = T.L * k;
+    const unsigned mblocks = (unsigned)((rows * 32 + 255) / 256);
+    if (k <= 8) topk_merge_kernel<8><<<mblocks, 256, 0, s>>>(lists, val_out, reinterpret_cast<long long *>(idx_out), rows, n, k, epilogue == TPW_DOT_EUCLIDEAN);
+    else topk_merge_kernel<16><<<mblocks, 256, 0, s>>>(lists, val_out, reinterpret_cast<long long *>(idx_out), rows, n, k, epilogue == TPW_DOT_EUCLIDEAN);
+    TPW_LAUNCH_OK("topk_merge_kernel");
+    return TPW_OK;
+}
 
 extern "C" int64_t tpw_dot_rowmin_scratch_bytes(int64_t B, int64_t N1, int64_t N2, int64_t D) {
     if (B <= 0 || N1 <= 0 || N2 <= 0 || D <= 0) return 0;

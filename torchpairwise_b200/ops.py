@@ -1004,6 +1004,13 @@ def k_neighbors_mask(x1: Tensor, x2: Optional[Tensor] = None, k: int = 1, metric
             inds = pairwise_argmin_min(x1_, x2_, metric, kwargs.get("p"))[0].unsqueeze(1)
             out = torch.zeros((x1_.size(0), x2_.size(0)), dtype=torch.bool, device=x1_.device)
             return out.scatter_(1, inds, True)
+        if metric in ("euclidean", "l2", "sqeuclidean", "cosine") and not kwargs and x1_.is_cuda and x1_.dtype == torch.float32 \
+                and x2_.dtype == torch.float32 and 0 < k + 1 <= min(lib.tpw_dot_topk_max_k(), x2_.size(0)) \
+                and _tensor_engine_selected(x1_.unsqueeze(0), x2_.unsqueeze(0)):
+            # large problem: the k + 1 nearest rows straight from the tensor-core epilogue, no distance matrix
+            inds = pairwise_argkmin(x1_, x2_, k + 1, metric)[0]
+            out = torch.zeros((x1_.size(0), x2_.size(0)), dtype=torch.bool, device=x1_.device)
+            return out.scatter_(1, inds, True)
         dists = cdist(x1_, x2_, metric, **kwargs)
         # the k + 1 smallest of every row: a partial selection, not the reference's full argsort of each row
         inds = dists.topk(min(k + 1, dists.size(1)), dim=1, largest=False, sorted=False).indices
@@ -1098,3 +1105,41 @@ def pairwise_argmin_min(x1: Tensor, x2: Optional[Tensor] = None, metric: str = "
         if unbatched:
             mins, args = mins.squeeze(0), args.squeeze(0)
         return args, mins
+
+
+def pairwise_argkmin(x1: Tensor, x2: Optional[Tensor] = None, k: int = 1, metric: str = "euclidean",
+                     **kwargs) -> Tuple[Tensor, Tensor]:
+    """The k nearest x2 rows of every x1 row: ``(indices [.., N1, k] int64, distances [.., N1, k])``,
+    ascending by distance, no gradient.  The reference's README lists ``argkmin`` as future work; its
+    ``k_neighbors_mask`` sorts every row of the materialised matrix (OPS/neighbors.cpp:10-35).
+
+    Large float32 problems with a Euclidean, squared Euclidean or cosine metric and
+    ``k <= tpw_dot_topk_max_k()`` run the tensor-core kernel whose epilogue keeps the k smallest keys
+    of each accumulator row in registers (``tpw_dot_topk_forward_ws``; no distance matrix is written).
+    Everything else takes this package's distance kernel followed by a partial selection."""
+    from .cpdist import cdist
+    if k < 1:
+        raise RuntimeError(f"k must be positive. Got k={k}")
+    x1_, x2_ = check_pairwise_inputs("pairwise_argkmin", x1, x2)
+    _require_cuda(x1_, x2_)
+    if k > x2_.size(-2):
+        raise RuntimeError(f"k={k} exceeds the number of x2 rows ({x2_.size(-2)})")
+    epilogue = {"euclidean": _abi.DOT_EUCLIDEAN, "l2": _abi.DOT_EUCLIDEAN, "sqeuclidean": _abi.DOT_SQEUCLIDEAN,
+                "cosine": _abi.DOT_COSINE_DIST}.get(metric)
+    with torch.no_grad():
+        if epilogue is not None and not kwargs and x1_.dtype == torch.float32 and x2_.dtype == torch.float32 \
+                and x1_.size(-1) > 0 and k <= lib.tpw_dot_topk_max_k():
+            x1c, x2c, unbatched = _batched(x1_, x2_, "pairwise_argkmin")
+            if _tensor_engine_selected(x1c, x2c):
+                B, N1, N2, D = _sizes(x1c, x2c)
+                vals = torch.empty((B, N1, k), dtype=torch.float32, device=x1c.device)
+                inds = torch.empty((B, N1, k), dtype=torch.int64, device=x1c.device)
+                nbytes = lib.tpw_dot_topk_scratch_bytes(k, B, N1, N2, D)
+                scratch = torch.empty((nbytes,), dtype=torch.uint8, device=x1c.device)
+                with torch.cuda.device(x1c.device):
+                    check(lib.tpw_dot_topk_forward_ws(epilogue, k, _ptr(x1c), _ptr(x2c), _ptr(vals), _ptr(inds), _ptr(scratch), nbytes,
+                                                      B, N1, N2, D, _stream(x1c)), "tpw_dot_topk_forward_ws")
+                return (inds.squeeze(0), vals.squeeze(0)) if unbatched else (inds, vals)
+        dist = cdist(x1_, x2_, metric, **kwargs)
+        vals, inds = dist.topk(k, dim=-1, largest=False, sorted=True)
+        return inds, vals

@@ -695,7 +695,8 @@ def test_pairwise_argmin_min_tensor_cores(tensor_engine, shape):
 
 
 @pytest.mark.parametrize("shape,k", [((1, 300, 520, 96), 1), ((1, 300, 520, 96), 3), ((1, 300, 520, 96), 8), ((1, 300, 520, 96), 16),
-                                     ((2, 257, 1030, 130), 5), ((1, 128, 256, 64), 8), ((1, 40, 9, 16), 9), ((1, 700, 2100, 64), 12)],
+                                     ((2, 257, 1030, 130), 5), ((1, 128, 256, 64), 8), ((1, 40, 9, 16), 9), ((1, 700, 2100, 64), 12),
+                                     ((1, 260, 4500, 64), 8), ((2, 130, 9000, 72), 16)],   # 18 and 36 column tiles: three column ranges
                          ids=lambda v: "x".join(map(str, v)) if isinstance(v, tuple) else str(v))
 def test_pairwise_argkmin_tensor_cores(tensor_engine, shape, k):
     """The k nearest rows from the tcgen05 top-k epilogue (forced) against the float64 matrix: ascending

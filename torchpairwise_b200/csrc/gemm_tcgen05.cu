@@ -70,6 +70,7 @@ struct GemmParams {
     // [B*N1][topk_L][topk_k], and [B*N1] published upper bounds of the row's k-th smallest key
     unsigned long long *topk_lists, *topk_thr;
     int topk_k, topk_L;
+    long long tn0;            // first column tile of this launch (tiles_n counts from it); top-k runs in column ranges
     int *status;
 };
 
@@ -121,6 +122,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
+}
+// 32 lanes x 8 consecutive 32-bit columns
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -187,6 +195,23 @@ __device__ __forceinline__ float dot_epilogue(float dot, float n1, float n2, boo
 // TF32 = false: operands are bf16 high/low parts, 64 per k-step; true: tf32 high/low parts in fp32
 // containers, 32 per k-step.  Either way a k-step is one 128-byte swizzled row per operand row and
 // four MMAs per operand pair, so the pipeline below is the same.
+// Tile index -> (column tile, row tile, batch).  Column tiles vary fastest, so that consecutive tiles
+// share the x1 rows and stream the (usually L2-resident) x2 rows -- except for the top-k epilogue, where
+// row tiles vary fastest: a row's column tiles are then visited one after another over the run, and the
+// bound published by its earlier column tiles prunes the later ones.
+template <bool ROW_TILES_FASTEST>
+__device__ __forceinline__ void decode_tile(long long tile, const GemmParams &P, long long &tn, long long &tm, long long &b) {
+    if (ROW_TILES_FASTEST) {
+        tm = tile % P.tiles_m; tile /= P.tiles_m;
+        tn = tile % P.tiles_n + P.tn0;
+        b = tile / P.tiles_n;
+    } else {
+        tn = tile % P.tiles_n; tile /= P.tiles_n;
+        tm = tile % P.tiles_m;
+        b = tile / P.tiles_m;
+    }
+}
+
 // Sorted insertion into an ascending register-resident list (branch-free: slot t becomes
 // min(max(previous slot, key), slot t)); the largest entry falls off the end.
 template <int N>
@@ -248,10 +273,8 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
             uint32_t it = 0;
             bool ok = true;
             for (long long tile = blockIdx.x; tile < P.tiles && ok; tile += gridDim.x) {
-                long long t = tile;
-                const long long tn = t % P.tiles_n; t /= P.tiles_n;
-                const long long tm = t % P.tiles_m;
-                const long long b = t / P.tiles_m;
+                long long tn, tm, b;
+                decode_tile<TOPK != 0>(tile, P, tn, tm, b);
                 for (int kb = 0; kb < nkb; ++kb, ++it) {
                     const int s = it % kStages;
                     const uint32_t use = it / kStages;
@@ -430,10 +453,8 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
             }
         } else
         for (long long tile = blockIdx.x; tile < P.tiles && ok; tile += gridDim.x, ++tcount) {
-            long long t = tile;
-            const long long tn = t % P.tiles_n; t /= P.tiles_n;
-            const long long tm = t % P.tiles_m;
-            const long long b = t / P.tiles_m;
+            long long tn, tm, b;
+            decode_tile<TOPK != 0>(tile, P, tn, tm, b);
             const uint32_t a = tcount & 1;
             if (!wait_or_abort(&tmem_full[a], (tcount >> 1) & 1, abort_flag)) {
                 *abort_flag = 1;
@@ -457,6 +478,29 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
                 for (int t = 0; t < TOPK; ++t) lst[t] = ~0ull;
                 if (row_ok) bound = *reinterpret_cast<volatile unsigned long long *>(P.topk_thr + b * P.N1 + i);
             }
+            if constexpr (TOPK > 0) {
+                // eight columns at a time, so that the unrolled body (and its insertion code) stays small;
+                // the insertion is entered only when some lane of the warp has a candidate below its bounds
+#pragma unroll 1
+                for (int g = 0; g < BN / 16; ++g) {
+                    const long long j0 = tn * BN + chalf * (BN / 2) + g * 8;
+                    if (j0 >= P.N2) break;
+                    uint32_t r8[8];
+                    tmem_ld8(tmem_base + ((uint32_t)(q * 32) << 16) + a * BN + chalf * (BN / 2) + g * 8, r8);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) {
+                        const long long j = j0 + v;
+                        const float nn = j < P.N2 ? __ldg(n2p + j) : 0.f;
+                        const float o = dot_epilogue<EPI>(__uint_as_float(r8[v]), n1, nn, false);
+                        const unsigned long long key = ((unsigned long long)__float_as_uint(o) << 32) | (unsigned long long)(uint32_t)j;
+                        const bool cand = j < P.N2 && key < bound && key < lst[TOPK - 1];
+                        if (__any_sync(0xffffffffu, cand)) {
+                            if (cand) sorted_insert<TOPK>(lst, key);
+                        }
+                    }
+                }
+            } else
 #pragma unroll 1
             for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
                 uint32_t r[32];
@@ -465,17 +509,6 @@ gemm_metric_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_cons
                 tmem_ld_wait();
                 const long long j0 = tn * BN + c * 32;
                 if (j0 >= P.N2) continue;
-                if constexpr (TOPK > 0) {
-#pragma unroll
-                    for (int v = 0; v < 32; ++v) { // fully unrolled: r[] must stay in registers
-                        const long long j = j0 + v;
-                        const float nn = j < P.N2 ? __ldg(n2p + j) : 0.f;
-                        const float o = dot_epilogue<EPI>(__uint_as_float(r[v]), n1, nn, false);
-                        const unsigned long long key = ((unsigned long long)__float_as_uint(o) << 32) | (unsigned long long)(uint32_t)j;
-                        if (j < P.N2 && key < bound && key < lst[TOPK - 1]) sorted_insert<TOPK>(lst, key);
-                    }
-                    continue;
-                }
                 if constexpr (ROWMIN) {
                     // streaming row minimum: this thread owns row i and folds its 32 columns into one key
                     // (the epilogue value is non-negative, so its bit pattern orders like an unsigned integer)
@@ -898,16 +931,18 @@ namespace {
 // One warp per row: the k smallest of the row's n candidate keys (lists written by the top-k epilogue;
 // unused slots hold ~0), ascending.  Every lane keeps the TOPK smallest of its share, then the warp
 // extracts the global minimum k times (keys are unique: the x2 row is part of the key).
+// bound_out (optional): the k-th smallest key itself, left untouched when fewer than k candidates exist.
 template <int TOPK>
 __global__ void topk_merge_kernel(const unsigned long long *__restrict__ lists, float *__restrict__ val_out,
-                                  long long *__restrict__ idx_out, long long rows, long long n, int k, int take_sqrt) {
+                                  long long *__restrict__ idx_out, unsigned long long *__restrict__ bound_out,
+                                  long long rows, long long row_stride, long long n, int k, int take_sqrt) {
     const int lane = threadIdx.x & 31;
     const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (row >= rows) return;
     unsigned long long mine[TOPK];
 #pragma unroll
     for (int t = 0; t < TOPK; ++t) mine[t] = ~0ull;
-    const unsigned long long *src = lists + row * n;
+    const unsigned long long *src = lists + row * row_stride;
     for (long long e = lane; e < n; e += 32) {
         const unsigned long long key = src[e];
         if (key < mine[TOPK - 1]) sorted_insert<TOPK>(mine, key);
@@ -930,6 +965,7 @@ __global__ void topk_merge_kernel(const unsigned long long *__restrict__ lists, 
             if (take_sqrt) v = sqrtf(v);
             if (val_out) val_out[row * k + r] = v;
             if (idx_out) idx_out[row * k + r] = none ? -1ll : (long long)(uint32_t)m;
+            if (bound_out && r == k - 1 && !none) bound_out[row] = m;
         }
     }
 }
@@ -1006,21 +1042,38 @@ extern "C" int tpw_dot_topk_forward_ws(int epilogue, int k, const void *x1, cons
     P.topk_lists = lists; P.topk_thr = thr; P.topk_k = k; P.topk_L = (int)T.L;
     P.status = device_status_ptr();
     const long long nsm = sm_count();
-    const unsigned grid = (unsigned)(P.tiles < nsm ? P.tiles : nsm);
+    const long long tiles_n_all = (N2 + BN - 1) / BN;
+    const long long rows = B * N1;
+    const unsigned mblocks = (unsigned)((rows * 32 + 255) / 256);
+    long long *idx64 = reinterpret_cast<long long *>(idx_out);
+    const int take_sqrt = epilogue == TPW_DOT_EUCLIDEAN ? 1 : 0;
 #define TPW_TOPK_LAUNCH(EPI, CAP)                                                                                         \
     do {                                                                                                                  \
         auto kern = gemm_metric_kernel<EPI, false, false, false, false, false, CAP>;                                      \
         TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));                 \
         kern<<<grid, kThreads, SMEM_ALLOC, s>>>(mxh, mxl, myh, myl, P);                                                   \
     } while (0)
-    if (cosine) { if (k <= 8) TPW_TOPK_LAUNCH(TPW_DOT_COSINE_DIST, 8); else TPW_TOPK_LAUNCH(TPW_DOT_COSINE_DIST, 16); }
-    else { if (k <= 8) TPW_TOPK_LAUNCH(TPW_DOT_SQEUCLIDEAN, 8); else TPW_TOPK_LAUNCH(TPW_DOT_SQEUCLIDEAN, 16); }
+    // Column ranges [0, 1/16), [1/16, 1/4), [1/4, 1) of the column tiles: after each range the lists so far
+    // are merged into an exact bound of every row's k-th smallest key, which prunes the next range down to
+    // the few candidates that can still matter (an insertion costs the whole warp as soon as one lane has one).
+    const long long cut[4] = {0, tiles_n_all >= 16 ? tiles_n_all / 16 : 0, tiles_n_all >= 16 ? tiles_n_all / 4 : 0, tiles_n_all};
+    for (int ph = 0; ph < 3; ++ph) {
+        if (cut[ph + 1] <= cut[ph]) continue;
+        P.tn0 = cut[ph];
+        P.tiles_n = cut[ph + 1] - cut[ph];
+        P.tiles = B * P.tiles_m * P.tiles_n;
+        const unsigned grid = (unsigned)(P.tiles < nsm ? P.tiles : nsm);
+        if (cosine) { if (k <= 8) TPW_TOPK_LAUNCH(TPW_DOT_COSINE_DIST, 8); else TPW_TOPK_LAUNCH(TPW_DOT_COSINE_DIST, 16); }
+        else { if (k <= 8) TPW_TOPK_LAUNCH(TPW_DOT_SQEUCLIDEAN, 8); else TPW_TOPK_LAUNCH(TPW_DOT_SQEUCLIDEAN, 16); }
+        TPW_LAUNCH_OK("gemm_metric_kernel (top-k)");
+        const bool last = cut[ph + 1] == tiles_n_all;
+        const long long n = 2 * cut[ph + 1] * k; // the lists of all column tiles processed so far
+        if (k <= 8) topk_merge_kernel<8><<<mblocks, 256, 0, s>>>(lists, last ? val_out : nullptr, last ? idx64 : nullptr, last ? nullptr : thr,
+                                                                  rows, T.L * k, n, k, take_sqrt);
+        else topk_merge_kernel<16><<<mblocks, 256, 0, s>>>(lists, last ? val_out : nullptr, last ? idx64 : nullptr, last ? nullptr : thr,
+                                                                   rows, T.L * k, n, k, take_sqrt);
+    }
 #undef TPW_TOPK_LAUNCH
-    TPW_LAUNCH_OK("gemm_metric_kernel (top-k)");
-    const long long rows = B * N1, n = T.L * k;
-    const unsigned mblocks = (unsigned)((rows * 32 + 255) / 256);
-    if (k <= 8) topk_merge_kernel<8><<<mblocks, 256, 0, s>>>(lists, val_out, reinterpret_cast<long long *>(idx_out), rows, n, k, epilogue == TPW_DOT_EUCLIDEAN);
-    else topk_merge_kernel<16><<<mblocks, 256, 0, s>>>(lists, val_out, reinterpret_cast<long long *>(idx_out), rows, n, k, epilogue == TPW_DOT_EUCLIDEAN);
     TPW_LAUNCH_OK("topk_merge_kernel");
     return TPW_OK;
 }

@@ -987,6 +987,46 @@ inline TopkScratch topk_scratch_layout(long long B, long long N1, long long N2, 
 } // namespace
 } // namespace tpw
 
+namespace tpw {
+namespace {
+// Common front end of the bf16 x 3 launches: splits x1 and x2 into the scratch (bf16 high/low parts, row
+// norms: squared, or reciprocal for the cosine family), encodes the four tensor maps and fills the
+// problem sizes of `P`.  The caller sets the epilogue-specific fields and launches.
+struct Bf16Operands {
+    CUtensorMap mxh, mxl, myh, myl;
+};
+int prepare_bf16_operands(const void *x1, const void *x2, void *scratch, bool reciprocal_norms,
+                          long long B, long long N1, long long N2, long long D, cudaStream_t s,
+                          Bf16Operands &M, GemmParams &P) {
+    const ScratchLayout L = scratch_layout(B, N1, N2, D, false);
+    unsigned char *base = static_cast<unsigned char *>(scratch);
+    __nv_bfloat16 *xh = reinterpret_cast<__nv_bfloat16 *>(base + L.off_xh), *xl = reinterpret_cast<__nv_bfloat16 *>(base + L.off_xl);
+    __nv_bfloat16 *yh = reinterpret_cast<__nv_bfloat16 *>(base + L.off_yh), *yl = reinterpret_cast<__nv_bfloat16 *>(base + L.off_yl);
+    float *n1 = reinterpret_cast<float *>(base + L.off_n1), *n2 = reinterpret_cast<float *>(base + L.off_n2);
+    const int threads = 256;
+    const long long cap = (long long)sm_count() * 16;
+    long long blocks = (B * N1 * 32 + threads - 1) / threads;
+    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x1, xh, xl, n1, B * N1, D, L.Dp, reciprocal_norms ? 1 : 0);
+    blocks = (B * N2 * 32 + threads - 1) / threads;
+    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x2, yh, yl, n2, B * N2, D, L.Dp, reciprocal_norms ? 1 : 0);
+    TPW_LAUNCH_OK("split_rows_kernel");
+    int st;
+    if ((st = make_tensor_map_3d(&M.mxh, xh, 2, L.Dp, N1, B, BK, BM, true)) != TPW_OK) return st;
+    if ((st = make_tensor_map_3d(&M.mxl, xl, 2, L.Dp, N1, B, BK, BM, true)) != TPW_OK) return st;
+    if ((st = make_tensor_map_3d(&M.myh, yh, 2, L.Dp, N2, B, BK, BN, true)) != TPW_OK) return st;
+    if ((st = make_tensor_map_3d(&M.myl, yl, 2, L.Dp, N2, B, BK, BN, true)) != TPW_OK) return st;
+    memset(&P, 0, sizeof(P));
+    P.n1sq = n1; P.n2sq = n2;
+    P.B = B; P.N1 = N1; P.N2 = N2; P.D = L.Dp;
+    P.tiles_m = (N1 + BM - 1) / BM;
+    P.tiles_n = (N2 + BN - 1) / BN;
+    P.tiles = B * P.tiles_m * P.tiles_n;
+    P.status = device_status_ptr();
+    return TPW_OK;
+}
+} // namespace
+} // namespace tpw
+
 extern "C" int tpw_dot_topk_max_k(void) { return kTopkMax; }
 
 extern "C" int64_t tpw_dot_topk_scratch_bytes(int64_t k, int64_t B, int64_t N1, int64_t N2, int64_t D) {
@@ -1006,41 +1046,20 @@ extern "C" int tpw_dot_topk_forward_ws(int epilogue, int k, const void *x1, cons
     TPW_CHECK_ARG(N1 < (1ll << 31) && N2 < (1ll << 31) && B < (1ll << 31) && D < (1ll << 31),
                   "tpw_dot_topk_forward_ws: a dimension exceeds 2^31-1");
     const bool cosine = epilogue == TPW_DOT_COSINE_DIST;
-    const ScratchLayout L = scratch_layout(B, N1, N2, D, false);
     const TopkScratch T = topk_scratch_layout(B, N1, N2, D, k);
     TPW_CHECK_ARG(scratch != nullptr && scratch_bytes >= T.total && aligned16(scratch),
                   "tpw_dot_topk_forward_ws: needs %lld bytes of 16-byte aligned scratch (got %lld)", T.total, (long long)scratch_bytes);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     unsigned char *base = static_cast<unsigned char *>(scratch);
-    __nv_bfloat16 *xh = reinterpret_cast<__nv_bfloat16 *>(base + L.off_xh), *xl = reinterpret_cast<__nv_bfloat16 *>(base + L.off_xl);
-    __nv_bfloat16 *yh = reinterpret_cast<__nv_bfloat16 *>(base + L.off_yh), *yl = reinterpret_cast<__nv_bfloat16 *>(base + L.off_yl);
-    float *n1 = reinterpret_cast<float *>(base + L.off_n1), *n2 = reinterpret_cast<float *>(base + L.off_n2);
     unsigned long long *lists = reinterpret_cast<unsigned long long *>(base + T.off_lists);
     unsigned long long *thr = reinterpret_cast<unsigned long long *>(base + T.off_thr);
     TPW_CUDA_OK(cudaMemsetAsync(lists, 0xFF, (size_t)(T.total - T.off_lists), s)); // lists and bounds: "nothing yet"
-    const int threads = 256;
-    const long long cap = (long long)sm_count() * 16;
-    long long blocks = (B * N1 * 32 + threads - 1) / threads;
-    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x1, xh, xl, n1, B * N1, D, L.Dp, cosine ? 1 : 0);
-    blocks = (B * N2 * 32 + threads - 1) / threads;
-    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x2, yh, yl, n2, B * N2, D, L.Dp, cosine ? 1 : 0);
-    TPW_LAUNCH_OK("split_rows_kernel");
-    CUtensorMap mxh, mxl, myh, myl;
-    int st;
-    if ((st = make_tensor_map_3d(&mxh, xh, 2, L.Dp, N1, B, BK, BM, true)) != TPW_OK) return st;
-    if ((st = make_tensor_map_3d(&mxl, xl, 2, L.Dp, N1, B, BK, BM, true)) != TPW_OK) return st;
-    if ((st = make_tensor_map_3d(&myh, yh, 2, L.Dp, N2, B, BK, BN, true)) != TPW_OK) return st;
-    if ((st = make_tensor_map_3d(&myl, yl, 2, L.Dp, N2, B, BK, BN, true)) != TPW_OK) return st;
+    Bf16Operands M;
     GemmParams P;
-    memset(&P, 0, sizeof(P));
-    P.n1sq = n1; P.n2sq = n2; P.out = nullptr;
-    P.B = B; P.N1 = N1; P.N2 = N2; P.D = L.Dp;
-    P.tiles_m = (N1 + BM - 1) / BM;
-    P.tiles_n = (N2 + BN - 1) / BN;
-    P.tiles = B * P.tiles_m * P.tiles_n;
+    int st;
+    if ((st = prepare_bf16_operands(x1, x2, scratch, cosine, B, N1, N2, D, s, M, P)) != TPW_OK) return st;
     P.epilogue = cosine ? TPW_DOT_COSINE_DIST : TPW_DOT_SQEUCLIDEAN;
     P.topk_lists = lists; P.topk_thr = thr; P.topk_k = k; P.topk_L = (int)T.L;
-    P.status = device_status_ptr();
     const long long nsm = sm_count();
     const long long tiles_n_all = (N2 + BN - 1) / BN;
     const long long rows = B * N1;
@@ -1051,7 +1070,7 @@ extern "C" int tpw_dot_topk_forward_ws(int epilogue, int k, const void *x1, cons
     do {                                                                                                                  \
         auto kern = gemm_metric_kernel<EPI, false, false, false, false, false, CAP>;                                      \
         TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));                 \
-        kern<<<grid, kThreads, SMEM_ALLOC, s>>>(mxh, mxl, myh, myl, P);                                                   \
+        kern<<<grid, kThreads, SMEM_ALLOC, s>>>(M.mxh, M.mxl, M.myh, M.myl, P);                                           \
     } while (0)
     // Column ranges [0, 1/16), [1/16, 1/4), [1/4, 1) of the column tiles: after each range the lists so far
     // are merged into an exact bound of every row's k-th smallest key, which prunes the next range down to
@@ -1099,45 +1118,24 @@ extern "C" int tpw_dot_rowmin_forward_ws(int epilogue, const void *x1, const voi
     TPW_CHECK_ARG(scratch != nullptr && scratch_bytes >= need && aligned16(scratch),
                   "tpw_dot_rowmin_forward_ws: needs %lld bytes of 16-byte aligned scratch (got %lld)", need, (long long)scratch_bytes);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    unsigned char *base = static_cast<unsigned char *>(scratch);
-    __nv_bfloat16 *xh = reinterpret_cast<__nv_bfloat16 *>(base + L.off_xh), *xl = reinterpret_cast<__nv_bfloat16 *>(base + L.off_xl);
-    __nv_bfloat16 *yh = reinterpret_cast<__nv_bfloat16 *>(base + L.off_yh), *yl = reinterpret_cast<__nv_bfloat16 *>(base + L.off_yl);
-    float *n1 = reinterpret_cast<float *>(base + L.off_n1), *n2 = reinterpret_cast<float *>(base + L.off_n2);
-    unsigned long long *keys = reinterpret_cast<unsigned long long *>(base + L.total);
+    unsigned long long *keys = reinterpret_cast<unsigned long long *>(static_cast<unsigned char *>(scratch) + L.total);
     TPW_CUDA_OK(cudaMemsetAsync(keys, 0xFF, (size_t)(B * N1) * 8, s));
-    const int threads = 256;
-    const long long cap = (long long)sm_count() * 16;
-    long long blocks = (B * N1 * 32 + threads - 1) / threads;
-    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x1, xh, xl, n1, B * N1, D, L.Dp, cosine ? 1 : 0);
-    blocks = (B * N2 * 32 + threads - 1) / threads;
-    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x2, yh, yl, n2, B * N2, D, L.Dp, cosine ? 1 : 0);
-    TPW_LAUNCH_OK("split_rows_kernel");
-    CUtensorMap mxh, mxl, myh, myl;
-    int st;
-    if ((st = make_tensor_map_3d(&mxh, xh, 2, L.Dp, N1, B, BK, BM, true)) != TPW_OK) return st;
-    if ((st = make_tensor_map_3d(&mxl, xl, 2, L.Dp, N1, B, BK, BM, true)) != TPW_OK) return st;
-    if ((st = make_tensor_map_3d(&myh, yh, 2, L.Dp, N2, B, BK, BN, true)) != TPW_OK) return st;
-    if ((st = make_tensor_map_3d(&myl, yl, 2, L.Dp, N2, B, BK, BN, true)) != TPW_OK) return st;
+    Bf16Operands M;
     GemmParams P;
-    memset(&P, 0, sizeof(P));
-    P.n1sq = n1; P.n2sq = n2; P.out = nullptr;
-    P.B = B; P.N1 = N1; P.N2 = N2; P.D = L.Dp;
-    P.tiles_m = (N1 + BM - 1) / BM;
-    P.tiles_n = (N2 + BN - 1) / BN;
-    P.tiles = B * P.tiles_m * P.tiles_n;
+    int st;
+    if ((st = prepare_bf16_operands(x1, x2, scratch, cosine, B, N1, N2, D, s, M, P)) != TPW_OK) return st;
     P.epilogue = cosine ? TPW_DOT_COSINE_DIST : TPW_DOT_SQEUCLIDEAN;
     P.rowmin_keys = keys;
-    P.status = device_status_ptr();
     const long long nsm = sm_count();
     const unsigned grid = (unsigned)(P.tiles < nsm ? P.tiles : nsm);
     if (cosine) {
         auto kern = gemm_metric_kernel<TPW_DOT_COSINE_DIST, false, false, true>;
         TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
-        kern<<<grid, kThreads, SMEM_ALLOC, s>>>(mxh, mxl, myh, myl, P);
+        kern<<<grid, kThreads, SMEM_ALLOC, s>>>(M.mxh, M.mxl, M.myh, M.myl, P);
     } else {
         auto kern = gemm_metric_kernel<TPW_DOT_SQEUCLIDEAN, false, false, true>;
         TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
-        kern<<<grid, kThreads, SMEM_ALLOC, s>>>(mxh, mxl, myh, myl, P);
+        kern<<<grid, kThreads, SMEM_ALLOC, s>>>(M.mxh, M.mxl, M.myh, M.myl, P);
     }
     TPW_LAUNCH_OK("gemm_metric_kernel (row minimum)");
     dot_rowmin_finish_kernel<<<(unsigned)((B * N1 + 255) / 256), 256, 0, s>>>(keys, min_out, reinterpret_cast<long long *>(arg_out), B * N1,
@@ -1210,38 +1208,15 @@ extern "C" int tpw_dot_metric_forward_ws(int dtype, int epilogue, int engine,
                   L.total, (long long)scratch_bytes);
     TPW_CHECK_ARG(aligned16(scratch), "tpw_dot_metric_forward_ws: scratch must be 16-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    unsigned char *base = static_cast<unsigned char *>(scratch);
-    __nv_bfloat16 *xh = reinterpret_cast<__nv_bfloat16 *>(base + L.off_xh), *xl = reinterpret_cast<__nv_bfloat16 *>(base + L.off_xl);
-    __nv_bfloat16 *yh = reinterpret_cast<__nv_bfloat16 *>(base + L.off_yh), *yl = reinterpret_cast<__nv_bfloat16 *>(base + L.off_yl);
-    float *n1 = reinterpret_cast<float *>(base + L.off_n1), *n2 = reinterpret_cast<float *>(base + L.off_n2);
-
-    const int threads = 256;
-    const long long cap = (long long)sm_count() * 16;
-    long long blocks = (B * N1 * 32 + threads - 1) / threads;
-    const int recip = (epilogue == TPW_DOT_COSINE_SIM || epilogue == TPW_DOT_COSINE_DIST || epilogue == TPW_DOT_ONE_MINUS_SIM) ? 1 : 0;
-    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x1, xh, xl, n1, B * N1, D, L.Dp, recip);
-    blocks = (B * N2 * 32 + threads - 1) / threads;
-    split_rows_kernel<<<(unsigned)(blocks < cap ? blocks : cap), threads, 0, s>>>((const float *)x2, yh, yl, n2, B * N2, D, L.Dp, recip);
-    TPW_LAUNCH_OK("split_rows_kernel");
-
-    CUtensorMap mxh, mxl, myh, myl;
-    int st;
-    if ((st = make_tensor_map_3d(&mxh, xh, 2, L.Dp, N1, B, BK, BM, true)) != TPW_OK) return st;
-    if ((st = make_tensor_map_3d(&mxl, xl, 2, L.Dp, N1, B, BK, BM, true)) != TPW_OK) return st;
-    if ((st = make_tensor_map_3d(&myh, yh, 2, L.Dp, N2, B, BK, BN, true)) != TPW_OK) return st;
-    if ((st = make_tensor_map_3d(&myl, yl, 2, L.Dp, N2, B, BK, BN, true)) != TPW_OK) return st;
-
+    const bool recip = epilogue == TPW_DOT_COSINE_SIM || epilogue == TPW_DOT_COSINE_DIST || epilogue == TPW_DOT_ONE_MINUS_SIM;
+    Bf16Operands M;
     GemmParams P;
-    memset(&P, 0, sizeof(P));
-    P.n1sq = n1; P.n2sq = n2; P.out = static_cast<float *>(out);
-    P.B = B; P.N1 = N1; P.N2 = N2; P.D = L.Dp;
-    P.tiles_m = (N1 + BM - 1) / BM;
-    P.tiles_n = (N2 + BN - 1) / BN;
-    P.tiles = B * P.tiles_m * P.tiles_n;
+    int st;
+    if ((st = prepare_bf16_operands(x1, x2, scratch, recip, B, N1, N2, D, s, M, P)) != TPW_OK) return st;
+    P.out = static_cast<float *>(out);
     P.epilogue = epilogue;
     P.self = self ? 1 : 0;
     P.vec_store = (N2 % 4 == 0 && aligned16(out)) ? 1 : 0;
-    P.status = device_status_ptr();
     TPW_CHECK_ARG(P.tiles < (1ll << 40), "tpw_dot_metric_forward_ws: too many tiles");
     const long long nsm = sm_count();
     const unsigned grid = (unsigned)(P.tiles < nsm ? P.tiles : nsm);
@@ -1249,7 +1224,7 @@ extern "C" int tpw_dot_metric_forward_ws(int dtype, int epilogue, int engine,
     do {                                                                                                                  \
         auto kern = gemm_metric_kernel<EPI, SELF, false>;                                                                        \
         TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));                 \
-        kern<<<grid, kThreads, SMEM_ALLOC, s>>>(mxh, mxl, myh, myl, P);                                                   \
+        kern<<<grid, kThreads, SMEM_ALLOC, s>>>(M.mxh, M.mxl, M.myh, M.myl, P);                                           \
     } while (0)
     switch (epilogue) {
         case TPW_DOT_LINEAR: TPW_GEMM_LAUNCH(TPW_DOT_LINEAR, false); break;

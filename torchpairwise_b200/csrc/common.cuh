@@ -4,6 +4,7 @@
 
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <math.h>
 #include <stdint.h>
 #include <stdio.h>
 #include <stdarg.h>
@@ -61,7 +62,31 @@ int make_tensor_map_3d(CUtensorMap *map, const void *base, int elem_bytes,
 int make_tensor_map_3d_atom32(CUtensorMap *map, const void *base, int elem_bytes,
                               uint64_t dim0, uint64_t dim1, uint64_t dim2, uint32_t box0, uint32_t box1);
 
+// |d|^q in the float kernels.  spec = mode | m << 2 (uniform over a launch): mode 0 is the general
+// exp2(q log2 a) (two MUFU operations per element); mode 1 is q = m + 1/2, one approximate square
+// root (MUFU.SQRT, 1 ulp) times a^m; mode 2 is the integer q = m as repeated multiplication.
+// The special modes cover q <= 4.5 and are both faster and more accurate than the general form.
+inline int make_pow_spec(double q) {
+    const double fl = floor(q);
+    if (q == fl && q >= 1.0 && q <= 4.0) return 2 | ((int)q << 2);
+    if (q - fl == 0.5 && fl >= 0.0 && fl <= 4.0) return 1 | ((int)fl << 2);
+    return 0;
+}
+
 #ifdef __CUDACC__
+__device__ __forceinline__ float pow_abs_spec(float a, float q, int spec) {
+    const int mode = spec & 3, m = spec >> 2;
+    if (mode == 0) return a == 0.f ? 0.f : exp2f(q * __log2f(a));
+    float r = 1.f;
+    if (mode == 1) asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a));
+    if (m >= 1) r *= a;
+    if (m >= 2) r *= a;
+    if (m >= 3) r *= a;
+    if (m >= 4) r *= a;
+    return r;
+}
+__device__ __forceinline__ double pow_abs_spec(double a, double q, int) { return a == 0.0 ? 0.0 : pow(a, q); }
+
 // ---- device-side PTX wrappers -----------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

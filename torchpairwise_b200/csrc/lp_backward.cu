@@ -45,6 +45,7 @@ struct BwdParams {
     long long B, N1, N2, D, NR, NS;
     long long tiles_r, tiles_k;
     double q;           // exponent of PHI_SGNPOW / PHI_ABSPOW, and of COEF_DIV_POW
+    int pow_spec;       // make_pow_spec(q): how the float kernels evaluate |d|^q
     double post;        // scalar applied to every result
     int coef_mode;
     int *status;
@@ -86,7 +87,7 @@ __device__ __forceinline__ double b_pow(double a, double q) { return pow(a, q); 
 
 // acc += c * phi(x - y)
 template <int PHI, typename T>
-__device__ __forceinline__ void bwd_accumulate(T &acc, T x, T y, T c, T o, T q) {
+__device__ __forceinline__ void bwd_accumulate(T &acc, T x, T y, T c, T o, T q, int pspec) {
     if (PHI == PHI_Y) {
         acc = b_fma(c, y, acc);
         return;
@@ -99,9 +100,9 @@ __device__ __forceinline__ void bwd_accumulate(T &acc, T x, T y, T c, T o, T q) 
     } else if (PHI == PHI_SGN) {
         if (d != T(0)) acc += b_copysign_of(c, d);
     } else if (PHI == PHI_SGNPOW) {
-        acc = b_fma(c, b_copysign(b_powabs(b_abs(d), q), d), acc);
+        acc = b_fma(c, b_copysign(pow_abs_spec(b_abs(d), q, pspec), d), acc);
     } else if (PHI == PHI_ABSPOW) {
-        acc = b_fma(c, b_powabs(b_abs(d), q), acc);
+        acc = b_fma(c, pow_abs_spec(b_abs(d), q, pspec), acc);
     } else if (PHI == PHI_SGN_EQ) {
         // c is already zero where o == 0, and |d| == o > 0 implies d != 0
         if (b_abs(d) == o) acc += b_copysign_of(c, d);
@@ -206,6 +207,7 @@ lp_backward_kernel(const __grid_constant__ CUtensorMap map_stream, const __grid_
     }
 
     const T q = (T)P.q;
+    const int pspec = P.pow_spec;
     int failed = 0;
 
     for (int t = 0; t < nchunks; ++t) {
@@ -289,7 +291,7 @@ lp_backward_kernel(const __grid_constant__ CUtensorMap map_stream, const __grid_
                     const T c = TRANS ? ct[a] : cv[a][u];
                     const T o = AUX_IN_LOOP ? (TRANS ? ot[a] : ov[a][u]) : T(0);
 #pragma unroll
-                    for (int kk = 0; kk < RK; ++kk) bwd_accumulate<PHI, T>(acc[a][kk], xr[a][kk], yv[kk], c, o, q);
+                    for (int kk = 0; kk < RK; ++kk) bwd_accumulate<PHI, T>(acc[a][kk], xr[a][kk], yv[kk], c, o, q, pspec);
                 }
             }
         }
@@ -393,6 +395,7 @@ int lp_backward_typed(int mode, BwdParams P, const void *x1, const void *x2, voi
                       cudaStream_t stream) {
     P.post = 1.0;
     P.q = p - 1.0;
+    P.pow_spec = make_pow_spec(P.q);
     P.coef_mode = COEF_G;
     switch (mode) {
         case TPW_LP_BWD_MATMUL:
@@ -521,7 +524,7 @@ extern "C" int tpw_wminkowski_backward_w(int dtype, const void *grad, const void
     memset(&P, 0, sizeof(P));
     P.grad = grad; P.aux = aux; P.w = nullptr;
     P.B = B; P.N1 = N1; P.N2 = N2; P.D = D;
-    P.post = 1.0; P.q = p; P.coef_mode = COEF_MUL;
+    P.post = 1.0; P.q = p; P.pow_spec = make_pow_spec(p); P.coef_mode = COEF_MUL;
     int st = dtype == TPW_F32 ? launch_side<float, PHI_ABSPOW, true>(P, false, x1, x2, scratch, s)
                               : launch_side<double, PHI_ABSPOW, true>(P, false, x1, x2, scratch, s);
     if (st != TPW_OK) return st;

@@ -27,6 +27,7 @@ struct FwdParams {
     long long B, N1, N2, D;
     long long tiles_i, tiles_j;
     double p;            // exponent of K_PGEN
+    int pow_spec;        // make_pow_spec(p): how the float kernel evaluates |d|^p
     double out_exponent; // finite kinds: out = sum ^ out_exponent
     int root_mode;       // 0 none, 1 sqrt, 2 cbrt, 3 pow(out_exponent)
     int epilogue;        // K_DOT: tpw_dot_epilogue; K_NE*: bit0 = report equal count, bit1 = mean
@@ -72,7 +73,7 @@ __device__ __forceinline__ bool bits_differ(double a, double b) {
 }
 
 template <int KIND, bool WEIGHTED, typename T>
-__device__ __forceinline__ void accumulate(T &acc, T x, T y, T w, T p) {
+__device__ __forceinline__ void accumulate(T &acc, T x, T y, T w, T p, int pspec) {
     if (KIND == K_DOT) {
         acc = t_fma(x, y, acc);
     } else if (KIND == K_NE) {
@@ -89,7 +90,7 @@ __device__ __forceinline__ void accumulate(T &acc, T x, T y, T w, T p) {
             T a = t_abs(d);
             acc = WEIGHTED ? t_fma(a * a, a * w, acc) : t_fma(a * a, a, acc);
         } else if (KIND == K_PGEN) {
-            T t = t_powabs(t_abs(d), p);
+            T t = pow_abs_spec(t_abs(d), p, pspec);
             acc = WEIGHTED ? t_fma(t, w, acc) : acc + t;
         } else if (KIND == K_MAX) {
             acc = t_max(acc, WEIGHTED ? t_abs(d) * w : t_abs(d));
@@ -247,6 +248,7 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
     }
 
     const T pexp = (T)P.p;
+    const int pspec = P.pow_spec;
     int failed = 0;
 
     for (int t = 0; t < nchunks; ++t) {
@@ -315,9 +317,9 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
                     for (int e = 0; e < VN; ++e) {
                         if (KIND == K_MIN) {
                             // zero padding beyond D must not win the minimum
-                            if (kbase + c * VN + e < P.D) accumulate<KIND, WEIGHTED, T>(acc[ri][rj], xe[e], ye[e], wv[e], pexp);
+                            if (kbase + c * VN + e < P.D) accumulate<KIND, WEIGHTED, T>(acc[ri][rj], xe[e], ye[e], wv[e], pexp, pspec);
                         } else {
-                            accumulate<KIND, WEIGHTED, T>(acc[ri][rj], xe[e], ye[e], wv[e], pexp);
+                            accumulate<KIND, WEIGHTED, T>(acc[ri][rj], xe[e], ye[e], wv[e], pexp, pspec);
                         }
                     }
                 }
@@ -512,6 +514,7 @@ int launch_forward_w(const FwdParams &P, cudaStream_t stream) {
 template <typename T, int EPI = EPI_STORE>
 int lp_forward_typed(FwdParams P, double p, double out_exponent, cudaStream_t stream) {
     P.p = p;
+    P.pow_spec = make_pow_spec(p);
     P.out_exponent = out_exponent;
     if (isinf(p)) {
         if constexpr (EPI == EPI_STORE) {

@@ -436,6 +436,23 @@ def run_suite(args):
                 out.backward(G, retain_graph=True)
             entry(name + "_bwd", n, timeit(bwd), "fp32_issue", n * 256 * bo, fp32_peak, 0)
             del out
+    # weighted Minkowski p = 3 at C2 (w [16,256]): forward, and backward including grad_w
+    if want("C2_wminkowski_p3_fwd") or want("C2_wminkowski_p3_bwd"):
+        W = (torch.rand(args.batches, 256, generator=g) + 0.5).to(dev).requires_grad_(True)
+        if want("C2_wminkowski_p3_fwd"):
+            with torch.no_grad():
+                entry("C2_wminkowski_p3_fwd", n, timeit(lambda: tpw.wminkowski_distances(X, Y, 3.0, W)), "fp32_issue", n * 256 * 3, fp32_peak, 4 * n)
+        if want("C2_wminkowski_p3_bwd"):
+            out = tpw.wminkowski_distances(X, Y, 3.0, W)
+
+            def bwdw():
+                X.grad = None
+                Y.grad = None
+                W.grad = None
+                out.backward(G, retain_graph=True)
+            entry("C2_wminkowski_p3_bwd", n, timeit(bwdw), "fp32_issue (coefficient forward + grad_x1, grad_x2, grad_w passes)", n * 256 * (3 + 4 + 4 + 4), fp32_peak, 0)
+            del out
+        del W
     # dense-contraction backward at C2: two tf32x3 tensor-core products per call (executed flops = 3 x 4 n D);
     # the tf32 rate is taken as half of the measured sustained bf16 rate
     for name, fn in (("C2_sqeuclidean_bwd", tpw.sqeuclidean_distances), ("C2_euclidean_bwd", tpw.euclidean_distances),

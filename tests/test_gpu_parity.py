@@ -829,7 +829,7 @@ def test_bounded_wait_reports_instead_of_hanging(tpw):
     code = tpw.device_status()  # synchronises, reads and clears
     dt = time.perf_counter() - t0
     assert code == (15 << 16) | 1
-    assert 0.04 < dt < 1.0, dt
+    assert 0.04 < dt < 5.0, dt   # 50 ms of waiting plus launch, module load and the status read-back
     assert tpw.device_status() == 0  # cleared
     x = torch.randn(64, 32, device="cuda")
     assert torch.isfinite(tpw.euclidean_distances(x)).all()  # the context still works

@@ -539,6 +539,15 @@ def run_suite(args):
     if want("OB_cosine_D64_tensor"):
         entry("OB_cosine_D64_tensor", n, timeit(lambda: tpw.cosine_distances(X, Y)), "hbm (output write)", 4 * n / 1e9, hbm_peak, 4 * n)
     del X, Y, Xb, Yb
+    # ---- condensed self-distances: X[32768,256], 537 M pairs (i < j), against the full 1.07 G-pair matrix ----
+    if want("PD_manhattan_pdist") or want("PD_manhattan_cdist_self"):
+        Xp = torch.randn(32768, 256, generator=g).to(dev)
+        npairs = 32768 * 32767 // 2
+        if want("PD_manhattan_pdist"):
+            entry("PD_manhattan_pdist", npairs, timeit(lambda: tpw.pdist(Xp, "manhattan")), "fp32_issue (pairs i < j only)", npairs * 256 * 2, fp32_peak, 4 * npairs)
+        if want("PD_manhattan_cdist_self"):
+            entry("PD_manhattan_cdist_self", 32768 * 32768, timeit(lambda: tpw.manhattan_distances(Xp)), "fp32_issue", 32768 * 32768 * 256 * 2, fp32_peak, 4 * 32768 * 32768)
+        del Xp
     # ---- C5: point clouds [64,1,8192,3] ------------------------------------------------------------------
     P_ = torch.rand(64, 8192, 3, generator=g) * 2 - 1
     Q_ = P_ + 0.05 * torch.randn(64, 8192, 3, generator=g)

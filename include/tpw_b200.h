@@ -122,6 +122,16 @@ TPW_API int tpw_lp_radius_mask_forward(int dtype, const void *x1, const void *x2
                                int64_t B, int64_t N1, int64_t N2, int64_t D,
                                double p, double out_exponent, double radius, tpw_stream_t stream);
 
+/*
+ * Condensed self-distances: out[b, i (2N - i - 1) / 2 + (j - i - 1)] = d(x[b,i], x[b,j]) for i < j, i.e.
+ * the upper triangle of tpw_lp_forward(x, x) row by row, [B, N (N - 1) / 2].  Tiles on or below the
+ * diagonal are skipped, so about half of the pairs are evaluated.  Finite p > 0 or p = +inf.
+ * The reference declares pdist and raises "yet to be implemented" (OPS/cpdist.cpp:233-246); its README
+ * defines it as cdist(x, x) without the duplicated positions.
+ */
+TPW_API int tpw_lp_pdist_forward(int dtype, const void *x, void *out, int64_t B, int64_t N, int64_t D,
+                         double p, double out_exponent, tpw_stream_t stream);
+
 enum tpw_lp_backward_mode {
     /* ATen cdist backward: aux = forward output o.  p=1: g*sgn(d); p=2: g*d/o;
        other finite p: g*d*|d|^(p-2)/o^(p-1); +inf: g*sgn(d)*[|d|==o]; all 0 where o==0.

@@ -285,8 +285,8 @@ def test_cdist_dispatcher(tpw):
         tpw.cdist(x1, x2, "euclidean", p=3.0)
     with pytest.raises(RuntimeError, match="unkown distance metric"):
         tpw.cdist(x1, x2, "nope")
-    with pytest.raises(NotImplementedError):
-        tpw.pdist(x1)
+    with pytest.raises(NotImplementedError, match="outside"):
+        tpw.pdist(x1, "canberra")
 
 
 def test_gradcheck_float64(tpw):
@@ -816,6 +816,50 @@ def test_radius_mask_fused_equals_compare_pass(tpw, shapes):
     assert torch.equal(tpw.radius_neighbors_mask(a, None, 0.0, "manhattan").diagonal(dim1=-2, dim2=-1).all(), torch.tensor(True, device="cuda"))
     with pytest.raises(RuntimeError, match="non-negative"):
         tpw.radius_neighbors_mask(a, b, -1.0)
+
+
+@pytest.mark.parametrize("n,d", [(2, 3), (5, 1), (129, 7), (300, 64), (515, 33)])
+def test_pdist_condensed(tpw, n, d):
+    """pdist against scipy.spatial.distance.pdist (the layout and the definitions the reference's README
+    points to) in float64, the fused condensed kernel against the gathered triangle of cdist in float32,
+    batched inputs, and the gradient through the composition path."""
+    from scipy.spatial.distance import pdist as sp_pdist
+    rng = np.random.default_rng(n * 1000 + d)
+    xn = rng.standard_normal((n, d))
+    x64 = cuda(xn)
+    m = n * (n - 1) // 2
+    for metric, kw, sp_metric, sp_kw in (("euclidean", {}, "euclidean", {}), ("sqeuclidean", {}, "sqeuclidean", {}),
+                                         ("cityblock", {}, "cityblock", {}), ("chebyshev", {}, "chebyshev", {}),
+                                         ("minkowski", {"p": 3.0}, "minkowski", {"p": 3.0}),
+                                         ("minkowski", {"p": 1.5}, "minkowski", {"p": 1.5}),
+                                         ("cosine", {}, "cosine", {}), ("correlation", {}, "correlation", {})):
+        if metric == "correlation" and d < 2:
+            continue
+        got = tpw.pdist(x64, metric, **kw)
+        assert got.shape == (m,) and got.dtype == torch.float64
+        close(got, sp_pdist(xn, sp_metric, **sp_kw), TOL[torch.float64] if metric not in ("cosine", "correlation") else dict(rtol=1e-9, atol=1e-9),
+              msg=f"pdist {metric}")
+        x32 = x64.float()
+        iu = torch.triu_indices(n, n, offset=1, device="cuda")
+        tri = tpw.cdist(x32, x32, metric, **kw)[iu[0], iu[1]]
+        fused = tpw.pdist(x32, metric, **kw)
+        if metric in ("cosine", "correlation"):
+            assert torch.equal(fused, tri)
+        else:
+            close(fused, tri.cpu().numpy(), TOL[torch.float32], msg=f"pdist {metric} float32")
+    xb = cuda(rng.standard_normal((3, n, d)).astype(np.float32))
+    pb = tpw.pdist(xb, "manhattan")
+    assert pb.shape == (3, m)
+    for b in range(3):
+        assert torch.equal(pb[b], tpw.pdist(xb[b], "manhattan"))
+    xb_bool = cuda(rng.random((n, max(d, 8))) < 0.4)
+    close(tpw.pdist(xb_bool, "jaccard").double(), sp_pdist(xb_bool.cpu().numpy(), "jaccard"), dict(rtol=1e-6, atol=1e-7), msg="pdist jaccard")
+    if n > 2:
+        xg = cuda(xn.astype(np.float32), True)
+        tpw.pdist(xg, "euclidean").sum().backward()
+        xr = torch.from_numpy(xn.astype(np.float32)).requires_grad_(True)
+        torch.nn.functional.pdist(xr).sum().backward()
+        close(xg.grad, xr.grad.numpy(), TOL[torch.float32], 10, "pdist gradient")
 
 
 def test_bounded_wait_reports_instead_of_hanging(tpw):

@@ -55,7 +55,12 @@ def test_cdist_keyword_validation():
         tpw.cdist(x, x, "foo")
     with pytest.raises(NotImplementedError, match="outside"):
         tpw.cdist(x, x, "canberra")
-    with pytest.raises(NotImplementedError, match="pdist is yet to be implemented"):
+    # pdist validates like cdist, then needs a CUDA tensor (the reference only has a stub that raises)
+    with pytest.raises(TypeError, match="incompatible arguments p"):
+        tpw.pdist(x, "euclidean", p=2.0)
+    with pytest.raises(RuntimeError, match="Got unkown distance metric: foo"):
+        tpw.pdist(x, "foo")
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
         tpw.pdist(x)
     # valid keywords get past validation and then hit the device check
     with pytest.raises(RuntimeError, match="CUDA tensors only"):

@@ -42,6 +42,7 @@ SIGNATURES = {
     "tpw_lp_rowmin_scratch_bytes": (_L, [_L, _L]),
     "tpw_lp_rowmin_forward": (_I, [_I, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _D, _D, _P]),
     "tpw_lp_radius_mask_forward": (_I, [_I, _P, _P, _P, _P, _L, _L, _L, _L, _D, _D, _D, _P]),
+    "tpw_lp_pdist_forward": (_I, [_I, _P, _P, _L, _L, _L, _D, _D, _P]),
     "tpw_lp_backward": (_I, [_I, _I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _D, _P]),
     "tpw_wminkowski_backward_w": (_I, [_I, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _D, _P]),
     "tpw_lp_inf_backward": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _P]),

@@ -4,13 +4,15 @@ Same metric names, the same per-metric keyword validation (a keyword the metric 
 raises ``TypeError`` naming it, OPS/cpdist.cpp:35-79), the same defaults (``p`` defaults to 2) and
 the same quirk that ``metric="kulsinski"`` evaluates kulczynski1 (the inline helper at
 OPS/pairwise_metrics.h:557-561 calls that functor).  Metrics outside the accelerated path raise
-``NotImplementedError``; ``pdist`` raises it for everything, as the reference does
-(OPS/cpdist.cpp:233-246).
+``NotImplementedError``.  ``pdist``, which the reference declares but does not implement
+(OPS/cpdist.cpp:233-246), is the condensed form of ``cdist(x, x)``.
 """
 from __future__ import annotations
 
+import math
 from typing import Optional
 
+import torch
 from torch import Tensor
 
 from . import ops
@@ -80,5 +82,41 @@ def cdist(x1: Tensor, x2: Tensor, metric: str = "minkowski", *, w: Optional[Tens
     return getattr(ops, f"{metric}_distances")(x1, x2)
 
 
-def pdist(input: Tensor, metric: str = "minkowski", **kwargs) -> Tensor:
-    raise NotImplementedError("pdist is yet to be implemented.")
+def pdist(input: Tensor, metric: str = "minkowski", *, w: Optional[Tensor] = None, V: Optional[Tensor] = None,
+          VI: Optional[Tensor] = None, p: Optional[float] = None, base: Optional[float] = None,
+          shuffle: Optional[bool] = None, generator=None) -> Tensor:
+    """Condensed self-distances of ``input`` [N, D] (or [B, N, D]): the upper triangle of
+    ``cdist(input, input, metric)`` row by row, shape [.., N (N - 1) / 2], the layout of ``torch.pdist``
+    and ``scipy.spatial.distance.pdist``.
+
+    The reference declares this function with the arguments of ``cdist`` and raises "pdist is yet to be
+    implemented" (OPS/cpdist.cpp:233-246); its README defines it as ``cdist(x1, x1)`` without the
+    duplicated positions.  The L_p metrics run the tile kernel with a condensed epilogue that skips the
+    tiles on or below the diagonal (about half of the pairs are evaluated) when no gradient is needed;
+    everything else, and every differentiable call, evaluates ``cdist`` and gathers the triangle."""
+    from .ops import _FLOAT_CODES, _ROWMIN_METRICS, _abi, _ptr, _require_cuda, _stream, check, lib  # noqa: F401
+    if metric not in SUPPORTED_METRICS:
+        raise RuntimeError(f"Got unkown distance metric: {metric}. Supported metrics are [{', '.join(SUPPORTED_METRICS)}]")
+    _check_extra_args(metric, w=w, V=V, VI=VI, p=p, base=base, shuffle=shuffle, generator=generator)
+    if input.dim() not in (2, 3):
+        raise RuntimeError("input must be 2D tensor (unbatched) or 3D tensor (batched)")
+    _require_cuda(input)
+    n = input.size(-2)
+    fused = (metric in _ROWMIN_METRICS and w is None and input.dtype in _FLOAT_CODES and input.size(-1) > 0
+             and not (input.requires_grad and torch.is_grad_enabled()))
+    if fused:
+        pp, ex = _ROWMIN_METRICS[metric]
+        if pp is None:
+            pp = 2.0 if p is None else float(p)
+            ex = 1.0 if math.isinf(pp) else (1.0 / pp if pp > 0 else None)
+        if ex is not None:
+            xc = input.contiguous()
+            xb = xc if xc.dim() == 3 else xc.unsqueeze(0)
+            out = torch.empty((xb.size(0), n * (n - 1) // 2), dtype=xb.dtype, device=xb.device)
+            with torch.cuda.device(xb.device):
+                check(lib.tpw_lp_pdist_forward(_FLOAT_CODES[xb.dtype], _ptr(xb), _ptr(out), xb.size(0), n, xb.size(2),
+                                               pp, ex, _stream(xb)), "tpw_lp_pdist_forward")
+            return out if input.dim() == 3 else out.squeeze(0)
+    full = cdist(input, input, metric, w=w, V=V, VI=VI, p=p, base=base, shuffle=shuffle, generator=generator)
+    iu = torch.triu_indices(n, n, offset=1, device=input.device)
+    return full[..., iu[0], iu[1]]

@@ -81,3 +81,19 @@ extern "C" int tpw_lp_radius_mask_forward(int dtype, const void *x1, const void 
     return dtype == TPW_F32 ? lp_forward_typed<float, EPI_MASK>(P, p, out_exponent, s) : lp_forward_typed<double, EPI_MASK>(P, p, out_exponent, s);
 }
 
+extern "C" int tpw_lp_pdist_forward(int dtype, const void *x, void *out, int64_t B, int64_t N, int64_t D,
+                                    double p, double out_exponent, tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(dtype == TPW_F32 || dtype == TPW_F64, "tpw_lp_pdist_forward: dtype must be TPW_F32 or TPW_F64");
+    TPW_CHECK_ARG(B >= 0 && N >= 0 && D >= 0, "tpw_lp_pdist_forward: negative size");
+    if (B == 0 || N < 2) return TPW_OK;
+    TPW_CHECK_ARG(x && out, "tpw_lp_pdist_forward: NULL pointer");
+    TPW_CHECK_ARG(D > 0, "tpw_lp_pdist_forward: D must be positive");
+    TPW_CHECK_ARG(p > 0 && !isnan(p) && !isnan(out_exponent), "tpw_lp_pdist_forward: p must be positive (got %g)", p);
+    FwdParams P;
+    memset(&P, 0, sizeof(P));
+    P.x1 = x; P.x2 = x; P.w = nullptr; P.out = out;
+    P.B = B; P.N1 = N; P.N2 = N; P.D = D;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return dtype == TPW_F32 ? lp_forward_typed<float, EPI_PDIST>(P, p, out_exponent, s) : lp_forward_typed<double, EPI_PDIST>(P, p, out_exponent, s);
+}

@@ -153,7 +153,7 @@ __device__ __forceinline__ void apply_root(T (&acc)[R][R], const FwdParams &P) {
 }
 
 // what the epilogue does with a finished tile
-enum { EPI_STORE = 0, EPI_ROWMIN = 1, EPI_MASK = 2 };
+enum { EPI_STORE = 0, EPI_ROWMIN = 1, EPI_MASK = 2, EPI_PDIST = 3 };
 
 constexpr int kThreads = 256;
 constexpr int kStages = 3;
@@ -209,6 +209,11 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
     const long long tix = tile % P.tiles_i;
     const long long b = tile / P.tiles_i;
     const long long i0 = tix * TILE, j0 = tjx * TILE;
+
+    if constexpr (EPI == EPI_PDIST) {
+        // condensed self-distances: only pairs j > i are wanted, tiles that hold none do no work at all
+        if (j0 + TILE - 1 <= i0) return;
+    }
 
     const T *x1 = reinterpret_cast<const T *>(P.x1) + b * P.N1 * P.D;
     const T *x2 = reinterpret_cast<const T *>(P.x2) + b * P.N2 * P.D;
@@ -417,6 +422,24 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
             }
             return;
         }
+    }
+
+    if constexpr (EPI == EPI_PDIST) {
+        // row i of the condensed layout starts at i (2N - i - 1) / 2 and holds j = i + 1 .. N - 1
+        const long long N = P.N1;
+        OutT *cond = reinterpret_cast<OutT *>(P.out) + b * (N * (N - 1) / 2);
+#pragma unroll
+        for (int ri = 0; ri < R; ++ri) {
+            const long long i = i0 + ti + 16 * ri;
+            if (i >= N) continue;
+            OutT *crow = cond + i * (2 * N - i - 1) / 2 - i - 1;
+#pragma unroll
+            for (int rj = 0; rj < R; ++rj) {
+                const long long j = j0 + tj + 16 * rj;
+                if (j > i && j < N) crow[j] = finish<T, OutT, KIND>(acc[ri][rj], T(0), T(0), P);
+            }
+        }
+        return;
     }
 
     OutT *out = reinterpret_cast<OutT *>(P.out) + b * P.N1 * P.N2;

@@ -294,6 +294,40 @@ def seuclidean(x1, x2, V):
     return wminkowski(x1, x2, w, 2.0)
 
 
+def braycurtis(x1, x2):
+    """sum_k |x1 - x2| / sum_k |x1 + x2| (OPS/cpu/braycurtis_kernel.cpp:22-27; 0/0 is NaN as there)."""
+    a, ub = _b3(x1)
+    b, _ = _b3(x2)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        out = np.abs(_diff(a, b)).sum(-1) / np.abs(a[:, :, None, :] + b[:, None, :, :]).sum(-1)
+    return _un(out.astype(a.dtype), ub)
+
+
+def snr_distances(x1, x2):
+    """1 / _snr with _snr = D var(x1 row, population) / sum_k (e_k - mean(e))^2, e = x2 - x1
+    (OPS/cpu/snr_kernel.cpp:22-34,96; OPS/pairwise_metrics.cpp:407)."""
+    a, ub = _b3(x1)
+    b, _ = _b3(x2)
+    e = -_diff(a, b)
+    diff_var = ((e - e.mean(-1, keepdims=True)) ** 2).sum(-1)
+    x1_var = ((a - a.mean(-1, keepdims=True)) ** 2).sum(-1)[:, :, None]
+    with np.errstate(divide="ignore", invalid="ignore"):
+        out = 1.0 / (x1_var / diff_var)
+    return _un(out.astype(a.dtype), ub)
+
+
+def mahalanobis(x1, x2, VI):
+    """sqrt(sum_kl d_k VI[k,l] d_l) (OPS/cpu/sqmahalanobis_kernel.cpp:23-31; sqrt at
+    OPS/pairwise_metrics.cpp:296).  VI [D,D] or [B,D,D], not assumed symmetric."""
+    a, ub = _b3(x1)
+    b, _ = _b3(x2)
+    V = np.asarray(VI)
+    V = V[None] if V.ndim == 2 else V
+    d = _diff(a, b)
+    out = np.sqrt(np.einsum("bijk,bkl,bijl->bij", d, V, d))
+    return _un(out.astype(a.dtype), ub)
+
+
 def k_neighbors_mask(dists, k):
     """True at the k + 1 smallest entries of every row (OPS/neighbors.cpp:29-33)."""
     d = np.asarray(dists)

@@ -7,7 +7,8 @@ except for the config-shaped cases whose inputs are regenerated from the seed (t
 checksum is stored so that a generator drift is detected rather than mis-reported as a parity
 failure).
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py            # everything
+    python tests/golden/make_golden.py composed   # one file
 """
 from __future__ import annotations
 
@@ -163,10 +164,49 @@ def extras_golden():
     print("extras.npz", len(out), "arrays")
 
 
+def composed_golden():
+    """braycurtis, snr and mahalanobis: reference kernels of their own (OPS/cpu/braycurtis_kernel.cpp,
+    snr_kernel.cpp, sqmahalanobis_kernel.cpp) that the B200 build states as compositions of the
+    path's kernels.  Unbatched and batched inputs, float32 and float64, forward and gradients."""
+    out = {}
+    g = torch.Generator().manual_seed(57)
+    for tag, s1, s2, dt in (("u32", (14, 6), (9, 6), torch.float32), ("b64", (2, 7, 5), (2, 8, 5), torch.float64)):
+        x1, x2 = torch.randn(*s1, generator=g, dtype=dt), torch.randn(*s2, generator=g, dtype=dt)
+        d = s1[-1]
+        A = torch.randn(*s1[:-2], d, d, generator=g, dtype=dt)
+        VI = A @ A.transpose(-1, -2) / d + 0.5 * torch.eye(d, dtype=dt) + 0.1 * torch.randn(*s1[:-2], d, d, generator=g, dtype=dt)
+        up = torch.randn(*s1[:-1], s2[-2], generator=g, dtype=dt)
+        ups = torch.randn(*s1[:-1], s1[-2], generator=g, dtype=dt)
+        out[f"{tag}/x1"], out[f"{tag}/x2"], out[f"{tag}/VI"], out[f"{tag}/up"], out[f"{tag}/ups"] = npy(x1), npy(x2), npy(VI), npy(up), npy(ups)
+        for name in ("braycurtis_distances", "snr_distances"):
+            a, b = x1.clone().requires_grad_(True), x2.clone().requires_grad_(True)
+            r = getattr(T, name)(a, b)
+            r.backward(up)
+            out[f"{tag}/{name}/out"], out[f"{tag}/{name}/gx1"], out[f"{tag}/{name}/gx2"] = npy(r), npy(a.grad), npy(b.grad)
+            a = x1.clone().requires_grad_(True)
+            r = getattr(T, name)(a, None)
+            out[f"{tag}/{name}/self_out"] = npy(r)
+        a, b, v = x1.clone().requires_grad_(True), x2.clone().requires_grad_(True), VI.clone().requires_grad_(True)
+        r = T.mahalanobis_distances(a, b, v)
+        r.backward(up)
+        out[f"{tag}/mahalanobis_distances/out"] = npy(r)
+        out[f"{tag}/mahalanobis_distances/gx1"], out[f"{tag}/mahalanobis_distances/gx2"] = npy(a.grad), npy(b.grad)
+        out[f"{tag}/mahalanobis_distances/gVI"] = npy(v.grad)
+        if len(s1) == 2:
+            out[f"{tag}/cdist_braycurtis"] = npy(T.cdist(x1, x2, "braycurtis"))
+            out[f"{tag}/cdist_snr"] = npy(T.cdist(x1, x2, "snr"))
+            out[f"{tag}/cdist_mahalanobis"] = npy(T.cdist(x1, x2, "mahalanobis", VI=VI))
+            big = torch.randn(40, 6, generator=g, dtype=dt)
+            out[f"{tag}/big"] = npy(big)
+            out[f"{tag}/mahalanobis_default_VI"] = npy(T.mahalanobis_distances(big, None, None))
+    np.savez_compressed(HERE / "composed.npz", **out)
+    print("composed.npz", len(out), "arrays")
+
+
 if __name__ == "__main__":
     torch.set_num_threads(8)
-    float_golden()
-    bool_golden()
-    hausdorff_golden()
-    config_golden()
-    extras_golden()
+    which = set(sys.argv[1:])
+    for name, fn in (("float", float_golden), ("bool", bool_golden), ("hausdorff", hausdorff_golden), ("configs", config_golden),
+                     ("extras", extras_golden), ("composed", composed_golden)):
+        if not which or name in which:
+            fn()

@@ -862,6 +862,41 @@ def test_pdist_condensed(tpw, n, d):
         close(xg.grad, xr.grad.numpy(), TOL[torch.float32], 10, "pdist gradient")
 
 
+@pytest.mark.parametrize("tag", ["u32", "b64"])
+def test_composed_metrics_golden(tpw, golden, tag):
+    """braycurtis, snr and mahalanobis (reference kernels of their own, stated here as compositions of the
+    path's kernels) against the reference's outputs and gradients."""
+    G = golden("composed")
+    dt = torch.float32 if tag == "u32" else torch.float64
+    tol = TOL[dt]
+    up, VI = cuda(G[f"{tag}/up"]), cuda(G[f"{tag}/VI"])
+    for name in ("braycurtis_distances", "snr_distances"):
+        x1, x2 = cuda(G[f"{tag}/x1"], True), cuda(G[f"{tag}/x2"], True)
+        out = getattr(tpw, name)(x1, x2)
+        close(out, G[f"{tag}/{name}/out"], tol, msg=name)
+        out.backward(up)
+        close(x1.grad, G[f"{tag}/{name}/gx1"], tol, 10, name + " grad_x1")
+        close(x2.grad, G[f"{tag}/{name}/gx2"], tol, 10, name + " grad_x2")
+        close(getattr(tpw, name)(x1.detach()), G[f"{tag}/{name}/self_out"], tol, 10, name + " self")
+    x1, x2, v = cuda(G[f"{tag}/x1"], True), cuda(G[f"{tag}/x2"], True), VI.clone().requires_grad_(True)
+    out = tpw.mahalanobis_distances(x1, x2, v)
+    close(out, G[f"{tag}/mahalanobis_distances/out"], tol, 10, "mahalanobis")
+    out.backward(up)
+    close(x1.grad, G[f"{tag}/mahalanobis_distances/gx1"], tol, 100, "mahalanobis grad_x1")
+    close(x2.grad, G[f"{tag}/mahalanobis_distances/gx2"], tol, 100, "mahalanobis grad_x2")
+    close(v.grad, G[f"{tag}/mahalanobis_distances/gVI"], tol, 100, "mahalanobis grad_VI")
+    if tag == "u32":
+        a, b = x1.detach(), x2.detach()
+        close(tpw.cdist(a, b, "braycurtis"), G["u32/cdist_braycurtis"], tol, msg="cdist braycurtis")
+        close(tpw.cdist(a, b, "snr"), G["u32/cdist_snr"], tol, msg="cdist snr")
+        close(tpw.cdist(a, b, "mahalanobis", VI=VI), G["u32/cdist_mahalanobis"], tol, 10, "cdist mahalanobis")
+        big = cuda(G["u32/big"])
+        got = tpw.mahalanobis_distances(big)
+        torch.testing.assert_close(got.cpu(), torch.from_numpy(G["u32/mahalanobis_default_VI"]), rtol=1e-3, atol=3e-3)
+        with pytest.raises(RuntimeError, match="VI is required"):
+            tpw.mahalanobis_distances(a, b)
+
+
 def test_bounded_wait_reports_instead_of_hanging(tpw):
     """A wait that can never complete gives up after its budget, leaves a code in the device status
     word and leaves the context usable (no trap, no fault, no endless loop)."""

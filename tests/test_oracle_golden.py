@@ -126,3 +126,20 @@ def test_extras_match_reference(golden):
     np.testing.assert_array_equal(O.k_neighbors_mask(O.cdist(x1, x1, 1.0), 2), G["k_neighbors_self_k2_manhattan"])
     np.testing.assert_array_equal(O.cdist(x1, x2, 2.0) <= 2.5, G["radius_2.5"])
     np.testing.assert_array_equal(O.cdist(x1, x1, 3.0) <= 3.0, G["radius_self_3_minkowski3"])
+
+
+def test_composed_metrics_match_reference(golden):
+    """braycurtis, snr, mahalanobis: the numpy restatements against the reference's own kernels."""
+    G = golden("composed")
+    for tag in ("u32", "b64"):
+        x1, x2, VI = G[f"{tag}/x1"], G[f"{tag}/x2"], G[f"{tag}/VI"]
+        tol = TOL[x1.dtype]
+        np.testing.assert_allclose(O.braycurtis(x1, x2), G[f"{tag}/braycurtis_distances/out"], **tol)
+        np.testing.assert_allclose(O.braycurtis(x1, x1), G[f"{tag}/braycurtis_distances/self_out"], **tol)
+        np.testing.assert_allclose(O.snr_distances(x1, x2), G[f"{tag}/snr_distances/out"], **tol)
+        np.testing.assert_allclose(O.snr_distances(x1, x1), G[f"{tag}/snr_distances/self_out"], **tol)
+        np.testing.assert_allclose(O.mahalanobis(x1, x2, VI), G[f"{tag}/mahalanobis_distances/out"], **tol)
+    np.testing.assert_allclose(O.braycurtis(G["u32/x1"], G["u32/x2"]), G["u32/cdist_braycurtis"], **TOL[np.dtype("float32")])
+    big = G["u32/big"]
+    VI = np.linalg.inv(np.cov(big.T.astype(np.float64))).T
+    np.testing.assert_allclose(O.mahalanobis(big.astype(np.float64), big.astype(np.float64), VI), G["u32/mahalanobis_default_VI"], rtol=1e-3, atol=2e-3)

@@ -10,6 +10,7 @@ from .ops import (
     _directed_hausdorff,
     _ppminkowski,
     _wminkowski,
+    braycurtis_distances,
     chebyshev_distances,
     cityblock_distances,
     correlation_distances,
@@ -30,6 +31,7 @@ from .ops import (
     linear_kernel,
     linf_distances,
     lp_distances,
+    mahalanobis_distances,
     manhattan_distances,
     minkowski_distances,
     pairwise_argkmin,
@@ -50,6 +52,7 @@ from .ops import (
     set_dot_engine,
     seuclidean_distances,
     sigmoid_kernel,
+    snr_distances,
     sokalmichener_distances,
     sokalsneath_distances,
     sqeuclidean_distances,

@@ -44,7 +44,7 @@ _SCHEMAS = {
                           "-> (Tensor output, Tensor x1_indices, Tensor x2_indices)",
 }
 
-_OUT_OF_SCOPE = {"braycurtis", "canberra", "haversine", "jensenshannon", "mahalanobis", "snr"}
+_OUT_OF_SCOPE = {"canberra", "haversine", "jensenshannon"}
 
 
 def _check_extra_args(metric: str, **given) -> None:
@@ -75,6 +75,8 @@ def cdist(x1: Tensor, x2: Tensor, metric: str = "minkowski", *, w: Optional[Tens
         return ops.wminkowski_distances(x1, x2, 2.0 if p is None else p, w)
     if metric == "seuclidean":
         return ops.seuclidean_distances(x1, x2, V)
+    if metric == "mahalanobis":
+        return ops.mahalanobis_distances(x1, x2, VI)
     if metric == "kulsinski":
         return ops.kulczynski1_distances(x1, x2)
     if metric == "cosine":

@@ -963,6 +963,48 @@ def seuclidean_distances(x1: Tensor, x2: Optional[Tensor] = None, V: Optional[Te
     return _wminkowski(x1_, x2_, w, 2.0)
 
 
+def braycurtis_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    """sum_k |x1 - x2| / sum_k |x1 + x2| (the reference's own kernel, OPS/cpu/braycurtis_kernel.cpp:22-27,
+    called at OPS/pairwise_metrics.cpp:308-315): two passes of the L1 tile kernel, the second against
+    -x2, and a plain division (0/0 is NaN as in the reference); differentiable through both passes."""
+    x1_, x2_ = check_pairwise_inputs("braycurtis_distances", x1, x2)
+    _require_cuda(x1_, x2_)
+    return _cdist_p(x1_, x2_, 1.0) / _cdist_p(x1_, -x2_, 1.0)
+
+
+def snr_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    """1 / _snr = sum_k (e_k - mean e)^2 / sum_k (x1_k - mean x1)^2 with e = x2 - x1 (OPS/pairwise_metrics.cpp:401-408,
+    OPS/cpu/snr_kernel.cpp:22-34,96).  sum_k (e_k - mean e)^2 = |x1 - x2|^2 - (sum x2 - sum x1)^2 / D: the
+    squared-Euclidean kernel of the path plus rank-one terms, differentiable through both."""
+    x1_, x2_ = check_pairwise_inputs("snr_distances", x1, x2)
+    _require_cuda(x1_, x2_)
+    d = x1_.size(-1)
+    shift = x2_.sum(-1).unsqueeze(-2) - x1_.sum(-1, keepdim=True)
+    diff_var = _ppminkowski(x1_, x2_, 2.0) - shift * shift / d
+    x1_var = (x1_ - x1_.mean(-1, keepdim=True)).pow(2).sum(-1, keepdim=True)
+    return diff_var / x1_var
+
+
+def mahalanobis_distances(x1: Tensor, x2: Optional[Tensor] = None, VI: Optional[Tensor] = None) -> Tensor:
+    """sqrt((x1 - x2) VI (x1 - x2)^T) (OPS/pairwise_metrics.cpp:272-297, OPS/cpu/sqmahalanobis_kernel.cpp:23-31); VI
+    defaults to the transposed inverse covariance of x1 (no gradient), as there.  Expanded into four
+    bilinear terms, the two cross terms being plain dot-product kernels of the path (tensor cores on
+    large problems): like every contraction form it loses relative accuracy for near-duplicate rows."""
+    if x2 is not None and VI is None:
+        raise RuntimeError("VI is required for manhalanobis when x2 is passed.")
+    x1_, x2_ = check_pairwise_inputs("mahalanobis_distances", x1, x2)
+    _require_cuda(x1_, x2_)
+    if VI is None:
+        with torch.no_grad():
+            VI = torch.linalg.inv(torch.cov(x1_.transpose(-1, -2)) if x1_.dim() == 2 else
+                                  torch.stack([torch.cov(xb.transpose(-1, -2)) for xb in x1_])).transpose(-1, -2)
+    x1v = linear_kernel(x1_, VI.transpose(-1, -2))          # x1 VI
+    x2v = x1v if x2 is None else linear_kernel(x2_, VI.transpose(-1, -2))
+    sq = ((x1v * x1_).sum(-1, keepdim=True) + (x2v * x2_).sum(-1).unsqueeze(-2)
+          - linear_kernel(x1v, x2_) - linear_kernel(x1_, x2v))
+    return sq.clamp_min(0).sqrt()
+
+
 def radius_neighbors_mask(x1: Tensor, x2: Optional[Tensor] = None, epsilon: float = 0.0, metric: str = "euclidean",
                           **kwargs) -> Tensor:
     """cdist(x1, x2, metric) <= epsilon (OPS/neighbors.cpp:37-58)."""

@@ -453,6 +453,19 @@ def run_suite(args):
             entry("C2_wminkowski_p3_bwd", n, timeit(bwdw), "fp32_issue (coefficient forward + grad_x1, grad_x2, grad_w passes)", n * 256 * (3 + 4 + 4 + 4), fp32_peak, 0)
             del out
         del W
+    # canberra at C2: a sum of two-argument terms (one approximate reciprocal per term)
+    if want("C2_canberra_fwd"):
+        with torch.no_grad():
+            entry("C2_canberra_fwd", n, timeit(lambda: tpw.canberra_distances(X, Y)), "fp32_issue (4 lane-ops + 1 MUFU per term)", n * 256 * 4, fp32_peak, 4 * n)
+    if want("C2_canberra_bwd"):
+        out = tpw.canberra_distances(X, Y)
+
+        def bwdc():
+            X.grad = None
+            Y.grad = None
+            out.backward(G, retain_graph=True)
+        entry("C2_canberra_bwd", n, timeit(bwdc), "fp32_issue (two passes)", n * 256 * 2 * 8, fp32_peak, 0)
+        del out
     # dense-contraction backward at C2: two tf32x3 tensor-core products per call (executed flops = 3 x 4 n D);
     # the tf32 rate is taken as half of the measured sustained bf16 rate
     for name, fn in (("C2_sqeuclidean_bwd", tpw.sqeuclidean_distances), ("C2_euclidean_bwd", tpw.euclidean_distances),

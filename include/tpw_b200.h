@@ -354,6 +354,25 @@ enum tpw_cmp_reduction { TPW_RED_SUM = 0, TPW_RED_MEAN = 1 };
 TPW_API int tpw_cmp_reduce_forward(int dtype, int op, int reduction, const void *x1, const void *x2, float *out,
                            int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream);
 
+/* ---- sums of two-argument terms that are not functions of the difference alone ------------------ */
+
+enum tpw_pair_metric {
+    TPW_PAIR_CANBERRA = 0,      /* sum_k |x - y| / (|x| + |y|), zero denominators skipped (OPS/cpu/canberra_kernel.cpp:22-29) */
+    TPW_PAIR_ADDITIVE_CHI2 = 1  /* - sum_k (x - y)^2 / (x + y), zero denominators skipped (OPS/cpu/additive_chi2_kernel.cpp:22-31) */
+};
+
+/*
+ * out[b,i,j] = sum_k term(x1[b,i,k], x2[b,j,k]) on the CUDA-core forward tile, and its backward
+ * grad_x1[b,i,k] = sum_j g[b,i,j] d term / d x1 (grad_x2 by symmetry of the terms), deterministic.
+ * Replaces _canberra / _additive_chi2_kernel forward and backward
+ * (OPS/cpu/canberra_kernel.cpp:85-125, OPS/cpu/additive_chi2_kernel.cpp:88-131 and their CUDA twins).
+ */
+TPW_API int tpw_pair_sum_forward(int dtype, int metric, const void *x1, const void *x2, void *out,
+                         int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream);
+TPW_API int tpw_pair_sum_backward(int dtype, int metric, const void *grad, const void *x1, const void *x2,
+                          void *grad_x1, void *grad_x2,
+                          int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream);
+
 /* ---- directed Hausdorff ---------------------------------------------------------------------- */
 
 /*

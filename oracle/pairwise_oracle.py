@@ -328,6 +328,33 @@ def mahalanobis(x1, x2, VI):
     return _un(out.astype(a.dtype), ub)
 
 
+def canberra(x1, x2):
+    """sum_k |x1 - x2| / (|x1| + |x2|), terms with a zero denominator skipped (OPS/cpu/canberra_kernel.cpp:22-29)."""
+    a, ub = _b3(x1)
+    b, _ = _b3(x2)
+    num = np.abs(_diff(a, b))
+    den = np.abs(a)[:, :, None, :] + np.abs(b)[:, None, :, :]
+    with np.errstate(divide="ignore", invalid="ignore"):
+        out = np.where(den != 0, num / den, 0).sum(-1)
+    return _un(out.astype(a.dtype), ub)
+
+
+def additive_chi2_kernel(x1, x2):
+    """- sum_k (x1 - x2)^2 / (x1 + x2), terms with a zero denominator skipped (OPS/cpu/additive_chi2_kernel.cpp:22-31)."""
+    a, ub = _b3(x1)
+    b, _ = _b3(x2)
+    d = _diff(a, b)
+    nom = a[:, :, None, :] + b[:, None, :, :]
+    with np.errstate(divide="ignore", invalid="ignore"):
+        out = -np.where(nom != 0, d * d / nom, 0).sum(-1)
+    return _un(out.astype(a.dtype), ub)
+
+
+def chi2_kernel(x1, x2, gamma=1.0):
+    """exp(gamma * additive_chi2_kernel) (OPS/pairwise_metrics.cpp:144)."""
+    return np.exp(additive_chi2_kernel(x1, x2) * np.asarray(x1).dtype.type(gamma))
+
+
 def k_neighbors_mask(dists, k):
     """True at the k + 1 smallest entries of every row (OPS/neighbors.cpp:29-33)."""
     d = np.asarray(dists)

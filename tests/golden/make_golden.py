@@ -203,10 +203,38 @@ def composed_golden():
     print("composed.npz", len(out), "arrays")
 
 
+def pair_sums_golden():
+    """canberra and the chi-squared kernels: sums of two-argument terms with reference kernels of their
+    own (OPS/cpu/canberra_kernel.cpp, additive_chi2_kernel.cpp).  Mixed-sign inputs for canberra,
+    non-negative histograms (with exact zeros, so that skipped terms occur) for chi2."""
+    out = {}
+    g = torch.Generator().manual_seed(63)
+    for tag, s1, s2, dt in (("u32", (33, 19), (21, 19), torch.float32), ("b64", (2, 9, 7), (2, 6, 7), torch.float64),
+                            ("w32", (140, 70), (131, 70), torch.float32)):
+        x1, x2 = torch.randn(*s1, generator=g, dtype=dt), torch.randn(*s2, generator=g, dtype=dt)
+        h1, h2 = torch.rand(*s1, generator=g, dtype=dt), torch.rand(*s2, generator=g, dtype=dt)
+        h1[..., 0, :3] = 0
+        h2[..., 1, :4] = 0
+        up = torch.randn(*s1[:-1], s2[-2], generator=g, dtype=dt)
+        for k, v in (("x1", x1), ("x2", x2), ("h1", h1), ("h2", h2), ("up", up)):
+            out[f"{tag}/{k}"] = npy(v)
+        for name, a0, b0, kw in (("canberra_distances", x1, x2, {}), ("additive_chi2_kernel", h1, h2, {}),
+                                 ("chi2_kernel", h1, h2, {"gamma": 0.7})):
+            a, b = a0.clone().requires_grad_(True), b0.clone().requires_grad_(True)
+            r = getattr(T, name)(a, b, **kw)
+            r.backward(up)
+            out[f"{tag}/{name}/out"], out[f"{tag}/{name}/gx1"], out[f"{tag}/{name}/gx2"] = npy(r), npy(a.grad), npy(b.grad)
+            out[f"{tag}/{name}/self_out"] = npy(getattr(T, name)(a0, None, **kw))
+        if len(s1) == 2:
+            out[f"{tag}/cdist_canberra"] = npy(T.cdist(x1, x2, "canberra"))
+    np.savez_compressed(HERE / "pair_sums.npz", **out)
+    print("pair_sums.npz", len(out), "arrays")
+
+
 if __name__ == "__main__":
     torch.set_num_threads(8)
     which = set(sys.argv[1:])
     for name, fn in (("float", float_golden), ("bool", bool_golden), ("hausdorff", hausdorff_golden), ("configs", config_golden),
-                     ("extras", extras_golden), ("composed", composed_golden)):
+                     ("extras", extras_golden), ("composed", composed_golden), ("pair_sums", pair_sums_golden)):
         if not which or name in which:
             fn()

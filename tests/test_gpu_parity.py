@@ -286,7 +286,7 @@ def test_cdist_dispatcher(tpw):
     with pytest.raises(RuntimeError, match="unkown distance metric"):
         tpw.cdist(x1, x2, "nope")
     with pytest.raises(NotImplementedError, match="outside"):
-        tpw.pdist(x1, "canberra")
+        tpw.pdist(x1, "haversine")
 
 
 def test_gradcheck_float64(tpw):
@@ -895,6 +895,38 @@ def test_composed_metrics_golden(tpw, golden, tag):
         torch.testing.assert_close(got.cpu(), torch.from_numpy(G["u32/mahalanobis_default_VI"]), rtol=1e-3, atol=3e-3)
         with pytest.raises(RuntimeError, match="VI is required"):
             tpw.mahalanobis_distances(a, b)
+
+
+@pytest.mark.parametrize("tag", ["u32", "b64", "w32"])
+def test_pair_sum_metrics_golden(tpw, golden, tag):
+    """canberra_distances, additive_chi2_kernel and chi2_kernel against the reference's outputs and gradients."""
+    G = golden("pair_sums")
+    dt = torch.float32 if tag != "b64" else torch.float64
+    tol = TOL[dt]
+    up = cuda(G[f"{tag}/up"])
+    for name, k1, k2, kw in (("canberra_distances", "x1", "x2", {}), ("additive_chi2_kernel", "h1", "h2", {}),
+                             ("chi2_kernel", "h1", "h2", {"gamma": 0.7})):
+        x1, x2 = cuda(G[f"{tag}/{k1}"], True), cuda(G[f"{tag}/{k2}"], True)
+        out = getattr(tpw, name)(x1, x2, **kw)
+        close(out, G[f"{tag}/{name}/out"], tol, msg=name)
+        out.backward(up)
+        close(x1.grad, G[f"{tag}/{name}/gx1"], tol, 10, name + " grad_x1")
+        close(x2.grad, G[f"{tag}/{name}/gx2"], tol, 10, name + " grad_x2")
+        close(getattr(tpw, name)(x1.detach(), **kw), G[f"{tag}/{name}/self_out"], tol, msg=name + " self")
+    if tag == "u32":
+        a, b = cuda(G["u32/x1"]), cuda(G["u32/x2"])
+        close(tpw.cdist(a, b, "canberra"), G["u32/cdist_canberra"], tol, msg="cdist canberra")
+        with pytest.raises(RuntimeError, match="must be positive"):
+            tpw.chi2_kernel(a, b)
+        # a feature that is zero on both sides contributes nothing, forward and backward
+        z1, z2 = a.clone(), b.clone()
+        z1[:, 3] = 0
+        z2[:, 3] = 0
+        z1.requires_grad_(True)
+        o = tpw.canberra_distances(z1, z2)
+        close(o, O.canberra(z1.detach().cpu().numpy(), z2.cpu().numpy()), tol, msg="canberra with a zero feature")
+        o.sum().backward()
+        assert torch.isfinite(z1.grad).all() and float(z1.grad[:, 3].abs().max()) == 0.0
 
 
 def test_bounded_wait_reports_instead_of_hanging(tpw):

@@ -54,7 +54,7 @@ def test_cdist_keyword_validation():
     with pytest.raises(RuntimeError, match="Got unkown distance metric: foo"):
         tpw.cdist(x, x, "foo")
     with pytest.raises(NotImplementedError, match="outside"):
-        tpw.cdist(x, x, "canberra")
+        tpw.cdist(x, x, "haversine")
     # pdist validates like cdist, then needs a CUDA tensor (the reference only has a stub that raises)
     with pytest.raises(TypeError, match="incompatible arguments p"):
         tpw.pdist(x, "euclidean", p=2.0)

@@ -143,3 +143,17 @@ def test_composed_metrics_match_reference(golden):
     big = G["u32/big"]
     VI = np.linalg.inv(np.cov(big.T.astype(np.float64))).T
     np.testing.assert_allclose(O.mahalanobis(big.astype(np.float64), big.astype(np.float64), VI), G["u32/mahalanobis_default_VI"], rtol=1e-3, atol=2e-3)
+
+
+def test_pair_sum_metrics_match_reference(golden):
+    """canberra and the chi-squared kernels: numpy restatements against the reference's own kernels."""
+    G = golden("pair_sums")
+    for tag in ("u32", "b64", "w32"):
+        x1, x2, h1, h2 = G[f"{tag}/x1"], G[f"{tag}/x2"], G[f"{tag}/h1"], G[f"{tag}/h2"]
+        tol = TOL[x1.dtype]
+        np.testing.assert_allclose(O.canberra(x1, x2), G[f"{tag}/canberra_distances/out"], **tol)
+        np.testing.assert_allclose(O.canberra(x1, x1), G[f"{tag}/canberra_distances/self_out"], **tol)
+        np.testing.assert_allclose(O.additive_chi2_kernel(h1, h2), G[f"{tag}/additive_chi2_kernel/out"], **tol)
+        np.testing.assert_allclose(O.additive_chi2_kernel(h1, h1), G[f"{tag}/additive_chi2_kernel/self_out"], **tol)
+        np.testing.assert_allclose(O.chi2_kernel(h1, h2, 0.7), G[f"{tag}/chi2_kernel/out"], **tol)
+    np.testing.assert_allclose(O.canberra(G["u32/x1"], G["u32/x2"]), G["u32/cdist_canberra"], **TOL[np.dtype("float32")])

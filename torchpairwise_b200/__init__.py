@@ -10,8 +10,11 @@ from .ops import (
     _directed_hausdorff,
     _ppminkowski,
     _wminkowski,
+    additive_chi2_kernel,
     braycurtis_distances,
+    canberra_distances,
     chebyshev_distances,
+    chi2_kernel,
     cityblock_distances,
     correlation_distances,
     cosine_distances,

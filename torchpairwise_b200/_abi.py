@@ -18,6 +18,7 @@ TPW_OK = 0
 F32, F64, I32, I64 = 0, 1, 2, 3
 LP_BWD_CDIST, LP_BWD_PPMINKOWSKI, LP_BWD_WMINKOWSKI, LP_BWD_MATMUL = 0, 1, 2, 3
 DOT_LINEAR, DOT_COSINE_SIM, DOT_COSINE_DIST, DOT_ONE_MINUS_SIM, DOT_SQEUCLIDEAN, DOT_EUCLIDEAN = range(6)
+PAIR_CANBERRA, PAIR_ADDITIVE_CHI2 = 0, 1
 ENGINE_AUTO, ENGINE_SIMT_FP32, ENGINE_TCGEN05_BF16X3, ENGINE_TCGEN05_TF32X3 = 0, 1, 2, 3
 CMP_EQ, CMP_NE = 0, 1
 RED_SUM, RED_MEAN = 0, 1
@@ -43,6 +44,8 @@ SIGNATURES = {
     "tpw_lp_rowmin_forward": (_I, [_I, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _D, _D, _P]),
     "tpw_lp_radius_mask_forward": (_I, [_I, _P, _P, _P, _P, _L, _L, _L, _L, _D, _D, _D, _P]),
     "tpw_lp_pdist_forward": (_I, [_I, _P, _P, _L, _L, _L, _D, _D, _P]),
+    "tpw_pair_sum_forward": (_I, [_I, _I, _P, _P, _P, _L, _L, _L, _L, _P]),
+    "tpw_pair_sum_backward": (_I, [_I, _I, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P]),
     "tpw_lp_backward": (_I, [_I, _I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _D, _P]),
     "tpw_wminkowski_backward_w": (_I, [_I, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _D, _P]),
     "tpw_lp_inf_backward": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _P]),

@@ -44,7 +44,7 @@ _SCHEMAS = {
                           "-> (Tensor output, Tensor x1_indices, Tensor x2_indices)",
 }
 
-_OUT_OF_SCOPE = {"canberra", "haversine", "jensenshannon"}
+_OUT_OF_SCOPE = {"haversine", "jensenshannon"}
 
 
 def _check_extra_args(metric: str, **given) -> None:

@@ -30,7 +30,10 @@ enum Phi {
     PHI_SGNPOW = 3, // sgn(d)*|d|^q
     PHI_ABSPOW = 4, // |d|^q
     PHI_Y = 5,      // the streamed operand itself (plain contraction)
-    PHI_SGN_EQ = 6  // sgn(d) where |d| equals the auxiliary value, else 0
+    PHI_SGN_EQ = 6, // sgn(d) where |d| equals the auxiliary value, else 0
+    // derivatives of symmetric two-argument terms with respect to the register-resident operand x
+    PHI_CANBERRA = 7, // sgn(d)/n - sgn(x)|d|/n^2, n = |x| + |y| (0 where n == 0)
+    PHI_CHI2 = 8      // t^2 - 2t, t = d/(x + y) (0 where x + y == 0): d/dx of -(x - y)^2/(x + y)
 };
 
 enum CoefMode { COEF_G = 0, COEF_DIV_O = 1, COEF_DIV_O2 = 2, COEF_DIV_POW = 3, COEF_MUL = 4, COEF_ZERO_WHERE_O0 = 5 };
@@ -90,6 +93,23 @@ template <int PHI, typename T>
 __device__ __forceinline__ void bwd_accumulate(T &acc, T x, T y, T c, T o, T q, int pspec) {
     if (PHI == PHI_Y) {
         acc = b_fma(c, y, acc);
+        return;
+    }
+    if (PHI == PHI_CANBERRA) {
+        const T n = b_abs(x) + b_abs(y);
+        if (n != T(0)) {
+            const T d = x - y, r = b_div(T(1), n);
+            const T sd = d > T(0) ? T(1) : (d < T(0) ? T(-1) : T(0)), sx = x > T(0) ? T(1) : (x < T(0) ? T(-1) : T(0));
+            acc = b_fma(c, (sd - sx * b_abs(d) * r) * r, acc);
+        }
+        return;
+    }
+    if (PHI == PHI_CHI2) {
+        const T n = x + y;
+        if (n != T(0)) {
+            const T t = b_div(x - y, n);
+            acc = b_fma(c, t * t - T(2) * t, acc);
+        }
         return;
     }
     T d = x - y;
@@ -567,4 +587,31 @@ extern "C" int tpw_lp_inf_backward(int dtype, const void *grad, const void *x1, 
 #undef TPW_INF_LAUNCH
     TPW_LAUNCH_OK("lp_inf_backward_kernel");
     return TPW_OK;
+}
+
+extern "C" int tpw_pair_sum_backward(int dtype, int metric, const void *grad, const void *x1, const void *x2,
+                                     void *grad_x1, void *grad_x2,
+                                     int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(dtype == TPW_F32 || dtype == TPW_F64, "tpw_pair_sum_backward: dtype must be TPW_F32 or TPW_F64");
+    TPW_CHECK_ARG(metric == TPW_PAIR_CANBERRA || metric == TPW_PAIR_ADDITIVE_CHI2, "tpw_pair_sum_backward: bad metric %d", metric);
+    TPW_CHECK_ARG(B >= 0 && N1 >= 0 && N2 >= 0 && D >= 0, "tpw_pair_sum_backward: negative size");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t es = dtype == TPW_F32 ? 4 : 8;
+    if (B * D == 0 || N1 == 0 || N2 == 0) {
+        if (grad_x1 && B * N1 * D > 0) TPW_CUDA_OK(cudaMemsetAsync(grad_x1, 0, (size_t)(B * N1 * D) * es, s));
+        if (grad_x2 && B * N2 * D > 0) TPW_CUDA_OK(cudaMemsetAsync(grad_x2, 0, (size_t)(B * N2 * D) * es, s));
+        return TPW_OK;
+    }
+    TPW_CHECK_ARG(grad && x1 && x2 && (grad_x1 || grad_x2), "tpw_pair_sum_backward: NULL pointer");
+    BwdParams P;
+    memset(&P, 0, sizeof(P));
+    P.grad = grad; P.aux = nullptr; P.w = nullptr;
+    P.B = B; P.N1 = N1; P.N2 = N2; P.D = D;
+    P.post = 1.0; P.coef_mode = COEF_G;
+    if (metric == TPW_PAIR_CANBERRA)
+        return dtype == TPW_F32 ? launch_both<float, PHI_CANBERRA, false>(P, x1, x2, grad_x1, grad_x2, s)
+                                : launch_both<double, PHI_CANBERRA, false>(P, x1, x2, grad_x1, grad_x2, s);
+    return dtype == TPW_F32 ? launch_both<float, PHI_CHI2, false>(P, x1, x2, grad_x1, grad_x2, s)
+                            : launch_both<double, PHI_CHI2, false>(P, x1, x2, grad_x1, grad_x2, s);
 }

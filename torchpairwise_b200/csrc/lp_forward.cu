@@ -78,3 +78,22 @@ extern "C" int tpw_cmp_reduce_forward(int dtype, int op, int reduction, const vo
         default: return launch_forward<double, float, K_NE_BITS, false>(P, s);
     }
 }
+
+extern "C" int tpw_pair_sum_forward(int dtype, int metric, const void *x1, const void *x2, void *out,
+                                    int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(dtype == TPW_F32 || dtype == TPW_F64, "tpw_pair_sum_forward: dtype must be TPW_F32 or TPW_F64");
+    TPW_CHECK_ARG(metric == TPW_PAIR_CANBERRA || metric == TPW_PAIR_ADDITIVE_CHI2, "tpw_pair_sum_forward: bad metric %d", metric);
+    TPW_CHECK_ARG(B >= 0 && N1 >= 0 && N2 >= 0 && D >= 0, "tpw_pair_sum_forward: negative size");
+    if (B == 0 || N1 == 0 || N2 == 0) return TPW_OK;
+    TPW_CHECK_ARG(x1 && x2 && out, "tpw_pair_sum_forward: NULL pointer");
+    TPW_CHECK_ARG(D > 0, "tpw_pair_sum_forward: D must be positive");
+    FwdParams P;
+    memset(&P, 0, sizeof(P));
+    P.x1 = x1; P.x2 = x2; P.out = out;
+    P.B = B; P.N1 = N1; P.N2 = N2; P.D = D;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (metric == TPW_PAIR_CANBERRA)
+        return dtype == TPW_F32 ? launch_forward<float, float, K_CANBERRA, false>(P, s) : launch_forward<double, double, K_CANBERRA, false>(P, s);
+    return dtype == TPW_F32 ? launch_forward<float, float, K_CHI2, false>(P, s) : launch_forward<double, double, K_CHI2, false>(P, s);
+}

@@ -18,7 +18,9 @@ enum Kind {
     K_MIN = 5,    // min |d| (padding masked)
     K_DOT = 6,    // sum x*y with row norms accumulated on the side
     K_NE = 7,     // count of x != y (IEEE compare)
-    K_NE_BITS = 8 // count of differing bit patterns (integer payloads)
+    K_NE_BITS = 8, // count of differing bit patterns (integer payloads)
+    K_CANBERRA = 9, // sum |x - y| / (|x| + |y|), terms with a zero denominator skipped
+    K_CHI2 = 10     // - sum (x - y)^2 / (x + y), terms with a zero denominator skipped
 };
 
 struct FwdParams {
@@ -61,6 +63,9 @@ template <> __device__ __forceinline__ double t_min<double>(double a, double b) 
 // |a|^p for a >= 0.  fp32: two MUFU operations; 0^p = exp2(-inf) = 0 for p > 0.
 __device__ __forceinline__ float t_powabs(float a, float p) { return exp2f(p * __log2f(a)); }
 __device__ __forceinline__ double t_powabs(double a, double p) { return pow(a, p); }
+// quotient of one term of a sum: the approximate divide (2 ulp) is far inside the fp32 parity tolerance
+__device__ __forceinline__ float t_div(float a, float b) { return __fdividef(a, b); }
+__device__ __forceinline__ double t_div(double a, double b) { return a / b; }
 __device__ __forceinline__ float t_sqrt(float v) { return sqrtf(v); }
 __device__ __forceinline__ double t_sqrt(double v) { return sqrt(v); }
 __device__ __forceinline__ float t_cbrt(float v) { return cbrtf(v); }
@@ -80,6 +85,16 @@ __device__ __forceinline__ void accumulate(T &acc, T x, T y, T w, T p, int pspec
         acc += (x != y) ? T(1) : T(0);
     } else if (KIND == K_NE_BITS) {
         acc += bits_differ(x, y) ? T(1) : T(0);
+    } else if (KIND == K_CANBERRA) {
+        // zero padding contributes nothing: its denominator is 0
+        const T den = t_abs(x) + t_abs(y);
+        if (den != T(0)) acc += t_div(t_abs(x - y), den);
+    } else if (KIND == K_CHI2) {
+        const T nom = x + y;
+        if (nom != T(0)) {
+            const T d = x - y;
+            acc -= t_div(d * d, nom);
+        }
     } else {
         T d = x - y;
         if (KIND == K_L1) {

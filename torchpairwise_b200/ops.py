@@ -963,6 +963,74 @@ def seuclidean_distances(x1: Tensor, x2: Optional[Tensor] = None, V: Optional[Te
     return _wminkowski(x1_, x2_, w, 2.0)
 
 
+class _PairSumFunction(torch.autograd.Function):
+    """sum_k term(x1_k, x2_k) for terms that are not functions of the difference alone: _canberra
+    (OPS/autograd/canberra_kernel.cpp, kernels OPS/cpu/canberra_kernel.cpp:22-29,85-125) and
+    _additive_chi2_kernel (OPS/cpu/additive_chi2_kernel.cpp:22-31,88-131).  Where a term's denominator is 0
+    the forward skips it and the backward contributes 0 (the reference's canberra backward divides by it)."""
+
+    @staticmethod
+    def forward(ctx, x1: Tensor, x2: Tensor, metric: int):
+        in_dtype = x1.dtype
+        cdt = _compute_dtype(in_dtype)
+        x1c, x2c, unbatched = _batched(x1.to(cdt), x2.to(cdt), "pair_sum")
+        B, N1, N2, D = _sizes(x1c, x2c)
+        out = torch.empty((B, N1, N2), dtype=cdt, device=x1c.device)
+        if D == 0:
+            out.zero_()
+        else:
+            with torch.cuda.device(x1c.device):
+                check(lib.tpw_pair_sum_forward(_FLOAT_CODES[cdt], metric, _ptr(x1c), _ptr(x2c), _ptr(out), B, N1, N2, D,
+                                               _stream(x1c)), "tpw_pair_sum_forward")
+        ctx.save_for_backward(x1c, x2c)
+        ctx.metric, ctx.unbatched, ctx.in_dtype = metric, unbatched, in_dtype
+        return (out.squeeze(0) if unbatched else out).to(in_dtype)
+
+    @staticmethod
+    def backward(ctx, grad):
+        x1c, x2c = ctx.saved_tensors
+        g = grad.to(x1c.dtype).contiguous()
+        if ctx.unbatched:
+            g = g.unsqueeze(0)
+        B, N1, N2, D = _sizes(x1c, x2c)
+        need1, need2 = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        g1 = torch.empty_like(x1c) if need1 else None
+        g2 = torch.empty_like(x2c) if need2 else None
+        with torch.cuda.device(x1c.device):
+            check(lib.tpw_pair_sum_backward(_FLOAT_CODES[x1c.dtype], ctx.metric, _ptr(g), _ptr(x1c), _ptr(x2c), _ptr(g1), _ptr(g2),
+                                            B, N1, N2, D, _stream(x1c)), "tpw_pair_sum_backward")
+        if ctx.unbatched:
+            g1 = None if g1 is None else g1.squeeze(0)
+            g2 = None if g2 is None else g2.squeeze(0)
+        return (None if g1 is None else g1.to(ctx.in_dtype)), (None if g2 is None else g2.to(ctx.in_dtype)), None
+
+
+def canberra_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    """sum_k |x1 - x2| / (|x1| + |x2|) (OPS/pairwise_metrics.cpp:317-324)."""
+    x1_, x2_ = check_pairwise_inputs("canberra_distances", x1, x2)
+    _require_cuda(x1_, x2_)
+    return _PairSumFunction.apply(x1_, x2_, _abi.PAIR_CANBERRA)
+
+
+def _require_non_negative(x1: Tensor, x2: Optional[Tensor], x2_: Tensor) -> None:
+    # the reference's check (and message), OPS/pairwise_metrics.cpp:130-131; it synchronises there too
+    if not (bool(x1.ge(0).all()) and (x2 is None or bool(x2_.ge(0).all()))):
+        raise RuntimeError("All elements of x1 and x2 must be positive")
+
+
+def additive_chi2_kernel(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    """- sum_k (x1 - x2)^2 / (x1 + x2) on non-negative inputs (OPS/pairwise_metrics.cpp:124-133)."""
+    x1_, x2_ = check_pairwise_inputs("additive_chi2_kernel", x1, x2)
+    _require_cuda(x1_, x2_)
+    _require_non_negative(x1_, x2, x2_)
+    return _PairSumFunction.apply(x1_, x2_, _abi.PAIR_ADDITIVE_CHI2)
+
+
+def chi2_kernel(x1: Tensor, x2: Optional[Tensor] = None, gamma: float = 1.0) -> Tensor:
+    """exp(gamma * additive_chi2_kernel(x1, x2)) (OPS/pairwise_metrics.cpp:135-145)."""
+    return (additive_chi2_kernel(x1, x2) * gamma).exp()
+
+
 def braycurtis_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
     """sum_k |x1 - x2| / sum_k |x1 + x2| (the reference's own kernel, OPS/cpu/braycurtis_kernel.cpp:22-27,
     called at OPS/pairwise_metrics.cpp:308-315): two passes of the L1 tile kernel, the second against

@@ -86,6 +86,13 @@ __device__ __forceinline__ float pow_abs_spec(float a, float q, int spec) {
     return r;
 }
 __device__ __forceinline__ double pow_abs_spec(double a, double q, int) { return a == 0.0 ? 0.0 : pow(a, q); }
+// 1 / v for one term of a sum: the bare MUFU reciprocal (1 ulp) in float, the exact divide in double
+__device__ __forceinline__ float rcp_term(float v) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+    return r;
+}
+__device__ __forceinline__ double rcp_term(double v) { return 1.0 / v; }
 
 // ---- device-side PTX wrappers -----------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {

@@ -96,20 +96,20 @@ __device__ __forceinline__ void bwd_accumulate(T &acc, T x, T y, T c, T o, T q, 
         return;
     }
     if (PHI == PHI_CANBERRA) {
-        const T n = b_abs(x) + b_abs(y);
-        if (n != T(0)) {
-            const T d = x - y, r = b_div(T(1), n);
-            const T sd = d > T(0) ? T(1) : (d < T(0) ? T(-1) : T(0)), sx = x > T(0) ? T(1) : (x < T(0) ? T(-1) : T(0));
-            acc = b_fma(c, (sd - sx * b_abs(d) * r) * r, acc);
-        }
+        // r (sgn(d) - sgn(x) |d| r), branch-free: a zero denominator selects r = 0, and the two signs are
+        // copied onto r and |d| r^2 (zero where d, respectively x, is zero)
+        const T n = b_abs(x) + b_abs(y), d = x - y;
+        const T r = n != T(0) ? rcp_term(n) : T(0);
+        const T t1 = d != T(0) ? b_copysign(r, d) : T(0);
+        const T t2 = x != T(0) ? b_copysign(b_abs(d) * r * r, x) : T(0);
+        acc = b_fma(c, t1 - t2, acc);
         return;
     }
     if (PHI == PHI_CHI2) {
         const T n = x + y;
-        if (n != T(0)) {
-            const T t = b_div(x - y, n);
-            acc = b_fma(c, t * t - T(2) * t, acc);
-        }
+        const T r = n != T(0) ? rcp_term(n) : T(0);
+        const T t = (x - y) * r;
+        acc = b_fma(c, t * (t - T(2)), acc);
         return;
     }
     T d = x - y;

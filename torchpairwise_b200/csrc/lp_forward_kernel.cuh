@@ -63,9 +63,6 @@ template <> __device__ __forceinline__ double t_min<double>(double a, double b) 
 // |a|^p for a >= 0.  fp32: two MUFU operations; 0^p = exp2(-inf) = 0 for p > 0.
 __device__ __forceinline__ float t_powabs(float a, float p) { return exp2f(p * __log2f(a)); }
 __device__ __forceinline__ double t_powabs(double a, double p) { return pow(a, p); }
-// quotient of one term of a sum: the approximate divide (2 ulp) is far inside the fp32 parity tolerance
-__device__ __forceinline__ float t_div(float a, float b) { return __fdividef(a, b); }
-__device__ __forceinline__ double t_div(double a, double b) { return a / b; }
 __device__ __forceinline__ float t_sqrt(float v) { return sqrtf(v); }
 __device__ __forceinline__ double t_sqrt(double v) { return sqrt(v); }
 __device__ __forceinline__ float t_cbrt(float v) { return cbrtf(v); }
@@ -86,15 +83,14 @@ __device__ __forceinline__ void accumulate(T &acc, T x, T y, T w, T p, int pspec
     } else if (KIND == K_NE_BITS) {
         acc += bits_differ(x, y) ? T(1) : T(0);
     } else if (KIND == K_CANBERRA) {
-        // zero padding contributes nothing: its denominator is 0
+        // branch-free: a zero denominator (zero padding included) selects a zero reciprocal
         const T den = t_abs(x) + t_abs(y);
-        if (den != T(0)) acc += t_div(t_abs(x - y), den);
+        const T r = den != T(0) ? rcp_term(den) : T(0);
+        acc = t_fma(t_abs(x - y), r, acc);
     } else if (KIND == K_CHI2) {
-        const T nom = x + y;
-        if (nom != T(0)) {
-            const T d = x - y;
-            acc -= t_div(d * d, nom);
-        }
+        const T nom = x + y, d = x - y;
+        const T r = nom != T(0) ? rcp_term(nom) : T(0);
+        acc = t_fma(-(d * d), r, acc);
     } else {
         T d = x - y;
         if (KIND == K_L1) {

@@ -86,13 +86,15 @@ __device__ __forceinline__ float pow_abs_spec(float a, float q, int spec) {
     return r;
 }
 __device__ __forceinline__ double pow_abs_spec(double a, double q, int) { return a == 0.0 ? 0.0 : pow(a, q); }
-// 1 / v for one term of a sum: the bare MUFU reciprocal (1 ulp) in float, the exact divide in double
-__device__ __forceinline__ float rcp_term(float v) {
+// 1 / v for one term of a sum, 0 where the term is to be skipped (v == 0).  float: the bare MUFU
+// reciprocal (1 ulp, flush-to-zero), so denominators below the smallest normal number count as zero;
+// double: the exact divide.
+__device__ __forceinline__ float rcp_or_zero(float v) {
     float r;
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
-    return r;
+    return fabsf(v) >= 1.17549435e-38f ? r : 0.f;
 }
-__device__ __forceinline__ double rcp_term(double v) { return 1.0 / v; }
+__device__ __forceinline__ double rcp_or_zero(double v) { return v != 0.0 ? 1.0 / v : 0.0; }
 
 // ---- device-side PTX wrappers -----------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {

@@ -99,7 +99,7 @@ __device__ __forceinline__ void bwd_accumulate(T &acc, T x, T y, T c, T o, T q, 
         // r (sgn(d) - sgn(x) |d| r), branch-free: a zero denominator selects r = 0, and the two signs are
         // copied onto r and |d| r^2 (zero where d, respectively x, is zero)
         const T n = b_abs(x) + b_abs(y), d = x - y;
-        const T r = n != T(0) ? rcp_term(n) : T(0);
+        const T r = rcp_or_zero(n);
         const T t1 = d != T(0) ? b_copysign(r, d) : T(0);
         const T t2 = x != T(0) ? b_copysign(b_abs(d) * r * r, x) : T(0);
         acc = b_fma(c, t1 - t2, acc);
@@ -107,7 +107,7 @@ __device__ __forceinline__ void bwd_accumulate(T &acc, T x, T y, T c, T o, T q, 
     }
     if (PHI == PHI_CHI2) {
         const T n = x + y;
-        const T r = n != T(0) ? rcp_term(n) : T(0);
+        const T r = rcp_or_zero(n);
         const T t = (x - y) * r;
         acc = b_fma(c, t * (t - T(2)), acc);
         return;

@@ -85,11 +85,11 @@ __device__ __forceinline__ void accumulate(T &acc, T x, T y, T w, T p, int pspec
     } else if (KIND == K_CANBERRA) {
         // branch-free: a zero denominator (zero padding included) selects a zero reciprocal
         const T den = t_abs(x) + t_abs(y);
-        const T r = den != T(0) ? rcp_term(den) : T(0);
+        const T r = rcp_or_zero(den);
         acc = t_fma(t_abs(x - y), r, acc);
     } else if (KIND == K_CHI2) {
         const T nom = x + y, d = x - y;
-        const T r = nom != T(0) ? rcp_term(nom) : T(0);
+        const T r = rcp_or_zero(nom);
         acc = t_fma(-(d * d), r, acc);
     } else {
         T d = x - y;

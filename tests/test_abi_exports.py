@@ -76,3 +76,63 @@ def test_cpp_host_layer_registers_the_reference_schemas():
     )
     r = subprocess.run([sys.executable, "-c", code], cwd=str(ROOT), capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr
+
+
+def test_stand_alone_schemas_equal_the_reference_strings():
+    """Every schema the host layer defines on its own, overloads included, reads exactly like the one the
+    reference registers (the reference library is loaded in a separate process; nothing is executed)."""
+    import json, subprocess, sys
+    ref = ROOT / "oracle" / "_ref" / "torchpairwise_ref.so"
+    if not ref.exists():
+        import pytest
+        pytest.skip("oracle/_ref is not built on this machine")
+    dump = ("s = {str(x.name) + '.' + str(x.overload_name): str(x) for x in torch._C._jit_get_all_schemas()"
+            " if x.name.startswith('torchpairwise::')}\nimport json; print('SCHEMAS' + json.dumps(s))\n")
+    outs = []
+    for head in (f"import torch\ntorch.ops.load_library({str(ref)!r})\n",
+                 "import torch, torchpairwise_b200 as t\nt.load_torch_ops()\n"):
+        r = subprocess.run([sys.executable, "-c", head + dump], cwd=str(ROOT), capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stdout + r.stderr
+        outs.append(json.loads(r.stdout.split("SCHEMAS", 1)[1]))
+    theirs, ours = outs
+    assert len(ours) >= 59, len(ours)
+    for key, text in ours.items():
+        assert theirs.get(key) == text, (key, text, theirs.get(key))
+    for name in ("prf_div.", "prf_div.Scalar", "prf_ldiv.rScalar", "prf_div_.", "prf_ldiv_.Scalar", "_prf_div_backward.rScalar",
+                 "_prf_ldiv__backward.Scalar", "__directed_hausdorff_backward.", "_directed_hausdorff.", "cdist."):
+        assert "torchpairwise::" + name in ours, name
+
+
+def test_host_layer_loads_next_to_the_reference_library():
+    """Loaded after the reference's CPU build, every kernel registered here has the C++ signature the reference
+    registered for the same schema (a mismatch aborts the process at load time)."""
+    import subprocess, sys
+    ref = ROOT / "oracle" / "_ref" / "torchpairwise_ref.so"
+    if not ref.exists():
+        pytest.skip("oracle/_ref is not built on this machine")
+    code = (f"import torch\ntorch.ops.load_library({str(ref)!r})\nimport torchpairwise_b200 as t\nt.load_torch_ops()\n"
+            "tab = torch._C._dispatch_dump_table('torchpairwise::prf_div_')\n"
+            "assert 'AutogradCUDA' in tab and 'tpw_torch.cpp' in tab and 'CPU' in tab\nprint('ok')\n")
+    r = subprocess.run([sys.executable, "-c", code], cwd=str(ROOT), capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_host_layer_error_messages_format_numbers():
+    """The argument checks run before anything touches a device, so the kernels registered for CUDA tensors can
+    be entered with CPU tensors through an explicit dispatch key: the messages must come back as exceptions
+    (a privately linked copy of the C++ stream classes once crashed the process here)."""
+    import subprocess, sys
+    code = (
+        "import torch, torchpairwise_b200 as t\nt.load_torch_ops()\n"
+        "ks = torch._C.DispatchKeySet(torch._C.DispatchKey.AutogradCUDA)\n"
+        "T = torch.ops.torchpairwise\n"
+        "for op, args, text in ((T.euclidean_distances.default, (torch.zeros(6, 50), torch.zeros(3, 40)), 'x1.size(1)=50, x2.size(1)=40'),\n"
+        "                       (T.prf_div.default, (torch.zeros(6, 50), torch.zeros(3, 50), 'zero'), 'self.shape=[6, 50], while other.shape=[3, 50]'),\n"
+        "                       (T.prf_div.default, (torch.zeros(2), torch.zeros(2), 'nope'), 'mode must be either zero or identity. Got nope'),\n"
+        "                       (T.manhattan_distances.default, (torch.zeros(2, 3), torch.zeros(2, 3)), 'CUDA tensors only')):\n"
+        "    try:\n        op.redispatch(ks, *args)\n        raise SystemExit('no error from ' + str(op))\n"
+        "    except RuntimeError as e:\n        assert text in str(e), str(e)\n"
+        "print('ok')\n"
+    )
+    r = subprocess.run([sys.executable, "-c", code], cwd=str(ROOT), capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]

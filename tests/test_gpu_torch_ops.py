@@ -115,6 +115,72 @@ def test_hausdorff_and_cdist_dispatcher(T):
         T.cdist(x1.cuda(), x2.cuda(), "canberra")
 
 
+def test_prf_div_family_and_hausdorff_backward_op(T):
+    """Every prf_div / prf_ldiv overload (tensor, Scalar, rScalar, in place) with its gradient, the stand-alone
+    backward ops, and __directed_hausdorff_backward: the reference on CPU tensors, these kernels on CUDA tensors."""
+    g = torch.Generator().manual_seed(16)
+    x = torch.randn(6, 50, generator=g)
+    y = torch.randn(6, 50, generator=g)
+    x[torch.rand(6, 50, generator=g) < 0.2] = 0
+    y[torch.rand(6, 50, generator=g) < 0.3] = 0
+    up = torch.randn(6, 50, generator=g)
+
+    def both(fn, *tensors):
+        res = []
+        for dev in ("cpu", "cuda"):
+            leaves = [t.to(dev).clone().requires_grad_(t.is_floating_point()) for t in tensors]
+            out = fn(*leaves)
+            out.backward(up.to(dev))
+            res.append((out.detach().cpu(), [l.grad.cpu() for l in leaves if l.requires_grad]))
+        (o_ref, g_ref), (o_got, g_got) = res
+        torch.testing.assert_close(o_got, o_ref, rtol=1e-6, atol=0, equal_nan=True)
+        for a, b in zip(g_got, g_ref):
+            torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-7, equal_nan=True)
+
+    for mode in ("zero", "identity"):
+        both(lambda a, b: T.prf_div(a, b, mode), x, y)
+        both(lambda a, b: T.prf_ldiv(a, b, mode), x, y)
+        for s in (2.5, 0.0):
+            both(lambda a: T.prf_div(a, s, mode), x)
+            both(lambda a: T.prf_ldiv(a, s, mode), y)
+            both(lambda b: T.prf_div(s, b, mode), y)
+            both(lambda b: T.prf_ldiv(s, b, mode), x)
+        # in place: values, and the input really is overwritten
+        for name, args in (("prf_div_", (y,)), ("prf_ldiv_", (y,)), ("prf_div_", (2.0,)), ("prf_ldiv_", (0.0,))):
+            outs = []
+            for dev in ("cpu", "cuda"):
+                a = x.to(dev).clone()
+                r = getattr(T, name)(a, *[v.to(dev) if isinstance(v, torch.Tensor) else v for v in args], mode)
+                assert r.data_ptr() == a.data_ptr()
+                outs.append(a.cpu())
+            torch.testing.assert_close(outs[1], outs[0], rtol=1e-6, atol=0, equal_nan=True)
+        for name in ("_prf_div_backward", "_prf_ldiv_backward", "_prf_div__backward", "_prf_ldiv__backward"):
+            ref = getattr(T, name)(up, x, y, mode)
+            got = getattr(T, name)(up.cuda(), x.cuda(), y.cuda(), mode)
+            for a, b in zip(got, ref):
+                torch.testing.assert_close(a.cpu(), b, rtol=1e-5, atol=1e-7, equal_nan=True)
+            torch.testing.assert_close(getattr(T, name)(up.cuda(), x.cuda(), 1.5, mode).cpu(), getattr(T, name)(up, x, 1.5, mode),
+                                       rtol=1e-5, atol=1e-7, equal_nan=True)
+        for name in ("_prf_div_backward", "_prf_ldiv_backward"):
+            torch.testing.assert_close(getattr(T, name)(up.cuda(), 1.5, y.cuda(), mode).cpu(), getattr(T, name)(up, 1.5, y, mode),
+                                       rtol=1e-5, atol=1e-7, equal_nan=True)
+    xi = torch.randint(-2, 3, (4, 9), generator=g)
+    yi = torch.randint(-1, 2, (4, 9), generator=g)
+    got, ref = T.prf_div(xi.cuda(), yi.cuda(), "identity"), T.prf_div(xi, yi, "identity")
+    assert got.dtype == ref.dtype == torch.float32 and torch.equal(got.cpu(), ref)
+    with pytest.raises(RuntimeError, match="mode must be either zero or identity"):
+        T.prf_div(x.cuda(), y.cuda(), "nope")
+    with pytest.raises(RuntimeError, match="Broadcasting semantic is not implemented"):
+        T.prf_div(x.cuda(), y.cuda()[:3], "zero")
+
+    s1, s2 = torch.rand(2, 3, 40, 3, generator=g), torch.rand(2, 2, 33, 3, generator=g)
+    gu = torch.randn(2, 3, 2, generator=g)
+    r1, r2 = T.__directed_hausdorff_backward(gu, s1, s2)
+    g1, g2 = T.__directed_hausdorff_backward(gu.cuda(), s1.cuda(), s2.cuda())
+    torch.testing.assert_close(g1.cpu(), r1, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(g2.cpu(), r2, rtol=1e-4, atol=1e-5)
+
+
 def test_cpp_layer_agrees_with_python_layer(T):
     import torchpairwise_b200 as tpw
     g = torch.Generator().manual_seed(14)

@@ -116,7 +116,11 @@ def build_torch_ops(force: bool = False) -> Path:
            *[f"-I{p}" for p in ce.include_paths()], f"-I{cuda_home}/include", f"-I{INCLUDE}",
            str(TORCH_SRC), "-o", str(tmp),
            f"-L{tdir / 'lib'}", "-ltorch", "-ltorch_cpu", "-lc10", "-ltorch_cuda", "-lc10_cuda",
-           f"-L{LIB_DIR}", "-ltpw_b200", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{tdir / 'lib'}"]
+           f"-L{LIB_DIR}", "-ltpw_b200", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{tdir / 'lib'}",
+           # the shared C++ runtime by name: a toolchain whose own libstdc++.so link is broken would otherwise
+           # fall back to libstdc++.a, and a second, private copy of the stream classes inside this library
+           # crashes as soon as an error message formats a number
+           "-nostdlib++", "-l:libstdc++.so.6"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"building the torch host layer failed:\n{r.stdout[-3000:]}\n{r.stderr[-3000:]}")

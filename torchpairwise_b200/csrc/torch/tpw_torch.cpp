@@ -402,42 +402,69 @@ struct RowCenterFn : torch::autograd::Function<RowCenterFn> {
 };
 
 // ---- directed Hausdorff (OPS/autograd/hausdorff_kernel.cpp:9-61) -------------------------------------------
+struct HausdorffRun {
+    Tensor a, b, out, i1, i2;
+    bool unbatched;
+    at::ScalarType in_dt;
+};
+
+// Checks, contiguous float32/float64 operands with a leading batch dimension, the visiting orders when
+// `shuffle` is set, and the forward kernels (OPS/cuda/hausdorff_kernel.cu:107-196).
+HausdorffRun hausdorff_run(const Tensor &x1, const Tensor &x2, bool shuffle, c10::optional<at::Generator> generator) {
+    require_cuda(x1);
+    require_cuda(x2);
+    const auto in_dt = x1.scalar_type();
+    TORCH_CHECK(in_dt == x2.scalar_type(), "x1 and x2 must have the same dtype (while checking arguments for _directed_hausdorff_forward)");
+    const bool ub = x1.dim() == 3;
+    TORCH_CHECK(ub || x1.dim() == 4, "x1 must be 3-D (unbatched) or 4-D (batched) tensor.");
+    TORCH_CHECK(x2.dim() == x1.dim(), "x2 must be 3-D (unbatched) or 4-D (batched) tensor.");
+    TORCH_CHECK(ub || x1.size(0) == x2.size(0), "batch_size of x1 and x2 do not match.");
+    TORCH_CHECK(x1.size(-1) == x2.size(-1), "feature dimension of x1 and x2 do not match.");
+    const auto dt = compute_type(in_dt);
+    Tensor a = x1.to(dt).contiguous(), b = x2.is_same(x1) ? a : x2.to(dt).contiguous();
+    if (ub) { a = a.unsqueeze(0); b = b.unsqueeze(0); }
+    const int64_t B = a.size(0), N1 = a.size(1), M1 = a.size(2), D = a.size(3), N2 = b.size(1), M2 = b.size(2);
+    c10::cuda::CUDAGuard dg(a.device());
+    Tensor out = at::empty({B, N1, N2}, a.options());
+    Tensor i1 = at::empty({B, N1, N2}, a.options().dtype(at::kLong)), i2 = at::empty_like(i1);
+    Tensor o1, o2;
+    if (shuffle && B > 0) {
+        // per batch, x1's permutation then x2's (OPS/cuda/hausdorff_kernel.cu:158-167); order[perm[t]] = t
+        o1 = at::empty({B, M1}, i1.options());
+        o2 = at::empty({B, M2}, i1.options());
+        for (int64_t bb = 0; bb < B; ++bb) {
+            Tensor p1 = at::randperm(M1, generator, i1.options()), p2 = at::randperm(M2, generator, i1.options());
+            o1[bb].index_put_({p1}, at::arange(M1, i1.options()));
+            o2[bb].index_put_({p2}, at::arange(M2, i1.options()));
+        }
+    }
+    const int64_t bytes = std::max<int64_t>(tpw_hausdorff_scratch_bytes(B, N1, N2, M1), 8);
+    Tensor scratch = at::empty({bytes}, a.options().dtype(at::kByte));
+    TPW_CALL(tpw_hausdorff_forward(code_of(a), a.data_ptr(), b.data_ptr(), o1.defined() ? o1.data_ptr<int64_t>() : nullptr,
+                                   o2.defined() ? o2.data_ptr<int64_t>() : nullptr, out.data_ptr(), i1.data_ptr<int64_t>(),
+                                   i2.data_ptr<int64_t>(), scratch.data_ptr(), B, N1, N2, M1, M2, D, stream_of(a)));
+    return {a, b, out, i1, i2, ub, in_dt};
+}
+
+// grad [B,N1,N2] (batched layout) -> one point per set and pair (OPS/cuda/hausdorff_kernel.cu:198-246)
+std::pair<Tensor, Tensor> hausdorff_grads(const Tensor &g, const Tensor &a, const Tensor &b, const Tensor &out,
+                                          const Tensor &i1, const Tensor &i2) {
+    c10::cuda::CUDAGuard dg(a.device());
+    Tensor g1 = at::empty_like(a), g2 = at::empty_like(b);
+    TPW_CALL(tpw_hausdorff_backward(code_of(a), g.data_ptr(), out.data_ptr(), i1.data_ptr<int64_t>(), i2.data_ptr<int64_t>(),
+                                    a.data_ptr(), b.data_ptr(), g1.data_ptr(), g2.data_ptr(), a.size(0), a.size(1), b.size(1),
+                                    a.size(2), b.size(2), a.size(3), stream_of(a)));
+    return {g1, g2};
+}
+
 struct HausdorffFn : torch::autograd::Function<HausdorffFn> {
     static variable_list forward(AutogradContext *ctx, const Tensor &x1, const Tensor &x2, bool shuffle,
                                  c10::optional<at::Generator> generator) {
         at::AutoDispatchBelowADInplaceOrView guard;
-        require_cuda(x1);
-        require_cuda(x2);
-        const auto in_dt = x1.scalar_type();
-        TORCH_CHECK(in_dt == x2.scalar_type(), "x1 and x2 must have the same dtype (while checking arguments for _directed_hausdorff_forward)");
-        const bool ub = x1.dim() == 3;
-        TORCH_CHECK(ub || x1.dim() == 4, "x1 must be 3-D (unbatched) or 4-D (batched) tensor.");
-        TORCH_CHECK(x2.dim() == x1.dim(), "x2 must be 3-D (unbatched) or 4-D (batched) tensor.");
-        TORCH_CHECK(ub || x1.size(0) == x2.size(0), "batch_size of x1 and x2 do not match.");
-        TORCH_CHECK(x1.size(-1) == x2.size(-1), "feature dimension of x1 and x2 do not match.");
-        const auto dt = compute_type(in_dt);
-        Tensor a = x1.to(dt).contiguous(), b = x2.is_same(x1) ? a : x2.to(dt).contiguous();
-        if (ub) { a = a.unsqueeze(0); b = b.unsqueeze(0); }
-        const int64_t B = a.size(0), N1 = a.size(1), M1 = a.size(2), D = a.size(3), N2 = b.size(1), M2 = b.size(2);
-        c10::cuda::CUDAGuard dg(a.device());
-        Tensor out = at::empty({B, N1, N2}, a.options());
-        Tensor i1 = at::empty({B, N1, N2}, a.options().dtype(at::kLong)), i2 = at::empty_like(i1);
-        Tensor o1, o2;
-        if (shuffle && B > 0) {
-            // per batch, x1's permutation then x2's (OPS/cuda/hausdorff_kernel.cu:158-167); order[perm[t]] = t
-            o1 = at::empty({B, M1}, i1.options());
-            o2 = at::empty({B, M2}, i1.options());
-            for (int64_t bb = 0; bb < B; ++bb) {
-                Tensor p1 = at::randperm(M1, generator, i1.options()), p2 = at::randperm(M2, generator, i1.options());
-                o1[bb].index_put_({p1}, at::arange(M1, i1.options()));
-                o2[bb].index_put_({p2}, at::arange(M2, i1.options()));
-            }
-        }
-        const int64_t bytes = std::max<int64_t>(tpw_hausdorff_scratch_bytes(B, N1, N2, M1), 8);
-        Tensor scratch = at::empty({bytes}, a.options().dtype(at::kByte));
-        TPW_CALL(tpw_hausdorff_forward(code_of(a), a.data_ptr(), b.data_ptr(), o1.defined() ? o1.data_ptr<int64_t>() : nullptr,
-                                       o2.defined() ? o2.data_ptr<int64_t>() : nullptr, out.data_ptr(), i1.data_ptr<int64_t>(),
-                                       i2.data_ptr<int64_t>(), scratch.data_ptr(), B, N1, N2, M1, M2, D, stream_of(a)));
+        HausdorffRun r0 = hausdorff_run(x1, x2, shuffle, generator);
+        const Tensor &a = r0.a, &b = r0.b, &out = r0.out, &i1 = r0.i1, &i2 = r0.i2;
+        const bool ub = r0.unbatched;
+        const auto in_dt = r0.in_dt;
         ctx->save_for_backward({a, b, out, i1, i2});
         ctx->saved_data["unbatched"] = ub;
         ctx->saved_data["dt"] = static_cast<int64_t>(in_dt);
@@ -450,13 +477,10 @@ struct HausdorffFn : torch::autograd::Function<HausdorffFn> {
         const Tensor &a = s[0], &b = s[1], &out = s[2], &i1 = s[3], &i2 = s[4];
         const bool ub = ctx->saved_data["unbatched"].toBool();
         const auto dt = static_cast<at::ScalarType>(ctx->saved_data["dt"].toInt());
-        c10::cuda::CUDAGuard dg(a.device());
         Tensor g = go[0].to(a.scalar_type()).contiguous();
         if (ub) g = g.unsqueeze(0);
-        Tensor g1 = at::empty_like(a), g2 = at::empty_like(b);
-        TPW_CALL(tpw_hausdorff_backward(code_of(a), g.data_ptr(), out.data_ptr(), i1.data_ptr<int64_t>(), i2.data_ptr<int64_t>(),
-                                        a.data_ptr(), b.data_ptr(), g1.data_ptr(), g2.data_ptr(), a.size(0), a.size(1), b.size(1),
-                                        a.size(2), b.size(2), a.size(3), stream_of(a)));
+        auto gg = hausdorff_grads(g, a, b, out, i1, i2);
+        const Tensor &g1 = gg.first, &g2 = gg.second;
         return {finish(g1, ub, dt), finish(g2, ub, dt), Tensor(), Tensor()};
     }
 };
@@ -651,8 +675,170 @@ Tensor cdist(const Tensor &x1, const Tensor &x2, c10::string_view metric, const 
     TORCH_CHECK_NOT_IMPLEMENTED(false, "metric '", m, "' is outside the B200 pairwise-reduction path of this library");
 }
 
-bool defined(const char *name) {
-    return c10::Dispatcher::singleton().findSchema({std::string("torchpairwise::") + name, ""}).has_value();
+// ---- prf_div family (OPS/prf_div.cpp:359-400, OPS/cuda/prf_div_kernel.cu, OPS/autograd/prf_div_kernel.cpp) -----
+// Every overload is "numerator / denominator where the denominator is non-zero, else 0 (zero) or the
+// numerator (identity)": prf_div(self, other) = self / other, prf_ldiv(self, other) = other / self.  A Scalar
+// operand is expanded to a tensor of the other operand's shape before the element-wise kernel.
+int prf_mode(c10::string_view mode) {
+    if (mode == "zero") return TPW_PRF_ZERO;
+    if (mode == "identity") return TPW_PRF_IDENTITY;
+    TORCH_CHECK(false, "mode must be either zero or identity. Got ", mode);
+}
+
+at::ScalarType prf_result_type(at::ScalarType t) {
+    return at::isIntegralType(t, /*includeBool=*/true) ? at::kFloat : t;   // OPS/cuda/prf_div_kernel.cu:93-95
+}
+
+void prf_same_shape(const Tensor &self, const Tensor &other) {
+    TORCH_CHECK(self.sizes() == other.sizes(), "Broadcasting semantic is not implemented for prf_div. "
+                "Expect self's shape to be identical to other's shape. Got self.shape=", self.sizes(),
+                ", while other.shape=", other.sizes());
+}
+
+// num, den: same shape, any dtype; the kernel runs in float32 or float64 and the result has dtype `rt`.
+Tensor prf_raw_forward(const Tensor &num, const Tensor &den, int mode, at::ScalarType rt) {
+    require_cuda(num);
+    require_cuda(den);
+    TORCH_CHECK(num.get_device() == den.get_device(), "Expected all tensors to be on the same device");
+    const auto ct = compute_type(rt);
+    Tensor n = num.to(ct).contiguous(), d = den.to(ct).contiguous();
+    c10::cuda::CUDAGuard dg(n.device());
+    Tensor out = at::empty_like(n);
+    TPW_CALL(tpw_prf_div_forward(code_of(n), mode, n.data_ptr(), d.data_ptr(), out.data_ptr(), n.numel(), stream_of(n)));
+    return out.to(rt);
+}
+
+// (grad_num, grad_den) in grad's dtype; an unwanted one stays undefined.
+std::pair<Tensor, Tensor> prf_raw_backward(const Tensor &grad, const Tensor &num, const Tensor &den, int mode,
+                                           bool want_num, bool want_den) {
+    require_cuda(grad);
+    const auto rt = grad.scalar_type();
+    const auto ct = compute_type(rt);
+    Tensor g = grad.to(ct).contiguous(), n = num.to(ct).contiguous(), d = den.to(ct).contiguous();
+    c10::cuda::CUDAGuard dg(g.device());
+    Tensor gn = want_num ? at::empty_like(g) : Tensor(), gd = want_den ? at::empty_like(g) : Tensor();
+    TPW_CALL(tpw_prf_div_backward(code_of(g), mode, g.data_ptr(), n.data_ptr(), d.data_ptr(), want_num ? gn.data_ptr() : nullptr,
+                                  want_den ? gd.data_ptr() : nullptr, g.numel(), stream_of(g)));
+    return {want_num ? gn.to(rt) : gn, want_den ? gd.to(rt) : gd};
+}
+
+Tensor scalar_like(const Tensor &t, const at::Scalar &v, at::ScalarType dt) { return at::full_like(t, v, t.options().dtype(dt)); }
+
+struct PRFDivFn : torch::autograd::Function<PRFDivFn> {
+    static Tensor forward(AutogradContext *ctx, const Tensor &num, const Tensor &den, int64_t mode, int64_t rt) {
+        at::AutoDispatchBelowADInplaceOrView guard;
+        ctx->save_for_backward({num, den});
+        ctx->saved_data["mode"] = mode;
+        return prf_raw_forward(num, den, static_cast<int>(mode), static_cast<at::ScalarType>(rt));
+    }
+    static variable_list backward(AutogradContext *ctx, variable_list go) {
+        auto s = ctx->get_saved_variables();
+        auto g = prf_raw_backward(go[0], s[0], s[1], static_cast<int>(ctx->saved_data["mode"].toInt()),
+                                  ctx->needs_input_grad(0), ctx->needs_input_grad(1));
+        if (g.first.defined()) g.first = g.first.to(s[0].scalar_type());
+        if (g.second.defined()) g.second = g.second.to(s[1].scalar_type());
+        return {g.first, g.second, Tensor(), Tensor()};
+    }
+};
+
+// In place on `self` (OPS/cuda/prf_div_kernel.cu:189-300; the kernels return at::Tensor by value, as the
+// reference's do, so that both libraries can be registered on one schema): `left` selects self = other / self.  The operands are
+// saved before `self` is overwritten, so the gradient is that of the out-of-place op.
+struct PRFDivInplaceFn : torch::autograd::Function<PRFDivInplaceFn> {
+    static Tensor forward(AutogradContext *ctx, Tensor &self, const Tensor &other, int64_t mode, bool left) {
+        at::AutoDispatchBelowADInplaceOrView guard;
+        const auto rt = prf_result_type(at::result_type(self, other));
+        TORCH_CHECK(at::can_cast(rt, self.scalar_type()), "result type ", rt, " can't be cast to the desired output type ",
+                    self.scalar_type());
+        ctx->mark_dirty({self});
+        const bool track = self.requires_grad() || other.requires_grad();
+        Tensor before = track ? self.clone() : self;
+        const Tensor &num = left ? other : before, &den = left ? before : other;
+        if (track) ctx->save_for_backward({num, den});
+        ctx->saved_data["mode"] = mode;
+        ctx->saved_data["left"] = left;
+        self.copy_(prf_raw_forward(left ? other : self, left ? self : other, static_cast<int>(mode), rt));
+        return self;
+    }
+    static variable_list backward(AutogradContext *ctx, variable_list go) {
+        auto s = ctx->get_saved_variables();
+        const bool left = ctx->saved_data["left"].toBool();
+        // inputs are (self, other); saved are (numerator, denominator)
+        const bool want_num = ctx->needs_input_grad(left ? 1 : 0), want_den = ctx->needs_input_grad(left ? 0 : 1);
+        auto g = prf_raw_backward(go[0], s[0], s[1], static_cast<int>(ctx->saved_data["mode"].toInt()), want_num, want_den);
+        if (g.first.defined()) g.first = g.first.to(s[0].scalar_type());
+        if (g.second.defined()) g.second = g.second.to(s[1].scalar_type());
+        return {left ? g.second : g.first, left ? g.first : g.second, Tensor(), Tensor()};
+    }
+};
+
+template <bool left>
+Tensor prf_div_tensor(const Tensor &self, const Tensor &other, c10::string_view mode) {
+    prf_same_shape(self, other);
+    const auto rt = static_cast<int64_t>(prf_result_type(at::result_type(self, other)));
+    return left ? PRFDivFn::apply(other, self, prf_mode(mode), rt) : PRFDivFn::apply(self, other, prf_mode(mode), rt);
+}
+template <bool left>
+Tensor prf_div_scalar(const Tensor &self, const at::Scalar &other, c10::string_view mode) {
+    const auto rt = prf_result_type(at::result_type(self, other));
+    Tensor o = scalar_like(self, other, compute_type(rt));
+    return left ? PRFDivFn::apply(o, self, prf_mode(mode), static_cast<int64_t>(rt))
+                : PRFDivFn::apply(self, o, prf_mode(mode), static_cast<int64_t>(rt));
+}
+// prf_div.rScalar(s, t) = s / t; prf_ldiv.rScalar(s, t) = t / s (OPS/cuda/prf_div_kernel.cu:181-187)
+template <bool left>
+Tensor prf_div_rscalar(const at::Scalar &self, const Tensor &other, c10::string_view mode) {
+    return prf_div_scalar<!left>(other, self, mode);
+}
+template <bool left>
+Tensor prf_div_inplace(Tensor &self, const Tensor &other, c10::string_view mode) {
+    prf_same_shape(self, other);
+    PRFDivInplaceFn::apply(self, other, prf_mode(mode), left);
+    return self;
+}
+template <bool left>
+Tensor prf_div_inplace_scalar(Tensor &self, const at::Scalar &other, c10::string_view mode) {
+    const auto rt = prf_result_type(at::result_type(self, other));
+    PRFDivInplaceFn::apply(self, scalar_like(self, other, compute_type(rt)), prf_mode(mode), left);
+    return self;
+}
+
+// The stand-alone backward ops (OPS/cuda/prf_div_kernel.cu:372-520); gradients in the operands' dtypes.
+template <bool left>
+std::tuple<Tensor, Tensor> prf_div_backward_op(const Tensor &grad, const Tensor &self, const Tensor &other, c10::string_view mode) {
+    auto g = left ? prf_raw_backward(grad, other, self, prf_mode(mode), true, true)
+                  : prf_raw_backward(grad, self, other, prf_mode(mode), true, true);
+    const Tensor &gs = left ? g.second : g.first, &go = left ? g.first : g.second;
+    return std::make_tuple(gs.to(self.scalar_type()), go.to(other.scalar_type()));
+}
+template <bool left>
+Tensor prf_div_backward_scalar_op(const Tensor &grad, const Tensor &self, const at::Scalar &other, c10::string_view mode) {
+    Tensor o = scalar_like(self, other, compute_type(grad.scalar_type()));
+    auto g = left ? prf_raw_backward(grad, o, self, prf_mode(mode), false, true)
+                  : prf_raw_backward(grad, self, o, prf_mode(mode), true, false);
+    return (left ? g.second : g.first).to(self.scalar_type());
+}
+template <bool left>
+Tensor prf_div_backward_rscalar_op(const Tensor &grad, const at::Scalar &self, const Tensor &other, c10::string_view mode) {
+    Tensor sc = scalar_like(other, self, compute_type(grad.scalar_type()));
+    auto g = left ? prf_raw_backward(grad, other, sc, prf_mode(mode), true, false)
+                  : prf_raw_backward(grad, sc, other, prf_mode(mode), false, true);
+    return (left ? g.first : g.second).to(other.scalar_type());
+}
+
+// __directed_hausdorff_backward re-runs the forward for the attaining pair, as the reference's backward op does
+// (OPS/cuda/hausdorff_kernel.cu:283-321).
+std::tuple<Tensor, Tensor> directed_hausdorff_backward_op(const Tensor &grad, const Tensor &x1, const Tensor &x2, bool shuffle,
+                                                         c10::optional<at::Generator> generator) {
+    HausdorffRun r = hausdorff_run(x1, x2, shuffle, generator);
+    Tensor g = grad.to(r.a.scalar_type()).contiguous();
+    if (r.unbatched) g = g.unsqueeze(0);
+    auto gg = hausdorff_grads(g, r.a, r.b, r.out, r.i1, r.i2);
+    return std::make_tuple(finish(gg.first, r.unbatched, r.in_dt), finish(gg.second, r.unbatched, r.in_dt));
+}
+
+bool defined(const char *name, const char *overload = "") {
+    return c10::Dispatcher::singleton().findSchema({std::string("torchpairwise::") + name, overload}).has_value();
 }
 
 #define OPT2 "(Tensor x1, Tensor? x2=None) -> Tensor"
@@ -681,6 +867,31 @@ TORCH_LIBRARY_FRAGMENT(torchpairwise, m) {
         "(Tensor x1, Tensor x2, *, bool shuffle=False, Generator? generator=None) -> (Tensor output, Tensor x1_indices, Tensor x2_indices)");
     for (const char *n : {"pwand_sum", "pwor_sum", "pwxor_sum", "pweq_sum", "pwne_sum", "pweq_mean", "pwne_mean"})
         def(n, "(Tensor x1, Tensor x2) -> Tensor");
+    def("__directed_hausdorff_backward",
+        "(Tensor grad, Tensor x1, Tensor x2, *, bool shuffle=False, Generator? generator=None) -> (Tensor grad_x1, Tensor grad_x2)");
+    // OPS/prf_div.cpp:359-400
+    auto def_ov = [&](const char *name, const char *overload, const char *sig) {
+        if (defined(name, overload))
+            return;
+        std::string full = std::string("torchpairwise::") + name;
+        if (overload[0]) full += std::string(".") + overload;
+        m.def((full + sig).c_str());
+    };
+    for (const char *n : {"prf_div", "prf_ldiv"}) {
+        def_ov(n, "", "(Tensor input, Tensor other, str mode=\"zero\") -> Tensor");
+        def_ov(n, "Scalar", "(Tensor input, Scalar other, str mode=\"zero\") -> Tensor");
+        def_ov(n, "rScalar", "(Scalar input, Tensor other, str mode=\"zero\") -> Tensor");
+    }
+    for (const char *n : {"prf_div_", "prf_ldiv_"}) {
+        def_ov(n, "", "(Tensor(a!) input, Tensor other, str mode=\"zero\") -> Tensor(a!)");
+        def_ov(n, "Scalar", "(Tensor(a!) input, Scalar other, str mode=\"zero\") -> Tensor(a!)");
+    }
+    for (const char *n : {"_prf_div_backward", "_prf_ldiv_backward", "_prf_div__backward", "_prf_ldiv__backward"}) {
+        def_ov(n, "", "(Tensor grad, Tensor self, Tensor other, str mode=\"zero\") -> (Tensor grad_self, Tensor grad_other)");
+        def_ov(n, "Scalar", "(Tensor grad, Tensor self, Scalar other, str mode=\"zero\") -> Tensor grad_self");
+    }
+    for (const char *n : {"_prf_div_backward", "_prf_ldiv_backward"})
+        def_ov(n, "rScalar", "(Tensor grad, Scalar self, Tensor other, str mode=\"zero\") -> Tensor grad_other");
     def("cdist", "(Tensor x1, Tensor x2, str metric=\"minkowski\", *, Tensor? w=None, Tensor? V=None, Tensor? VI=None, "
                  "float? p=None, float? base=None, bool? shuffle=None, Generator? generator=None) -> Tensor");
 }
@@ -717,6 +928,16 @@ TORCH_LIBRARY_IMPL(torchpairwise, AutogradCUDA, m) {
     m.impl("_wminkowski", wminkowski);
     m.impl("_directed_hausdorff", directed_hausdorff_raw);
     m.impl("cdist", cdist);
+    m.impl("prf_div", prf_div_tensor<false>);
+    m.impl("prf_ldiv", prf_div_tensor<true>);
+    m.impl("prf_div.Scalar", prf_div_scalar<false>);
+    m.impl("prf_ldiv.Scalar", prf_div_scalar<true>);
+    m.impl("prf_div.rScalar", prf_div_rscalar<false>);
+    m.impl("prf_ldiv.rScalar", prf_div_rscalar<true>);
+    m.impl("prf_div_", prf_div_inplace<false>);
+    m.impl("prf_ldiv_", prf_div_inplace<true>);
+    m.impl("prf_div_.Scalar", prf_div_inplace_scalar<false>);
+    m.impl("prf_ldiv_.Scalar", prf_div_inplace_scalar<true>);
 }
 
 // Ops without a gradient, and the stand-alone backward ops the reference's own Autograd kernels call.
@@ -742,6 +963,17 @@ TORCH_LIBRARY_IMPL(torchpairwise, CUDA, m) {
         return std::make_tuple(finish(std::get<0>(g), q.unbatched, dt), finish(std::get<1>(g), q.unbatched, dt),
                                finish(std::get<2>(g), q.unbatched, dt));
     });
+    m.impl("__directed_hausdorff_backward", directed_hausdorff_backward_op);
+    m.impl("_prf_div_backward", prf_div_backward_op<false>);
+    m.impl("_prf_ldiv_backward", prf_div_backward_op<true>);
+    m.impl("_prf_div_backward.Scalar", prf_div_backward_scalar_op<false>);
+    m.impl("_prf_ldiv_backward.Scalar", prf_div_backward_scalar_op<true>);
+    m.impl("_prf_div_backward.rScalar", prf_div_backward_rscalar_op<false>);
+    m.impl("_prf_ldiv_backward.rScalar", prf_div_backward_rscalar_op<true>);
+    m.impl("_prf_div__backward", prf_div_backward_op<false>);
+    m.impl("_prf_ldiv__backward", prf_div_backward_op<true>);
+    m.impl("_prf_div__backward.Scalar", prf_div_backward_scalar_op<false>);
+    m.impl("_prf_ldiv__backward.Scalar", prf_div_backward_scalar_op<true>);
 }
 
 } // namespace

@@ -466,6 +466,44 @@ def run_suite(args):
             out.backward(G, retain_graph=True)
         entry("C2_canberra_bwd", n, timeit(bwdc), "fp32_issue (two passes)", n * 256 * 2 * 8, fp32_peak, 0)
         del out
+    # Jensen-Shannon at C2 shape on non-negative rows: bound by the special-function unit (one reciprocal and two
+    # logarithms per term forward, one and one backward; 16 per clock and SM)
+    mufu_peak = fp32_peak / 8.0
+    if want("C2_jensenshannon_fwd") or want("C2_jensenshannon_bwd"):
+        Hx, Hy = X.detach().abs().requires_grad_(True), Y.detach().abs().requires_grad_(True)
+        if want("C2_jensenshannon_fwd"):
+            with torch.no_grad():
+                entry("C2_jensenshannon_fwd", n, timeit(lambda: tpw.jensenshannon_distances(Hx, Hy)), "mufu (3 per term)", n * 256 * 3, mufu_peak, 4 * n)
+        if want("C2_jensenshannon_bwd"):
+            out = tpw.jensenshannon_distances(Hx, Hy)
+
+            def bwdj():
+                Hx.grad = None
+                Hy.grad = None
+                out.backward(G, retain_graph=True)
+            entry("C2_jensenshannon_bwd", n, timeit(bwdj), "mufu (two passes, 2 per term)", n * 256 * 2 * 2, mufu_peak, 0)
+            del out
+        del Hx, Hy
+    # haversine on (latitude, longitude) rows: D = 2, the forward writes 4 bytes per pair, the backward reads 4
+    if want("haversine_fwd") or want("haversine_bwd"):
+        scale = torch.tensor([math.pi, 2 * math.pi])
+        P1 = ((torch.rand(32768, 2, generator=g) - 0.5) * scale).to(dev).requires_grad_(True)
+        P2 = ((torch.rand(16384, 2, generator=g) - 0.5) * scale).to(dev).requires_grad_(True)
+        nh = 32768 * 16384
+        if want("haversine_fwd"):
+            with torch.no_grad():
+                entry("haversine_fwd", nh, timeit(lambda: tpw.haversine_distances(P1, P2)), "hbm (output write)", 4 * nh, hbm_peak * 1e9, 4 * nh)
+        if want("haversine_bwd"):
+            out = tpw.haversine_distances(P1, P2)
+            GH = torch.randn(32768, 16384, generator=g).to(dev)
+
+            def bwdh():
+                P1.grad = None
+                P2.grad = None
+                out.backward(GH, retain_graph=True)
+            entry("haversine_bwd", nh, timeit(bwdh), "hbm (gradient read twice)", 8 * nh, hbm_peak * 1e9, 0)
+            del out, GH
+        del P1, P2
     # dense-contraction backward at C2: two tf32x3 tensor-core products per call (executed flops = 3 x 4 n D);
     # the tf32 rate is taken as half of the measured sustained bf16 rate
     for name, fn in (("C2_sqeuclidean_bwd", tpw.sqeuclidean_distances), ("C2_euclidean_bwd", tpw.euclidean_distances),

@@ -373,6 +373,39 @@ TPW_API int tpw_pair_sum_backward(int dtype, int metric, const void *grad, const
                           void *grad_x1, void *grad_x2,
                           int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream);
 
+/*
+ * Jensen-Shannon sums: out[b,i,j] = f(scale * sum_k (x log(x/m) + y log(y/m))), m = (x + y)/2, x = x1[b,i,k],
+ * y = x2[b,j,k], f = square root when take_sqrt is 1 (clamped at 0), identity when 0.  A zero entry
+ * contributes 0, a negative one +inf (OPS/cpu/rel_entr.h:9-18).  Same forward tile as the sums above.
+ * Replaces _sqjensenshannon (OPS/cpu/sqjensenshannon_kernel.cpp:13-81 and its CUDA twin) with
+ * scale = 1/(2 log base) or 1/2, and the sqrt_ of jensenshannon_distances (OPS/pairwise_metrics.cpp:326-337).
+ * Backward: `out` is the saved forward result when it was computed with take_sqrt = 1 (coefficient
+ * grad * scale / (2 out), nothing where out is 0) and NULL otherwise; the derivative of a term with respect
+ * to x is log(x/m) where x > 0 and -y/(x + y) at x == 0 (OPS/cpu/sqjensenshannon_kernel.cpp:84-141).
+ * Either gradient may be NULL.
+ */
+TPW_API int tpw_jensenshannon_forward(int dtype, const void *x1, const void *x2, void *out,
+                              int64_t B, int64_t N1, int64_t N2, int64_t D, double scale, int take_sqrt,
+                              tpw_stream_t stream);
+TPW_API int tpw_jensenshannon_backward(int dtype, const void *grad, const void *out, const void *x1, const void *x2,
+                               void *grad_x1, void *grad_x2,
+                               int64_t B, int64_t N1, int64_t N2, int64_t D, double scale, tpw_stream_t stream);
+
+/* ---- haversine ------------------------------------------------------------------------------- */
+
+/*
+ * x1 [B,N1,2], x2 [B,N2,2] = (latitude, longitude) in radians  ->  out [B,N1,N2] = 2 asin(sqrt(a)),
+ * a = sin^2(dlat/2) + cos(lat1) cos(lat2) sin^2(dlon/2), evaluated as 2 atan2(sqrt(a), sqrt(1 - a)) with 1 - a
+ * formed without cancellation (nearly antipodal pairs keep their accuracy); a point against itself gives exactly 0.  Replaces _haversine (OPS/cpu/haversine_kernel.cpp:12-75 and its CUDA twin).
+ * Backward (OPS/cpu/haversine_kernel.cpp:77-217): grad_x1 [B,N1,2], grad_x2 [B,N2,2], either may be NULL;
+ * one deterministic pass per gradient, no scratch (the reference materialises a [B,N1,N2] denominator);
+ * pairs whose denominator sqrt(a) sqrt(1 - a) is 0 contribute nothing (the reference divides by it).
+ */
+TPW_API int tpw_haversine_forward(int dtype, const void *x1, const void *x2, void *out,
+                          int64_t B, int64_t N1, int64_t N2, tpw_stream_t stream);
+TPW_API int tpw_haversine_backward(int dtype, const void *grad, const void *x1, const void *x2, void *grad_x1, void *grad_x2,
+                           int64_t B, int64_t N1, int64_t N2, tpw_stream_t stream);
+
 /* ---- directed Hausdorff ---------------------------------------------------------------------- */
 
 /*

@@ -355,6 +355,39 @@ def chi2_kernel(x1, x2, gamma=1.0):
     return np.exp(additive_chi2_kernel(x1, x2) * np.asarray(x1).dtype.type(gamma))
 
 
+def sqjensenshannon(x1, x2, base=None):
+    """sum_k rel_entr(x1, m) + rel_entr(x2, m), m = (x1 + x2)/2, divided by 2 log(base) (by 2 without a base)
+    (OPS/cpu/sqjensenshannon_kernel.cpp:13-31,75; rel_entr: v log(v/m) for v > 0, 0 at v == 0, OPS/cpu/rel_entr.h:9-18).
+    Inputs are non-negative."""
+    a, ub = _b3(x1)
+    b, _ = _b3(x2)
+    x, y = a[:, :, None, :], b[:, None, :, :]
+    m = (x + y) / a.dtype.type(2)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        tx = np.where(x > 0, x * np.log(x / m), 0)
+        ty = np.where(y > 0, y * np.log(y / m), 0)
+    out = (tx + ty).sum(-1) / a.dtype.type(2 * np.log(base) if base is not None else 2)
+    return _un(out.astype(a.dtype), ub)
+
+
+def jensenshannon(x1, x2, base=None):
+    """sqrt(sqjensenshannon) of the rows scaled to sum one (OPS/pairwise_metrics.cpp:326-337)."""
+    a, b = np.asarray(x1), np.asarray(x2)
+    return np.sqrt(sqjensenshannon(a / a.sum(-1, keepdims=True), b / b.sum(-1, keepdims=True), base))
+
+
+def haversine(x1, x2):
+    """2 asin(sqrt(sin^2(dlat/2) + cos(lat1) cos(lat2) sin^2(dlon/2))) for (latitude, longitude) rows in radians
+    (OPS/cpu/haversine_kernel.cpp:12-27)."""
+    a, ub = _b3(x1)
+    b, _ = _b3(x2)
+    two = a.dtype.type(2)
+    dlat = (a[:, :, None, 0] - b[:, None, :, 0]) / two
+    dlon = (a[:, :, None, 1] - b[:, None, :, 1]) / two
+    val = np.sin(dlat) ** 2 + np.cos(a[:, :, None, 0]) * np.cos(b[:, None, :, 0]) * np.sin(dlon) ** 2
+    return _un((two * np.arcsin(np.sqrt(val))).astype(a.dtype), ub)
+
+
 def k_neighbors_mask(dists, k):
     """True at the k + 1 smallest entries of every row (OPS/neighbors.cpp:29-33)."""
     d = np.asarray(dists)

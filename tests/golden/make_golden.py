@@ -231,10 +231,65 @@ def pair_sums_golden():
     print("pair_sums.npz", len(out), "arrays")
 
 
+def jensenshannon_golden():
+    """jensenshannon_distances and _sqjensenshannon (OPS/cpu/sqjensenshannon_kernel.cpp): non-negative
+    histograms with exact zeros (terms that vanish on one or both sides), with and without a base."""
+    out = {}
+    g = torch.Generator().manual_seed(64)
+    for tag, s1, s2, dt in (("u32", (33, 19), (21, 19), torch.float32), ("b64", (2, 9, 7), (2, 6, 7), torch.float64),
+                            ("w32", (140, 70), (131, 70), torch.float32)):
+        h1, h2 = torch.rand(*s1, generator=g, dtype=dt), torch.rand(*s2, generator=g, dtype=dt)
+        h1[..., 0, :3] = 0
+        h2[..., 1, :4] = 0
+        h2[..., 2, 2:9] = 0
+        up = torch.randn(*s1[:-1], s2[-2], generator=g, dtype=dt)
+        for k, v in (("h1", h1), ("h2", h2), ("up", up)):
+            out[f"{tag}/{k}"] = npy(v)
+        for name, base in (("nat", None), ("base2", 2.0)):
+            a, b = h1.clone().requires_grad_(True), h2.clone().requires_grad_(True)
+            r = T.jensenshannon_distances(a, b, base)
+            r.backward(up)
+            out[f"{tag}/{name}/out"], out[f"{tag}/{name}/gx1"], out[f"{tag}/{name}/gx2"] = npy(r), npy(a.grad), npy(b.grad)
+            n1, n2 = h1 / h1.sum(-1, keepdim=True), h2 / h2.sum(-1, keepdim=True)
+            a, b = n1.clone().requires_grad_(True), n2.clone().requires_grad_(True)
+            r = T._sqjensenshannon(a, b, base)
+            r.backward(up)
+            out[f"{tag}/{name}/sq_out"], out[f"{tag}/{name}/sq_gx1"], out[f"{tag}/{name}/sq_gx2"] = npy(r), npy(a.grad), npy(b.grad)
+        out[f"{tag}/self_out"] = npy(T.jensenshannon_distances(h1, None, None))
+        if len(s1) == 2:
+            out[f"{tag}/cdist_base3"] = npy(T.cdist(h1, h2, "jensenshannon", base=3.0))
+    np.savez_compressed(HERE / "jensenshannon.npz", **out)
+    print("jensenshannon.npz", len(out), "arrays")
+
+
+def haversine_golden():
+    """haversine_distances (OPS/cpu/haversine_kernel.cpp): latitudes in [-pi/2, pi/2], longitudes in [-pi, pi]."""
+    out = {}
+    g = torch.Generator().manual_seed(65)
+    for tag, s1, s2, dt in (("u32", (37, 2), (23, 2), torch.float32), ("b64", (2, 9, 2), (2, 6, 2), torch.float64),
+                            ("w32", (150, 2), (261, 2), torch.float32)):
+        scale = torch.tensor([math.pi, 2 * math.pi], dtype=dt)
+        x1 = (torch.rand(*s1, generator=g, dtype=dt) - 0.5) * scale
+        x2 = (torch.rand(*s2, generator=g, dtype=dt) - 0.5) * scale
+        up = torch.randn(*s1[:-1], s2[-2], generator=g, dtype=dt)
+        for k, v in (("x1", x1), ("x2", x2), ("up", up)):
+            out[f"{tag}/{k}"] = npy(v)
+        a, b = x1.clone().requires_grad_(True), x2.clone().requires_grad_(True)
+        r = T.haversine_distances(a, b)
+        r.backward(up)
+        out[f"{tag}/out"], out[f"{tag}/gx1"], out[f"{tag}/gx2"] = npy(r), npy(a.grad), npy(b.grad)
+        out[f"{tag}/self_out"] = npy(T.haversine_distances(x1, None))
+        if tag == "u32":
+            out[f"{tag}/cdist"] = npy(T.cdist(x1, x2, "haversine"))
+    np.savez_compressed(HERE / "haversine.npz", **out)
+    print("haversine.npz", len(out), "arrays")
+
+
 if __name__ == "__main__":
     torch.set_num_threads(8)
     which = set(sys.argv[1:])
     for name, fn in (("float", float_golden), ("bool", bool_golden), ("hausdorff", hausdorff_golden), ("configs", config_golden),
-                     ("extras", extras_golden), ("composed", composed_golden), ("pair_sums", pair_sums_golden)):
+                     ("extras", extras_golden), ("composed", composed_golden), ("pair_sums", pair_sums_golden),
+                     ("jensenshannon", jensenshannon_golden), ("haversine", haversine_golden)):
         if not which or name in which:
             fn()

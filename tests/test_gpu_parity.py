@@ -285,7 +285,7 @@ def test_cdist_dispatcher(tpw):
         tpw.cdist(x1, x2, "euclidean", p=3.0)
     with pytest.raises(RuntimeError, match="unkown distance metric"):
         tpw.cdist(x1, x2, "nope")
-    with pytest.raises(NotImplementedError, match="outside"):
+    with pytest.raises(RuntimeError, match="feature dimension of x1 and x2 must be 2"):
         tpw.pdist(x1, "haversine")
 
 
@@ -927,6 +927,100 @@ def test_pair_sum_metrics_golden(tpw, golden, tag):
         close(o, O.canberra(z1.detach().cpu().numpy(), z2.cpu().numpy()), tol, msg="canberra with a zero feature")
         o.sum().backward()
         assert torch.isfinite(z1.grad).all() and float(z1.grad[:, 3].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("tag", ["u32", "b64", "w32"])
+def test_jensenshannon_golden(tpw, golden, tag):
+    """jensenshannon_distances (fused scale and root) and _sqjensenshannon against the reference's outputs and
+    gradients, with and without a base; zero entries on one or both sides; a set against itself."""
+    G = golden("jensenshannon")
+    dt = torch.float32 if tag != "b64" else torch.float64
+    tol = TOL[dt]
+    up = cuda(G[f"{tag}/up"])
+    for name, base in (("nat", None), ("base2", 2.0)):
+        h1, h2 = cuda(G[f"{tag}/h1"], True), cuda(G[f"{tag}/h2"], True)
+        out = tpw.jensenshannon_distances(h1, h2, base)
+        close(out, G[f"{tag}/{name}/out"], tol, msg="jensenshannon " + name)
+        out.backward(up)
+        close(h1.grad, G[f"{tag}/{name}/gx1"], tol, 10, "jensenshannon grad_x1 " + name)
+        close(h2.grad, G[f"{tag}/{name}/gx2"], tol, 10, "jensenshannon grad_x2 " + name)
+        n1 = (h1.detach() / h1.detach().sum(-1, keepdim=True)).requires_grad_(True)
+        n2 = (h2.detach() / h2.detach().sum(-1, keepdim=True)).requires_grad_(True)
+        sq = tpw._sqjensenshannon(n1, n2, base)
+        close(sq, G[f"{tag}/{name}/sq_out"], tol, msg="_sqjensenshannon " + name)
+        sq.backward(up)
+        close(n1.grad, G[f"{tag}/{name}/sq_gx1"], tol, 10, "_sqjensenshannon grad_x1 " + name)
+        close(n2.grad, G[f"{tag}/{name}/sq_gx2"], tol, 10, "_sqjensenshannon grad_x2 " + name)
+    h1 = cuda(G[f"{tag}/h1"], True)
+    own = tpw.jensenshannon_distances(h1)
+    close(own, G[f"{tag}/self_out"], tol, msg="jensenshannon self")
+    assert float(own.detach().diagonal(dim1=-2, dim2=-1).abs().max()) == 0.0
+    own.sum().backward()           # the zero diagonal contributes nothing instead of dividing by it
+    assert torch.isfinite(h1.grad).all()
+    if tag == "u32":
+        close(tpw.cdist(cuda(G["u32/h1"]), cuda(G["u32/h2"]), "jensenshannon", base=3.0), G["u32/cdist_base3"], tol, msg="cdist base 3")
+        with pytest.raises(TypeError, match="incompatible arguments base"):
+            tpw.cdist(cuda(G["u32/h1"]), cuda(G["u32/h2"]), "euclidean", base=2.0)
+
+
+@pytest.mark.parametrize("tag", ["u32", "b64", "w32"])
+def test_haversine_golden(tpw, golden, tag):
+    """haversine_distances against the reference's outputs and gradients; a set against itself has an exactly
+    zero diagonal and finite gradients."""
+    G = golden("haversine")
+    dt = torch.float32 if tag != "b64" else torch.float64
+    tol = TOL[dt]
+    x1, x2 = cuda(G[f"{tag}/x1"], True), cuda(G[f"{tag}/x2"], True)
+    out = tpw.haversine_distances(x1, x2)
+    close(out, G[f"{tag}/out"], tol, msg="haversine")
+    out.backward(cuda(G[f"{tag}/up"]))
+    # The coefficient 1 / (sqrt(a) sqrt(1 - a)) grows without bound towards coincident and antipodal pairs, and
+    # the float32 reference carries its own rounding there (its float32 and float64 gradients differ by 5e-4 on
+    # these inputs).  Each term is therefore allowed a few float32 roundings of its own magnitude:
+    # |grad - ref| <= rtol |ref| + atol + 4e-6 sum |g| / (sqrt(a) sqrt(1 - a)) over the reduced index.
+    ref64 = O.haversine(G[f"{tag}/x1"].astype(np.float64), G[f"{tag}/x2"].astype(np.float64))
+    a64 = np.sin(ref64 / 2) ** 2
+    amp = np.abs(G[f"{tag}/up"].astype(np.float64)) / np.maximum(np.sqrt(a64 * (1 - a64)), 1e-300)
+    eps = 4e-6 if dt == torch.float32 else 1e-14
+    for got, key, axis in ((x1.grad, "gx1", -1), (x2.grad, "gx2", -2)):
+        ref = G[f"{tag}/{key}"].astype(np.float64)
+        bound = tol["rtol"] * np.abs(ref) + tol["atol"] + eps * amp.sum(axis)[..., None]
+        err = np.abs(got.cpu().numpy().astype(np.float64) - ref)
+        assert (err <= bound).all(), ("haversine " + key, float((err / bound).max()))
+    y = cuda(G[f"{tag}/x1"], True)
+    own = tpw.haversine_distances(y)
+    close(own, G[f"{tag}/self_out"], tol, msg="haversine self")
+    assert float(own.detach().diagonal(dim1=-2, dim2=-1).abs().max()) == 0.0
+    own.sum().backward()
+    assert torch.isfinite(y.grad).all()
+    if tag == "u32":
+        close(tpw.cdist(x1.detach(), x2.detach(), "haversine"), G["u32/cdist"], tol, msg="cdist haversine")
+        with pytest.raises(RuntimeError, match="feature dimension of x1 and x2 must be 2"):
+            tpw.haversine_distances(torch.zeros(4, 3, device="cuda"))
+
+
+def test_haversine_large_identities(tpw):
+    """At a size no CPU loop finishes quickly: symmetry, the triangle inequality through a third set, the range
+    [0, pi], and the backward of sum(out) against a float64 run of the same kernels."""
+    g = torch.Generator().manual_seed(70)
+    scale = torch.tensor([math.pi, 2 * math.pi])
+    x1 = ((torch.rand(3001, 2, generator=g) - 0.5) * scale).cuda()
+    x2 = ((torch.rand(2050, 2, generator=g) - 0.5) * scale).cuda()
+    d12, d21 = tpw.haversine_distances(x1, x2), tpw.haversine_distances(x2, x1)
+    assert torch.equal(d12, d21.t())
+    assert float(d12.min()) >= 0.0 and float(d12.max()) <= math.pi + 1e-6
+    x3 = x2[:64]
+    via = (tpw.haversine_distances(x1, x3).unsqueeze(1) + tpw.haversine_distances(x2, x3).unsqueeze(0)).min(-1).values
+    assert bool((d12 <= via + 2e-3).all())   # nearly antipodal pairs are ill-conditioned in float32 (asin near 1)
+    # gradients on one octant of the sphere: no pair is close to antipodal, where the coefficient is unbounded
+    x1, x2 = x1.abs() * 0.45, x2.abs() * 0.45
+    a, b = x1.clone().requires_grad_(True), x2.clone().requires_grad_(True)
+    tpw.haversine_distances(a, b).sum().backward()
+    c, d = x1.double().requires_grad_(True), x2.double().requires_grad_(True)
+    tpw.haversine_distances(c, d).sum().backward()
+    for got, ref in ((a.grad, c.grad), (b.grad, d.grad)):
+        bound = 1e-4 * ref.abs() + 1e-3 * ref.abs().median()   # sums over thousands of pairs, some nearly antipodal
+        assert bool(((got.double() - ref).abs() <= bound).all())
 
 
 def test_bounded_wait_reports_instead_of_hanging(tpw):

@@ -112,7 +112,7 @@ def test_hausdorff_and_cdist_dispatcher(T):
     with pytest.raises(RuntimeError, match="unkown distance metric"):
         T.cdist(x1.cuda(), x2.cuda(), "nope")
     with pytest.raises(NotImplementedError):
-        T.cdist(x1.cuda(), x2.cuda(), "canberra")
+        T.cdist(x1.cuda(), x2.cuda(), "mahalanobis", VI=torch.eye(8).cuda())
 
 
 def test_prf_div_family_and_hausdorff_backward_op(T):
@@ -179,6 +179,79 @@ def test_prf_div_family_and_hausdorff_backward_op(T):
     g1, g2 = T.__directed_hausdorff_backward(gu.cuda(), s1.cuda(), s2.cuda())
     torch.testing.assert_close(g1.cpu(), r1, rtol=1e-4, atol=1e-5)
     torch.testing.assert_close(g2.cpu(), r2, rtol=1e-4, atol=1e-5)
+
+
+def test_jensenshannon_and_haversine_ops(T):
+    """jensenshannon_distances / _sqjensenshannon and haversine_distances / _haversine with their gradients, the
+    stand-alone backward ops and the cdist spellings: the reference on CPU tensors, these kernels on CUDA tensors."""
+    g = torch.Generator().manual_seed(17)
+    h1, h2 = torch.rand(31, 24, generator=g), torch.rand(27, 24, generator=g)
+    h1[0, :5] = 0
+    h2[1, 3:9] = 0
+    up = torch.randn(31, 27, generator=g)
+    scale = torch.tensor([math.pi, 2 * math.pi])
+    p1, p2 = (torch.rand(31, 2, generator=g) - 0.5) * scale, (torch.rand(27, 2, generator=g) - 0.5) * scale
+    n1, n2 = h1 / h1.sum(-1, keepdim=True), h2 / h2.sum(-1, keepdim=True)
+    for fn, x1, x2 in ((lambda a, b: T.jensenshannon_distances(a, b, None), h1, h2),
+                       (lambda a, b: T.jensenshannon_distances(a, b, 2.0), h1, h2),
+                       (lambda a, b: T._sqjensenshannon(a, b, 3.0), n1, n2),
+                       (lambda a, b: T.haversine_distances(a, b), p1, p2),
+                       (lambda a, b: T._haversine(a, b), p1, p2)):
+        res = []
+        for dev in ("cpu", "cuda"):
+            a, b = x1.detach().clone().to(dev).requires_grad_(True), x2.detach().clone().to(dev).requires_grad_(True)
+            out = fn(a, b)
+            out.backward(up.to(dev))
+            res.append((out.detach().cpu(), a.grad.cpu(), b.grad.cpu()))
+        torch.testing.assert_close(res[1][0], res[0][0], rtol=1e-4, atol=1e-5)
+        torch.testing.assert_close(res[1][1], res[0][1], rtol=1e-4, atol=1e-4)
+        torch.testing.assert_close(res[1][2], res[0][2], rtol=1e-4, atol=1e-4)
+    for ref, got in ((T.__sqjensenshannon_backward(up, n1, n2, 2.0), T.__sqjensenshannon_backward(up.cuda(), n1.cuda(), n2.cuda(), 2.0)),
+                     (T.__haversine_backward(up, p1, p2), T.__haversine_backward(up.cuda(), p1.cuda(), p2.cuda()))):
+        for a, b in zip(got, ref):
+            torch.testing.assert_close(a.cpu(), b, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(T.cdist(h1.cuda(), h2.cuda(), "jensenshannon", base=2.0).cpu(), T.cdist(h1, h2, "jensenshannon", base=2.0),
+                               rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(T.cdist(p1.cuda(), p2.cuda(), "haversine").cpu(), T.cdist(p1, p2, "haversine"), rtol=1e-4, atol=1e-5)
+    with pytest.raises(RuntimeError, match="feature dimension of x1 and x2 must be 2"):
+        T.haversine_distances(h1.cuda(), h2.cuda())
+
+
+def test_composed_and_pair_sum_ops(T):
+    """canberra, additive_chi2 / chi2, braycurtis, snr and seuclidean through the C++ layer, with gradients, and
+    their cdist spellings: the reference on CPU tensors, these kernels on CUDA tensors."""
+    g = torch.Generator().manual_seed(18)
+    x1, x2 = torch.randn(33, 21, generator=g), torch.randn(26, 21, generator=g)
+    h1, h2 = torch.rand(33, 21, generator=g), torch.rand(26, 21, generator=g)
+    h1[0, :4] = 0
+    h2[2, :6] = 0
+    V = torch.rand(21, generator=g) + 0.2
+    up = torch.randn(33, 26, generator=g)
+    cases = ((lambda a, b: T.canberra_distances(a, b), x1, x2), (lambda a, b: T._canberra(a, b), x1, x2),
+             (lambda a, b: T.additive_chi2_kernel(a, b), h1, h2), (lambda a, b: T.chi2_kernel(a, b, 0.7), h1, h2),
+             (lambda a, b: T.braycurtis_distances(a, b), x1, x2), (lambda a, b: T.snr_distances(a, b), x1, x2),
+             (lambda a, b: T.seuclidean_distances(a, b, V.to(a.device)), x1, x2))
+    for fn, u, v in cases:
+        res = []
+        for dev in ("cpu", "cuda"):
+            a, b = u.detach().clone().to(dev).requires_grad_(True), v.detach().clone().to(dev).requires_grad_(True)
+            out = fn(a, b)
+            out.backward(up.to(dev))
+            res.append((out.detach().cpu(), a.grad.cpu(), b.grad.cpu()))
+        torch.testing.assert_close(res[1][0], res[0][0], rtol=1e-4, atol=1e-5)
+        scale = 10 * max(1.0, float(res[0][1].abs().max()))
+        torch.testing.assert_close(res[1][1], res[0][1], rtol=1e-4, atol=1e-5 * scale)
+        torch.testing.assert_close(res[1][2], res[0][2], rtol=1e-4, atol=1e-5 * scale)
+    torch.testing.assert_close(T.seuclidean_distances(x1.cuda(), None, None).cpu(), T.seuclidean_distances(x1, None, None), rtol=1e-4, atol=1e-5)
+    for ref, got in ((T.__canberra_backward(up, x1, x2), T.__canberra_backward(up.cuda(), x1.cuda(), x2.cuda())),
+                     (T.__additive_chi2_kernel_backward(up, h1, h2), T.__additive_chi2_kernel_backward(up.cuda(), h1.cuda(), h2.cuda()))):
+        for a, b in zip(got, ref):
+            torch.testing.assert_close(a.cpu(), b, rtol=1e-4, atol=1e-4)
+    for metric, kw in (("canberra", {}), ("braycurtis", {}), ("snr", {}), ("seuclidean", {"V": V})):
+        kc = {k: v.cuda() for k, v in kw.items()}
+        torch.testing.assert_close(T.cdist(x1.cuda(), x2.cuda(), metric, **kc).cpu(), T.cdist(x1, x2, metric, **kw), rtol=1e-4, atol=1e-5)
+    with pytest.raises(RuntimeError, match="must be positive"):
+        T.chi2_kernel(x1.cuda(), x2.cuda(), 1.0)
 
 
 def test_cpp_layer_agrees_with_python_layer(T):

@@ -53,8 +53,10 @@ def test_cdist_keyword_validation():
         tpw.cdist(x, x, "hamming", shuffle=True)
     with pytest.raises(RuntimeError, match="Got unkown distance metric: foo"):
         tpw.cdist(x, x, "foo")
-    with pytest.raises(NotImplementedError, match="outside"):
-        tpw.cdist(x, x, "haversine")
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        tpw.cdist(x[:, :2], x[:, :2], "haversine")
+    with pytest.raises(TypeError, match="incompatible arguments base"):
+        tpw.cdist(x, x, "haversine", base=2.0)
     # pdist validates like cdist, then needs a CUDA tensor (the reference only has a stub that raises)
     with pytest.raises(TypeError, match="incompatible arguments p"):
         tpw.pdist(x, "euclidean", p=2.0)

@@ -157,3 +157,29 @@ def test_pair_sum_metrics_match_reference(golden):
         np.testing.assert_allclose(O.additive_chi2_kernel(h1, h1), G[f"{tag}/additive_chi2_kernel/self_out"], **tol)
         np.testing.assert_allclose(O.chi2_kernel(h1, h2, 0.7), G[f"{tag}/chi2_kernel/out"], **tol)
     np.testing.assert_allclose(O.canberra(G["u32/x1"], G["u32/x2"]), G["u32/cdist_canberra"], **TOL[np.dtype("float32")])
+
+
+def test_jensenshannon_matches_reference(golden):
+    """Jensen-Shannon distance and its squared form: numpy restatement against the reference's kernel."""
+    G = golden("jensenshannon")
+    for tag in ("u32", "b64", "w32"):
+        h1, h2 = G[f"{tag}/h1"], G[f"{tag}/h2"]
+        tol = TOL[h1.dtype]
+        for name, base in (("nat", None), ("base2", 2.0)):
+            np.testing.assert_allclose(O.jensenshannon(h1, h2, base), G[f"{tag}/{name}/out"], **tol)
+            n1, n2 = h1 / h1.sum(-1, keepdims=True), h2 / h2.sum(-1, keepdims=True)
+            np.testing.assert_allclose(O.sqjensenshannon(n1, n2, base), G[f"{tag}/{name}/sq_out"], **tol)
+        self_ref = G[f"{tag}/self_out"]
+        assert float(np.abs(np.diagonal(self_ref, axis1=-2, axis2=-1)).max()) == 0.0
+    np.testing.assert_allclose(O.jensenshannon(G["u32/h1"], G["u32/h2"], 3.0), G["u32/cdist_base3"], **TOL[np.dtype("float32")])
+
+
+def test_haversine_matches_reference(golden):
+    G = golden("haversine")
+    for tag in ("u32", "b64", "w32"):
+        x1, x2 = G[f"{tag}/x1"], G[f"{tag}/x2"]
+        tol = TOL[x1.dtype]
+        np.testing.assert_allclose(O.haversine(x1, x2), G[f"{tag}/out"], **tol)
+        np.testing.assert_allclose(O.haversine(x1, x1), G[f"{tag}/self_out"], **tol)
+        assert float(np.abs(np.diagonal(G[f"{tag}/self_out"], axis1=-2, axis2=-1)).max()) == 0.0
+    np.testing.assert_allclose(O.haversine(G["u32/x1"], G["u32/x2"]), G["u32/cdist"], **TOL[np.dtype("float32")])

@@ -8,7 +8,9 @@ from ._abi import LIB_PATH, TpwError, device_status, lib, measure_issue_peak
 from .cpdist import cdist, pdist
 from .ops import (
     _directed_hausdorff,
+    _haversine,
     _ppminkowski,
+    _sqjensenshannon,
     _wminkowski,
     additive_chi2_kernel,
     braycurtis_distances,
@@ -24,7 +26,9 @@ from .ops import (
     euclidean_distances,
     get_dot_engine,
     hamming_distances,
+    haversine_distances,
     jaccard_distances,
+    jensenshannon_distances,
     k_neighbors_mask,
     kulczynski1_distances,
     kulsinski_distances,

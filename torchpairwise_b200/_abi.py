@@ -46,6 +46,10 @@ SIGNATURES = {
     "tpw_lp_pdist_forward": (_I, [_I, _P, _P, _L, _L, _L, _D, _D, _P]),
     "tpw_pair_sum_forward": (_I, [_I, _I, _P, _P, _P, _L, _L, _L, _L, _P]),
     "tpw_pair_sum_backward": (_I, [_I, _I, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P]),
+    "tpw_haversine_forward": (_I, [_I, _P, _P, _P, _L, _L, _L, _P]),
+    "tpw_haversine_backward": (_I, [_I, _P, _P, _P, _P, _P, _L, _L, _L, _P]),
+    "tpw_jensenshannon_forward": (_I, [_I, _P, _P, _P, _L, _L, _L, _L, _D, _I, _P]),
+    "tpw_jensenshannon_backward": (_I, [_I, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _D, _P]),
     "tpw_lp_backward": (_I, [_I, _I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _D, _P]),
     "tpw_wminkowski_backward_w": (_I, [_I, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _D, _P]),
     "tpw_lp_inf_backward": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _P]),

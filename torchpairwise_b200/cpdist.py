@@ -3,8 +3,8 @@
 Same metric names, the same per-metric keyword validation (a keyword the metric does not take
 raises ``TypeError`` naming it, OPS/cpdist.cpp:35-79), the same defaults (``p`` defaults to 2) and
 the same quirk that ``metric="kulsinski"`` evaluates kulczynski1 (the inline helper at
-OPS/pairwise_metrics.h:557-561 calls that functor).  Metrics outside the accelerated path raise
-``NotImplementedError``.  ``pdist``, which the reference declares but does not implement
+OPS/pairwise_metrics.h:557-561 calls that functor).  Every metric name of the reference is served.
+``pdist``, which the reference declares but does not implement
 (OPS/cpdist.cpp:233-246), is the condensed form of ``cdist(x, x)``.
 """
 from __future__ import annotations
@@ -44,9 +44,6 @@ _SCHEMAS = {
                           "-> (Tensor output, Tensor x1_indices, Tensor x2_indices)",
 }
 
-_OUT_OF_SCOPE = {"haversine", "jensenshannon"}
-
-
 def _check_extra_args(metric: str, **given) -> None:
     bad = [k for k in ("w", "V", "VI", "p", "base", "shuffle", "generator")
            if given.get(k) is not None and k not in _ACCEPTS[metric]]
@@ -64,8 +61,6 @@ def cdist(x1: Tensor, x2: Tensor, metric: str = "minkowski", *, w: Optional[Tens
     if metric not in SUPPORTED_METRICS:
         raise RuntimeError(f"Got unkown distance metric: {metric}. Supported metrics are [{', '.join(SUPPORTED_METRICS)}]")
     _check_extra_args(metric, w=w, V=V, VI=VI, p=p, base=base, shuffle=shuffle, generator=generator)
-    if metric in _OUT_OF_SCOPE:
-        raise NotImplementedError(f"metric '{metric}' is outside the B200 pairwise-reduction path of this library")
     if metric == "directed_hausdorff":
         return ops.directed_hausdorff_distances(x1, x2, shuffle=bool(shuffle) if shuffle is not None else False,
                                                 generator=generator)[0]
@@ -77,6 +72,8 @@ def cdist(x1: Tensor, x2: Tensor, metric: str = "minkowski", *, w: Optional[Tens
         return ops.seuclidean_distances(x1, x2, V)
     if metric == "mahalanobis":
         return ops.mahalanobis_distances(x1, x2, VI)
+    if metric == "jensenshannon":
+        return ops.jensenshannon_distances(x1, x2, base)
     if metric == "kulsinski":
         return ops.kulczynski1_distances(x1, x2)
     if metric == "cosine":

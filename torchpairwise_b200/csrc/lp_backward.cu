@@ -33,7 +33,8 @@ enum Phi {
     PHI_SGN_EQ = 6, // sgn(d) where |d| equals the auxiliary value, else 0
     // derivatives of symmetric two-argument terms with respect to the register-resident operand x
     PHI_CANBERRA = 7, // sgn(d)/n - sgn(x)|d|/n^2, n = |x| + |y| (0 where n == 0)
-    PHI_CHI2 = 8      // t^2 - 2t, t = d/(x + y) (0 where x + y == 0): d/dx of -(x - y)^2/(x + y)
+    PHI_CHI2 = 8,     // t^2 - 2t, t = d/(x + y) (0 where x + y == 0): d/dx of -(x - y)^2/(x + y)
+    PHI_JS = 9        // log(2x/(x + y)) where x > 0, else -y/(x + y) (0 where x + y == 0)
 };
 
 enum CoefMode { COEF_G = 0, COEF_DIV_O = 1, COEF_DIV_O2 = 2, COEF_DIV_POW = 3, COEF_MUL = 4, COEF_ZERO_WHERE_O0 = 5 };
@@ -85,6 +86,12 @@ __device__ __forceinline__ double b_copysign_of(double c, double d) { return d <
 // tolerance and an order of magnitude cheaper than the IEEE sequence; fp64 keeps the exact divide
 __device__ __forceinline__ float b_div(float g, float v) { return __fdividef(g, v); }
 __device__ __forceinline__ double b_div(double g, double v) { return g / v; }
+__device__ __forceinline__ float b_log(float v) {   // flush-to-zero MUFU logarithm; callers pass normal numbers or guard the result
+    float l;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(l) : "f"(fmaxf(v, 1.17549435e-38f)));
+    return 0.693147181f * l;
+}
+__device__ __forceinline__ double b_log(double v) { return log(v); }
 __device__ __forceinline__ float b_pow(float a, double q) { return powf(a, (float)q); }
 __device__ __forceinline__ double b_pow(double a, double q) { return pow(a, q); }
 
@@ -110,6 +117,17 @@ __device__ __forceinline__ void bwd_accumulate(T &acc, T x, T y, T c, T o, T q, 
         const T r = rcp_or_zero(n);
         const T t = (x - y) * r;
         acc = b_fma(c, t * (t - T(2)), acc);
+        return;
+    }
+    if (PHI == PHI_JS) {
+        // d/dx of x log(x/m) + y log(y/m), m = (x + y)/2, is log(x/m); the reference's branches
+        // (OPS/cpu/sqjensenshannon_kernel.cpp:98-112) add up to log 2 at y == 0 and to -1 at x == 0 < y
+        const T r = rcp_or_zero(x + y);
+        // x/m = 1 + t, t = (x - y)/(x + y): exactly 1 for equal entries; where x is much smaller than y
+        // the sum 1 + t cancels, and the quotient 2x/(x + y) keeps the relative accuracy the logarithm needs
+        const T t = (x - y) * r;
+        const T ratio = b_abs(t) < T(0.5) ? T(1) + t : T(2) * x * r;
+        acc = b_fma(c, x > T(0) ? b_log(ratio) : -y * r, acc);
         return;
     }
     T d = x - y;
@@ -614,4 +632,33 @@ extern "C" int tpw_pair_sum_backward(int dtype, int metric, const void *grad, co
                                 : launch_both<double, PHI_CANBERRA, false>(P, x1, x2, grad_x1, grad_x2, s);
     return dtype == TPW_F32 ? launch_both<float, PHI_CHI2, false>(P, x1, x2, grad_x1, grad_x2, s)
                             : launch_both<double, PHI_CHI2, false>(P, x1, x2, grad_x1, grad_x2, s);
+}
+
+extern "C" int tpw_jensenshannon_backward(int dtype, const void *grad, const void *out, const void *x1, const void *x2,
+                                          void *grad_x1, void *grad_x2,
+                                          int64_t B, int64_t N1, int64_t N2, int64_t D, double scale, tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(dtype == TPW_F32 || dtype == TPW_F64, "tpw_jensenshannon_backward: dtype must be TPW_F32 or TPW_F64");
+    TPW_CHECK_ARG(B >= 0 && N1 >= 0 && N2 >= 0 && D >= 0, "tpw_jensenshannon_backward: negative size");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t es = dtype == TPW_F32 ? 4 : 8;
+    if (B * D == 0 || N1 == 0 || N2 == 0) {
+        if (grad_x1 && B * N1 * D > 0) TPW_CUDA_OK(cudaMemsetAsync(grad_x1, 0, (size_t)(B * N1 * D) * es, s));
+        if (grad_x2 && B * N2 * D > 0) TPW_CUDA_OK(cudaMemsetAsync(grad_x2, 0, (size_t)(B * N2 * D) * es, s));
+        return TPW_OK;
+    }
+    TPW_CHECK_ARG(grad && x1 && x2 && (grad_x1 || grad_x2), "tpw_jensenshannon_backward: NULL pointer");
+    BwdParams P;
+    memset(&P, 0, sizeof(P));
+    P.grad = grad; P.aux = out; P.w = nullptr;
+    P.B = B; P.N1 = N1; P.N2 = N2; P.D = D;
+    if (out) {
+        // out = sqrt(scale * sum): d out = scale / (2 out) d sum, nothing where out == 0
+        P.post = 0.5 * scale; P.coef_mode = COEF_DIV_O;
+        return dtype == TPW_F32 ? launch_both<float, PHI_JS, true>(P, x1, x2, grad_x1, grad_x2, s)
+                                : launch_both<double, PHI_JS, true>(P, x1, x2, grad_x1, grad_x2, s);
+    }
+    P.post = scale; P.coef_mode = COEF_G;
+    return dtype == TPW_F32 ? launch_both<float, PHI_JS, false>(P, x1, x2, grad_x1, grad_x2, s)
+                            : launch_both<double, PHI_JS, false>(P, x1, x2, grad_x1, grad_x2, s);
 }

@@ -97,3 +97,27 @@ extern "C" int tpw_pair_sum_forward(int dtype, int metric, const void *x1, const
         return dtype == TPW_F32 ? launch_forward<float, float, K_CANBERRA, false>(P, s) : launch_forward<double, double, K_CANBERRA, false>(P, s);
     return dtype == TPW_F32 ? launch_forward<float, float, K_CHI2, false>(P, s) : launch_forward<double, double, K_CHI2, false>(P, s);
 }
+
+extern "C" int tpw_jensenshannon_forward(int dtype, const void *x1, const void *x2, void *out,
+                                         int64_t B, int64_t N1, int64_t N2, int64_t D, double scale, int take_sqrt,
+                                         tpw_stream_t stream) {
+    clear_error();
+    TPW_CHECK_ARG(dtype == TPW_F32 || dtype == TPW_F64, "tpw_jensenshannon_forward: dtype must be TPW_F32 or TPW_F64");
+    TPW_CHECK_ARG(B >= 0 && N1 >= 0 && N2 >= 0 && D >= 0, "tpw_jensenshannon_forward: negative size");
+    TPW_CHECK_ARG(take_sqrt == 0 || take_sqrt == 1, "tpw_jensenshannon_forward: take_sqrt must be 0 or 1");
+    if (B == 0 || N1 == 0 || N2 == 0) return TPW_OK;
+    TPW_CHECK_ARG(x1 && x2 && out, "tpw_jensenshannon_forward: NULL pointer");
+    TPW_CHECK_ARG(D > 0, "tpw_jensenshannon_forward: D must be positive");
+    FwdParams P;
+    memset(&P, 0, sizeof(P));
+    P.x1 = x1; P.x2 = x2; P.out = out;
+    P.B = B; P.N1 = N1; P.N2 = N2; P.D = D;
+    P.root_mode = take_sqrt;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == TPW_F32) {
+        P.scale = scale * 0.69314718055994530942;   // the float kernel sums in units of log 2
+        return launch_forward<float, float, K_JS, false>(P, s);
+    }
+    P.scale = scale;
+    return launch_forward<double, double, K_JS, false>(P, s);
+}

@@ -20,7 +20,8 @@ enum Kind {
     K_NE = 7,     // count of x != y (IEEE compare)
     K_NE_BITS = 8, // count of differing bit patterns (integer payloads)
     K_CANBERRA = 9, // sum |x - y| / (|x| + |y|), terms with a zero denominator skipped
-    K_CHI2 = 10     // - sum (x - y)^2 / (x + y), terms with a zero denominator skipped
+    K_CHI2 = 10,    // - sum (x - y)^2 / (x + y), terms with a zero denominator skipped
+    K_JS = 11       // sum x log(x/m) + y log(y/m), m = (x + y)/2 (float: in units of log 2, scaled at the end)
 };
 
 struct FwdParams {
@@ -32,6 +33,7 @@ struct FwdParams {
     int pow_spec;        // make_pow_spec(p): how the float kernel evaluates |d|^p
     double out_exponent; // finite kinds: out = sum ^ out_exponent
     int root_mode;       // 0 none, 1 sqrt, 2 cbrt, 3 pow(out_exponent)
+    double scale;        // K_JS: factor applied to the finished sum (before the optional square root)
     int epilogue;        // K_DOT: tpw_dot_epilogue; K_NE*: bit0 = report equal count, bit1 = mean
     int vec_store;       // 4-byte outputs, N2 % 4 == 0, 16-byte aligned base: staged 128-bit stores
     int *status;
@@ -69,6 +71,19 @@ __device__ __forceinline__ float t_cbrt(float v) { return cbrtf(v); }
 __device__ __forceinline__ double t_cbrt(double v) { return cbrt(v); }
 __device__ __forceinline__ float t_pow(float v, double e) { return powf(v, (float)e); }
 __device__ __forceinline__ double t_pow(double v, double e) { return pow(v, e); }
+// One relative-entropy term v log(v/m) given q = v/m: zero at v == 0, +inf for a negative v (the
+// reference's CPU loop returns its upper bound there, OPS/cpu/rel_entr.h:9-18).  The float form is in
+// units of log 2 (one MUFU lg2); the caller folds log 2 into the final scale.
+__device__ __forceinline__ float rel_entr_term(float v, float q) {
+    // the ratio is kept above the smallest normal number, so the flush-to-zero logarithm stays finite and a
+    // zero entry gives 0 * finite = 0 without a branch
+    float l;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(l) : "f"(fmaxf(q, 1.17549435e-38f)));
+    return v >= 0.f ? v * l : __int_as_float(0x7f800000);
+}
+__device__ __forceinline__ double rel_entr_term(double v, double q) {
+    return v > 0.0 ? v * log(q) : (v == 0.0 ? 0.0 : __longlong_as_double(0x7ff0000000000000ll));
+}
 __device__ __forceinline__ bool bits_differ(float a, float b) { return __float_as_int(a) != __float_as_int(b); }
 __device__ __forceinline__ bool bits_differ(double a, double b) {
     return __double_as_longlong(a) != __double_as_longlong(b);
@@ -91,6 +106,12 @@ __device__ __forceinline__ void accumulate(T &acc, T x, T y, T w, T p, int pspec
         const T nom = x + y, d = x - y;
         const T r = rcp_or_zero(nom);
         acc = t_fma(-(d * d), r, acc);
+    } else if (KIND == K_JS) {
+        // x/m = 1 + t and y/m = 1 - t with t = (x - y)/(x + y): one reciprocal for both ratios, and equal
+        // entries give exactly log 1 = 0, so that a row against itself sums to exactly 0 as in the
+        // reference; zero padding gives two zero terms
+        const T t = (x - y) * rcp_or_zero(x + y);
+        acc += rel_entr_term(x, T(1) + t) + rel_entr_term(y, T(1) - t);
     } else {
         T d = x - y;
         if (KIND == K_L1) {
@@ -134,6 +155,9 @@ __device__ __forceinline__ OutT finish(T acc, T n1, T n2, const FwdParams &P) {
         return (OutT)cnt;
     } else if (KIND == K_MAX || KIND == K_MIN) {
         return (OutT)acc;
+    } else if (KIND == K_JS) {
+        const T v = acc * (T)P.scale;
+        return (OutT)(P.root_mode == 1 ? t_sqrt(t_max(v, T(0))) : v);
     } else {
         return (OutT)acc; // the root of the finite-p kinds is applied to the whole register tile by apply_root
     }

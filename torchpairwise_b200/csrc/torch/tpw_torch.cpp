@@ -279,6 +279,118 @@ struct PPMinkowskiFn : torch::autograd::Function<PPMinkowskiFn> {
     }
 };
 
+// ---- _sqjensenshannon / jensenshannon_distances (OPS/autograd/sqjensenshannon_kernel.cpp, OPS/pairwise_metrics.cpp:326-337)
+double js_scale(const c10::optional<double> &base) { return base.has_value() ? 0.5 / std::log(base.value()) : 0.5; }
+
+struct JensenShannonFn : torch::autograd::Function<JensenShannonFn> {
+    // rooted = false: _sqjensenshannon; true: the square root that jensenshannon_distances applies, fused
+    static Tensor forward(AutogradContext *ctx, const Tensor &x1, const Tensor &x2, double scale, bool rooted) {
+        at::AutoDispatchBelowADInplaceOrView guard;
+        const auto in_dt = x1.scalar_type();
+        TORCH_CHECK(in_dt == x2.scalar_type(), "x1 and x2 must have the same dtype (while checking arguments for _sqjensenshannon_forward)");
+        Prepared q = prepare(x1, x2, compute_type(in_dt));
+        c10::cuda::CUDAGuard dg(q.a.device());
+        Tensor out = at::empty({q.B, q.N1, q.N2}, q.a.options());
+        if (q.D == 0) out.zero_();
+        else
+            TPW_CALL(tpw_jensenshannon_forward(code_of(q.a), q.a.data_ptr(), q.b.data_ptr(), out.data_ptr(), q.B, q.N1, q.N2, q.D,
+                                               scale, rooted ? 1 : 0, stream_of(q.a)));
+        ctx->save_for_backward({q.a, q.b, rooted ? out : Tensor()});
+        ctx->saved_data["scale"] = scale;
+        ctx->saved_data["unbatched"] = q.unbatched;
+        ctx->saved_data["dt"] = static_cast<int64_t>(in_dt);
+        return finish(out, q.unbatched, in_dt);
+    }
+    static std::pair<Tensor, Tensor> raw_backward(const Tensor &grad, const Tensor &a, const Tensor &b, const Tensor &out,
+                                                  double scale, bool ub) {
+        c10::cuda::CUDAGuard dg(a.device());
+        Tensor g = grad.to(a.scalar_type()).contiguous();
+        if (ub) g = g.unsqueeze(0);
+        Tensor g1 = at::empty_like(a), g2 = at::empty_like(b);
+        TPW_CALL(tpw_jensenshannon_backward(code_of(a), g.data_ptr(), out.defined() ? out.data_ptr() : nullptr, a.data_ptr(), b.data_ptr(),
+                                            g1.data_ptr(), g2.data_ptr(), a.size(0), a.size(1), b.size(1), a.size(2), scale, stream_of(a)));
+        return {g1, g2};
+    }
+    static variable_list backward(AutogradContext *ctx, variable_list go) {
+        auto s = ctx->get_saved_variables();
+        const bool ub = ctx->saved_data["unbatched"].toBool();
+        const auto dt = static_cast<at::ScalarType>(ctx->saved_data["dt"].toInt());
+        auto g = raw_backward(go[0], s[0], s[1], s[2], ctx->saved_data["scale"].toDouble(), ub);
+        return {finish(g.first, ub, dt), finish(g.second, ub, dt), Tensor(), Tensor()};
+    }
+};
+
+// ---- _canberra, _additive_chi2_kernel (OPS/autograd/canberra_kernel.cpp, additive_chi2_kernel.cpp) ----------
+struct PairSumFn : torch::autograd::Function<PairSumFn> {
+    static Tensor forward(AutogradContext *ctx, const Tensor &x1, const Tensor &x2, int64_t metric) {
+        at::AutoDispatchBelowADInplaceOrView guard;
+        const auto in_dt = x1.scalar_type();
+        TORCH_CHECK(in_dt == x2.scalar_type(), "x1 and x2 must have the same dtype");
+        Prepared q = prepare(x1, x2, compute_type(in_dt));
+        c10::cuda::CUDAGuard dg(q.a.device());
+        Tensor out = at::empty({q.B, q.N1, q.N2}, q.a.options());
+        if (q.D == 0) out.zero_();
+        else
+            TPW_CALL(tpw_pair_sum_forward(code_of(q.a), static_cast<int>(metric), q.a.data_ptr(), q.b.data_ptr(), out.data_ptr(),
+                                          q.B, q.N1, q.N2, q.D, stream_of(q.a)));
+        ctx->save_for_backward({q.a, q.b});
+        ctx->saved_data["metric"] = metric;
+        ctx->saved_data["unbatched"] = q.unbatched;
+        ctx->saved_data["dt"] = static_cast<int64_t>(in_dt);
+        return finish(out, q.unbatched, in_dt);
+    }
+    static std::pair<Tensor, Tensor> raw_backward(const Tensor &grad, const Tensor &a, const Tensor &b, int metric, bool ub) {
+        c10::cuda::CUDAGuard dg(a.device());
+        Tensor g = grad.to(a.scalar_type()).contiguous();
+        if (ub) g = g.unsqueeze(0);
+        Tensor g1 = at::empty_like(a), g2 = at::empty_like(b);
+        TPW_CALL(tpw_pair_sum_backward(code_of(a), metric, g.data_ptr(), a.data_ptr(), b.data_ptr(), g1.data_ptr(), g2.data_ptr(),
+                                       a.size(0), a.size(1), b.size(1), a.size(2), stream_of(a)));
+        return {g1, g2};
+    }
+    static variable_list backward(AutogradContext *ctx, variable_list go) {
+        auto s = ctx->get_saved_variables();
+        const bool ub = ctx->saved_data["unbatched"].toBool();
+        const auto dt = static_cast<at::ScalarType>(ctx->saved_data["dt"].toInt());
+        auto g = raw_backward(go[0], s[0], s[1], static_cast<int>(ctx->saved_data["metric"].toInt()), ub);
+        return {finish(g.first, ub, dt), finish(g.second, ub, dt), Tensor()};
+    }
+};
+
+// ---- _haversine (OPS/autograd/haversine_kernel.cpp, kernels OPS/cpu/haversine_kernel.cpp:12-217) -------------
+struct HaversineFn : torch::autograd::Function<HaversineFn> {
+    static Tensor forward(AutogradContext *ctx, const Tensor &x1, const Tensor &x2) {
+        at::AutoDispatchBelowADInplaceOrView guard;
+        const auto in_dt = x1.scalar_type();
+        TORCH_CHECK(in_dt == x2.scalar_type(), "x1 and x2 must have the same dtype (while checking arguments for _haversine_forward)");
+        Prepared q = prepare(x1, x2, compute_type(in_dt));
+        TORCH_CHECK(q.D == 2, "feature dimension of x1 and x2 must be 2.");
+        c10::cuda::CUDAGuard dg(q.a.device());
+        Tensor out = at::empty({q.B, q.N1, q.N2}, q.a.options());
+        TPW_CALL(tpw_haversine_forward(code_of(q.a), q.a.data_ptr(), q.b.data_ptr(), out.data_ptr(), q.B, q.N1, q.N2, stream_of(q.a)));
+        ctx->save_for_backward({q.a, q.b});
+        ctx->saved_data["unbatched"] = q.unbatched;
+        ctx->saved_data["dt"] = static_cast<int64_t>(in_dt);
+        return finish(out, q.unbatched, in_dt);
+    }
+    static std::pair<Tensor, Tensor> raw_backward(const Tensor &grad, const Tensor &a, const Tensor &b, bool ub) {
+        c10::cuda::CUDAGuard dg(a.device());
+        Tensor g = grad.to(a.scalar_type()).contiguous();
+        if (ub) g = g.unsqueeze(0);
+        Tensor g1 = at::empty_like(a), g2 = at::empty_like(b);
+        TPW_CALL(tpw_haversine_backward(code_of(a), g.data_ptr(), a.data_ptr(), b.data_ptr(), g1.data_ptr(), g2.data_ptr(),
+                                        a.size(0), a.size(1), b.size(1), stream_of(a)));
+        return {g1, g2};
+    }
+    static variable_list backward(AutogradContext *ctx, variable_list go) {
+        auto s = ctx->get_saved_variables();
+        const bool ub = ctx->saved_data["unbatched"].toBool();
+        const auto dt = static_cast<at::ScalarType>(ctx->saved_data["dt"].toInt());
+        auto g = raw_backward(go[0], s[0], s[1], ub);
+        return {finish(g.first, ub, dt), finish(g.second, ub, dt)};
+    }
+};
+
 // ---- _wminkowski (OPS/autograd/wminkowski_kernel.cpp:9-50) ---------------------------------------------
 struct WMinkowskiFn : torch::autograd::Function<WMinkowskiFn> {
     static Tensor forward(AutogradContext *ctx, const Tensor &x1, const Tensor &x2, const Tensor &w, double p) {
@@ -565,116 +677,6 @@ Tensor pw_logic(const Tensor &x1, const Tensor &x2, int metric) {
     return bool_metric(x1, x2, metric);
 }
 
-// ---- public ops ------------------------------------------------------------------------------------------------
-Tensor cdist_p(const char *name, const Tensor &x1, const OptTensor &x2, double p) {
-    auto ab = check_pairwise_inputs(name, x1, x2);
-    return CdistFn::apply(ab.first, ab.second, p);
-}
-Tensor euclidean_distances(const Tensor &x1, const OptTensor &x2) { return cdist_p("euclidean_distances", x1, x2, 2.0); }
-Tensor manhattan_distances(const Tensor &x1, const OptTensor &x2) { return cdist_p("manhattan_distances", x1, x2, 1.0); }
-Tensor chebyshev_distances(const Tensor &x1, const OptTensor &x2) {
-    return cdist_p("chebyshev_distances", x1, x2, std::numeric_limits<double>::infinity());
-}
-Tensor minkowski_distances(const Tensor &x1, const OptTensor &x2, double p) { return cdist_p("minkowski_distances", x1, x2, p); }
-Tensor ppminkowski(const Tensor &x1, const Tensor &x2, double p) { return PPMinkowskiFn::apply(x1, x2, p); }
-Tensor wminkowski(const Tensor &x1, const Tensor &x2, const Tensor &w, double p) { return WMinkowskiFn::apply(x1, x2, w, p); }
-Tensor wminkowski_distances(const Tensor &x1, const OptTensor &x2, double p, const OptTensor &w) {
-    auto ab = check_pairwise_inputs("wminkowski_distances", x1, x2);
-    return w.has_value() ? WMinkowskiFn::apply(ab.first, ab.second, w.value(), p) : CdistFn::apply(ab.first, ab.second, p);
-}
-Tensor sqeuclidean_distances(const Tensor &x1, const OptTensor &x2) {
-    auto ab = check_pairwise_inputs("sqeuclidean_distances", x1, x2);
-    return PPMinkowskiFn::apply(ab.first, ab.second, 2.0);
-}
-Tensor cosine_similarity(const Tensor &x1, const OptTensor &x2) {
-    auto ab = check_pairwise_inputs("cosine_similarity", x1, x2);
-    return CosineFn::apply(ab.first, ab.second, static_cast<int64_t>(TPW_DOT_COSINE_SIM));
-}
-Tensor cosine_distances(const Tensor &x1, const OptTensor &x2) {
-    auto ab = check_pairwise_inputs("cosine_similarity", x1, x2);
-    return CosineFn::apply(ab.first, ab.second, static_cast<int64_t>(TPW_DOT_COSINE_DIST));
-}
-Tensor correlation_distances(const Tensor &x1, const OptTensor &x2) {
-    auto ab = check_pairwise_inputs("correlation_distances", x1, x2);
-    Tensor c1 = RowCenterFn::apply(ab.first);
-    Tensor c2 = x2.has_value() ? RowCenterFn::apply(ab.second) : c1;
-    return CosineFn::apply(c1, c2, static_cast<int64_t>(TPW_DOT_ONE_MINUS_SIM));
-}
-Tensor hamming_distances(const Tensor &x1, const OptTensor &x2) {
-    auto ab = check_pairwise_inputs("hamming_distances", x1, x2);
-    return pairwise_compare(ab.first, ab.second, TPW_CMP_NE, TPW_RED_MEAN);
-}
-template <int METRIC>
-Tensor boolean_metric_op(const Tensor &x1, const OptTensor &x2) {
-    static const char *names[] = {"", "", "", "", "", "", "", "jaccard_distances", "kulsinski_distances", "kulczynski1_distances",
-                                  "yule_distances", "dice_distances", "rogerstanimoto_distances", "russellrao_distances",
-                                  "sokalmichener_distances", "sokalsneath_distances"};
-    if (METRIC == TPW_BOOL_KULSINSKI)
-        TORCH_WARN_DEPRECATION("kulsinski_distances is deprecated in SciPy 1.9.0 and might be removed in the future. "
-                               "Please use kulczynski1_distances.");
-    auto ab = check_pairwise_inputs(names[METRIC], x1, x2, /*boolean=*/true);
-    return bool_metric(ab.first, ab.second, METRIC);
-}
-std::tuple<Tensor, Tensor, Tensor> directed_hausdorff_raw(const Tensor &x1, const Tensor &x2, bool shuffle,
-                                                          c10::optional<at::Generator> generator) {
-    auto r = HausdorffFn::apply(x1, x2, shuffle, generator);
-    return {r[0], r[1], r[2]};
-}
-std::tuple<Tensor, Tensor, Tensor> directed_hausdorff_distances(const Tensor &x1, const OptTensor &x2, bool shuffle,
-                                                                c10::optional<at::Generator> generator) {
-    auto ab = check_pairwise_inputs("directed_hausdorff_distances", x1, x2, false, /*sets=*/true);
-    return directed_hausdorff_raw(ab.first, ab.second, shuffle, generator);
-}
-
-// ---- cdist: string dispatcher with the reference's keyword validation (OPS/cpdist.cpp:35-79,149-231) -----------
-Tensor cdist(const Tensor &x1, const Tensor &x2, c10::string_view metric, const OptTensor &w, const OptTensor &V,
-             const OptTensor &VI, c10::optional<double> p, c10::optional<double> base, c10::optional<bool> shuffle,
-             c10::optional<at::Generator> generator) {
-    static const char *supported =
-        "braycurtis, canberra, chebyshev, cityblock, correlation, cosine, dice, directed_hausdorff, euclidean, hamming, "
-        "haversine, jaccard, jensenshannon, kulczynski1, kulsinski, l1, l2, lp, linf, mahalanobis, manhattan, minkowski, "
-        "rogerstanimoto, russellrao, seuclidean, snr, sokalmichener, sokalsneath, sqeuclidean, wminkowski, yule";
-    const std::string m(metric.data(), metric.size());
-    auto accepts = [&](const char *arg) {
-        if (m == "directed_hausdorff") return !strcmp(arg, "shuffle") || !strcmp(arg, "generator");
-        if (m == "minkowski" || m == "lp") return !strcmp(arg, "p");
-        if (m == "wminkowski") return !strcmp(arg, "w") || !strcmp(arg, "p");
-        if (m == "seuclidean") return !strcmp(arg, "V");
-        if (m == "mahalanobis") return !strcmp(arg, "VI");
-        if (m == "jensenshannon") return !strcmp(arg, "base");
-        return false;
-    };
-    std::string bad;
-    auto note = [&](bool given, const char *arg) {
-        if (given && !accepts(arg)) bad += (bad.empty() ? "" : ", ") + std::string(arg);
-    };
-    const bool known = std::string(", ").append(supported).append(", ").find(", " + m + ", ") != std::string::npos;
-    TORCH_CHECK(known, "Got unkown distance metric: ", m, ". Supported metrics are [", supported, "]");
-    note(w.has_value(), "w"); note(V.has_value(), "V"); note(VI.has_value(), "VI"); note(p.has_value(), "p");
-    note(base.has_value(), "base"); note(shuffle.has_value(), "shuffle"); note(generator.has_value(), "generator");
-    TORCH_CHECK_TYPE(bad.empty(), "torchpairwise::", m, "_distances was called with incompatible arguments ", bad, ".");
-    if (m == "euclidean" || m == "l2") return euclidean_distances(x1, x2);
-    if (m == "manhattan" || m == "cityblock" || m == "l1") return manhattan_distances(x1, x2);
-    if (m == "chebyshev" || m == "linf") return chebyshev_distances(x1, x2);
-    if (m == "minkowski" || m == "lp") return minkowski_distances(x1, x2, p.value_or(2));
-    if (m == "wminkowski") return wminkowski_distances(x1, x2, p.value_or(2), w);
-    if (m == "sqeuclidean") return sqeuclidean_distances(x1, x2);
-    if (m == "cosine") return cosine_distances(x1, x2);
-    if (m == "correlation") return correlation_distances(x1, x2);
-    if (m == "hamming") return hamming_distances(x1, x2);
-    if (m == "jaccard") return boolean_metric_op<TPW_BOOL_JACCARD>(x1, x2);
-    // the reference's cdist routes "kulsinski" through the kulczynski1 functor (OPS/pairwise_metrics.h:557-561)
-    if (m == "kulsinski" || m == "kulczynski1") return boolean_metric_op<TPW_BOOL_KULCZYNSKI1>(x1, x2);
-    if (m == "yule") return boolean_metric_op<TPW_BOOL_YULE>(x1, x2);
-    if (m == "dice") return boolean_metric_op<TPW_BOOL_DICE>(x1, x2);
-    if (m == "rogerstanimoto") return boolean_metric_op<TPW_BOOL_ROGERSTANIMOTO>(x1, x2);
-    if (m == "russellrao") return boolean_metric_op<TPW_BOOL_RUSSELLRAO>(x1, x2);
-    if (m == "sokalmichener") return boolean_metric_op<TPW_BOOL_SOKALMICHENER>(x1, x2);
-    if (m == "sokalsneath") return boolean_metric_op<TPW_BOOL_SOKALSNEATH>(x1, x2);
-    if (m == "directed_hausdorff") return std::get<0>(directed_hausdorff_distances(x1, x2, shuffle.value_or(false), generator));
-    TORCH_CHECK_NOT_IMPLEMENTED(false, "metric '", m, "' is outside the B200 pairwise-reduction path of this library");
-}
-
 // ---- prf_div family (OPS/prf_div.cpp:359-400, OPS/cuda/prf_div_kernel.cu, OPS/autograd/prf_div_kernel.cpp) -----
 // Every overload is "numerator / denominator where the denominator is non-zero, else 0 (zero) or the
 // numerator (identity)": prf_div(self, other) = self / other, prf_ldiv(self, other) = other / self.  A Scalar
@@ -826,6 +828,181 @@ Tensor prf_div_backward_rscalar_op(const Tensor &grad, const at::Scalar &self, c
     return (left ? g.first : g.second).to(other.scalar_type());
 }
 
+// ---- public ops ------------------------------------------------------------------------------------------------
+Tensor cdist_p(const char *name, const Tensor &x1, const OptTensor &x2, double p) {
+    auto ab = check_pairwise_inputs(name, x1, x2);
+    return CdistFn::apply(ab.first, ab.second, p);
+}
+Tensor euclidean_distances(const Tensor &x1, const OptTensor &x2) { return cdist_p("euclidean_distances", x1, x2, 2.0); }
+Tensor manhattan_distances(const Tensor &x1, const OptTensor &x2) { return cdist_p("manhattan_distances", x1, x2, 1.0); }
+Tensor chebyshev_distances(const Tensor &x1, const OptTensor &x2) {
+    return cdist_p("chebyshev_distances", x1, x2, std::numeric_limits<double>::infinity());
+}
+Tensor minkowski_distances(const Tensor &x1, const OptTensor &x2, double p) { return cdist_p("minkowski_distances", x1, x2, p); }
+Tensor ppminkowski(const Tensor &x1, const Tensor &x2, double p) { return PPMinkowskiFn::apply(x1, x2, p); }
+Tensor wminkowski(const Tensor &x1, const Tensor &x2, const Tensor &w, double p) { return WMinkowskiFn::apply(x1, x2, w, p); }
+Tensor wminkowski_distances(const Tensor &x1, const OptTensor &x2, double p, const OptTensor &w) {
+    auto ab = check_pairwise_inputs("wminkowski_distances", x1, x2);
+    return w.has_value() ? WMinkowskiFn::apply(ab.first, ab.second, w.value(), p) : CdistFn::apply(ab.first, ab.second, p);
+}
+Tensor sqeuclidean_distances(const Tensor &x1, const OptTensor &x2) {
+    auto ab = check_pairwise_inputs("sqeuclidean_distances", x1, x2);
+    return PPMinkowskiFn::apply(ab.first, ab.second, 2.0);
+}
+Tensor cosine_similarity(const Tensor &x1, const OptTensor &x2) {
+    auto ab = check_pairwise_inputs("cosine_similarity", x1, x2);
+    return CosineFn::apply(ab.first, ab.second, static_cast<int64_t>(TPW_DOT_COSINE_SIM));
+}
+Tensor cosine_distances(const Tensor &x1, const OptTensor &x2) {
+    auto ab = check_pairwise_inputs("cosine_similarity", x1, x2);
+    return CosineFn::apply(ab.first, ab.second, static_cast<int64_t>(TPW_DOT_COSINE_DIST));
+}
+Tensor correlation_distances(const Tensor &x1, const OptTensor &x2) {
+    auto ab = check_pairwise_inputs("correlation_distances", x1, x2);
+    Tensor c1 = RowCenterFn::apply(ab.first);
+    Tensor c2 = x2.has_value() ? RowCenterFn::apply(ab.second) : c1;
+    return CosineFn::apply(c1, c2, static_cast<int64_t>(TPW_DOT_ONE_MINUS_SIM));
+}
+Tensor hamming_distances(const Tensor &x1, const OptTensor &x2) {
+    auto ab = check_pairwise_inputs("hamming_distances", x1, x2);
+    return pairwise_compare(ab.first, ab.second, TPW_CMP_NE, TPW_RED_MEAN);
+}
+template <int METRIC>
+Tensor boolean_metric_op(const Tensor &x1, const OptTensor &x2) {
+    static const char *names[] = {"", "", "", "", "", "", "", "jaccard_distances", "kulsinski_distances", "kulczynski1_distances",
+                                  "yule_distances", "dice_distances", "rogerstanimoto_distances", "russellrao_distances",
+                                  "sokalmichener_distances", "sokalsneath_distances"};
+    if (METRIC == TPW_BOOL_KULSINSKI)
+        TORCH_WARN_DEPRECATION("kulsinski_distances is deprecated in SciPy 1.9.0 and might be removed in the future. "
+                               "Please use kulczynski1_distances.");
+    auto ab = check_pairwise_inputs(names[METRIC], x1, x2, /*boolean=*/true);
+    return bool_metric(ab.first, ab.second, METRIC);
+}
+std::tuple<Tensor, Tensor, Tensor> directed_hausdorff_raw(const Tensor &x1, const Tensor &x2, bool shuffle,
+                                                          c10::optional<at::Generator> generator) {
+    auto r = HausdorffFn::apply(x1, x2, shuffle, generator);
+    return {r[0], r[1], r[2]};
+}
+std::tuple<Tensor, Tensor, Tensor> directed_hausdorff_distances(const Tensor &x1, const OptTensor &x2, bool shuffle,
+                                                                c10::optional<at::Generator> generator) {
+    auto ab = check_pairwise_inputs("directed_hausdorff_distances", x1, x2, false, /*sets=*/true);
+    return directed_hausdorff_raw(ab.first, ab.second, shuffle, generator);
+}
+
+Tensor sqjensenshannon_raw(const Tensor &x1, const Tensor &x2, c10::optional<double> base) {
+    return JensenShannonFn::apply(x1, x2, js_scale(base), false);
+}
+// OPS/pairwise_metrics.cpp:326-337: rows scaled to sum one (plain tensor operations), then one kernel for the sum and the root
+Tensor jensenshannon_distances(const Tensor &x1, const OptTensor &x2, c10::optional<double> base) {
+    auto ab = check_pairwise_inputs("jensenshannon_distances", x1, x2);
+    Tensor n1 = ab.first / ab.first.sum(-1, true);
+    Tensor n2 = x2.has_value() ? ab.second / ab.second.sum(-1, true) : n1;
+    return JensenShannonFn::apply(n1, n2, js_scale(base), true);
+}
+Tensor canberra_raw(const Tensor &x1, const Tensor &x2) { return PairSumFn::apply(x1, x2, static_cast<int64_t>(TPW_PAIR_CANBERRA)); }
+Tensor additive_chi2_raw(const Tensor &x1, const Tensor &x2) { return PairSumFn::apply(x1, x2, static_cast<int64_t>(TPW_PAIR_ADDITIVE_CHI2)); }
+Tensor canberra_distances(const Tensor &x1, const OptTensor &x2) {
+    auto ab = check_pairwise_inputs("canberra_distances", x1, x2);
+    return canberra_raw(ab.first, ab.second);
+}
+// OPS/pairwise_metrics.cpp:124-145 (the sign check synchronises there as well)
+Tensor additive_chi2_kernel(const Tensor &x1, const OptTensor &x2) {
+    auto ab = check_pairwise_inputs("additive_chi2_kernel", x1, x2);
+    TORCH_CHECK(ab.first.ge(0).all().item<bool>() && (!x2.has_value() || ab.second.ge(0).all().item<bool>()),
+                "All elements of x1 and x2 must be positive");
+    return additive_chi2_raw(ab.first, ab.second);
+}
+Tensor chi2_kernel(const Tensor &x1, const OptTensor &x2, double gamma) { return (additive_chi2_kernel(x1, x2) * gamma).exp(); }
+// OPS/pairwise_metrics.cpp:308-315 with OPS/cpu/braycurtis_kernel.cpp:22-27: sum |x - y| / sum |x + y| as two L1 passes
+Tensor braycurtis_distances(const Tensor &x1, const OptTensor &x2) {
+    auto ab = check_pairwise_inputs("braycurtis_distances", x1, x2);
+    return CdistFn::apply(ab.first, ab.second, 1.0) / CdistFn::apply(ab.first, ab.second.neg(), 1.0);
+}
+// OPS/pairwise_metrics.cpp:401-408 with OPS/cpu/snr_kernel.cpp:22-34: var(x2 - x1) / var(x1) per pair, the first variance
+// as |x1 - x2|^2 - (sum x2 - sum x1)^2 / D on the squared-Euclidean kernel
+Tensor snr_distances(const Tensor &x1, const OptTensor &x2) {
+    auto ab = check_pairwise_inputs("snr_distances", x1, x2);
+    const double d = static_cast<double>(ab.first.size(-1));
+    Tensor shift = ab.second.sum(-1).unsqueeze(-2) - ab.first.sum(-1, true);
+    Tensor diff_var = PPMinkowskiFn::apply(ab.first, ab.second, 2.0) - shift * shift / d;
+    Tensor x1_var = (ab.first - ab.first.mean(-1, true)).pow(2).sum(-1, true);
+    return diff_var / x1_var;
+}
+// OPS/pairwise_metrics.cpp:245-263: weighted Minkowski with w = 1/V (1 where V is 0), p = 2
+Tensor seuclidean_distances(const Tensor &x1, const OptTensor &x2, const OptTensor &V) {
+    TORCH_CHECK(!x2.has_value() || V.has_value(), "V is required for seuclidean when x2 is passed.");
+    auto ab = check_pairwise_inputs("euclidean_distances", x1, x2);
+    Tensor v;
+    if (V.has_value()) v = V.value();
+    else {
+        at::NoGradGuard ng;
+        v = ab.first.dim() == 2 ? ab.first.var(at::IntArrayRef{0}) : ab.first.var(at::IntArrayRef{0, 1});
+    }
+    Tensor w = PRFDivFn::apply(at::ones_like(v), v, static_cast<int64_t>(TPW_PRF_IDENTITY), static_cast<int64_t>(v.scalar_type()));
+    return WMinkowskiFn::apply(ab.first, ab.second, w, 2.0);
+}
+Tensor haversine_raw(const Tensor &x1, const Tensor &x2) { return HaversineFn::apply(x1, x2); }
+Tensor haversine_distances(const Tensor &x1, const OptTensor &x2) {
+    auto ab = check_pairwise_inputs("haversine_distances", x1, x2);
+    return HaversineFn::apply(ab.first, ab.second);
+}
+
+// ---- cdist: string dispatcher with the reference's keyword validation (OPS/cpdist.cpp:35-79,149-231) -----------
+Tensor cdist(const Tensor &x1, const Tensor &x2, c10::string_view metric, const OptTensor &w, const OptTensor &V,
+             const OptTensor &VI, c10::optional<double> p, c10::optional<double> base, c10::optional<bool> shuffle,
+             c10::optional<at::Generator> generator) {
+    static const char *supported =
+        "braycurtis, canberra, chebyshev, cityblock, correlation, cosine, dice, directed_hausdorff, euclidean, hamming, "
+        "haversine, jaccard, jensenshannon, kulczynski1, kulsinski, l1, l2, lp, linf, mahalanobis, manhattan, minkowski, "
+        "rogerstanimoto, russellrao, seuclidean, snr, sokalmichener, sokalsneath, sqeuclidean, wminkowski, yule";
+    const std::string m(metric.data(), metric.size());
+    auto accepts = [&](const char *arg) {
+        if (m == "directed_hausdorff") return !strcmp(arg, "shuffle") || !strcmp(arg, "generator");
+        if (m == "minkowski" || m == "lp") return !strcmp(arg, "p");
+        if (m == "wminkowski") return !strcmp(arg, "w") || !strcmp(arg, "p");
+        if (m == "seuclidean") return !strcmp(arg, "V");
+        if (m == "mahalanobis") return !strcmp(arg, "VI");
+        if (m == "jensenshannon") return !strcmp(arg, "base");
+        return false;
+    };
+    std::string bad;
+    auto note = [&](bool given, const char *arg) {
+        if (given && !accepts(arg)) bad += (bad.empty() ? "" : ", ") + std::string(arg);
+    };
+    const bool known = std::string(", ").append(supported).append(", ").find(", " + m + ", ") != std::string::npos;
+    TORCH_CHECK(known, "Got unkown distance metric: ", m, ". Supported metrics are [", supported, "]");
+    note(w.has_value(), "w"); note(V.has_value(), "V"); note(VI.has_value(), "VI"); note(p.has_value(), "p");
+    note(base.has_value(), "base"); note(shuffle.has_value(), "shuffle"); note(generator.has_value(), "generator");
+    TORCH_CHECK_TYPE(bad.empty(), "torchpairwise::", m, "_distances was called with incompatible arguments ", bad, ".");
+    if (m == "euclidean" || m == "l2") return euclidean_distances(x1, x2);
+    if (m == "manhattan" || m == "cityblock" || m == "l1") return manhattan_distances(x1, x2);
+    if (m == "chebyshev" || m == "linf") return chebyshev_distances(x1, x2);
+    if (m == "minkowski" || m == "lp") return minkowski_distances(x1, x2, p.value_or(2));
+    if (m == "wminkowski") return wminkowski_distances(x1, x2, p.value_or(2), w);
+    if (m == "sqeuclidean") return sqeuclidean_distances(x1, x2);
+    if (m == "cosine") return cosine_distances(x1, x2);
+    if (m == "correlation") return correlation_distances(x1, x2);
+    if (m == "hamming") return hamming_distances(x1, x2);
+    if (m == "jensenshannon") return jensenshannon_distances(x1, x2, base);
+    if (m == "haversine") return haversine_distances(x1, x2);
+    if (m == "canberra") return canberra_distances(x1, x2);
+    if (m == "braycurtis") return braycurtis_distances(x1, x2);
+    if (m == "snr") return snr_distances(x1, x2);
+    if (m == "seuclidean") return seuclidean_distances(x1, x2, V);
+    if (m == "jaccard") return boolean_metric_op<TPW_BOOL_JACCARD>(x1, x2);
+    // the reference's cdist routes "kulsinski" through the kulczynski1 functor (OPS/pairwise_metrics.h:557-561)
+    if (m == "kulsinski" || m == "kulczynski1") return boolean_metric_op<TPW_BOOL_KULCZYNSKI1>(x1, x2);
+    if (m == "yule") return boolean_metric_op<TPW_BOOL_YULE>(x1, x2);
+    if (m == "dice") return boolean_metric_op<TPW_BOOL_DICE>(x1, x2);
+    if (m == "rogerstanimoto") return boolean_metric_op<TPW_BOOL_ROGERSTANIMOTO>(x1, x2);
+    if (m == "russellrao") return boolean_metric_op<TPW_BOOL_RUSSELLRAO>(x1, x2);
+    if (m == "sokalmichener") return boolean_metric_op<TPW_BOOL_SOKALMICHENER>(x1, x2);
+    if (m == "sokalsneath") return boolean_metric_op<TPW_BOOL_SOKALSNEATH>(x1, x2);
+    if (m == "directed_hausdorff") return std::get<0>(directed_hausdorff_distances(x1, x2, shuffle.value_or(false), generator));
+    // mahalanobis: served by the Python layer (a composition over the dot-product kernels); not bound here
+    TORCH_CHECK_NOT_IMPLEMENTED(false, "metric '", m, "' is not bound in the C++ layer of this library");
+}
+
 // __directed_hausdorff_backward re-runs the forward for the attaining pair, as the reference's backward op does
 // (OPS/cuda/hausdorff_kernel.cu:283-321).
 std::tuple<Tensor, Tensor> directed_hausdorff_backward_op(const Tensor &grad, const Tensor &x1, const Tensor &x2, bool shuffle,
@@ -867,6 +1044,19 @@ TORCH_LIBRARY_FRAGMENT(torchpairwise, m) {
         "(Tensor x1, Tensor x2, *, bool shuffle=False, Generator? generator=None) -> (Tensor output, Tensor x1_indices, Tensor x2_indices)");
     for (const char *n : {"pwand_sum", "pwor_sum", "pwxor_sum", "pweq_sum", "pwne_sum", "pweq_mean", "pwne_mean"})
         def(n, "(Tensor x1, Tensor x2) -> Tensor");
+    for (const char *n : {"haversine_distances", "canberra_distances", "braycurtis_distances", "snr_distances", "additive_chi2_kernel"})
+        def(n, OPT2);
+    def("chi2_kernel", "(Tensor x1, Tensor? x2=None, float gamma=1.0) -> Tensor");
+    def("seuclidean_distances", "(Tensor x1, Tensor? x2=None, Tensor? V=None) -> Tensor");
+    def("_canberra", "(Tensor x1, Tensor x2) -> Tensor");
+    def("__canberra_backward", "(Tensor grad, Tensor x1, Tensor x2) -> (Tensor grad_x1, Tensor grad_x2)");
+    def("_additive_chi2_kernel", "(Tensor x1, Tensor x2) -> Tensor");
+    def("__additive_chi2_kernel_backward", "(Tensor grad, Tensor x1, Tensor x2) -> (Tensor grad_x1, Tensor grad_x2)");
+    def("jensenshannon_distances", "(Tensor x1, Tensor? x2=None, float? base=None) -> Tensor");
+    def("_sqjensenshannon", "(Tensor x1, Tensor x2, float? base=None) -> Tensor");
+    def("__sqjensenshannon_backward", "(Tensor grad, Tensor x1, Tensor x2, float? base) -> (Tensor grad_x1, Tensor grad_x2)");
+    def("_haversine", "(Tensor x1, Tensor x2) -> Tensor");
+    def("__haversine_backward", "(Tensor grad, Tensor x1, Tensor x2) -> (Tensor grad_x1, Tensor grad_x2)");
     def("__directed_hausdorff_backward",
         "(Tensor grad, Tensor x1, Tensor x2, *, bool shuffle=False, Generator? generator=None) -> (Tensor grad_x1, Tensor grad_x2)");
     // OPS/prf_div.cpp:359-400
@@ -928,6 +1118,18 @@ TORCH_LIBRARY_IMPL(torchpairwise, AutogradCUDA, m) {
     m.impl("_wminkowski", wminkowski);
     m.impl("_directed_hausdorff", directed_hausdorff_raw);
     m.impl("cdist", cdist);
+    m.impl("haversine_distances", haversine_distances);
+    m.impl("canberra_distances", canberra_distances);
+    m.impl("braycurtis_distances", braycurtis_distances);
+    m.impl("snr_distances", snr_distances);
+    m.impl("seuclidean_distances", seuclidean_distances);
+    m.impl("additive_chi2_kernel", additive_chi2_kernel);
+    m.impl("chi2_kernel", chi2_kernel);
+    m.impl("_canberra", canberra_raw);
+    m.impl("_additive_chi2_kernel", additive_chi2_raw);
+    m.impl("jensenshannon_distances", jensenshannon_distances);
+    m.impl("_sqjensenshannon", sqjensenshannon_raw);
+    m.impl("_haversine", haversine_raw);
     m.impl("prf_div", prf_div_tensor<false>);
     m.impl("prf_ldiv", prf_div_tensor<true>);
     m.impl("prf_div.Scalar", prf_div_scalar<false>);
@@ -964,6 +1166,26 @@ TORCH_LIBRARY_IMPL(torchpairwise, CUDA, m) {
                                finish(std::get<2>(g), q.unbatched, dt));
     });
     m.impl("__directed_hausdorff_backward", directed_hausdorff_backward_op);
+    m.impl("__sqjensenshannon_backward", [](const Tensor &grad, const Tensor &x1, const Tensor &x2, c10::optional<double> base) {
+        Prepared q = prepare(x1, x2, compute_type(x1.scalar_type()));
+        auto g = JensenShannonFn::raw_backward(grad, q.a, q.b, Tensor(), js_scale(base), q.unbatched);
+        return std::make_tuple(finish(g.first, q.unbatched, x1.scalar_type()), finish(g.second, q.unbatched, x1.scalar_type()));
+    });
+    m.impl("__canberra_backward", [](const Tensor &grad, const Tensor &x1, const Tensor &x2) {
+        Prepared q = prepare(x1, x2, compute_type(x1.scalar_type()));
+        auto g = PairSumFn::raw_backward(grad, q.a, q.b, TPW_PAIR_CANBERRA, q.unbatched);
+        return std::make_tuple(finish(g.first, q.unbatched, x1.scalar_type()), finish(g.second, q.unbatched, x1.scalar_type()));
+    });
+    m.impl("__additive_chi2_kernel_backward", [](const Tensor &grad, const Tensor &x1, const Tensor &x2) {
+        Prepared q = prepare(x1, x2, compute_type(x1.scalar_type()));
+        auto g = PairSumFn::raw_backward(grad, q.a, q.b, TPW_PAIR_ADDITIVE_CHI2, q.unbatched);
+        return std::make_tuple(finish(g.first, q.unbatched, x1.scalar_type()), finish(g.second, q.unbatched, x1.scalar_type()));
+    });
+    m.impl("__haversine_backward", [](const Tensor &grad, const Tensor &x1, const Tensor &x2) {
+        Prepared q = prepare(x1, x2, compute_type(x1.scalar_type()));
+        auto g = HaversineFn::raw_backward(grad, q.a, q.b, q.unbatched);
+        return std::make_tuple(finish(g.first, q.unbatched, x1.scalar_type()), finish(g.second, q.unbatched, x1.scalar_type()));
+    });
     m.impl("_prf_div_backward", prf_div_backward_op<false>);
     m.impl("_prf_ldiv_backward", prf_div_backward_op<true>);
     m.impl("_prf_div_backward.Scalar", prf_div_backward_scalar_op<false>);

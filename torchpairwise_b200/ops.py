@@ -1031,6 +1031,124 @@ def chi2_kernel(x1: Tensor, x2: Optional[Tensor] = None, gamma: float = 1.0) -> 
     return (additive_chi2_kernel(x1, x2) * gamma).exp()
 
 
+class _JensenShannonFunction(torch.autograd.Function):
+    """f(scale * sum_k (x1 log(x1/m) + x2 log(x2/m))), m = (x1 + x2)/2, with f the identity (_sqjensenshannon,
+    OPS/autograd/sqjensenshannon_kernel.cpp, kernels OPS/cpu/sqjensenshannon_kernel.cpp:13-141) or the square
+    root that jensenshannon_distances applies in place (OPS/pairwise_metrics.cpp:336), fused into the tile's
+    epilogue.  Where the rooted output is 0 the backward contributes 0 (the reference's sqrt backward divides
+    by it)."""
+
+    @staticmethod
+    def forward(ctx, x1: Tensor, x2: Tensor, scale: float, take_sqrt: bool):
+        in_dtype = x1.dtype
+        cdt = _compute_dtype(in_dtype)
+        x1c, x2c, unbatched = _batched(x1.to(cdt), x2.to(cdt), "_sqjensenshannon")
+        B, N1, N2, D = _sizes(x1c, x2c)
+        out = torch.empty((B, N1, N2), dtype=cdt, device=x1c.device)
+        if D == 0:
+            out.zero_()
+        else:
+            with torch.cuda.device(x1c.device):
+                check(lib.tpw_jensenshannon_forward(_FLOAT_CODES[cdt], _ptr(x1c), _ptr(x2c), _ptr(out), B, N1, N2, D,
+                                                    float(scale), int(take_sqrt), _stream(x1c)), "tpw_jensenshannon_forward")
+        ctx.save_for_backward(x1c, x2c, out if take_sqrt else None)
+        ctx.scale, ctx.unbatched, ctx.in_dtype = float(scale), unbatched, in_dtype
+        return (out.squeeze(0) if unbatched else out).to(in_dtype)
+
+    @staticmethod
+    def backward(ctx, grad):
+        x1c, x2c, out = ctx.saved_tensors
+        g = grad.to(x1c.dtype).contiguous()
+        if ctx.unbatched:
+            g = g.unsqueeze(0)
+        B, N1, N2, D = _sizes(x1c, x2c)
+        need1, need2 = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        g1 = torch.empty_like(x1c) if need1 else None
+        g2 = torch.empty_like(x2c) if need2 else None
+        if need1 or need2:
+            with torch.cuda.device(x1c.device):
+                check(lib.tpw_jensenshannon_backward(_FLOAT_CODES[x1c.dtype], _ptr(g), _ptr(out), _ptr(x1c), _ptr(x2c),
+                                                     _ptr(g1), _ptr(g2), B, N1, N2, D, ctx.scale, _stream(x1c)),
+                      "tpw_jensenshannon_backward")
+        if ctx.unbatched:
+            g1 = None if g1 is None else g1.squeeze(0)
+            g2 = None if g2 is None else g2.squeeze(0)
+        return (None if g1 is None else g1.to(ctx.in_dtype)), (None if g2 is None else g2.to(ctx.in_dtype)), None, None
+
+
+def _js_scale(base: Optional[float]) -> float:
+    # output.div_(2 log(base)), or 2 without a base (OPS/cpu/sqjensenshannon_kernel.cpp:75)
+    return 0.5 if base is None else 0.5 / math.log(base)
+
+
+def _sqjensenshannon(x1: Tensor, x2: Tensor, base: Optional[float] = None) -> Tensor:
+    """Squared Jensen-Shannon distance of rows that already sum to one (OPS/sqjensenshannon.cpp)."""
+    _require_cuda(x1, x2)
+    return _JensenShannonFunction.apply(x1, x2, _js_scale(base), False)
+
+
+def jensenshannon_distances(x1: Tensor, x2: Optional[Tensor] = None, base: Optional[float] = None) -> Tensor:
+    """sqrt(_sqjensenshannon(x1 / sum x1, x2 / sum x2, base)) (OPS/pairwise_metrics.cpp:326-337): the rows are
+    normalised with plain tensor operations (differentiable), the sum and the root run in one kernel."""
+    x1_, x2_ = check_pairwise_inputs("jensenshannon_distances", x1, x2)
+    _require_cuda(x1_, x2_)
+    n1 = x1_ / x1_.sum(-1, keepdim=True)
+    n2 = n1 if x2 is None else x2_ / x2_.sum(-1, keepdim=True)
+    return _JensenShannonFunction.apply(n1, n2, _js_scale(base), True)
+
+
+class _HaversineFunction(torch.autograd.Function):
+    """_haversine and its backward (OPS/autograd/haversine_kernel.cpp, kernels OPS/cpu/haversine_kernel.cpp:12-217):
+    rows are (latitude, longitude) in radians.  Coincident or antipodal pairs contribute no gradient (the
+    reference divides by a zero denominator there)."""
+
+    @staticmethod
+    def forward(ctx, x1: Tensor, x2: Tensor):
+        in_dtype = x1.dtype
+        cdt = _compute_dtype(in_dtype)
+        x1c, x2c, unbatched = _batched(x1.to(cdt), x2.to(cdt), "_haversine")
+        B, N1, N2, D = _sizes(x1c, x2c)
+        if D != 2:
+            raise RuntimeError("feature dimension of x1 and x2 must be 2.")
+        out = torch.empty((B, N1, N2), dtype=cdt, device=x1c.device)
+        with torch.cuda.device(x1c.device):
+            check(lib.tpw_haversine_forward(_FLOAT_CODES[cdt], _ptr(x1c), _ptr(x2c), _ptr(out), B, N1, N2, _stream(x1c)),
+                  "tpw_haversine_forward")
+        ctx.save_for_backward(x1c, x2c)
+        ctx.unbatched, ctx.in_dtype = unbatched, in_dtype
+        return (out.squeeze(0) if unbatched else out).to(in_dtype)
+
+    @staticmethod
+    def backward(ctx, grad):
+        x1c, x2c = ctx.saved_tensors
+        g = grad.to(x1c.dtype).contiguous()
+        if ctx.unbatched:
+            g = g.unsqueeze(0)
+        B, N1, N2, _ = _sizes(x1c, x2c)
+        g1 = torch.empty_like(x1c) if ctx.needs_input_grad[0] else None
+        g2 = torch.empty_like(x2c) if ctx.needs_input_grad[1] else None
+        if g1 is not None or g2 is not None:
+            with torch.cuda.device(x1c.device):
+                check(lib.tpw_haversine_backward(_FLOAT_CODES[x1c.dtype], _ptr(g), _ptr(x1c), _ptr(x2c), _ptr(g1), _ptr(g2),
+                                                 B, N1, N2, _stream(x1c)), "tpw_haversine_backward")
+        if ctx.unbatched:
+            g1 = None if g1 is None else g1.squeeze(0)
+            g2 = None if g2 is None else g2.squeeze(0)
+        return (None if g1 is None else g1.to(ctx.in_dtype)), (None if g2 is None else g2.to(ctx.in_dtype))
+
+
+def _haversine(x1: Tensor, x2: Tensor) -> Tensor:
+    _require_cuda(x1, x2)
+    return _HaversineFunction.apply(x1, x2)
+
+
+def haversine_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
+    """Great-circle distance on the unit sphere between (latitude, longitude) rows in radians
+    (OPS/pairwise_metrics.cpp:33-40)."""
+    x1_, x2_ = check_pairwise_inputs("haversine_distances", x1, x2)
+    return _haversine(x1_, x2_)
+
+
 def braycurtis_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
     """sum_k |x1 - x2| / sum_k |x1 + x2| (the reference's own kernel, OPS/cpu/braycurtis_kernel.cpp:22-27,
     called at OPS/pairwise_metrics.cpp:308-315): two passes of the L1 tile kernel, the second against

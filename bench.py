@@ -580,6 +580,16 @@ def run_suite(args):
                      ("OB_sqeuclidean_D16", tpw.sqeuclidean_distances)):
         if want(name):
             entry(name, n, timeit(lambda: fn(X, Y)), "hbm (output write)", 4 * n / 1e9, hbm_peak, 4 * n)
+    # D = 16 costs 32 lane-operations per 4-byte output: the fp32 pipe (0.92 ms at peak) bounds it before the write
+    # does (0.66 ms).  D = 8, 4 and 3 are the shapes the output write really bounds.
+    for dd in (8, 4, 3):
+        if want(f"OB_manhattan_D{dd}") or want(f"OB_euclidean_D{dd}"):
+            Xs, Ys = torch.randn(ro, dd, generator=g).to(dev), torch.randn(16384, dd, generator=g).to(dev)
+            if want(f"OB_manhattan_D{dd}"):
+                entry(f"OB_manhattan_D{dd}", n, timeit(lambda: tpw.manhattan_distances(Xs, Ys)), "hbm (output write)", 4 * n / 1e9, hbm_peak, 4 * n)
+            if want(f"OB_euclidean_D{dd}"):
+                entry(f"OB_euclidean_D{dd}", n, timeit(lambda: tpw.euclidean_distances(Xs, Ys)), "hbm (output write)", 4 * n / 1e9, hbm_peak, 4 * n)
+            del Xs, Ys
     if want("OB_manhattan_D16_rowmin"):
         entry("OB_manhattan_D16_rowmin", n, timeit(lambda: tpw.pairwise_argmin_min(X, Y, "manhattan")),
               "fp32_issue (matrix never written)", n * 16 * 2, fp32_peak, 0)

@@ -212,6 +212,31 @@ def test_ragged_shapes_vs_oracle(tpw, shape, p):
     close(b.grad, g2.astype(np.float32), tol, scale, f"grad_x2 {shape} p={p}")
 
 
+@pytest.mark.parametrize("d", [1, 3, 4, 7, 8, 13, 16, 17, 31, 32])
+@pytest.mark.parametrize("p", [1.0, 2.0, 3.0, math.inf])
+def test_few_feature_kernel_vs_oracle_and_tile_kernel(tpw, monkeypatch, d, p):
+    """D <= 32 on enough rows and columns takes the streaming few-feature kernel: against the oracle on ragged
+    sizes (row count not a multiple of 128, column count odd, so the scalar-store edge is taken), on an
+    unaligned-width output, and bit for bit against the tile kernel, which accumulates in the same order."""
+    g = torch.Generator().manual_seed(300 + d)
+    for n1, n2 in ((131, 1029), (256, 2048)):
+        x1, x2 = torch.randn(2, n1, d, generator=g), torch.randn(2, n2, d, generator=g)
+        a, b = x1.cuda(), x2.cuda()
+        out = tpw.minkowski_distances(a, b, p)
+        close(out, O.cdist(x1.numpy(), x2.numpy(), p), TOL[torch.float32], msg=f"few features D={d} p={p} {n1}x{n2}")
+        if p == 2.0:
+            sq_small = tpw.sqeuclidean_distances(a, b)
+            close(sq_small, O.cdist(x1.numpy(), x2.numpy(), 2.0) ** 2, TOL[torch.float32], msg="sqeuclidean")
+        monkeypatch.setenv("TPW_DISABLE_SMALL_D", "1")
+        tile = tpw.minkowski_distances(a, b, p)
+        if p == 2.0:   # the approximate square root of the few-feature kernel is within 1 ulp of the tile kernel's
+            assert bool(((out - tile).abs() <= 1.2e-7 * tile.abs()).all())
+            assert torch.equal(tpw.sqeuclidean_distances(a, b), sq_small)
+        else:
+            assert torch.equal(out, tile), f"D={d} p={p} {n1}x{n2}: max diff {float((out - tile).abs().max())}"
+        monkeypatch.delenv("TPW_DISABLE_SMALL_D")
+
+
 def test_tma_and_plain_load_paths_agree(tpw):
     """An input whose base address is not 16-byte aligned takes the guarded plain-load path; it
     stages the same layout, so results are bit-identical to the TMA path."""

@@ -62,6 +62,11 @@ int make_tensor_map_3d(CUtensorMap *map, const void *base, int elem_bytes,
 int make_tensor_map_3d_atom32(CUtensorMap *map, const void *base, int elem_bytes,
                               uint64_t dim0, uint64_t dim1, uint64_t dim2, uint32_t box0, uint32_t box1);
 
+// lp_small_d.cu: float32 L_p forward for few features (output-bound shapes)
+bool lp_small_d_eligible(long long N1, long long N2, long long D, double p);
+int lp_small_d_forward(const void *x1, const void *x2, void *out, long long B, long long N1, long long N2, long long D,
+                       double p, double out_exponent, cudaStream_t s);
+
 // |d|^q in the float kernels.  spec = mode | m << 2 (uniform over a launch): mode 0 is the general
 // exp2(q log2 a) (two MUFU operations per element); mode 1 is q = m + 1/2, one approximate square
 // root (MUFU.SQRT, 1 ulp) times a^m; mode 2 is the integer q = m as repeated multiplication.

@@ -32,6 +32,8 @@ extern "C" int tpw_lp_forward(int dtype, const void *x1, const void *x2, const v
     P.x1 = x1; P.x2 = x2; P.w = w; P.out = out;
     P.B = B; P.N1 = N1; P.N2 = N2; P.D = D;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // few features: the streaming kernel of lp_small_d.cu, bound by the output write instead of tile set-up
+    if (dtype == TPW_F32 && !w && lp_small_d_eligible(N1, N2, D, p)) return lp_small_d_forward(x1, x2, out, B, N1, N2, D, p, out_exponent, s);
     return dtype == TPW_F32 ? lp_forward_typed<float>(P, p, out_exponent, s)
                             : lp_forward_typed<double>(P, p, out_exponent, s);
 }

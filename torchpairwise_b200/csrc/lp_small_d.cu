@@ -1,0 +1,177 @@
+// L_p forward for few features (D <= 32, float32, unweighted, p in {1, 2, 3, +inf}): the output-bound shapes.
+//
+// With a handful of features the 128 x 128 register tile spends more on staging operands, barriers and the
+// shared-memory epilogue than on arithmetic, and the kernel should be limited by the 4 bytes it writes per
+// pair.  Here the roles are fixed instead: every lane keeps JL consecutive x2 rows in registers (JL * DP <= 64
+// values, DP = D rounded up to 4, 8, 16 or 32), loaded once per CTA; x1 rows pass through shared memory 128 at a
+// time (four such tiles per CTA), and the warp walks over them: one broadcast shared load of an x1 row (DP / 4 128-bit loads), 2 * DP * JL arithmetic lane operations,
+// and one JL-wide store, so that a warp writes 32 * JL consecutive outputs of one output row with full
+// 128-byte lines and nothing is staged.  Features are accumulated in ascending order exactly as the tile
+// kernel does, with the same operations; only the square root differs (approximate, within 1 ulp).
+#include "common.cuh"
+
+#include <math.h>
+#include <stdlib.h>
+
+namespace tpw {
+namespace {
+
+enum SmallKind { SK_L1 = 0, SK_P2 = 1, SK_P3 = 2, SK_MAX = 3 };
+
+constexpr int SD_THREADS = 256;
+constexpr int SD_ROWS = 128;   // x1 rows per shared-memory tile
+constexpr int SD_TILES = 4;    // row tiles per CTA (the x2 registers are loaded once for all of them)
+
+template <int KIND>
+__device__ __forceinline__ void sd_acc(float &acc, float x, float y) {
+    const float d = x - y;
+    if (KIND == SK_L1) acc += fabsf(d);
+    else if (KIND == SK_P2) acc = fmaf(d, d, acc);
+    else if (KIND == SK_P3) { const float a = fabsf(d); acc = fmaf(a * a, a, acc); }
+    else acc = fmaxf(acc, fabsf(d));
+}
+
+// root_mode: 0 none, 1 sqrt, 2 cbrt, 3 powf(exponent)
+__device__ __forceinline__ float sd_root(float v, int root_mode, float exponent) {
+    if (root_mode == 0) return v;
+    if (root_mode == 1) {   // one MUFU operation (1 ulp, flush-to-zero): the IEEE sequence would cost as much as D = 8 features
+        float r;
+        asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+        return r;
+    }
+    if (root_mode == 2) return cbrtf(v);
+    return powf(v, exponent);
+}
+
+template <int KIND, int DP, int JL>
+__global__ void __launch_bounds__(SD_THREADS, 2)
+lp_small_d_kernel(const float *__restrict__ x1, const float *__restrict__ x2, float *__restrict__ out,
+                  long long N1, long long N2, int D, long long tiles_i, long long tiles_j, int root_mode, float exponent,
+                  int vec_store, int vec_load) {
+    constexpr int COLS = SD_THREADS * JL;   // x2 rows per CTA
+    __shared__ __align__(16) float rows[SD_ROWS * DP];
+    const long long tile = blockIdx.x;
+    const long long tj = tile % tiles_j, ti = (tile / tiles_j) % tiles_i, b = tile / (tiles_j * tiles_i);
+    const long long j0 = tj * COLS + (long long)threadIdx.x * JL;
+
+    // this lane's x2 rows -> registers, once for all row tiles of the CTA (zero padding contributes |0 - 0| = 0);
+    // 128-bit loads when the rows are whole 16-byte groups
+    float y[JL][DP];
+    if (vec_load && j0 + JL <= N2) {
+        const float4 *src = reinterpret_cast<const float4 *>(x2 + (b * N2 + j0) * DP);
+#pragma unroll
+        for (int c = 0; c < JL; ++c)
+#pragma unroll
+            for (int k4 = 0; k4 < DP / 4; ++k4) {
+                const float4 v = __ldg(src + c * (DP / 4) + k4);
+                y[c][4 * k4] = v.x; y[c][4 * k4 + 1] = v.y; y[c][4 * k4 + 2] = v.z; y[c][4 * k4 + 3] = v.w;
+            }
+    } else {
+#pragma unroll
+        for (int c = 0; c < JL; ++c) {
+            const long long j = j0 + c;
+            const float *src = x2 + (b * N2 + (j < N2 ? j : 0)) * D;
+#pragma unroll
+            for (int k = 0; k < DP; ++k) y[c][k] = (j < N2 && k < D) ? src[k] : 0.f;
+        }
+    }
+
+    for (int t = 0; t < SD_TILES; ++t) {
+        const long long i0 = (ti * SD_TILES + t) * SD_ROWS;
+        if (i0 >= N1) break;
+        const int nr = (int)min((long long)SD_ROWS, N1 - i0);
+        // x1 rows -> shared memory, zero beyond D and beyond the last row
+        const float *x1b = x1 + (b * N1 + i0) * D;
+        __syncthreads();
+        if (vec_load) {
+            const float4 *src = reinterpret_cast<const float4 *>(x1b);
+            for (int e = threadIdx.x; e < SD_ROWS * DP / 4; e += SD_THREADS)
+                reinterpret_cast<float4 *>(rows)[e] = e < nr * (DP / 4) ? __ldg(src + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+        } else {
+            for (int e = threadIdx.x; e < SD_ROWS * DP; e += SD_THREADS) {
+                const int r = e / DP, k = e % DP;
+                rows[e] = (r < nr && k < D) ? x1b[(long long)r * D + k] : 0.f;
+            }
+        }
+        __syncthreads();
+        if (j0 >= N2) continue;
+
+        float *o = out + (b * N1 + i0) * N2 + j0;
+        for (int r = 0; r < nr; ++r) {
+            float acc[JL];
+#pragma unroll
+            for (int c = 0; c < JL; ++c) acc[c] = 0.f;
+#pragma unroll
+            for (int k4 = 0; k4 < DP; k4 += 4) {
+                const float4 xv = *reinterpret_cast<const float4 *>(&rows[r * DP + k4]);
+#pragma unroll
+                for (int c = 0; c < JL; ++c) {
+                    sd_acc<KIND>(acc[c], xv.x, y[c][k4]);
+                    sd_acc<KIND>(acc[c], xv.y, y[c][k4 + 1]);
+                    sd_acc<KIND>(acc[c], xv.z, y[c][k4 + 2]);
+                    sd_acc<KIND>(acc[c], xv.w, y[c][k4 + 3]);
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < JL; ++c) acc[c] = sd_root(acc[c], root_mode, exponent);
+            float *dst = o + (long long)r * N2;
+            if (vec_store && j0 + JL <= N2) {
+                if (JL == 4) __stcs(reinterpret_cast<float4 *>(dst), make_float4(acc[0], acc[1], acc[JL > 2 ? 2 : 0], acc[JL > 3 ? 3 : 0]));
+                else __stcs(reinterpret_cast<float2 *>(dst), make_float2(acc[0], acc[1]));
+            } else {
+#pragma unroll
+                for (int c = 0; c < JL; ++c)
+                    if (j0 + c < N2) dst[c] = acc[c];
+            }
+        }
+    }
+}
+
+template <int KIND, int DP, int JL>
+int launch_small(const float *x1, const float *x2, float *out, long long B, long long N1, long long N2, int D,
+                 int root_mode, float exponent, cudaStream_t s) {
+    const long long ti = (N1 + SD_ROWS * SD_TILES - 1) / (SD_ROWS * SD_TILES), tj = (N2 + SD_THREADS * JL - 1) / (SD_THREADS * JL), tiles = B * ti * tj;
+    TPW_CHECK_ARG(tiles < (1ll << 31), "lp forward (few features): too many tiles (%lld)", tiles);
+    const int vec = (N2 % JL == 0 && (reinterpret_cast<uintptr_t>(out) % (4 * JL)) == 0) ? 1 : 0;
+    const int vload = (D == DP && reinterpret_cast<uintptr_t>(x1) % 16 == 0 && reinterpret_cast<uintptr_t>(x2) % 16 == 0) ? 1 : 0;
+    lp_small_d_kernel<KIND, DP, JL><<<(unsigned)tiles, SD_THREADS, 0, s>>>(x1, x2, out, N1, N2, D, ti, tj, root_mode, exponent, vec, vload);
+    TPW_LAUNCH_OK("lp_small_d_kernel");
+    return TPW_OK;
+}
+
+template <int KIND>
+int launch_small_d(const float *x1, const float *x2, float *out, long long B, long long N1, long long N2, int D,
+                   int root_mode, float exponent, cudaStream_t s) {
+    if (D <= 4) return launch_small<KIND, 4, 4>(x1, x2, out, B, N1, N2, D, root_mode, exponent, s);
+    if (D <= 8) return launch_small<KIND, 8, 4>(x1, x2, out, B, N1, N2, D, root_mode, exponent, s);
+    if (D <= 16) return launch_small<KIND, 16, 4>(x1, x2, out, B, N1, N2, D, root_mode, exponent, s);
+    return launch_small<KIND, 32, 2>(x1, x2, out, B, N1, N2, D, root_mode, exponent, s);
+}
+
+} // namespace
+
+// Whether the few-feature kernel serves this float32 problem: D <= 32, an exponent with a closed form, and
+// enough output rows and columns for its fixed roles to pay (it keeps 128 x1 rows per CTA and 512 or 1024 x2
+// rows; small problems stay on the tile kernel).
+bool lp_small_d_eligible(long long N1, long long N2, long long D, double p) {
+    if (getenv("TPW_DISABLE_SMALL_D")) return false;
+    return D >= 1 && D <= 32 && N1 >= 128 && N2 >= 1024 && (p == 1.0 || p == 2.0 || p == 3.0 || (isinf(p) && p > 0));
+}
+
+int lp_small_d_forward(const void *x1, const void *x2, void *out, long long B, long long N1, long long N2, long long D,
+                       double p, double out_exponent, cudaStream_t s) {
+    int root_mode;
+    if (isinf(p) || out_exponent == 1.0) root_mode = 0;
+    else if (out_exponent == 0.5) root_mode = 1;
+    else if (p == 3.0 && out_exponent == 1.0 / 3.0) root_mode = 2;
+    else root_mode = 3;
+    const float *a = (const float *)x1, *b = (const float *)x2;
+    float *o = (float *)out;
+    const float ex = (float)out_exponent;
+    if (isinf(p)) return launch_small_d<SK_MAX>(a, b, o, B, N1, N2, (int)D, root_mode, ex, s);
+    if (p == 1.0) return launch_small_d<SK_L1>(a, b, o, B, N1, N2, (int)D, root_mode, ex, s);
+    if (p == 2.0) return launch_small_d<SK_P2>(a, b, o, B, N1, N2, (int)D, root_mode, ex, s);
+    return launch_small_d<SK_P3>(a, b, o, B, N1, N2, (int)D, root_mode, ex, s);
+}
+
+} // namespace tpw

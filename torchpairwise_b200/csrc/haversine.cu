@@ -70,27 +70,53 @@ __device__ __forceinline__ T hav_a(const Half4<T> &p, const Half4<T> &q, T &u, T
     return a < T(0) ? T(0) : a;
 }
 
-constexpr int FT = 256;   // columns (x2 rows) per CTA, one per thread
-constexpr int FR = 32;    // x1 rows per CTA
+constexpr int FT = 256;   // threads per CTA
+constexpr int FJ = 4;     // consecutive columns (x2 rows) per thread: one 128-bit store per output row
+constexpr int FR = 64;    // x1 rows per CTA
+
+template <typename T> struct Out4 { T v[FJ]; };
+__device__ __forceinline__ void store_out4(float *dst, const Out4<float> &o) {
+    __stcs(reinterpret_cast<float4 *>(dst), make_float4(o.v[0], o.v[1], o.v[2], o.v[3]));
+}
+__device__ __forceinline__ void store_out4(double *dst, const Out4<double> &o) {
+    __stcs(reinterpret_cast<double2 *>(dst), make_double2(o.v[0], o.v[1]));
+    __stcs(reinterpret_cast<double2 *>(dst) + 1, make_double2(o.v[2], o.v[3]));
+}
 
 template <typename T>
 __global__ void __launch_bounds__(FT) haversine_forward_kernel(const T *x1, const T *x2, T *out, long long N1, long long N2,
-                                                               long long tiles_i, long long tiles_j) {
+                                                               long long tiles_i, long long tiles_j, int vec_store) {
     __shared__ Half4<T> rows[FR];
     const long long tile = blockIdx.x;
     const long long tj = tile % tiles_j, ti = (tile / tiles_j) % tiles_i, b = tile / (tiles_j * tiles_i);
-    const long long i0 = ti * FR, j = tj * FT + threadIdx.x;
+    const long long i0 = ti * FR, j0 = (tj * FT + threadIdx.x) * FJ;
     if (threadIdx.x < FR && i0 + threadIdx.x < N1) rows[threadIdx.x] = half_angles(x1 + (b * N1 + i0 + threadIdx.x) * 2);
-    Half4<T> q;
-    if (j < N2) q = half_angles(x2 + (b * N2 + j) * 2);
+    Half4<T> q[FJ];
+#pragma unroll
+    for (int c = 0; c < FJ; ++c)
+        if (j0 + c < N2) q[c] = half_angles(x2 + (b * N2 + j0 + c) * 2);
+        else q[c] = Half4<T>{T(0), T(1), T(0), T(1), T(1)};
     __syncthreads();
-    if (j >= N2) return;
+    if (j0 >= N2) return;
     const int nr = (int)min((long long)FR, N1 - i0);
-    T *o = out + (b * N1 + i0) * N2 + j;
+    T *o = out + (b * N1 + i0) * N2 + j0;
+    const bool whole = vec_store && j0 + FJ <= N2;
     for (int r = 0; r < nr; ++r) {
-        T u, v, cc, c;
-        const T a = hav_a(rows[r], q, u, v, cc, c);
-        o[(long long)r * N2] = hav_dist(a, c);
+        const Half4<T> p = rows[r];
+        Out4<T> res;
+#pragma unroll
+        for (int c = 0; c < FJ; ++c) {
+            T u, v, cc, cm;
+            const T a = hav_a(p, q[c], u, v, cc, cm);
+            res.v[c] = hav_dist(a, cm);
+        }
+        T *dst = o + (long long)r * N2;
+        if (whole) store_out4(dst, res);
+        else {
+#pragma unroll
+            for (int c = 0; c < FJ; ++c)
+                if (j0 + c < N2) dst[c] = res.v[c];
+        }
     }
 }
 
@@ -197,9 +223,10 @@ __global__ void __launch_bounds__(CW * CG) haversine_backward_x2_kernel(const T 
 
 template <typename T>
 int haversine_forward_typed(const void *x1, const void *x2, void *out, long long B, long long N1, long long N2, cudaStream_t s) {
-    const long long ti = (N1 + FR - 1) / FR, tj = (N2 + FT - 1) / FT, tiles = B * ti * tj;
+    const long long ti = (N1 + FR - 1) / FR, tj = (N2 + FT * FJ - 1) / (FT * FJ), tiles = B * ti * tj;
     TPW_CHECK_ARG(tiles < (1ll << 31), "tpw_haversine_forward: too many tiles (%lld)", tiles);
-    haversine_forward_kernel<T><<<(unsigned)tiles, FT, 0, s>>>((const T *)x1, (const T *)x2, (T *)out, N1, N2, ti, tj);
+    const int vec = (N2 % FJ == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) ? 1 : 0;
+    haversine_forward_kernel<T><<<(unsigned)tiles, FT, 0, s>>>((const T *)x1, (const T *)x2, (T *)out, N1, N2, ti, tj, vec);
     TPW_LAUNCH_OK("haversine_forward_kernel");
     return TPW_OK;
 }

@@ -2,7 +2,7 @@
 //
 // With a handful of features the 128 x 128 register tile spends more on staging operands, barriers and the
 // shared-memory epilogue than on arithmetic, and the kernel should be limited by the 4 bytes it writes per
-// pair.  Here the roles are fixed instead: every lane keeps JL consecutive x2 rows in registers (JL * DP <= 64
+// pair.  Here the roles are fixed instead: every lane keeps JL = 8, 4 or 2 consecutive x2 rows in registers (JL * DP <= 64
 // values, DP = D rounded up to 4, 8, 16 or 32), loaded once per CTA; x1 rows pass through shared memory 128 at a
 // time (four such tiles per CTA), and the warp walks over them: one broadcast shared load of an x1 row (DP / 4 128-bit loads), 2 * DP * JL arithmetic lane operations,
 // and one JL-wide store, so that a warp writes 32 * JL consecutive outputs of one output row with full
@@ -52,24 +52,32 @@ lp_small_d_kernel(const float *__restrict__ x1, const float *__restrict__ x2, fl
     __shared__ __align__(16) float rows[SD_ROWS * DP];
     const long long tile = blockIdx.x;
     const long long tj = tile % tiles_j, ti = (tile / tiles_j) % tiles_i, b = tile / (tiles_j * tiles_i);
-    const long long j0 = tj * COLS + (long long)threadIdx.x * JL;
+    // A lane's columns come in groups of G = min(JL, 4) consecutive x2 rows, the groups of one warp side by side:
+    // column(c) = jw + (c / G) * 32 G + lane * G + c % G, so that every store instruction of a warp covers
+    // 32 * G consecutive outputs (full lines) however many groups a lane holds.
+    constexpr int G = JL < 4 ? JL : 4;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long jw = tj * COLS + (long long)warp * (32 * JL);
+    const long long j0 = jw + lane * G;                       // first column of this lane's first group
+    const long long jlast = jw + (JL / G - 1) * (32 * G) + lane * G + G - 1;   // its last column
 
     // this lane's x2 rows -> registers, once for all row tiles of the CTA (zero padding contributes |0 - 0| = 0);
     // 128-bit loads when the rows are whole 16-byte groups
     float y[JL][DP];
-    if (vec_load && j0 + JL <= N2) {
-        const float4 *src = reinterpret_cast<const float4 *>(x2 + (b * N2 + j0) * DP);
+    if (vec_load && jlast < N2) {
 #pragma unroll
-        for (int c = 0; c < JL; ++c)
+        for (int c = 0; c < JL; ++c) {
+            const float4 *src = reinterpret_cast<const float4 *>(x2 + (b * N2 + j0 + (c / G) * (32 * G) + c % G) * DP);
 #pragma unroll
             for (int k4 = 0; k4 < DP / 4; ++k4) {
-                const float4 v = __ldg(src + c * (DP / 4) + k4);
+                const float4 v = __ldg(src + k4);
                 y[c][4 * k4] = v.x; y[c][4 * k4 + 1] = v.y; y[c][4 * k4 + 2] = v.z; y[c][4 * k4 + 3] = v.w;
             }
+        }
     } else {
 #pragma unroll
         for (int c = 0; c < JL; ++c) {
-            const long long j = j0 + c;
+            const long long j = j0 + (c / G) * (32 * G) + c % G;
             const float *src = x2 + (b * N2 + (j < N2 ? j : 0)) * D;
 #pragma unroll
             for (int k = 0; k < DP; ++k) y[c][k] = (j < N2 && k < D) ? src[k] : 0.f;
@@ -115,13 +123,18 @@ lp_small_d_kernel(const float *__restrict__ x1, const float *__restrict__ x2, fl
 #pragma unroll
             for (int c = 0; c < JL; ++c) acc[c] = sd_root(acc[c], root_mode, exponent);
             float *dst = o + (long long)r * N2;
-            if (vec_store && j0 + JL <= N2) {
-                if (JL == 4) __stcs(reinterpret_cast<float4 *>(dst), make_float4(acc[0], acc[1], acc[JL > 2 ? 2 : 0], acc[JL > 3 ? 3 : 0]));
-                else __stcs(reinterpret_cast<float2 *>(dst), make_float2(acc[0], acc[1]));
+            if (vec_store && jlast < N2) {
+                if constexpr (JL == 2) {
+                    __stcs(reinterpret_cast<float2 *>(dst), make_float2(acc[0], acc[1]));
+                } else {
+#pragma unroll
+                    for (int c = 0; c < JL; c += 4)
+                        __stcs(reinterpret_cast<float4 *>(dst + (c / 4) * 128), make_float4(acc[c], acc[c + 1], acc[c + 2], acc[c + 3]));
+                }
             } else {
 #pragma unroll
                 for (int c = 0; c < JL; ++c)
-                    if (j0 + c < N2) dst[c] = acc[c];
+                    if (j0 + (c / G) * (32 * G) + c % G < N2) dst[(c / G) * (32 * G) + c % G] = acc[c];
             }
         }
     }
@@ -132,7 +145,7 @@ int launch_small(const float *x1, const float *x2, float *out, long long B, long
                  int root_mode, float exponent, cudaStream_t s) {
     const long long ti = (N1 + SD_ROWS * SD_TILES - 1) / (SD_ROWS * SD_TILES), tj = (N2 + SD_THREADS * JL - 1) / (SD_THREADS * JL), tiles = B * ti * tj;
     TPW_CHECK_ARG(tiles < (1ll << 31), "lp forward (few features): too many tiles (%lld)", tiles);
-    const int vec = (N2 % JL == 0 && (reinterpret_cast<uintptr_t>(out) % (4 * JL)) == 0) ? 1 : 0;
+    const int vec = (N2 % (JL < 4 ? JL : 4) == 0 && (reinterpret_cast<uintptr_t>(out) % (JL == 2 ? 8 : 16)) == 0) ? 1 : 0;
     const int vload = (D == DP && reinterpret_cast<uintptr_t>(x1) % 16 == 0 && reinterpret_cast<uintptr_t>(x2) % 16 == 0) ? 1 : 0;
     lp_small_d_kernel<KIND, DP, JL><<<(unsigned)tiles, SD_THREADS, 0, s>>>(x1, x2, out, N1, N2, D, ti, tj, root_mode, exponent, vec, vload);
     TPW_LAUNCH_OK("lp_small_d_kernel");
@@ -142,8 +155,8 @@ int launch_small(const float *x1, const float *x2, float *out, long long B, long
 template <int KIND>
 int launch_small_d(const float *x1, const float *x2, float *out, long long B, long long N1, long long N2, int D,
                    int root_mode, float exponent, cudaStream_t s) {
-    if (D <= 4) return launch_small<KIND, 4, 4>(x1, x2, out, B, N1, N2, D, root_mode, exponent, s);
-    if (D <= 8) return launch_small<KIND, 8, 4>(x1, x2, out, B, N1, N2, D, root_mode, exponent, s);
+    if (D <= 4) return launch_small<KIND, 4, 8>(x1, x2, out, B, N1, N2, D, root_mode, exponent, s);
+    if (D <= 8) return launch_small<KIND, 8, 8>(x1, x2, out, B, N1, N2, D, root_mode, exponent, s);
     if (D <= 16) return launch_small<KIND, 16, 4>(x1, x2, out, B, N1, N2, D, root_mode, exponent, s);
     return launch_small<KIND, 32, 2>(x1, x2, out, B, N1, N2, D, root_mode, exponent, s);
 }
@@ -151,7 +164,7 @@ int launch_small_d(const float *x1, const float *x2, float *out, long long B, lo
 } // namespace
 
 // Whether the few-feature kernel serves this float32 problem: D <= 32, an exponent with a closed form, and
-// enough output rows and columns for its fixed roles to pay (it keeps 128 x1 rows per CTA and 512 or 1024 x2
+// enough output rows and columns for its fixed roles to pay (a CTA covers up to 512 x1 rows and 512 to 2048 x2
 // rows; small problems stay on the tile kernel).
 bool lp_small_d_eligible(long long N1, long long N2, long long D, double p) {
     if (getenv("TPW_DISABLE_SMALL_D")) return false;

@@ -237,6 +237,34 @@ def test_few_feature_kernel_vs_oracle_and_tile_kernel(tpw, monkeypatch, d, p):
         monkeypatch.delenv("TPW_DISABLE_SMALL_D")
 
 
+@pytest.mark.parametrize("d", [1, 31, 32, 33, 64, 100, 128])
+def test_few_words_boolean_kernel_is_bit_exact(tpw, monkeypatch, d):
+    """Boolean rows of at most 128 bits on enough rows and columns take the streaming few-words kernel: every
+    boolean metric and the pw*_sum / mean counts equal the tile kernel bit for bit (NaN where it has NaN), and
+    jaccard / hamming equal the oracle, on ragged sizes and on sizes that take the 128-bit stores."""
+    g = torch.Generator().manual_seed(400 + d)
+    names = ("hamming", "jaccard", "kulsinski", "kulczynski1", "yule", "dice", "rogerstanimoto", "russellrao",
+             "sokalmichener", "sokalsneath")
+    for n1, n2 in ((131, 2051), (256, 4096)):
+        xb, yb = torch.rand(n1, d, generator=g) < 0.3, torch.rand(n2, d, generator=g) < 0.3
+        xb[0] = False   # an empty row: the 0/0 cases of the ratios
+        yb[1] = False
+        a, b = xb.cuda(), yb.cuda()
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            small = {n: getattr(tpw, n + "_distances")(a, b) for n in names}
+            small.update({n: getattr(tpw, n)(a, b) for n in ("pwand_sum", "pwor_sum", "pwxor_sum", "pweq_sum", "pwne_mean")})
+            monkeypatch.setenv("TPW_DISABLE_SMALL_D", "1")
+            tile = {n: getattr(tpw, n + "_distances")(a, b) for n in names}
+            tile.update({n: getattr(tpw, n)(a, b) for n in ("pwand_sum", "pwor_sum", "pwxor_sum", "pweq_sum", "pwne_mean")})
+            monkeypatch.delenv("TPW_DISABLE_SMALL_D")
+        for n in small:
+            s_, t_ = small[n], tile[n]
+            assert bool(((s_ == t_) | (s_.isnan() & t_.isnan())).all()), (n, d, n1, n2)
+        assert np.array_equal(small["jaccard"].cpu().numpy(), O.boolean_metric("jaccard", xb.numpy(), yb.numpy())), d
+        assert np.array_equal(small["hamming"].cpu().numpy(), O.hamming(xb.numpy(), yb.numpy())), d
+
+
 def test_tma_and_plain_load_paths_agree(tpw):
     """An input whose base address is not 16-byte aligned takes the guarded plain-load path; it
     stages the same layout, so results are bit-identical to the TMA path."""

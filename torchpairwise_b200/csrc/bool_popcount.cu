@@ -14,6 +14,8 @@
 // a 7:3 carry-save adder tree (four 3-input logic pairs) and cost four POPCs instead of eight.
 #include "common.cuh"
 
+#include <stdlib.h>
+
 namespace tpw {
 namespace {
 
@@ -61,11 +63,20 @@ __global__ void bitpack_kernel(const uint8_t *__restrict__ src, uint32_t *__rest
     }
 }
 
+// int -> float for 0 <= v < 2^23.  The conversion instruction issues at a quarter of the arithmetic rate; placing
+// the integer in the mantissa of 2^23 and subtracting 2^23 gives the same exact value with one logic operation and
+// one add.  FAST is set by the few-words kernel, where the conversions are a large share of the work per pair.
+template <bool FAST>
+__device__ __forceinline__ float count_to_float(int v) {
+    return FAST ? __int_as_float(0x4B000000 | v) - 8388608.f : (float)v;
+}
+
+template <bool FAST = false>
 __device__ __forceinline__ float bool_epilogue(int metric, int n11, int a, int b, int D, float inv_d) {
     const int nxor_i = a + b - 2 * n11;
     const int nor_i = a + b - n11;
-    const float fand = (float)n11, fxor = (float)nxor_i, f_or = (float)nor_i;
-    const float feq = (float)(D - nxor_i), fD = (float)D;
+    const float fand = count_to_float<FAST>(n11), fxor = count_to_float<FAST>(nxor_i), f_or = count_to_float<FAST>(nor_i);
+    const float feq = count_to_float<FAST>(D - nxor_i), fD = count_to_float<FAST>(D);
     switch (metric) {
         case TPW_BOOL_AND_SUM: return fand;
         case TPW_BOOL_OR_SUM: return f_or;
@@ -79,8 +90,8 @@ __device__ __forceinline__ float bool_epilogue(int metric, int n11, int a, int b
         case TPW_BOOL_KULSINSKI: return __fdiv_rn(__fadd_rn(__fsub_rn(fxor, fand), fD), __fadd_rn(fxor, fD));
         case TPW_BOOL_KULCZYNSKI1: return __fdiv_rn(fand, fxor);
         case TPW_BOOL_YULE: {
-            const float half_r = __fmul_rn((float)(a - n11), (float)(b - n11));
-            const float den = __fadd_rn(__fmul_rn(fand, (float)(D - nor_i)), half_r);
+            const float half_r = __fmul_rn(count_to_float<FAST>(a - n11), count_to_float<FAST>(b - n11));
+            const float den = __fadd_rn(__fmul_rn(fand, count_to_float<FAST>(D - nor_i)), half_r);
             return den != 0.f ? __fdiv_rn(__fmul_rn(2.f, half_r), den) : 0.f;
         }
         case TPW_BOOL_DICE: return __fdiv_rn(fxor, __fadd_rn(__fmul_rn(2.f, fand), fxor));
@@ -268,6 +279,104 @@ bool_popcount_kernel(const __grid_constant__ CUtensorMap map1, const __grid_cons
     }
 }
 
+// ---- few words per row (D <= 128 bits): the output-bound shapes --------------------------------------------
+// Same fixed roles as the few-feature L_p kernel: every lane keeps 8 x2 rows (their words and row counts) in
+// registers, in two groups of 4 consecutive rows 128 apart so that each store instruction of a warp covers 512
+// contiguous bytes; 128 x1 rows at a time sit in shared memory and are read as broadcasts.  Per pair: one AND and
+// one POPC per word, the integer contingency counts, and the metric's float32 epilogue -- nothing is staged.
+constexpr int FW_THREADS = 256, FW_ROWS = 128, FW_TILES = 4, FW_JL = 8;
+
+// WN: words that carry features, ceil(D / 32), 1..4 (rows are stored with 4 words).  METRIC: compiled in for the two
+// common metrics (jaccard, hamming), -1 = the launch's metric through the epilogue's switch.
+template <int WN, int METRIC>
+__global__ void __launch_bounds__(FW_THREADS, 2) bool_few_words_kernel(BoolParams P) {
+    constexpr int COLS = FW_THREADS * FW_JL;
+    __shared__ __align__(16) uint32_t xs[FW_ROWS * 4];
+    __shared__ int xp[FW_ROWS];
+    const long long tile = blockIdx.x;
+    const long long tj = tile % P.tiles_j, ti = (tile / P.tiles_j) % P.tiles_i, b = tile / (P.tiles_j * P.tiles_i);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long jw = tj * COLS + (long long)warp * (32 * FW_JL);
+    const long long j0 = jw + lane * 4, jlast = jw + 128 + lane * 4 + 3;
+    uint32_t y[FW_JL][WN];
+    int yp[FW_JL];
+#pragma unroll
+    for (int c = 0; c < FW_JL; ++c) {
+        const long long j = j0 + (c >> 2) * 128 + (c & 3);
+        if (j < P.N2) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(P.x2 + (b * P.N2 + j) * 4));
+            const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < WN; ++q) y[c][q] = w4[q];
+            yp[c] = P.pop2[b * P.N2 + j];
+        } else {
+#pragma unroll
+            for (int q = 0; q < WN; ++q) y[c][q] = 0u;
+            yp[c] = 0;
+        }
+    }
+    const int D = (int)P.D, metric = METRIC >= 0 ? METRIC : P.metric;
+    const float inv_d = P.inv_d;
+    for (int t = 0; t < FW_TILES; ++t) {
+        const long long i0 = (ti * FW_TILES + t) * FW_ROWS;
+        if (i0 >= P.N1) break;
+        const int nr = (int)min((long long)FW_ROWS, P.N1 - i0);
+        __syncthreads();
+        if (threadIdx.x < FW_ROWS) {
+            const bool in = threadIdx.x < nr;
+            reinterpret_cast<uint4 *>(xs)[threadIdx.x] =
+                in ? __ldg(reinterpret_cast<const uint4 *>(P.x1 + (b * P.N1 + i0 + threadIdx.x) * 4)) : make_uint4(0u, 0u, 0u, 0u);
+            xp[threadIdx.x] = in ? P.pop1[b * P.N1 + i0 + threadIdx.x] : 0;
+        }
+        __syncthreads();
+        if (j0 >= P.N2) continue;
+        float *o = P.out + (b * P.N1 + i0) * P.N2 + j0;
+        for (int r = 0; r < nr; ++r) {
+            const uint4 xv = reinterpret_cast<const uint4 *>(xs)[r];
+            const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+            const int a = xp[r];
+            float res[FW_JL];
+#pragma unroll
+            for (int c = 0; c < FW_JL; ++c) {
+                int n11 = 0;
+#pragma unroll
+                for (int q = 0; q < WN; ++q) n11 += __popc(xw[q] & y[c][q]);
+                res[c] = bool_epilogue<true>(metric, n11, a, yp[c], D, inv_d);
+            }
+            float *dst = o + (long long)r * P.N2;
+            if (P.vec_store && jlast < P.N2) {
+                __stcs(reinterpret_cast<float4 *>(dst), make_float4(res[0], res[1], res[2], res[3]));
+                __stcs(reinterpret_cast<float4 *>(dst + 128), make_float4(res[4], res[5], res[6], res[7]));
+            } else {
+#pragma unroll
+                for (int c = 0; c < FW_JL; ++c)
+                    if (j0 + (c >> 2) * 128 + (c & 3) < P.N2) dst[(c >> 2) * 128 + (c & 3)] = res[c];
+            }
+        }
+    }
+}
+
+int launch_few_words(BoolParams P, cudaStream_t s) {
+    P.tiles_i = (P.N1 + FW_ROWS * FW_TILES - 1) / (FW_ROWS * FW_TILES);
+    P.tiles_j = (P.N2 + FW_THREADS * FW_JL - 1) / (FW_THREADS * FW_JL);
+    const long long tiles = P.B * P.tiles_i * P.tiles_j;
+    TPW_CHECK_ARG(tiles < (1ll << 31), "tpw_bool_metric_forward: too many tiles");
+    const int wn = (int)((P.D + 31) / 32);
+#define TPW_FEW_WORDS(M)                                                                                  \
+    switch (wn) {                                                                                         \
+        case 1: bool_few_words_kernel<1, M><<<(unsigned)tiles, FW_THREADS, 0, s>>>(P); break;            \
+        case 2: bool_few_words_kernel<2, M><<<(unsigned)tiles, FW_THREADS, 0, s>>>(P); break;            \
+        case 3: bool_few_words_kernel<3, M><<<(unsigned)tiles, FW_THREADS, 0, s>>>(P); break;            \
+        default: bool_few_words_kernel<4, M><<<(unsigned)tiles, FW_THREADS, 0, s>>>(P); break;           \
+    }
+    if (P.metric == TPW_BOOL_JACCARD) { TPW_FEW_WORDS(TPW_BOOL_JACCARD) }
+    else if (P.metric == TPW_BOOL_NE_MEAN) { TPW_FEW_WORDS(TPW_BOOL_NE_MEAN) }
+    else { TPW_FEW_WORDS(-1) }
+#undef TPW_FEW_WORDS
+    TPW_LAUNCH_OK("bool_few_words_kernel");
+    return TPW_OK;
+}
+
 } // namespace
 } // namespace tpw
 
@@ -310,6 +419,12 @@ extern "C" int tpw_bool_metric_forward(int metric, const uint32_t *x1_words, con
     P.metric = metric;
     P.vec_store = (N2 % 4 == 0 && aligned16(out) && aligned16(x2_popcount)) ? 1 : 0;
     P.inv_d = (D & (D - 1)) == 0 ? 1.0f / (float)D : 0.f;
+    // few words per row on enough rows and columns: the streaming kernel (TPW_DISABLE_SMALL_D=1 keeps the tile kernel)
+    if (D <= 128 && words_per_row == 4 && N1 >= 128 && N2 >= 2048 && aligned16(x1_words) && aligned16(x2_words) &&
+        !getenv("TPW_DISABLE_SMALL_D")) {
+        P.vec_store = (N2 % 4 == 0 && aligned16(out)) ? 1 : 0;
+        return launch_few_words(P, static_cast<cudaStream_t>(stream));
+    }
     P.tiles_i = (N1 + TILE_I - 1) / TILE_I;
     P.tiles_j = (N2 + TILE_J - 1) / TILE_J;
     const long long tiles = B * P.tiles_i * P.tiles_j;

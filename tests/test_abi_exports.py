@@ -50,6 +50,15 @@ def test_argument_errors_are_reported_before_any_launch():
     assert b"NULL" in lib.tpw_last_error()
     assert lib.tpw_bool_metric_forward(77, None, None, None, None, None, 1, 1, 1, 1, 4, None) == 1
     assert lib.tpw_bitpack(None, None, None, 4, 100, 2, None) == 1  # 2 words cannot hold 100 bits
+    assert lib.tpw_jensenshannon_forward(7, None, None, None, 1, 1, 1, 1, 0.5, 0, None) == 1
+    assert b"dtype" in lib.tpw_last_error()
+    assert lib.tpw_jensenshannon_forward(0, None, None, None, 1, 1, 1, 1, 0.5, 2, None) == 1
+    assert b"take_sqrt" in lib.tpw_last_error()
+    assert lib.tpw_jensenshannon_backward(0, None, None, None, None, None, None, 1, 2, 2, 2, 0.5, None) == 1
+    assert lib.tpw_haversine_forward(0, None, None, None, 1, 3, 3, None) == 1
+    assert b"NULL" in lib.tpw_last_error()
+    assert lib.tpw_haversine_backward(0, None, None, None, None, None, 1, -3, 3, None) == 1
+    assert lib.tpw_haversine_forward(0, None, None, None, 1, 0, 3, None) == 0
     # empty problems are fine and launch nothing
     assert lib.tpw_lp_forward(0, None, None, None, None, 0, 4, 4, 4, 2.0, 0.5, None) == 0
     assert lib.tpw_last_error() == b""

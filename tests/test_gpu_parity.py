@@ -1052,6 +1052,35 @@ def test_haversine_golden(tpw, golden, tag):
             tpw.haversine_distances(torch.zeros(4, 3, device="cuda"))
 
 
+def test_jensenshannon_and_haversine_edge_cases(tpw):
+    """Empty operands, batched inputs and narrow dtypes (widened to float32 on entry, rounded once on exit)."""
+    z = torch.zeros(0, 2, device="cuda", requires_grad=True)
+    y = torch.rand(5, 2, device="cuda", requires_grad=True)
+    out = tpw.haversine_distances(z, y)
+    assert out.shape == (0, 5)
+    out.sum().backward()
+    assert z.grad.shape == (0, 2) and float(y.grad.abs().max()) == 0.0
+    h = torch.rand(0, 7, device="cuda")
+    assert tpw.jensenshannon_distances(h, torch.rand(4, 7, device="cuda")).shape == (0, 4)
+    g = torch.Generator().manual_seed(71)
+    hb1, hb2 = torch.rand(3, 20, 11, generator=g).cuda(), torch.rand(3, 17, 11, generator=g).cuda()
+    full = tpw.jensenshannon_distances(hb1, hb2, 2.0)
+    for b in range(3):
+        assert torch.equal(full[b], tpw.jensenshannon_distances(hb1[b], hb2[b], 2.0))
+    pb1, pb2 = (torch.rand(3, 20, 2, generator=g) - 0.5).cuda(), (torch.rand(3, 17, 2, generator=g) - 0.5).cuda()
+    fullh = tpw.haversine_distances(pb1, pb2)
+    for b in range(3):
+        assert torch.equal(fullh[b], tpw.haversine_distances(pb1[b], pb2[b]))
+    for dt, tol in ((torch.float16, 2e-3), (torch.bfloat16, 2e-2)):
+        o = tpw.jensenshannon_distances(hb1.to(dt), hb2.to(dt))
+        assert o.dtype == dt
+        ref = tpw.jensenshannon_distances(hb1.to(dt).float(), hb2.to(dt).float())
+        assert float((o.float() - ref).abs().max()) <= tol
+        o = tpw.haversine_distances(pb1.to(dt), pb2.to(dt))
+        assert o.dtype == dt
+        assert float((o.float() - tpw.haversine_distances(pb1.to(dt).float(), pb2.to(dt).float())).abs().max()) <= tol
+
+
 def test_haversine_large_identities(tpw):
     """At a size no CPU loop finishes quickly: symmetry, the triangle inequality through a third set, the range
     [0, pi], and the backward of sum(out) against a float64 run of the same kernels."""

@@ -590,6 +590,11 @@ def run_suite(args):
             if want(f"OB_euclidean_D{dd}"):
                 entry(f"OB_euclidean_D{dd}", n, timeit(lambda: tpw.euclidean_distances(Xs, Ys)), "hbm (output write)", 4 * n / 1e9, hbm_peak, 4 * n)
             del Xs, Ys
+    if want("NN_euclidean_D3"):
+        Xs, Ys = torch.randn(ro, 3, generator=g).to(dev), torch.randn(16384, 3, generator=g).to(dev)
+        entry("NN_euclidean_D3", n, timeit(lambda: tpw.pairwise_argmin_min(Xs, Ys, "euclidean")),
+              "fp32_issue (nearest row of 16384 for every point, matrix never written)", n * 3 * 2, fp32_peak, 0)
+        del Xs, Ys
     if want("OB_manhattan_D16_rowmin"):
         entry("OB_manhattan_D16_rowmin", n, timeit(lambda: tpw.pairwise_argmin_min(X, Y, "manhattan")),
               "fp32_issue (matrix never written)", n * 16 * 2, fp32_peak, 0)

@@ -265,6 +265,38 @@ def test_few_words_boolean_kernel_is_bit_exact(tpw, monkeypatch, d):
         assert np.array_equal(small["hamming"].cpu().numpy(), O.hamming(xb.numpy(), yb.numpy())), d
 
 
+@pytest.mark.parametrize("d", [1, 3, 4, 8, 13, 16, 32])
+@pytest.mark.parametrize("metric,p", [("manhattan", None), ("sqeuclidean", None), ("euclidean", None), ("chebyshev", None), ("minkowski", 3.0)])
+def test_few_feature_row_minimum(tpw, monkeypatch, d, metric, p):
+    """Nearest x2 row on few features (streaming kernel with the x1 rows in registers) against the tile kernel's
+    row-minimum epilogue: the same column and the same value (within 1 ulp where the two use different square
+    roots), against the matrix written for the same problem (bit-identical), with exact duplicates (ties go to
+    the smaller x2 row) and ragged sizes; and against the float64 oracle."""
+    g = torch.Generator().manual_seed(500 + d)
+    for n1, n2 in ((2051, 131), (2304, 1500)):
+        x1, x2 = torch.randn(2, n1, d, generator=g), torch.randn(2, n2, d, generator=g)
+        x2[:, 77] = x2[:, 5]          # duplicates: ties
+        x1[:, 9] = x2[:, 5]
+        a, b = x1.cuda(), x2.cuda()
+        arg, mn = tpw.pairwise_argmin_min(a, b, metric, p)
+        full = tpw.cdist(a, b, metric, p=p) if p is not None else tpw.cdist(a, b, metric)
+        assert torch.equal(full.min(-1).values, mn), (metric, d, n1, n2)
+        assert torch.equal(full.gather(-1, arg.unsqueeze(-1))[..., 0], mn)
+        assert int(arg[0, 9]) == 5 and float(mn[0, 9]) == 0.0
+        monkeypatch.setenv("TPW_DISABLE_SMALL_D", "1")
+        arg_t, mn_t = tpw.pairwise_argmin_min(a, b, metric, p)
+        monkeypatch.delenv("TPW_DISABLE_SMALL_D")
+        assert bool(((mn - mn_t).abs() <= 1.2e-7 * mn_t.abs()).all())
+        if metric != "euclidean":
+            assert torch.equal(arg, arg_t) and torch.equal(mn, mn_t)
+        pp = {"manhattan": 1.0, "sqeuclidean": 2.0, "euclidean": 2.0, "chebyshev": math.inf, "minkowski": 3.0}[metric]
+        ref = O.cdist(x1.double().numpy(), x2.double().numpy(), pp)
+        ref = ref * ref if metric == "sqeuclidean" else ref
+        close(mn.double(), ref.min(-1), TOL[torch.float32], msg="row minimum")
+        picked = np.take_along_axis(ref, arg.cpu().numpy()[..., None], -1)[..., 0]
+        np.testing.assert_allclose(picked, ref.min(-1), rtol=1e-4, atol=1e-5)
+
+
 def test_tma_and_plain_load_paths_agree(tpw):
     """An input whose base address is not 16-byte aligned takes the guarded plain-load path; it
     stages the same layout, so results are bit-identical to the TMA path."""

@@ -50,7 +50,10 @@ extern "C" int tpw_lp_rowmin_forward(int dtype, const void *x1, const void *x2, 
         P.x1 = x1; P.x2 = x2; P.w = w; P.out = nullptr;
         P.B = B; P.N1 = N1; P.N2 = N2; P.D = D;
         P.rowmin_keys = static_cast<unsigned long long *>(scratch);
-        int st = lp_forward_typed<float, EPI_ROWMIN>(P, p, out_exponent, s);
+        // few features: x1 rows and their running minima in registers, x2 rows broadcast (lp_small_d.cu)
+        int st = lp_small_d_rowmin_eligible(N1, N2, D, p)
+                     ? lp_small_d_rowmin(x1, x2, static_cast<unsigned long long *>(scratch), B, N1, N2, D, p, out_exponent, s)
+                     : lp_forward_typed<float, EPI_ROWMIN>(P, p, out_exponent, s);
         if (st != TPW_OK) return st;
     }
     rowmin_finish_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(static_cast<const unsigned long long *>(scratch), min_out,

@@ -161,6 +161,111 @@ int launch_small_d(const float *x1, const float *x2, float *out, long long B, lo
     return launch_small<KIND, 32, 2>(x1, x2, out, B, N1, N2, D, root_mode, exponent, s);
 }
 
+// ---- streaming row minimum on few features -------------------------------------------------------------------
+// The roles are swapped: every lane keeps JL x1 rows in registers together with their running minimum (as the bit
+// pattern of the non-negative sum, so that NaN ranks above +inf) and the column that gave it; x2 rows pass through
+// shared memory 128 at a time and are read as broadcasts.  Nothing is written per pair and no shuffle is needed:
+// per x2 row a lane spends DP / 4 shared loads, 2 * DP * JL arithmetic lane operations and three compare / select
+// operations per x1 row.  A CTA covers 256 * JL x1 rows and a range of x2 rows; ranges are merged by one atomicMin
+// per x1 row on the key (bits of the finished value << 32 | x2 row), the contract of the tile kernel's epilogue.
+// DC <= DP: features actually combined (D = 2 and D = 3 skip the zero padding of the 4-wide shared-memory rows)
+template <int KIND, int DP, int JL, int DC>
+__global__ void __launch_bounds__(SD_THREADS, 2)
+lp_small_d_rowmin_kernel(const float *__restrict__ x1, const float *__restrict__ x2, unsigned long long *__restrict__ keys,
+                         long long N1, long long N2, int D, long long tiles_i, long long chunks_j, int tiles_per_chunk,
+                         int root_mode, float exponent, int exact_sqrt) {
+    __shared__ __align__(16) float cols[SD_ROWS * DP];
+    const long long tile = blockIdx.x;
+    const long long cj = tile % chunks_j, ti = (tile / chunks_j) % tiles_i, b = tile / (chunks_j * tiles_i);
+    const long long i0 = ti * (SD_THREADS * JL) + threadIdx.x;   // this lane's rows: i0 + c * 256 (coalesced loads)
+    float x[JL][DP];
+    unsigned best[JL], bestj[JL];
+#pragma unroll
+    for (int c = 0; c < JL; ++c) {
+        const long long i = i0 + (long long)c * SD_THREADS;
+        const float *src = x1 + (b * N1 + (i < N1 ? i : 0)) * D;
+#pragma unroll
+        for (int k = 0; k < DP; ++k) x[c][k] = (i < N1 && k < D) ? src[k] : 0.f;
+        best[c] = 0xFFFFFFFFu;
+        bestj[c] = 0xFFFFFFFFu;
+    }
+    const long long jbeg = cj * tiles_per_chunk * SD_ROWS;
+    for (int t = 0; t < tiles_per_chunk; ++t) {
+        const long long j0 = jbeg + (long long)t * SD_ROWS;
+        if (j0 >= N2) break;
+        const int nc = (int)min((long long)SD_ROWS, N2 - j0);
+        const float *x2b = x2 + (b * N2 + j0) * D;
+        __syncthreads();
+        for (int e = threadIdx.x; e < SD_ROWS * DP; e += SD_THREADS) {
+            const int r = e / DP, k = e % DP;
+            cols[e] = (r < nc && k < D) ? x2b[(long long)r * D + k] : 0.f;
+        }
+        __syncthreads();
+        for (int r = 0; r < nc; ++r) {
+            float acc[JL];
+#pragma unroll
+            for (int c = 0; c < JL; ++c) acc[c] = 0.f;
+#pragma unroll
+            for (int k4 = 0; k4 < DP; k4 += 4) {
+                const float4 yv = *reinterpret_cast<const float4 *>(&cols[r * DP + k4]);
+#pragma unroll
+                for (int c = 0; c < JL; ++c) {
+                    if (k4 < DC) sd_acc<KIND>(acc[c], x[c][k4], yv.x);
+                    if (k4 + 1 < DC) sd_acc<KIND>(acc[c], x[c][k4 + 1], yv.y);
+                    if (k4 + 2 < DC) sd_acc<KIND>(acc[c], x[c][k4 + 2], yv.z);
+                    if (k4 + 3 < DC) sd_acc<KIND>(acc[c], x[c][k4 + 3], yv.w);
+                }
+            }
+            const unsigned j = (unsigned)(j0 + r);
+#pragma unroll
+            for (int c = 0; c < JL; ++c) {
+                const unsigned bits = __float_as_uint(acc[c]);
+                const bool better = bits < best[c];   // strict: the first (smallest) column keeps an exact tie
+                best[c] = better ? bits : best[c];
+                bestj[c] = better ? j : bestj[c];
+            }
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < JL; ++c) {
+        const long long i = i0 + (long long)c * SD_THREADS;
+        if (i < N1 && bestj[c] != 0xFFFFFFFFu) {
+            // monotone: the root of the minimum; the square root is the one the matrix-writing kernel of the same
+            // problem uses, so that the row minimum equals the minimum of that matrix bit for bit
+            const float m = __uint_as_float(best[c]);
+            const float v = (root_mode == 1 && exact_sqrt) ? sqrtf(m) : sd_root(m, root_mode, exponent);
+            atomicMin(&keys[b * N1 + i], ((unsigned long long)__float_as_uint(v) << 32) | bestj[c]);
+        }
+    }
+}
+
+template <int KIND, int DP, int JL, int DC = DP>
+int launch_small_rowmin(const float *x1, const float *x2, unsigned long long *keys, long long B, long long N1, long long N2, int D,
+                        int root_mode, float exponent, cudaStream_t s) {
+    const long long ti = (N1 + SD_THREADS * JL - 1) / (SD_THREADS * JL);
+    const long long col_tiles = (N2 + SD_ROWS - 1) / SD_ROWS;
+    // x2 ranges of up to 8 tiles, shortened while the grid would leave SMs idle
+    long long per = 8;
+    while (per > 1 && B * ti * ((col_tiles + per - 1) / per) < 592) per /= 2;
+    const long long cj = (col_tiles + per - 1) / per, tiles = B * ti * cj;
+    TPW_CHECK_ARG(tiles < (1ll << 31), "lp row minimum (few features): too many tiles (%lld)", tiles);
+    const int exact_sqrt = lp_small_d_eligible(N1, N2, D, 2.0) ? 0 : 1;
+    lp_small_d_rowmin_kernel<KIND, DP, JL, DC><<<(unsigned)tiles, SD_THREADS, 0, s>>>(x1, x2, keys, N1, N2, D, ti, cj, (int)per, root_mode, exponent, exact_sqrt);
+    TPW_LAUNCH_OK("lp_small_d_rowmin_kernel");
+    return TPW_OK;
+}
+
+template <int KIND>
+int launch_small_d_rowmin(const float *x1, const float *x2, unsigned long long *keys, long long B, long long N1, long long N2, int D,
+                          int root_mode, float exponent, cudaStream_t s) {
+    if (D <= 2) return launch_small_rowmin<KIND, 4, 8, 2>(x1, x2, keys, B, N1, N2, D, root_mode, exponent, s);
+    if (D == 3) return launch_small_rowmin<KIND, 4, 8, 3>(x1, x2, keys, B, N1, N2, D, root_mode, exponent, s);
+    if (D <= 4) return launch_small_rowmin<KIND, 4, 8>(x1, x2, keys, B, N1, N2, D, root_mode, exponent, s);
+    if (D <= 8) return launch_small_rowmin<KIND, 8, 8>(x1, x2, keys, B, N1, N2, D, root_mode, exponent, s);
+    if (D <= 16) return launch_small_rowmin<KIND, 16, 4>(x1, x2, keys, B, N1, N2, D, root_mode, exponent, s);
+    return launch_small_rowmin<KIND, 32, 2>(x1, x2, keys, B, N1, N2, D, root_mode, exponent, s);
+}
+
 } // namespace
 
 // Whether the few-feature kernel serves this float32 problem: D <= 32, an exponent with a closed form, and
@@ -185,6 +290,32 @@ int lp_small_d_forward(const void *x1, const void *x2, void *out, long long B, l
     if (p == 1.0) return launch_small_d<SK_L1>(a, b, o, B, N1, N2, (int)D, root_mode, ex, s);
     if (p == 2.0) return launch_small_d<SK_P2>(a, b, o, B, N1, N2, (int)D, root_mode, ex, s);
     return launch_small_d<SK_P3>(a, b, o, B, N1, N2, (int)D, root_mode, ex, s);
+}
+
+} // namespace tpw
+
+namespace tpw {
+
+// The row-minimum variant: same exponents, at least 2048 x1 rows (a CTA holds 512 to 2048 of them) and 128 x2 rows.
+bool lp_small_d_rowmin_eligible(long long N1, long long N2, long long D, double p) {
+    if (getenv("TPW_DISABLE_SMALL_D")) return false;
+    return D >= 1 && D <= 32 && N1 >= 2048 && N2 >= 128 && (p == 1.0 || p == 2.0 || p == 3.0 || (isinf(p) && p > 0));
+}
+
+// keys: B * N1 64-bit keys already set to all ones
+int lp_small_d_rowmin(const void *x1, const void *x2, unsigned long long *keys, long long B, long long N1, long long N2, long long D,
+                      double p, double out_exponent, cudaStream_t s) {
+    int root_mode;
+    if (isinf(p) || out_exponent == 1.0) root_mode = 0;
+    else if (out_exponent == 0.5) root_mode = 1;
+    else if (p == 3.0 && out_exponent == 1.0 / 3.0) root_mode = 2;
+    else root_mode = 3;
+    const float *a = (const float *)x1, *b = (const float *)x2;
+    const float ex = (float)out_exponent;
+    if (isinf(p)) return launch_small_d_rowmin<SK_MAX>(a, b, keys, B, N1, N2, (int)D, root_mode, ex, s);
+    if (p == 1.0) return launch_small_d_rowmin<SK_L1>(a, b, keys, B, N1, N2, (int)D, root_mode, ex, s);
+    if (p == 2.0) return launch_small_d_rowmin<SK_P2>(a, b, keys, B, N1, N2, (int)D, root_mode, ex, s);
+    return launch_small_d_rowmin<SK_P3>(a, b, keys, B, N1, N2, (int)D, root_mode, ex, s);
 }
 
 } // namespace tpw

@@ -595,6 +595,11 @@ def run_suite(args):
         entry("NN_euclidean_D3", n, timeit(lambda: tpw.pairwise_argmin_min(Xs, Ys, "euclidean")),
               "fp32_issue (nearest row of 16384 for every point, matrix never written)", n * 3 * 2, fp32_peak, 0)
         del Xs, Ys
+    if want("RM_euclidean_D3"):
+        Xs, Ys = torch.randn(ro, 3, generator=g).to(dev), torch.randn(16384, 3, generator=g).to(dev)
+        entry("RM_euclidean_D3", n, timeit(lambda: tpw.radius_neighbors_mask(Xs, Ys, 1.0, "euclidean")),
+              "fp32_issue (radius test, one byte per pair)", n * 3 * 2, fp32_peak, n)
+        del Xs, Ys
     if want("OB_manhattan_D16_rowmin"):
         entry("OB_manhattan_D16_rowmin", n, timeit(lambda: tpw.pairwise_argmin_min(X, Y, "manhattan")),
               "fp32_issue (matrix never written)", n * 16 * 2, fp32_peak, 0)

@@ -879,7 +879,9 @@ def test_pairwise_argmin_min_ties_and_edges(tpw):
     assert e_arg.shape == (0,) and e_mn.shape == (0,)
 
 
-@pytest.mark.parametrize("shapes", [((130, 7), (257, 7)), ((3, 200, 32), (3, 144, 32)), ((513, 36), (1008, 36)), ((1, 5), (1, 5))],
+@pytest.mark.parametrize("shapes", [((130, 7), (257, 7)), ((3, 200, 32), (3, 144, 32)), ((513, 36), (1008, 36)), ((1, 5), (1, 5)),
+                                    # few features on enough rows and columns: the streaming kernel's mask epilogue
+                                    ((131, 3), (1029, 3)), ((2, 256, 8), (2, 2048, 8)), ((300, 16), (1026, 16)), ((130, 29), (1031, 29))],
                          ids=lambda s: "x".join(map(str, s[0])) + "_" + "x".join(map(str, s[1])))
 def test_radius_mask_fused_equals_compare_pass(tpw, shapes):
     """radius_neighbors_mask through the fused epilogue (one byte per pair, no float matrix) equals

@@ -66,6 +66,8 @@ int make_tensor_map_3d_atom32(CUtensorMap *map, const void *base, int elem_bytes
 bool lp_small_d_eligible(long long N1, long long N2, long long D, double p);
 int lp_small_d_forward(const void *x1, const void *x2, void *out, long long B, long long N1, long long N2, long long D,
                        double p, double out_exponent, cudaStream_t s);
+int lp_small_d_mask(const void *x1, const void *x2, unsigned char *mask, long long B, long long N1, long long N2, long long D,
+                    double p, double out_exponent, double radius, cudaStream_t s);
 bool lp_small_d_rowmin_eligible(long long N1, long long N2, long long D, double p);
 int lp_small_d_rowmin(const void *x1, const void *x2, unsigned long long *keys, long long B, long long N1, long long N2, long long D,
                       double p, double out_exponent, cudaStream_t s);

@@ -81,6 +81,8 @@ extern "C" int tpw_lp_radius_mask_forward(int dtype, const void *x1, const void 
     P.threshold = radius;
     P.mask_vec = (N2 % 16 == 0 && aligned16(mask)) ? 1 : 0;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // few features: the streaming kernel of lp_small_d.cu with the radius test as its epilogue
+    if (dtype == TPW_F32 && lp_small_d_eligible(N1, N2, D, p)) return lp_small_d_mask(x1, x2, mask, B, N1, N2, D, p, out_exponent, radius, s);
     return dtype == TPW_F32 ? lp_forward_typed<float, EPI_MASK>(P, p, out_exponent, s) : lp_forward_typed<double, EPI_MASK>(P, p, out_exponent, s);
 }
 

@@ -43,9 +43,12 @@ __device__ __forceinline__ float sd_root(float v, int root_mode, float exponent)
     return powf(v, exponent);
 }
 
-template <int KIND, int DP, int JL>
+// MASK: instead of the float matrix, one byte per pair: finished value <= threshold (the radius test), written as
+// 4-byte groups so that a warp's store still covers 128 contiguous bytes.
+template <int KIND, int DP, int JL, bool MASK>
 __global__ void __launch_bounds__(SD_THREADS, 2)
 lp_small_d_kernel(const float *__restrict__ x1, const float *__restrict__ x2, float *__restrict__ out,
+                  unsigned char *__restrict__ mask, float threshold,
                   long long N1, long long N2, int D, long long tiles_i, long long tiles_j, int root_mode, float exponent,
                   int vec_store, int vec_load) {
     constexpr int COLS = SD_THREADS * JL;   // x2 rows per CTA
@@ -104,7 +107,8 @@ lp_small_d_kernel(const float *__restrict__ x1, const float *__restrict__ x2, fl
         __syncthreads();
         if (j0 >= N2) continue;
 
-        float *o = out + (b * N1 + i0) * N2 + j0;
+        float *o = MASK ? nullptr : out + (b * N1 + i0) * N2 + j0;
+        unsigned char *om = MASK ? mask + (b * N1 + i0) * N2 + j0 : nullptr;
         for (int r = 0; r < nr; ++r) {
             float acc[JL];
 #pragma unroll
@@ -122,6 +126,24 @@ lp_small_d_kernel(const float *__restrict__ x1, const float *__restrict__ x2, fl
             }
 #pragma unroll
             for (int c = 0; c < JL; ++c) acc[c] = sd_root(acc[c], root_mode, exponent);
+            if constexpr (MASK) {
+                unsigned char *dm = om + (long long)r * N2;
+                if (vec_store && jlast < N2) {
+                    if constexpr (JL == 2) {
+                        *reinterpret_cast<uchar2 *>(dm) = make_uchar2(acc[0] <= threshold, acc[1] <= threshold);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < JL; c += 4)
+                            *reinterpret_cast<uchar4 *>(dm + (c / 4) * 128) =
+                                make_uchar4(acc[c] <= threshold, acc[c + 1] <= threshold, acc[c + 2] <= threshold, acc[c + 3] <= threshold);
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < JL; ++c)
+                        if (j0 + (c / G) * (32 * G) + c % G < N2) dm[(c / G) * (32 * G) + c % G] = acc[c] <= threshold;
+                }
+                continue;
+            }
             float *dst = o + (long long)r * N2;
             if (vec_store && jlast < N2) {
                 if constexpr (JL == 2) {
@@ -140,25 +162,45 @@ lp_small_d_kernel(const float *__restrict__ x1, const float *__restrict__ x2, fl
     }
 }
 
-template <int KIND, int DP, int JL>
-int launch_small(const float *x1, const float *x2, float *out, long long B, long long N1, long long N2, int D,
-                 int root_mode, float exponent, cudaStream_t s) {
+template <int KIND, int DP, int JL, bool MASK>
+int launch_small(const float *x1, const float *x2, float *out, unsigned char *mask, float threshold, long long B, long long N1,
+                 long long N2, int D, int root_mode, float exponent, cudaStream_t s) {
     const long long ti = (N1 + SD_ROWS * SD_TILES - 1) / (SD_ROWS * SD_TILES), tj = (N2 + SD_THREADS * JL - 1) / (SD_THREADS * JL), tiles = B * ti * tj;
     TPW_CHECK_ARG(tiles < (1ll << 31), "lp forward (few features): too many tiles (%lld)", tiles);
-    const int vec = (N2 % (JL < 4 ? JL : 4) == 0 && (reinterpret_cast<uintptr_t>(out) % (JL == 2 ? 8 : 16)) == 0) ? 1 : 0;
+    constexpr int G = JL < 4 ? JL : 4;
+    const int vec = MASK ? ((N2 % G == 0 && reinterpret_cast<uintptr_t>(mask) % G == 0) ? 1 : 0)
+                         : ((N2 % G == 0 && (reinterpret_cast<uintptr_t>(out) % (JL == 2 ? 8 : 16)) == 0) ? 1 : 0);
     const int vload = (D == DP && reinterpret_cast<uintptr_t>(x1) % 16 == 0 && reinterpret_cast<uintptr_t>(x2) % 16 == 0) ? 1 : 0;
-    lp_small_d_kernel<KIND, DP, JL><<<(unsigned)tiles, SD_THREADS, 0, s>>>(x1, x2, out, N1, N2, D, ti, tj, root_mode, exponent, vec, vload);
+    lp_small_d_kernel<KIND, DP, JL, MASK><<<(unsigned)tiles, SD_THREADS, 0, s>>>(x1, x2, out, mask, threshold, N1, N2, D, ti, tj, root_mode,
+                                                                               exponent, vec, vload);
     TPW_LAUNCH_OK("lp_small_d_kernel");
     return TPW_OK;
 }
 
-template <int KIND>
-int launch_small_d(const float *x1, const float *x2, float *out, long long B, long long N1, long long N2, int D,
-                   int root_mode, float exponent, cudaStream_t s) {
-    if (D <= 4) return launch_small<KIND, 4, 8>(x1, x2, out, B, N1, N2, D, root_mode, exponent, s);
-    if (D <= 8) return launch_small<KIND, 8, 8>(x1, x2, out, B, N1, N2, D, root_mode, exponent, s);
-    if (D <= 16) return launch_small<KIND, 16, 4>(x1, x2, out, B, N1, N2, D, root_mode, exponent, s);
-    return launch_small<KIND, 32, 2>(x1, x2, out, B, N1, N2, D, root_mode, exponent, s);
+template <int KIND, bool MASK>
+int launch_small_d(const float *x1, const float *x2, float *out, unsigned char *mask, float threshold, long long B, long long N1,
+                   long long N2, int D, int root_mode, float exponent, cudaStream_t s) {
+    if (D <= 4) return launch_small<KIND, 4, 8, MASK>(x1, x2, out, mask, threshold, B, N1, N2, D, root_mode, exponent, s);
+    if (D <= 8) return launch_small<KIND, 8, 8, MASK>(x1, x2, out, mask, threshold, B, N1, N2, D, root_mode, exponent, s);
+    if (D <= 16) return launch_small<KIND, 16, 4, MASK>(x1, x2, out, mask, threshold, B, N1, N2, D, root_mode, exponent, s);
+    return launch_small<KIND, 32, 2, MASK>(x1, x2, out, mask, threshold, B, N1, N2, D, root_mode, exponent, s);
+}
+
+template <bool MASK>
+int small_d_dispatch(const void *x1, const void *x2, void *out, unsigned char *mask, double threshold, long long B, long long N1,
+                     long long N2, long long D, double p, double out_exponent, cudaStream_t s) {
+    int root_mode;
+    if (isinf(p) || out_exponent == 1.0) root_mode = 0;
+    else if (out_exponent == 0.5) root_mode = 1;
+    else if (p == 3.0 && out_exponent == 1.0 / 3.0) root_mode = 2;
+    else root_mode = 3;
+    const float *a = (const float *)x1, *b = (const float *)x2;
+    float *o = (float *)out;
+    const float ex = (float)out_exponent, th = (float)threshold;
+    if (isinf(p)) return launch_small_d<SK_MAX, MASK>(a, b, o, mask, th, B, N1, N2, (int)D, root_mode, ex, s);
+    if (p == 1.0) return launch_small_d<SK_L1, MASK>(a, b, o, mask, th, B, N1, N2, (int)D, root_mode, ex, s);
+    if (p == 2.0) return launch_small_d<SK_P2, MASK>(a, b, o, mask, th, B, N1, N2, (int)D, root_mode, ex, s);
+    return launch_small_d<SK_P3, MASK>(a, b, o, mask, th, B, N1, N2, (int)D, root_mode, ex, s);
 }
 
 // ---- streaming row minimum on few features -------------------------------------------------------------------
@@ -278,18 +320,13 @@ bool lp_small_d_eligible(long long N1, long long N2, long long D, double p) {
 
 int lp_small_d_forward(const void *x1, const void *x2, void *out, long long B, long long N1, long long N2, long long D,
                        double p, double out_exponent, cudaStream_t s) {
-    int root_mode;
-    if (isinf(p) || out_exponent == 1.0) root_mode = 0;
-    else if (out_exponent == 0.5) root_mode = 1;
-    else if (p == 3.0 && out_exponent == 1.0 / 3.0) root_mode = 2;
-    else root_mode = 3;
-    const float *a = (const float *)x1, *b = (const float *)x2;
-    float *o = (float *)out;
-    const float ex = (float)out_exponent;
-    if (isinf(p)) return launch_small_d<SK_MAX>(a, b, o, B, N1, N2, (int)D, root_mode, ex, s);
-    if (p == 1.0) return launch_small_d<SK_L1>(a, b, o, B, N1, N2, (int)D, root_mode, ex, s);
-    if (p == 2.0) return launch_small_d<SK_P2>(a, b, o, B, N1, N2, (int)D, root_mode, ex, s);
-    return launch_small_d<SK_P3>(a, b, o, B, N1, N2, (int)D, root_mode, ex, s);
+    return small_d_dispatch<false>(x1, x2, out, nullptr, 0.0, B, N1, N2, D, p, out_exponent, s);
+}
+
+// mask[b,i,j] = finished value <= radius, one byte per pair; same eligibility as the matrix-writing kernel
+int lp_small_d_mask(const void *x1, const void *x2, unsigned char *mask, long long B, long long N1, long long N2, long long D,
+                    double p, double out_exponent, double radius, cudaStream_t s) {
+    return small_d_dispatch<true>(x1, x2, nullptr, mask, radius, B, N1, N2, D, p, out_exponent, s);
 }
 
 } // namespace tpw

@@ -595,6 +595,13 @@ def run_suite(args):
         entry("NN_euclidean_D3", n, timeit(lambda: tpw.pairwise_argmin_min(Xs, Ys, "euclidean")),
               "fp32_issue (nearest row of 16384 for every point, matrix never written)", n * 3 * 2, fp32_peak, 0)
         del Xs, Ys
+    if want("KNN8_euclidean_D3") or want("KNN16_euclidean_D3"):
+        Xs, Ys = torch.randn(ro, 3, generator=g).to(dev), torch.randn(16384, 3, generator=g).to(dev)
+        for kk in (8, 16):
+            if want(f"KNN{kk}_euclidean_D3"):
+                entry(f"KNN{kk}_euclidean_D3", n, timeit(lambda: tpw.pairwise_argkmin(Xs, Ys, kk, "euclidean")),
+                      f"fp32_issue ({kk} nearest of 16384 points for every point, matrix never written)", n * 3 * 2, fp32_peak, 0)
+        del Xs, Ys
     if want("RM_euclidean_D3"):
         Xs, Ys = torch.randn(ro, 3, generator=g).to(dev), torch.randn(16384, 3, generator=g).to(dev)
         entry("RM_euclidean_D3", n, timeit(lambda: tpw.radius_neighbors_mask(Xs, Ys, 1.0, "euclidean")),

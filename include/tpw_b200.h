@@ -113,6 +113,21 @@ TPW_API int tpw_lp_rowmin_forward(int dtype, const void *x1, const void *x2, con
                           double p, double out_exponent, tpw_stream_t stream);
 
 /*
+ * The k nearest x2 rows of every x1 row on few features, ascending: vals[b,i,t] = the t-th smallest out[b,i,j] as
+ * tpw_lp_forward defines it (p in {1, 2, 3, +inf}), inds[b,i,t] = its j; exact ties go to the smaller j.
+ * float32, D <= tpw_lp_topk_max_features(), k <= min(tpw_lp_topk_max_k(), N2).  One x1 row per thread with its k
+ * best keys in registers; every thread walks over all x2 rows of its batch, so nothing but B*N1*k results is
+ * written, no scratch is needed, and the result is deterministic.  A NaN distance ranks above +inf.
+ * No counterpart in the reference (k_neighbors_mask sorts every row of the materialised matrix,
+ * OPS/neighbors.cpp:10-35; its README lists argkmin as future work).
+ */
+TPW_API int tpw_lp_topk_max_features(void);
+TPW_API int tpw_lp_topk_max_k(void);
+TPW_API int tpw_lp_topk_forward(int dtype, const void *x1, const void *x2, float *vals, int64_t *inds,
+                        int64_t B, int64_t N1, int64_t N2, int64_t D, int k, double p, double out_exponent,
+                        tpw_stream_t stream);
+
+/*
  * mask[b,i,j] = (out[b,i,j] <= radius) as one byte (0 / 1) per pair, for out as tpw_lp_forward
  * defines it with finite p > 0 or p = +inf: the comparison of radius_neighbors_mask
  * (OPS/neighbors.cpp:37-58: cdist(x1, x2, metric) <= epsilon) fused into the tile epilogue, so the

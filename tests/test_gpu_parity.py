@@ -297,6 +297,36 @@ def test_few_feature_row_minimum(tpw, monkeypatch, d, metric, p):
         np.testing.assert_allclose(picked, ref.min(-1), rtol=1e-4, atol=1e-5)
 
 
+@pytest.mark.parametrize("d", [1, 2, 3, 4, 7, 8, 12, 16])
+@pytest.mark.parametrize("metric,kw,k", [("euclidean", {}, 8), ("sqeuclidean", {}, 1), ("manhattan", {}, 16), ("chebyshev", {}, 5),
+                                         ("minkowski", {"p": 3.0}, 3)])
+def test_few_feature_k_nearest(tpw, d, metric, kw, k):
+    """The streaming k-nearest kernel on few features against a partial selection on the matrix of the same problem:
+    the same ascending values bit for bit, valid distinct columns that attain them, exact duplicates resolved to
+    the smaller x2 row, ragged sizes, batched inputs; and the neighbour mask built from it."""
+    g = torch.Generator().manual_seed(600 + d)
+    for shape1, shape2 in (((4099, d), (333, d)), ((2, 2100, d), (2, 1030, d))):
+        x1, x2 = torch.randn(*shape1, generator=g), torch.randn(*shape2, generator=g)
+        x2[..., 40, :] = x2[..., 7, :]      # a duplicate: ties between columns 7 and 40
+        x1[..., 3, :] = x2[..., 7, :]
+        a, b = x1.cuda(), x2.cuda()
+        inds, vals = tpw.pairwise_argkmin(a, b, k, metric, **kw)
+        assert inds.shape == (*shape1[:-1], k) and inds.dtype == torch.int64 and vals.dtype == torch.float32
+        full = tpw.cdist(a, b, metric, **kw)
+        ref_vals = full.topk(k, dim=-1, largest=False, sorted=True).values
+        assert torch.equal(vals, ref_vals), (metric, d)
+        assert torch.equal(full.gather(-1, inds), vals)
+        assert int((inds.sort(-1).values.diff(dim=-1) == 0).sum()) == 0          # distinct columns
+        row = inds[3] if len(shape1) == 2 else inds[0, 3]
+        assert int(row[0]) == 7 and (k == 1 or int(row[1]) == 40)
+    if metric == "euclidean":
+        xs = torch.randn(4200, d, generator=g).cuda()
+        mask = tpw.k_neighbors_mask(xs, None, 4, metric)
+        assert mask.dtype == torch.bool and bool((mask.sum(-1) == 5).all()) and bool(mask.diagonal().all())
+        assert torch.equal(mask, tpw.k_neighbors_mask(xs.double(), None, 4, metric)) or \
+            int((mask != tpw.k_neighbors_mask(xs.double(), None, 4, metric)).sum()) <= 8     # float32 / float64 near ties
+
+
 def test_tma_and_plain_load_paths_agree(tpw):
     """An input whose base address is not 16-byte aligned takes the guarded plain-load path; it
     stages the same layout, so results are bit-identical to the TMA path."""

@@ -42,6 +42,9 @@ SIGNATURES = {
     "tpw_lp_forward": (_I, [_I, _P, _P, _P, _P, _L, _L, _L, _L, _D, _D, _P]),
     "tpw_lp_rowmin_scratch_bytes": (_L, [_L, _L]),
     "tpw_lp_rowmin_forward": (_I, [_I, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _D, _D, _P]),
+    "tpw_lp_topk_max_features": (_I, []),
+    "tpw_lp_topk_max_k": (_I, []),
+    "tpw_lp_topk_forward": (_I, [_I, _P, _P, _P, _P, _L, _L, _L, _L, _I, _D, _D, _P]),
     "tpw_lp_radius_mask_forward": (_I, [_I, _P, _P, _P, _P, _L, _L, _L, _L, _D, _D, _D, _P]),
     "tpw_lp_pdist_forward": (_I, [_I, _P, _P, _L, _L, _L, _D, _D, _P]),
     "tpw_pair_sum_forward": (_I, [_I, _I, _P, _P, _P, _L, _L, _L, _L, _P]),

@@ -308,6 +308,97 @@ int launch_small_d_rowmin(const float *x1, const float *x2, unsigned long long *
     return launch_small_rowmin<KIND, 32, 2>(x1, x2, keys, B, N1, N2, D, root_mode, exponent, s);
 }
 
+// ---- streaming k nearest rows on few features ------------------------------------------------------------------
+// One x1 row per thread: its features and an ascending list of the K smallest keys (bits of the non-negative sum << 32
+// | x2 row) stay in registers while the CTA walks over all of x2 through shared memory, 128 rows at a time.  A
+// candidate costs the distance arithmetic and one comparison against the list's last key; the unrolled insertion
+// (K compare-select pairs) runs only when some lane of the warp has a candidate below its bound, which happens about
+// K ln(N2 / K) times per row.  No scratch, no atomics: a thread sees every x2 row of its batch.
+constexpr int TK_THREADS = 128;
+
+template <int KIND, int DP, int DC, int K>
+__global__ void __launch_bounds__(TK_THREADS)
+lp_small_d_topk_kernel(const float *__restrict__ x1, const float *__restrict__ x2, float *__restrict__ vals, long long *__restrict__ inds,
+                       long long N1, long long N2, int D, long long tiles_i, int k_out, int root_mode, float exponent, int exact_sqrt) {
+    __shared__ __align__(16) float cols[SD_ROWS * DP];
+    const long long b = blockIdx.x / tiles_i, i = (blockIdx.x % tiles_i) * TK_THREADS + threadIdx.x;
+    float x[DP];
+    {
+        const float *src = x1 + (b * N1 + (i < N1 ? i : 0)) * D;
+#pragma unroll
+        for (int k = 0; k < DP; ++k) x[k] = (i < N1 && k < D) ? src[k] : 0.f;
+    }
+    unsigned long long list[K];
+#pragma unroll
+    for (int t = 0; t < K; ++t) list[t] = ~0ull;
+    for (long long j0 = 0; j0 < N2; j0 += SD_ROWS) {
+        const int nc = (int)min((long long)SD_ROWS, N2 - j0);
+        const float *x2b = x2 + (b * N2 + j0) * D;
+        __syncthreads();
+        for (int e = threadIdx.x; e < SD_ROWS * DP; e += TK_THREADS) {
+            const int r = e / DP, k = e % DP;
+            cols[e] = (r < nc && k < D) ? x2b[(long long)r * D + k] : 0.f;
+        }
+        __syncthreads();
+        for (int r = 0; r < nc; ++r) {
+            float acc = 0.f;
+#pragma unroll
+            for (int k4 = 0; k4 < DP; k4 += 4) {
+                const float4 yv = *reinterpret_cast<const float4 *>(&cols[r * DP + k4]);
+                if (k4 < DC) sd_acc<KIND>(acc, x[k4], yv.x);
+                if (k4 + 1 < DC) sd_acc<KIND>(acc, x[k4 + 1], yv.y);
+                if (k4 + 2 < DC) sd_acc<KIND>(acc, x[k4 + 2], yv.z);
+                if (k4 + 3 < DC) sd_acc<KIND>(acc, x[k4 + 3], yv.w);
+            }
+            const unsigned long long key = ((unsigned long long)__float_as_uint(acc) << 32) | (unsigned)(j0 + r);
+            if (key < list[K - 1]) {
+#pragma unroll
+                for (int t = K - 1; t > 0; --t) {
+                    const unsigned long long below = list[t - 1];
+                    list[t] = key < below ? below : (key < list[t] ? key : list[t]);
+                }
+                list[0] = key < list[0] ? key : list[0];
+            }
+        }
+    }
+    if (i >= N1) return;
+    float *vo = vals + (b * N1 + i) * k_out;
+    long long *io = inds + (b * N1 + i) * k_out;
+#pragma unroll
+    for (int t = 0; t < K; ++t) {
+        if (t < k_out) {
+            const float m = __uint_as_float((unsigned)(list[t] >> 32));
+            vo[t] = (root_mode == 1 && exact_sqrt) ? sqrtf(m) : sd_root(m, root_mode, exponent);
+            io[t] = (long long)(unsigned)(list[t] & 0xFFFFFFFFull);
+        }
+    }
+}
+
+template <int KIND, int DP, int DC>
+int launch_small_topk(const float *x1, const float *x2, float *vals, long long *inds, long long B, long long N1, long long N2, int D,
+                      int k, int root_mode, float exponent, cudaStream_t s) {
+    const long long ti = (N1 + TK_THREADS - 1) / TK_THREADS, tiles = B * ti;
+    TPW_CHECK_ARG(tiles < (1ll << 31), "lp k nearest (few features): too many tiles (%lld)", tiles);
+    const int ex = lp_small_d_eligible(N1, N2, D, 2.0) ? 0 : 1;
+#define TPW_TOPK(KK) lp_small_d_topk_kernel<KIND, DP, DC, KK><<<(unsigned)tiles, TK_THREADS, 0, s>>>(x1, x2, vals, inds, N1, N2, D, ti, k, root_mode, exponent, ex)
+    if (k <= 4) TPW_TOPK(4);
+    else if (k <= 8) TPW_TOPK(8);
+    else TPW_TOPK(16);
+#undef TPW_TOPK
+    TPW_LAUNCH_OK("lp_small_d_topk_kernel");
+    return TPW_OK;
+}
+
+template <int KIND>
+int launch_small_d_topk(const float *x1, const float *x2, float *vals, long long *inds, long long B, long long N1, long long N2, int D,
+                        int k, int root_mode, float exponent, cudaStream_t s) {
+    if (D <= 2) return launch_small_topk<KIND, 4, 2>(x1, x2, vals, inds, B, N1, N2, D, k, root_mode, exponent, s);
+    if (D == 3) return launch_small_topk<KIND, 4, 3>(x1, x2, vals, inds, B, N1, N2, D, k, root_mode, exponent, s);
+    if (D <= 4) return launch_small_topk<KIND, 4, 4>(x1, x2, vals, inds, B, N1, N2, D, k, root_mode, exponent, s);
+    if (D <= 8) return launch_small_topk<KIND, 8, 8>(x1, x2, vals, inds, B, N1, N2, D, k, root_mode, exponent, s);
+    return launch_small_topk<KIND, 16, 16>(x1, x2, vals, inds, B, N1, N2, D, k, root_mode, exponent, s);
+}
+
 } // namespace
 
 // Whether the few-feature kernel serves this float32 problem: D <= 32, an exponent with a closed form, and
@@ -356,3 +447,43 @@ int lp_small_d_rowmin(const void *x1, const void *x2, unsigned long long *keys, 
 }
 
 } // namespace tpw
+
+namespace tpw {
+
+int lp_small_d_topk(const void *x1, const void *x2, float *vals, long long *inds, long long B, long long N1, long long N2, long long D,
+                    int k, double p, double out_exponent, cudaStream_t s) {
+    int root_mode;
+    if (isinf(p) || out_exponent == 1.0) root_mode = 0;
+    else if (out_exponent == 0.5) root_mode = 1;
+    else if (p == 3.0 && out_exponent == 1.0 / 3.0) root_mode = 2;
+    else root_mode = 3;
+    const float *a = (const float *)x1, *b = (const float *)x2;
+    const float ex = (float)out_exponent;
+    if (isinf(p)) return launch_small_d_topk<SK_MAX>(a, b, vals, inds, B, N1, N2, (int)D, k, root_mode, ex, s);
+    if (p == 1.0) return launch_small_d_topk<SK_L1>(a, b, vals, inds, B, N1, N2, (int)D, k, root_mode, ex, s);
+    if (p == 2.0) return launch_small_d_topk<SK_P2>(a, b, vals, inds, B, N1, N2, (int)D, k, root_mode, ex, s);
+    return launch_small_d_topk<SK_P3>(a, b, vals, inds, B, N1, N2, (int)D, k, root_mode, ex, s);
+}
+
+} // namespace tpw
+
+extern "C" int tpw_lp_topk_max_features() { return 16; }
+extern "C" int tpw_lp_topk_max_k() { return 16; }
+
+extern "C" int tpw_lp_topk_forward(int dtype, const void *x1, const void *x2, float *vals, int64_t *inds,
+                                   int64_t B, int64_t N1, int64_t N2, int64_t D, int k, double p, double out_exponent,
+                                   tpw_stream_t stream) {
+    using namespace tpw;
+    clear_error();
+    TPW_CHECK_ARG(dtype == TPW_F32, "tpw_lp_topk_forward: dtype must be TPW_F32");
+    TPW_CHECK_ARG(B >= 0 && N1 >= 0 && N2 >= 0 && D >= 0, "tpw_lp_topk_forward: negative size");
+    TPW_CHECK_ARG(k >= 1 && k <= 16 && k <= N2, "tpw_lp_topk_forward: k must be in [1, min(16, N2)] (got %d)", k);
+    TPW_CHECK_ARG(D >= 1 && D <= 16, "tpw_lp_topk_forward: D must be in [1, 16] (got %lld)", (long long)D);
+    TPW_CHECK_ARG(p == 1.0 || p == 2.0 || p == 3.0 || (isinf(p) && p > 0), "tpw_lp_topk_forward: p must be 1, 2, 3 or +inf (got %g)", p);
+    TPW_CHECK_ARG(!isnan(out_exponent), "tpw_lp_topk_forward: NaN exponent");
+    TPW_CHECK_ARG(N2 < (1ll << 32), "tpw_lp_topk_forward: N2 must fit 32 bits");
+    if (B == 0 || N1 == 0) return TPW_OK;
+    TPW_CHECK_ARG(x1 && x2 && vals && inds, "tpw_lp_topk_forward: NULL pointer");
+    return lp_small_d_topk(x1, x2, vals, reinterpret_cast<long long *>(inds), B, N1, N2, D, k, p, out_exponent,
+                           static_cast<cudaStream_t>(stream));
+}

@@ -1232,6 +1232,14 @@ def k_neighbors_mask(x1: Tensor, x2: Optional[Tensor] = None, k: int = 1, metric
             inds = pairwise_argmin_min(x1_, x2_, metric, kwargs.get("p"))[0].unsqueeze(1)
             out = torch.zeros((x1_.size(0), x2_.size(0)), dtype=torch.bool, device=x1_.device)
             return out.scatter_(1, inds, True)
+        few = (metric in _ROWMIN_METRICS and set(kwargs) <= {"p"} and kwargs.get("p") in (None, 1.0, 2.0, 3.0, math.inf)
+               and x1_.is_cuda and x1_.dtype == torch.float32 and x2_.dtype == torch.float32 and x1_.dim() == 2
+               and 0 < x1_.size(-1) <= lib.tpw_lp_topk_max_features() and x1_.size(0) >= 4096
+               and 0 < k + 1 <= min(lib.tpw_lp_topk_max_k(), x2_.size(0)) and not os.environ.get("TPW_DISABLE_SMALL_D"))
+        if few:
+            inds = pairwise_argkmin(x1_, x2_, k + 1, metric, **kwargs)[0]
+            out = torch.zeros((x1_.size(0), x2_.size(0)), dtype=torch.bool, device=x1_.device)
+            return out.scatter_(1, inds, True)
         if metric in ("euclidean", "l2", "sqeuclidean", "cosine") and not kwargs and x1_.is_cuda and x1_.dtype == torch.float32 \
                 and x2_.dtype == torch.float32 and 0 < k + 1 <= min(lib.tpw_dot_topk_max_k(), x2_.size(0)) \
                 and _tensor_engine_selected(x1_.unsqueeze(0), x2_.unsqueeze(0)):
@@ -1344,7 +1352,9 @@ def pairwise_argkmin(x1: Tensor, x2: Optional[Tensor] = None, k: int = 1, metric
     Large float32 problems with a Euclidean, squared Euclidean or cosine metric and
     ``k <= tpw_dot_topk_max_k()`` run the tensor-core kernel whose epilogue keeps the k smallest keys
     of each accumulator row in registers (``tpw_dot_topk_forward_ws``; no distance matrix is written).
-    Everything else takes this package's distance kernel followed by a partial selection."""
+    float32 L_p metrics (p in 1, 2, 3, inf) on at most ``tpw_lp_topk_max_features()`` features and at least 4096
+    query rows run the streaming kernel that keeps one query row and its k best keys per thread
+    (``tpw_lp_topk_forward``).  Everything else takes this package's distance kernel followed by a partial selection."""
     from .cpdist import cdist
     if k < 1:
         raise RuntimeError(f"k must be positive. Got k={k}")
@@ -1367,6 +1377,23 @@ def pairwise_argkmin(x1: Tensor, x2: Optional[Tensor] = None, k: int = 1, metric
                 with torch.cuda.device(x1c.device):
                     check(lib.tpw_dot_topk_forward_ws(epilogue, k, _ptr(x1c), _ptr(x2c), _ptr(vals), _ptr(inds), _ptr(scratch), nbytes,
                                                       B, N1, N2, D, _stream(x1c)), "tpw_dot_topk_forward_ws")
+                return (inds.squeeze(0), vals.squeeze(0)) if unbatched else (inds, vals)
+        # few features (point clouds): one x1 row per thread with its k best keys in registers, no distance matrix
+        if (metric in _ROWMIN_METRICS and set(kwargs) <= {"p"} and x1_.dtype == torch.float32 and x2_.dtype == torch.float32
+                and 0 < x1_.size(-1) <= lib.tpw_lp_topk_max_features() and k <= lib.tpw_lp_topk_max_k()
+                and not os.environ.get("TPW_DISABLE_SMALL_D")):
+            pp, ex = _ROWMIN_METRICS[metric]
+            if pp is None:
+                pp = 2.0 if kwargs.get("p") is None else float(kwargs["p"])
+                ex = 1.0 if math.isinf(pp) else (1.0 / pp if pp > 0 else None)
+            x1c, x2c, unbatched = _batched(x1_, x2_, "pairwise_argkmin")
+            B, N1, N2, D = _sizes(x1c, x2c)
+            if pp in (1.0, 2.0, 3.0, math.inf) and ex is not None and B * N1 >= 4096:
+                vals = torch.empty((B, N1, k), dtype=torch.float32, device=x1c.device)
+                inds = torch.empty((B, N1, k), dtype=torch.int64, device=x1c.device)
+                with torch.cuda.device(x1c.device):
+                    check(lib.tpw_lp_topk_forward(_abi.F32, _ptr(x1c), _ptr(x2c), _ptr(vals), _ptr(inds), B, N1, N2, D, k, pp, ex,
+                                                  _stream(x1c)), "tpw_lp_topk_forward")
                 return (inds.squeeze(0), vals.squeeze(0)) if unbatched else (inds, vals)
         dist = cdist(x1_, x2_, metric, **kwargs)
         vals, inds = dist.topk(k, dim=-1, largest=False, sorted=True)

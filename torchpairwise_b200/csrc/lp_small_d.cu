@@ -350,8 +350,10 @@ lp_small_d_topk_kernel(const float *__restrict__ x1, const float *__restrict__ x
                 if (k4 + 2 < DC) sd_acc<KIND>(acc, x[k4 + 2], yv.z);
                 if (k4 + 3 < DC) sd_acc<KIND>(acc, x[k4 + 3], yv.w);
             }
-            const unsigned long long key = ((unsigned long long)__float_as_uint(acc) << 32) | (unsigned)(j0 + r);
-            if (key < list[K - 1]) {
+            // one 32-bit comparison per candidate; a value equal to the bound passes too, and the insertion below leaves
+            // the list unchanged for a key that is not smaller than its last entry
+            if (__float_as_uint(acc) <= (unsigned)(list[K - 1] >> 32)) {
+                const unsigned long long key = ((unsigned long long)__float_as_uint(acc) << 32) | (unsigned)(j0 + r);
 #pragma unroll
                 for (int t = K - 1; t > 0; --t) {
                     const unsigned long long below = list[t - 1];

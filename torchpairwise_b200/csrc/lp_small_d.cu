@@ -314,7 +314,7 @@ int launch_small_d_rowmin(const float *x1, const float *x2, unsigned long long *
 // candidate costs the distance arithmetic and one comparison against the list's last key; the unrolled insertion
 // (K compare-select pairs) runs only when some lane of the warp has a candidate below its bound, which happens about
 // K ln(N2 / K) times per row.  No scratch, no atomics: a thread sees every x2 row of its batch.
-constexpr int TK_THREADS = 128;
+constexpr int TK_THREADS = 64;
 
 template <int KIND, int DP, int DC, int K>
 __global__ void __launch_bounds__(TK_THREADS)
@@ -340,7 +340,8 @@ lp_small_d_topk_kernel(const float *__restrict__ x1, const float *__restrict__ x
             cols[e] = (r < nc && k < D) ? x2b[(long long)r * D + k] : 0.f;
         }
         __syncthreads();
-        for (int r = 0; r < nc; ++r) {
+#pragma unroll 4
+        for (int r = 0; r < nc; ++r) {   // four candidates in flight: their shared loads and sums overlap, the filters follow
             float acc = 0.f;
 #pragma unroll
             for (int k4 = 0; k4 < DP; k4 += 4) {

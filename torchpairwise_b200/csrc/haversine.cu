@@ -158,7 +158,8 @@ __global__ void __launch_bounds__(BW * 32) haversine_backward_x1_kernel(const T 
         if (!live) continue;
         const int nc = (int)min((long long)BC, N2 - j0);
         const T *g = grad + (b * N1 + i) * N2 + j0;
-        for (int c = lane; c < nc; c += 32) {
+#pragma unroll 4
+        for (int c = lane; c < nc; c += 32) {   // several gradient loads in flight per lane
             T u, v, cc, dlat, dlon, om;
             const T a = hav_a(p, cols[c], u, v, cc, om);
             const T k = hav_coef(g[c], a, om);
@@ -199,7 +200,8 @@ __global__ void __launch_bounds__(CW * CG) haversine_backward_x2_kernel(const T 
         __syncthreads();
         if (!live) continue;
         const int nr = (int)min((long long)CR, N1 - i0);
-        for (int r = grp; r < nr; r += CG) {
+#pragma unroll 4
+        for (int r = grp; r < nr; r += CG) {   // several gradient loads in flight per thread
             T u, v, cc, dlat, dlon, om;
             // the pair seen from x2: u and v change sign, a and cc do not
             const T a = hav_a(q, rows[r], u, v, cc, om);

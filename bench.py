@@ -8,15 +8,29 @@ step, seeded synthetic data.  One step = one forward + backward over the batch. 
 every rank runs its own 16 batches (the path shards by batch with no data-path collective), so the
 job is weakly scaled and ``value`` is the sum over ranks divided by the slowest rank's time.
 
-One JSON line is printed by rank 0.  ``value`` is timed with the inputs resident in HBM; ``e2e``
-times the same step through the public API from pinned host buffers (inputs copied in, both
-gradients copied out, every step).  ``roofline`` describes the dominant kernel (the backward tile
-kernel, two launches per step), timed alone with CUDA events on its stream; its bound is the fp32
-issue rate, measured live by the library's register-only microbenchmark, and ``roofline_hbm``
-restates the same launch against the measured copy bandwidth.  ``cpu_baseline`` times the
-reference's own CPU operators (built from its sources into oracle/_ref) on a bounded row block.
+One JSON line is printed by rank 0.  ``value`` is timed with the inputs resident in HBM through
+``torch.ops.torchpairwise.minkowski_distances`` -- the reference's own operator name, served for CUDA
+tensors by this package's C++ host layer (``drop_in`` puts the Python mirror of the same call beside
+it).  ``e2e`` times the same step from pinned host buffers (inputs copied in, both gradients copied
+out, every step) and carries the measured host-to-device ceiling of the box at this N.  ``roofline``
+describes the dominant kernel (the backward tile kernel, two launches per step), timed alone with
+CUDA events on its stream: ``frac`` counts the algorithmic lane-operations (difference, shape term
+and two accumulations per pair and feature for both gradients, i.e. two per launch),
+``frac_executed`` the three a launch really issues; the bound is the fp32 issue rate measured live
+by the library's register-only microbenchmark, and ``roofline_hbm`` restates the same launch against
+the measured copy bandwidth.  ``cpu_baseline`` times the reference's own CPU operators (built from
+its sources into oracle/_ref) on a bounded row block, best of three.
 
-``--impl reference`` times that CPU implementation alone, on the same workload definition, each
+On one GPU the line also carries ``configs`` -- every benchmark configuration (C1 euclidean /
+manhattan / cosine, C2 minkowski p=3 / chebyshev, C3 hamming / jaccard, C4 sqeuclidean / cosine, C5
+directed Hausdorff) with its time, throughput and fraction of the bounding rate on the algorithmic
+and on the executed work -- and ``parity``: the same outputs and gradients compared with the
+reference's CPU operators on a row block (max error over tolerance; 0 mismatches for the boolean
+metrics).  ``sharded_dense`` is the row-sharded C4 workload with the broadcast of Y inside the step
+(at every N, with a same-run one-GPU time), ``sharded_backward`` the row-sharded forward + backward
+whose x2 gradient is all-reduced (N > 1).
+
+``--impl reference`` times the CPU implementation alone, on the same workload definition, each
 step a bounded row block.
 """
 from __future__ import annotations
@@ -38,8 +52,13 @@ sys.path.insert(0, str(ROOT))
 METRIC = "Gpairs/s, minkowski_distances(p=3) forward+backward, fp32"
 B, N1, N2, D, P = 16, 4096, 4096, 256, 3.0
 PAIRS_PER_STEP = B * N1 * N2
-# lane-operations of the dominant kernel per pair and feature: subtract, d*|d|, fused multiply-add
+# lane-operations of the dominant kernel per pair and feature as executed: subtract, d*|d|, fused multiply-add
 BWD_OPS_PER_ELEMENT = 3
+# the algorithmic count: difference, shape term and two accumulations for BOTH gradients (4 per pair and feature),
+# of which one launch produces one gradient
+BWD_ALG_OPS_PER_ELEMENT_PER_LAUNCH = 2
+# lane-operations per point pair of the Hausdorff row-minimum loop as executed
+HAUSDORFF_EXECUTED_OPS = 9
 # algorithmic HBM bytes of one backward launch: upstream gradient + forward output read once,
 # both operands read once, one gradient written
 BWD_BYTES_PER_LAUNCH = 4 * (2 * B * N1 * N2 + 3 * B * N1 * D)
@@ -118,43 +137,92 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def cpu_reference_step(rows: int, threads: int):
-    """One forward + backward of the reference's CPU operators on a row block of the workload:
-    X[1, rows, 256] against Y[1, 4096, 256].  Returns (seconds, pairs, kind)."""
+RTOL, ATOL = 1e-4, 1e-5  # the fp32 parity contract; boolean metrics and Hausdorff indices are compared bit for bit
+
+
+def load_reference_ops():
+    """``torch.ops.torchpairwise`` served by the reference's own CPU operators (oracle/_ref), or None."""
     import torch
-    torch.set_num_threads(threads)
-    g = torch.Generator().manual_seed(0)
-    X = torch.randn(1, rows, D, generator=g).requires_grad_(True)
-    Y = torch.randn(1, N2, D, generator=g).requires_grad_(True)
-    G = torch.randn(1, rows, N2, generator=g)
-    if REF_SO.exists():
-        if not getattr(cpu_reference_step, "_loaded", False):
-            torch.ops.load_library(str(REF_SO))
-            cpu_reference_step._loaded = True
-        fn = lambda: torch.ops.torchpairwise.minkowski_distances(X, Y, P).backward(G)  # noqa: E731
-        kind = "reference"
-    else:
-        from oracle import pairwise_oracle as O
-        xn, yn, gn = X.detach().numpy(), Y.detach().numpy(), G.numpy()
-        fn = lambda: O.cdist_backward(gn, xn, yn, P, out=O.cdist(xn, yn, P))  # noqa: E731
-        kind = "port"
-    t0 = time.perf_counter()
-    fn()
-    return time.perf_counter() - t0, rows * N2, kind
+    if not REF_SO.exists():
+        return None
+    if not getattr(load_reference_ops, "_loaded", False):
+        torch.ops.load_library(str(REF_SO))
+        load_reference_ops._loaded = True
+    return torch.ops.torchpairwise
+
+
+def err_over_tol(got, ref, scale: float = 1.0) -> float:
+    """max |got - ref| / (atol * scale + rtol * |ref|) over all elements; <= 1 meets the contract."""
+    got, ref = got.detach().double().cpu(), ref.detach().double().cpu()
+    if got.numel() == 0:
+        return 0.0
+    return float(((got - ref).abs() / (ATOL * scale + RTOL * ref.abs())).max())
+
+
+def grad_scale(ref) -> float:
+    """Gradients are sums of thousands of terms: their absolute tolerance is taken relative to the largest entry."""
+    return 10.0 * max(1.0, float(ref.abs().max()))
+
+
+def mismatches(got, ref) -> int:
+    return int((got.cpu() != ref.cpu()).sum())
+
+
+def best_of(fn, n: int = 3, warm: int = 1) -> float:
+    for _ in range(warm):
+        fn()
+    best = math.inf
+    for _ in range(n):
+        t0 = time.perf_counter()
+        fn()
+        best = min(best, time.perf_counter() - t0)
+    return best
+
+
+def c2_inputs(seed: int):
+    """X, Y [16,4096,256] and the upstream gradient [16,4096,4096] drawn in that order from one CPU generator."""
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(B, N1, D, generator=g), torch.randn(B, N2, D, generator=g), torch.randn(B, N1, N2, generator=g)
+
+
+def c2_block(X, Y, G, rows: int):
+    """Batch 0, rows 0:rows of X against all of Y: the row block the CPU reference is timed and compared on."""
+    return X[0:1, :rows].clone(), Y[0:1].clone(), G[0:1, :rows].clone()
+
+
+def cpu_fwd_bwd(op, x1, x2, g, **kw):
+    """One forward + backward of a reference operator on CPU tensors; returns (out, grad_x1, grad_x2)."""
+    a, b = x1.clone().requires_grad_(True), x2.clone().requires_grad_(True)
+    out = op(a, b, **kw)
+    out.backward(g)
+    return out.detach(), a.grad, b.grad
 
 
 def run_reference(args, rank: int):
+    """The reference's CPU implementation alone: every step is one forward + backward on the row block."""
     if rank != 0:
         return
-    threads = os.cpu_count() or 1
-    rows = 512  # the same row block as the cpu_baseline leg of the GPU arm
-    cpu_reference_step(rows, threads)  # library load + first-touch, not counted as a warm-up step
+    import torch
+    threads = len(os.sched_getaffinity(0))
+    torch.set_num_threads(threads)
+    rows = 512
+    Xb, Yb, Gb = c2_block(*c2_inputs_block(0, rows), rows)
+    T = load_reference_ops()
+    if T is not None:
+        kind = "reference"
+        step = lambda: cpu_fwd_bwd(T.minkowski_distances, Xb, Yb, Gb, p=P)  # noqa: E731
+    else:
+        from oracle import pairwise_oracle as O
+        kind = "port"
+        xn, yn, gn = Xb.numpy(), Yb.numpy(), Gb.numpy()
+        step = lambda: O.cdist_backward(gn, xn, yn, P, out=O.cdist(xn, yn, P))  # noqa: E731
+    step()  # library load and first touch, not counted as a warm-up step
     for _ in range(args.warmup):
-        cpu_reference_step(rows, threads)
+        step()
     t0 = time.perf_counter()
-    kind = "port"
     for _ in range(args.steps):
-        _, pairs, kind = cpu_reference_step(rows, threads)
+        step()
     dt = time.perf_counter() - t0
     value = args.steps * rows * N2 / dt / 1e9
     sample = f"per step: batch 1 of 16, rows 0:{rows} of 4096 against all 4096 columns, D=256, forward+backward"
@@ -171,14 +239,359 @@ def run_reference(args, rank: int):
     print(json.dumps(line), flush=True)
 
 
+def c2_inputs_block(seed: int, rows: int):
+    """The same draws as ``c2_inputs`` restricted to what the row block needs (batch 0), without the 1 GB gradient:
+    X and Y are drawn in full, of the gradient only batch 0."""
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    X, Y = torch.randn(B, N1, D, generator=g), torch.randn(B, N2, D, generator=g)
+    G0 = torch.randn(1, N1, N2, generator=g)  # the first N1*N2 draws of the [16,4096,4096] gradient are its batch 0
+    return X, Y, G0
+
+
+def load_tensor_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"bf16_burst": float(d["bf16_tflops"]) * 1e12, "bf16_sustained": float(d["bf16_tflops_sustained"]) * 1e12,
+                "tensor_source": "measured"}
+    return {"bf16_burst": 1.59e15, "bf16_sustained": 1.4e15, "tensor_source": "fallback"}
+
+
+def run_sharded_dense(T, tpw, dev, rank, world, barrier, max_over_ranks, gpu_ms):
+    """C4 sqeuclidean with the rows of X cut over the ranks and Y broadcast from rank 0 by NCCL in every step
+    (strong scaling).  Reports the step with and without the broadcast, a same-run one-GPU time of the whole
+    problem, and the worst error of a sampled row block of every rank's slab against a float64 evaluation."""
+    import torch
+    from torchpairwise_b200 import sharding
+    rows_total, cols, feat = 131072, 16384, 512
+    _, ranges = sharding.plan_shards((rows_total, feat), world)
+    lo, hi = ranges[rank]
+    Xs = torch.randn(hi - lo, feat, generator=torch.Generator().manual_seed(2000 + rank)).to(dev)
+    Ys = torch.randn(cols, feat, generator=torch.Generator().manual_seed(7)).to(dev) if rank == 0 else torch.empty(cols, feat, device=dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(fn, reps=5, warm=2):
+        for _ in range(warm):
+            fn()
+        barrier()
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1) / reps)
+
+    slab = [None]
+
+    def sharded_step():
+        with torch.no_grad():
+            slab[0] = sharding.sharded_pairwise(T.sqeuclidean_distances, Xs, Ys, src=0)
+
+    def kernel_only():
+        with torch.no_grad():
+            slab[0] = T.sqeuclidean_distances(Xs, Ys)
+
+    ms_step = timed(sharded_step)
+    ms_kernel = timed(kernel_only)  # Y is local on every rank after the broadcasts above
+    sharded_step()
+    blk = slice(max(0, (hi - lo) - 256), hi - lo)
+    xd, yd = Xs[blk].double(), Ys.double()
+    ref = (xd * xd).sum(1)[:, None] + (yd * yd).sum(1)[None, :] - 2.0 * (xd @ yd.t())
+    err = float(((slab[0][blk].double() - ref).abs() / (ATOL + RTOL * ref.abs())).max())
+    del xd, yd, ref
+    worst = max_over_ranks(err)
+    slab[0] = None
+    t1 = ms_step
+    if world > 1:
+        t1 = None
+        if rank == 0:
+            Xfull = torch.randn(rows_total, feat, device=dev)
+            with torch.no_grad():
+                t1 = gpu_ms(lambda: T.sqeuclidean_distances(Xfull, Ys), reps=3, warm=1)
+            del Xfull
+    del Xs, Ys
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    return {"workload": "C4 sqeuclidean X[131072,512] row-sharded (each rank generates its block in place), Y[16384,512] "
+                        "broadcast from rank 0 every step (NCCL)" if world > 1 else
+                        "C4 sqeuclidean X[131072,512] x Y[16384,512] on one GPU (nothing to broadcast)",
+            "ms_per_step": ms_step, "kernel_only_ms": ms_kernel, "Gpairs_s": rows_total * cols / (ms_step * 1e-3) / 1e9,
+            "one_gpu_ms_same_run": t1, "efficiency_vs_n1": t1 / (world * ms_step),
+            "kernel_only_efficiency_vs_n1": t1 / (world * ms_kernel),
+            "slab_rows_rank0": hi - lo, "scaling": "strong",
+            "parity_worst_err_over_tol": worst,
+            "parity_what": "last 256 rows of every rank's slab against a float64 evaluation on the same GPU, all 16384 columns, "
+                           "max over ranks of max |err| / (1e-5 + 1e-4 |ref|)"}
+
+
+def run_sharded_backward(T, dev, rank, world, barrier, max_over_ranks):
+    """Forward + backward of minkowski p=3 with the rows of x1 cut over the ranks inside each batch: x2 is broadcast
+    from rank 0 and the x2-gradient partials are summed by one all-reduce, the one collective that follows a
+    kernel on this path.  Every rank also runs the whole problem alone and compares its slab and gradients."""
+    import torch
+    from torchpairwise_b200 import sharding
+    nb = 2 if world > 2 else 1  # fewer batches than ranks, so the plan cuts rows
+    g = torch.Generator().manual_seed(99)
+    X1 = torch.randn(nb, 4096, 256, generator=g).to(dev)
+    X2 = torch.randn(nb, 4096, 256, generator=g).to(dev)
+    Gf = torch.randn(nb, 4096, 4096, generator=g).to(dev)
+    kind, ranges = sharding.plan_shards(tuple(X1.shape), world)
+    lo, hi = ranges[rank]
+    x1l = sharding.local_block(X1, kind, ranges, rank).contiguous().requires_grad_(True)
+    x2l = (X2.clone() if rank == 0 else torch.zeros_like(X2)).requires_grad_(True)
+    gl = sharding.local_block(Gf, kind, ranges, rank).contiguous()
+    out = [None]
+
+    def step():
+        x1l.grad = None
+        x2l.grad = None
+        out[0] = sharding.sharded_pairwise(T.minkowski_distances, x1l, x2l, src=0, p=P)
+        out[0].backward(gl)
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(2):
+        step()
+    barrier()
+    e0.record()
+    for _ in range(5):
+        step()
+    e1.record()
+    barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1) / 5)
+    a, b = X1.clone().requires_grad_(True), X2.clone().requires_grad_(True)
+    full = T.minkowski_distances(a, b, P)
+    full.backward(Gf)
+    sl = (slice(None), slice(lo, hi))
+    errs = {"out": err_over_tol(out[0], full.detach()[sl]),
+            "grad_x1": err_over_tol(x1l.grad, a.grad[sl], grad_scale(a.grad)),
+            "grad_x2_after_all_reduce": err_over_tol(x2l.grad, b.grad, grad_scale(b.grad))}
+    errs = {k: max_over_ranks(v) for k, v in errs.items()}
+    if rank != 0:
+        return None
+    return {"workload": f"minkowski p=3 forward+backward, X1,X2[{nb},4096,256], plan '{kind}' over {world} ranks: x2 broadcast from "
+                        "rank 0, x2-gradient partials all-reduced (NCCL), every step",
+            "ms_per_step": ms, "Gpairs_s": nb * 4096 * 4096 / (ms * 1e-3) / 1e9,
+            "parity_err_over_tol_vs_one_gpu": errs}
+
+
+def run_configs(T, R, dev, gpu_ms, peaks, X, Y, G, hosts, args):
+    """Every benchmark configuration on one GPU: time, throughput, fraction of the bounding rate on the algorithmic
+    and on the executed work, and parity with the reference's CPU operators on the row block (or, for the small
+    configurations, the whole problem).  Returns (configs, parity)."""
+    import torch
+    cfg, par = {}, {}
+    fp32, popc, hbm = peaks["fp32"], peaks["popc"], peaks["hbm"]
+    g0 = torch.Generator().manual_seed(0)
+
+    def cpu_time(fn, n=1, warm=0):
+        return best_of(fn, n=n, warm=warm) if R is not None else None
+
+    def rate(pairs, secs):
+        return None if not secs else pairs / secs / 1e9
+
+    # ---- C1: X[1024,128] x Y[2048,128], whole problem on both sides --------------------------------------------
+    X1, Y1 = torch.randn(1024, 128, generator=g0), torch.randn(2048, 128, generator=g0)
+    G1 = torch.randn(1024, 2048, generator=g0)
+    n = 1024 * 2048
+    for name, lane_ops in (("euclidean_distances", 2), ("manhattan_distances", 2), ("cosine_distances", 1)):
+        op = getattr(T, name)
+        a, b, gd = X1.to(dev).requires_grad_(True), Y1.to(dev).requires_grad_(True), G1.to(dev)
+
+        def fb():
+            a.grad = None
+            b.grad = None
+            op(a, b).backward(gd)
+        fwd = gpu_ms(lambda: op(a.detach(), b.detach()), reps=20, warm=3)
+        both = gpu_ms(fb, reps=20, warm=3)
+        e = {"fwd_ms": fwd, "fwd_bwd_ms": both, "Gpairs_s_fwd": n / (fwd * 1e-3) / 1e9, "Gpairs_s_fwd_bwd": n / (both * 1e-3) / 1e9,
+             "bound": "launch latency and host overhead (2.1 M pairs, L2 resident)",
+             "frac_algorithmic": n * 128 * lane_ops / (fwd * 1e-3) / fp32, "frac_of": "fp32 issue, forward"}
+        if R is not None:
+            ref = cpu_fwd_bwd(getattr(R, name), X1, Y1, G1)
+            e["cpu_Gpairs_s_fwd_bwd"] = rate(n, cpu_time(lambda: cpu_fwd_bwd(getattr(R, name), X1, Y1, G1), n=3, warm=1))
+            fb()
+            par["C1/" + name] = {"fwd": err_over_tol(op(a.detach(), b.detach()), ref[0]),
+                                 "grad_x1": err_over_tol(a.grad, ref[1], grad_scale(ref[1])),
+                                 "grad_x2": err_over_tol(b.grad, ref[2], grad_scale(ref[2]))}
+        cfg["C1/" + name] = e
+    # ---- C2: the resident benchmark tensors; CPU on batch 0, rows 0:512 ---------------------------------------------
+    rows = 512
+    Xb, Yb, Gb = c2_block(*hosts, rows)
+    pairs = B * N1 * N2
+    for name, kw, fwd_alg, bwd_alg, fwd_exe, bwd_exe in (("minkowski_distances", {"p": P}, 3, 4, 3, 6),
+                                                         ("chebyshev_distances", {}, 2, 2, 2, 8)):
+        op = getattr(T, name)
+
+        def fb():
+            X.grad = None
+            Y.grad = None
+            res = op(X, Y, **kw)
+            res.backward(G)
+            return res
+        fwd = gpu_ms(lambda: op(X.detach(), Y.detach(), **kw), reps=5)
+        both = gpu_ms(fb, reps=5)
+        key = "C2/" + name + ("_p3" if kw else "")
+        e = {"fwd_ms": fwd, "fwd_bwd_ms": both, "Gpairs_s_fwd": pairs / (fwd * 1e-3) / 1e9,
+             "Gpairs_s_fwd_bwd": pairs / (both * 1e-3) / 1e9, "bound": "fp32_issue",
+             "frac_algorithmic": pairs * D * (fwd_alg + bwd_alg) / (both * 1e-3) / fp32,
+             "frac_executed": pairs * D * (fwd_exe + bwd_exe) / (both * 1e-3) / fp32,
+             "fwd_frac_algorithmic": pairs * D * fwd_alg / (fwd * 1e-3) / fp32,
+             "bwd_frac_algorithmic": pairs * D * bwd_alg / ((both - fwd) * 1e-3) / fp32,
+             "lane_ops_per_pair_feature": {"algorithmic": [fwd_alg, bwd_alg], "executed": [fwd_exe, bwd_exe]}}
+        if R is not None:
+            ref = [None]
+
+            def cpu():
+                ref[0] = cpu_fwd_bwd(getattr(R, name), Xb, Yb, Gb, **kw)
+            e["cpu_Gpairs_s_fwd_bwd"] = rate(rows * N2, cpu_time(cpu))
+            e["cpu_sample"] = f"batch 1 of 16, rows 0:{rows}"
+            res = fb()  # the full-size step: its output rows and grad_x1 rows of the block are compared as they are
+            xb, yb = X[0:1, :rows].detach().clone().requires_grad_(True), Y[0:1].detach().clone().requires_grad_(True)
+            op(xb, yb, **kw).backward(G[0:1, :rows])  # grad_x2 needs every row of x1: compared on the block alone
+            par[key] = {"fwd": err_over_tol(res[0:1, :rows], ref[0][0]),
+                        "grad_x1": err_over_tol(X.grad[0:1, :rows], ref[0][1], grad_scale(ref[0][1])),
+                        "grad_x2": err_over_tol(yb.grad, ref[0][2], grad_scale(ref[0][2]))}
+            del res, xb, yb
+        cfg[key] = e
+    X.grad = None
+    Y.grad = None
+    torch.cuda.empty_cache()
+    # ---- C3: bool X[65536,1024] x Y[16384,1024], Bernoulli(0.1); CPU on rows 0:1024 ------------------------------
+    rows = 1024
+    Xb3, Yb3 = torch.rand(65536, 1024, generator=g0) < 0.1, torch.rand(16384, 1024, generator=g0) < 0.1
+    xd, yd = Xb3.to(dev), Yb3.to(dev)
+    pairs = 65536 * 16384
+    for name in ("hamming_distances", "jaccard_distances"):
+        op = getattr(T, name)
+        t = gpu_ms(lambda: op(xd, yd), reps=3)
+        e = {"fwd_ms": t, "Gpairs_s_fwd": pairs / (t * 1e-3) / 1e9, "bound": "popc_issue, then the 4.29 GB output write",
+             "frac_algorithmic": pairs * 32 / (t * 1e-3) / popc, "frac_executed": pairs * 16 / (t * 1e-3) / popc,
+             "frac_hbm_output_write": 4 * pairs / (t * 1e-3) / hbm,
+             "work_per_pair": "algorithmic 32 POPC (one per 32-bit word pair); executed 16 (carry-save tree), bit-pack pre-pass included"}
+        if R is not None:
+            ref = [None]
+
+            def cpu():
+                ref[0] = getattr(R, name)(Xb3[:rows], Yb3)
+            e["cpu_Gpairs_s_fwd"] = rate(rows * 16384, cpu_time(cpu))
+            e["cpu_sample"] = f"rows 0:{rows} against all 16384"
+            par["C3/" + name] = {"mismatching_elements": mismatches(op(xd, yd)[:rows], ref[0]), "rule": "bit-exact"}
+        cfg["C3/" + name] = e
+    del xd, yd, Xb3, Yb3
+    torch.cuda.empty_cache()
+    # ---- C4: X[131072,512] x Y[16384,512]; CPU on rows 0:1024 -------------------------------------------------
+    X4, Y4 = torch.randn(131072, 512, generator=g0), torch.randn(16384, 512, generator=g0)
+    xd, yd = X4.to(dev), Y4.to(dev)
+    pairs = 131072 * 16384
+    for name, rows in (("sqeuclidean_distances", 1024), ("cosine_distances", 1024)):
+        op = getattr(T, name)
+        t = gpu_ms(lambda: op(xd, yd), reps=3)
+        e = {"fwd_ms": t, "Gpairs_s_fwd": pairs / (t * 1e-3) / 1e9, "bound": "tensor (bf16, fp32 accumulate), then the 8.59 GB output write",
+             "frac_algorithmic": pairs * 512 * 2 / (t * 1e-3) / peaks["bf16_burst"],
+             "frac_executed": pairs * 512 * 6 / (t * 1e-3) / peaks["bf16_burst"],
+             "frac_executed_of_sustained": pairs * 512 * 6 / (t * 1e-3) / peaks["bf16_sustained"],
+             "frac_hbm_output_write": 4 * pairs / (t * 1e-3) / hbm,
+             "work_per_pair": "algorithmic 2 D flop; executed 6 D (three bf16 products keep the fp32 tolerance); split pre-pass included",
+             "peak_source": peaks["tensor_source"]}
+        if R is not None:
+            ref = [None]
+
+            def cpu():
+                ref[0] = getattr(R, name)(X4[:rows], Y4)
+            e["cpu_Gpairs_s_fwd"] = rate(rows * 16384, cpu_time(cpu))
+            e["cpu_sample"] = f"rows 0:{rows} against all 16384"
+            par["C4/" + name] = {"fwd": err_over_tol(op(xd, yd)[:rows], ref[0])}
+        cfg["C4/" + name] = e
+    del xd, yd, X4, Y4
+    torch.cuda.empty_cache()
+    # ---- C5: 64 clouds of 8192 points, whole problem on both sides ------------------------------------------------
+    P5 = torch.rand(64, 8192, 3, generator=g0) * 2 - 1
+    Q5 = P5 + 0.05 * torch.randn(64, 8192, 3, generator=g0)
+    x1h, x2h = P5[:, None].contiguous(), Q5[:, None].contiguous()
+    a, b = x1h.to(dev).requires_grad_(True), x2h.to(dev).requires_grad_(True)
+    ppairs = 64 * 8192 * 8192
+    op = T.directed_hausdorff_distances
+
+    def hd():
+        a.grad = None
+        b.grad = None
+        res = op(a, b)
+        res[0].backward(torch.ones_like(res[0]))
+        return res
+    fwd = gpu_ms(lambda: op(a.detach(), b.detach()), reps=5)
+    both = gpu_ms(hd, reps=5)
+    e = {"fwd_ms": fwd, "fwd_bwd_ms": both, "Gpointpairs_s_fwd": ppairs / (fwd * 1e-3) / 1e9,
+         "Gpointpairs_s_fwd_bwd": ppairs / (both * 1e-3) / 1e9, "bound": "fp32_issue (point pairs; nothing but 64 results written)",
+         "frac_algorithmic": ppairs * 7 / (both * 1e-3) / fp32, "frac_executed": ppairs * HAUSDORFF_EXECUTED_OPS / (both * 1e-3) / fp32,
+         "fwd_frac_algorithmic": ppairs * 7 / (fwd * 1e-3) / fp32,
+         "work_per_point_pair": f"algorithmic 7 lane-ops (3 subtract, multiply, 2 fused multiply-add, minimum); executed {HAUSDORFF_EXECUTED_OPS}"}
+    if R is not None:
+        ref = [None]
+
+        def cpu():
+            u, v = x1h.clone().requires_grad_(True), x2h.clone().requires_grad_(True)
+            r = R.directed_hausdorff_distances(u, v)
+            r[0].backward(torch.ones_like(r[0]))
+            ref[0] = (r[0].detach(), r[1], r[2], u.grad, v.grad)
+        e["cpu_Gpointpairs_s_fwd_bwd"] = rate(ppairs, cpu_time(cpu, n=3, warm=1))
+        e["cpu_note"] = "the reference's loop leaves a row as soon as it falls below the running maximum, so it visits a fraction of the point pairs"
+        res = hd()
+        par["C5/directed_hausdorff_distances"] = {
+            "fwd": err_over_tol(res[0], ref[0][0]), "values_bit_equal": bool(torch.equal(res[0].detach().cpu(), ref[0][0])),
+            "index_mismatches": mismatches(res[1], ref[0][1]) + mismatches(res[2], ref[0][2]),
+            "grad_x1": err_over_tol(a.grad, ref[0][3]), "grad_x2": err_over_tol(b.grad, ref[0][4])}
+    cfg["C5/directed_hausdorff_distances"] = e
+    return cfg, par
+
+
+def bind_host_threads_near_gpu(local_rank: int):
+    """Keep this process (and the pinned buffers it allocates afterwards) on the CPUs that sit next to its GPU,
+    when the operating system says which those are and the process is allowed to run there.  Returns a note."""
+    try:
+        bus = subprocess.run(["nvidia-smi", "-i", str(local_rank), "--query-gpu=pci.bus_id", "--format=csv,noheader"],
+                             capture_output=True, text=True, timeout=20).stdout.strip().lower()
+        node = Path(f"/sys/bus/pci/devices/{bus}/local_cpulist")
+        if not node.exists():  # nvidia-smi prints an 8-digit PCI domain, sysfs a 4-digit one
+            node = Path(f"/sys/bus/pci/devices/{bus[-12:]}/local_cpulist")
+        cpus = set()
+        for part in node.read_text().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0)
+        near = cpus & allowed
+        if near and near != allowed:
+            bind_host_threads_near_gpu.allowed = allowed
+            os.sched_setaffinity(0, near)
+            return f"bound to {len(near)} of {len(allowed)} allowed CPUs local to GPU {local_rank}"
+        return f"all {len(allowed)} allowed CPUs are " + ("local" if near else "remote") + f" to GPU {local_rank}"
+    except Exception as e:  # no sysfs entry, no permission: timing still valid, just not placed
+        return f"not bound ({type(e).__name__})"
+
+
+def host_threads_everywhere() -> int:
+    """Undo ``bind_host_threads_near_gpu`` (the CPU reference legs get every CPU the process may use); returns how many."""
+    allowed = getattr(bind_host_threads_near_gpu, "allowed", None)
+    if allowed:
+        os.sched_setaffinity(0, allowed)
+    return len(os.sched_getaffinity(0))
+
+
 def run_ours(args, rank: int, world: int, local_rank: int):
     import torch
     import torch.distributed as dist
-    import torchpairwise_b200 as tpw
-    from torchpairwise_b200 import _abi
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    affinity = bind_host_threads_near_gpu(local_rank)
+    # The reference's CPU library first (when it was built): it defines the schemas and keeps serving CPU tensors;
+    # the host layer of this package then registers the CUDA and AutogradCUDA kernels under the same names.
+    R = load_reference_ops()
+    import torchpairwise_b200 as tpw
+    from torchpairwise_b200 import _abi
+    tpw.load_torch_ops()
+    T = torch.ops.torchpairwise
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
@@ -187,27 +600,49 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             dist.barrier()
         torch.cuda.synchronize()
 
-    # per-rank seeded synthetic inputs, generated on the host so that the e2e leg can reuse them
-    g = torch.Generator().manual_seed(1000 + rank)
-    Xh = torch.randn(B, N1, D, generator=g).pin_memory()
-    Yh = torch.randn(B, N2, D, generator=g).pin_memory()
-    Gh = torch.randn(B, N1, N2, generator=g).pin_memory()
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def gpu_ms(fn, reps: int = 3, warm: int = 1) -> float:
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    # per-rank seeded synthetic inputs (rank 0: seed 0), generated on the host so that the e2e leg can reuse them
+    Xc, Yc, Gc = c2_inputs(rank)
+    Xh, Yh, Gh = Xc.pin_memory(), Yc.pin_memory(), Gc.pin_memory()
+    del Xc, Yc, Gc
     X = Xh.to(dev).requires_grad_(True)
     Y = Yh.to(dev).requires_grad_(True)
     G = Gh.to(dev)
 
-    def step():
+    def step():  # the drop-in: the reference's operator name, dispatched to the sm_100a kernels for CUDA tensors
         X.grad = None
         Y.grad = None
-        out = tpw.minkowski_distances(X, Y, P)
-        out.backward(G)
+        T.minkowski_distances(X, Y, P).backward(G)
+
+    def mirror_step():  # the same kernels through the Python mirror of the operator surface (ctypes on the C ABI)
+        X.grad = None
+        Y.grad = None
+        tpw.minkowski_distances(X, Y, P).backward(G)
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()  # started before the warm-up so that nvidia-smi is already streaming in the timed region
     for _ in range(args.warmup):
         step()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     sampler.mark_begin()
     e0.record()
@@ -216,12 +651,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     e1.record()
     barrier()
     sampler.mark_end()
-    ms = e0.elapsed_time(e1)
+    ms = max_over_ranks(e0.elapsed_time(e1))
     clocks = sampler.stop() if rank == 0 else None
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
     value = world * args.steps * PAIRS_PER_STEP / (ms * 1e-3) / 1e9
     if args.profile:
         if rank == 0:
@@ -229,16 +660,16 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         if world > 1:
             dist.destroy_process_group()
         return
+    mirror_ms = gpu_ms(mirror_step, reps=max(3, args.steps // 2))
 
     # ---- end to end: host buffers in, gradients out, every step ---------------------------------
     g1h = torch.empty(B, N1, D).pin_memory()
     g2h = torch.empty(B, N2, D).pin_memory()
-
     from torchpairwise_b200.host_pipeline import forward_backward_from_host
 
     def e2e_step():
         # public API for host-resident operands: copies of chunk c+1 overlap the kernels of chunk c
-        forward_backward_from_host(tpw.minkowski_distances, Xh, Yh, Gh, g1h, g2h, dev, chunk=2, p=P)
+        forward_backward_from_host(T.minkowski_distances, Xh, Yh, Gh, g1h, g2h, dev, chunk=2, p=P)
 
     e2e_step()
     barrier()
@@ -247,48 +678,40 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         e2e_step()
     e1.record()
     barrier()
-    ms_e2e = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms_e2e], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_e2e = float(t.item())
+    ms_e2e = max_over_ranks(e0.elapsed_time(e1))
     e2e = world * args.steps * PAIRS_PER_STEP / (ms_e2e * 1e-3) / 1e9
+    h2d_bytes = 4 * (B * N1 * D + B * N2 * D + B * N1 * N2)
+    # what the host side can deliver at this N: every rank copies the same pinned buffers to its GPU, nothing else runs
+    stage = [torch.empty_like(t, device=dev) for t in (Xh, Yh, Gh)]
 
-    # ---- row-sharded dense metric with x2 broadcast over NCCL (strong scaling; reported beside the headline) ----
-    sharded = None
-    if world > 1:
-        from torchpairwise_b200 import sharding
-        rows_total, cols, feat = 131072, 16384, 512
-        kind, ranges = sharding.plan_shards((rows_total, feat), world)
-        lo, hi = ranges[rank]
-        gs = torch.Generator().manual_seed(2000 + rank)
-        Xs = torch.randn(hi - lo, feat, generator=gs).to(dev)
-        Ys = torch.randn(cols, feat, generator=torch.Generator().manual_seed(7)).to(dev) if rank == 0 else torch.empty(cols, feat, device=dev)
+    def copy_in():
+        for d_, h_ in zip(stage, (Xh, Yh, Gh)):
+            d_.copy_(h_, non_blocking=True)
 
-        def sharded_step():
-            with torch.no_grad():
-                return sharding.sharded_pairwise(tpw.sqeuclidean_distances, Xs, Ys, src=0)
+    copy_in()
+    barrier()
+    e0.record()
+    for _ in range(3):
+        copy_in()
+    e1.record()
+    barrier()
+    ms_copy = max_over_ranks(e0.elapsed_time(e1) / 3)
+    del stage
+    h2d_ceiling = {"GBps_all_ranks": world * h2d_bytes / (ms_copy * 1e-3) / 1e9, "ms_per_step_floor": ms_copy,
+                   "what": f"{world} rank(s) copying the step's {h2d_bytes / 1e9:.2f} GB of pinned inputs concurrently, no compute"}
 
-        for _ in range(2):
-            slab = sharded_step()
-        barrier()
-        e0.record()
-        for _ in range(5):
-            slab = sharded_step()
-        e1.record()
-        barrier()
-        t = torch.tensor([e0.elapsed_time(e1) / 5], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        sharded = {"workload": "C4 sqeuclidean X[131072,512] row-sharded, Y[16384,512] broadcast from rank 0 every step (NCCL)",
-                   "ms_per_step": float(t.item()), "Gpairs_s": rows_total * cols / (float(t.item()) * 1e-3) / 1e9,
-                   "slab_rows_rank0": hi - lo, "scaling": "strong"}
-        del slab, Xs, Ys
+    # ---- the split the path shards by when it is not batched: X rows over ranks, Y broadcast (C4) -------------
+    sharded = run_sharded_dense(T, tpw, dev, rank, world, barrier, max_over_ranks, gpu_ms)
+    sharded_bwd = run_sharded_backward(T, dev, rank, world, barrier, max_over_ranks) if world > 1 else None
 
     line = None
     if rank == 0:
+        fp32_peak = tpw.measure_issue_peak(0)
+        hbm_peak, hbm_src = load_peaks()
         # ---- dominant kernel alone: backward w.r.t. x1 (grad + forward output streamed) -----------
         with torch.no_grad():
-            out = tpw.minkowski_distances(X, Y, P)
+            out = T.minkowski_distances(X, Y, P)
+            drop_in_same_bits = bool(torch.equal(out, tpw.minkowski_distances(X, Y, P)))
         g1 = torch.empty_like(X)
         stream = torch.cuda.current_stream().cuda_stream
 
@@ -297,71 +720,67 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                                                 X.data_ptr(), Y.data_ptr(), None, g1.data_ptr(), None,
                                                 B, N1, N2, D, P, stream))
 
-        for _ in range(3):
-            bwd_launch()
-        torch.cuda.synchronize()
-        reps = max(5, args.steps)
-        e0.record()
-        for _ in range(reps):
-            bwd_launch()
-        e1.record()
-        torch.cuda.synchronize()
-        k_ms = e0.elapsed_time(e1) / reps
-        ops = PAIRS_PER_STEP * D * BWD_OPS_PER_ELEMENT
-        fp32_peak = tpw.measure_issue_peak(0)
-        achieved = ops / (k_ms * 1e-3)
-        hbm_peak, hbm_src = load_peaks()
-        roofline = {"bound": "fp32_issue", "achieved": achieved / 1e12, "peak": fp32_peak / 1e12,
-                    "unit": "Tlane-op/s", "frac": achieved / fp32_peak, "traffic": BWD_DRAM_TRAFFIC_BYTES_PER_BATCH * B,
+        k_ms = gpu_ms(bwd_launch, reps=max(5, args.steps), warm=3)
+        executed = PAIRS_PER_STEP * D * BWD_OPS_PER_ELEMENT
+        algorithmic = PAIRS_PER_STEP * D * BWD_ALG_OPS_PER_ELEMENT_PER_LAUNCH
+        fwd_ms = gpu_ms(lambda: T.minkowski_distances(X.detach(), Y.detach(), P), reps=5)
+        step_ms = ms / args.steps
+        roofline = {"bound": "fp32_issue", "achieved": algorithmic / (k_ms * 1e-3) / 1e12, "peak": fp32_peak / 1e12,
+                    "unit": "Tlane-op/s", "frac": algorithmic / (k_ms * 1e-3) / fp32_peak,
+                    "frac_executed": executed / (k_ms * 1e-3) / fp32_peak,
+                    "traffic": BWD_DRAM_TRAFFIC_BYTES_PER_BATCH * B,
                     "kernel": "lp_backward_kernel (grad_x1 pass, p=3)", "ms_per_launch": k_ms,
+                    "algorithmic_work": "2 lane-ops per pair and feature per launch (one of the two gradients; the backward of "
+                                        "both counts 4 per pair and feature), 3 executed (subtract, d*|d|, fused multiply-add)",
+                    "step_frac_algorithmic": PAIRS_PER_STEP * D * 7 / (step_ms * 1e-3) / fp32_peak,
+                    "backward_frac_algorithmic": PAIRS_PER_STEP * D * 4 / ((step_ms - fwd_ms) * 1e-3) / fp32_peak,
+                    "forward_frac_algorithmic": PAIRS_PER_STEP * D * 3 / (fwd_ms * 1e-3) / fp32_peak,
                     "peak_source": "live register-only FFMA microbenchmark (tpw_measure_issue_peak)"}
         roofline_hbm = {"bound": "hbm", "achieved": BWD_BYTES_PER_LAUNCH / (k_ms * 1e-3) / 1e9, "peak": hbm_peak,
                         "unit": "GB/s", "frac": BWD_BYTES_PER_LAUNCH / (k_ms * 1e-3) / 1e9 / hbm_peak,
                         "traffic": BWD_DRAM_TRAFFIC_BYTES_PER_BATCH * B, "peak_source": hbm_src}
-        # ---- other metrics of the path, a few launches each (not part of the timed K steps) --------
-        extra = {}
-
-        def timeit(fn, n=3):
-            fn()
-            torch.cuda.synchronize()
-            e0.record()
-            for _ in range(n):
-                fn()
-            e1.record()
-            torch.cuda.synchronize()
-            return e0.elapsed_time(e1) / n
-
-        def cheb():
-            X.grad = None
-            Y.grad = None
-            tpw.chebyshev_distances(X, Y).backward(G)
-
-        extra["chebyshev_fwd_bwd_C2_Gpairs_s"] = PAIRS_PER_STEP / (timeit(cheb) * 1e-3) / 1e9
-        with torch.no_grad():
-            extra["minkowski_p3_fwd_C2_Gpairs_s"] = PAIRS_PER_STEP / (timeit(lambda: tpw.minkowski_distances(X, Y, P)) * 1e-3) / 1e9
         del out, g1
-        # ---- CPU baseline: the reference's own operators on a bounded row block -------------------
-        threads = os.cpu_count() or 1
+        # ---- CPU baseline and parity on the row block: the reference's own operators ---------------
+        threads = host_threads_everywhere()
+        torch.set_num_threads(threads)
         rows = 512
-        cpu_reference_step(64, threads)
-        secs, pairs, kind = cpu_reference_step(rows, threads)
-        cpu_baseline = {"value": pairs / secs / 1e9, "unit": "Gpairs/s", "cores": threads, "kind": kind,
+        Xb, Yb, Gb = c2_block(Xh, Yh, Gh, rows)
+        configs, parity = {}, {}
+        if R is not None:
+            secs = best_of(lambda: cpu_fwd_bwd(R.minkowski_distances, Xb, Yb, Gb, p=P), n=3, warm=1)
+            kind = "reference"
+        else:
+            from oracle import pairwise_oracle as O
+            xn, yn, gn = Xb.numpy(), Yb.numpy(), Gb.numpy()
+            secs = best_of(lambda: O.cdist_backward(gn, xn, yn, P, out=O.cdist(xn, yn, P)), n=1, warm=0)
+            kind = "port"
+        cpu_baseline = {"value": rows * N2 / secs / 1e9, "unit": "Gpairs/s", "cores": threads, "kind": kind,
                         "sample": f"batch 1 of 16, rows 0:{rows} of 4096 against all 4096 columns, D=256, forward+backward, "
-                                  f"{secs:.1f} s"}
+                                  f"best of 3 after one warm-up, {secs:.2f} s"}
+        if world == 1 and not args.no_configs:
+            peaks = {"fp32": fp32_peak, "popc": tpw.measure_issue_peak(2), "hbm": hbm_peak * 1e9}
+            peaks.update(load_tensor_peaks())
+            configs, parity = run_configs(T, R, dev, gpu_ms, peaks, X, Y, G, (Xh, Yh, Gh), args)
         line = {
             "metric": METRIC, "value": value, "unit": "Gpairs/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "C2 minkowski p=3 fwd+bwd: X,Y[16,4096,256], G[16,4096,4096] fp32 N(0,1) per GPU",
                        "pairs_per_step_per_gpu": PAIRS_PER_STEP, "parallelism": f"batch-sharded x{world}, no collective",
-                       "l2": "inputs larger than L2 (2.1 GB of gradient + output streamed per step)"},
+                       "l2": "inputs larger than L2 (2.1 GB of gradient + output streamed per step)",
+                       "api": "torch.ops.torchpairwise.minkowski_distances (the reference's operator name; CUDA tensors are "
+                              "served by libtpw_b200_torch.so)",
+                       "reference_cpu_library_loaded": R is not None},
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "Gpairs/s", "ms_per_step": ms_e2e / args.steps,
-                    "h2d_bytes_per_step": 4 * (B * N1 * D + B * N2 * D + B * N1 * N2),
-                    "d2h_bytes_per_step": 4 * (B * N1 * D + B * N2 * D)},
+                    "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4 * (B * N1 * D + B * N2 * D),
+                    "host_h2d_gbs_ceiling": h2d_ceiling, "host_placement": affinity},
             "gpu_launches": 3 * args.steps,
-            "roofline": roofline, "roofline_hbm": roofline_hbm, "cpu_baseline": cpu_baseline, "extra": extra,
-            "sharded_dense": sharded,
+            "roofline": roofline, "roofline_hbm": roofline_hbm, "cpu_baseline": cpu_baseline,
+            "drop_in": {"ms_per_step": ms / args.steps, "python_mirror_ms_per_step": mirror_ms,
+                        "same_bits_as_mirror": drop_in_same_bits},
+            "configs": configs, "parity": parity,
+            "sharded_dense": sharded, "sharded_backward": sharded_bwd,
             "device_status": tpw.device_status(),
         }
     if world > 1:
@@ -658,6 +1077,8 @@ def main():
                          "and print one JSON object with throughputs and roofline fractions; not the driver's bench line")
     ap.add_argument("--suite-only", default="", help="comma-separated subset of suite entries (for profiler captures)")
     ap.add_argument("--rows", type=int, default=0, help="suite: cap N1 of the unbatched configurations (profiler captures)")
+    ap.add_argument("--no-configs", action="store_true",
+                    help="skip the per-configuration entries and their CPU parity legs (headline, e2e and roofline only)")
     ap.add_argument("--profile", action="store_true",
                     help="run only the warm-up and timed steps (for ncu captures); prints a reduced line that is not a bench value")
     args = ap.parse_args()

@@ -104,11 +104,14 @@ def test_stand_alone_schemas_equal_the_reference_strings():
         assert r.returncode == 0, r.stdout + r.stderr
         outs.append(json.loads(r.stdout.split("SCHEMAS", 1)[1]))
     theirs, ours = outs
-    assert len(ours) >= 59, len(ours)
+    assert len(ours) >= 74, len(ours)
     for key, text in ours.items():
         assert theirs.get(key) == text, (key, text, theirs.get(key))
     for name in ("prf_div.", "prf_div.Scalar", "prf_ldiv.rScalar", "prf_div_.", "prf_ldiv_.Scalar", "_prf_div_backward.rScalar",
-                 "_prf_ldiv__backward.Scalar", "__directed_hausdorff_backward.", "_directed_hausdorff.", "cdist."):
+                 "_prf_ldiv__backward.Scalar", "__directed_hausdorff_backward.", "_directed_hausdorff.", "cdist.", "pdist.",
+                 "k_neighbors_mask.", "radius_neighbors_mask.", "linear_kernel.", "polynomial_kernel.", "sigmoid_kernel.", "rbf_kernel.",
+                 "laplacian_kernel.", "mahalanobis_distances.", "_sqmahalanobis.", "__sqmahalanobis_backward.", "_cuda_version.",
+                 "_cuda_arch_flags."):
         assert "torchpairwise::" + name in ours, name
 
 

@@ -111,8 +111,10 @@ def test_hausdorff_and_cdist_dispatcher(T):
         T.cdist(x1.cuda(), x2.cuda(), "euclidean", p=2.0)
     with pytest.raises(RuntimeError, match="unkown distance metric"):
         T.cdist(x1.cuda(), x2.cuda(), "nope")
-    with pytest.raises(NotImplementedError):
-        T.cdist(x1.cuda(), x2.cuda(), "mahalanobis", VI=torch.eye(8).cuda())
+    A = torch.randn(8, 8, generator=g)
+    VI = A @ A.t() + 0.5 * torch.eye(8)
+    torch.testing.assert_close(T.cdist(x1.cuda(), x2.cuda(), "mahalanobis", VI=VI.cuda()).cpu(), T.cdist(x1, x2, "mahalanobis", VI=VI),
+                               rtol=1e-4, atol=1e-5)
 
 
 def test_prf_div_family_and_hausdorff_backward_op(T):
@@ -254,6 +256,136 @@ def test_composed_and_pair_sum_ops(T):
         T.chi2_kernel(x1.cuda(), x2.cuda(), 1.0)
 
 
+def _both_devices(fn, tensors, up):
+    """fn on CPU leaves (the reference) and on CUDA leaves (these kernels): outputs and gradients of every leaf."""
+    res = []
+    for dev in ("cpu", "cuda"):
+        leaves = [t.detach().clone().to(dev).requires_grad_(True) for t in tensors]
+        out = fn(*leaves)
+        out.backward(up.to(dev))
+        res.append((out.detach().cpu(), [l.grad.cpu() for l in leaves]))
+    return res
+
+
+def test_kernel_functions_and_mahalanobis_ops(T):
+    """linear / polynomial / sigmoid / rbf / laplacian kernels, mahalanobis_distances, _sqmahalanobis and its stand-alone
+    backward op through the C++ layer: the reference on CPU tensors, these kernels on CUDA tensors."""
+    g = torch.Generator().manual_seed(19)
+    x1, x2 = torch.randn(35, 12, generator=g), torch.randn(29, 12, generator=g)
+    up = torch.randn(35, 29, generator=g)
+    for fn in (lambda a, b: T.linear_kernel(a, b), lambda a, b: T.polynomial_kernel(a, b, 2, 0.05, 0.5),
+               lambda a, b: T.polynomial_kernel(a, b, 3, None, 1.0), lambda a, b: T.sigmoid_kernel(a, b, 0.02, 0.1),
+               lambda a, b: T.sigmoid_kernel(a, b, None, 1.0), lambda a, b: T.rbf_kernel(a, b, 0.3), lambda a, b: T.rbf_kernel(a, b, None)):
+        (o_ref, g_ref), (o_got, g_got) = _both_devices(fn, (x1, x2), up)
+        torch.testing.assert_close(o_got, o_ref, rtol=1e-4, atol=1e-5)
+        for a, b in zip(g_got, g_ref):
+            torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-5 * 10 * max(1.0, float(b.abs().max())))
+    # the reference's own backward of laplacian_kernel fails (in-place exp on the output of cdist): forward only
+    torch.testing.assert_close(T.laplacian_kernel(x1.cuda(), x2.cuda(), 0.2).cpu(), T.laplacian_kernel(x1, x2, 0.2), rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(T.laplacian_kernel(x1.cuda(), None, None).cpu(), T.laplacian_kernel(x1, None, None), rtol=1e-4, atol=1e-5)
+    T.laplacian_kernel(x1.cuda().requires_grad_(True), x2.cuda(), 0.2).sum().backward()  # differentiable here
+
+    A = torch.randn(12, 12, generator=g)
+    spd = A @ A.t() / 12 + 0.3 * torch.eye(12)
+    skew = torch.randn(12, 12, generator=g)
+    general = spd + 0.2 * (skew - skew.t())          # not symmetric; its symmetric part is positive definite
+    indefinite = spd - 0.8 * torch.eye(12)           # symmetric part has negative eigenvalues: no Cholesky factor
+    assert float(torch.linalg.eigvalsh(indefinite).min()) < 0
+    for VI in (spd, general, indefinite):
+        (o_ref, g_ref), (o_got, g_got) = _both_devices(lambda a, b, v: T._sqmahalanobis(a, b, v), (x1, x2, VI), up)
+        torch.testing.assert_close(o_got, o_ref, rtol=1e-4, atol=1e-5 * max(1.0, float(o_ref.abs().max())))
+        for a, b in zip(g_got, g_ref):
+            torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-5 * 10 * max(1.0, float(b.abs().max())))
+        ref = T.__sqmahalanobis_backward(up, x1, x2, VI)
+        got = T.__sqmahalanobis_backward(up.cuda(), x1.cuda(), x2.cuda(), VI.cuda())
+        for a, b in zip(got, ref):
+            torch.testing.assert_close(a.cpu(), b, rtol=1e-4, atol=1e-5 * 10 * max(1.0, float(b.abs().max())))
+    (o_ref, g_ref), (o_got, g_got) = _both_devices(lambda a, b, v: T.mahalanobis_distances(a, b, v), (x1, x2, spd), up)
+    torch.testing.assert_close(o_got, o_ref, rtol=1e-4, atol=1e-5)
+    for a, b in zip(g_got, g_ref):
+        torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-5 * 10 * max(1.0, float(b.abs().max())))
+    # x2 = None: the default VI (inverse covariance of x1) and an exactly zero self-distance diagonal, like the reference's
+    big = torch.randn(60, 12, generator=g)
+    got, ref = T.mahalanobis_distances(big.cuda(), None, None).cpu(), T.mahalanobis_distances(big, None, None)
+    torch.testing.assert_close(got, ref, rtol=1e-4, atol=1e-5)
+    assert bool((got.diagonal() == 0).all())
+    # near-duplicate rows keep their relative accuracy (an expansion into bilinear terms would return rounding noise)
+    near = big + 1e-4 * torch.randn(60, 12, generator=g)
+    got = T.mahalanobis_distances(big.cuda(), near.cuda(), spd.cuda()).cpu().diagonal()
+    ref = T.mahalanobis_distances(big.double(), near.double(), spd.double()).diagonal()
+    torch.testing.assert_close(got.double(), ref, rtol=2e-3, atol=0)
+    got = T.snr_distances(big.cuda(), near.cuda()).cpu().diagonal()
+    ref = T.snr_distances(big.double(), near.double()).diagonal()
+    torch.testing.assert_close(got.double(), ref, rtol=2e-3, atol=0)
+    with pytest.raises(RuntimeError, match="VI is required"):
+        T.mahalanobis_distances(x1.cuda(), x2.cuda(), None)
+
+
+def test_neighbour_masks_and_pdist_ops(T):
+    """k_neighbors_mask / radius_neighbors_mask through the C++ layer equal the reference's masks (its composition is
+    cdist + argsort / compare), on small problems and on the shapes that reach the fused kernels; pdist, which the
+    reference only declares, returns the upper triangle of the reference's cdist."""
+    g = torch.Generator().manual_seed(20)
+
+    def masks_agree(x1, x2, k, metric, **kw):
+        ref = T.k_neighbors_mask(x1, x2, k, metric, **kw)
+        got = T.k_neighbors_mask(x1.cuda(), None if x2 is None else x2.cuda(), k, metric, **kw).cpu()
+        assert got.dtype == torch.bool and got.shape == ref.shape
+        assert bool((got.sum(1) == k + 1).all())
+        # a row may differ only where two candidates are closer than float32 resolves
+        d = T.cdist(x1.double(), (x1 if x2 is None else x2).double(), metric, **kw)
+        bad = (got != ref).any(1).nonzero().flatten()
+        for i in bad.tolist():
+            kth = d[i].sort().values[k]
+            assert float((d[i][got[i] != ref[i]] - kth).abs().max()) <= 1e-4 * max(1.0, float(kth)), (metric, i)
+        assert bad.numel() <= max(1, x1.size(0) // 500)
+
+    x1, x2 = torch.randn(40, 7, generator=g), torch.randn(33, 7, generator=g)
+    for metric, kw in (("euclidean", {}), ("manhattan", {}), ("chebyshev", {}), ("minkowski", {"p": 3.0}), ("cosine", {}),
+                       ("sqeuclidean", {}), ("correlation", {})):
+        for k in (0, 1, 5):
+            masks_agree(x1, x2, k, metric, **kw)
+    masks_agree(x1, None, 3, "euclidean")
+    pts1, pts2 = torch.randn(4500, 3, generator=g), torch.randn(700, 3, generator=g)
+    masks_agree(pts1, pts2, 0, "euclidean")          # streaming row minimum
+    masks_agree(pts1, pts2, 7, "euclidean")          # few features: k best keys per thread
+    masks_agree(pts1, pts2, 3, "manhattan")
+    w1, w2 = torch.randn(2048, 64, generator=g), torch.randn(2048, 64, generator=g)
+    masks_agree(w1, w2, 0, "sqeuclidean")            # tensor-core row-minimum epilogue
+    masks_agree(w1, w2, 4, "euclidean")              # tensor-core top-k epilogue
+    with pytest.raises(RuntimeError, match="k must be non-negative"):
+        T.k_neighbors_mask(x1.cuda(), x2.cuda(), -1, "euclidean")
+    with pytest.raises(TypeError, match="incompatible arguments p"):
+        T.k_neighbors_mask(x1.cuda(), x2.cuda(), 1, "euclidean", p=3.0)
+
+    for a, b in ((x1, x2), (pts1, pts2), (w1[:300], w2[:200])):
+        for metric, kw, eps in (("euclidean", {}, None), ("manhattan", {}, None), ("minkowski", {"p": 3.0}, None), ("cosine", {}, None)):
+            d = T.cdist(a.double(), b.double(), metric, **kw)
+            eps = float(d.median())
+            ref = T.radius_neighbors_mask(a, b, eps, metric, **kw)
+            got = T.radius_neighbors_mask(a.cuda(), b.cuda(), eps, metric, **kw).cpu()
+            clear = (d - eps).abs() > 1e-4 * max(1.0, eps)
+            assert got.dtype == torch.bool and torch.equal(got[clear], ref[clear]), metric
+            assert torch.equal(got[clear], (d <= eps)[clear])
+    with pytest.raises(RuntimeError, match="epsilon must be non-negative"):
+        T.radius_neighbors_mask(x1.cuda(), x2.cuda(), -0.5, "euclidean")
+    with pytest.raises(TypeError, match="incompatible arguments p"):
+        T.radius_neighbors_mask(x1.cuda(), x2.cuda(), 1.0, "manhattan", p=1.0)
+
+    with pytest.raises(NotImplementedError):
+        T.pdist(x1, "euclidean")                     # the reference itself
+    iu = torch.triu_indices(40, 40, offset=1)
+    for metric, kw in (("euclidean", {}), ("manhattan", {}), ("minkowski", {"p": 3.0}), ("chebyshev", {}), ("cosine", {}), ("canberra", {})):
+        ref = T.cdist(x1, x1, metric, **kw)[iu[0], iu[1]]
+        torch.testing.assert_close(T.pdist(x1.cuda(), metric, **kw).cpu(), ref, rtol=1e-4, atol=1e-5)
+    xb = torch.randn(2, 300, 20, generator=g)
+    iu = torch.triu_indices(300, 300, offset=1)
+    torch.testing.assert_close(T.pdist(xb.cuda(), "manhattan").cpu(), T.cdist(xb, xb, "manhattan")[:, iu[0], iu[1]], rtol=1e-4, atol=1e-5)
+    leaf = x1.cuda().requires_grad_(True)
+    T.pdist(leaf, "euclidean").sum().backward()      # differentiable calls gather the triangle of cdist
+    assert leaf.grad is not None and bool(torch.isfinite(leaf.grad).all())
+
+
 def test_cpp_layer_agrees_with_python_layer(T):
     import torchpairwise_b200 as tpw
     g = torch.Generator().manual_seed(14)
@@ -302,6 +434,9 @@ def test_stand_alone_registration():
         "assert x.grad.shape == x.shape and torch.isfinite(x.grad).all()\n"
         "assert torch.equal(T.jaccard_distances(x > 0, y > 0), t.jaccard_distances(x > 0, y > 0))\n"
         "assert torch.equal(T.cdist(x, y, 'manhattan'), t.manhattan_distances(x, y))\n"
+        "assert T._cuda_version() == t.cuda_version() >= 12000 and T._cuda_arch_flags() == 'sm_100a'\n"
+        "assert torch.equal(T.k_neighbors_mask(x, y, 2, 'euclidean'), t.k_neighbors_mask(x, y, 2, 'euclidean'))\n"
+        "assert torch.equal(T.pdist(x.detach(), 'manhattan'), t.pdist(x.detach(), 'manhattan'))\n"
         "print('standalone ok')\n"
     )
     r = subprocess.run([sys.executable, "-c", code], cwd=str(ROOT), capture_output=True, text=True, timeout=300)

@@ -17,6 +17,8 @@
 #include <ATen/core/dispatch/Dispatcher.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
+#include <c10/util/Logging.h>
+#include <nvtx3/nvToolsExt.h>
 #include <torch/autograd.h>
 #include <torch/library.h>
 
@@ -39,6 +41,19 @@ using OptTensor = c10::optional<Tensor>;
         int status_ = (expr);                                                 \
         TORCH_CHECK(status_ == TPW_OK, #expr " failed: ", tpw_last_error());  \
     } while (0)
+
+// Every public operator logs the reference's API-usage string once (OPS/pairwise_metrics.cpp:27,36,45,...;
+// OPS/cpdist.cpp:160; OPS/neighbors.cpp:21,48) and brackets its body with an NVTX range, so that a timeline shows the
+// operator name around its kernels.  The ranges cost nothing when no profiler is attached.
+struct NvtxRange {
+    explicit NvtxRange(const char *name) { nvtxRangePushA(name); }
+    ~NvtxRange() { nvtxRangePop(); }
+    NvtxRange(const NvtxRange &) = delete;
+    NvtxRange &operator=(const NvtxRange &) = delete;
+};
+#define TPW_OP(file, name)                                            \
+    C10_LOG_API_USAGE_ONCE("torchpairwise.csrc.ops." file "." name);  \
+    NvtxRange nvtx_range_("torchpairwise::" name)
 
 int code_of(const Tensor &t) { return t.scalar_type() == at::kDouble ? TPW_F64 : TPW_F32; }
 tpw_stream_t stream_of(const Tensor &t) { return c10::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
@@ -829,41 +844,85 @@ Tensor prf_div_backward_rscalar_op(const Tensor &grad, const at::Scalar &self, c
 }
 
 // ---- public ops ------------------------------------------------------------------------------------------------
+#define PM "pairwise_metrics"
 Tensor cdist_p(const char *name, const Tensor &x1, const OptTensor &x2, double p) {
     auto ab = check_pairwise_inputs(name, x1, x2);
     return CdistFn::apply(ab.first, ab.second, p);
 }
-Tensor euclidean_distances(const Tensor &x1, const OptTensor &x2) { return cdist_p("euclidean_distances", x1, x2, 2.0); }
-Tensor manhattan_distances(const Tensor &x1, const OptTensor &x2) { return cdist_p("manhattan_distances", x1, x2, 1.0); }
+Tensor euclidean_distances(const Tensor &x1, const OptTensor &x2) {
+    TPW_OP(PM, "euclidean_distances");
+    return cdist_p("euclidean_distances", x1, x2, 2.0);
+}
+Tensor manhattan_distances(const Tensor &x1, const OptTensor &x2) {
+    TPW_OP(PM, "manhattan_distances");
+    return cdist_p("manhattan_distances", x1, x2, 1.0);
+}
 Tensor chebyshev_distances(const Tensor &x1, const OptTensor &x2) {
+    TPW_OP(PM, "chebyshev_distances");
     return cdist_p("chebyshev_distances", x1, x2, std::numeric_limits<double>::infinity());
 }
-Tensor minkowski_distances(const Tensor &x1, const OptTensor &x2, double p) { return cdist_p("minkowski_distances", x1, x2, p); }
-Tensor ppminkowski(const Tensor &x1, const Tensor &x2, double p) { return PPMinkowskiFn::apply(x1, x2, p); }
-Tensor wminkowski(const Tensor &x1, const Tensor &x2, const Tensor &w, double p) { return WMinkowskiFn::apply(x1, x2, w, p); }
+Tensor minkowski_distances(const Tensor &x1, const OptTensor &x2, double p) {
+    TPW_OP(PM, "minkowski_distances");
+    return cdist_p("minkowski_distances", x1, x2, p);
+}
+// the aliases of OPS/pairwise_metrics.cpp:265-270,411-438 log their own names there as well
+Tensor cityblock_distances(const Tensor &x1, const OptTensor &x2) {
+    TPW_OP(PM, "cityblock_distances");
+    return cdist_p("manhattan_distances", x1, x2, 1.0);
+}
+Tensor l1_distances(const Tensor &x1, const OptTensor &x2) {
+    TPW_OP(PM, "l1_distances");
+    return cdist_p("manhattan_distances", x1, x2, 1.0);
+}
+Tensor l2_distances(const Tensor &x1, const OptTensor &x2) {
+    TPW_OP(PM, "l2_distances");
+    return cdist_p("euclidean_distances", x1, x2, 2.0);
+}
+Tensor lp_distances(const Tensor &x1, const OptTensor &x2, double p) {
+    TPW_OP(PM, "lp_distances");
+    return cdist_p("minkowski_distances", x1, x2, p);
+}
+Tensor linf_distances(const Tensor &x1, const OptTensor &x2) {
+    TPW_OP(PM, "linf_distances");
+    return cdist_p("chebyshev_distances", x1, x2, std::numeric_limits<double>::infinity());
+}
+Tensor ppminkowski(const Tensor &x1, const Tensor &x2, double p) {
+    TPW_OP("ppminkowski", "_ppminkowski");
+    return PPMinkowskiFn::apply(x1, x2, p);
+}
+Tensor wminkowski(const Tensor &x1, const Tensor &x2, const Tensor &w, double p) {
+    TPW_OP("wminkowski", "_wminkowski");
+    return WMinkowskiFn::apply(x1, x2, w, p);
+}
 Tensor wminkowski_distances(const Tensor &x1, const OptTensor &x2, double p, const OptTensor &w) {
+    TPW_OP(PM, "wminkowski_distances");
     auto ab = check_pairwise_inputs("wminkowski_distances", x1, x2);
     return w.has_value() ? WMinkowskiFn::apply(ab.first, ab.second, w.value(), p) : CdistFn::apply(ab.first, ab.second, p);
 }
 Tensor sqeuclidean_distances(const Tensor &x1, const OptTensor &x2) {
+    TPW_OP(PM, "sqeuclidean_distances");
     auto ab = check_pairwise_inputs("sqeuclidean_distances", x1, x2);
     return PPMinkowskiFn::apply(ab.first, ab.second, 2.0);
 }
 Tensor cosine_similarity(const Tensor &x1, const OptTensor &x2) {
+    TPW_OP(PM, "cosine_similarity");
     auto ab = check_pairwise_inputs("cosine_similarity", x1, x2);
     return CosineFn::apply(ab.first, ab.second, static_cast<int64_t>(TPW_DOT_COSINE_SIM));
 }
 Tensor cosine_distances(const Tensor &x1, const OptTensor &x2) {
+    TPW_OP(PM, "cosine_distances");
     auto ab = check_pairwise_inputs("cosine_similarity", x1, x2);
     return CosineFn::apply(ab.first, ab.second, static_cast<int64_t>(TPW_DOT_COSINE_DIST));
 }
 Tensor correlation_distances(const Tensor &x1, const OptTensor &x2) {
+    TPW_OP(PM, "correlation_distances");
     auto ab = check_pairwise_inputs("correlation_distances", x1, x2);
     Tensor c1 = RowCenterFn::apply(ab.first);
     Tensor c2 = x2.has_value() ? RowCenterFn::apply(ab.second) : c1;
     return CosineFn::apply(c1, c2, static_cast<int64_t>(TPW_DOT_ONE_MINUS_SIM));
 }
 Tensor hamming_distances(const Tensor &x1, const OptTensor &x2) {
+    TPW_OP(PM, "hamming_distances");
     auto ab = check_pairwise_inputs("hamming_distances", x1, x2);
     return pairwise_compare(ab.first, ab.second, TPW_CMP_NE, TPW_RED_MEAN);
 }
@@ -872,6 +931,11 @@ Tensor boolean_metric_op(const Tensor &x1, const OptTensor &x2) {
     static const char *names[] = {"", "", "", "", "", "", "", "jaccard_distances", "kulsinski_distances", "kulczynski1_distances",
                                   "yule_distances", "dice_distances", "rogerstanimoto_distances", "russellrao_distances",
                                   "sokalmichener_distances", "sokalsneath_distances"};
+    static const std::string usage = std::string("torchpairwise.csrc.ops.pairwise_metrics.") + names[METRIC];
+    static const std::string range = std::string("torchpairwise::") + names[METRIC];
+    static bool logged = (c10::LogAPIUsage(usage), true);
+    (void) logged;
+    NvtxRange nvtx_range_(range.c_str());
     if (METRIC == TPW_BOOL_KULSINSKI)
         TORCH_WARN_DEPRECATION("kulsinski_distances is deprecated in SciPy 1.9.0 and might be removed in the future. "
                                "Please use kulczynski1_distances.");
@@ -885,6 +949,7 @@ std::tuple<Tensor, Tensor, Tensor> directed_hausdorff_raw(const Tensor &x1, cons
 }
 std::tuple<Tensor, Tensor, Tensor> directed_hausdorff_distances(const Tensor &x1, const OptTensor &x2, bool shuffle,
                                                                 c10::optional<at::Generator> generator) {
+    TPW_OP(PM, "directed_hausdorff_distances");
     auto ab = check_pairwise_inputs("directed_hausdorff_distances", x1, x2, false, /*sets=*/true);
     return directed_hausdorff_raw(ab.first, ab.second, shuffle, generator);
 }
@@ -894,6 +959,7 @@ Tensor sqjensenshannon_raw(const Tensor &x1, const Tensor &x2, c10::optional<dou
 }
 // OPS/pairwise_metrics.cpp:326-337: rows scaled to sum one (plain tensor operations), then one kernel for the sum and the root
 Tensor jensenshannon_distances(const Tensor &x1, const OptTensor &x2, c10::optional<double> base) {
+    TPW_OP(PM, "jensenshannon_distances");
     auto ab = check_pairwise_inputs("jensenshannon_distances", x1, x2);
     Tensor n1 = ab.first / ab.first.sum(-1, true);
     Tensor n2 = x2.has_value() ? ab.second / ab.second.sum(-1, true) : n1;
@@ -902,34 +968,43 @@ Tensor jensenshannon_distances(const Tensor &x1, const OptTensor &x2, c10::optio
 Tensor canberra_raw(const Tensor &x1, const Tensor &x2) { return PairSumFn::apply(x1, x2, static_cast<int64_t>(TPW_PAIR_CANBERRA)); }
 Tensor additive_chi2_raw(const Tensor &x1, const Tensor &x2) { return PairSumFn::apply(x1, x2, static_cast<int64_t>(TPW_PAIR_ADDITIVE_CHI2)); }
 Tensor canberra_distances(const Tensor &x1, const OptTensor &x2) {
+    TPW_OP(PM, "canberra_distances");
     auto ab = check_pairwise_inputs("canberra_distances", x1, x2);
     return canberra_raw(ab.first, ab.second);
 }
 // OPS/pairwise_metrics.cpp:124-145 (the sign check synchronises there as well)
 Tensor additive_chi2_kernel(const Tensor &x1, const OptTensor &x2) {
+    TPW_OP(PM, "additive_chi2_kernel");
     auto ab = check_pairwise_inputs("additive_chi2_kernel", x1, x2);
     TORCH_CHECK(ab.first.ge(0).all().item<bool>() && (!x2.has_value() || ab.second.ge(0).all().item<bool>()),
                 "All elements of x1 and x2 must be positive");
     return additive_chi2_raw(ab.first, ab.second);
 }
-Tensor chi2_kernel(const Tensor &x1, const OptTensor &x2, double gamma) { return (additive_chi2_kernel(x1, x2) * gamma).exp(); }
+Tensor chi2_kernel(const Tensor &x1, const OptTensor &x2, double gamma) {
+    TPW_OP(PM, "chi2_kernel");
+    return (additive_chi2_kernel(x1, x2) * gamma).exp();
+}
 // OPS/pairwise_metrics.cpp:308-315 with OPS/cpu/braycurtis_kernel.cpp:22-27: sum |x - y| / sum |x + y| as two L1 passes
 Tensor braycurtis_distances(const Tensor &x1, const OptTensor &x2) {
+    TPW_OP(PM, "braycurtis_distances");
     auto ab = check_pairwise_inputs("braycurtis_distances", x1, x2);
     return CdistFn::apply(ab.first, ab.second, 1.0) / CdistFn::apply(ab.first, ab.second.neg(), 1.0);
 }
-// OPS/pairwise_metrics.cpp:401-408 with OPS/cpu/snr_kernel.cpp:22-34: var(x2 - x1) / var(x1) per pair, the first variance
-// as |x1 - x2|^2 - (sum x2 - sum x1)^2 / D on the squared-Euclidean kernel
+// OPS/pairwise_metrics.cpp:401-408 with OPS/cpu/snr_kernel.cpp:22-34: var(x2 - x1) / var(x1) per pair.  The deviations of
+// x2 - x1 from their mean are the differences of the centred rows, so the first variance is the squared Euclidean
+// distance of the centred rows, taken by the direct-difference kernel: a row against itself gives exactly 0.
 Tensor snr_distances(const Tensor &x1, const OptTensor &x2) {
+    TPW_OP(PM, "snr_distances");
     auto ab = check_pairwise_inputs("snr_distances", x1, x2);
-    const double d = static_cast<double>(ab.first.size(-1));
-    Tensor shift = ab.second.sum(-1).unsqueeze(-2) - ab.first.sum(-1, true);
-    Tensor diff_var = PPMinkowskiFn::apply(ab.first, ab.second, 2.0) - shift * shift / d;
-    Tensor x1_var = (ab.first - ab.first.mean(-1, true)).pow(2).sum(-1, true);
+    Tensor c1 = RowCenterFn::apply(ab.first);
+    Tensor c2 = x2.has_value() ? RowCenterFn::apply(ab.second) : c1;
+    Tensor diff_var = PPMinkowskiFn::apply(c1, c2, 2.0);
+    Tensor x1_var = c1.pow(2).sum(-1, true);
     return diff_var / x1_var;
 }
 // OPS/pairwise_metrics.cpp:245-263: weighted Minkowski with w = 1/V (1 where V is 0), p = 2
 Tensor seuclidean_distances(const Tensor &x1, const OptTensor &x2, const OptTensor &V) {
+    TPW_OP(PM, "seuclidean_distances");
     TORCH_CHECK(!x2.has_value() || V.has_value(), "V is required for seuclidean when x2 is passed.");
     auto ab = check_pairwise_inputs("euclidean_distances", x1, x2);
     Tensor v;
@@ -943,19 +1018,149 @@ Tensor seuclidean_distances(const Tensor &x1, const OptTensor &x2, const OptTens
 }
 Tensor haversine_raw(const Tensor &x1, const Tensor &x2) { return HaversineFn::apply(x1, x2); }
 Tensor haversine_distances(const Tensor &x1, const OptTensor &x2) {
+    TPW_OP(PM, "haversine_distances");
     auto ab = check_pairwise_inputs("haversine_distances", x1, x2);
     return HaversineFn::apply(ab.first, ab.second);
 }
 
+// ---- kernel functions (OPS/pairwise_metrics.cpp:58-110) ---------------------------------------------------------
+// x1 x2^T.  The raw dot product has no norm to hide bf16 rounding behind: large float32 problems take the tf32 x 3
+// tensor-core pipeline with chunked accumulation (as accurate as the fp32 FMA chain), everything else the exact tile.
+struct LinearKernelFn : torch::autograd::Function<LinearKernelFn> {
+    static Tensor forward(AutogradContext *ctx, const Tensor &x1, const Tensor &x2) {
+        at::AutoDispatchBelowADInplaceOrView guard;
+        const auto in_dt = x1.scalar_type();
+        TORCH_CHECK(in_dt == x2.scalar_type(), "x1 and x2 must have the same dtype");
+        Prepared q = prepare(x1, x2, compute_type(in_dt));
+        c10::cuda::CUDAGuard dg(q.a.device());
+        Tensor out = dot_forward(q, TPW_DOT_LINEAR, tensor_engine_selected(q) ? TPW_ENGINE_TCGEN05_TF32X3 : TPW_ENGINE_SIMT_FP32);
+        ctx->save_for_backward({q.a, q.b});
+        ctx->saved_data["unbatched"] = q.unbatched;
+        ctx->saved_data["dt"] = static_cast<int64_t>(in_dt);
+        return finish(out, q.unbatched, in_dt);
+    }
+    static variable_list backward(AutogradContext *ctx, variable_list go) {
+        auto s = ctx->get_saved_variables();
+        const Tensor &a = s[0], &b = s[1];
+        const bool ub = ctx->saved_data["unbatched"].toBool();
+        const auto dt = static_cast<at::ScalarType>(ctx->saved_data["dt"].toInt());
+        c10::cuda::CUDAGuard dg(a.device());
+        Tensor g = go[0].to(a.scalar_type()).contiguous();
+        if (ub) g = g.unsqueeze(0);
+        Tensor g1 = at::zeros_like(a), g2 = at::zeros_like(b);
+        if (a.numel() > 0 && b.numel() > 0) dense_backward(TPW_LP_BWD_MATMUL, g, nullptr, a, b, g1, g2);
+        return {finish(g1, ub, dt), finish(g2, ub, dt)};
+    }
+};
+Tensor linear_kernel(const Tensor &x1, const OptTensor &x2) {
+    TPW_OP(PM, "linear_kernel");
+    auto ab = check_pairwise_inputs("linear_kernel", x1, x2);
+    return LinearKernelFn::apply(ab.first, ab.second);
+}
+// the reference divides by x1.size(1) whatever the rank (OPS/pairwise_metrics.cpp:76,88,97,108)
+double default_gamma(const Tensor &x1, c10::optional<double> gamma) { return gamma.value_or(1.0 / static_cast<double>(x1.size(1))); }
+Tensor polynomial_kernel(const Tensor &x1, const OptTensor &x2, int64_t degree, c10::optional<double> gamma, double coef0) {
+    TPW_OP(PM, "polynomial_kernel");
+    auto ab = check_pairwise_inputs("polynomial_kernel", x1, x2);
+    return (LinearKernelFn::apply(ab.first, ab.second) * default_gamma(x1, gamma) + coef0).pow(degree);
+}
+Tensor sigmoid_kernel(const Tensor &x1, const OptTensor &x2, c10::optional<double> gamma, double coef0) {
+    TPW_OP(PM, "sigmoid_kernel");
+    auto ab = check_pairwise_inputs("sigmoid_kernel", x1, x2);
+    return (LinearKernelFn::apply(ab.first, ab.second) * default_gamma(x1, gamma) + coef0).tanh();
+}
+Tensor rbf_kernel(const Tensor &x1, const OptTensor &x2, c10::optional<double> gamma) {
+    TPW_OP(PM, "rbf_kernel");
+    auto ab = check_pairwise_inputs("sqeuclidean_distances", x1, x2);
+    return (PPMinkowskiFn::apply(ab.first, ab.second, 2.0) * -default_gamma(x1, gamma)).exp();
+}
+// the reference's own backward of this one fails (an in-place exp on the output of cdist); here it is differentiable
+Tensor laplacian_kernel(const Tensor &x1, const OptTensor &x2, c10::optional<double> gamma) {
+    TPW_OP(PM, "laplacian_kernel");
+    auto ab = check_pairwise_inputs("laplacian_kernel", x1, x2);
+    return (CdistFn::apply(ab.first, ab.second, 1.0) * -default_gamma(x1, gamma)).exp();
+}
+
+// ---- Mahalanobis (OPS/pairwise_metrics.cpp:272-297, OPS/sqmahalanobis.cpp:31-38, OPS/cpu/sqmahalanobis_kernel.cpp:23-31) --
+// (x1 - x2) VI (x1 - x2)^T depends on the symmetric part S of VI only.  Where S is positive definite (every inverse
+// covariance is) S = L L^T and the form is the squared Euclidean distance of x1 L and x2 L, taken by the
+// direct-difference kernel: a sum of squares, exactly 0 for a row against itself and accurate for near-duplicate
+// rows.  Otherwise d.e with d = x1 - x2, e = d S is taken as (|d/c + c e|^2 - |d/c - c e|^2) / 4, again two
+// direct-difference kernels (c balances the two magnitudes).  Differentiable in x1, x2 and VI through both.
+Tensor sqmahalanobis_impl(const Tensor &x1, const Tensor &x2, const Tensor &VI) {
+    TORCH_CHECK(x1.scalar_type() == x2.scalar_type() && x1.scalar_type() == VI.scalar_type(),
+                "x1, x2 and VI must have the same dtype (while checking arguments for _sqmahalanobis_forward)");
+    const bool unbatched = x1.dim() == 2;
+    TORCH_CHECK(unbatched || x1.dim() == 3, "x1 must be 2-D (unbatched) or 3-D (batched) tensor.");
+    TORCH_CHECK(x2.dim() == x1.dim(), "x2 must be 2-D (unbatched) or 3-D (batched) tensor.");
+    TORCH_CHECK(VI.dim() == x1.dim(), "VI must be 2-D (unbatched) or 3-D (batched) tensor.");
+    TORCH_CHECK(unbatched || (x1.size(0) == x2.size(0) && x1.size(0) == VI.size(0)), "batch_size of x1, x2, and VI do not match.");
+    TORCH_CHECK(x1.size(-1) == x2.size(-1) && x1.size(-1) == VI.size(-2) && VI.size(-1) == VI.size(-2),
+                "feature dimension of x1, x2, and VI do not match.");
+    const bool same = x2.is_same(x1);
+    Tensor S = (VI + VI.transpose(-1, -2)) * 0.5;
+    Tensor L, info;
+    std::tie(L, info) = at::linalg_cholesky_ex(S, /*upper=*/false, /*check_errors=*/false);
+    if (x1.size(-1) > 0 && info.eq(0).all().item<bool>()) {
+        Tensor u1 = x1.matmul(L);
+        Tensor u2 = same ? u1 : x2.matmul(L);
+        return PPMinkowskiFn::apply(u1, u2, 2.0);
+    }
+    Tensor e1 = x1.matmul(S);
+    Tensor e2 = same ? e1 : x2.matmul(S);
+    double c = 1.0;
+    {
+        at::NoGradGuard ng;
+        const double nx = x1.norm().item<double>(), ne = e1.norm().item<double>();
+        if (nx > 0 && ne > 0 && std::isfinite(nx / ne)) c = std::sqrt(nx / ne);
+    }
+    Tensor p1 = x1 / c + e1 * c, m1 = x1 / c - e1 * c;
+    Tensor p2 = same ? p1 : x2 / c + e2 * c, m2 = same ? m1 : x2 / c - e2 * c;
+    return (PPMinkowskiFn::apply(p1, p2, 2.0) - PPMinkowskiFn::apply(m1, m2, 2.0)) * 0.25;
+}
+Tensor sqmahalanobis_raw(const Tensor &x1, const Tensor &x2, const Tensor &VI) {
+    TPW_OP("sqmahalanobis", "_sqmahalanobis");
+    require_cuda(x1);
+    return sqmahalanobis_impl(x1, x2, VI);
+}
+std::tuple<Tensor, Tensor, Tensor> sqmahalanobis_backward_op(const Tensor &grad, const Tensor &x1, const Tensor &x2, const Tensor &VI) {
+    at::AutoGradMode enable(true);
+    Tensor a = x1.detach().requires_grad_(true), b = x2.detach().requires_grad_(true), v = VI.detach().requires_grad_(true);
+    Tensor out = sqmahalanobis_impl(a, b, v);
+    auto g = torch::autograd::grad({out}, {a, b, v}, {grad.to(out.scalar_type())}, /*retain_graph=*/false, /*create_graph=*/false,
+                                   /*allow_unused=*/true);
+    auto or_zero = [](const Tensor &t, const Tensor &like) { return t.defined() ? t : at::zeros_like(like); };
+    return std::make_tuple(or_zero(g[0], x1), or_zero(g[1], x2), or_zero(g[2], VI));
+}
+Tensor mahalanobis_distances(const Tensor &x1, const OptTensor &x2, const OptTensor &VI) {
+    TPW_OP(PM, "mahalanobis_distances");
+    TORCH_CHECK(!x2.has_value() || VI.has_value(), "VI is required for manhalanobis when x2 is passed.");
+    auto ab = check_pairwise_inputs("mahalanobis_distances", x1, x2);
+    require_cuda(ab.first);
+    Tensor vi;
+    if (VI.has_value()) vi = VI.value();
+    else {
+        at::NoGradGuard ng;
+        if (ab.first.dim() == 2) vi = at::cov(ab.first.transpose(-1, -2)).inverse().transpose(-1, -2);
+        else {
+            std::vector<Tensor> covs;
+            for (int64_t b = 0; b < ab.first.size(0); ++b) covs.push_back(at::cov(ab.first[b].transpose(-1, -2)));
+            vi = at::stack(covs).inverse().transpose(-1, -2);
+        }
+    }
+    return sqmahalanobis_impl(ab.first, ab.second, vi).sqrt();
+}
+
 // ---- cdist: string dispatcher with the reference's keyword validation (OPS/cpdist.cpp:35-79,149-231) -----------
-Tensor cdist(const Tensor &x1, const Tensor &x2, c10::string_view metric, const OptTensor &w, const OptTensor &V,
-             const OptTensor &VI, c10::optional<double> p, c10::optional<double> base, c10::optional<bool> shuffle,
-             c10::optional<at::Generator> generator) {
-    static const char *supported =
-        "braycurtis, canberra, chebyshev, cityblock, correlation, cosine, dice, directed_hausdorff, euclidean, hamming, "
-        "haversine, jaccard, jensenshannon, kulczynski1, kulsinski, l1, l2, lp, linf, mahalanobis, manhattan, minkowski, "
-        "rogerstanimoto, russellrao, seuclidean, snr, sokalmichener, sokalsneath, sqeuclidean, wminkowski, yule";
-    const std::string m(metric.data(), metric.size());
+const char *const kSupportedMetrics =
+    "braycurtis, canberra, chebyshev, cityblock, correlation, cosine, dice, directed_hausdorff, euclidean, hamming, "
+    "haversine, jaccard, jensenshannon, kulczynski1, kulsinski, l1, l2, lp, linf, mahalanobis, manhattan, minkowski, "
+    "rogerstanimoto, russellrao, seuclidean, snr, sokalmichener, sokalsneath, sqeuclidean, wminkowski, yule";
+
+// Unknown metric: RuntimeError; a keyword the metric does not take: TypeError (OPS/cpdist.cpp:35-79).
+void check_metric_and_extra_args(const std::string &m, const OptTensor &w, const OptTensor &V, const OptTensor &VI,
+                                 const c10::optional<double> &p, const c10::optional<double> &base, const c10::optional<bool> &shuffle,
+                                 const c10::optional<at::Generator> &generator) {
     auto accepts = [&](const char *arg) {
         if (m == "directed_hausdorff") return !strcmp(arg, "shuffle") || !strcmp(arg, "generator");
         if (m == "minkowski" || m == "lp") return !strcmp(arg, "p");
@@ -969,11 +1174,16 @@ Tensor cdist(const Tensor &x1, const Tensor &x2, c10::string_view metric, const 
     auto note = [&](bool given, const char *arg) {
         if (given && !accepts(arg)) bad += (bad.empty() ? "" : ", ") + std::string(arg);
     };
-    const bool known = std::string(", ").append(supported).append(", ").find(", " + m + ", ") != std::string::npos;
-    TORCH_CHECK(known, "Got unkown distance metric: ", m, ". Supported metrics are [", supported, "]");
+    const bool known = std::string(", ").append(kSupportedMetrics).append(", ").find(", " + m + ", ") != std::string::npos;
+    TORCH_CHECK(known, "Got unkown distance metric: ", m, ". Supported metrics are [", kSupportedMetrics, "]");
     note(w.has_value(), "w"); note(V.has_value(), "V"); note(VI.has_value(), "VI"); note(p.has_value(), "p");
     note(base.has_value(), "base"); note(shuffle.has_value(), "shuffle"); note(generator.has_value(), "generator");
     TORCH_CHECK_TYPE(bad.empty(), "torchpairwise::", m, "_distances was called with incompatible arguments ", bad, ".");
+}
+
+Tensor cdist_dispatch(const Tensor &x1, const OptTensor &x2, const std::string &m, const OptTensor &w, const OptTensor &V,
+                      const OptTensor &VI, c10::optional<double> p, c10::optional<double> base, c10::optional<bool> shuffle,
+                      c10::optional<at::Generator> generator) {
     if (m == "euclidean" || m == "l2") return euclidean_distances(x1, x2);
     if (m == "manhattan" || m == "cityblock" || m == "l1") return manhattan_distances(x1, x2);
     if (m == "chebyshev" || m == "linf") return chebyshev_distances(x1, x2);
@@ -989,6 +1199,7 @@ Tensor cdist(const Tensor &x1, const Tensor &x2, c10::string_view metric, const 
     if (m == "braycurtis") return braycurtis_distances(x1, x2);
     if (m == "snr") return snr_distances(x1, x2);
     if (m == "seuclidean") return seuclidean_distances(x1, x2, V);
+    if (m == "mahalanobis") return mahalanobis_distances(x1, x2, VI);
     if (m == "jaccard") return boolean_metric_op<TPW_BOOL_JACCARD>(x1, x2);
     // the reference's cdist routes "kulsinski" through the kulczynski1 functor (OPS/pairwise_metrics.h:557-561)
     if (m == "kulsinski" || m == "kulczynski1") return boolean_metric_op<TPW_BOOL_KULCZYNSKI1>(x1, x2);
@@ -999,9 +1210,167 @@ Tensor cdist(const Tensor &x1, const Tensor &x2, c10::string_view metric, const 
     if (m == "sokalmichener") return boolean_metric_op<TPW_BOOL_SOKALMICHENER>(x1, x2);
     if (m == "sokalsneath") return boolean_metric_op<TPW_BOOL_SOKALSNEATH>(x1, x2);
     if (m == "directed_hausdorff") return std::get<0>(directed_hausdorff_distances(x1, x2, shuffle.value_or(false), generator));
-    // mahalanobis: served by the Python layer (a composition over the dot-product kernels); not bound here
-    TORCH_CHECK_NOT_IMPLEMENTED(false, "metric '", m, "' is not bound in the C++ layer of this library");
+    TORCH_CHECK(false, "Got unkown distance metric: ", m, ". Supported metrics are [", kSupportedMetrics, "]");
 }
+
+Tensor cdist(const Tensor &x1, const Tensor &x2, c10::string_view metric, const OptTensor &w, const OptTensor &V,
+             const OptTensor &VI, c10::optional<double> p, c10::optional<double> base, c10::optional<bool> shuffle,
+             c10::optional<at::Generator> generator) {
+    TPW_OP("cpdist", "cdist");
+    const std::string m(metric.data(), metric.size());
+    check_metric_and_extra_args(m, w, V, VI, p, base, shuffle, generator);
+    return cdist_dispatch(x1, x2, m, w, V, VI, p, base, shuffle, generator);
+}
+
+// The L_p metrics the fused neighbour and condensed kernels serve: exponent p and the exponent applied to the sum.
+// Returns false for every other metric, for weights, and for exponents the kernels do not take.
+bool lp_metric_of(const std::string &m, const c10::optional<double> &p_arg, double *p, double *out_exponent) {
+    const double inf = std::numeric_limits<double>::infinity();
+    if (m == "euclidean" || m == "l2") { *p = 2; *out_exponent = 0.5; return true; }
+    if (m == "sqeuclidean") { *p = 2; *out_exponent = 1; return true; }
+    if (m == "manhattan" || m == "cityblock" || m == "l1") { *p = 1; *out_exponent = 1; return true; }
+    if (m == "chebyshev" || m == "linf") { *p = inf; *out_exponent = 1; return true; }
+    if (m == "minkowski" || m == "lp") {
+        *p = p_arg.value_or(2.0);
+        if (!(*p > 0)) return false;
+        *out_exponent = std::isinf(*p) ? 1.0 : 1.0 / *p;
+        return true;
+    }
+    return false;
+}
+
+// ---- pdist (OPS/cpdist.cpp:233-255: declared with the arguments of cdist, raises "yet to be implemented") ---------
+// The condensed upper triangle of cdist(input, input), row by row (the layout of torch.pdist).  The L_p metrics run the
+// tile kernel with a condensed epilogue that skips the tiles on or below the diagonal when no gradient is needed;
+// everything else, and every differentiable call, evaluates cdist and gathers the triangle.
+Tensor pdist(const Tensor &input, c10::string_view metric, const OptTensor &w, const OptTensor &V, const OptTensor &VI,
+             c10::optional<double> p, c10::optional<double> base, c10::optional<bool> shuffle,
+             c10::optional<at::Generator> generator) {
+    TPW_OP("cpdist", "pdist");
+    const std::string m(metric.data(), metric.size());
+    check_metric_and_extra_args(m, w, V, VI, p, base, shuffle, generator);
+    TORCH_CHECK(input.dim() == 2 || input.dim() == 3, "input must be 2D tensor (unbatched) or 3D tensor (batched)");
+    require_cuda(input);
+    const int64_t n = input.size(-2);
+    double pp = 0, ex = 0;
+    const auto dt = input.scalar_type();
+    if (lp_metric_of(m, p, &pp, &ex) && (dt == at::kFloat || dt == at::kDouble) && input.size(-1) > 0 &&
+        !(input.requires_grad() && at::GradMode::is_enabled())) {
+        Tensor x = input.contiguous();
+        if (x.dim() == 2) x = x.unsqueeze(0);
+        c10::cuda::CUDAGuard dg(x.device());
+        Tensor out = at::empty({x.size(0), n * (n - 1) / 2}, x.options());
+        TPW_CALL(tpw_lp_pdist_forward(code_of(x), x.data_ptr(), out.data_ptr(), x.size(0), n, x.size(2), pp, ex, stream_of(x)));
+        return input.dim() == 3 ? out : out.squeeze(0);
+    }
+    Tensor full = cdist_dispatch(input, input, m, w, V, VI, p, base, shuffle, generator);
+    Tensor iu = at::triu_indices(n, n, 1, at::TensorOptions().dtype(at::kLong).device(input.device()));
+    return full.index({at::indexing::Ellipsis, iu[0], iu[1]});
+}
+
+// ---- neighbour masks (OPS/neighbors.cpp:10-68) -------------------------------------------------------------------
+// The reference evaluates cdist and compares / sorts the whole matrix.  Float32 L_p metrics (and, for the k nearest
+// rows, the contraction metrics on large problems) go to the fused kernels instead, which never write the
+// float matrix; everything else follows the reference's composition with a partial selection in place of the sort.
+Tensor radius_neighbors_mask(const Tensor &x1, const OptTensor &x2, double epsilon, c10::string_view metric, const OptTensor &w,
+                             const OptTensor &V, const OptTensor &VI, c10::optional<double> p, c10::optional<double> base,
+                             c10::optional<bool> shuffle, c10::optional<at::Generator> generator) {
+    C10_LOG_API_USAGE_ONCE("torchpairwise.csrc.ops.neighbors.k_neighbors_mask");  // the name the reference logs here too (OPS/neighbors.cpp:48)
+    NvtxRange nvtx_range_("torchpairwise::radius_neighbors_mask");
+    auto ab = check_pairwise_inputs("radius_neighbors_mask", x1, x2);
+    TORCH_CHECK(epsilon >= 0., "epsilon must be non-negative. Got epsilon=", epsilon);
+    const std::string m(metric.data(), metric.size());
+    check_metric_and_extra_args(m, w, V, VI, p, base, shuffle, generator);
+    at::NoGradGuard ng;
+    double pp = 0, ex = 0;
+    const auto dt = ab.first.scalar_type();
+    if (lp_metric_of(m, p, &pp, &ex) && ab.first.is_cuda() && dt == ab.second.scalar_type() && (dt == at::kFloat || dt == at::kDouble) &&
+        ab.first.size(-1) > 0 && (ab.first.dim() == 2 || ab.first.dim() == 3)) {
+        Prepared q = prepare(ab.first, ab.second, dt);
+        // p = 2 on a large float32 problem is faster as a tensor-core contraction plus a compare pass
+        if (!(pp == 2.0 && tensor_engine_selected(q))) {
+            c10::cuda::CUDAGuard dg(q.a.device());
+            Tensor mask = at::empty({q.B, q.N1, q.N2}, q.a.options().dtype(at::kBool));
+            TPW_CALL(tpw_lp_radius_mask_forward(code_of(q.a), q.a.data_ptr(), q.b.data_ptr(), nullptr,
+                                                static_cast<uint8_t *>(mask.data_ptr()), q.B, q.N1, q.N2, q.D, pp, ex, epsilon,
+                                                stream_of(q.a)));
+            return q.unbatched ? mask.squeeze(0) : mask;
+        }
+    }
+    return cdist_dispatch(ab.first, ab.second, m, w, V, VI, p, base, shuffle, generator).le(epsilon);
+}
+
+Tensor k_neighbors_mask(const Tensor &x1, const OptTensor &x2, int64_t k, c10::string_view metric, const OptTensor &w,
+                        const OptTensor &V, const OptTensor &VI, c10::optional<double> p, c10::optional<double> base,
+                        c10::optional<bool> shuffle, c10::optional<at::Generator> generator) {
+    TPW_OP("neighbors", "k_neighbors_mask");
+    auto ab = check_pairwise_inputs("k_neighbors_mask", x1, x2);
+    TORCH_CHECK(k >= 0, "k must be non-negative. Got k=", k);
+    const std::string m(metric.data(), metric.size());
+    check_metric_and_extra_args(m, w, V, VI, p, base, shuffle, generator);
+    at::NoGradGuard ng;
+    const Tensor &a = ab.first, &b = ab.second;
+    auto scatter_mask = [&](const Tensor &inds) {
+        Tensor out = at::zeros({a.size(0), b.size(0)}, a.options().dtype(at::kBool));
+        return out.scatter_(1, inds, true);
+    };
+    double pp = 0, ex = 0;
+    const bool f32 = a.is_cuda() && a.dim() == 2 && a.scalar_type() == at::kFloat && b.scalar_type() == at::kFloat &&
+                     a.size(-1) > 0 && b.size(0) > 0;
+    const int64_t kk = k + 1;  // the reference keeps k + 1 columns: the point itself plus k neighbours when x2 is x1
+    if (f32 && kk <= b.size(0)) {
+        Prepared q = prepare(a, b, at::kFloat);
+        c10::cuda::CUDAGuard dg(q.a.device());
+        const bool lp = lp_metric_of(m, p, &pp, &ex);
+        const bool tensor = tensor_engine_selected(q);
+        const int dot_epilogue = (m == "euclidean" || m == "l2") ? TPW_DOT_EUCLIDEAN : m == "sqeuclidean" ? TPW_DOT_SQEUCLIDEAN
+                                 : m == "cosine" ? TPW_DOT_COSINE_DIST : -1;
+        auto st = stream_of(q.a);
+        if (kk == 1 && (lp || (dot_epilogue >= 0 && tensor))) {
+            // one column per row: the streaming row minimum, no distance matrix and no sort
+            Tensor mins = at::empty({q.B, q.N1}, q.a.options()), args = at::empty({q.B, q.N1}, q.a.options().dtype(at::kLong));
+            if (dot_epilogue >= 0 && tensor) {
+                const int64_t bytes = tpw_dot_rowmin_scratch_bytes(q.B, q.N1, q.N2, q.D);
+                Tensor scratch = at::empty({bytes}, q.a.options().dtype(at::kByte));
+                TPW_CALL(tpw_dot_rowmin_forward_ws(dot_epilogue, q.a.data_ptr(), q.b.data_ptr(), mins.data_ptr<float>(),
+                                                   args.data_ptr<int64_t>(), scratch.data_ptr(), bytes, q.B, q.N1, q.N2, q.D, st));
+            } else {
+                const int64_t bytes = std::max<int64_t>(8, tpw_lp_rowmin_scratch_bytes(q.B, q.N1));
+                Tensor scratch = at::empty({bytes}, q.a.options().dtype(at::kByte));
+                TPW_CALL(tpw_lp_rowmin_forward(TPW_F32, q.a.data_ptr(), q.b.data_ptr(), nullptr, mins.data_ptr<float>(),
+                                               args.data_ptr<int64_t>(), scratch.data_ptr(), q.B, q.N1, q.N2, q.D, pp, ex, st));
+            }
+            return scatter_mask(args.squeeze(0).unsqueeze(1));
+        }
+        const bool few_p = pp == 1.0 || pp == 2.0 || pp == 3.0 || std::isinf(pp);
+        if (lp && few_p && q.D <= tpw_lp_topk_max_features() && q.N1 >= 4096 && kk <= tpw_lp_topk_max_k() &&
+            !std::getenv("TPW_DISABLE_SMALL_D")) {
+            // few features: one x1 row per thread with its k + 1 best keys in registers
+            Tensor vals = at::empty({q.B, q.N1, kk}, q.a.options()), inds = at::empty({q.B, q.N1, kk}, q.a.options().dtype(at::kLong));
+            TPW_CALL(tpw_lp_topk_forward(TPW_F32, q.a.data_ptr(), q.b.data_ptr(), vals.data_ptr<float>(), inds.data_ptr<int64_t>(),
+                                         q.B, q.N1, q.N2, q.D, static_cast<int>(kk), pp, ex, st));
+            return scatter_mask(inds.squeeze(0));
+        }
+        if (dot_epilogue >= 0 && tensor && kk <= tpw_dot_topk_max_k()) {
+            // large problem: the k + 1 nearest rows straight from the tensor-core epilogue
+            Tensor vals = at::empty({q.B, q.N1, kk}, q.a.options()), inds = at::empty({q.B, q.N1, kk}, q.a.options().dtype(at::kLong));
+            const int64_t bytes = tpw_dot_topk_scratch_bytes(kk, q.B, q.N1, q.N2, q.D);
+            Tensor scratch = at::empty({bytes}, q.a.options().dtype(at::kByte));
+            TPW_CALL(tpw_dot_topk_forward_ws(dot_epilogue, static_cast<int>(kk), q.a.data_ptr(), q.b.data_ptr(), vals.data_ptr<float>(),
+                                             inds.data_ptr<int64_t>(), scratch.data_ptr(), bytes, q.B, q.N1, q.N2, q.D, st));
+            return scatter_mask(inds.squeeze(0));
+        }
+    }
+    Tensor dists = cdist_dispatch(a, b, m, w, V, VI, p, base, shuffle, generator);
+    // the k + 1 smallest of every row: a partial selection, not the reference's full argsort of each row
+    Tensor inds = std::get<1>(dists.topk(std::min<int64_t>(kk, dists.size(1)), 1, /*largest=*/false, /*sorted=*/false));
+    return scatter_mask(inds);
+}
+
+// torchpairwise::_cuda_version / _cuda_arch_flags (csrc/torchpairwise.cpp:28-56): what the loader of the reference's
+// Python package checks (torchpairwise/extension.py:98-136).  Only registered when the reference library is absent.
+int64_t cuda_version_op() { return tpw_cuda_version(); }
+std::string cuda_arch_flags_op() { return tpw_cuda_arch_flags(); }
 
 // __directed_hausdorff_backward re-runs the forward for the attaining pair, as the reference's backward op does
 // (OPS/cuda/hausdorff_kernel.cu:283-321).
@@ -1082,22 +1451,49 @@ TORCH_LIBRARY_FRAGMENT(torchpairwise, m) {
     }
     for (const char *n : {"_prf_div_backward", "_prf_ldiv_backward"})
         def_ov(n, "rScalar", "(Tensor grad, Scalar self, Tensor other, str mode=\"zero\") -> Tensor grad_other");
-    def("cdist", "(Tensor x1, Tensor x2, str metric=\"minkowski\", *, Tensor? w=None, Tensor? V=None, Tensor? VI=None, "
-                 "float? p=None, float? base=None, bool? shuffle=None, Generator? generator=None) -> Tensor");
+#define EXTRA_ARGS "Tensor? w=None, Tensor? V=None, Tensor? VI=None, float? p=None, float? base=None, bool? shuffle=None, Generator? generator=None"
+    def("cdist", "(Tensor x1, Tensor x2, str metric=\"minkowski\", *, " EXTRA_ARGS ") -> Tensor");
+    // OPS/cpdist.cpp:252-255, OPS/neighbors.cpp:60-68
+    def("pdist", "(Tensor input, str metric=\"minkowski\", *, " EXTRA_ARGS ") -> Tensor");
+    def("k_neighbors_mask", "(Tensor x1, Tensor? x2=None, int k=1, str metric=\"euclidean\", *, " EXTRA_ARGS ") -> Tensor");
+    def("radius_neighbors_mask", "(Tensor x1, Tensor? x2=None, float epsilon=0., str metric=\"euclidean\", *, " EXTRA_ARGS ") -> Tensor");
+    // OPS/pairwise_metrics.h:114-150,286; OPS/sqmahalanobis.cpp:31-38
+    def("linear_kernel", OPT2);
+    def("polynomial_kernel", "(Tensor x1, Tensor? x2=None, int degree=3, float? gamma=None, float coef0=1) -> Tensor");
+    def("sigmoid_kernel", "(Tensor x1, Tensor? x2=None, float? gamma=None, float coef0=1) -> Tensor");
+    def("rbf_kernel", "(Tensor x1, Tensor? x2=None, float? gamma=None) -> Tensor");
+    def("laplacian_kernel", "(Tensor x1, Tensor? x2=None, float? gamma=None) -> Tensor");
+    def("mahalanobis_distances", "(Tensor x1, Tensor? x2=None, Tensor? VI=None) -> Tensor");
+    def("_sqmahalanobis", "(Tensor x1, Tensor x2, Tensor VI) -> Tensor");
+    def("__sqmahalanobis_backward", "(Tensor grad, Tensor x1, Tensor x2, Tensor VI) -> (Tensor grad_x1, Tensor grad_x2, Tensor grad_VI)");
+    // csrc/torchpairwise.cpp:53-56: defined with their bodies, as there; the reference's own answer stands when it is loaded
+    if (!defined("_cuda_version")) m.def("_cuda_version", &cuda_version_op);
+    if (!defined("_cuda_arch_flags")) m.def("_cuda_arch_flags", &cuda_arch_flags_op);
 }
 
 // CUDA tensors of every op above.  AutogradCUDA sits in front of both the reference's
 // CompositeImplicitAutograd bodies and its `Autograd` alias kernels, for CUDA tensors only.
 TORCH_LIBRARY_IMPL(torchpairwise, AutogradCUDA, m) {
     m.impl("euclidean_distances", euclidean_distances);
-    m.impl("l2_distances", euclidean_distances);
+    m.impl("l2_distances", l2_distances);
     m.impl("manhattan_distances", manhattan_distances);
-    m.impl("cityblock_distances", manhattan_distances);
-    m.impl("l1_distances", manhattan_distances);
+    m.impl("cityblock_distances", cityblock_distances);
+    m.impl("l1_distances", l1_distances);
     m.impl("chebyshev_distances", chebyshev_distances);
-    m.impl("linf_distances", chebyshev_distances);
+    m.impl("linf_distances", linf_distances);
     m.impl("minkowski_distances", minkowski_distances);
-    m.impl("lp_distances", minkowski_distances);
+    m.impl("lp_distances", lp_distances);
+    m.impl("linear_kernel", linear_kernel);
+    m.impl("polynomial_kernel", polynomial_kernel);
+    m.impl("sigmoid_kernel", sigmoid_kernel);
+    m.impl("rbf_kernel", rbf_kernel);
+    m.impl("laplacian_kernel", laplacian_kernel);
+    m.impl("mahalanobis_distances", mahalanobis_distances);
+    m.impl("_sqmahalanobis", sqmahalanobis_raw);
+    m.impl("__sqmahalanobis_backward", sqmahalanobis_backward_op);  // runs a differentiable composition: needs the autograd key
+    m.impl("pdist", pdist);
+    m.impl("k_neighbors_mask", k_neighbors_mask);
+    m.impl("radius_neighbors_mask", radius_neighbors_mask);
     m.impl("wminkowski_distances", wminkowski_distances);
     m.impl("sqeuclidean_distances", sqeuclidean_distances);
     m.impl("cosine_similarity", cosine_similarity);

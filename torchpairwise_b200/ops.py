@@ -1160,22 +1160,49 @@ def braycurtis_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
 
 def snr_distances(x1: Tensor, x2: Optional[Tensor] = None) -> Tensor:
     """1 / _snr = sum_k (e_k - mean e)^2 / sum_k (x1_k - mean x1)^2 with e = x2 - x1 (OPS/pairwise_metrics.cpp:401-408,
-    OPS/cpu/snr_kernel.cpp:22-34,96).  sum_k (e_k - mean e)^2 = |x1 - x2|^2 - (sum x2 - sum x1)^2 / D: the
-    squared-Euclidean kernel of the path plus rank-one terms, differentiable through both."""
+    OPS/cpu/snr_kernel.cpp:22-34,96).  The deviations of e from its mean are the differences of the centred rows, so
+    the numerator is the squared Euclidean distance of the centred rows, taken by the direct-difference kernel: a row
+    against itself gives exactly 0 and near-duplicate rows keep their relative accuracy."""
     x1_, x2_ = check_pairwise_inputs("snr_distances", x1, x2)
     _require_cuda(x1_, x2_)
-    d = x1_.size(-1)
-    shift = x2_.sum(-1).unsqueeze(-2) - x1_.sum(-1, keepdim=True)
-    diff_var = _ppminkowski(x1_, x2_, 2.0) - shift * shift / d
-    x1_var = (x1_ - x1_.mean(-1, keepdim=True)).pow(2).sum(-1, keepdim=True)
-    return diff_var / x1_var
+    c1 = x1_ - x1_.mean(-1, keepdim=True)
+    c2 = c1 if x2 is None else x2_ - x2_.mean(-1, keepdim=True)
+    return _ppminkowski(c1, c2, 2.0) / c1.pow(2).sum(-1, keepdim=True)
+
+
+def _sqmahalanobis(x1: Tensor, x2: Tensor, VI: Tensor) -> Tensor:
+    """(x1 - x2) VI (x1 - x2)^T per pair (OPS/sqmahalanobis.cpp:31-38, OPS/cpu/sqmahalanobis_kernel.cpp:23-31), from
+    direct differences.  The form depends on the symmetric part S of VI only.  Where S is positive definite (every
+    inverse covariance is) S = L L^T and the form is the squared Euclidean distance of x1 L and x2 L: a sum of
+    squares, exactly 0 for a row against itself and accurate for near-duplicate rows.  Otherwise d.e with
+    d = x1 - x2, e = d S is taken as (|d/c + c e|^2 - |d/c - c e|^2) / 4, two more direct-difference kernels
+    (c balances the two magnitudes).  Differentiable in x1, x2 and VI through both."""
+    _require_cuda(x1, x2, VI)
+    if not (x1.dtype == x2.dtype == VI.dtype):
+        raise RuntimeError("x1, x2 and VI must have the same dtype (while checking arguments for _sqmahalanobis_forward)")
+    if x1.dim() not in (2, 3) or x2.dim() != x1.dim() or VI.dim() != x1.dim():
+        raise RuntimeError("x1, x2 and VI must all be 2-D (unbatched) or 3-D (batched) tensors.")
+    if x1.size(-1) != x2.size(-1) or x1.size(-1) != VI.size(-2) or VI.size(-1) != VI.size(-2):
+        raise RuntimeError("feature dimension of x1, x2, and VI do not match.")
+    same = x2 is x1
+    S = (VI + VI.transpose(-1, -2)) * 0.5
+    L, info = torch.linalg.cholesky_ex(S)
+    if x1.size(-1) > 0 and bool((info == 0).all()):
+        u1 = x1 @ L
+        return _ppminkowski(u1, u1 if same else x2 @ L, 2.0)
+    e1 = x1 @ S
+    e2 = e1 if same else x2 @ S
+    with torch.no_grad():
+        nx, ne = float(x1.norm()), float(e1.norm())
+    c = math.sqrt(nx / ne) if nx > 0 and ne > 0 and math.isfinite(nx / ne) else 1.0
+    p1, m1 = x1 / c + e1 * c, x1 / c - e1 * c
+    p2, m2 = (p1, m1) if same else (x2 / c + e2 * c, x2 / c - e2 * c)
+    return (_ppminkowski(p1, p2, 2.0) - _ppminkowski(m1, m2, 2.0)) * 0.25
 
 
 def mahalanobis_distances(x1: Tensor, x2: Optional[Tensor] = None, VI: Optional[Tensor] = None) -> Tensor:
-    """sqrt((x1 - x2) VI (x1 - x2)^T) (OPS/pairwise_metrics.cpp:272-297, OPS/cpu/sqmahalanobis_kernel.cpp:23-31); VI
-    defaults to the transposed inverse covariance of x1 (no gradient), as there.  Expanded into four
-    bilinear terms, the two cross terms being plain dot-product kernels of the path (tensor cores on
-    large problems): like every contraction form it loses relative accuracy for near-duplicate rows."""
+    """sqrt((x1 - x2) VI (x1 - x2)^T) (OPS/pairwise_metrics.cpp:272-297); VI defaults to the transposed inverse
+    covariance of x1 (no gradient), as there.  See ``_sqmahalanobis`` for how the form is evaluated."""
     if x2 is not None and VI is None:
         raise RuntimeError("VI is required for manhalanobis when x2 is passed.")
     x1_, x2_ = check_pairwise_inputs("mahalanobis_distances", x1, x2)
@@ -1184,11 +1211,20 @@ def mahalanobis_distances(x1: Tensor, x2: Optional[Tensor] = None, VI: Optional[
         with torch.no_grad():
             VI = torch.linalg.inv(torch.cov(x1_.transpose(-1, -2)) if x1_.dim() == 2 else
                                   torch.stack([torch.cov(xb.transpose(-1, -2)) for xb in x1_])).transpose(-1, -2)
-    x1v = linear_kernel(x1_, VI.transpose(-1, -2))          # x1 VI
-    x2v = x1v if x2 is None else linear_kernel(x2_, VI.transpose(-1, -2))
-    sq = ((x1v * x1_).sum(-1, keepdim=True) + (x2v * x2_).sum(-1).unsqueeze(-2)
-          - linear_kernel(x1v, x2_) - linear_kernel(x1_, x2v))
-    return sq.clamp_min(0).sqrt()
+    return _sqmahalanobis(x1_, x2_, VI).sqrt()
+
+
+def _validate_metric_kwargs(metric: str, kwargs: dict) -> None:
+    """The keyword check ``cdist`` applies (OPS/cpdist.cpp:35-79), run before any fused kernel is chosen so that a call
+    raises or does not raise whatever the problem size: an unknown metric is a RuntimeError, a keyword the metric
+    does not take a TypeError."""
+    from .cpdist import SUPPORTED_METRICS, _check_extra_args
+    if metric not in SUPPORTED_METRICS:
+        raise RuntimeError(f"Got unkown distance metric: {metric}. Supported metrics are [{', '.join(SUPPORTED_METRICS)}]")
+    unknown = set(kwargs) - {"w", "V", "VI", "p", "base", "shuffle", "generator"}
+    if unknown:
+        raise TypeError(f"unexpected keyword argument(s): {', '.join(sorted(unknown))}")
+    _check_extra_args(metric, **kwargs)
 
 
 def radius_neighbors_mask(x1: Tensor, x2: Optional[Tensor] = None, epsilon: float = 0.0, metric: str = "euclidean",
@@ -1198,6 +1234,7 @@ def radius_neighbors_mask(x1: Tensor, x2: Optional[Tensor] = None, epsilon: floa
     x1_, x2_ = check_pairwise_inputs("radius_neighbors_mask", x1, x2)
     if epsilon < 0:
         raise RuntimeError(f"epsilon must be non-negative. Got epsilon={epsilon}")
+    _validate_metric_kwargs(metric, kwargs)
     with torch.no_grad():
         if metric in _ROWMIN_METRICS and x1_.is_cuda and set(kwargs) <= {"p"} and x1_.dtype == x2_.dtype \
                 and x1_.dtype in _FLOAT_CODES and x1_.size(-1) > 0:
@@ -1225,6 +1262,7 @@ def k_neighbors_mask(x1: Tensor, x2: Optional[Tensor] = None, k: int = 1, metric
     x1_, x2_ = check_pairwise_inputs("k_neighbors_mask", x1, x2)
     if k < 0:
         raise RuntimeError(f"k must be non-negative. Got k={k}")
+    _validate_metric_kwargs(metric, kwargs)
     with torch.no_grad():
         if (k == 0 and metric in _ROWMIN_METRICS and x1_.dtype == torch.float32 and x2_.dtype == torch.float32
                 and x1_.is_cuda and x2_.size(0) > 0 and set(kwargs) <= {"p"}):
@@ -1360,6 +1398,7 @@ def pairwise_argkmin(x1: Tensor, x2: Optional[Tensor] = None, k: int = 1, metric
         raise RuntimeError(f"k must be positive. Got k={k}")
     x1_, x2_ = check_pairwise_inputs("pairwise_argkmin", x1, x2)
     _require_cuda(x1_, x2_)
+    _validate_metric_kwargs(metric, kwargs)
     if k > x2_.size(-2):
         raise RuntimeError(f"k={k} exceeds the number of x2 rows ({x2_.size(-2)})")
     epilogue = {"euclidean": _abi.DOT_EUCLIDEAN, "l2": _abi.DOT_EUCLIDEAN, "sqeuclidean": _abi.DOT_SQEUCLIDEAN,

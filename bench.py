@@ -421,7 +421,7 @@ def run_configs(T, R, dev, gpu_ms, peaks, X, Y, G, hosts, args):
     Xb, Yb, Gb = c2_block(*hosts, rows)
     pairs = B * N1 * N2
     for name, kw, fwd_alg, bwd_alg, fwd_exe, bwd_exe in (("minkowski_distances", {"p": P}, 3, 4, 3, 6),
-                                                         ("chebyshev_distances", {}, 2, 2, 2, 8)):
+                                                         ("chebyshev_distances", {}, 2, 2, 2, 4)):
         op = getattr(T, name)
 
         def fb():

@@ -189,6 +189,24 @@ TPW_API int tpw_wminkowski_backward_w(int dtype, const void *grad, const void *a
                               double p, tpw_stream_t stream);
 
 /*
+ * The p = +inf case of TPW_LP_BWD_CDIST (the backward of chebyshev_distances, ATen's cdist backward under
+ * OPS/pairwise_metrics.cpp:305) for float32 in three steps: one pass over (i, j, k) finds the coordinate that
+ * attains each pair's maximum (compared against the saved forward output `out`) and writes a 4-byte code per
+ * pair; two scatter kernels then add +-g into grad_x1 / grad_x2 at that coordinate, one thread per gradient
+ * row in a fixed order (deterministic, no atomics).  The dense form does the comparison for every (i, j, k)
+ * once per gradient.  Pairs whose maximum is attained by several coordinates (lattice-valued data) make the
+ * call fall back, on the device and without a host round trip, to the dense kernel, so the result always
+ * equals tpw_lp_backward(TPW_LP_BWD_CDIST, p = +inf).
+ * The scratch query returns 0 when the problem is to be given to tpw_lp_backward instead (float64, fewer than
+ * 16 or more than 65535 features, an empty dimension); otherwise 256 + 4 * B * N1 * N2 bytes, 16-byte aligned.
+ * Either gradient may be NULL.
+ */
+TPW_API int64_t tpw_chebyshev_backward_scratch_bytes(int dtype, int64_t B, int64_t N1, int64_t N2, int64_t D);
+TPW_API int tpw_chebyshev_backward_ws(const void *grad, const void *out, const void *x1, const void *x2,
+                              void *grad_x1, void *grad_x2, void *scratch, int64_t scratch_bytes,
+                              int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream);
+
+/*
  * Single-coordinate backward of the +-inf variants: for each pair the FIRST k attaining the
  * extreme of w_k*|d_k| receives the gradient (float atomics; grads must be zero-filled by
  * the caller).  w/grad_w may be NULL (un-weighted _ppminkowski form).
@@ -494,7 +512,10 @@ TPW_API int tpw_prf_div_backward(int dtype, int mode, const void *grad, const vo
 /*
  * Runs a register-only microbenchmark on the current device, synchronises, and reports the
  * sustained rate in operations per second: kind 0 = fp32 FMA lane-operations (scalar FFMA),
- * 1 = fp32 FMA lane-operations issued as packed fma.rn.f32x2, 2 = 32-bit POPC lane-operations.
+ * 1 = fp32 FMA lane-operations issued as packed fma.rn.f32x2, 2 = 32-bit POPC lane-operations,
+ * 3 = fp32 additions, 4 = fp32 multiplications, 5 = the instruction mix of the p = 3 tiles (subtract,
+ * d * |d|, fused multiply-add: three lane-operations per element), 6 = the same three results from
+ * fused multiply-adds only, 7 = fp32 compares into a register, 8 = fp32 maxima, 9 = 32-bit integer additions.
  * No counterpart in the reference.
  */
 TPW_API int tpw_measure_issue_peak(int kind, double *ops_per_second);

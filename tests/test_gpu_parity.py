@@ -189,6 +189,55 @@ def test_config_shaped_golden(tpw, golden):
     close(b.grad.cpu()[tuple(r2.t())], G["C5/gx2_vals"], tol, msg="C5 grad_x2")
 
 
+@pytest.mark.parametrize("shape", [(1, 70, 50, 16), (2, 129, 67, 36), (1, 64, 64, 70), (2, 200, 333, 300), (1, 300, 130, 257)])
+@pytest.mark.parametrize("lattice", [False, True])
+def test_chebyshev_backward_match_and_scatter(tpw, shape, lattice):
+    """The Chebyshev backward that finds each pair's attaining coordinate once and scatters both gradients against the
+    oracle (ATen's rule: every tied coordinate receives the gradient) and, bit for bit, against the dense kernel.
+    Lattice-valued inputs have tied maxima in most pairs and take the on-device hand-over to the dense kernel, the
+    continuous inputs carry three engineered ties that the scatter kernels resolve themselves; D = 70 is not a
+    multiple of 16 bytes (plain loads instead of TMA), D = 300 and 257 span two feature blocks of the scatter."""
+    from torchpairwise_b200 import _abi
+    b, n1, n2, d = shape
+    g = torch.Generator().manual_seed(b * 7 + n1 + n2 + d + int(lattice))
+    if lattice:
+        x1 = torch.randint(0, 4, (b, n1, d), generator=g).float()
+        x2 = torch.randint(0, 4, (b, n2, d), generator=g).float()
+        x2[:, 0] = x1[:, 0]                       # one pair at distance 0: no gradient
+    else:
+        x1, x2 = torch.randn(b, n1, d, generator=g), torch.randn(b, n2, d, generator=g)
+        # a few exactly tied maxima (opposite signs, three-way), handled pair by pair inside the scatter kernels
+        for r, c, ks, vals in ((0, 0, (1, d - 1), (9.0, -9.0)), (n1 - 1, n2 - 1, (0, 3, d - 2), (-8.5, -8.5, 8.5)), (n1 // 2, 1, (2, 5), (7.0, 7.0))):
+            for k, v in zip(ks, vals):
+                x2[0, c, k] = 0.0
+                x1[0, r, k] = v
+    gr = torch.randn(b, n1, n2, generator=g)
+    assert _abi.lib.tpw_chebyshev_backward_scratch_bytes(_abi.F32, b, n1, n2, d) == 256 + 4 * b * n1 * n2
+    a, c = x1.cuda().requires_grad_(True), x2.cuda().requires_grad_(True)
+    out = tpw.chebyshev_distances(a, c)
+    out.backward(gr.cuda())
+    r1, r2 = O.cdist_backward(gr.numpy(), x1.numpy(), x2.numpy(), math.inf, out=out.detach().cpu().numpy())
+    scale = 10 * max(1.0, float(np.abs(r1).max()))
+    close(a.grad, r1, TOL[torch.float32], scale, "grad_x1")
+    close(c.grad, r2, TOL[torch.float32], scale, "grad_x2")
+    # the dense kernel on the same inputs
+    d1, d2 = torch.empty_like(a.grad), torch.empty_like(c.grad)
+    _abi.check(_abi.lib.tpw_lp_backward(_abi.F32, _abi.LP_BWD_CDIST, gr.cuda().data_ptr(), out.data_ptr(), a.data_ptr(), c.data_ptr(),
+                                        None, d1.data_ptr(), d2.data_ptr(), b, n1, n2, d, math.inf,
+                                        torch.cuda.current_stream().cuda_stream))
+    if lattice:
+        assert torch.equal(a.grad, d1) and torch.equal(c.grad, d2)     # the fallback is that kernel
+    else:
+        torch.testing.assert_close(a.grad, d1, rtol=1e-5, atol=1e-5 * scale)   # same terms, another order of addition
+        torch.testing.assert_close(c.grad, d2, rtol=1e-5, atol=1e-5 * scale)
+    # run to run reproducible, and one-sided calls leave the other gradient alone
+    a2, c2 = x1.cuda().requires_grad_(True), x2.cuda()
+    tpw.chebyshev_distances(a2, c2).backward(gr.cuda())
+    assert torch.equal(a2.grad, a.grad)
+    assert _abi.lib.tpw_chebyshev_backward_scratch_bytes(_abi.F64, b, n1, n2, d) == 0
+    assert _abi.lib.tpw_chebyshev_backward_scratch_bytes(_abi.F32, b, n1, n2, 8) == 0
+
+
 @pytest.mark.parametrize("shape", [(1, 1, 1), (3, 1, 2), (129, 127, 33), (2, 257, 130), (50, 300, 7), (64, 64, 260)])
 @pytest.mark.parametrize("p", [1.0, 2.0, 3.0, 2.5, math.inf])
 def test_ragged_shapes_vs_oracle(tpw, shape, p):

@@ -162,11 +162,61 @@ __global__ void __launch_bounds__(256) issue_peak_kernel(float *sink, int iters,
                     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(v) : "l"(v), "l"(mm), "l"(cc));
                     asm("mov.b64 {%0, %1}, %2;" : "=f"(a[i]), "=f"(a[i + 1]) : "l"(v));
                 }
-        } else {
+        } else if (KIND == 2) {
 #pragma unroll
             for (int r = 0; r < 4; ++r)
 #pragma unroll
                 for (int i = 0; i < 16; ++i) u[i] = __popc(u[i]) + u[(i + 1) & 15];
+        } else if (KIND == 3) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) asm volatile("add.rn.f32 %0, %0, %1;" : "+f"(a[i]) : "f"(c));
+        } else if (KIND == 4) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) asm volatile("mul.rn.f32 %0, %0, %1;" : "+f"(a[i]) : "f"(m));
+        } else if (KIND == 5) {
+            // the instruction mix of the p = 3 tiles: subtract, d * |d|, fused multiply-add (3 operations per element)
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int i = 0; i < 16; i += 3) {
+                    float d, t;
+                    asm volatile("sub.rn.f32 %0, %1, %2;" : "=f"(d) : "f"(a[i]), "f"(m));
+                    asm volatile("mul.rn.f32 %0, %1, %2;" : "=f"(t) : "f"(d), "f"(fabsf(d)));
+                    asm volatile("fma.rn.f32 %0, %1, %2, %0;" : "+f"(a[i]) : "f"(t), "f"(c));
+                }
+        } else if (KIND == 7) {
+            // fp32 compare into a register (1.0 / 0.0)
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) asm volatile("set.eq.f32.f32 %0, %0, %1;" : "+f"(a[i]) : "f"(c));
+        } else if (KIND == 8) {
+            // fp32 maximum
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) asm volatile("max.f32 %0, %0, %1;" : "+f"(a[i]) : "f"(a[(i + 1) & 15]));
+        } else if (KIND == 9) {
+            // 32-bit integer addition
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) asm volatile("add.u32 %0, %0, %1;" : "+r"(u[i]) : "r"(u[(i + 1) & 15]));
+        } else {
+            // the same three results from fused multiply-adds only
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int i = 0; i < 16; i += 3) {
+                    float d, t;
+                    asm volatile("fma.rn.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(m), "f"(-1.0f), "f"(a[i]));
+                    asm volatile("fma.rn.f32 %0, %1, %2, %3;" : "=f"(t) : "f"(d), "f"(fabsf(d)), "f"(0.0f));
+                    asm volatile("fma.rn.f32 %0, %1, %2, %0;" : "+f"(a[i]) : "f"(t), "f"(c));
+                }
         }
     }
     float s = 0.f;
@@ -229,7 +279,7 @@ int tpw_selftest_bounded_wait(int budget_ms, tpw_stream_t stream) {
 
 int tpw_measure_issue_peak(int kind, double *ops_per_second) {
     TPW_CHECK_ARG(ops_per_second != nullptr, "tpw_measure_issue_peak: output pointer is NULL");
-    TPW_CHECK_ARG(kind >= 0 && kind <= 2, "tpw_measure_issue_peak: kind must be 0, 1 or 2");
+    TPW_CHECK_ARG(kind >= 0 && kind <= 9, "tpw_measure_issue_peak: kind must be 0 .. 9");
     int *sink_i = tpw::device_status_ptr();
     if (!sink_i) return tpw::fail(TPW_ERR_CUDA, "tpw_measure_issue_peak: no device");
     float *sink = reinterpret_cast<float *>(sink_i); // never written (see kernel)
@@ -242,7 +292,14 @@ int tpw_measure_issue_peak(int kind, double *ops_per_second) {
         cudaEventRecord(e0, 0);
         if (kind == 0) tpw::issue_peak_kernel<0><<<blocks, threads>>>(sink, iters, 1.0f);
         else if (kind == 1) tpw::issue_peak_kernel<1><<<blocks, threads>>>(sink, iters, 1.0f);
-        else tpw::issue_peak_kernel<2><<<blocks, threads>>>(sink, iters, 1.0f);
+        else if (kind == 2) tpw::issue_peak_kernel<2><<<blocks, threads>>>(sink, iters, 1.0f);
+        else if (kind == 3) tpw::issue_peak_kernel<3><<<blocks, threads>>>(sink, iters, 1.0f);
+        else if (kind == 4) tpw::issue_peak_kernel<4><<<blocks, threads>>>(sink, iters, 1.0f);
+        else if (kind == 5) tpw::issue_peak_kernel<5><<<blocks, threads>>>(sink, iters, 1.0f);
+        else if (kind == 6) tpw::issue_peak_kernel<6><<<blocks, threads>>>(sink, iters, 1.0f);
+        else if (kind == 7) tpw::issue_peak_kernel<7><<<blocks, threads>>>(sink, iters, 1.0f);
+        else if (kind == 8) tpw::issue_peak_kernel<8><<<blocks, threads>>>(sink, iters, 1.0f);
+        else tpw::issue_peak_kernel<9><<<blocks, threads>>>(sink, iters, 1.0f);
         cudaEventRecord(e1, 0);
         cudaError_t e = cudaEventSynchronize(e1);
         if (e != cudaSuccess) {
@@ -256,7 +313,8 @@ int tpw_measure_issue_peak(int kind, double *ops_per_second) {
     }
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
-    const double ops = (double)blocks * threads * (double)iters * 64.0; // 4 x 16 operations per iteration
+    // 4 x 16 operations per iteration; the two mixes run 4 x 6 chains of three operations each
+    const double ops = (double)blocks * threads * (double)iters * (kind == 5 || kind == 6 ? 72.0 : 64.0);
     *ops_per_second = ops / (best_ms * 1e-3);
     return TPW_OK;
 }

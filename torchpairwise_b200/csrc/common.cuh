@@ -72,6 +72,11 @@ bool lp_small_d_rowmin_eligible(long long N1, long long N2, long long D, double 
 int lp_small_d_rowmin(const void *x1, const void *x2, unsigned long long *keys, long long B, long long N1, long long N2, long long D,
                       double p, double out_exponent, cudaStream_t s);
 
+// lp_backward.cu: the dense cdist backward for p = +inf (float32), run only when *only_if > above on the device
+int lp_backward_cdist_inf_if(const unsigned long long *only_if, unsigned long long above, const void *grad, const void *out, const void *x1, const void *x2,
+                             void *grad_x1, void *grad_x2, long long B, long long N1, long long N2, long long D,
+                             cudaStream_t stream);
+
 // |d|^q in the float kernels.  spec = mode | m << 2 (uniform over a launch): mode 0 is the general
 // exp2(q log2 a) (two MUFU operations per element); mode 1 is q = m + 1/2, one approximate square
 // root (MUFU.SQRT, 1 ulp) times a^m; mode 2 is the integer q = m as repeated multiplication.

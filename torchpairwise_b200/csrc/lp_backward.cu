@@ -53,6 +53,8 @@ struct BwdParams {
     double post;        // scalar applied to every result
     int coef_mode;
     int *status;
+    const unsigned long long *only_if; // non-NULL: the kernel does nothing unless this device counter exceeds only_if_above
+    unsigned long long only_if_above;
 };
 
 constexpr int kStages = 2;
@@ -94,6 +96,55 @@ __device__ __forceinline__ float b_log(float v) {   // flush-to-zero MUFU logari
 __device__ __forceinline__ double b_log(double v) { return log(v); }
 __device__ __forceinline__ float b_pow(float a, double q) { return powf(a, (float)q); }
 __device__ __forceinline__ double b_pow(double a, double q) { return pow(a, q); }
+
+// Two float32 lanes per instruction (sm_100 packed arithmetic).  The FMA pipe retires the same number of lanes per
+// clock either way, but a packed instruction takes one issue slot for two results, which leaves the scheduler
+// room for the shared-memory loads and lets four warps per scheduler cover the arithmetic latency.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ f32x2 abs2(f32x2 a) { return a & 0x7fffffff7fffffffull; }
+
+template <typename T, int PHI> struct PackedPhi {
+    static constexpr bool value = false;
+};
+template <> struct PackedPhi<float, PHI_DABS> { static constexpr bool value = true; };
+template <> struct PackedPhi<float, PHI_D> { static constexpr bool value = true; };
+template <> struct PackedPhi<float, PHI_Y> { static constexpr bool value = true; };
+
+// acc += c * phi(x - y) on two adjacent features: the same operations, in the same order and rounding, as the scalar form
+template <int PHI>
+__device__ __forceinline__ f32x2 bwd_accumulate2(f32x2 acc, f32x2 x, f32x2 y, f32x2 c) {
+    if (PHI == PHI_Y) return fma2(c, y, acc);
+    const f32x2 d = sub2(x, y);
+    if (PHI == PHI_D) return fma2(c, d, acc);
+    // d |d| lane by lane: the scalar multiply takes |.| as an operand modifier, a packed one would need two logic
+    // operations for it, and those occupy the same lanes as the arithmetic
+    float lo, hi;
+    unpack2(d, lo, hi);
+    return fma2(c, pack2(lo * fabsf(lo), hi * fabsf(hi)), acc);
+}
 
 // acc += c * phi(x - y)
 template <int PHI, typename T>
@@ -169,6 +220,7 @@ __global__ void __launch_bounds__(NTHR, 1)
 lp_backward_kernel(const __grid_constant__ CUtensorMap map_stream, const __grid_constant__ CUtensorMap map_grad,
                    const __grid_constant__ CUtensorMap map_aux, const BwdParams P) {
     typedef BwdSmem<T, RR, RK, NTHR> S;
+    if (P.only_if && *P.only_if <= P.only_if_above) return;
     constexpr int TR = S::TR, TK = S::TK, GK = RK / 4;
     constexpr int RSTRIDE = (NTHR / 16) * 4;      // distance between a thread's groups of four rows
     constexpr int kThreads = NTHR;
@@ -211,6 +263,17 @@ lp_backward_kernel(const __grid_constant__ CUtensorMap map_stream, const __grid_
     for (int a = 0; a < RR; ++a)
 #pragma unroll
         for (int c = 0; c < RK; ++c) acc[a][c] = T(0);
+    constexpr bool PACKED = PackedPhi<T, PHI>::value;
+    f32x2 acc2[PACKED ? RR : 1][PACKED ? RK / 2 : 1], xr2[PACKED ? RR : 1][PACKED ? RK / 2 : 1];
+    if constexpr (PACKED) {
+#pragma unroll
+        for (int a = 0; a < RR; ++a)
+#pragma unroll
+            for (int c = 0; c < RK / 2; ++c) {
+                acc2[a][c] = 0ull;
+                xr2[a][c] = PHI != PHI_Y ? pack2(xr[a][2 * c], xr[a][2 * c + 1]) : 0ull;
+            }
+    }
 
     const int nchunks = (int)((P.NS + SC - 1) / SC);
     const uint32_t tx_bytes = S::YS_BYTES + S::GS_BYTES + (NEED_AUX ? S::GS_BYTES : 0);
@@ -324,12 +387,25 @@ lp_backward_kernel(const __grid_constant__ CUtensorMap map_stream, const __grid_
                         if (AUX_IN_LOOP) load4<T>(&ot[g * 4], as + (s + u) * TR + g * RSTRIDE + tr * 4);
                     }
                 }
+                if constexpr (PACKED) {
+                    f32x2 yv2[RK / 2];
 #pragma unroll
-                for (int a = 0; a < RR; ++a) {
-                    const T c = TRANS ? ct[a] : cv[a][u];
-                    const T o = AUX_IN_LOOP ? (TRANS ? ot[a] : ov[a][u]) : T(0);
+                    for (int kk = 0; kk < RK / 2; ++kk) yv2[kk] = pack2(yv[2 * kk], yv[2 * kk + 1]);
 #pragma unroll
-                    for (int kk = 0; kk < RK; ++kk) bwd_accumulate<PHI, T>(acc[a][kk], xr[a][kk], yv[kk], c, o, q, pspec);
+                    for (int a = 0; a < RR; ++a) {
+                        const float c = TRANS ? ct[a] : cv[a][u];
+                        const f32x2 c2 = pack2(c, c);
+#pragma unroll
+                        for (int kk = 0; kk < RK / 2; ++kk) acc2[a][kk] = bwd_accumulate2<PHI>(acc2[a][kk], xr2[a][kk], yv2[kk], c2);
+                    }
+                } else {
+#pragma unroll
+                    for (int a = 0; a < RR; ++a) {
+                        const T c = TRANS ? ct[a] : cv[a][u];
+                        const T o = AUX_IN_LOOP ? (TRANS ? ot[a] : ov[a][u]) : T(0);
+#pragma unroll
+                        for (int kk = 0; kk < RK; ++kk) bwd_accumulate<PHI, T>(acc[a][kk], xr[a][kk], yv[kk], c, o, q, pspec);
+                    }
                 }
             }
         }
@@ -341,6 +417,12 @@ lp_backward_kernel(const __grid_constant__ CUtensorMap map_stream, const __grid_
         }
     }
 
+    if constexpr (PACKED) {
+#pragma unroll
+        for (int a = 0; a < RR; ++a)
+#pragma unroll
+            for (int c = 0; c < RK / 2; ++c) unpack2(acc2[a][c], acc[a][2 * c], acc[a][2 * c + 1]);
+    }
     T *out = reinterpret_cast<T *>(P.out) + b * P.NR * P.D;
     const T *w = P.w ? reinterpret_cast<const T *>(P.w) + b * P.D : nullptr;
     const T post = (T)P.post;
@@ -503,6 +585,20 @@ __global__ void lp_inf_backward_kernel(const T *grad, const T *x1, const T *x2, 
 } // namespace tpw
 
 using namespace tpw;
+
+// The dense p = +inf backward of cdist in float32, run only when the device counter *only_if exceeds `above` (the
+// fallback of chebyshev_backward.cu for data full of tied maxima).
+int tpw::lp_backward_cdist_inf_if(const unsigned long long *only_if, unsigned long long above, const void *grad, const void *out, const void *x1, const void *x2,
+                                  void *grad_x1, void *grad_x2, long long B, long long N1, long long N2, long long D,
+                                  cudaStream_t stream) {
+    BwdParams P;
+    memset(&P, 0, sizeof(P));
+    P.grad = grad; P.aux = out; P.w = nullptr;
+    P.B = B; P.N1 = N1; P.N2 = N2; P.D = D;
+    P.post = 1.0; P.q = 0.0; P.pow_spec = 0; P.coef_mode = COEF_ZERO_WHERE_O0;
+    P.only_if = only_if; P.only_if_above = above;
+    return launch_both<float, PHI_SGN_EQ, true>(P, x1, x2, grad_x1, grad_x2, stream);
+}
 
 extern "C" int tpw_lp_backward(int dtype, int mode, const void *grad, const void *aux,
                                const void *x1, const void *x2, const void *w,

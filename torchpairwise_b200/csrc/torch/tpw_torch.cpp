@@ -243,6 +243,13 @@ struct CdistFn : torch::autograd::Function<CdistFn> {
         Tensor g1 = at::empty_like(a), g2 = at::empty_like(b);
         if (p == 0) { g1.zero_(); g2.zero_(); }
         else if (p == 2 && a.numel() > 0 && b.numel() > 0) dense_backward(TPW_LP_BWD_CDIST, g, &out, a, b, g1, g2);
+        else if (std::isinf(p) && tpw_chebyshev_backward_scratch_bytes(code_of(a), a.size(0), a.size(1), b.size(1), a.size(2)) > 0) {
+            // Chebyshev: find the attaining coordinate of every pair once, then scatter both gradients
+            const int64_t bytes = tpw_chebyshev_backward_scratch_bytes(code_of(a), a.size(0), a.size(1), b.size(1), a.size(2));
+            Tensor scratch = at::empty({bytes}, a.options().dtype(at::kByte));
+            TPW_CALL(tpw_chebyshev_backward_ws(g.data_ptr(), out.data_ptr(), a.data_ptr(), b.data_ptr(), g1.data_ptr(), g2.data_ptr(),
+                                               scratch.data_ptr(), bytes, a.size(0), a.size(1), b.size(1), a.size(2), stream_of(a)));
+        }
         else TPW_CALL(tpw_lp_backward(code_of(a), TPW_LP_BWD_CDIST, g.data_ptr(), out.data_ptr(), a.data_ptr(), b.data_ptr(), nullptr,
                                       g1.data_ptr(), g2.data_ptr(), a.size(0), a.size(1), b.size(1), a.size(2), p, stream_of(a)));
         return {finish(g1, ub, dt), finish(g2, ub, dt), Tensor()};

@@ -149,6 +149,18 @@ def _lp_forward_raw(x1c: Tensor, x2c: Tensor, w: Optional[Tensor], p: float, out
 def _lp_backward_raw(mode: int, grad: Tensor, aux: Optional[Tensor], x1c: Tensor, x2c: Tensor,
                      w: Optional[Tensor], p: float, need1: bool = True, need2: bool = True):
     B, N1, N2, D = _sizes(x1c, x2c)
+    if mode == _abi.LP_BWD_CDIST and w is None and math.isinf(p) and p > 0 and (need1 or need2):
+        # Chebyshev: find the attaining coordinate of every pair once, then scatter both gradients
+        code = _FLOAT_CODES[x1c.dtype]
+        nbytes = lib.tpw_chebyshev_backward_scratch_bytes(code, B, N1, N2, D)
+        if nbytes > 0:
+            g1 = torch.empty_like(x1c) if need1 else None
+            g2 = torch.empty_like(x2c) if need2 else None
+            scratch = torch.empty((nbytes,), dtype=torch.uint8, device=x1c.device)
+            with torch.cuda.device(x1c.device):
+                check(lib.tpw_chebyshev_backward_ws(_ptr(grad), _ptr(aux), _ptr(x1c), _ptr(x2c), _ptr(g1), _ptr(g2), _ptr(scratch),
+                                                    nbytes, B, N1, N2, D, _stream(x1c)), "tpw_chebyshev_backward_ws")
+            return g1, g2
     if w is None and (mode == _abi.LP_BWD_MATMUL or (p == 2.0 and mode in (_abi.LP_BWD_CDIST, _abi.LP_BWD_PPMINKOWSKI))):
         res = _dense_backward_tensor(mode, grad, aux, x1c, x2c, need1, need2)
         if res is not None:

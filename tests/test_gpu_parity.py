@@ -121,6 +121,38 @@ def test_hausdorff_golden(tpw, golden, case):
     close(x2.grad, G[f"{n}/gx2"], tol, msg=n + " grad_x2")
 
 
+@pytest.mark.parametrize("d", [1, 3, 4, 7, 8])
+def test_hausdorff_fused_loop_equals_exact_loop(tpw, monkeypatch, d):
+    """The hot loop that forms squared distances with fused multiply-adds and refines the few rows near the maximum
+    returns the same bits -- values and both index tensors -- as evaluating every point pair in the reference's
+    separately rounded arithmetic, on continuous clouds, on a cloud against itself (every row minimum is 0), on
+    lattice points (most rows tie) and with a caller-chosen visiting order."""
+    g = torch.Generator().manual_seed(40 + d)
+    clouds = [
+        (torch.rand(2, 2, 3000, d, generator=g), torch.rand(2, 3, 2500, d, generator=g)),
+        (torch.randint(0, 3, (1, 2, 1300, d), generator=g).float(), torch.randint(0, 3, (1, 2, 1100, d), generator=g).float() + 0.5),
+    ]
+    same = torch.rand(1, 1, 2100, d, generator=g)
+    clouds.append((same, same.clone()))
+    for x1, x2 in clouds:
+        for shuffle in (False, True):
+            res = []
+            for exact in (False, True):
+                if exact:
+                    monkeypatch.setenv("TPW_HAUSDORFF_EXACT_LOOP", "1")
+                else:
+                    monkeypatch.delenv("TPW_HAUSDORFF_EXACT_LOOP", raising=False)
+                gen = torch.Generator(device="cuda").manual_seed(5)
+                res.append(tpw.directed_hausdorff_distances(x1.cuda(), x2.cuda(), shuffle=shuffle, generator=gen if shuffle else None))
+            monkeypatch.delenv("TPW_HAUSDORFF_EXACT_LOOP", raising=False)
+            for a, b in zip(*res):
+                assert torch.equal(a, b), (d, shuffle)
+            if not shuffle:
+                o_ref, i_ref, j_ref = O.directed_hausdorff(x1.numpy(), x2.numpy())
+                assert np.array_equal(res[0][0].cpu().numpy(), o_ref)
+                assert np.array_equal(res[0][1].cpu().numpy(), i_ref) and np.array_equal(res[0][2].cpu().numpy(), j_ref)
+
+
 def test_hausdorff_shuffle_and_cdist(tpw):
     g = torch.Generator().manual_seed(3)
     x1 = torch.rand(2, 3, 40, 3, generator=g).cuda()

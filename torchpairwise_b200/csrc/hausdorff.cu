@@ -1,9 +1,9 @@
 // Directed Hausdorff distance between point sets, fused so that the [M1, M2] distance matrix is
 // never written.
 //
-// Fast path (float32, D <= 4): a CTA of 256 threads owns 1024 points of x1 for one set pair;
+// Fast path (float32, D <= 8): a CTA of 256 threads owns 1024 points of x1 for one set pair;
 // each thread keeps four of them in registers and streams the whole x2 cloud through shared
-// memory (one broadcast 128-bit load per x2 point feeds four point pairs).  Only the running row
+// memory (one broadcast 128-bit load per x2 point, two for D > 4, feeds four point pairs).  Only the running row
 // minimum is kept in the hot loop.  Row minima are packed as (float bits << 32 | visiting
 // position of m), reduced with warp shuffles, and merged across CTAs with one 64-bit atomicMax
 // per warp: the float bits of a non-negative value order like the value, and the low word makes
@@ -15,17 +15,26 @@
 // add (no FMA contraction), i.e. bit-for-bit what the reference's CPU loop computes, so the
 // selected indices agree with it whenever they are determined at all.
 //
+// With caller-provided scratch the hot loop does not pay for that: it forms the squared distance
+// with fused multiply-adds (3 subtractions, 1 multiplication, 2 fused multiply-adds and the minimum:
+// 7 operations per point pair instead of 9), which is within a few units in the last place of the
+// separately rounded value, and stores every row's approximate minimum.  The finishing kernel then
+// re-evaluates, with the exact arithmetic, only the rows whose approximate minimum lies within that
+// error of the largest one (usually one or two per set pair) and applies the tie rules to them, so
+// values and indices are still bit-identical to the exact path.
+//
 // Any other dtype / feature count runs a plain one-CTA-per-set-pair kernel with the same rules.
 #include "common.cuh"
 
 #include <math.h>
+#include <stdlib.h>
 
 namespace tpw {
 namespace {
 
 constexpr int kThreads = 256;
 constexpr int PM = 4;            // x1 points per thread
-constexpr int CHUNK = 2048;      // x2 points staged per pass (float4 each: 32 KB)
+constexpr int CHUNK_VECS = 2048; // float4 slots staged per pass (32 KB): 2048 x2 points of up to 4 features, 1024 of up to 8
 
 __device__ __forceinline__ float sqdist_exact(const float *a, const float *b, int D) {
     float d = 0.f;
@@ -50,15 +59,25 @@ struct HdParams {
     void *out;
     long long *idx1, *idx2;
     unsigned long long *keys;
+    float *rowmins;   // [pairs, M1] approximate row minima (fused path only)
     long long B, N1, N2, M1, M2, D;
     long long mtiles;
 };
 
-// keys[pair] = max over m of (bits(rowmin) << 32 | position(m))
-template <int D>
+// An upper bound on the relative difference between the fused and the separately rounded sum of D <= 8 squares
+// (each is within D roundings of the real sum, all terms non-negative), with room to spare; below kTiny the
+// relative bound gives way to an absolute one (products that underflow).
+constexpr float kFusedSlack = 3.8146973e-6f;   // 2^-18
+constexpr float kTiny = 1e-35f;
+
+// keys[pair] = max over m of (bits(rowmin) << 32 | position(m)).  FUSED: the distance is formed with fused
+// multiply-adds and every row's minimum is also stored for the refining kernel.
+template <int D, bool FUSED>
 __global__ void __launch_bounds__(kThreads)
 hausdorff_rowmin_kernel(const HdParams P) {
-    __shared__ float4 pts[CHUNK];
+    constexpr int V = (D + 3) / 4;           // float4 slots per x2 point
+    constexpr int CHUNK = CHUNK_VECS / V;
+    __shared__ float4 pts[CHUNK_VECS];
     const int tid = threadIdx.x;
     long long blk = blockIdx.x;
     const long long mt = blk % P.mtiles;
@@ -86,25 +105,29 @@ hausdorff_rowmin_kernel(const HdParams P) {
         __syncthreads();
         for (int e = tid; e < cnt; e += kThreads) {
             const float *s = x2 + (n0 + e) * D;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            v.x = s[0];
-            if (D > 1) v.y = s[1];
-            if (D > 2) v.z = s[2];
-            if (D > 3) v.w = s[3];
-            pts[e] = v;
+            float c[4 * V];
+#pragma unroll
+            for (int k = 0; k < 4 * V; ++k) c[k] = k < D ? s[k] : 0.f;
+#pragma unroll
+            for (int v = 0; v < V; ++v) pts[e * V + v] = make_float4(c[4 * v], c[4 * v + 1], c[4 * v + 2], c[4 * v + 3]);
         }
         __syncthreads();
 #pragma unroll 4
         for (int e = 0; e < cnt; ++e) {
-            const float4 v = pts[e];
-            const float c[4] = {v.x, v.y, v.z, v.w};
+            float c[4 * V];
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                const float4 t = pts[e * V + v];
+                c[4 * v] = t.x; c[4 * v + 1] = t.y; c[4 * v + 2] = t.z; c[4 * v + 3] = t.w;
+            }
 #pragma unroll
             for (int q = 0; q < PM; ++q) {
                 float d = 0.f;
 #pragma unroll
                 for (int k = 0; k < D; ++k) {
                     const float diff = __fsub_rn(px[q][k], c[k]);
-                    d = __fadd_rn(d, __fmul_rn(diff, diff));
+                    if (FUSED) d = k == 0 ? __fmul_rn(diff, diff) : __fmaf_rn(diff, diff, d);
+                    else d = __fadd_rn(d, __fmul_rn(diff, diff));
                 }
                 rowmin[q] = fminf(rowmin[q], d);
             }
@@ -115,6 +138,7 @@ hausdorff_rowmin_kernel(const HdParams P) {
 #pragma unroll
     for (int q = 0; q < PM; ++q) {
         if (mm[q] < P.M1) {
+            if (FUSED) P.rowmins[pair * P.M1 + mm[q]] = rowmin[q];
             const unsigned long long pos =
                 (unsigned long long)(P.order1 ? P.order1[b * P.M1 + mm[q]] : mm[q]);
             const unsigned long long kq = ((unsigned long long)__float_as_uint(rowmin[q]) << 32) | (pos & 0xffffffffull);
@@ -189,6 +213,99 @@ hausdorff_finish_kernel(const HdParams P) {
     }
 }
 
+// Fused path: one CTA per set pair.  Every row whose approximate minimum could be the exact maximum is re-evaluated with
+// the separately rounded arithmetic by one warp (lanes over n, first visited n on ties); the largest exact minimum wins,
+// the last visited m on ties.
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+hausdorff_refine_kernel(const HdParams P) {
+    constexpr int kWarps = kThreads / 32;
+    __shared__ unsigned long long s_row[kWarps], s_n[kWarps];
+    __shared__ long long s_m[kWarps];
+    __shared__ long long s_nstar;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const long long pair = blockIdx.x;
+    const long long j = pair % P.N2;
+    const long long bi = pair / P.N2;
+    const long long b = bi / P.N1;
+    const float *x1 = reinterpret_cast<const float *>(P.x1) + bi * P.M1 * D;
+    const float *x2 = reinterpret_cast<const float *>(P.x2) + (b * P.N2 + j) * P.M2 * D;
+    const float *rm = P.rowmins + pair * P.M1;
+    const unsigned long long key = P.keys[pair];
+    const float amax = __uint_as_float((unsigned int)(key >> 32));
+    const unsigned int pos_max = (unsigned int)(key & 0xffffffffull);
+    // An approximate minimum of exactly 0 means every difference squared to 0, in either arithmetic: all rows then
+    // tie at 0 and the last visited one, which the key already names, wins.  Otherwise a row can hold the exact
+    // maximum only if its approximate minimum is within the rounding slack of the largest approximate minimum.
+    const bool all_zero = amax == 0.f;
+    const float lower = amax * (1.f - kFusedSlack) - kTiny;
+
+    unsigned long long wrow = 0ull, wn = ~0ull;   // best (bits(min) << 32 | position(m)) of this warp, its n key
+    long long wm = -1;
+    for (long long base = (long long)warp * 32; base < P.M1; base += kThreads) {
+        const long long m = base + lane;
+        unsigned int pos = 0;
+        bool cand = false;
+        if (m < P.M1) {
+            pos = (unsigned int)(P.order1 ? P.order1[b * P.M1 + m] : m);
+            cand = all_zero ? (pos == pos_max) : (rm[m] >= lower);
+        }
+        unsigned int todo = __ballot_sync(0xffffffffu, cand);
+        while (todo) {
+            const int src = __ffs(todo) - 1;
+            todo &= todo - 1;
+            const long long mc = base + src;
+            const unsigned int posc = __shfl_sync(0xffffffffu, pos, src);
+            float a[D];
+#pragma unroll
+            for (int k = 0; k < D; ++k) a[k] = x1[mc * D + k];
+            unsigned long long mine = ~0ull;
+            for (long long n = lane; n < P.M2; n += 32) {
+                float c[D];
+#pragma unroll
+                for (int k = 0; k < D; ++k) c[k] = x2[n * D + k];
+                const float d = sqdist_exact(a, c, D);
+                if (d == d) {   // a NaN distance never lowers a minimum
+                    const unsigned long long p2 = (unsigned long long)(P.order2 ? P.order2[b * P.M2 + n] : n);
+                    const unsigned long long kq = ((unsigned long long)__float_as_uint(d) << 32) | (p2 & 0xffffffffull);
+                    mine = kq < mine ? kq : mine;
+                }
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const unsigned long long other = __shfl_xor_sync(0xffffffffu, mine, off);
+                mine = other < mine ? other : mine;
+            }
+            // a row without any comparable distance has the minimum +inf, as in the streaming kernel
+            const unsigned int vbits = mine == ~0ull ? 0x7f800000u : (unsigned int)(mine >> 32);
+            const unsigned long long rkey = ((unsigned long long)vbits << 32) | posc;
+            if (wm < 0 || rkey > wrow) { wrow = rkey; wn = mine; wm = mc; }
+        }
+    }
+    if (lane == 0) { s_row[warp] = wrow; s_n[warp] = wn; s_m[warp] = wm; }
+    __syncthreads();
+    int bw = -1;
+    for (int w = 0; w < kWarps; ++w)
+        if (s_m[w] >= 0 && (bw < 0 || s_row[w] > s_row[bw])) bw = w;
+    if (bw < 0) {   // cannot happen for M1 > 0: the row the key names is always a candidate
+        if (tid == 0) { reinterpret_cast<float *>(P.out)[pair] = sqrtf(amax); P.idx1[pair] = 0; P.idx2[pair] = 0; }
+        return;
+    }
+    const unsigned int npos = (unsigned int)(s_n[bw] & 0xffffffffull);
+    if (tid == 0) s_nstar = (P.order2 || s_n[bw] == ~0ull) ? 0 : (long long)npos;
+    __syncthreads();
+    if (P.order2 && s_n[bw] != ~0ull) {
+        for (long long n = tid; n < P.M2; n += kThreads)
+            if ((unsigned int)P.order2[b * P.M2 + n] == npos) s_nstar = n;
+        __syncthreads();
+    }
+    if (tid == 0) {
+        reinterpret_cast<float *>(P.out)[pair] = sqrtf(__uint_as_float((unsigned int)(s_row[bw] >> 32)));
+        P.idx1[pair] = s_m[bw];
+        P.idx2[pair] = s_nstar;
+    }
+}
+
 // Plain path: any dtype, any D.  One CTA per set pair; thread t scans rows m = t, t+256, ...
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
@@ -259,6 +376,7 @@ __global__ void hausdorff_backward_kernel(const T *grad, const T *out, const lon
     }
 }
 
+// P.rowmins != NULL selects the fused hot loop with the refining kernel, NULL the exact hot loop.
 template <int D>
 int launch_fast(HdParams P, cudaStream_t s) {
     const long long pairs = P.B * P.N1 * P.N2;
@@ -266,7 +384,14 @@ int launch_fast(HdParams P, cudaStream_t s) {
     const long long blocks = pairs * P.mtiles;
     TPW_CHECK_ARG(blocks < (1ll << 31), "hausdorff: too many blocks");
     TPW_CUDA_OK(cudaMemsetAsync(P.keys, 0, (size_t)pairs * sizeof(unsigned long long), s));
-    hausdorff_rowmin_kernel<D><<<(unsigned)blocks, kThreads, 0, s>>>(P);
+    if (P.rowmins) {
+        hausdorff_rowmin_kernel<D, true><<<(unsigned)blocks, kThreads, 0, s>>>(P);
+        TPW_LAUNCH_OK("hausdorff_rowmin_kernel");
+        hausdorff_refine_kernel<D><<<(unsigned)pairs, kThreads, 0, s>>>(P);
+        TPW_LAUNCH_OK("hausdorff_refine_kernel");
+        return TPW_OK;
+    }
+    hausdorff_rowmin_kernel<D, false><<<(unsigned)blocks, kThreads, 0, s>>>(P);
     TPW_LAUNCH_OK("hausdorff_rowmin_kernel");
     hausdorff_finish_kernel<D><<<(unsigned)pairs, kThreads, 0, s>>>(P);
     TPW_LAUNCH_OK("hausdorff_finish_kernel");
@@ -278,10 +403,11 @@ int launch_fast(HdParams P, cudaStream_t s) {
 
 using namespace tpw;
 
+// one 8-byte key per set pair, then one float per x1 point of every set pair (the approximate row minima)
 extern "C" int64_t tpw_hausdorff_scratch_bytes(int64_t B, int64_t N1, int64_t N2, int64_t M1) {
-    (void)M1;
     if (B <= 0 || N1 <= 0 || N2 <= 0) return 0;
-    return B * N1 * N2 * (int64_t)sizeof(unsigned long long);
+    const int64_t pairs = B * N1 * N2;
+    return pairs * (int64_t)sizeof(unsigned long long) + (M1 > 0 ? (pairs * M1 * 4 + 7) / 8 * 8 : 0);
 }
 
 extern "C" int tpw_hausdorff_forward(int dtype, const void *x1, const void *x2,
@@ -310,14 +436,19 @@ extern "C" int tpw_hausdorff_forward(int dtype, const void *x1, const void *x2,
     P.keys = reinterpret_cast<unsigned long long *>(scratch);
     P.B = B; P.N1 = N1; P.N2 = N2; P.M1 = M1; P.M2 = M2; P.D = D;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == TPW_F32 && D <= 4) {
+    if (dtype == TPW_F32 && D <= 8) {
         TPW_CHECK_ARG(scratch != nullptr, "tpw_hausdorff_forward: scratch is NULL");
         TPW_CHECK_ARG((reinterpret_cast<uintptr_t>(scratch) & 7u) == 0, "tpw_hausdorff_forward: scratch must be 8-byte aligned");
+        if (!getenv("TPW_HAUSDORFF_EXACT_LOOP")) P.rowmins = reinterpret_cast<float *>(P.keys + pairs);
         switch (D) {
             case 1: return launch_fast<1>(P, s);
             case 2: return launch_fast<2>(P, s);
             case 3: return launch_fast<3>(P, s);
-            default: return launch_fast<4>(P, s);
+            case 4: return launch_fast<4>(P, s);
+            case 5: return launch_fast<5>(P, s);
+            case 6: return launch_fast<6>(P, s);
+            case 7: return launch_fast<7>(P, s);
+            default: return launch_fast<8>(P, s);
         }
     }
     if (dtype == TPW_F32) hausdorff_plain_kernel<float><<<(unsigned)pairs, kThreads, 0, s>>>(P);
@@ -425,15 +556,20 @@ extern "C" int tpw_hausdorff_forward_static(int dtype, const void *x1, const voi
     P.idx2 = reinterpret_cast<long long *>(idx2);
     P.B = B; P.N1 = N1; P.N2 = N2; P.M1 = M1; P.M2 = M2; P.D = D;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == TPW_F32 && D <= 4) {
+    if (dtype == TPW_F32 && D <= 8) {
         int st = resolve_static_keys(&P.keys);
         if (st != TPW_OK) return st;
-        // launch_fast clears the first `pairs` keys on the stream before the kernels use them
+        // launch_fast clears the first `pairs` keys on the stream before the kernels use them; without room for
+        // the approximate row minima (P.rowmins stays NULL) it evaluates every point pair in the exact arithmetic
         switch (D) {
             case 1: return launch_fast<1>(P, s);
             case 2: return launch_fast<2>(P, s);
             case 3: return launch_fast<3>(P, s);
-            default: return launch_fast<4>(P, s);
+            case 4: return launch_fast<4>(P, s);
+            case 5: return launch_fast<5>(P, s);
+            case 6: return launch_fast<6>(P, s);
+            case 7: return launch_fast<7>(P, s);
+            default: return launch_fast<8>(P, s);
         }
     }
     // the one-CTA-per-pair kernel keeps its state in shared memory and needs no scratch at all

@@ -375,6 +375,22 @@ TPW_API int tpw_bool_metric_forward(int metric, const uint32_t *x1_words, const 
                             int64_t B, int64_t N1, int64_t N2, int64_t D, int64_t words_per_row,
                             tpw_stream_t stream);
 
+/*
+ * The same metrics with the pair counts n11 = |x & y| taken on the tensor cores: the one-byte booleans x1
+ * [B,N1,D], x2 [B,N2,D] (0 / 1, as they lie in memory; 16-byte aligned, D a multiple of 16) are the unsigned
+ * 8-bit operands of tcgen05.mma.kind::i8, whose 32-bit integer accumulators hold the counts exactly, and the
+ * epilogue is the one of tpw_bool_metric_forward, so the float32 output is bit-identical to it.  The popcount
+ * tile is bound by the POPC issue rate; this kernel by the operand stream from L2 and the output write.
+ * x1_popcount / x2_popcount are the row counts tpw_bitpack produces.  tpw_bool_metric_tc_eligible returns 1 for
+ * the problems this entry serves (rows of more than 128 and fewer than 2^23 features, at least 128 x 256 pairs per batch, a large
+ * enough contraction; TPW_DISABLE_BOOL_TC=1 turns it off), 0 when tpw_bool_metric_forward is to be used.
+ * Replaces the same reference code as tpw_bool_metric_forward.
+ */
+TPW_API int tpw_bool_metric_tc_eligible(int64_t B, int64_t N1, int64_t N2, int64_t D);
+TPW_API int tpw_bool_metric_forward_tc(int metric, const uint8_t *x1, const uint8_t *x2,
+                               const int32_t *x1_popcount, const int32_t *x2_popcount, float *out,
+                               int64_t B, int64_t N1, int64_t N2, int64_t D, tpw_stream_t stream);
+
 enum tpw_cmp_op { TPW_CMP_EQ = 0, TPW_CMP_NE = 1 };
 enum tpw_cmp_reduction { TPW_RED_SUM = 0, TPW_RED_MEAN = 1 };
 

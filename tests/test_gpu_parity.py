@@ -121,6 +121,51 @@ def test_hausdorff_golden(tpw, golden, case):
     close(x2.grad, G[f"{n}/gx2"], tol, msg=n + " grad_x2")
 
 
+@pytest.mark.parametrize("shape", [(1, 1000, 1100, 256), (2, 700, 520, 400), (1, 130, 4100, 1024), (1, 2100, 1300, 144), (1, 300, 900, 1200)])
+def test_boolean_tensor_core_counts_equal_popcount_counts(tpw, monkeypatch, shape):
+    """The boolean family with the pair counts taken on the tensor cores (8-bit integer contraction of the 0 / 1 bytes)
+    returns, for every metric, exactly the bits of the popcount kernel, which the golden vectors pin to the
+    reference: ragged row counts, feature counts that are not a multiple of the 128-feature step, batches, a set
+    against itself, and degenerate all-zero / all-one rows (the 0/0 branches)."""
+    from torchpairwise_b200 import _abi
+    b, n1, n2, d = shape
+    assert _abi.lib.tpw_bool_metric_tc_eligible(b, n1, n2, d) == 1
+    g = torch.Generator().manual_seed(n1 + n2 + d)
+    x1 = (torch.rand(b, n1, d, generator=g) < 0.1).cuda()
+    x2 = (torch.rand(b, n2, d, generator=g) < 0.3).cuda()
+    x1[:, 0] = False
+    x2[:, 0] = False
+    x1[:, 1] = True
+    x2[:, 1] = True
+    if b == 1:
+        x1, x2 = x1[0], x2[0]
+    names = ["hamming", "jaccard", "kulsinski", "kulczynski1", "yule", "dice", "rogerstanimoto", "russellrao", "sokalmichener", "sokalsneath"]
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        for name in names:
+            fn = getattr(tpw, name + "_distances")
+            monkeypatch.delenv("TPW_DISABLE_BOOL_TC", raising=False)
+            got = fn(x1, x2)
+            got_self = fn(x1)
+            monkeypatch.setenv("TPW_DISABLE_BOOL_TC", "1")
+            ref, ref_self = fn(x1, x2), fn(x1)
+            monkeypatch.delenv("TPW_DISABLE_BOOL_TC", raising=False)
+            assert bool(((got == ref) | (got.isnan() & ref.isnan())).all()), name
+            assert bool(((got_self == ref_self) | (got_self.isnan() & ref_self.isnan())).all()), name + " (self)"
+        for name in ("pwand_sum", "pwor_sum", "pwxor_sum", "pweq_sum", "pwne_sum", "pweq_mean", "pwne_mean"):
+            fn = getattr(tpw, name)
+            got = fn(x1, x2)
+            monkeypatch.setenv("TPW_DISABLE_BOOL_TC", "1")
+            ref = fn(x1, x2)
+            monkeypatch.delenv("TPW_DISABLE_BOOL_TC", raising=False)
+            assert torch.equal(got, ref), name
+    # against the oracle's integer counts directly
+    a, c = (x1, x2) if x1.dim() == 2 else (x1[0], x2[0])
+    assert np.array_equal(tpw.jaccard_distances(a, c).cpu().numpy(), O.boolean_metric("jaccard", a.cpu().numpy(), c.cpu().numpy()))
+    assert _abi.lib.tpw_bool_metric_tc_eligible(1, 64, 4096, 1024) == 0      # fewer rows than a tile
+    assert _abi.lib.tpw_bool_metric_tc_eligible(1, 1000, 1100, 250) == 0     # rows not 16-byte aligned
+
+
 @pytest.mark.parametrize("d", [1, 3, 4, 7, 8])
 def test_hausdorff_fused_loop_equals_exact_loop(tpw, monkeypatch, d):
     """The hot loop that forms squared distances with fused multiply-adds and refines the few rows near the maximum

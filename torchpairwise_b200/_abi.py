@@ -75,6 +75,8 @@ SIGNATURES = {
     "tpw_cosine_backward_finish": (_I, [_I, _P, _P, _P, _P, _L, _L, _P]),
     "tpw_bitpack": (_I, [_P, _P, _P, _L, _L, _L, _P]),
     "tpw_bool_metric_forward": (_I, [_I, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P]),
+    "tpw_bool_metric_tc_eligible": (_I, [_L, _L, _L, _L]),
+    "tpw_bool_metric_forward_tc": (_I, [_I, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P]),
     "tpw_cmp_reduce_forward": (_I, [_I, _I, _I, _P, _P, _P, _L, _L, _L, _L, _P]),
     "tpw_hausdorff_scratch_bytes": (_L, [_L, _L, _L, _L]),
     "tpw_hausdorff_forward": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P]),

@@ -113,6 +113,7 @@ static int encode_map_3d(CUtensorMap *map, const void *base, int elem_bytes,
     }
     CUtensorMapDataType dt;
     switch (elem_bytes) {
+        case 1: dt = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
         case 2: dt = CU_TENSOR_MAP_DATA_TYPE_UINT16; break;
         case 4: dt = CU_TENSOR_MAP_DATA_TYPE_UINT32; break;
         case 8: dt = CU_TENSOR_MAP_DATA_TYPE_UINT64; break;

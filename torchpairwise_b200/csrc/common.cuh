@@ -52,7 +52,7 @@ bool tma_disabled();
 int sm_count();
 
 // Builds a tiled tensor map over a dense row-major [dim2, dim1, dim0] tensor (dim0 innermost).
-// elem_bytes is 2, 4 or 8; swizzle128 selects CU_TENSOR_MAP_SWIZZLE_128B (inner box must span
+// elem_bytes is 1, 2, 4 or 8; swizzle128 selects CU_TENSOR_MAP_SWIZZLE_128B (inner box must span
 // exactly 128 bytes) or no swizzle.  Returns a tpw_status.
 int make_tensor_map_3d(CUtensorMap *map, const void *base, int elem_bytes,
                        uint64_t dim0, uint64_t dim1, uint64_t dim2,

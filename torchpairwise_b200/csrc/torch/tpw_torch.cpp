@@ -649,6 +649,15 @@ Tensor bool_metric(const Tensor &x1, const Tensor &x2, int metric) {
     } else if (out.numel() > 0) {
         auto pa = pack_bool(a);
         auto pb = x2.is_same(x1) ? pa : pack_bool(b);
+        Tensor ab = a.contiguous(), bb = x2.is_same(x1) ? ab : b.contiguous();
+        if (tpw_bool_metric_tc_eligible(B, N1, N2, D) && reinterpret_cast<uintptr_t>(ab.data_ptr()) % 16 == 0 &&
+            reinterpret_cast<uintptr_t>(bb.data_ptr()) % 16 == 0) {
+            // large problem: the counts come from the tensor cores (8-bit integer contraction of the 0 / 1 bytes)
+            TPW_CALL(tpw_bool_metric_forward_tc(metric, static_cast<const uint8_t *>(ab.data_ptr()), static_cast<const uint8_t *>(bb.data_ptr()),
+                                                static_cast<const int32_t *>(std::get<1>(pa).data_ptr()),
+                                                static_cast<const int32_t *>(std::get<1>(pb).data_ptr()), out.data_ptr<float>(),
+                                                B, N1, N2, D, stream_of(a)));
+        } else
         TPW_CALL(tpw_bool_metric_forward(metric, static_cast<const uint32_t *>(std::get<0>(pa).data_ptr()),
                                          static_cast<const uint32_t *>(std::get<0>(pb).data_ptr()),
                                          static_cast<const int32_t *>(std::get<1>(pa).data_ptr()),

@@ -657,8 +657,15 @@ def _bool_metric_raw(x1: Tensor, x2: Tensor, metric: str) -> Tensor:
         else:
             w2, p2, _ = _pack_bool(x2c)
         with torch.cuda.device(x1.device):
-            check(lib.tpw_bool_metric_forward(_abi.BOOL_METRICS[metric], _ptr(w1), _ptr(w2), _ptr(p1), _ptr(p2),
-                                              _ptr(out), B, N1, N2, D, W, _stream(x1)), "tpw_bool_metric_forward")
+            b1 = x1c.contiguous().view(torch.uint8)
+            b2 = b1 if w2 is w1 else x2c.contiguous().view(torch.uint8)
+            if lib.tpw_bool_metric_tc_eligible(B, N1, N2, D) and b1.data_ptr() % 16 == 0 and b2.data_ptr() % 16 == 0:
+                # large problem: the counts come from the tensor cores (8-bit integer contraction of the 0 / 1 bytes)
+                check(lib.tpw_bool_metric_forward_tc(_abi.BOOL_METRICS[metric], _ptr(b1), _ptr(b2), _ptr(p1), _ptr(p2),
+                                                     _ptr(out), B, N1, N2, D, _stream(x1)), "tpw_bool_metric_forward_tc")
+            else:
+                check(lib.tpw_bool_metric_forward(_abi.BOOL_METRICS[metric], _ptr(w1), _ptr(w2), _ptr(p1), _ptr(p2),
+                                                  _ptr(out), B, N1, N2, D, W, _stream(x1)), "tpw_bool_metric_forward")
     return out.squeeze(0) if unbatched else out
 
 

@@ -139,22 +139,50 @@ def hausdorff_inputs(case):
 
 
 def config_inputs(name):
-    """Row blocks of the five benchmark configurations, generated as the full configurations are
-    (CPU generator, seed 0) so that CPU and GPU see identical bits."""
+    """Row blocks of the five benchmark configurations (a row block of X against all of Y: C2 one batch and 512
+    rows, C3 / C4 1024 rows; C1 and C5 whole), generated as the full configurations are (CPU generator, seed 0)
+    so that CPU and GPU see identical bits."""
     g = torch.Generator().manual_seed(0)
     if name == "C1":
         return torch.randn(1024, 128, generator=g), torch.randn(2048, 128, generator=g)
     if name == "C2":
-        X = torch.randn(1, 256, 256, generator=g)
-        Y = torch.randn(1, 256, 256, generator=g)
-        G = torch.randn(1, 256, 256, generator=g)
+        X = torch.randn(1, 512, 256, generator=g)
+        Y = torch.randn(1, 4096, 256, generator=g)
+        G = torch.randn(1, 512, 4096, generator=g)
         return X, Y, G
     if name == "C3":
-        return torch.rand(256, 1024, generator=g) < 0.1, torch.rand(512, 1024, generator=g) < 0.1
+        return torch.rand(1024, 1024, generator=g) < 0.1, torch.rand(16384, 1024, generator=g) < 0.1
     if name == "C4":
-        return torch.randn(256, 512, generator=g), torch.randn(1024, 512, generator=g)
+        return torch.randn(1024, 512, generator=g), torch.randn(16384, 512, generator=g)
     if name == "C5":
-        X = torch.rand(4, 2048, 3, generator=g) * 2 - 1
-        Y = X + 0.05 * torch.randn(4, 2048, 3, generator=g)
+        X = torch.rand(64, 8192, 3, generator=g) * 2 - 1
+        Y = X + 0.05 * torch.randn(64, 8192, 3, generator=g)
         return X[:, None], Y[:, None]
     raise ValueError(name)
+
+
+# float16 / bfloat16 inputs through the operators whose reference kernels accumulate in the narrow type itself
+NARROW_CASES = [
+    {"name": "f16_40x30x70", "dtype": torch.float16, "x1": (40, 70), "x2": (30, 70), "seed": 31},
+    {"name": "bf16_40x30x70", "dtype": torch.bfloat16, "x1": (40, 70), "x2": (30, 70), "seed": 32},
+    {"name": "f16_b2_33x17x260", "dtype": torch.float16, "x1": (2, 33, 260), "x2": (2, 17, 260), "seed": 33},
+]
+NARROW_METRICS = [
+    {"name": "ppminkowski_p2", "fn": "_ppminkowski", "kw": {"p": 2.0}},
+    {"name": "ppminkowski_p3", "fn": "_ppminkowski", "kw": {"p": 3.0}},
+    {"name": "sqeuclidean", "fn": "sqeuclidean_distances"},
+    {"name": "euclidean", "fn": "euclidean_distances"},
+    {"name": "cosine", "fn": "cosine_distances"},
+    {"name": "wminkowski_p2", "fn": "_wminkowski", "kw": {"p": 2.0}, "weighted": True},
+]
+
+
+def narrow_inputs(case):
+    g = torch.Generator().manual_seed(case["seed"])
+    dt = case["dtype"]
+    x1 = torch.randn(*case["x1"], generator=g).to(dt)
+    x2 = torch.randn(*case["x2"], generator=g).to(dt)
+    w = (torch.rand(case["x1"][-1], generator=g) + 0.5).to(dt)
+    if len(case["x1"]) == 3:
+        w = w.expand(case["x1"][0], -1).contiguous()
+    return x1, x2, w

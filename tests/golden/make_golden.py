@@ -22,8 +22,8 @@ import torch
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
 sys.path.insert(0, str(HERE.parent))
-from cases import (BOOL_METRICS, FLOAT_CASES, FLOAT_METRICS, HAUSDORFF_CASES, config_inputs, float_inputs,  # noqa: E402
-                   bool_inputs, hausdorff_inputs, BOOL_CASES, call_metric)
+from cases import (BOOL_METRICS, FLOAT_CASES, FLOAT_METRICS, HAUSDORFF_CASES, NARROW_CASES, NARROW_METRICS, config_inputs,  # noqa: E402
+                   float_inputs, bool_inputs, hausdorff_inputs, narrow_inputs, BOOL_CASES, call_metric)
 
 torch.ops.load_library(str(ROOT / "oracle" / "_ref" / "torchpairwise_ref.so"))
 T = torch.ops.torchpairwise
@@ -101,7 +101,7 @@ def config_golden():
     for name in ("euclidean_distances", "manhattan_distances", "cosine_distances", "chebyshev_distances",
                  "sqeuclidean_distances", "correlation_distances"):
         out[f"C1/{name}"] = npy(getattr(T, name)(X, Y)[::128])
-    # C2 shape, one batch and a 256-row block: minkowski p=3 and chebyshev, forward + backward
+    # C2: batch 0, rows 0:512 against all 4096 columns: minkowski p=3 and chebyshev, forward + backward (sub-sampled)
     X, Y, G = config_inputs("C2")
     out["C2/checksum"] = np.array([X.double().sum().item(), Y.double().sum().item(), G.double().sum().item()])
     for name, fn in (("minkowski3", lambda a, b: T.minkowski_distances(a, b, 3.0)),
@@ -110,20 +110,20 @@ def config_golden():
         b = Y.clone().requires_grad_(True)
         res = fn(a, b)
         res.backward(G)
-        out[f"C2/{name}/out"] = npy(res[:, ::16, ::4])
+        out[f"C2/{name}/out"] = npy(res[:, ::8, ::16])
         out[f"C2/{name}/gx1"] = npy(a.grad[:, ::8])
-        out[f"C2/{name}/gx2"] = npy(b.grad[:, ::8])
-    # C3 shape: bool X[256,1024], Y[512,1024]
+        out[f"C2/{name}/gx2"] = npy(b.grad[:, ::16])
+    # C3: bool X rows 0:1024 against all 16384 rows of Y (sub-sampled)
     X, Y = config_inputs("C3")
     out["C3/checksum"] = np.array([X.double().sum().item(), Y.double().sum().item()])
-    out["C3/hamming_distances"] = npy(T.hamming_distances(X, Y)[::4, ::4])
-    out["C3/jaccard_distances"] = npy(T.jaccard_distances(X, Y)[::4, ::4])
-    # C4 shape: X[256,512], Y[1024,512]
+    out["C3/hamming_distances"] = npy(T.hamming_distances(X, Y)[::16, ::64])
+    out["C3/jaccard_distances"] = npy(T.jaccard_distances(X, Y)[::16, ::64])
+    # C4: X rows 0:1024 against all 16384 rows of Y (sub-sampled)
     X, Y = config_inputs("C4")
     out["C4/checksum"] = np.array([X.double().sum().item(), Y.double().sum().item()])
-    out["C4/sqeuclidean_distances"] = npy(T.sqeuclidean_distances(X, Y)[::8, ::8])
-    out["C4/cosine_distances"] = npy(T.cosine_distances(X, Y)[::8, ::8])
-    # C5 shape: x1, x2 [4,1,2048,3]
+    out["C4/sqeuclidean_distances"] = npy(T.sqeuclidean_distances(X, Y)[::16, ::64])
+    out["C4/cosine_distances"] = npy(T.cosine_distances(X, Y)[::16, ::64])
+    # C5 whole: x1, x2 [64,1,8192,3]
     X, Y = config_inputs("C5")
     out["C5/checksum"] = np.array([X.double().sum().item(), Y.double().sum().item()])
     a = X.clone().requires_grad_(True)
@@ -285,11 +285,34 @@ def haversine_golden():
     print("haversine.npz", len(out), "arrays")
 
 
+def narrow_golden():
+    """float16 / bfloat16 inputs: the reference's own result (its kernels accumulate in the narrow type) and the same
+    operator evaluated in float64 on the same narrow inputs, so that a test can place another implementation between them."""
+    out = {}
+    for case in NARROW_CASES:
+        x1, x2, w = narrow_inputs(case)
+        n = case["name"]
+        out[f"{n}/x1"], out[f"{n}/x2"], out[f"{n}/w"] = npy(x1.float()), npy(x2.float()), npy(w.float())
+        for metric in NARROW_METRICS:
+            if metric.get("weighted") and x1.dim() == 3:
+                continue  # the reference rejects batched weights unless N1 == D (its shape check compares the wrong axis)
+            out[f"{n}/{metric['name']}/ref"] = npy(call_metric(T, metric, x1, x2, w if metric.get("weighted") else None).float())
+            out[f"{n}/{metric['name']}/f64"] = npy(call_metric(T, metric, x1.double(), x2.double(), w.double() if metric.get("weighted") else None))
+    p, q, _ = hausdorff_inputs({"seed": 34, "dtype": torch.float32, "x1": (2, 2, 60, 3), "x2": (2, 3, 45, 3)})
+    p, q = p.half(), q.half()
+    r = T.directed_hausdorff_distances(p, q)
+    out["hd_f16/x1"], out["hd_f16/x2"] = npy(p.float()), npy(q.float())
+    out["hd_f16/ref"] = npy(r[0].float())
+    out["hd_f16/f64"] = npy(T.directed_hausdorff_distances(p.double(), q.double())[0])
+    np.savez_compressed(HERE / "narrow.npz", **out)
+    print("narrow.npz", len(out), "arrays")
+
+
 if __name__ == "__main__":
     torch.set_num_threads(8)
     which = set(sys.argv[1:])
     for name, fn in (("float", float_golden), ("bool", bool_golden), ("hausdorff", hausdorff_golden), ("configs", config_golden),
                      ("extras", extras_golden), ("composed", composed_golden), ("pair_sums", pair_sums_golden),
-                     ("jensenshannon", jensenshannon_golden), ("haversine", haversine_golden)):
+                     ("jensenshannon", jensenshannon_golden), ("haversine", haversine_golden), ("narrow", narrow_golden)):
         if not which or name in which:
             fn()

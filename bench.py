@@ -292,8 +292,20 @@ def run_sharded_dense(T, tpw, dev, rank, world, barrier, max_over_ranks, gpu_ms)
         with torch.no_grad():
             slab[0] = T.sqeuclidean_distances(Xs, Ys)
 
-    ms_step = timed(sharded_step)
+    def panel_step():
+        # Y crosses NVLink in two row chunks; the contraction of the first column panel runs while the second chunk lands
+        slab[0] = sharding.sharded_pairwise_panels(T.sqeuclidean_distances, Xs, Ys, src=0, panels=2)
+
+    ms_single = timed(sharded_step)
     ms_kernel = timed(kernel_only)  # Y is local on every rank after the broadcasts above
+    ms_step = timed(panel_step) if world > 1 else ms_single
+    if world > 1:   # the panels against the one-piece slab, bit for bit
+        panels = slab[0]
+        sharded_step()
+        same = bool(torch.equal(torch.cat(panels, -1), slab[0]))
+        del panels
+    else:
+        same = True
     sharded_step()
     blk = slice(max(0, (hi - lo) - 256), hi - lo)
     xd, yd = Xs[blk].double(), Ys.double()
@@ -301,6 +313,7 @@ def run_sharded_dense(T, tpw, dev, rank, world, barrier, max_over_ranks, gpu_ms)
     err = float(((slab[0][blk].double() - ref).abs() / (ATOL + RTOL * ref.abs())).max())
     del xd, yd, ref
     worst = max_over_ranks(err)
+    all_same = bool(max_over_ranks(0.0 if same else 1.0) == 0.0)   # a collective: every rank calls it
     slab[0] = None
     t1 = ms_step
     if world > 1:
@@ -315,9 +328,11 @@ def run_sharded_dense(T, tpw, dev, rank, world, barrier, max_over_ranks, gpu_ms)
     if rank != 0:
         return None
     return {"workload": "C4 sqeuclidean X[131072,512] row-sharded (each rank generates its block in place), Y[16384,512] "
-                        "broadcast from rank 0 every step (NCCL)" if world > 1 else
+                        "broadcast from rank 0 every step (NCCL) in two row chunks, the second under the first column panel's kernel" if world > 1 else
                         "C4 sqeuclidean X[131072,512] x Y[16384,512] on one GPU (nothing to broadcast)",
-            "ms_per_step": ms_step, "kernel_only_ms": ms_kernel, "Gpairs_s": rows_total * cols / (ms_step * 1e-3) / 1e9,
+            "ms_per_step": ms_step, "ms_per_step_one_broadcast": ms_single, "kernel_only_ms": ms_kernel,
+            "panels_equal_one_piece_slab": all_same,
+            "Gpairs_s": rows_total * cols / (ms_step * 1e-3) / 1e9,
             "one_gpu_ms_same_run": t1, "efficiency_vs_n1": t1 / (world * ms_step),
             "kernel_only_efficiency_vs_n1": t1 / (world * ms_kernel),
             "slab_rows_rank0": hi - lo, "scaling": "strong",
@@ -412,9 +427,12 @@ def run_configs(T, R, dev, gpu_ms, peaks, X, Y, G, hosts, args):
             ref = cpu_fwd_bwd(getattr(R, name), X1, Y1, G1)
             e["cpu_Gpairs_s_fwd_bwd"] = rate(n, cpu_time(lambda: cpu_fwd_bwd(getattr(R, name), X1, Y1, G1), n=3, warm=1))
             fb()
-            par["C1/" + name] = {"fwd": err_over_tol(op(a.detach(), b.detach()), ref[0]),
+            got = op(a.detach(), b.detach())
+            exact = getattr(R, name)(X1.double(), Y1.double())   # the same operator in float64: which side an error is on
+            par["C1/" + name] = {"fwd": err_over_tol(got, ref[0]),
                                  "grad_x1": err_over_tol(a.grad, ref[1], grad_scale(ref[1])),
-                                 "grad_x2": err_over_tol(b.grad, ref[2], grad_scale(ref[2]))}
+                                 "grad_x2": err_over_tol(b.grad, ref[2], grad_scale(ref[2])),
+                                 "fwd_gpu_vs_float64": err_over_tol(got, exact), "fwd_cpu_reference_vs_float64": err_over_tol(ref[0], exact)}
         cfg["C1/" + name] = e
     # ---- C2: the resident benchmark tensors; CPU on batch 0, rows 0:512 ---------------------------------------------
     rows = 512
@@ -597,7 +615,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     tpw.load_torch_ops()
     T = torch.ops.torchpairwise
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # a short collective timeout: a rank that falls out of step ends the job in minutes, not in the default ten
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
 
     def barrier():
         if world > 1:

@@ -498,12 +498,19 @@ TPW_API int tpw_hausdorff_backward(int dtype, const void *grad, const void *out,
  * take the device-wide stall an allocation may cause.  Same inputs, outputs and results as
  * tpw_hausdorff_forward, no scratch argument: the 8-byte key per set pair lives in a fixed
  * array inside the library's device image (tpw_hausdorff_static_max_pairs() * 8 bytes = 512 KiB,
- * held by every GPU that loads the library until the process exits).  The call itself performs
- * no allocation of any kind.
+ * held by every GPU that loads the library until the process exits).  After a first call on the
+ * device, a call performs no allocation of any kind.  Because there is no room for per-row minima
+ * the hot loop evaluates every point pair in the reference's separately rounded arithmetic; the
+ * results are bit-identical to tpw_hausdorff_forward.
  *   - Limit: B*N1*N2 <= tpw_hausdorff_static_max_pairs() (65536); larger problems are refused
  *     with TPW_ERR_INVALID and a message, nothing is launched.
  *   - The first call on each device looks up the array's device address (a host-side query, not
- *     a stream operation); make that first call outside any stream capture.
+ *     a stream operation).  Under the runtime's lazy loading that lookup may load this library's
+ *     device image on the device -- memory for the image, the array included, and an implicit
+ *     synchronisation -- so make one warm-up call per device at start-up, outside any stream capture
+ *     and before the region in which nothing may allocate; the guarantee holds from then on.
+ *   - The looked-up address is cached per device ordinal; cudaDeviceReset invalidates it, and a
+ *     host that resets a device must not call into this library on that device again.
  *   - All calls on a device share the one array; the part a call uses is cleared on `stream`
  *     before its kernels run, but two calls whose kernels may overlap on the GPU (different
  *     streams, or different host threads) would race on it: keep them on one stream or serialise.

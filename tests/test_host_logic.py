@@ -122,6 +122,12 @@ def _sharded_worker(rank, world, port, n1, n2, d):
         torch.cdist(xr, yr, p=1.0).backward(up)
         assert torch.allclose(a.grad, xr.grad[lo:hi])
         assert torch.allclose(b.grad, yr.grad), "grad_x2 must be the sum over all row blocks"
+        # the same slab as column panels, x2 broadcast in row chunks that are queued at once
+        for panels in (1, 2, 3, 7):
+            buf = x2.clone() if rank == 0 else torch.zeros_like(x2)
+            parts = sharding.sharded_pairwise_panels(lambda u, v: torch.cdist(u, v, p=1.0), a.detach(), buf, src=0, panels=panels)
+            assert len(parts) == min(panels, n2) and torch.allclose(torch.cat(parts, -1), full[lo:hi])
+            assert torch.equal(buf, x2), "every rank holds the broadcast x2 afterwards"
     finally:
         dist.destroy_process_group()
 

@@ -3,6 +3,8 @@
 // give the CUDA-core kernels their roofline denominators.
 #include "common.cuh"
 
+#include <atomic>
+
 #include <mutex>
 #include <stdlib.h>
 #include <string.h>
@@ -27,16 +29,19 @@ __device__ int g_device_status_word = 0;
 
 static const int kMaxDevices = 64;
 
+// The per-device caches below are read and written from any host thread: atomic slots, and a value that every
+// thread computes identically, so a race only repeats the lookup.  A cudaDeviceReset invalidates device addresses;
+// a host that resets a device must not keep using this library on it in the same process.
 int *device_status_ptr() {
-    static int *cache[kMaxDevices] = {nullptr};
+    static std::atomic<int *> cache[kMaxDevices];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
-    if (!cache[dev]) {
-        int *p = nullptr;
+    int *p = cache[dev].load(std::memory_order_acquire);
+    if (!p) {
         if (cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_device_status_word) != cudaSuccess) return nullptr;
-        cache[dev] = p;
+        cache[dev].store(p, std::memory_order_release);
     }
-    return cache[dev];
+    return p;
 }
 
 bool tma_disabled() {
@@ -48,15 +53,15 @@ bool tma_disabled() {
 }
 
 int sm_count() {
-    static int cache[kMaxDevices] = {0};
+    static std::atomic<int> cache[kMaxDevices];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
-    if (!cache[dev]) {
-        int n = 0;
+    int n = cache[dev].load(std::memory_order_relaxed);
+    if (!n) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        cache[dev] = n;
+        cache[dev].store(n, std::memory_order_relaxed);
     }
-    return cache[dev];
+    return n;
 }
 
 typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,

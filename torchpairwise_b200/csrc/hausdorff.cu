@@ -29,6 +29,8 @@
 #include <math.h>
 #include <stdlib.h>
 
+#include <atomic>
+
 namespace tpw {
 namespace {
 
@@ -508,19 +510,26 @@ constexpr long long kStaticMaxPairs = 65536; // 512 KiB of keys
 static __device__ __align__(256) unsigned long long g_hausdorff_static_keys[kStaticMaxPairs];
 
 // `g_hausdorff_static_keys` names a host-side shadow here, not device memory; the device address
-// has to be asked for, once per device, while that device is current.
+// has to be asked for, once per device, while that device is current.  That first lookup may make the
+// runtime load this library's device image on the device (memory for the image, the 512 KiB array
+// included, and an implicit synchronisation): it belongs in the host's start-up, before the region in
+// which nothing may allocate.  The slots are atomic (any host thread may be first; all store the same
+// address).  A cudaDeviceReset invalidates the address: a host that resets a device must not call into
+// this library on it again in the same process.
 int resolve_static_keys(unsigned long long **ptr) {
-    static unsigned long long *cache[64] = {nullptr};
+    static std::atomic<unsigned long long *> cache[64];
     int dev = 0;
     TPW_CUDA_OK(cudaGetDevice(&dev));
     TPW_CHECK_ARG(dev >= 0 && dev < 64, "tpw_hausdorff_forward_static: device ordinal %d is out of range", dev);
-    if (!cache[dev]) {
+    unsigned long long *cached = cache[dev].load(std::memory_order_acquire);
+    if (!cached) {
         void *p = nullptr;
         TPW_CUDA_OK(cudaGetSymbolAddress(&p, g_hausdorff_static_keys));
         TPW_CHECK_ARG(p != nullptr, "tpw_hausdorff_forward_static: the scratch symbol resolved to NULL");
-        cache[dev] = static_cast<unsigned long long *>(p);
+        cached = static_cast<unsigned long long *>(p);
+        cache[dev].store(cached, std::memory_order_release);
     }
-    *ptr = cache[dev];
+    *ptr = cached;
     return TPW_OK;
 }
 

@@ -19,6 +19,7 @@
 #include "common.cuh"
 
 #include <math.h>
+#include <stdlib.h>
 
 namespace tpw {
 namespace {
@@ -441,6 +442,45 @@ lp_backward_kernel(const __grid_constant__ CUtensorMap map_stream, const __grid_
     }
 }
 
+// Few gradient blocks (a small problem, or few rows against many): the tile kernel would occupy a handful of SMs, one
+// CTA per 128 x 128 gradient block walking over the whole streamed dimension.  Here every gradient element has a
+// thread of its own that walks over the streamed rows in ascending order -- the same terms in the same order as the
+// tile kernel adds them, so the results are bit-identical and deterministic.  A warp holds 32 consecutive features of
+// one gradient row: the streamed operand is read in 128-byte segments, the coefficient is a broadcast.
+template <typename T, int PHI, bool NEED_AUX, bool TRANS>
+__global__ void __launch_bounds__(256) lp_backward_small_kernel(const BwdParams P) {
+    if (P.only_if && *P.only_if <= P.only_if_above) return;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= P.B * P.NR * P.D) return;
+    const long long k = idx % P.D, r = (idx / P.D) % P.NR, b = idx / (P.D * P.NR);
+    const T *stream = reinterpret_cast<const T *>(P.stream) + b * P.NS * P.D + k;
+    const T *grad = reinterpret_cast<const T *>(P.grad) + b * P.N1 * P.N2;
+    const T *aux = NEED_AUX ? reinterpret_cast<const T *>(P.aux) + b * P.N1 * P.N2 : nullptr;
+    const T x = PHI != PHI_Y ? reinterpret_cast<const T *>(P.rowop)[(b * P.NR + r) * P.D + k] : T(0);
+    const long long g0 = TRANS ? r : r * P.N2, gstep = TRANS ? P.N2 : 1;   // g[i][j]: i = r (rows) or i = s (columns)
+    const T q = (T)P.q;
+    T acc = T(0);
+    for (long long s = 0; s < P.NS; ++s) {
+        const T g = grad[g0 + s * gstep];
+        T c = g, o = T(0);
+        if (NEED_AUX) {
+            o = aux[g0 + s * gstep];
+            switch (P.coef_mode) {
+                case COEF_DIV_O: c = o == T(0) ? T(0) : b_div(g, o); break;
+                case COEF_DIV_O2: c = o == T(0) ? T(0) : b_div(g, o * o); break;
+                case COEF_DIV_POW: c = o == T(0) ? T(0) : b_div(g, b_pow(o, P.q)); break;
+                case COEF_MUL: c = g * o; break;
+                case COEF_ZERO_WHERE_O0: c = o == T(0) ? T(0) : g; break;
+                default: break;
+            }
+        }
+        bwd_accumulate<PHI, T>(acc, x, stream[s * P.D], c, o, q, P.pow_spec);
+    }
+    T v = acc * (T)P.post;
+    if (P.w) v *= reinterpret_cast<const T *>(P.w)[b * P.D + k];
+    reinterpret_cast<T *>(P.out)[idx] = v;
+}
+
 template <typename T, int PHI, bool NEED_AUX, bool TRANS>
 int launch_backward(BwdParams P, cudaStream_t stream) {
     constexpr int RR = 4;
@@ -455,6 +495,15 @@ int launch_backward(BwdParams P, cudaStream_t stream) {
     TPW_CHECK_ARG(P.N1 < (1ll << 31) && P.N2 < (1ll << 31) && P.B < (1ll << 31) && P.D < (1ll << 31),
                   "lp backward: a dimension exceeds 2^31-1");
     P.status = device_status_ptr();
+
+    // fewer gradient blocks than a third of the SMs: one thread per gradient element instead (TPW_DISABLE_SMALL_BWD=1
+    // keeps the tile kernel); the walk per thread is bounded so that a launch stays in the millisecond range
+    if (tiles * 3 < sm_count() && P.NS <= 65536 && P.B * P.NR * P.D < (1ll << 31) * 256 && !getenv("TPW_DISABLE_SMALL_BWD")) {
+        const long long n = P.B * P.NR * P.D;
+        lp_backward_small_kernel<T, PHI, NEED_AUX, TRANS><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(P);
+        TPW_LAUNCH_OK("lp_backward_small_kernel");
+        return TPW_OK;
+    }
 
     bool tma_ok = !tma_disabled() && aligned16(P.stream) && aligned16(P.grad) && (!NEED_AUX || aligned16(P.aux)) &&
                   (P.D * (long long)sizeof(T)) % 16 == 0 && (P.N2 * (long long)sizeof(T)) % 16 == 0;

@@ -88,3 +88,28 @@ def sharded_pairwise(metric: Callable[..., Tensor], x1_local: Tensor, x2: Tensor
     if replicate and dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
         x2 = replicate_x2(x2, src, group)
     return metric(x1_local, x2, **kwargs)
+
+
+def sharded_pairwise_panels(metric: Callable[..., Tensor], x1_local: Tensor, x2: Tensor, *, src: int = 0, group=None,
+                            panels: int = 2, **kwargs) -> List[Tensor]:
+    """Distances of this rank's ``x1`` block against all of ``x2``, as ``panels`` column panels
+    ``[.., N1_local, N2 / panels]`` (``torch.cat(result, -1)`` is the slab ``sharded_pairwise`` returns).
+
+    ``x2`` (unbatched, ``[N2, D]``, the owner's values on ``src`` and a buffer of the same shape elsewhere) is
+    broadcast in ``panels`` row chunks that are all queued at once; the operator runs on chunk c as soon as it
+    has landed, while chunk c + 1 is still crossing NVLink, so all but the first chunk of the broadcast hides
+    behind the kernels.  Each panel is a dense matrix of its own: the operator is called as it is, with a
+    contiguous block of ``x2`` rows.  Forward only (no gradient flows back through the broadcast); ``x2`` holds the
+    broadcast values on every rank afterwards."""
+    if x2.dim() != 2 or not x2.is_contiguous():
+        raise ValueError("sharded_pairwise_panels takes an unbatched, contiguous x2 [N2, D]")
+    bounds = [b for b in split_range(x2.size(0), max(1, panels)) if b[1] > b[0]]
+    live = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+    works = [dist.broadcast(x2[lo:hi], src=src, group=group, async_op=True) for lo, hi in bounds] if live else []
+    outs = []
+    with torch.no_grad():
+        for c, (lo, hi) in enumerate(bounds):
+            if live:
+                works[c].wait()
+            outs.append(metric(x1_local, x2[lo:hi], **kwargs))
+    return outs

@@ -10,7 +10,7 @@
 // Kernel: persistent, one CTA per SM, 320 threads -- warp 0 issues TMA (one lane), warp 1 owns tensor memory and
 // issues the MMAs (one lane), warps 2..9 drain the accumulators (TMEM lane quarter = warp % 4, column half =
 // (warp - 2) / 4).  Output tile 128 x 256; a k-step is 128 features = one 128-byte swizzled row per operand row,
-// consumed by four MMAs of K = 32; four stages of 16 KB (x1) + 32 KB (x2); two 256-column accumulators in tensor
+// consumed by four MMAs of K = 32; three stages of 16 KB (x1) + 32 KB (x2); two 256-column accumulators in tensor
 // memory, so the epilogue of tile t overlaps the MMAs of tile t + 1.  The operands are the caller's boolean
 // matrices as they lie in memory (row pitch D bytes): no packed or padded copy is made, the TMA unit zero-fills
 // rows and features past the edge, and zeros add nothing to a count.  Every CTA loads its own tiles with plain
@@ -30,17 +30,18 @@ namespace {
 constexpr int BM = 128;             // x1 rows per tile (TMEM lanes)
 constexpr int BN = 256;             // x2 rows per tile (TMEM columns per accumulator)
 constexpr int BKB = 128;            // features (bytes) per k-step
-constexpr int kStages = 4;
+constexpr int kStages = 3;
 constexpr int A_BYTES = BM * BKB;   // 16 KB
 constexpr int B_BYTES = BN * BKB;   // 32 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int OFF_BAR = kStages * STAGE_BYTES;
-// barriers: full[4], empty[4], tmem_full[2], tmem_empty[2]; then the TMEM base address and the abort flag
+// barriers: full[3], empty[3], tmem_full[2], tmem_empty[2]; then the TMEM base address and the abort flag
 constexpr int OFF_TMEM_PTR = OFF_BAR + (2 * kStages + 4) * 8;
 constexpr int OFF_ABORT = OFF_TMEM_PTR + 4;
 constexpr int OFF_STAGE = (OFF_ABORT + 4 + 127) / 128 * 128;   // per epilogue warp a 32 x 32 float staging block
 constexpr int kEpilogueWarps = 8;
-constexpr int SMEM_BYTES = OFF_STAGE + kEpilogueWarps * 4096;
+constexpr int OFF_POP = OFF_STAGE + kEpilogueWarps * 4096;      // per epilogue warp the 128 x2 row counts of its column half
+constexpr int SMEM_BYTES = OFF_POP + kEpilogueWarps * 512;
 constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
 constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr uint32_t kTmemCols = 512;
@@ -183,6 +184,27 @@ bool_count_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
             const long long tm = t % P.tiles_m;
             const long long b = t / P.tiles_m;
             const uint32_t a = tcount & 1;
+            // What the epilogue needs besides the counts depends on the tile index alone: fetch it before waiting for the
+            // accumulator, so that the L2 round trip hides behind the contraction instead of sitting in every column block.
+            const long long i = tm * BM + q * 32 + lane;
+            const bool row_ok = i < P.N1;
+            const int pa = row_ok ? __ldg(P.pop1 + b * P.N1 + i) : 0;
+            const int32_t *pb = P.pop2 + b * P.N2;
+            int32_t *popw = reinterpret_cast<int32_t *>(smem + OFF_POP + (warp - 2) * 512);
+            {
+                const long long jc = tn * BN + chalf * (BN / 2) + lane * 4;
+                int4 v = make_int4(0, 0, 0, 0);
+                if (P.vec_store && jc + 4 <= P.N2) v = __ldg(reinterpret_cast<const int4 *>(pb + jc));
+                else {
+                    if (jc + 0 < P.N2) v.x = __ldg(pb + jc + 0);
+                    if (jc + 1 < P.N2) v.y = __ldg(pb + jc + 1);
+                    if (jc + 2 < P.N2) v.z = __ldg(pb + jc + 2);
+                    if (jc + 3 < P.N2) v.w = __ldg(pb + jc + 3);
+                }
+                __syncwarp();   // the previous tile's reads of this area are done
+                *reinterpret_cast<int4 *>(popw + lane * 4) = v;
+                __syncwarp();
+            }
             if (!wait_or_abort(&tmem_full[a], (tcount >> 1) & 1, abort_flag)) {
                 *abort_flag = 1;
                 if (lane == 0 && P.status) atomicCAS(P.status, 0, (10 << 16) | 4);
@@ -190,10 +212,6 @@ bool_count_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
                 break;
             }
             tc_fence_after();
-            const long long i = tm * BM + q * 32 + lane;
-            const bool row_ok = i < P.N1;
-            const int pa = row_ok ? P.pop1[b * P.N1 + i] : 0;
-            const int32_t *pb = P.pop2 + b * P.N2;
             float *orow = P.out + (b * P.N1 + (row_ok ? i : 0)) * P.N2;
             const long long row_base = tm * BM + q * 32;
 #pragma unroll 1
@@ -207,7 +225,7 @@ bool_count_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
                     // this thread's row, staged with a 16-byte-chunk XOR swizzle ...
 #pragma unroll
                     for (int v = 0; v < 8; ++v) {
-                        const int4 nb = __ldg(reinterpret_cast<const int4 *>(pb + j0) + v);
+                        const int4 nb = *reinterpret_cast<const int4 *>(popw + (c - chalf * (BN / 64)) * 32 + 4 * v);
                         float4 o;
                         o.x = bool_epilogue<true>(METRIC, (int)r[4 * v + 0], pa, nb.x, D, P.inv_d);
                         o.y = bool_epilogue<true>(METRIC, (int)r[4 * v + 1], pa, nb.y, D, P.inv_d);
@@ -229,7 +247,7 @@ bool_count_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
 #pragma unroll
                     for (int v = 0; v < 32; ++v) {
                         const long long j = j0 + v;
-                        if (j < P.N2) orow[j] = bool_epilogue<true>(METRIC, (int)r[v], pa, __ldg(pb + j), D, P.inv_d);
+                        if (j < P.N2) orow[j] = bool_epilogue<true>(METRIC, (int)r[v], pa, popw[(c - chalf * (BN / 64)) * 32 + v], D, P.inv_d);
                     }
                 }
             }

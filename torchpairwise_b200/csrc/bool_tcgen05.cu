@@ -7,8 +7,8 @@
 // is pinned at the POPC issue rate (C3, 65536 x 16384 x 1024 bits: 7.9 ms), the integer contraction leaves only
 // the operand stream from L2 and the 4-byte output write.
 //
-// Kernel: persistent, one CTA per SM, 320 threads -- warp 0 issues TMA (one lane), warp 1 owns tensor memory and
-// issues the MMAs (one lane), warps 2..9 drain the accumulators (TMEM lane quarter = warp % 4, column half =
+// Kernel: persistent, one CTA per SM, 576 threads -- warp 0 issues TMA (one lane), warp 1 owns tensor memory and
+// issues the MMAs (one lane), warps 2..17 drain the accumulators (TMEM lane quarter = warp % 4, column quarter =
 // (warp - 2) / 4).  Output tile 128 x 256; a k-step is 128 features = one 128-byte swizzled row per operand row,
 // consumed by four MMAs of K = 32; three stages of 16 KB (x1) + 32 KB (x2); two 256-column accumulators in tensor
 // memory, so the epilogue of tile t overlaps the MMAs of tile t + 1.  The operands are the caller's boolean
@@ -39,9 +39,9 @@ constexpr int OFF_BAR = kStages * STAGE_BYTES;
 constexpr int OFF_TMEM_PTR = OFF_BAR + (2 * kStages + 4) * 8;
 constexpr int OFF_ABORT = OFF_TMEM_PTR + 4;
 constexpr int OFF_STAGE = (OFF_ABORT + 4 + 127) / 128 * 128;   // per epilogue warp a 32 x 32 float staging block
-constexpr int kEpilogueWarps = 8;
-constexpr int OFF_POP = OFF_STAGE + kEpilogueWarps * 4096;      // per epilogue warp the 128 x2 row counts of its column half
-constexpr int SMEM_BYTES = OFF_POP + kEpilogueWarps * 512;
+constexpr int kEpilogueWarps = 16;            // four per TMEM lane quarter, each draining a quarter of the columns
+constexpr int OFF_POP = OFF_STAGE + kEpilogueWarps * 4096;      // per epilogue warp the 64 x2 row counts of its column quarter
+constexpr int SMEM_BYTES = OFF_POP + kEpilogueWarps * 256;
 constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
 constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr uint32_t kTmemCols = 512;
@@ -171,9 +171,10 @@ bool_count_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
             }
         }
     } else {
-        // ---------------- epilogue: warps 2..9 ----------------
+        // ---------------- epilogue: warps 2..17 ----------------
         const int q = warp & 3;
-        const int chalf = (warp - 2) >> 2;
+        const int cpart = (warp - 2) >> 2;           // which quarter of the tile's 256 columns
+        constexpr int NCB = BN / 32 / (kEpilogueWarps / 4);   // 32-column blocks per warp and tile
         uint32_t tcount = 0;
         bool ok = true;
         const int D = (int)P.D;
@@ -190,19 +191,17 @@ bool_count_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
             const bool row_ok = i < P.N1;
             const int pa = row_ok ? __ldg(P.pop1 + b * P.N1 + i) : 0;
             const int32_t *pb = P.pop2 + b * P.N2;
-            int32_t *popw = reinterpret_cast<int32_t *>(smem + OFF_POP + (warp - 2) * 512);
+            int32_t *popw = reinterpret_cast<int32_t *>(smem + OFF_POP + (warp - 2) * 256);
             {
-                const long long jc = tn * BN + chalf * (BN / 2) + lane * 4;
-                int4 v = make_int4(0, 0, 0, 0);
-                if (P.vec_store && jc + 4 <= P.N2) v = __ldg(reinterpret_cast<const int4 *>(pb + jc));
+                const long long jc = tn * BN + cpart * (NCB * 32) + lane * 2;   // 64 counts per warp: two per lane
+                int2 v = make_int2(0, 0);
+                if (P.vec_store && jc + 2 <= P.N2) v = __ldg(reinterpret_cast<const int2 *>(pb + jc));
                 else {
                     if (jc + 0 < P.N2) v.x = __ldg(pb + jc + 0);
                     if (jc + 1 < P.N2) v.y = __ldg(pb + jc + 1);
-                    if (jc + 2 < P.N2) v.z = __ldg(pb + jc + 2);
-                    if (jc + 3 < P.N2) v.w = __ldg(pb + jc + 3);
                 }
                 __syncwarp();   // the previous tile's reads of this area are done
-                *reinterpret_cast<int4 *>(popw + lane * 4) = v;
+                *reinterpret_cast<int2 *>(popw + lane * 2) = v;
                 __syncwarp();
             }
             if (!wait_or_abort(&tmem_full[a], (tcount >> 1) & 1, abort_flag)) {
@@ -215,7 +214,7 @@ bool_count_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
             float *orow = P.out + (b * P.N1 + (row_ok ? i : 0)) * P.N2;
             const long long row_base = tm * BM + q * 32;
 #pragma unroll 1
-            for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
+            for (int c = cpart * NCB; c < (cpart + 1) * NCB; ++c) {
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + a * BN + c * 32, r);
                 tmem_ld_wait();
@@ -225,7 +224,7 @@ bool_count_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
                     // this thread's row, staged with a 16-byte-chunk XOR swizzle ...
 #pragma unroll
                     for (int v = 0; v < 8; ++v) {
-                        const int4 nb = *reinterpret_cast<const int4 *>(popw + (c - chalf * (BN / 64)) * 32 + 4 * v);
+                        const int4 nb = *reinterpret_cast<const int4 *>(popw + (c - cpart * NCB) * 32 + 4 * v);
                         float4 o;
                         o.x = bool_epilogue<true>(METRIC, (int)r[4 * v + 0], pa, nb.x, D, P.inv_d);
                         o.y = bool_epilogue<true>(METRIC, (int)r[4 * v + 1], pa, nb.y, D, P.inv_d);
@@ -247,7 +246,7 @@ bool_count_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
 #pragma unroll
                     for (int v = 0; v < 32; ++v) {
                         const long long j = j0 + v;
-                        if (j < P.N2) orow[j] = bool_epilogue<true>(METRIC, (int)r[v], pa, popw[(c - chalf * (BN / 64)) * 32 + v], D, P.inv_d);
+                        if (j < P.N2) orow[j] = bool_epilogue<true>(METRIC, (int)r[v], pa, popw[(c - cpart * NCB) * 32 + v], D, P.inv_d);
                     }
                 }
             }

@@ -465,8 +465,10 @@ TPW_API int tpw_haversine_backward(int dtype, const void *grad, const void *x1, 
  * Tie rule of the reference loop: n = first n reaching the row minimum, m = LAST m whose
  * row minimum equals the maximum.  order1/order2 (int64 [B,M1] / [B,M2], may be NULL) give
  * each point's visiting position when the caller shuffles; ties then follow visiting order.
- * `scratch` holds tpw_hausdorff_scratch_bytes() bytes (8 per set pair plus 4 per x1 point of every set
- * pair) and needs no initialisation.  The hot loop forms the squared distance with fused multiply-adds
+ * `scratch` holds tpw_hausdorff_scratch_bytes() bytes (8 per set pair plus 8 per x1 point of every set
+ * pair), 8-byte aligned, and needs no initialisation.  float64 clouds of up to 8 coordinates keep every
+ * row's exact minimum there and scan them once per set pair (TPW_HAUSDORFF_PLAIN_F64=1, or scratch ==
+ * NULL, selects the one-CTA-per-pair kernel instead; same bits).  For float32 the hot loop forms the squared distance with fused multiply-adds
  * (7 operations per point pair) and stores every row's approximate minimum there; the finishing kernel
  * re-evaluates the few rows that can hold the maximum with separately rounded multiply and add, the
  * arithmetic of the reference's CPU loop (OPS/cpu/hausdorff_kernel.cpp:30-33), so values and indices are

@@ -198,6 +198,38 @@ def test_hausdorff_fused_loop_equals_exact_loop(tpw, monkeypatch, d):
                 assert np.array_equal(res[0][1].cpu().numpy(), i_ref) and np.array_equal(res[0][2].cpu().numpy(), j_ref)
 
 
+@pytest.mark.parametrize("d", [1, 3, 8])
+def test_hausdorff_float64_streamed_equals_one_cta_per_pair(tpw, monkeypatch, d):
+    """float64 clouds of up to eight coordinates take the streamed kernels (row minima in scratch, one scan per
+    set pair); values and both index tensors equal the one-CTA-per-pair kernel's and the oracle's bit for bit,
+    also where most rows tie and with a caller-chosen visiting order."""
+    g = torch.Generator().manual_seed(70 + d)
+    clouds = [
+        (torch.rand(2, 2, 1500, d, generator=g, dtype=torch.float64), torch.rand(2, 3, 1200, d, generator=g, dtype=torch.float64)),
+        (torch.randint(0, 3, (1, 2, 700, d), generator=g).double(), torch.randint(0, 3, (1, 2, 600, d), generator=g).double() + 0.5),
+        (torch.rand(1, 1, 5, d, generator=g, dtype=torch.float64), torch.rand(1, 2, 3, d, generator=g, dtype=torch.float64)),
+    ]
+    same = torch.rand(1, 1, 900, d, generator=g, dtype=torch.float64)
+    clouds.append((same, same.clone()))
+    for x1, x2 in clouds:
+        for shuffle in (False, True):
+            res = []
+            for plain in (False, True):
+                if plain:
+                    monkeypatch.setenv("TPW_HAUSDORFF_PLAIN_F64", "1")
+                else:
+                    monkeypatch.delenv("TPW_HAUSDORFF_PLAIN_F64", raising=False)
+                gen = torch.Generator(device="cuda").manual_seed(5)
+                res.append(tpw.directed_hausdorff_distances(x1.cuda(), x2.cuda(), shuffle=shuffle, generator=gen if shuffle else None))
+            monkeypatch.delenv("TPW_HAUSDORFF_PLAIN_F64", raising=False)
+            for a, b in zip(*res):
+                assert torch.equal(a, b), (d, shuffle)
+            if not shuffle:
+                o_ref, i_ref, j_ref = O.directed_hausdorff(x1.numpy(), x2.numpy())
+                assert np.array_equal(res[0][0].cpu().numpy(), o_ref)
+                assert np.array_equal(res[0][1].cpu().numpy(), i_ref) and np.array_equal(res[0][2].cpu().numpy(), j_ref)
+
+
 def test_hausdorff_shuffle_and_cdist(tpw):
     g = torch.Generator().manual_seed(3)
     x1 = torch.rand(2, 3, 40, 3, generator=g).cuda()

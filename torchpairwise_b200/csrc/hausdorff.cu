@@ -308,6 +308,134 @@ hausdorff_refine_kernel(const HdParams P) {
     }
 }
 
+// ---- float64, D <= 8: the same streaming design ------------------------------------------------------------------------
+// A 64-bit distance leaves no room for the visiting position in a 64-bit key, so every row's exact minimum is stored
+// (8 bytes per x1 point in the caller's scratch) and one CTA per set pair then scans them: largest minimum, last
+// visited row on ties, and for that row the first visited x2 point that attains it.  Products and sums are rounded
+// separately, as in the reference's CPU loop, so values and indices equal the one-CTA-per-pair kernel's bit for bit.
+constexpr int PMD = 2;             // x1 points per thread
+constexpr int CHUNK_D = 4096;      // doubles staged per pass (32 KB)
+
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+hausdorff_rowmin_f64_kernel(const HdParams P) {
+    constexpr int CHUNK = CHUNK_D / D;
+    __shared__ double pts[CHUNK_D];
+    const int tid = threadIdx.x;
+    long long blk = blockIdx.x;
+    const long long mt = blk % P.mtiles;
+    const long long pair = blk / P.mtiles;
+    const long long j = pair % P.N2;
+    const long long bi = pair / P.N2;
+    const long long b = bi / P.N1;
+    const double *x1 = reinterpret_cast<const double *>(P.x1) + bi * P.M1 * D;
+    const double *x2 = reinterpret_cast<const double *>(P.x2) + (b * P.N2 + j) * P.M2 * D;
+    double px[PMD][D], rowmin[PMD];
+    long long mm[PMD];
+#pragma unroll
+    for (int q = 0; q < PMD; ++q) {
+        mm[q] = mt * (kThreads * PMD) + q * kThreads + tid;
+        rowmin[q] = INFINITY;
+#pragma unroll
+        for (int k = 0; k < D; ++k) px[q][k] = mm[q] < P.M1 ? x1[mm[q] * D + k] : 0.0;
+    }
+    for (long long n0 = 0; n0 < P.M2; n0 += CHUNK) {
+        const int cnt = (int)((P.M2 - n0) < CHUNK ? (P.M2 - n0) : CHUNK);
+        __syncthreads();
+        for (int e = tid; e < cnt * D; e += kThreads) pts[e] = x2[n0 * D + e];
+        __syncthreads();
+#pragma unroll 2
+        for (int e = 0; e < cnt; ++e) {
+            double c[D];
+#pragma unroll
+            for (int k = 0; k < D; ++k) c[k] = pts[e * D + k];
+#pragma unroll
+            for (int q = 0; q < PMD; ++q) rowmin[q] = fmin(rowmin[q], sqdist_exact(px[q], c, D));
+        }
+    }
+    double *rm = reinterpret_cast<double *>(P.rowmins) + pair * P.M1;
+#pragma unroll
+    for (int q = 0; q < PMD; ++q)
+        if (mm[q] < P.M1) rm[mm[q]] = rowmin[q];
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+hausdorff_finish_f64_kernel(const HdParams P) {
+    __shared__ double s_val[kThreads];
+    __shared__ long long s_pos[kThreads], s_m[kThreads];
+    __shared__ unsigned long long s_npos[kThreads];
+    __shared__ long long s_nstar;
+    const int tid = threadIdx.x;
+    const long long pair = blockIdx.x;
+    const long long j = pair % P.N2;
+    const long long bi = pair / P.N2;
+    const long long b = bi / P.N1;
+    const double *x1 = reinterpret_cast<const double *>(P.x1) + bi * P.M1 * D;
+    const double *x2 = reinterpret_cast<const double *>(P.x2) + (b * P.N2 + j) * P.M2 * D;
+    const double *rm = reinterpret_cast<const double *>(P.rowmins) + pair * P.M1;
+    // largest row minimum, the last visited row on ties
+    double best = -1.0;
+    long long best_pos = -1, best_m = 0;
+    for (long long m = tid; m < P.M1; m += kThreads) {
+        const double v = rm[m];
+        const long long p1 = P.order1 ? P.order1[b * P.M1 + m] : m;
+        if (v > best || (v == best && p1 > best_pos)) { best = v; best_pos = p1; best_m = m; }
+    }
+    s_val[tid] = best; s_pos[tid] = best_pos; s_m[tid] = best_m;
+    __syncthreads();
+    for (int off = kThreads / 2; off > 0; off >>= 1) {
+        if (tid < off) {
+            const double v = s_val[tid + off];
+            const long long p = s_pos[tid + off];
+            if (v > s_val[tid] || (v == s_val[tid] && p > s_pos[tid])) { s_val[tid] = v; s_pos[tid] = p; s_m[tid] = s_m[tid + off]; }
+        }
+        __syncthreads();
+    }
+    const long long mstar = s_m[0];
+    const double cmax = s_pos[0] >= 0 ? s_val[0] : 0.0;
+    // the first visited x2 point at the row's minimum distance
+    double a[D];
+#pragma unroll
+    for (int k = 0; k < D; ++k) a[k] = x1[mstar * D + k];
+    unsigned long long mine = ~0ull;     // visiting position of the best candidate of this thread
+    long long mine_n = 0;
+    for (long long n = tid; n < P.M2; n += kThreads) {
+        double c[D];
+#pragma unroll
+        for (int k = 0; k < D; ++k) c[k] = x2[n * D + k];
+        if (sqdist_exact(a, c, D) == cmax) {
+            const unsigned long long p2 = (unsigned long long)(P.order2 ? P.order2[b * P.M2 + n] : n);
+            if (p2 < mine) { mine = p2; mine_n = n; }
+        }
+    }
+    s_npos[tid] = mine; s_pos[tid] = mine_n;
+    __syncthreads();
+    for (int off = kThreads / 2; off > 0; off >>= 1) {
+        if (tid < off && s_npos[tid + off] < s_npos[tid]) { s_npos[tid] = s_npos[tid + off]; s_pos[tid] = s_pos[tid + off]; }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        s_nstar = s_npos[0] == ~0ull ? 0 : s_pos[0];
+        reinterpret_cast<double *>(P.out)[pair] = sqrt(cmax);
+        P.idx1[pair] = mstar;
+        P.idx2[pair] = s_nstar;
+    }
+}
+
+template <int D>
+int launch_f64(HdParams P, cudaStream_t s) {
+    const long long pairs = P.B * P.N1 * P.N2;
+    P.mtiles = (P.M1 + kThreads * PMD - 1) / (kThreads * PMD);
+    const long long blocks = pairs * P.mtiles;
+    TPW_CHECK_ARG(blocks < (1ll << 31), "hausdorff: too many blocks");
+    hausdorff_rowmin_f64_kernel<D><<<(unsigned)blocks, kThreads, 0, s>>>(P);
+    TPW_LAUNCH_OK("hausdorff_rowmin_f64_kernel");
+    hausdorff_finish_f64_kernel<D><<<(unsigned)pairs, kThreads, 0, s>>>(P);
+    TPW_LAUNCH_OK("hausdorff_finish_f64_kernel");
+    return TPW_OK;
+}
+
 // Plain path: any dtype, any D.  One CTA per set pair; thread t scans rows m = t, t+256, ...
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
@@ -405,11 +533,12 @@ int launch_fast(HdParams P, cudaStream_t s) {
 
 using namespace tpw;
 
-// one 8-byte key per set pair, then one float per x1 point of every set pair (the approximate row minima)
+// one 8-byte key per set pair, then 8 bytes per x1 point of every set pair (the row minima: approximate float32 values
+// for the fused float32 loop, exact float64 values for the float64 path; the query does not know the dtype)
 extern "C" int64_t tpw_hausdorff_scratch_bytes(int64_t B, int64_t N1, int64_t N2, int64_t M1) {
     if (B <= 0 || N1 <= 0 || N2 <= 0) return 0;
     const int64_t pairs = B * N1 * N2;
-    return pairs * (int64_t)sizeof(unsigned long long) + (M1 > 0 ? (pairs * M1 * 4 + 7) / 8 * 8 : 0);
+    return pairs * (int64_t)sizeof(unsigned long long) + (M1 > 0 ? pairs * M1 * 8 : 0);
 }
 
 extern "C" int tpw_hausdorff_forward(int dtype, const void *x1, const void *x2,
@@ -451,6 +580,20 @@ extern "C" int tpw_hausdorff_forward(int dtype, const void *x1, const void *x2,
             case 6: return launch_fast<6>(P, s);
             case 7: return launch_fast<7>(P, s);
             default: return launch_fast<8>(P, s);
+        }
+    }
+    if (dtype == TPW_F64 && D <= 8 && scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 7u) == 0 &&
+        !getenv("TPW_HAUSDORFF_PLAIN_F64")) {
+        P.rowmins = reinterpret_cast<float *>(P.keys + pairs);   // used as double[pairs * M1]
+        switch (D) {
+            case 1: return launch_f64<1>(P, s);
+            case 2: return launch_f64<2>(P, s);
+            case 3: return launch_f64<3>(P, s);
+            case 4: return launch_f64<4>(P, s);
+            case 5: return launch_f64<5>(P, s);
+            case 6: return launch_f64<6>(P, s);
+            case 7: return launch_f64<7>(P, s);
+            default: return launch_f64<8>(P, s);
         }
     }
     if (dtype == TPW_F32) hausdorff_plain_kernel<float><<<(unsigned)pairs, kThreads, 0, s>>>(P);

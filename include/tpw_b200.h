@@ -179,6 +179,28 @@ TPW_API int tpw_lp_backward(int dtype, int mode, const void *grad, const void *a
                     double p, tpw_stream_t stream);
 
 /*
+ * tpw_lp_backward with caller scratch: both gradients from ONE walk over the pairs.  A pair's term
+ * coef * phi(x1 - x2) is formed once and added to the grad_x1 sum and, negated, to the grad_x2 sum
+ * (4 operations per pair and feature where the two launches of tpw_lp_backward execute 6).  The sums of
+ * grad_x2 over blocks of 256 rows of x1 go to `scratch` and are added in ascending block order by a
+ * second kernel: no atomics, fixed summation order, bit-reproducible; the order differs from
+ * tpw_lp_backward's, so the two agree to rounding, not bit for bit.
+ * tpw_lp_backward_scratch_bytes() returns 0 where the kernel does not apply (float64, p = +inf, the
+ * plain contraction, fewer than 256 rows of x1, N2 or D not a multiple of 4, small problems,
+ * TPW_DISABLE_ONEPASS_BWD=1), else the scratch it wants: B * ceil(N1/256) * N2 * D * 4 bytes up to
+ * 2 GiB (larger problems run as several launches over batch or row-block ranges).  With scratch ==
+ * NULL, less than N2 * D * 4 bytes, a NULL gradient pointer or a pointer that is not 16-byte aligned the
+ * call is tpw_lp_backward.  Replaces the same reference kernels as tpw_lp_backward
+ * (OPS/cuda/ppminkowski_kernel.cu:133-218, OPS/cuda/wminkowski_kernel.cu:146-196, ATen's cdist backward).
+ */
+TPW_API int64_t tpw_lp_backward_scratch_bytes(int dtype, int mode, int64_t B, int64_t N1, int64_t N2, int64_t D, double p);
+TPW_API int tpw_lp_backward_ws(int dtype, int mode, const void *grad, const void *aux,
+                    const void *x1, const void *x2, const void *w,
+                    void *grad_x1, void *grad_x2,
+                    int64_t B, int64_t N1, int64_t N2, int64_t D,
+                    double p, void *scratch, int64_t scratch_bytes, tpw_stream_t stream);
+
+/*
  * grad_w[b,k] = sum_{i,j} grad*aux * |x1-x2|^p / p  (aux as in TPW_LP_BWD_WMINKOWSKI).
  * `scratch` holds B*N1*D elements of `dtype` (per-row partial sums reduced in a second,
  * ordered stage).  Replaces OPS/cuda/wminkowski_kernel.cu:198-221.

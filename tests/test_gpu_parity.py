@@ -335,6 +335,70 @@ def test_small_problem_backward_kernel_is_bit_identical_to_tile_kernel(tpw, monk
         close(res[0][1], r2, TOL[torch.float32], scale, "grad_x2")
 
 
+@pytest.mark.parametrize("mode,p", [("cdist", 1.0), ("cdist", 2.0), ("cdist", 3.0), ("cdist", 2.5), ("pp", 3.0), ("pp", 1.5), ("w", 3.0), ("w", 1.5)])
+def test_one_pass_backward(tpw, mode, p):
+    """The backward that forms a pair's term once and adds it to both gradient sums (`tpw_lp_backward_ws`) against the
+    oracle and against the two-launch kernel, on shapes with ragged row blocks, ragged feature tiles and a ragged
+    last stage; bit-reproducible from call to call, and unchanged to rounding when a small scratch forces several
+    launches over batch ranges or over row-block ranges (whose sums are then accumulated into grad_x2)."""
+    from torchpairwise_b200 import _abi
+    lib = _abi.lib
+    code = {"cdist": _abi.LP_BWD_CDIST, "pp": _abi.LP_BWD_PPMINKOWSKI, "w": _abi.LP_BWD_WMINKOWSKI}[mode]
+    g = torch.Generator().manual_seed(int(p * 10) + len(mode))
+    stream = torch.cuda.current_stream().cuda_stream
+    for shape in ((10, 1000, 300, 208), (3, 2560, 140, 256), (80, 256, 256, 64)):
+        b, n1, n2, d = shape
+        x1, x2 = torch.randn(b, n1, d, generator=g).cuda(), torch.randn(b, n2, d, generator=g).cuda()
+        gr = torch.randn(b, n1, n2, generator=g).cuda()
+        w = (torch.rand(b, d, generator=g) + 0.5).cuda() if mode == "w" else None
+        if mode == "cdist":
+            aux = tpw.minkowski_distances(x1, x2, p) if p != 1.0 else None
+        elif mode == "w":
+            aux = (torch.rand(b, n1, n2, generator=g) + 0.5).cuda()
+        else:
+            aux = None
+        ptr = lambda t: None if t is None else t.data_ptr()
+        want = lib.tpw_lp_backward_scratch_bytes(_abi.F32, code, b, n1, n2, d, p)
+        assert want > 0, shape
+        slab = n2 * d * 4
+        blocks = (n1 + 255) // 256
+
+        def run(nbytes):
+            g1, g2 = torch.full_like(x1, float("nan")), torch.full_like(x2, float("nan"))
+            if nbytes is None:
+                _abi.check(lib.tpw_lp_backward(_abi.F32, code, ptr(gr), ptr(aux), ptr(x1), ptr(x2), ptr(w), ptr(g1), ptr(g2),
+                                               b, n1, n2, d, p, stream))
+            else:
+                scratch = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+                _abi.check(lib.tpw_lp_backward_ws(_abi.F32, code, ptr(gr), ptr(aux), ptr(x1), ptr(x2), ptr(w), ptr(g1), ptr(g2),
+                                                  b, n1, n2, d, p, ptr(scratch), nbytes, stream))
+            assert _abi.device_status(stream) == 0
+            return g1, g2
+
+        two = run(None)
+        one = run(want)
+        again = run(want)
+        assert torch.equal(one[0], again[0]) and torch.equal(one[1], again[1]), shape
+        scale = float(two[0].abs().max()) + float(two[1].abs().max())
+        for nbytes in (want, slab * blocks * 2, slab * max(1, blocks - 1), slab):
+            res = run(nbytes)
+            for a, r in zip(res, two):
+                assert not torch.isnan(a).any()
+                assert float((a - r).abs().max()) <= 2e-5 * scale, (shape, nbytes)
+        # oracle: float64 autograd of the same composite
+        a64, b64 = x1.double().requires_grad_(), x2.double().requires_grad_()
+        if mode == "cdist":
+            torch.cdist(a64, b64, p=p).backward(gr.double())
+        elif mode == "pp":
+            ((a64[:, :, None, :] - b64[:, None, :, :]).abs() ** p).sum(-1).backward(gr.double())
+        else:
+            # _wminkowski backward with S^(1/p-1) replaced by the given auxiliary matrix
+            (((a64[:, :, None, :] - b64[:, None, :, :]).abs() ** p * w.double()[:, None, None, :]).sum(-1) / p).backward((gr * aux).double())
+        s1 = max(1.0, float(a64.grad.abs().max()))
+        assert float((one[0].double() - a64.grad).abs().max()) <= 1e-4 * s1, (shape, "grad_x1")
+        assert float((one[1].double() - b64.grad).abs().max()) <= 1e-4 * max(1.0, float(b64.grad.abs().max())), (shape, "grad_x2")
+
+
 @pytest.mark.parametrize("shape", [(1, 70, 50, 16), (2, 129, 67, 36), (1, 64, 64, 70), (2, 200, 333, 300), (1, 300, 130, 257)])
 @pytest.mark.parametrize("lattice", [False, True])
 def test_chebyshev_backward_match_and_scatter(tpw, shape, lattice):

@@ -54,6 +54,8 @@ SIGNATURES = {
     "tpw_jensenshannon_forward": (_I, [_I, _P, _P, _P, _L, _L, _L, _L, _D, _I, _P]),
     "tpw_jensenshannon_backward": (_I, [_I, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _D, _P]),
     "tpw_lp_backward": (_I, [_I, _I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _D, _P]),
+    "tpw_lp_backward_scratch_bytes": (_L, [_I, _I, _L, _L, _L, _L, _D]),
+    "tpw_lp_backward_ws": (_I, [_I, _I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _D, _P, _L, _P]),
     "tpw_chebyshev_backward_scratch_bytes": (_L, [_I, _L, _L, _L, _L]),
     "tpw_chebyshev_backward_ws": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P]),
     "tpw_wminkowski_backward_w": (_I, [_I, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _D, _P]),

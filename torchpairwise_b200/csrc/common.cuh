@@ -72,6 +72,13 @@ bool lp_small_d_rowmin_eligible(long long N1, long long N2, long long D, double 
 int lp_small_d_rowmin(const void *x1, const void *x2, unsigned long long *keys, long long B, long long N1, long long N2, long long D,
                       double p, double out_exponent, cudaStream_t s);
 
+// lp_backward_onepass.cu: both gradients of an L_p reduction from one walk over the pairs (float32).  The query
+// returns 0 where that kernel does not apply.
+long long lp_backward_onepass_scratch_bytes(int mode, long long B, long long N1, long long N2, long long D, double p);
+int lp_backward_onepass(int mode, const void *grad, const void *aux, const void *x1, const void *x2, const void *w,
+                        void *grad_x1, void *grad_x2, long long B, long long N1, long long N2, long long D, double p,
+                        void *scratch, long long scratch_bytes, cudaStream_t stream);
+
 // lp_backward.cu: the dense cdist backward for p = +inf (float32), run only when *only_if > above on the device
 int lp_backward_cdist_inf_if(const unsigned long long *only_if, unsigned long long above, const void *grad, const void *out, const void *x1, const void *x2,
                              void *grad_x1, void *grad_x2, long long B, long long N1, long long N2, long long D,

@@ -17,6 +17,7 @@
 // coefficient loads are broadcasts.  Aligned problems are fed by TMA (three-stage
 // mbarrier ring, one issuing thread); others use guarded plain loads into the same layout.
 #include "common.cuh"
+#include "lp_backward_phi.cuh"
 
 #include <math.h>
 #include <stdlib.h>
@@ -24,21 +25,6 @@
 namespace tpw {
 namespace {
 
-enum Phi {
-    PHI_SGN = 0,    // sgn(d)
-    PHI_D = 1,      // d
-    PHI_DABS = 2,   // d*|d|
-    PHI_SGNPOW = 3, // sgn(d)*|d|^q
-    PHI_ABSPOW = 4, // |d|^q
-    PHI_Y = 5,      // the streamed operand itself (plain contraction)
-    PHI_SGN_EQ = 6, // sgn(d) where |d| equals the auxiliary value, else 0
-    // derivatives of symmetric two-argument terms with respect to the register-resident operand x
-    PHI_CANBERRA = 7, // sgn(d)/n - sgn(x)|d|/n^2, n = |x| + |y| (0 where n == 0)
-    PHI_CHI2 = 8,     // t^2 - 2t, t = d/(x + y) (0 where x + y == 0): d/dx of -(x - y)^2/(x + y)
-    PHI_JS = 9        // log(2x/(x + y)) where x > 0, else -y/(x + y) (0 where x + y == 0)
-};
-
-enum CoefMode { COEF_G = 0, COEF_DIV_O = 1, COEF_DIV_O2 = 2, COEF_DIV_POW = 3, COEF_MUL = 4, COEF_ZERO_WHERE_O0 = 5 };
 
 struct BwdParams {
     const void *rowop;  // [B, NR, D] operand held in registers
@@ -61,143 +47,6 @@ struct BwdParams {
 constexpr int kStages = 2;
 constexpr int SC = 64; // streamed rows per stage
 
-template <typename T> __device__ __forceinline__ void load4(T *dst, const T *src);
-template <> __device__ __forceinline__ void load4<float>(float *dst, const float *src) {
-    float4 v = *reinterpret_cast<const float4 *>(src);
-    dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
-}
-template <> __device__ __forceinline__ void load4<double>(double *dst, const double *src) {
-    double2 a = *reinterpret_cast<const double2 *>(src);
-    double2 b = *reinterpret_cast<const double2 *>(src + 2);
-    dst[0] = a.x; dst[1] = a.y; dst[2] = b.x; dst[3] = b.y;
-}
-
-__device__ __forceinline__ float b_abs(float v) { return fabsf(v); }
-__device__ __forceinline__ double b_abs(double v) { return fabs(v); }
-__device__ __forceinline__ float b_fma(float a, float b, float c) { return fmaf(a, b, c); }
-__device__ __forceinline__ double b_fma(double a, double b, double c) { return fma(a, b, c); }
-__device__ __forceinline__ float b_powabs(float a, float q) { return a == 0.f ? 0.f : exp2f(q * __log2f(a)); }
-__device__ __forceinline__ double b_powabs(double a, double q) { return a == 0.0 ? 0.0 : pow(a, q); }
-__device__ __forceinline__ float b_copysign(float a, float s) { return copysignf(a, s); }
-__device__ __forceinline__ double b_copysign(double a, double s) { return copysign(a, s); }
-// c * sgn(d) for d != 0: flip c's sign bit with d's (one logic operation)
-__device__ __forceinline__ float b_copysign_of(float c, float d) {
-    return __int_as_float(__float_as_int(c) ^ (__float_as_int(d) & 0x80000000));
-}
-__device__ __forceinline__ double b_copysign_of(double c, double d) { return d < 0.0 ? -c : c; }
-// g / v for the coefficient tile: an approximate reciprocal (2 ulp) is far inside the fp32 parity
-// tolerance and an order of magnitude cheaper than the IEEE sequence; fp64 keeps the exact divide
-__device__ __forceinline__ float b_div(float g, float v) { return __fdividef(g, v); }
-__device__ __forceinline__ double b_div(double g, double v) { return g / v; }
-__device__ __forceinline__ float b_log(float v) {   // flush-to-zero MUFU logarithm; callers pass normal numbers or guard the result
-    float l;
-    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(l) : "f"(fmaxf(v, 1.17549435e-38f)));
-    return 0.693147181f * l;
-}
-__device__ __forceinline__ double b_log(double v) { return log(v); }
-__device__ __forceinline__ float b_pow(float a, double q) { return powf(a, (float)q); }
-__device__ __forceinline__ double b_pow(double a, double q) { return pow(a, q); }
-
-// Two float32 lanes per instruction (sm_100 packed arithmetic).  The FMA pipe retires the same number of lanes per
-// clock either way, but a packed instruction takes one issue slot for two results, which leaves the scheduler
-// room for the shared-memory loads and lets four warps per scheduler cover the arithmetic latency.
-typedef unsigned long long f32x2;
-__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
-    f32x2 r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ void unpack2(f32x2 v, float &lo, float &hi) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) {
-    f32x2 r;
-    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
-    f32x2 r;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
-    f32x2 r;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-    return r;
-}
-__device__ __forceinline__ f32x2 abs2(f32x2 a) { return a & 0x7fffffff7fffffffull; }
-
-template <typename T, int PHI> struct PackedPhi {
-    static constexpr bool value = false;
-};
-template <> struct PackedPhi<float, PHI_DABS> { static constexpr bool value = true; };
-template <> struct PackedPhi<float, PHI_D> { static constexpr bool value = true; };
-template <> struct PackedPhi<float, PHI_Y> { static constexpr bool value = true; };
-
-// acc += c * phi(x - y) on two adjacent features: the same operations, in the same order and rounding, as the scalar form
-template <int PHI>
-__device__ __forceinline__ f32x2 bwd_accumulate2(f32x2 acc, f32x2 x, f32x2 y, f32x2 c) {
-    if (PHI == PHI_Y) return fma2(c, y, acc);
-    const f32x2 d = sub2(x, y);
-    if (PHI == PHI_D) return fma2(c, d, acc);
-    // d |d| lane by lane: the scalar multiply takes |.| as an operand modifier, a packed one would need two logic
-    // operations for it, and those occupy the same lanes as the arithmetic
-    float lo, hi;
-    unpack2(d, lo, hi);
-    return fma2(c, pack2(lo * fabsf(lo), hi * fabsf(hi)), acc);
-}
-
-// acc += c * phi(x - y)
-template <int PHI, typename T>
-__device__ __forceinline__ void bwd_accumulate(T &acc, T x, T y, T c, T o, T q, int pspec) {
-    if (PHI == PHI_Y) {
-        acc = b_fma(c, y, acc);
-        return;
-    }
-    if (PHI == PHI_CANBERRA) {
-        // r (sgn(d) - sgn(x) |d| r), branch-free: a zero denominator selects r = 0, and the two signs are
-        // copied onto r and |d| r^2 (zero where d, respectively x, is zero)
-        const T n = b_abs(x) + b_abs(y), d = x - y;
-        const T r = rcp_or_zero(n);
-        const T t1 = d != T(0) ? b_copysign(r, d) : T(0);
-        const T t2 = x != T(0) ? b_copysign(b_abs(d) * r * r, x) : T(0);
-        acc = b_fma(c, t1 - t2, acc);
-        return;
-    }
-    if (PHI == PHI_CHI2) {
-        const T n = x + y;
-        const T r = rcp_or_zero(n);
-        const T t = (x - y) * r;
-        acc = b_fma(c, t * (t - T(2)), acc);
-        return;
-    }
-    if (PHI == PHI_JS) {
-        // d/dx of x log(x/m) + y log(y/m), m = (x + y)/2, is log(x/m); the reference's branches
-        // (OPS/cpu/sqjensenshannon_kernel.cpp:98-112) add up to log 2 at y == 0 and to -1 at x == 0 < y
-        const T r = rcp_or_zero(x + y);
-        // x/m = 1 + t, t = (x - y)/(x + y): exactly 1 for equal entries; where x is much smaller than y
-        // the sum 1 + t cancels, and the quotient 2x/(x + y) keeps the relative accuracy the logarithm needs
-        const T t = (x - y) * r;
-        const T ratio = b_abs(t) < T(0.5) ? T(1) + t : T(2) * x * r;
-        acc = b_fma(c, x > T(0) ? b_log(ratio) : -y * r, acc);
-        return;
-    }
-    T d = x - y;
-    if (PHI == PHI_D) {
-        acc = b_fma(c, d, acc);
-    } else if (PHI == PHI_DABS) {
-        acc = b_fma(c, d * b_abs(d), acc);
-    } else if (PHI == PHI_SGN) {
-        if (d != T(0)) acc += b_copysign_of(c, d);
-    } else if (PHI == PHI_SGNPOW) {
-        acc = b_fma(c, b_copysign(pow_abs_spec(b_abs(d), q, pspec), d), acc);
-    } else if (PHI == PHI_ABSPOW) {
-        acc = b_fma(c, pow_abs_spec(b_abs(d), q, pspec), acc);
-    } else if (PHI == PHI_SGN_EQ) {
-        // c is already zero where o == 0, and |d| == o > 0 implies d != 0
-        if (b_abs(d) == o) acc += b_copysign_of(c, d);
-    }
-}
 
 // RR rows x RK features per thread, NTHR threads: (NTHR/16)*RR rows by 16*RK features per CTA.
 // float: 4 x 8 on 512 threads (128 x 128, 16 warps per SM for latency hiding at <= 128 registers);
@@ -684,6 +533,29 @@ extern "C" int tpw_lp_backward(int dtype, int mode, const void *grad, const void
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return dtype == TPW_F32 ? lp_backward_typed<float>(mode, P, x1, x2, grad_x1, grad_x2, p, s)
                             : lp_backward_typed<double>(mode, P, x1, x2, grad_x1, grad_x2, p, s);
+}
+
+extern "C" int64_t tpw_lp_backward_scratch_bytes(int dtype, int mode, int64_t B, int64_t N1, int64_t N2, int64_t D, double p) {
+    if (dtype != TPW_F32) return 0;
+    return lp_backward_onepass_scratch_bytes(mode, B, N1, N2, D, p);
+}
+
+extern "C" int tpw_lp_backward_ws(int dtype, int mode, const void *grad, const void *aux,
+                                  const void *x1, const void *x2, const void *w,
+                                  void *grad_x1, void *grad_x2,
+                                  int64_t B, int64_t N1, int64_t N2, int64_t D,
+                                  double p, void *scratch, int64_t scratch_bytes, tpw_stream_t stream) {
+    const int64_t want = dtype == TPW_F32 && B >= 0 && N1 >= 0 && N2 >= 0 && D >= 0 && !isnan(p)
+                             ? lp_backward_onepass_scratch_bytes(mode, B, N1, N2, D, p) : 0;
+    const bool needs_aux = (mode == TPW_LP_BWD_WMINKOWSKI) || (mode == TPW_LP_BWD_CDIST && p != 1.0);
+    const bool usable = want > 0 && scratch != nullptr && scratch_bytes >= N2 * D * 4 && grad_x1 && grad_x2 && grad && x1 && x2 &&
+                        (!needs_aux || aux) && (mode != TPW_LP_BWD_WMINKOWSKI || w) &&
+                        aligned16(grad) && aligned16(x1) && aligned16(x2) && aligned16(grad_x1) && aligned16(grad_x2) &&
+                        aligned16(scratch) && (!needs_aux || aligned16(aux)) && (!w || aligned16(w));
+    if (!usable) return tpw_lp_backward(dtype, mode, grad, aux, x1, x2, w, grad_x1, grad_x2, B, N1, N2, D, p, stream);
+    clear_error();
+    return lp_backward_onepass(mode, grad, aux, x1, x2, w, grad_x1, grad_x2, B, N1, N2, D, p, scratch,
+                               scratch_bytes < want ? scratch_bytes : want, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int tpw_wminkowski_backward_w(int dtype, const void *grad, const void *aux,

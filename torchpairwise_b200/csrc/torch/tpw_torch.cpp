@@ -155,6 +155,20 @@ bool tensor_engine_selected(const Prepared &p) {
 // With `cosine` set (epilogue >= 0, the two norm vectors) the call is the whole cosine-family backward,
 // tpw_cosine_backward_ws, with g the upstream gradient and aux the saved forward result; it returns
 // false without doing anything when the engine rule keeps the problem on the CUDA cores.
+// tpw_lp_backward, through the one-pass kernel (both gradients from one walk over the pairs) where the library offers it
+void lp_backward_call(int code, int mode, const Tensor &g, const void *aux, const Tensor &a, const Tensor &b, const void *w,
+                      Tensor &g1, Tensor &g2, int64_t B, int64_t N1, int64_t N2, int64_t D, double p) {
+    const int64_t bytes = tpw_lp_backward_scratch_bytes(code, mode, B, N1, N2, D, p);
+    if (bytes <= 0) {
+        TPW_CALL(tpw_lp_backward(code, mode, g.data_ptr(), aux, a.data_ptr(), b.data_ptr(), w, g1.data_ptr(), g2.data_ptr(),
+                                 B, N1, N2, D, p, stream_of(a)));
+        return;
+    }
+    Tensor scratch = at::empty({bytes}, a.options().dtype(at::kByte));
+    TPW_CALL(tpw_lp_backward_ws(code, mode, g.data_ptr(), aux, a.data_ptr(), b.data_ptr(), w, g1.data_ptr(), g2.data_ptr(),
+                                B, N1, N2, D, p, scratch.data_ptr(), bytes, stream_of(a)));
+}
+
 struct CosineArgs {
     int epilogue = -1;
     const Tensor *n1 = nullptr, *n2 = nullptr;
@@ -167,8 +181,7 @@ bool dense_backward(int mode, const Tensor &g, const Tensor *aux, const Tensor &
     auto st = stream_of(a);
     if (tpw_dot_backward_scratch_bytes(code, mode, TPW_ENGINE_AUTO, B, N1, N2, D) <= 0) {
         if (cosine.epilogue >= 0) return false;
-        TPW_CALL(tpw_lp_backward(code, mode, g.data_ptr(), aux ? aux->data_ptr() : nullptr, a.data_ptr(), b.data_ptr(), nullptr,
-                                 g1.data_ptr(), g2.data_ptr(), B, N1, N2, D, 2.0, st));
+        lp_backward_call(code, mode, g, aux ? aux->data_ptr() : nullptr, a, b, nullptr, g1, g2, B, N1, N2, D, 2.0);
         return true;
     }
     const int eng = TPW_ENGINE_TCGEN05_TF32X3;
@@ -250,8 +263,7 @@ struct CdistFn : torch::autograd::Function<CdistFn> {
             TPW_CALL(tpw_chebyshev_backward_ws(g.data_ptr(), out.data_ptr(), a.data_ptr(), b.data_ptr(), g1.data_ptr(), g2.data_ptr(),
                                                scratch.data_ptr(), bytes, a.size(0), a.size(1), b.size(1), a.size(2), stream_of(a)));
         }
-        else TPW_CALL(tpw_lp_backward(code_of(a), TPW_LP_BWD_CDIST, g.data_ptr(), out.data_ptr(), a.data_ptr(), b.data_ptr(), nullptr,
-                                      g1.data_ptr(), g2.data_ptr(), a.size(0), a.size(1), b.size(1), a.size(2), p, stream_of(a)));
+        else lp_backward_call(code_of(a), TPW_LP_BWD_CDIST, g, out.data_ptr(), a, b, nullptr, g1, g2, a.size(0), a.size(1), b.size(1), a.size(2), p);
         return {finish(g1, ub, dt), finish(g2, ub, dt), Tensor()};
     }
 };
@@ -287,8 +299,7 @@ struct PPMinkowskiFn : torch::autograd::Function<PPMinkowskiFn> {
             else if (p == 2)
                 dense_backward(TPW_LP_BWD_PPMINKOWSKI, g, nullptr, a, b, g1, g2);
             else
-                TPW_CALL(tpw_lp_backward(code_of(a), TPW_LP_BWD_PPMINKOWSKI, g.data_ptr(), nullptr, a.data_ptr(), b.data_ptr(), nullptr,
-                                         g1.data_ptr(), g2.data_ptr(), B, N1, N2, D, p, stream_of(a)));
+                lp_backward_call(code_of(a), TPW_LP_BWD_PPMINKOWSKI, g, nullptr, a, b, nullptr, g1, g2, B, N1, N2, D, p);
         }
         return {g1, g2};
     }
@@ -452,8 +463,7 @@ struct WMinkowskiFn : torch::autograd::Function<WMinkowskiFn> {
             } else {
                 Prepared q{a, b, false, B, N1, N2, D};
                 Tensor coef = lp_forward(q, &w, p, 1.0 / p - 1.0); // S^(1/p-1), OPS/cuda/wminkowski_kernel.cu:16-37
-                TPW_CALL(tpw_lp_backward(code_of(a), TPW_LP_BWD_WMINKOWSKI, g.data_ptr(), coef.data_ptr(), a.data_ptr(), b.data_ptr(),
-                                         w.data_ptr(), g1.data_ptr(), g2.data_ptr(), B, N1, N2, D, p, stream_of(a)));
+                lp_backward_call(code_of(a), TPW_LP_BWD_WMINKOWSKI, g, coef.data_ptr(), a, b, w.data_ptr(), g1, g2, B, N1, N2, D, p);
                 Tensor scratch = at::empty({B, N1, D}, a.options());
                 TPW_CALL(tpw_wminkowski_backward_w(code_of(a), g.data_ptr(), coef.data_ptr(), a.data_ptr(), b.data_ptr(), gw.data_ptr(),
                                                    scratch.data_ptr(), B, N1, N2, D, p, stream_of(a)));

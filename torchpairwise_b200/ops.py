@@ -167,11 +167,25 @@ def _lp_backward_raw(mode: int, grad: Tensor, aux: Optional[Tensor], x1c: Tensor
             return res
     g1 = torch.empty_like(x1c) if need1 else None
     g2 = torch.empty_like(x2c) if need2 else None
-    with torch.cuda.device(x1c.device):
-        check(lib.tpw_lp_backward(_FLOAT_CODES[x1c.dtype], mode, _ptr(grad), _ptr(aux), _ptr(x1c), _ptr(x2c),
-                                  _ptr(w), _ptr(g1), _ptr(g2), B, N1, N2, D, float(p), _stream(x1c)),
-              "tpw_lp_backward")
+    _lp_backward_call(mode, grad, aux, x1c, x2c, w, g1, g2, p)
     return g1, g2
+
+
+def _lp_backward_call(mode: int, grad: Tensor, aux: Optional[Tensor], x1c: Tensor, x2c: Tensor, w: Optional[Tensor],
+                      g1: Optional[Tensor], g2: Optional[Tensor], p: float) -> None:
+    """``tpw_lp_backward``; with both gradients wanted and a positive scratch query, the one-pass kernel
+    (``tpw_lp_backward_ws``: a pair's term is formed once and added to both sums)."""
+    B, N1, N2, D = _sizes(x1c, x2c)
+    code = _FLOAT_CODES[x1c.dtype]
+    with torch.cuda.device(x1c.device):
+        nbytes = lib.tpw_lp_backward_scratch_bytes(code, mode, B, N1, N2, D, float(p)) if g1 is not None and g2 is not None else 0
+        if nbytes > 0:
+            scratch = torch.empty((nbytes,), dtype=torch.uint8, device=x1c.device)
+            check(lib.tpw_lp_backward_ws(code, mode, _ptr(grad), _ptr(aux), _ptr(x1c), _ptr(x2c), _ptr(w), _ptr(g1), _ptr(g2),
+                                         B, N1, N2, D, float(p), _ptr(scratch), nbytes, _stream(x1c)), "tpw_lp_backward_ws")
+        else:
+            check(lib.tpw_lp_backward(code, mode, _ptr(grad), _ptr(aux), _ptr(x1c), _ptr(x2c), _ptr(w), _ptr(g1), _ptr(g2),
+                                      B, N1, N2, D, float(p), _stream(x1c)), "tpw_lp_backward")
 
 
 def _bwd_scratch_cap() -> int:
@@ -429,9 +443,7 @@ def _wminkowski_backward_raw(grad, x1c, x2c, wc, p, unbatched):
                 # coefficient S^(1/p-1): the reference's forward kernel with its `backward` flag
                 # (OPS/cuda/wminkowski_kernel.cu:16-37 called at :300-320)
                 coef = _lp_forward_raw(x1c, x2c, wc, p, 1.0 / p - 1.0)
-                check(lib.tpw_lp_backward(code, _abi.LP_BWD_WMINKOWSKI, _ptr(g), _ptr(coef), _ptr(x1c), _ptr(x2c),
-                                          _ptr(wc), _ptr(g1), _ptr(g2), B, N1, N2, D, float(p), _stream(x1c)),
-                      "tpw_lp_backward")
+                _lp_backward_call(_abi.LP_BWD_WMINKOWSKI, g, coef, x1c, x2c, wc, g1, g2, p)
                 scratch = torch.empty((B, N1, D), dtype=x1c.dtype, device=x1c.device)
                 check(lib.tpw_wminkowski_backward_w(code, _ptr(g), _ptr(coef), _ptr(x1c), _ptr(x2c), _ptr(gw),
                                                     _ptr(scratch), B, N1, N2, D, float(p), _stream(x1c)),

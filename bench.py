@@ -13,12 +13,13 @@ One JSON line is printed by rank 0.  ``value`` is timed with the inputs resident
 tensors by this package's C++ host layer (``drop_in`` puts the Python mirror of the same call beside
 it).  ``e2e`` times the same step from pinned host buffers (inputs copied in, both gradients copied
 out, every step) and carries the measured host-to-device ceiling of the box at this N.  ``roofline``
-describes the dominant kernel (the backward tile kernel, two launches per step), timed alone with
-CUDA events on its stream: ``frac`` counts the algorithmic lane-operations (difference, shape term
-and two accumulations per pair and feature for both gradients, i.e. two per launch),
-``frac_executed`` the three a launch really issues; the bound is the fp32 issue rate measured live
-by the library's register-only microbenchmark, and ``roofline_hbm`` restates the same launch against
-the measured copy bandwidth.  ``cpu_baseline`` times the reference's own CPU operators (built from
+describes the dominant kernel (the one-pass backward: a pair's term is formed once and added to both
+gradient sums; its finishing kernel that adds the row-block sums of grad_x2 is inside the timed call),
+timed alone with CUDA events on its stream: ``frac`` counts the algorithmic lane-operations
+(difference, shape term and two accumulations per pair and feature), which is also what the kernel
+executes; the bound is the fp32 issue rate measured live by the library's register-only
+microbenchmark, and ``roofline_hbm`` restates the same call against the measured copy bandwidth.
+``two_launch_ms`` is the older form (one launch per gradient, 6 operations executed) on the same data.  ``cpu_baseline`` times the reference's own CPU operators (built from
 its sources into oracle/_ref) on a bounded row block, best of three.
 
 On one GPU the line also carries ``configs`` -- every benchmark configuration (C1 euclidean /
@@ -52,20 +53,19 @@ sys.path.insert(0, str(ROOT))
 METRIC = "Gpairs/s, minkowski_distances(p=3) forward+backward, fp32"
 B, N1, N2, D, P = 16, 4096, 4096, 256, 3.0
 PAIRS_PER_STEP = B * N1 * N2
-# lane-operations of the dominant kernel per pair and feature as executed: subtract, d*|d|, fused multiply-add
-BWD_OPS_PER_ELEMENT = 3
-# the algorithmic count: difference, shape term and two accumulations for BOTH gradients (4 per pair and feature),
-# of which one launch produces one gradient
-BWD_ALG_OPS_PER_ELEMENT_PER_LAUNCH = 2
+# lane-operations of the dominant kernel per pair and feature: subtract, d*|d| and one fused multiply-add into each of
+# the two gradient sums -- the algorithmic count for both gradients, and what the one-pass kernel executes
+BWD_OPS_PER_ELEMENT = 4
 # lane-operations per point pair of the Hausdorff row-minimum loop as executed
 HAUSDORFF_EXECUTED_OPS = 7
-# algorithmic HBM bytes of one backward launch: upstream gradient + forward output read once,
-# both operands read once, one gradient written
-BWD_BYTES_PER_LAUNCH = 4 * (2 * B * N1 * N2 + 3 * B * N1 * D)
-# dram__bytes_read.sum + dram__bytes_write.sum of one backward launch: 589.6 MB measured by ncu at
-# batch 4 (profiles/lp_kernels_c2_minkowski_p3.md); the traffic is the streamed gradient and forward
-# output, so it grows in proportion to the batch
-BWD_DRAM_TRAFFIC_BYTES_PER_BATCH = 589.6e6 / 4
+# algorithmic HBM bytes of the backward: upstream gradient + forward output read once, both operands read once,
+# both gradients written
+BWD_BYTES_PER_LAUNCH = 4 * (2 * B * N1 * N2 + 2 * B * N1 * D + 2 * B * N2 * D)
+# dram__bytes_read.sum + dram__bytes_write.sum of the backward call measured by ncu at batch 4
+# (profiles/lp_kernels_c2_minkowski_p3.md): 848.7 MB in the one-pass kernel (gradient and forward output streamed
+# once, 268 MB of row-block sums written) + 285 MB in the finishing kernel that reads them back; both grow in
+# proportion to the batch
+BWD_DRAM_TRAFFIC_BYTES_PER_BATCH = (848.7e6 + 285.0e6) / 4
 
 REF_SO = ROOT / "oracle" / "_ref" / "torchpairwise_ref.so"
 
@@ -438,7 +438,7 @@ def run_configs(T, R, dev, gpu_ms, peaks, X, Y, G, hosts, args):
     rows = 512
     Xb, Yb, Gb = c2_block(*hosts, rows)
     pairs = B * N1 * N2
-    for name, kw, fwd_alg, bwd_alg, fwd_exe, bwd_exe in (("minkowski_distances", {"p": P}, 3, 4, 3, 6),
+    for name, kw, fwd_alg, bwd_alg, fwd_exe, bwd_exe in (("minkowski_distances", {"p": P}, 3, 4, 3, 4),
                                                          ("chebyshev_distances", {}, 2, 2, 2, 4)):
         op = getattr(T, name)
 
@@ -736,26 +736,35 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         with torch.no_grad():
             out = T.minkowski_distances(X, Y, P)
             drop_in_same_bits = bool(torch.equal(out, tpw.minkowski_distances(X, Y, P)))
-        g1 = torch.empty_like(X)
+        g1, g2 = torch.empty_like(X), torch.empty_like(Y)
         stream = torch.cuda.current_stream().cuda_stream
+        nbytes = _abi.lib.tpw_lp_backward_scratch_bytes(_abi.F32, _abi.LP_BWD_CDIST, B, N1, N2, D, P)
+        scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
 
         def bwd_launch():
+            _abi.check(_abi.lib.tpw_lp_backward_ws(_abi.F32, _abi.LP_BWD_CDIST, G.data_ptr(), out.data_ptr(),
+                                                   X.data_ptr(), Y.data_ptr(), None, g1.data_ptr(), g2.data_ptr(),
+                                                   B, N1, N2, D, P, scratch.data_ptr(), nbytes, stream))
+
+        def bwd_two_launches():
             _abi.check(_abi.lib.tpw_lp_backward(_abi.F32, _abi.LP_BWD_CDIST, G.data_ptr(), out.data_ptr(),
-                                                X.data_ptr(), Y.data_ptr(), None, g1.data_ptr(), None,
+                                                X.data_ptr(), Y.data_ptr(), None, g1.data_ptr(), g2.data_ptr(),
                                                 B, N1, N2, D, P, stream))
 
         k_ms = gpu_ms(bwd_launch, reps=max(5, args.steps), warm=3)
-        executed = PAIRS_PER_STEP * D * BWD_OPS_PER_ELEMENT
-        algorithmic = PAIRS_PER_STEP * D * BWD_ALG_OPS_PER_ELEMENT_PER_LAUNCH
+        two_ms = gpu_ms(bwd_two_launches, reps=5, warm=2)
+        algorithmic = PAIRS_PER_STEP * D * BWD_OPS_PER_ELEMENT
         fwd_ms = gpu_ms(lambda: T.minkowski_distances(X.detach(), Y.detach(), P), reps=5)
         step_ms = ms / args.steps
         roofline = {"bound": "fp32_issue", "achieved": algorithmic / (k_ms * 1e-3) / 1e12, "peak": fp32_peak / 1e12,
                     "unit": "Tlane-op/s", "frac": algorithmic / (k_ms * 1e-3) / fp32_peak,
-                    "frac_executed": executed / (k_ms * 1e-3) / fp32_peak,
+                    "frac_executed": algorithmic / (k_ms * 1e-3) / fp32_peak,
                     "traffic": BWD_DRAM_TRAFFIC_BYTES_PER_BATCH * B,
-                    "kernel": "lp_backward_kernel (grad_x1 pass, p=3)", "ms_per_launch": k_ms,
-                    "algorithmic_work": "2 lane-ops per pair and feature per launch (one of the two gradients; the backward of "
-                                        "both counts 4 per pair and feature), 3 executed (subtract, d*|d|, fused multiply-add)",
+                    "kernel": "lp_backward_onepass_kernel (both gradients, p=3) with its finishing lp_backward_onepass_sum_kernel"
+                              if nbytes > 0 else "lp_backward_kernel, two launches",
+                    "ms_per_launch": k_ms, "two_launch_ms": two_ms,
+                    "algorithmic_work": "4 lane-ops per pair and feature for both gradients (subtract, d*|d|, one fused multiply-add "
+                                        "into each sum); the one-pass kernel executes exactly these, the two-launch form 6",
                     "step_frac_algorithmic": PAIRS_PER_STEP * D * 7 / (step_ms * 1e-3) / fp32_peak,
                     "backward_frac_algorithmic": PAIRS_PER_STEP * D * 4 / ((step_ms - fwd_ms) * 1e-3) / fp32_peak,
                     "forward_frac_algorithmic": PAIRS_PER_STEP * D * 3 / (fwd_ms * 1e-3) / fp32_peak,
@@ -763,7 +772,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         roofline_hbm = {"bound": "hbm", "achieved": BWD_BYTES_PER_LAUNCH / (k_ms * 1e-3) / 1e9, "peak": hbm_peak,
                         "unit": "GB/s", "frac": BWD_BYTES_PER_LAUNCH / (k_ms * 1e-3) / 1e9 / hbm_peak,
                         "traffic": BWD_DRAM_TRAFFIC_BYTES_PER_BATCH * B, "peak_source": hbm_src}
-        del out, g1
+        del out, g1, g2, scratch
         # ---- CPU baseline and parity on the row block: the reference's own operators ---------------
         threads = host_threads_everywhere()
         torch.set_num_threads(threads)

@@ -309,20 +309,29 @@ __global__ void __launch_bounds__(256) lp_backward_small_kernel(const BwdParams 
     const long long g0 = TRANS ? r : r * P.N2, gstep = TRANS ? P.N2 : 1;   // g[i][j]: i = r (rows) or i = s (columns)
     const T q = (T)P.q;
     T acc = T(0);
-    for (long long s = 0; s < P.NS; ++s) {
-        const T g = grad[g0 + s * gstep];
-        T c = g, o = T(0);
-        if (NEED_AUX) {
-            o = aux[g0 + s * gstep];
-            switch (P.coef_mode) {
-                case COEF_DIV_O: c = o == T(0) ? T(0) : b_div(g, o); break;
-                case COEF_DIV_O2: c = o == T(0) ? T(0) : b_div(g, o * o); break;
-                case COEF_DIV_POW: c = o == T(0) ? T(0) : b_div(g, b_pow(o, P.q)); break;
-                case COEF_MUL: c = g * o; break;
-                case COEF_ZERO_WHERE_O0: c = o == T(0) ? T(0) : g; break;
-                default: break;
-            }
+    // eight streamed rows at a time: all their loads are issued before the first term is added (the terms are still
+    // added in ascending order, so the sum keeps the tile kernel's bits); a walk that waits for each row's loads in
+    // turn is bound by their latency
+    constexpr int U = 8;
+    long long s = 0;
+    for (; s + U <= P.NS; s += U) {
+        T g[U], o[U], y[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            g[u] = grad[g0 + (s + u) * gstep];
+            o[u] = NEED_AUX ? aux[g0 + (s + u) * gstep] : T(0);
+            y[u] = stream[(s + u) * P.D];
         }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const T c = NEED_AUX ? bwd_coefficient<T>(P.coef_mode, g[u], o[u], P.q) : g[u];
+            bwd_accumulate<PHI, T>(acc, x, y[u], c, o[u], q, P.pow_spec);
+        }
+    }
+    for (; s < P.NS; ++s) {
+        const T g = grad[g0 + s * gstep];
+        const T o = NEED_AUX ? aux[g0 + s * gstep] : T(0);
+        const T c = NEED_AUX ? bwd_coefficient<T>(P.coef_mode, g, o, P.q) : g;
         bwd_accumulate<PHI, T>(acc, x, stream[s * P.D], c, o, q, P.pow_spec);
     }
     T v = acc * (T)P.post;

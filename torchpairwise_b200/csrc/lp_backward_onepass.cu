@@ -175,9 +175,9 @@ lp_backward_onepass_kernel(const __grid_constant__ CUtensorMap map_x2, const __g
 
 #pragma unroll 1
         for (int jg = 0; jg < OP_JT / 4; ++jg) {
-            float sj[4][4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
+                float sj[4];
                 const int j = jg * 4 + u;
                 const float4 yv = *reinterpret_cast<const float4 *>(ys + j * OP_FEAT + kofs);
                 const float y[4] = {yv.x, yv.y, yv.z, yv.w};
@@ -210,11 +210,11 @@ lp_backward_onepass_kernel(const __grid_constant__ CUtensorMap map_x2, const __g
                     for (int c = 0; c < 4; ++c) {
                         float lo, hi;
                         unpack2(sj2[c], lo, hi);
-                        sj[u][c] = lo + hi;
+                        sj[c] = lo + hi;
                     }
                 } else {
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) sj[u][c] = 0.f;
+                    for (int c = 0; c < 4; ++c) sj[c] = 0.f;
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         const float4 cv = *reinterpret_cast<const float4 *>(ct + j * OP_ROWS + h * 128 + lane * 4);
@@ -225,16 +225,15 @@ lp_backward_onepass_kernel(const __grid_constant__ CUtensorMap map_x2, const __g
                             for (int c = 0; c < 4; ++c) {
                                 const float term = onepass_term<PHI>(xr[h * 4 + r][c], y[c], cs[r], P.q, P.pow_spec);
                                 acc[h * 4 + r][c] += term;
-                                sj[u][c] += term;
+                                sj[c] += term;
                             }
                     }
                 }
+                // parked in the exchange buffer right away (the previous group's reads ended with a warp barrier)
+                *reinterpret_cast<float4 *>(red + lane * OP_RED_PITCH + u * 4) = make_float4(sj[0], sj[1], sj[2], sj[3]);
             }
-            // exchange: every lane writes its sums of (4 rows j) x (4 features); lanes l and l + 16 then add the even
+            // exchange: every lane has written its sums of (4 rows j) x (4 features); lanes l and l + 16 then add the even
             // and the odd lanes' contributions to one (j, feature) in ascending order, and the two are added
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-                *reinterpret_cast<float4 *>(red + lane * OP_RED_PITCH + u * 4) = make_float4(sj[u][0], sj[u][1], sj[u][2], sj[u][3]);
             __syncwarp();
             float tot = 0.f;
             const float *src = red + (lane >> 4) * OP_RED_PITCH + (lane & 15);

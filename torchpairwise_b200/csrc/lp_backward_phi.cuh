@@ -2,6 +2,7 @@
 // difference, the coefficient modes, and the packed two-lane float32 arithmetic.
 #pragma once
 #include "common.cuh"
+#include "packed_f32x2.cuh"
 
 #include <math.h>
 
@@ -61,34 +62,6 @@ __device__ __forceinline__ double b_log(double v) { return log(v); }
 __device__ __forceinline__ float b_pow(float a, double q) { return powf(a, (float)q); }
 __device__ __forceinline__ double b_pow(double a, double q) { return pow(a, q); }
 
-// Two float32 lanes per instruction (sm_100 packed arithmetic).  The FMA pipe retires the same number of lanes per
-// clock either way, but a packed instruction takes one issue slot for two results, which leaves the scheduler
-// room for the shared-memory loads and lets four warps per scheduler cover the arithmetic latency.
-typedef unsigned long long f32x2;
-__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
-    f32x2 r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ void unpack2(f32x2 v, float &lo, float &hi) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) {
-    f32x2 r;
-    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
-    f32x2 r;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
-    f32x2 r;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-    return r;
-}
-__device__ __forceinline__ f32x2 abs2(f32x2 a) { return a & 0x7fffffff7fffffffull; }
 
 template <typename T, int PHI> struct PackedPhi {
     static constexpr bool value = false;

@@ -3,6 +3,7 @@
 // epilogues are separate instantiations and leave the code of the stored-tile kernels untouched.
 #pragma once
 #include "common.cuh"
+#include "packed_f32x2.cuh"
 
 #include <math.h>
 
@@ -237,6 +238,14 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
 
     const int tid = threadIdx.x;
     const int ti = tid >> 4, tj = tid & 15;
+    // Packed form of the unweighted float32 p = 3 tile (full 128-byte chunks by TMA): a thread owns rows
+    // {32 a + 2 ti, 32 a + 2 ti + 1} and columns {32 c + 2 tj, 32 c + 2 tj + 1} instead of {ti + 16 a} and {tj + 16 c},
+    // so that two rows and two columns are adjacent words of the transposed operand tiles and fill the two lanes of
+    // the packed subtract / fused multiply-add without a register move.  Every pair still adds its features in
+    // ascending order with the same roundings, so the results are the scalar tile's bit for bit.
+    constexpr bool PK = (KIND == K_P3 && !WEIGHTED && sizeof(T) == 4 && USE_TMA && !PARTIAL && R == 8);
+    auto row_of = [&](int a) -> int { return PK ? 32 * (a >> 1) + 2 * ti + (a & 1) : ti + 16 * a; };
+    auto col_of = [&](int c) -> int { return PK ? 32 * (c >> 1) + 2 * tj + (c & 1) : tj + 16 * c; };
 
     long long tile = blockIdx.x;
     const long long tjx = tile % P.tiles_j;
@@ -262,6 +271,14 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
 #pragma unroll
         for (int c = 0; c < R; ++c) acc[a][c] = (KIND == K_MIN) ? T(INFINITY) : T(0);
     T nsq = T(0); // K_DOT: squared norm of the row this thread looks after
+    // packed accumulators: pa[a][c] = pairs (2a, 2c) and (2a+1, 2c+1), pb[a][c] = pairs (2a, 2c+1) and (2a+1, 2c)
+    f32x2 pa[PK ? R / 2 : 1][PK ? R / 2 : 1], pb[PK ? R / 2 : 1][PK ? R / 2 : 1];
+    if constexpr (PK) {
+#pragma unroll
+        for (int a = 0; a < R / 2; ++a)
+#pragma unroll
+            for (int c = 0; c < R / 2; ++c) { pa[a][c] = 0ull; pb[a][c] = 0ull; }
+    }
 
     if (USE_TMA) {
         if (tid == 0) {
@@ -337,6 +354,58 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
         // shapes output-bound; the others keep a constant trip count.
         const long long kleft = P.D - kbase;
         const int cmax = (PARTIAL && kleft < KC) ? (int)((kleft + VN - 1) / VN) : 8;
+        if constexpr (PK) {
+            // transpose both operand tiles in place: [128 rows][32 features] (swizzled) -> [32 features][128 rows].
+            // Consecutive lanes read consecutive rows of one 16-byte chunk (all banks) and write consecutive words.
+            {
+                const uint32_t trow = tid & 127u, th = tid >> 7;
+                float4 xv[4], yv[4];
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    xv[cc] = *reinterpret_cast<const float4 *>(xs + swz128(trow, th * 4 + cc));
+                    yv[cc] = *reinterpret_cast<const float4 *>(ys + swz128(trow, th * 4 + cc));
+                }
+                __syncthreads();
+                float *xw = reinterpret_cast<float *>(const_cast<unsigned char *>(xs)) + (th * 16) * 128 + trow;
+                float *yw = reinterpret_cast<float *>(const_cast<unsigned char *>(ys)) + (th * 16) * 128 + trow;
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    xw[(cc * 4 + 0) * 128] = xv[cc].x; xw[(cc * 4 + 1) * 128] = xv[cc].y;
+                    xw[(cc * 4 + 2) * 128] = xv[cc].z; xw[(cc * 4 + 3) * 128] = xv[cc].w;
+                    yw[(cc * 4 + 0) * 128] = yv[cc].x; yw[(cc * 4 + 1) * 128] = yv[cc].y;
+                    yw[(cc * 4 + 2) * 128] = yv[cc].z; yw[(cc * 4 + 3) * 128] = yv[cc].w;
+                }
+                __syncthreads();
+            }
+            const float *xt = reinterpret_cast<const float *>(xs) + 2 * ti;
+            const float *yt = reinterpret_cast<const float *>(ys) + 2 * tj;
+#pragma unroll 2
+            for (int e = 0; e < 32; ++e) {
+                f32x2 x2[R / 2], y2[R / 2], ys2[R / 2];
+#pragma unroll
+                for (int a = 0; a < R / 2; ++a) x2[a] = *reinterpret_cast<const f32x2 *>(xt + e * 128 + 32 * a);
+#pragma unroll
+                for (int c = 0; c < R / 2; ++c) {
+                    y2[c] = *reinterpret_cast<const f32x2 *>(yt + e * 128 + 32 * c);
+                    float lo, hi;
+                    unpack2(y2[c], lo, hi);
+                    ys2[c] = pack2(hi, lo);
+                }
+#pragma unroll
+                for (int a = 0; a < R / 2; ++a)
+#pragma unroll
+                    for (int c = 0; c < R / 2; ++c) {
+                        // |d|^3 = (d |d|) d: the scalar multiply takes |.| as an operand modifier
+                        float lo, hi;
+                        const f32x2 da = sub2(x2[a], y2[c]);
+                        unpack2(da, lo, hi);
+                        pa[a][c] = fma2(pack2(lo * fabsf(lo), hi * fabsf(hi)), da, pa[a][c]);
+                        const f32x2 db = sub2(x2[a], ys2[c]);
+                        unpack2(db, lo, hi);
+                        pb[a][c] = fma2(pack2(lo * fabsf(lo), hi * fabsf(hi)), db, pb[a][c]);
+                    }
+            }
+        } else {
 #pragma unroll 1
         for (int c = 0; c < cmax; ++c) {
             V xa[R];
@@ -365,6 +434,7 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
                 }
             }
         }
+        }
         if (KIND == K_DOT && tid < 2 * TILE) {
             // thread t < TILE sums squares of x1 row t, thread TILE + t of x2 row t
             const unsigned char *rows = tid < TILE ? xs : ys;
@@ -389,6 +459,18 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
         if (tid < 2 * TILE) norms[tid] = nsq;
         __syncthreads();
     }
+    if constexpr (PK) {
+#pragma unroll
+        for (int a = 0; a < R / 2; ++a)
+#pragma unroll
+            for (int c = 0; c < R / 2; ++c) {
+                float lo, hi;
+                unpack2(pa[a][c], lo, hi);
+                acc[2 * a][2 * c] = lo; acc[2 * a + 1][2 * c + 1] = hi;
+                unpack2(pb[a][c], lo, hi);
+                acc[2 * a][2 * c + 1] = lo; acc[2 * a + 1][2 * c] = hi;
+            }
+    }
     apply_root<T, R, KIND>(acc, P);
 
     if constexpr (EPI == EPI_ROWMIN) {
@@ -404,7 +486,7 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
                 unsigned long long best = ~0ull;
 #pragma unroll
                 for (int rj = 0; rj < R; ++rj) {
-                    const long long j = j0 + tj + 16 * rj;
+                    const long long j = j0 + col_of(rj);
                     const float v = (float)finish<T, OutT, KIND>(acc[ri][rj], T(0), T(0), P);
                     const unsigned long long key = ((unsigned long long)__float_as_uint(v) << 32) | (unsigned long long)(uint32_t)j;
                     if (j < P.N2 && key < best) best = key;
@@ -414,7 +496,7 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
                     const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, off);
                     best = other < best ? other : best;
                 }
-                const long long i = i0 + ti + 16 * ri;
+                const long long i = i0 + row_of(ri);
                 if (tj == 0 && i < P.N1) atomicMin(keys + i, best);
             }
             return;
@@ -434,7 +516,7 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
                 for (int ri = 0; ri < R; ++ri)
 #pragma unroll
                     for (int rj = 0; rj < R; ++rj)
-                        smem[(ti + 16 * ri) * ROWB + tj + 16 * rj] =
+                        smem[(row_of(ri)) * ROWB + col_of(rj)] =
                             static_cast<T>(finish<T, OutT, KIND>(acc[ri][rj], T(0), T(0), P)) <= thr ? 1 : 0;
                 __syncthreads();
                 for (int idx = tid; idx < TILE * (TILE / 16); idx += kThreads) {
@@ -446,11 +528,11 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
             } else {
 #pragma unroll
                 for (int ri = 0; ri < R; ++ri) {
-                    const long long i = i0 + ti + 16 * ri;
+                    const long long i = i0 + row_of(ri);
                     if (i >= P.N1) continue;
 #pragma unroll
                     for (int rj = 0; rj < R; ++rj) {
-                        const long long j = j0 + tj + 16 * rj;
+                        const long long j = j0 + col_of(rj);
                         if (j < P.N2) mout[i * P.N2 + j] = static_cast<T>(finish<T, OutT, KIND>(acc[ri][rj], T(0), T(0), P)) <= thr ? 1 : 0;
                     }
                 }
@@ -465,12 +547,12 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
         OutT *cond = reinterpret_cast<OutT *>(P.out) + b * (N * (N - 1) / 2);
 #pragma unroll
         for (int ri = 0; ri < R; ++ri) {
-            const long long i = i0 + ti + 16 * ri;
+            const long long i = i0 + row_of(ri);
             if (i >= N) continue;
             OutT *crow = cond + i * (2 * N - i - 1) / 2 - i - 1;
 #pragma unroll
             for (int rj = 0; rj < R; ++rj) {
-                const long long j = j0 + tj + 16 * rj;
+                const long long j = j0 + col_of(rj);
                 if (j > i && j < N) crow[j] = finish<T, OutT, KIND>(acc[ri][rj], T(0), T(0), P);
             }
         }
@@ -486,11 +568,11 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
         __syncthreads();
 #pragma unroll
         for (int ri = 0; ri < R; ++ri) {
-            const T n1 = KIND == K_DOT ? norms[ti + 16 * ri] : T(0);
+            const T n1 = KIND == K_DOT ? norms[row_of(ri)] : T(0);
 #pragma unroll
             for (int rj = 0; rj < R; ++rj) {
-                const T n2 = KIND == K_DOT ? norms[TILE + tj + 16 * rj] : T(0);
-                *reinterpret_cast<OutT *>(smem + (ti + 16 * ri) * ROWB + (tj + 16 * rj) * 4) =
+                const T n2 = KIND == K_DOT ? norms[TILE + col_of(rj)] : T(0);
+                *reinterpret_cast<OutT *>(smem + (row_of(ri)) * ROWB + (col_of(rj)) * 4) =
                     finish<T, OutT, KIND>(acc[ri][rj], n1, n2, P);
             }
         }
@@ -507,14 +589,14 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
     }
 #pragma unroll
     for (int ri = 0; ri < R; ++ri) {
-        const long long i = i0 + ti + 16 * ri;
+        const long long i = i0 + row_of(ri);
         if (i >= P.N1) continue;
-        const T n1 = KIND == K_DOT ? norms[ti + 16 * ri] : T(0);
+        const T n1 = KIND == K_DOT ? norms[row_of(ri)] : T(0);
 #pragma unroll
         for (int rj = 0; rj < R; ++rj) {
-            const long long j = j0 + tj + 16 * rj;
+            const long long j = j0 + col_of(rj);
             if (j >= P.N2) continue;
-            const T n2 = KIND == K_DOT ? norms[TILE + tj + 16 * rj] : T(0);
+            const T n2 = KIND == K_DOT ? norms[TILE + col_of(rj)] : T(0);
             out[i * P.N2 + j] = finish<T, OutT, KIND>(acc[ri][rj], n1, n2, P);
         }
     }

@@ -16,7 +16,10 @@ __device__ __forceinline__ float count_to_float(int v) {
     return FAST ? __int_as_float(0x4B000000 | v) - 8388608.f : (float)v;
 }
 
-template <bool FAST = false>
+// INV: -1 = decide per call from inv_d, 1 = D is a power of two and inv_d its reciprocal, 0 = divide.  A caller that
+// knows which holds for a whole tile passes it as a constant: decided per element, the division sequence is
+// if-converted and executed next to the multiplication for every element.
+template <bool FAST = false, int INV = -1>
 __device__ __forceinline__ float bool_epilogue(int metric, int n11, int a, int b, int D, float inv_d) {
     const int nxor_i = a + b - 2 * n11;
     const int nor_i = a + b - n11;
@@ -29,8 +32,14 @@ __device__ __forceinline__ float bool_epilogue(int metric, int n11, int a, int b
         case TPW_BOOL_NE_SUM: return fxor;
         case TPW_BOOL_EQ_SUM: return feq;
         // dividing by a power of two is exact, and so is multiplying by its reciprocal
-        case TPW_BOOL_EQ_MEAN: return inv_d != 0.f ? __fmul_rn(feq, inv_d) : __fdiv_rn(feq, fD);
-        case TPW_BOOL_NE_MEAN: return inv_d != 0.f ? __fmul_rn(fxor, inv_d) : __fdiv_rn(fxor, fD);
+        case TPW_BOOL_EQ_MEAN:
+            if (INV == 1) return __fmul_rn(feq, inv_d);
+            if (INV == 0) return __fdiv_rn(feq, fD);
+            return inv_d != 0.f ? __fmul_rn(feq, inv_d) : __fdiv_rn(feq, fD);
+        case TPW_BOOL_NE_MEAN:
+            if (INV == 1) return __fmul_rn(fxor, inv_d);
+            if (INV == 0) return __fdiv_rn(fxor, fD);
+            return inv_d != 0.f ? __fmul_rn(fxor, inv_d) : __fdiv_rn(fxor, fD);
         case TPW_BOOL_JACCARD: return f_or != 0.f ? __fdiv_rn(fxor, f_or) : 0.f;
         case TPW_BOOL_KULSINSKI: return __fdiv_rn(__fadd_rn(__fsub_rn(fxor, fand), fD), __fadd_rn(fxor, fD));
         case TPW_BOOL_KULCZYNSKI1: return __fdiv_rn(fand, fxor);

@@ -20,6 +20,8 @@
 // barrier, tensor memory is released and the device status word reports the site.
 #include "bool_epilogue.cuh"
 #include "common.cuh"
+
+#include <type_traits>
 #include "tcgen05.cuh"
 
 #include <stdlib.h>
@@ -213,6 +215,10 @@ bool_count_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
             tc_fence_after();
             float *orow = P.out + (b * P.N1 + (row_ok ? i : 0)) * P.N2;
             const long long row_base = tm * BM + q * 32;
+            // the mean metrics multiply by 1 / D where D is a power of two and divide otherwise: decided here, once per
+            // tile, so that the per-element code holds one of the two
+            auto drain = [&](auto inv_tag) {
+                constexpr int INV = decltype(inv_tag)::value;
 #pragma unroll 1
             for (int c = cpart * NCB; c < (cpart + 1) * NCB; ++c) {
                 uint32_t r[32];
@@ -226,10 +232,10 @@ bool_count_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
                     for (int v = 0; v < 8; ++v) {
                         const int4 nb = *reinterpret_cast<const int4 *>(popw + (c - cpart * NCB) * 32 + 4 * v);
                         float4 o;
-                        o.x = bool_epilogue<true>(METRIC, (int)r[4 * v + 0], pa, nb.x, D, P.inv_d);
-                        o.y = bool_epilogue<true>(METRIC, (int)r[4 * v + 1], pa, nb.y, D, P.inv_d);
-                        o.z = bool_epilogue<true>(METRIC, (int)r[4 * v + 2], pa, nb.z, D, P.inv_d);
-                        o.w = bool_epilogue<true>(METRIC, (int)r[4 * v + 3], pa, nb.w, D, P.inv_d);
+                        o.x = bool_epilogue<true, INV>(METRIC, (int)r[4 * v + 0], pa, nb.x, D, P.inv_d);
+                        o.y = bool_epilogue<true, INV>(METRIC, (int)r[4 * v + 1], pa, nb.y, D, P.inv_d);
+                        o.z = bool_epilogue<true, INV>(METRIC, (int)r[4 * v + 2], pa, nb.z, D, P.inv_d);
+                        o.w = bool_epilogue<true, INV>(METRIC, (int)r[4 * v + 3], pa, nb.w, D, P.inv_d);
                         *reinterpret_cast<float4 *>(stg + lane * 128 + ((v ^ (lane & 7)) << 4)) = o;
                     }
                     __syncwarp();
@@ -246,9 +252,16 @@ bool_count_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
 #pragma unroll
                     for (int v = 0; v < 32; ++v) {
                         const long long j = j0 + v;
-                        if (j < P.N2) orow[j] = bool_epilogue<true>(METRIC, (int)r[v], pa, popw[(c - cpart * NCB) * 32 + v], D, P.inv_d);
+                        if (j < P.N2) orow[j] = bool_epilogue<true, INV>(METRIC, (int)r[v], pa, popw[(c - cpart * NCB) * 32 + v], D, P.inv_d);
                     }
                 }
+            }
+            };
+            if (METRIC == TPW_BOOL_EQ_MEAN || METRIC == TPW_BOOL_NE_MEAN) {
+                if (P.inv_d != 0.f) drain(std::integral_constant<int, 1>{});
+                else drain(std::integral_constant<int, 0>{});
+            } else {
+                drain(std::integral_constant<int, -1>{});
             }
             // this warp has drained its part of accumulator `a`
             tc_fence_before();

@@ -159,6 +159,16 @@ def test_boolean_tensor_core_counts_equal_popcount_counts(tpw, monkeypatch, shap
             ref = fn(x1, x2)
             monkeypatch.delenv("TPW_DISABLE_BOOL_TC", raising=False)
             assert torch.equal(got, ref), name
+        # the staged tiles leave either through the warp's own stores or through the output's tensor map (the default
+        # depends on the metric): both ways write the same bits, ragged last rows and columns included
+        for name in ("hamming_distances", "jaccard_distances", "pwand_sum"):
+            fn = getattr(tpw, name)
+            res = []
+            for how in ("plain", "tma"):
+                monkeypatch.setenv("TPW_BOOL_TC_STORES", how)
+                res.append(fn(x1, x2))
+            monkeypatch.delenv("TPW_BOOL_TC_STORES", raising=False)
+            assert torch.equal(res[0], res[1]), name
     # against the oracle's integer counts directly
     a, c = (x1, x2) if x1.dim() == 2 else (x1[0], x2[0])
     assert np.array_equal(tpw.jaccard_distances(a, c).cpu().numpy(), O.boolean_metric("jaccard", a.cpu().numpy(), c.cpu().numpy()))

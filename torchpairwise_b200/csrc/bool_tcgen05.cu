@@ -40,7 +40,7 @@ constexpr int OFF_BAR = kStages * STAGE_BYTES;
 // barriers: full[3], empty[3], tmem_full[2], tmem_empty[2]; then the TMEM base address and the abort flag
 constexpr int OFF_TMEM_PTR = OFF_BAR + (2 * kStages + 4) * 8;
 constexpr int OFF_ABORT = OFF_TMEM_PTR + 4;
-constexpr int OFF_STAGE = (OFF_ABORT + 4 + 127) / 128 * 128;   // per epilogue warp a 32 x 32 float staging block
+constexpr int OFF_STAGE = (OFF_ABORT + 4 + 1023) / 1024 * 1024; // per epilogue warp a 32 x 32 float staging block (1024-byte aligned: it is also the source of a swizzled TMA store)
 constexpr int kEpilogueWarps = 16;            // four per TMEM lane quarter, each draining a quarter of the columns
 constexpr int OFF_POP = OFF_STAGE + kEpilogueWarps * 4096;      // per epilogue warp the 64 x2 row counts of its column quarter
 constexpr int SMEM_BYTES = OFF_POP + kEpilogueWarps * 256;
@@ -56,6 +56,7 @@ struct BoolTcParams {
     long long tiles_m, tiles_n, tiles;
     int metric;
     int vec_store;   // N2 % 4 == 0, out and pop2 16-byte aligned
+    int tma_store;   // the staged 32 x 32 blocks leave through the output's tensor map
     float inv_d;     // 1/D when D is a power of two, else 0
     int *status;
 };
@@ -81,7 +82,7 @@ __device__ __forceinline__ uint32_t make_idesc_i8(int M, int N) {
 template <int METRIC>
 __global__ void __launch_bounds__(kThreads, 1)
 bool_count_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
-                          const BoolTcParams P) {
+                          const __grid_constant__ CUtensorMap map_out, const BoolTcParams P) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + OFF_BAR);
@@ -227,27 +228,45 @@ bool_count_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
                 const long long j0 = tn * BN + c * 32;
                 if (j0 >= P.N2) continue;
                 if (P.vec_store && j0 + 32 <= P.N2) {
-                    // this thread's row, staged with a 16-byte-chunk XOR swizzle ...
+                    // this thread's row ...
+                    float4 o[8];
 #pragma unroll
                     for (int v = 0; v < 8; ++v) {
                         const int4 nb = *reinterpret_cast<const int4 *>(popw + (c - cpart * NCB) * 32 + 4 * v);
-                        float4 o;
-                        o.x = bool_epilogue<true, INV>(METRIC, (int)r[4 * v + 0], pa, nb.x, D, P.inv_d);
-                        o.y = bool_epilogue<true, INV>(METRIC, (int)r[4 * v + 1], pa, nb.y, D, P.inv_d);
-                        o.z = bool_epilogue<true, INV>(METRIC, (int)r[4 * v + 2], pa, nb.z, D, P.inv_d);
-                        o.w = bool_epilogue<true, INV>(METRIC, (int)r[4 * v + 3], pa, nb.w, D, P.inv_d);
-                        *reinterpret_cast<float4 *>(stg + lane * 128 + ((v ^ (lane & 7)) << 4)) = o;
+                        o[v].x = bool_epilogue<true, INV>(METRIC, (int)r[4 * v + 0], pa, nb.x, D, P.inv_d);
+                        o[v].y = bool_epilogue<true, INV>(METRIC, (int)r[4 * v + 1], pa, nb.y, D, P.inv_d);
+                        o[v].z = bool_epilogue<true, INV>(METRIC, (int)r[4 * v + 2], pa, nb.z, D, P.inv_d);
+                        o[v].w = bool_epilogue<true, INV>(METRIC, (int)r[4 * v + 3], pa, nb.w, D, P.inv_d);
                     }
-                    __syncwarp();
-                    // ... and written out four full 128-byte row segments per instruction
+                    if (P.tma_store) {
+                        // by now the copy engine has read the previous block out of the staging area
+                        if (lane == 0) tma_store_wait_read();
+                        __syncwarp();
+                    }
+                    // ... staged with a 16-byte-chunk XOR swizzle ...
 #pragma unroll
-                    for (int itr = 0; itr < 8; ++itr) {
-                        const int rr = itr * 4 + (lane >> 3), cc = lane & 7;
-                        const float4 o = *reinterpret_cast<const float4 *>(stg + rr * 128 + ((cc ^ (rr & 7)) << 4));
-                        if (row_base + rr < P.N1)
-                            __stcs(reinterpret_cast<float4 *>(P.out + (b * P.N1 + row_base + rr) * P.N2 + j0) + cc, o);
+                    for (int v = 0; v < 8; ++v) *reinterpret_cast<float4 *>(stg + lane * 128 + ((v ^ (lane & 7)) << 4)) = o[v];
+                    if (P.tma_store) {
+                        // ... which is the layout of a 128-byte swizzled 32 x 32 box: one lane hands the block to the copy
+                        // engine (rows past N1 are clipped by the tensor map) and the warp goes on to its next block
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_3d(&map_out, stg, (int)j0, (int)row_base, (int)b);
+                            tma_store_commit();
+                        }
+                    } else {
+                        __syncwarp();
+                        // ... and written out four full 128-byte row segments per instruction
+#pragma unroll
+                        for (int itr = 0; itr < 8; ++itr) {
+                            const int rr = itr * 4 + (lane >> 3), cc = lane & 7;
+                            const float4 o = *reinterpret_cast<const float4 *>(stg + rr * 128 + ((cc ^ (rr & 7)) << 4));
+                            if (row_base + rr < P.N1)
+                                __stcs(reinterpret_cast<float4 *>(P.out + (b * P.N1 + row_base + rr) * P.N2 + j0) + cc, o);
+                        }
+                        __syncwarp();
                     }
-                    __syncwarp();
                 } else if (row_ok) {
 #pragma unroll
                     for (int v = 0; v < 32; ++v) {
@@ -270,6 +289,7 @@ bool_count_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
         }
     }
 
+    if (warp >= 2 && lane == 0 && P.tma_store) tma_store_wait_read();   // shared memory stays valid until the last block is read
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -322,12 +342,26 @@ extern "C" int tpw_bool_metric_forward_tc(int metric, const uint8_t *x1, const u
     if (st != TPW_OK) return st;
     st = make_tensor_map_3d(&my, x2, 1, D, N2, B, BKB, BN, true);
     if (st != TPW_OK) return st;
+    CUtensorMap mo;
+    memset(&mo, 0, sizeof(mo));
+    // Metrics whose epilogue divides keep a warp busy long enough per block for the copy engine to drain the staging
+    // area behind it (jaccard at 65536 x 16384 x 1024: 2.06 -> 1.80 ms); for the sums and the power-of-two means the
+    // warp's own 128-bit stores are faster (hamming: 1.32 against 1.49 ms).  TPW_BOOL_TC_STORES=plain|tma overrides.
+    const bool cheap = metric == TPW_BOOL_AND_SUM || metric == TPW_BOOL_OR_SUM || metric == TPW_BOOL_XOR_SUM ||
+                       metric == TPW_BOOL_EQ_SUM || metric == TPW_BOOL_NE_SUM ||
+                       ((metric == TPW_BOOL_EQ_MEAN || metric == TPW_BOOL_NE_MEAN) && P.inv_d != 0.f);
+    const char *stores = getenv("TPW_BOOL_TC_STORES");
+    P.tma_store = P.vec_store && (stores ? stores[0] == 't' : !cheap) ? 1 : 0;
+    if (P.tma_store) {
+        st = make_tensor_map_3d(&mo, out, 4, N2, N1, B, 32, 32, true);
+        if (st != TPW_OK) return st;
+    }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const long long grid = P.tiles < sm_count() ? P.tiles : sm_count();
 #define TPW_BOOL_TC_CASE(M)                                                                                                    \
     case M:                                                                                                                    \
         TPW_CUDA_OK(cudaFuncSetAttribute(bool_count_tcgen05_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC)); \
-        bool_count_tcgen05_kernel<M><<<(unsigned)grid, kThreads, SMEM_ALLOC, s>>>(mx, my, P);                                  \
+        bool_count_tcgen05_kernel<M><<<(unsigned)grid, kThreads, SMEM_ALLOC, s>>>(mx, my, mo, P);                                  \
         break
     switch (metric) {
         TPW_BOOL_TC_CASE(TPW_BOOL_AND_SUM); TPW_BOOL_TC_CASE(TPW_BOOL_OR_SUM); TPW_BOOL_TC_CASE(TPW_BOOL_XOR_SUM);

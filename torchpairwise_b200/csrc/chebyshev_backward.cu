@@ -217,7 +217,8 @@ chebyshev_match_kernel(const __grid_constant__ CUtensorMap map1, const __grid_co
 
 // ---- scatter ---------------------------------------------------------------------------------------------------------
 constexpr int SR = 128;          // gradient rows per CTA
-constexpr int SQ = 4;            // threads per gradient row, each owning a quarter of the CTA's features
+constexpr int SQ = 4;            // threads per gradient row (all of them stage the pairs)
+constexpr int WQ = 4;            // of which this many walk over the pairs, each owning SD / WQ of the CTA's features
 constexpr int STHR = SR * SQ;    // 512 threads: sixteen warps keep the shared-memory read-modify-write chains overlapped
 constexpr int SD = 256;          // features per CTA
 constexpr int SP = 32;           // pairs per gradient row staged at a time
@@ -267,34 +268,46 @@ __global__ void __launch_bounds__(STHR, 1) chebyshev_scatter_kernel(const Scatte
     const float *grad = P.grad + b * P.N1 * P.N2;
     const uint32_t *code = P.code + b * P.N1 * P.N2;
     const int r = tid % SR, q = tid / SR;        // a warp holds 32 consecutive rows of one quarter
-    const int klo = q * (SD / SQ), khi = (klo + SD / SQ) < kn ? (klo + SD / SQ) : kn;
     float *mine = accs + r * ACC_STRIDE;
     const long long NS = COLS ? P.N1 : P.N2;     // length of the walk
 
-    // staging: element e of a tile is (row e / 32, step e % 32) for rows, (step e / 128, column e % 128) for columns,
-    // so that consecutive threads read consecutive addresses of g and code
+    // staging: element e = tid + u * STHR of a tile is (row e / SP, step e % SP) for rows and (step e / SR, column
+    // e % SR) for columns, so that consecutive threads read consecutive addresses of g and code.  Everything that does
+    // not depend on the tile is worked out once: a thread's step (column) is fixed, its rows (steps) advance by a
+    // constant, so a tile costs it one pointer bump and one predicate per element.
     constexpr int PER = SR * SP / STHR;          // 8 elements of each array per thread
+    constexpr int UR = COLS ? STHR / SR : STHR / SP;      // rows (steps) between a thread's consecutive elements
+    const int fix = COLS ? tid % SR : tid % SP;           // column of the gradient row block / step inside the tile
+    const int var0 = COLS ? tid / SR : tid / SP;          // first step / first row
+    // offset of element u = 0 of tile s0 = 0, then per element and per tile
+    const long long off0 = COLS ? (long long)var0 * P.N2 + r0 + fix : (r0 + var0) * P.N2 + fix;
+    const long long off_u = (long long)UR * P.N2;
+    const long long off_tile = COLS ? (long long)SP * P.N2 : (long long)SP;
+    const bool fix_ok = COLS ? (r0 + fix < P.N2) : true;
+    const long long var_end = COLS ? P.N1 : P.N1 - r0;    // rows: row index below this; columns: step s0 + step below this
+    const int sm0 = COLS ? fix * (SP + 1) + var0 : var0 * (SP + 1) + fix;
+    constexpr int sm_u = COLS ? UR : UR * (SP + 1);
     float gr[PER];
     uint32_t cr[PER];
     auto fetch = [&](long long s0) {
+        const float *gp = grad + off0 + (s0 / SP) * off_tile;
+        const uint32_t *cp = code + off0 + (s0 / SP) * off_tile;
+        const bool tile_ok = COLS ? fix_ok : (s0 + fix < P.N2);
+        const long long first = COLS ? s0 + var0 : (long long)var0;
 #pragma unroll
         for (int u = 0; u < PER; ++u) {
-            const int e = tid + u * STHR;
-            long long i, j;
-            if (!COLS) { i = r0 + e / SP; j = s0 + e % SP; }
-            else       { i = s0 + e / SR; j = r0 + e % SR; }
-            const bool ok = i < P.N1 && j < P.N2;
-            gr[u] = ok ? __ldg(grad + i * P.N2 + j) : 0.f;
-            cr[u] = ok ? __ldg(code + i * P.N2 + j) : kSkip;
+            const bool ok = tile_ok && first + (long long)u * UR < var_end;
+            gr[u] = ok ? __ldg(gp) : 0.f;
+            cr[u] = ok ? __ldg(cp) : kSkip;
+            gp += off_u;
+            cp += off_u;
         }
     };
     auto stash = [&]() {
 #pragma unroll
         for (int u = 0; u < PER; ++u) {
-            const int e = tid + u * STHR;
-            const int rr = COLS ? e % SR : e / SP, ss = COLS ? e / SR : e % SP;
-            gs[rr * (SP + 1) + ss] = gr[u];
-            cs[rr * (SP + 1) + ss] = cr[u];
+            gs[sm0 + u * sm_u] = gr[u];
+            cs[sm0 + u * sm_u] = cr[u];
         }
     };
     fetch(0);
@@ -303,20 +316,26 @@ __global__ void __launch_bounds__(STHR, 1) chebyshev_scatter_kernel(const Scatte
         stash();
         __syncthreads();
         if (s0 + SP < NS) fetch(s0 + SP);
-        if (klo < khi) {
+        if (q < WQ) {
+            // WQ walkers per gradient row, each owning SD / WQ features: a pair costs a walker a load, a subtract and an
+            // unsigned compare unless its coordinate falls into the walker's range
+            constexpr int WD = SD / WQ;
+            const int kq = k0 + q * WD;
+            const int kw = kn - q * WD < WD ? kn - q * WD : WD;     // features of this walker that exist (may be <= 0)
+            float *wmine = mine + q * WD;
 #pragma unroll 8
             for (int ss = 0; ss < SP; ++ss) {
                 const uint32_t cd = cs[r * (SP + 1) + ss];
-                const int k = (int)(cd & 0xffffu) - k0;
                 if (cd < kTied) {
-                    if (k >= klo && k < khi) {
+                    const int k = (int)(cd & 0xffffu) - kq;
+                    if ((unsigned)k < (unsigned)(kw > 0 ? kw : 0)) {
                         const float g = gs[r * (SP + 1) + ss];
-                        mine[k] += __uint_as_float(__float_as_uint(g) ^ ((cd ^ (COLS ? 0x80000000u : 0u)) & 0x80000000u));
+                        wmine[k] += __uint_as_float(__float_as_uint(g) ^ ((cd ^ (COLS ? 0x80000000u : 0u)) & 0x80000000u));
                     }
-                } else if (cd == kTied) {
+                } else if (cd == kTied && kw > 0) {
                     const long long i = COLS ? s0 + ss : r0 + r, j = COLS ? r0 + r : s0 + ss;
-                    scatter_tied(mine, P.x1 + (b * P.N1 + i) * P.D, P.x2 + (b * P.N2 + j) * P.D, P.fwd[(b * P.N1 + i) * P.N2 + j],
-                                 gs[r * (SP + 1) + ss], k0, klo, khi, COLS);
+                    scatter_tied(wmine, P.x1 + (b * P.N1 + i) * P.D, P.x2 + (b * P.N2 + j) * P.D, P.fwd[(b * P.N1 + i) * P.N2 + j],
+                                 gs[r * (SP + 1) + ss], kq, 0, kw, COLS);
                 }
             }
         }

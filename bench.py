@@ -62,10 +62,10 @@ HAUSDORFF_EXECUTED_OPS = 7
 # both gradients written
 BWD_BYTES_PER_LAUNCH = 4 * (2 * B * N1 * N2 + 2 * B * N1 * D + 2 * B * N2 * D)
 # dram__bytes_read.sum + dram__bytes_write.sum of the backward call measured by ncu at batch 4
-# (profiles/lp_kernels_c2_minkowski_p3.md): 848.7 MB in the one-pass kernel (gradient and forward output streamed
-# once, 268 MB of row-block sums written) + 285 MB in the finishing kernel that reads them back; both grow in
+# (profiles/lp_kernels_c2_minkowski_p3.md): 831.9 MB in the one-pass kernel (gradient and forward output streamed
+# once, 256 MB of row-block sums written) + 281.3 MB in the finishing kernel that reads them back; both grow in
 # proportion to the batch
-BWD_DRAM_TRAFFIC_BYTES_PER_BATCH = (848.7e6 + 285.0e6) / 4
+BWD_DRAM_TRAFFIC_BYTES_PER_BATCH = (831.9e6 + 281.3e6) / 4
 
 REF_SO = ROOT / "oracle" / "_ref" / "torchpairwise_ref.so"
 

@@ -7,14 +7,16 @@
 // feature in each launch.  Here a pair's term coef * phi is formed once and added to both sums: 4 operations.
 //
 // A CTA of 16 warps owns 256 rows i and 64 features k and walks over all rows j, 32 per stage (TMA, two-stage mbarrier
-// ring: the x2 rows, and the 256 x 32 tiles of the upstream gradient and of the auxiliary matrix, stored with the
-// 128-byte swizzle and turned into coefficients in place).  A thread holds 16 rows i x 2 features of x1 and of the
-// grad_x1 sums in registers for the whole walk (lanes 0-15 of a warp are 16 row groups, the two half warps and the
-// sixteen warps are thirty-two pairs of features), so grad_x1 needs no exchange at all.  For grad_x2 a thread has
-// the sum over its own 16 rows; per four rows j the row groups of a half warp exchange these through shared memory,
-// the sixteen contributions of one (j, k) are added in a fixed order, and the CTA's sum over its 256 rows goes to a
-// scratch array [B][row blocks][N2][D].  A second kernel adds the row blocks in ascending order: no float atomics, every
-// sum in a fixed order, bit-reproducible from run to run.
+// ring: the x2 rows, and the 256 x 32 tiles of the upstream gradient and of the auxiliary matrix with the 128-byte
+// swizzle).  Every stage the CTA turns the two tiles into a coefficient tile stored transposed, [32 rows j][256 rows
+// i], so that the coefficients of two adjacent rows i for one j are one 8-byte word.  A warp owns four features; a
+// thread holds 8 rows i (4 lane, 4 lane + 1, ..., and the same 128 rows further on) x 4 features of x1 and of the
+// grad_x1 sums in registers for the whole walk, as packed pairs of adjacent ROWS, so the packed subtract and fused
+// multiply-adds take their coefficient pair straight from the tile, and grad_x1 needs no exchange at all.  For
+// grad_x2 a thread has the sum over its own 8 rows; it parks the four sums of each row j in a per-warp exchange
+// buffer, per four rows j the 32 lanes' contributions to one (j, k) are added in a fixed order, and the CTA's sum over
+// its 256 rows goes to a scratch array [B][row blocks][N2][D].  A second kernel adds the row blocks in ascending
+// order: no float atomics, every sum in a fixed order, bit-reproducible from run to run.
 #include "common.cuh"
 #include "lp_backward_phi.cuh"
 

@@ -16,8 +16,14 @@
 // rows and features past the edge, and zeros add nothing to a count.  Every CTA loads its own tiles with plain
 // per-CTA TMA loads from this GPU's memory.
 //
-// Every wait is bounded; a role that gives up raises a CTA-wide abort flag, everybody falls through to the final
-// barrier, tensor memory is released and the device status word reports the site.
+// An epilogue warp stages its 32 x 32 block of results in shared memory (128-byte swizzle) and writes it out either
+// with its own 128-bit stores or, for the metrics whose arithmetic is long enough to hide it, by handing the block to
+// the copy engine (a TMA store on the output's tensor map, which also clips the rows past N1).
+//
+// Every mbarrier wait is bounded; a role that gives up raises a CTA-wide abort flag, everybody falls through to the
+// final barrier, tensor memory is released and the device status word reports the site.  The one wait without a
+// bound of its own is cp.async.bulk.wait_group.read, which returns when the copy engine has read a block this warp
+// committed itself.
 #include "bool_epilogue.cuh"
 #include "common.cuh"
 

@@ -488,7 +488,7 @@ TPW_API int tpw_haversine_backward(int dtype, const void *grad, const void *x1, 
  * row minimum equals the maximum.  order1/order2 (int64 [B,M1] / [B,M2], may be NULL) give
  * each point's visiting position when the caller shuffles; ties then follow visiting order.
  * `scratch` holds tpw_hausdorff_scratch_bytes() bytes (8 per set pair plus 8 per x1 point of every set
- * pair), 8-byte aligned, and needs no initialisation.  float64 clouds of up to 8 coordinates keep every
+ * pair), 8-byte aligned, and needs no initialisation.  float64 clouds of up to 16 coordinates keep every
  * row's exact minimum there and scan them once per set pair (TPW_HAUSDORFF_PLAIN_F64=1, or scratch ==
  * NULL, selects the one-CTA-per-pair kernel instead; same bits).  For float32 the hot loop forms the squared distance with fused multiply-adds
  * (7 operations per point pair) and stores every row's approximate minimum there; the finishing kernel

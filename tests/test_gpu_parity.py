@@ -176,7 +176,7 @@ def test_boolean_tensor_core_counts_equal_popcount_counts(tpw, monkeypatch, shap
     assert _abi.lib.tpw_bool_metric_tc_eligible(1, 1000, 1100, 250) == 0     # rows not 16-byte aligned
 
 
-@pytest.mark.parametrize("d", [1, 3, 4, 7, 8])
+@pytest.mark.parametrize("d", [1, 3, 4, 7, 8, 11, 16])
 def test_hausdorff_fused_loop_equals_exact_loop(tpw, monkeypatch, d):
     """The hot loop that forms squared distances with fused multiply-adds and refines the few rows near the maximum
     returns the same bits -- values and both index tensors -- as evaluating every point pair in the reference's
@@ -208,9 +208,9 @@ def test_hausdorff_fused_loop_equals_exact_loop(tpw, monkeypatch, d):
                 assert np.array_equal(res[0][1].cpu().numpy(), i_ref) and np.array_equal(res[0][2].cpu().numpy(), j_ref)
 
 
-@pytest.mark.parametrize("d", [1, 3, 8])
+@pytest.mark.parametrize("d", [1, 3, 8, 12])
 def test_hausdorff_float64_streamed_equals_one_cta_per_pair(tpw, monkeypatch, d):
-    """float64 clouds of up to eight coordinates take the streamed kernels (row minima in scratch, one scan per
+    """float64 clouds of up to sixteen coordinates take the streamed kernels (row minima in scratch, one scan per
     set pair); values and both index tensors equal the one-CTA-per-pair kernel's and the oracle's bit for bit,
     also where most rows tie and with a caller-chosen visiting order."""
     g = torch.Generator().manual_seed(70 + d)

@@ -1,7 +1,7 @@
 // Directed Hausdorff distance between point sets, fused so that the [M1, M2] distance matrix is
 // never written.
 //
-// Fast path (float32, D <= 8): a CTA of 256 threads owns 1024 points of x1 for one set pair;
+// Fast path (float32, D <= 16): a CTA of 256 threads owns 1024 points of x1 for one set pair;
 // each thread keeps four of them in registers and streams the whole x2 cloud through shared
 // memory (one broadcast 128-bit load per x2 point, two for D > 4, feeds four point pairs).  Only the running row
 // minimum is kept in the hot loop.  Row minima are packed as (float bits << 32 | visiting
@@ -66,11 +66,14 @@ struct HdParams {
     long long mtiles;
 };
 
-// An upper bound on the relative difference between the fused and the separately rounded sum of D <= 8 squares
+// An upper bound on the relative difference between the fused and the separately rounded sum of up to 8 squares
 // (each is within D roundings of the real sum, all terms non-negative), with room to spare; below kTiny the
 // relative bound gives way to an absolute one (products that underflow).
 constexpr float kFusedSlack = 3.8146973e-6f;   // 2^-18
 constexpr float kTiny = 1e-35f;
+// 9 to 16 squares: (3 D - 1) roundings of 2^-24 between the two sums stay below 2^-17
+template <int D> __device__ __forceinline__ constexpr float fused_slack() { return D <= 8 ? kFusedSlack : 2.f * kFusedSlack; }
+constexpr int kMaxFastD = 16;                  // widest point the streamed kernels are instantiated for
 
 // keys[pair] = max over m of (bits(rowmin) << 32 | position(m)).  FUSED: the distance is formed with fused
 // multiply-adds and every row's minimum is also stored for the refining kernel.
@@ -240,7 +243,7 @@ hausdorff_refine_kernel(const HdParams P) {
     // tie at 0 and the last visited one, which the key already names, wins.  Otherwise a row can hold the exact
     // maximum only if its approximate minimum is within the rounding slack of the largest approximate minimum.
     const bool all_zero = amax == 0.f;
-    const float lower = amax * (1.f - kFusedSlack) - kTiny;
+    const float lower = amax * (1.f - fused_slack<D>()) - kTiny;
 
     unsigned long long wrow = 0ull, wn = ~0ull;   // best (bits(min) << 32 | position(m)) of this warp, its n key
     long long wm = -1;
@@ -308,7 +311,7 @@ hausdorff_refine_kernel(const HdParams P) {
     }
 }
 
-// ---- float64, D <= 8: the same streaming design ------------------------------------------------------------------------
+// ---- float64, D <= 16: the same streaming design ------------------------------------------------------------------------
 // A 64-bit distance leaves no room for the visiting position in a 64-bit key, so every row's exact minimum is stored
 // (8 bytes per x1 point in the caller's scratch) and one CTA per set pair then scans them: largest minimum, last
 // visited row on ties, and for that row the first visited x2 point that attains it.  Products and sums are rounded
@@ -567,7 +570,7 @@ extern "C" int tpw_hausdorff_forward(int dtype, const void *x1, const void *x2,
     P.keys = reinterpret_cast<unsigned long long *>(scratch);
     P.B = B; P.N1 = N1; P.N2 = N2; P.M1 = M1; P.M2 = M2; P.D = D;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == TPW_F32 && D <= 8) {
+    if (dtype == TPW_F32 && D <= kMaxFastD) {
         TPW_CHECK_ARG(scratch != nullptr, "tpw_hausdorff_forward: scratch is NULL");
         TPW_CHECK_ARG((reinterpret_cast<uintptr_t>(scratch) & 7u) == 0, "tpw_hausdorff_forward: scratch must be 8-byte aligned");
         if (!getenv("TPW_HAUSDORFF_EXACT_LOOP")) P.rowmins = reinterpret_cast<float *>(P.keys + pairs);
@@ -579,10 +582,18 @@ extern "C" int tpw_hausdorff_forward(int dtype, const void *x1, const void *x2,
             case 5: return launch_fast<5>(P, s);
             case 6: return launch_fast<6>(P, s);
             case 7: return launch_fast<7>(P, s);
-            default: return launch_fast<8>(P, s);
+            case 8: return launch_fast<8>(P, s);
+            case 9: return launch_fast<9>(P, s);
+            case 10: return launch_fast<10>(P, s);
+            case 11: return launch_fast<11>(P, s);
+            case 12: return launch_fast<12>(P, s);
+            case 13: return launch_fast<13>(P, s);
+            case 14: return launch_fast<14>(P, s);
+            case 15: return launch_fast<15>(P, s);
+            default: return launch_fast<16>(P, s);
         }
     }
-    if (dtype == TPW_F64 && D <= 8 && scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 7u) == 0 &&
+    if (dtype == TPW_F64 && D <= kMaxFastD && scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 7u) == 0 &&
         !getenv("TPW_HAUSDORFF_PLAIN_F64")) {
         P.rowmins = reinterpret_cast<float *>(P.keys + pairs);   // used as double[pairs * M1]
         switch (D) {
@@ -593,7 +604,15 @@ extern "C" int tpw_hausdorff_forward(int dtype, const void *x1, const void *x2,
             case 5: return launch_f64<5>(P, s);
             case 6: return launch_f64<6>(P, s);
             case 7: return launch_f64<7>(P, s);
-            default: return launch_f64<8>(P, s);
+            case 8: return launch_f64<8>(P, s);
+            case 9: return launch_f64<9>(P, s);
+            case 10: return launch_f64<10>(P, s);
+            case 11: return launch_f64<11>(P, s);
+            case 12: return launch_f64<12>(P, s);
+            case 13: return launch_f64<13>(P, s);
+            case 14: return launch_f64<14>(P, s);
+            case 15: return launch_f64<15>(P, s);
+            default: return launch_f64<16>(P, s);
         }
     }
     if (dtype == TPW_F32) hausdorff_plain_kernel<float><<<(unsigned)pairs, kThreads, 0, s>>>(P);
@@ -708,7 +727,7 @@ extern "C" int tpw_hausdorff_forward_static(int dtype, const void *x1, const voi
     P.idx2 = reinterpret_cast<long long *>(idx2);
     P.B = B; P.N1 = N1; P.N2 = N2; P.M1 = M1; P.M2 = M2; P.D = D;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == TPW_F32 && D <= 8) {
+    if (dtype == TPW_F32 && D <= kMaxFastD) {
         int st = resolve_static_keys(&P.keys);
         if (st != TPW_OK) return st;
         // launch_fast clears the first `pairs` keys on the stream before the kernels use them; without room for
@@ -721,7 +740,15 @@ extern "C" int tpw_hausdorff_forward_static(int dtype, const void *x1, const voi
             case 5: return launch_fast<5>(P, s);
             case 6: return launch_fast<6>(P, s);
             case 7: return launch_fast<7>(P, s);
-            default: return launch_fast<8>(P, s);
+            case 8: return launch_fast<8>(P, s);
+            case 9: return launch_fast<9>(P, s);
+            case 10: return launch_fast<10>(P, s);
+            case 11: return launch_fast<11>(P, s);
+            case 12: return launch_fast<12>(P, s);
+            case 13: return launch_fast<13>(P, s);
+            case 14: return launch_fast<14>(P, s);
+            case 15: return launch_fast<15>(P, s);
+            default: return launch_fast<16>(P, s);
         }
     }
     // the one-CTA-per-pair kernel keeps its state in shared memory and needs no scratch at all

@@ -150,7 +150,12 @@ lp_backward_onepass_kernel(const __grid_constant__ CUtensorMap map_x2, const __g
         const float *ys = reinterpret_cast<const float *>(base + 2 * OP_G_BYTES);
         // every thread is done with the other buffer and with the coefficient tile: refill, then wait for this stage
         if (__syncthreads_or(failed)) {
-            if (tid == 0 && P.status) atomicCAS(P.status, 0, (2 << 16) | 3);
+            if (tid == 0) {
+                if (P.status) atomicCAS(P.status, 0, (2 << 16) | 3);
+                // this stage's copy was issued an iteration ago and may still be landing: the CTA stays until it has
+                // (again with a bound), so that no copy writes into shared memory the CTA has given back
+                mbar_wait_bounded(&full[stage], (uint32_t)((t / OP_STAGES) & 1));
+            }
             return;
         }
         if (tid == 0 && t + 1 < nchunks) issue(t + 1);

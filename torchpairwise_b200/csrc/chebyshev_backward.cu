@@ -131,7 +131,11 @@ chebyshev_match_kernel(const __grid_constant__ CUtensorMap map1, const __grid_co
         int stage;
         if (USE_TMA) {
             if (__syncthreads_or(failed)) {
-                if (tid == 0 && P.status) atomicCAS(P.status, 0, (9 << 16) | 1);
+                if (tid == 0) {
+                    if (P.status) atomicCAS(P.status, 0, (9 << 16) | 1);
+                    // the chunks issued earlier may still be landing: the CTA stays (bounded) until they have
+                    for (int c = t; c < t + kStages - 1 && c < nchunks; ++c) mbar_wait_bounded(&full[c % kStages], (uint32_t)((c / kStages) & 1));
+                }
                 return;
             }
             const int nxt = t + kStages - 1;

@@ -171,7 +171,11 @@ lp_backward_kernel(const __grid_constant__ CUtensorMap map_stream, const __grid_
 
         if (USE_TMA) {
             if (__syncthreads_or(failed)) {
-                if (tid == 0 && P.status) atomicCAS(P.status, 0, (2 << 16) | 1);
+                if (tid == 0) {
+                    if (P.status) atomicCAS(P.status, 0, (2 << 16) | 1);
+                    // the chunks issued earlier may still be landing: the CTA stays (bounded) until they have
+                    for (int c = t; c < t + kStages - 1 && c < nchunks; ++c) mbar_wait_bounded(&full[c % kStages], (uint32_t)((c / kStages) & 1));
+                }
                 return;
             }
             if (tid == 0 && t + kStages - 1 < nchunks) issue(t + kStages - 1);

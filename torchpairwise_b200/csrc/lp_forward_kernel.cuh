@@ -313,7 +313,12 @@ lp_forward_kernel(const __grid_constant__ CUtensorMap map1, const __grid_constan
         if (USE_TMA) {
             // Everyone has finished chunk t-1, so its stage may be refilled with chunk t+kStages-1.
             if (__syncthreads_or(failed)) {
-                if (tid == 0 && P.status) atomicCAS(P.status, 0, (1 << 16) | 1);
+                if (tid == 0) {
+                    if (P.status) atomicCAS(P.status, 0, (1 << 16) | 1);
+                    // chunks t and t + 1 were issued earlier and may still be landing: the CTA stays (bounded) until
+                    // they have, so that no copy writes into shared memory the CTA has given back
+                    for (int c = t; c < t + kStages - 1 && c < nchunks; ++c) mbar_wait_bounded(&full[c % kStages], (uint32_t)((c / kStages) & 1));
+                }
                 return;
             }
             const int nxt = t + kStages - 1;

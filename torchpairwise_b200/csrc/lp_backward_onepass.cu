@@ -53,7 +53,6 @@ struct OnePassParams {
     float q;
     int pow_spec;
     float post;
-    int coef_mode;
     double qd;
     int *status;
 };
@@ -68,11 +67,14 @@ __device__ __forceinline__ float onepass_term(float x, float y, float c, float q
     return c * (d * fabsf(d));
 }
 
-template <int PHI, bool NEED_AUX>
+// COEF: how the coefficient of a pair is formed from the gradient and the auxiliary tile (COEF_G: the gradient itself, no
+// auxiliary tile is loaded); a compile-time constant, so that the coefficient pass holds one formula
+template <int PHI, int COEF>
 __global__ void __launch_bounds__(OP_THREADS, 1)
 lp_backward_onepass_kernel(const __grid_constant__ CUtensorMap map_x2, const __grid_constant__ CUtensorMap map_grad,
                            const __grid_constant__ CUtensorMap map_aux, const OnePassParams P) {
     constexpr bool PACKED = (PHI == PHI_DABS || PHI == PHI_D);
+    constexpr bool NEED_AUX = (COEF != COEF_G);
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + OP_OFF_BAR);
@@ -170,10 +172,10 @@ lp_backward_onepass_kernel(const __grid_constant__ CUtensorMap map_x2, const __g
             float4 g = *reinterpret_cast<const float4 *>(base + off);
             if (NEED_AUX) {
                 const float4 o = *reinterpret_cast<const float4 *>(base + OP_G_BYTES + off);
-                g.x = bwd_coefficient<float>(P.coef_mode, g.x, o.x, P.qd);
-                g.y = bwd_coefficient<float>(P.coef_mode, g.y, o.y, P.qd);
-                g.z = bwd_coefficient<float>(P.coef_mode, g.z, o.z, P.qd);
-                g.w = bwd_coefficient<float>(P.coef_mode, g.w, o.w, P.qd);
+                g.x = bwd_coefficient<float>(COEF, g.x, o.x, P.qd);
+                g.y = bwd_coefficient<float>(COEF, g.y, o.y, P.qd);
+                g.z = bwd_coefficient<float>(COEF, g.z, o.z, P.qd);
+                g.w = bwd_coefficient<float>(COEF, g.w, o.w, P.qd);
             }
             float *dst = ct + (chunk * 4) * OP_ROWS + t_row;
             dst[0] = g.x; dst[OP_ROWS] = g.y; dst[2 * OP_ROWS] = g.z; dst[3 * OP_ROWS] = g.w;
@@ -310,7 +312,7 @@ lp_backward_onepass_sum_kernel(const float *partial, float *g2, const float *w, 
 
 constexpr long long kScratchCap = 2ll << 30;
 
-template <int PHI, bool NEED_AUX>
+template <int PHI, int COEF>
 int launch_onepass(OnePassParams P, const void *grad, const void *aux, float *g2, void *scratch, long long scratch_bytes,
                    cudaStream_t stream) {
     CUtensorMap mx, mg, ma;
@@ -319,11 +321,11 @@ int launch_onepass(OnePassParams P, const void *grad, const void *aux, float *g2
     if (st != TPW_OK) return st;
     st = make_tensor_map_3d(&mg, grad, 4, P.N2, P.N1, P.B, OP_JT, OP_ROWS, true);
     if (st != TPW_OK) return st;
-    if (NEED_AUX) {
+    if (COEF != COEF_G) {
         st = make_tensor_map_3d(&ma, aux, 4, P.N2, P.N1, P.B, OP_JT, OP_ROWS, true);
         if (st != TPW_OK) return st;
     }
-    auto kern = lp_backward_onepass_kernel<PHI, NEED_AUX>;
+    auto kern = lp_backward_onepass_kernel<PHI, COEF>;
     TPW_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, OP_ALLOC));
     const long long nblk = (P.N1 + OP_ROWS - 1) / OP_ROWS;
     const long long slab = P.N2 * P.D * 4;                    // bytes of scratch per (batch, row block)
@@ -387,28 +389,25 @@ int lp_backward_onepass(int mode, const void *grad, const void *aux, const void 
     P.q = (float)(p - 1.0);
     P.pow_spec = make_pow_spec(p - 1.0);
     P.post = 1.f;
-    P.coef_mode = COEF_G;
     float *g2 = reinterpret_cast<float *>(grad_x2);
     switch (mode) {
         case TPW_LP_BWD_CDIST:
-            if (p == 1.0) return launch_onepass<PHI_SGN, false>(P, grad, nullptr, g2, scratch, scratch_bytes, stream);
-            if (p == 2.0) { P.coef_mode = COEF_DIV_O; return launch_onepass<PHI_D, true>(P, grad, aux, g2, scratch, scratch_bytes, stream); }
-            if (p == 3.0) { P.coef_mode = COEF_DIV_O2; return launch_onepass<PHI_DABS, true>(P, grad, aux, g2, scratch, scratch_bytes, stream); }
-            P.coef_mode = COEF_DIV_POW;
-            return launch_onepass<PHI_SGNPOW, true>(P, grad, aux, g2, scratch, scratch_bytes, stream);
+            if (p == 1.0) return launch_onepass<PHI_SGN, COEF_G>(P, grad, nullptr, g2, scratch, scratch_bytes, stream);
+            if (p == 2.0) return launch_onepass<PHI_D, COEF_DIV_O>(P, grad, aux, g2, scratch, scratch_bytes, stream);
+            if (p == 3.0) return launch_onepass<PHI_DABS, COEF_DIV_O2>(P, grad, aux, g2, scratch, scratch_bytes, stream);
+            return launch_onepass<PHI_SGNPOW, COEF_DIV_POW>(P, grad, aux, g2, scratch, scratch_bytes, stream);
         case TPW_LP_BWD_PPMINKOWSKI:
             P.post = (float)p;
-            if (p == 1.0) return launch_onepass<PHI_SGN, false>(P, grad, nullptr, g2, scratch, scratch_bytes, stream);
-            if (p == 2.0) return launch_onepass<PHI_D, false>(P, grad, nullptr, g2, scratch, scratch_bytes, stream);
-            if (p == 3.0) return launch_onepass<PHI_DABS, false>(P, grad, nullptr, g2, scratch, scratch_bytes, stream);
-            return launch_onepass<PHI_SGNPOW, false>(P, grad, nullptr, g2, scratch, scratch_bytes, stream);
+            if (p == 1.0) return launch_onepass<PHI_SGN, COEF_G>(P, grad, nullptr, g2, scratch, scratch_bytes, stream);
+            if (p == 2.0) return launch_onepass<PHI_D, COEF_G>(P, grad, nullptr, g2, scratch, scratch_bytes, stream);
+            if (p == 3.0) return launch_onepass<PHI_DABS, COEF_G>(P, grad, nullptr, g2, scratch, scratch_bytes, stream);
+            return launch_onepass<PHI_SGNPOW, COEF_G>(P, grad, nullptr, g2, scratch, scratch_bytes, stream);
         case TPW_LP_BWD_WMINKOWSKI:
-            P.coef_mode = COEF_MUL;
             P.w = reinterpret_cast<const float *>(w);
-            if (p == 1.0) return launch_onepass<PHI_SGN, true>(P, grad, aux, g2, scratch, scratch_bytes, stream);
-            if (p == 2.0) return launch_onepass<PHI_D, true>(P, grad, aux, g2, scratch, scratch_bytes, stream);
-            if (p == 3.0) return launch_onepass<PHI_DABS, true>(P, grad, aux, g2, scratch, scratch_bytes, stream);
-            return launch_onepass<PHI_SGNPOW, true>(P, grad, aux, g2, scratch, scratch_bytes, stream);
+            if (p == 1.0) return launch_onepass<PHI_SGN, COEF_MUL>(P, grad, aux, g2, scratch, scratch_bytes, stream);
+            if (p == 2.0) return launch_onepass<PHI_D, COEF_MUL>(P, grad, aux, g2, scratch, scratch_bytes, stream);
+            if (p == 3.0) return launch_onepass<PHI_DABS, COEF_MUL>(P, grad, aux, g2, scratch, scratch_bytes, stream);
+            return launch_onepass<PHI_SGNPOW, COEF_MUL>(P, grad, aux, g2, scratch, scratch_bytes, stream);
         default:
             return fail(TPW_ERR_INVALID, "lp backward: unknown mode %d", mode);
     }

@@ -22,6 +22,8 @@
 #include <math.h>
 #include <stdlib.h>
 
+#include <type_traits>
+
 namespace tpw {
 namespace {
 
@@ -199,19 +201,19 @@ lp_backward_kernel(const __grid_constant__ CUtensorMap map_stream, const __grid_
         }
 
         if (NEED_AUX) {
-            // coefficient tile in place: c = f(g, aux)
-            for (int e = tid; e < SC * TR; e += kThreads) {
-                const T g = gs[e], o = as[e];
-                T c;
-                switch (P.coef_mode) {
-                    case COEF_DIV_O: c = o == T(0) ? T(0) : b_div(g, o); break;
-                    case COEF_DIV_O2: c = o == T(0) ? T(0) : b_div(g, o * o); break;
-                    case COEF_DIV_POW: c = o == T(0) ? T(0) : b_div(g, b_pow(o, P.q)); break;
-                    case COEF_MUL: c = g * o; break;
-                    case COEF_ZERO_WHERE_O0: c = o == T(0) ? T(0) : g; break;
-                    default: c = g; break;
-                }
-                gs[e] = c;
+            // coefficient tile in place: c = f(g, aux).  The formula is picked once per stage, outside the element loop:
+            // picked per element, the compiler keeps every candidate formula in the loop body.
+            auto coefficients = [&](auto mode_tag) {
+                constexpr int MODE = decltype(mode_tag)::value;
+                for (int e = tid; e < SC * TR; e += kThreads) gs[e] = bwd_coefficient<T>(MODE, gs[e], as[e], P.q);
+            };
+            switch (P.coef_mode) {
+                case COEF_DIV_O: coefficients(std::integral_constant<int, COEF_DIV_O>{}); break;
+                case COEF_DIV_O2: coefficients(std::integral_constant<int, COEF_DIV_O2>{}); break;
+                case COEF_DIV_POW: coefficients(std::integral_constant<int, COEF_DIV_POW>{}); break;
+                case COEF_MUL: coefficients(std::integral_constant<int, COEF_MUL>{}); break;
+                case COEF_ZERO_WHERE_O0: coefficients(std::integral_constant<int, COEF_ZERO_WHERE_O0>{}); break;
+                default: break;
             }
             __syncthreads();
         }

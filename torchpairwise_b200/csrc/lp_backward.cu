@@ -318,27 +318,43 @@ __global__ void __launch_bounds__(256) lp_backward_small_kernel(const BwdParams 
     // eight streamed rows at a time: all their loads are issued before the first term is added (the terms are still
     // added in ascending order, so the sum keeps the tile kernel's bits); a walk that waits for each row's loads in
     // turn is bound by their latency
-    constexpr int U = 8;
-    long long s = 0;
-    for (; s + U <= P.NS; s += U) {
-        T g[U], o[U], y[U];
+    // The coefficient formula is picked once, outside the walk (picked per element, every candidate stays in the loop).
+    auto walk = [&](auto mode_tag) {
+        constexpr int MODE = decltype(mode_tag)::value;
+        constexpr int U = 8;
+        long long s = 0;
+        for (; s + U <= P.NS; s += U) {
+            T g[U], o[U], y[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            g[u] = grad[g0 + (s + u) * gstep];
-            o[u] = NEED_AUX ? aux[g0 + (s + u) * gstep] : T(0);
-            y[u] = stream[(s + u) * P.D];
-        }
+            for (int u = 0; u < U; ++u) {
+                g[u] = grad[g0 + (s + u) * gstep];
+                o[u] = NEED_AUX ? aux[g0 + (s + u) * gstep] : T(0);
+                y[u] = stream[(s + u) * P.D];
+            }
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const T c = NEED_AUX ? bwd_coefficient<T>(P.coef_mode, g[u], o[u], P.q) : g[u];
-            bwd_accumulate<PHI, T>(acc, x, y[u], c, o[u], q, P.pow_spec);
+            for (int u = 0; u < U; ++u) {
+                const T c = NEED_AUX ? bwd_coefficient<T>(MODE, g[u], o[u], P.q) : g[u];
+                bwd_accumulate<PHI, T>(acc, x, y[u], c, o[u], q, P.pow_spec);
+            }
         }
-    }
-    for (; s < P.NS; ++s) {
-        const T g = grad[g0 + s * gstep];
-        const T o = NEED_AUX ? aux[g0 + s * gstep] : T(0);
-        const T c = NEED_AUX ? bwd_coefficient<T>(P.coef_mode, g, o, P.q) : g;
-        bwd_accumulate<PHI, T>(acc, x, stream[s * P.D], c, o, q, P.pow_spec);
+        for (; s < P.NS; ++s) {
+            const T g = grad[g0 + s * gstep];
+            const T o = NEED_AUX ? aux[g0 + s * gstep] : T(0);
+            const T c = NEED_AUX ? bwd_coefficient<T>(MODE, g, o, P.q) : g;
+            bwd_accumulate<PHI, T>(acc, x, stream[s * P.D], c, o, q, P.pow_spec);
+        }
+    };
+    if (!NEED_AUX) {
+        walk(std::integral_constant<int, COEF_G>{});
+    } else {
+        switch (P.coef_mode) {
+            case COEF_DIV_O: walk(std::integral_constant<int, COEF_DIV_O>{}); break;
+            case COEF_DIV_O2: walk(std::integral_constant<int, COEF_DIV_O2>{}); break;
+            case COEF_DIV_POW: walk(std::integral_constant<int, COEF_DIV_POW>{}); break;
+            case COEF_MUL: walk(std::integral_constant<int, COEF_MUL>{}); break;
+            case COEF_ZERO_WHERE_O0: walk(std::integral_constant<int, COEF_ZERO_WHERE_O0>{}); break;
+            default: walk(std::integral_constant<int, COEF_G>{}); break;
+        }
     }
     T v = acc * (T)P.post;
     if (P.w) v *= reinterpret_cast<const T *>(P.w)[b * P.D + k];
